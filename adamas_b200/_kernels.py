@@ -1,0 +1,347 @@
+"""Operator module with the surface of the reference's pybind extension ``adamas._kernels``
+(adamas/ops/csrc/bsk_ops.cu:4-21, declarations adamas/ops/csrc/bsk_ops.h:23-124).
+
+Same function names, argument order and meaning, and the same error behaviour (bad shapes,
+dtypes or devices raise ``RuntimeError``, as ``TORCH_CHECK`` does).  Each function checks its
+tensors and hands raw device pointers to the C ABI in ``libadamas_b200.so``; torch is used for
+memory and streams only.  All launches go to torch's current CUDA stream.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import lib
+
+NHD, HND = 0, 1
+DEFAULT_THRESHOLDS = (-10.0, 0.0, 10.0)
+
+
+# ----------------------------------------------------------------------------------------------
+# checks (the reference's CHECK_INPUT / CHECK_DIM / CHECK_EQ, pytorch_extension_utils.h:52-66)
+# ----------------------------------------------------------------------------------------------
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _check_input(t: torch.Tensor, name: str, dim: Optional[int] = None) -> None:
+    _require(isinstance(t, torch.Tensor), f"{name} must be a tensor")
+    _require(t.is_cuda, f"{name} must be a CUDA tensor")
+    _require(t.is_contiguous(), f"{name} must be contiguous")
+    if dim is not None:
+        _require(t.dim() == dim, f"{name} must be a {dim}D tensor")
+
+
+def _check_rows(t: torch.Tensor, name: str) -> None:
+    """2-D CUDA tensor whose rows are dense; the row stride may exceed the row length or be 0
+    (one row shared by all heads)."""
+    _require(isinstance(t, torch.Tensor) and t.is_cuda, f"{name} must be a CUDA tensor")
+    _require(t.dim() == 2, f"{name} must be a 2D tensor")
+    _require(t.size(1) <= 1 or t.stride(1) == 1, f"{name} must have unit stride along its rows")
+    _require(t.size(0) <= 1 or t.stride(0) == 0 or t.stride(0) >= t.size(1), f"{name} has overlapping rows")
+
+
+def _dtype_code(dtype: torch.dtype, what: str) -> int:
+    if dtype == torch.float16:
+        return _lib.F16
+    if dtype == torch.bfloat16:
+        return _lib.BF16
+    raise RuntimeError(f"{what} failed to dispatch with dtype {dtype}")
+
+
+def _value_format(dtype: torch.dtype, what: str) -> int:
+    if dtype == torch.float16:
+        return _lib.VAL_F16
+    if dtype in (torch.int16, torch.uint16):
+        return _lib.VAL_U16
+    raise RuntimeError(f"{what} failed to dispatch with dtype {dtype}")
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _nhd_only(layout: int) -> None:
+    _require(int(layout) == NHD, "only the NHD layout is implemented (the reference's controller always uses it)")
+
+
+# ----------------------------------------------------------------------------------------------
+# stage 1
+# ----------------------------------------------------------------------------------------------
+def hadamard_transform(x: torch.Tensor, inplace: bool = False, scale: Optional[float] = None) -> torch.Tensor:
+    """Stand-in for ``faster_hadamard_transform.hadamard_transform`` (call sites
+    adamas/models/Adamas.py:120,150): Walsh-Hadamard transform of the last dimension (128),
+    scaled by 1/sqrt(128) unless `scale` is given, result in x.dtype."""
+    _check_input(x, "x")
+    _require(x.size(-1) == 128, "hadamard_transform supports a last dimension of 128")
+    y = x if inplace else torch.empty_like(x)
+    rows = x.numel() // 128
+    s = 1.0 / math.sqrt(128.0) if scale is None else float(scale)
+    _lib.check(lib.adamas_hadamard_transform(_ptr(x), _ptr(y), rows, 128, s,
+                                             _dtype_code(x.dtype, "hadamard_transform"), _stream()),
+               "hadamard_transform")
+    return y
+
+
+def bucketize_pack(h: torch.Tensor, o: torch.Tensor, thresholds=None) -> None:
+    """o[..., w] = packed 2-bit buckets of h[..., 8w:8w+8] (kernels/include/decode/decode_page.cuh:380-398)."""
+    _check_input(h, "h")
+    _check_input(o, "o")
+    _require(h.size(-1) == 128 and o.size(-1) == 16, "h must end in 128 and o in 16")
+    _require(o.element_size() == 2 and o.numel() * 8 == h.numel(), "o must hold one 16-bit word per 8 values")
+    _lib.check(lib.adamas_bucketize_pack(_ptr(h), _ptr(o), h.numel() // 128, 128, _lib.thresholds_arg(thresholds),
+                                         _dtype_code(h.dtype, "bucketize_pack"), _stream()), "bucketize_pack")
+
+
+def _check_append(k, v, kv_data, kv_indices, hadamard_data, hadamard_indices, layout):
+    _nhd_only(layout)
+    _check_input(k, "k", 3)
+    _check_input(v, "v", 3)
+    _check_input(kv_data, "kv_data", 5)
+    _check_input(kv_indices, "kv_indices", 1)
+    _check_input(hadamard_data, "hadamard_data", 5)
+    _check_input(hadamard_indices, "hadamard_indices", 1)
+    _require(kv_indices.dtype == torch.int32, "kv_indices must be int32")
+    _require(hadamard_indices.dtype == torch.int32, "hadamard_indices must be int32")
+    num_heads, head_dim = k.size(1), k.size(2)
+    _require(tuple(v.shape) == tuple(k.shape), "k and v must have the same shape")
+    page_size = kv_data.size(2)
+    _require(kv_data.size(1) == 2 and kv_data.size(3) == num_heads and kv_data.size(4) == head_dim,
+             "kv_data must be [pages, 2, page_size, num_heads, head_dim]")
+    _require(hadamard_data.size(1) == 1 and hadamard_data.size(2) == page_size
+             and hadamard_data.size(3) == num_heads and hadamard_data.size(4) == head_dim // 8,
+             "hadamard_data must be [pages, 1, page_size, num_heads, head_dim/8]")
+    _require(kv_data.dtype == k.dtype and v.dtype == k.dtype, "k, v and kv_data must share a dtype")
+    _require(hadamard_data.element_size() == 2, "hadamard_data must have 16-bit elements")
+    return num_heads, head_dim, page_size
+
+
+def append_kv_cache_decode(k, v, h, o, kv_data, kv_indices, kv_indptr, kv_last_page_len, kv_last_page_idx,
+                           hadamard_data, hadamard_indices, hadamard_indptr, hadamard_last_page_len,
+                           hadamard_last_page_idx, layout, thresholds=None) -> None:
+    """adamas/ops/csrc/page.cu:6-109.  k, v [1,H,D]; h [2,H,D] = Hadamard(q), Hadamard(k);
+    o [1,H,D/8] receives the packed query code.  The indptr tensors are [0, len(indices)]."""
+    num_heads, head_dim, page_size = _check_append(k, v, kv_data, kv_indices, hadamard_data, hadamard_indices, layout)
+    _check_input(h, "h", 3)
+    _check_input(o, "o", 3)
+    _require(k.size(0) == 1 and v.size(0) == 1 and h.size(0) == 2 and o.size(0) == 1, "decode appends one token")
+    _require(h.size(1) == num_heads and h.size(2) == head_dim and h.dtype == k.dtype, "h must be [2, H, D] in k.dtype")
+    _require(o.size(1) == num_heads and o.size(2) == head_dim // 8 and o.element_size() == 2, "o must be [1, H, D/8] 16-bit")
+    _lib.check(lib.adamas_append_decode(
+        _ptr(k), _ptr(v), _ptr(h), _ptr(o),
+        _ptr(kv_data), _ptr(kv_indices), kv_indices.numel(), int(kv_last_page_len),
+        _ptr(hadamard_data), _ptr(hadamard_indices), hadamard_indices.numel(), int(hadamard_last_page_len),
+        num_heads, head_dim, page_size, _lib.thresholds_arg(thresholds),
+        _dtype_code(k.dtype, "Append_kv_cache_decode"), _stream()), "Append_kv_cache_decode")
+
+
+def append_kv_cache_decode_fused(q, k, v, o, kv_data, kv_indices, kv_last_page_len, hadamard_data,
+                                 hadamard_indices, hadamard_last_page_len, layout=NHD, scale=None,
+                                 thresholds=None) -> None:
+    """One launch for torch.cat((q, k)) + hadamard_transform + append_kv_cache_decode
+    (adamas/models/Adamas.py:145-161)."""
+    num_heads, head_dim, page_size = _check_append(k, v, kv_data, kv_indices, hadamard_data, hadamard_indices, layout)
+    _check_input(q, "q", 3)
+    _check_input(o, "o", 3)
+    _require(tuple(q.shape) == tuple(k.shape) and q.dtype == k.dtype and k.size(0) == 1, "q, k, v must be [1, H, D]")
+    _require(o.size(1) == num_heads and o.size(2) == head_dim // 8 and o.element_size() == 2, "o must be [1, H, D/8] 16-bit")
+    s = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)
+    _lib.check(lib.adamas_append_decode_fused(
+        _ptr(q), _ptr(k), _ptr(v), _ptr(o),
+        _ptr(kv_data), _ptr(kv_indices), kv_indices.numel(), int(kv_last_page_len),
+        _ptr(hadamard_data), _ptr(hadamard_indices), hadamard_indices.numel(), int(hadamard_last_page_len),
+        num_heads, head_dim, page_size, s, _lib.thresholds_arg(thresholds),
+        _dtype_code(k.dtype, "append_kv_cache_decode_fused"), _stream()), "append_kv_cache_decode_fused")
+
+
+def append_kv_cache_prefill(k, v, h, kv_data, kv_indices, kv_indptr, kv_last_page_len, kv_last_page_idx,
+                            hadamard_data, hadamard_indices, hadamard_indptr, hadamard_last_page_len,
+                            hadamard_last_page_idx, layout, scale=None, thresholds=None) -> None:
+    """adamas/ops/csrc/page.cu:111-226.  k, v, h [N,H,D]; h = Hadamard(k).  Passing h=None
+    computes the transform inside the same launch."""
+    num_heads, head_dim, page_size = _check_append(k, v, kv_data, kv_indices, hadamard_data, hadamard_indices, layout)
+    if h is not None:
+        _check_input(h, "h", 3)
+        _require(tuple(h.shape) == tuple(k.shape) and h.dtype == k.dtype, "h must match k")
+    s = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)
+    _lib.check(lib.adamas_append_prefill(
+        _ptr(k), _ptr(v), _ptr(h), k.size(0),
+        _ptr(kv_data), _ptr(kv_indices), kv_indices.numel(), int(kv_last_page_len),
+        _ptr(hadamard_data), _ptr(hadamard_indices), hadamard_indices.numel(), int(hadamard_last_page_len),
+        num_heads, head_dim, page_size, s, _lib.thresholds_arg(thresholds),
+        _dtype_code(k.dtype, "Append_kv_cache_prefill"), _stream()), "Append_kv_cache_prefill")
+
+
+# ----------------------------------------------------------------------------------------------
+# stage 2
+# ----------------------------------------------------------------------------------------------
+def estimate_attn_score(q, o, metadata_data, metadata_indices, metadata_indptr, metadata_last_page_len,
+                        metadata_last_page_idx, layout, metric: str = "l1") -> None:
+    """adamas/ops/csrc/estimate.cu:6-84.  q [1,H,D/8] packed query code; o [H, n] with
+    n = (pages-1)*page_size + last_page_len - 1 (newest token excluded); o.dtype float16 stores the
+    distances as fp16 (reference), int16 as integers."""
+    _nhd_only(layout)
+    _check_input(q, "q", 3)
+    _check_rows(o, "o")
+    _check_input(metadata_data, "hadamard_data", 5)
+    _check_input(metadata_indices, "hadamard_indices", 1)
+    _require(q.size(0) == 1, "q.size(0) must be 1")
+    _require(metadata_indices.dtype == torch.int32, "hadamard_indices must be int32")
+    num_heads, code_words = q.size(1), q.size(2)
+    page_size = metadata_data.size(2)
+    _require(metadata_data.size(3) == num_heads and metadata_data.size(4) == code_words and code_words == 16,
+             "hadamard_data must be [pages, 1, page_size, num_heads, 16]")
+    _require(q.element_size() == 2 and metadata_data.element_size() == 2, "codes must be 16-bit words")
+    n = (metadata_indices.numel() - 1) * page_size + int(metadata_last_page_len) - 1
+    _require(o.size(0) == num_heads and o.size(1) == n, f"o must be [{num_heads}, {n}]")
+    _lib.check(lib.adamas_estimate(
+        _ptr(q), _ptr(metadata_data), _ptr(metadata_indices), metadata_indices.numel(),
+        int(metadata_last_page_len), page_size, num_heads, code_words * 8, _ptr(o), o.stride(0),
+        _value_format(o.dtype, "Estimate_attn_score"),
+        {"l1": _lib.METRIC_L1, "xor": _lib.METRIC_XOR}[metric], _stream()), "Estimate_attn_score")
+
+
+# ----------------------------------------------------------------------------------------------
+# stage 3
+# ----------------------------------------------------------------------------------------------
+def topk_filtering(estimated_value, estimated_indices, d_out, indices_out, buf, page_budget) -> None:
+    """adamas/ops/csrc/topk.cu:7-46.  Selects the `page_budget` smallest entries of every row of
+    estimated_value [H, n] and writes their values to d_out [H, k] and the matching entries of
+    estimated_indices [H, n] to indices_out [H, k].  `buf` (the reference's radix scratch) is
+    accepted and unused.  Unlike the reference the result is deterministic: equal values are taken
+    lowest position first and rows are emitted in ascending position order."""
+    _check_rows(estimated_value, "estimated_value")
+    _check_rows(estimated_indices, "estimated_indices")
+    _check_rows(d_out, "d_out")
+    _check_rows(indices_out, "indices_out")
+    _require(d_out.stride(0) == indices_out.stride(0), "d_out and indices_out must share a row stride")
+    rows, n = estimated_value.shape
+    k = int(page_budget)
+    _require(tuple(estimated_indices.shape) == (rows, n), "estimated_indices must match estimated_value")
+    _require(estimated_indices.dtype == torch.int32 and indices_out.dtype == torch.int32, "indices must be int32")
+    _require(n >= k, "num_pages must be >= page_budget")
+    _require(d_out.size(1) == k and indices_out.size(1) == k, "outputs must have page_budget columns")
+    _require(d_out.size(0) == rows and indices_out.size(0) == rows, "outputs must have one row per head")
+    _require(d_out.dtype == estimated_value.dtype, "d_out must have the dtype of estimated_value")
+    _lib.check(lib.adamas_topk(
+        _ptr(estimated_value), _value_format(estimated_value.dtype, "Top-k filtering"), estimated_value.stride(0), n,
+        _ptr(estimated_indices), estimated_indices.stride(0), 1, rows, k,
+        _ptr(d_out), _ptr(indices_out), indices_out.stride(0), _stream()), "Top-k filtering")
+
+
+def topk_select(values, k, indices_out, values_out=None, page_table=None, page_size=1) -> None:
+    """Token-granular select used when page_size > 1: positions p of the k smallest values per row
+    are mapped through one page table shared by all rows, out = page_table[p // page_size] *
+    page_size + p % page_size (or p itself when page_table is None)."""
+    _check_rows(values, "values")
+    _check_rows(indices_out, "indices_out")
+    rows, n = values.shape
+    _require(indices_out.dtype == torch.int32 and indices_out.size(0) == rows and indices_out.size(1) >= k,
+             "indices_out must be int32 [rows, >=k]")
+    if values_out is not None:
+        _check_rows(values_out, "values_out")
+        _require(values_out.dtype == values.dtype and values_out.stride(0) == indices_out.stride(0),
+                 "values_out must match values.dtype and the row stride of indices_out")
+    if page_table is not None:
+        _check_input(page_table, "page_table", 1)
+        _require(page_table.dtype == torch.int32 and page_table.numel() * page_size >= n, "page_table too short")
+    _lib.check(lib.adamas_topk(
+        _ptr(values), _value_format(values.dtype, "topk_select"), values.stride(0), n,
+        _ptr(page_table), 0, int(page_size), rows, int(k),
+        _ptr(values_out), _ptr(indices_out), indices_out.stride(0), _stream()), "topk_select")
+
+
+# ----------------------------------------------------------------------------------------------
+# stage 4
+# ----------------------------------------------------------------------------------------------
+class BatchDecodeWithPagedKVCachePyTorchWrapper:
+    """adamas/ops/csrc/bsk_ops.h:95-124, adamas/ops/csrc/approx_attn.cu:27-151."""
+
+    def __init__(self, layout: int):
+        _nhd_only(layout)
+        self._layout = int(layout)
+        self._handle = ctypes.c_void_p()
+        _lib.check(lib.adamas_decode_handler_create(ctypes.byref(self._handle)), "BatchDecodeWithPagedKVCache")
+        self._started = False
+        self._planned_tokens = 0
+        self._cfg = None
+
+    def __del__(self):
+        h = getattr(self, "_handle", None)
+        if h:
+            lib.adamas_decode_handler_destroy(h)
+            self._handle = None
+
+    def begin_forward(self, indptr, num_qo_heads, num_kv_heads, head_dim, page_size, empty_data) -> None:
+        _require(indptr.dim() == 1 and indptr.dtype == torch.int32 and indptr.is_contiguous(),
+                 "indptr must be a contiguous 1D int32 tensor")
+        _require(num_qo_heads == num_kv_heads, "grouped-query attention is not supported (the reference asserts MHA)")
+        self._cfg = (int(num_qo_heads), int(head_dim), int(page_size),
+                     _dtype_code(empty_data.dtype, "BatchDecodeWithPagedKVCache"))
+        self._started = True
+        self._planned_tokens = 0   # scratch is sized on the first forward, from the index tensor
+
+    def end_forward(self) -> None:
+        self._started = False
+        _lib.check(lib.adamas_decode_end_forward(self._handle), "BatchDecodeWithPagedKVCache")
+
+    def forward(self, q, o, paged_kv_data, paged_kv_indices, paged_kv_indptr, paged_kv_last_page_len,
+                paged_kv_last_page_idx, rope_scale=1.0, rope_theta=1e4, token_granular: bool = False,
+                lse: Optional[torch.Tensor] = None) -> None:
+        """q, o [1,H,D]; paged_kv_indices [H, n] per-head page ids (the reference's meaning: each
+        page is attended in full, then the last page's last_page_len entries).  With
+        token_granular=True the entries are physical token slots (page*page_size + entry) and only
+        the newest token is appended."""
+        if not self._started:
+            raise RuntimeError("BatchDecodeWithPagedKVCache failed with error: forward called before begin_forward")
+        _check_input(q, "q", 3)
+        _check_input(o, "o", 3)
+        _check_input(paged_kv_data, "paged_kv_data", 5)
+        _check_rows(paged_kv_indices, "paged_kv_indices")
+        num_heads, head_dim, page_size, dt = self._cfg
+        _require(q.size(0) == 1 and q.size(1) == num_heads and q.size(2) == head_dim, "q must be [1, H, D]")
+        _require(tuple(o.shape) == tuple(q.shape) and o.dtype == q.dtype, "o must match q")
+        _require(paged_kv_data.size(1) == 2 and paged_kv_data.size(2) == page_size
+                 and paged_kv_data.size(3) == num_heads and paged_kv_data.size(4) == head_dim,
+                 "paged_kv_data must be [pages, 2, page_size, H, D]")
+        _require(paged_kv_indices.size(0) == num_heads and paged_kv_indices.dtype == torch.int32,
+                 "paged_kv_indices must be int32 [H, n]")
+        _require(_dtype_code(q.dtype, "BatchDecodeWithPagedKVCache") == dt and paged_kv_data.dtype == q.dtype,
+                 "dtype differs from begin_forward")
+        n_idx = paged_kv_indices.size(1)
+        unit = 1 if token_granular else page_size
+        tail = 1 if token_granular else int(paged_kv_last_page_len)
+        n_tokens = n_idx * unit + tail
+        if n_tokens > self._planned_tokens:
+            _lib.check(lib.adamas_decode_begin_forward(self._handle, n_tokens, num_heads, head_dim, page_size, dt,
+                                                       _stream()), "BatchDecodeWithPagedKVCache")
+            self._planned_tokens = n_tokens
+        if lse is not None:
+            _require(lse.is_cuda and lse.dtype == torch.float32 and lse.numel() == num_heads and lse.is_contiguous(),
+                     "lse must be a contiguous float32 CUDA tensor of H elements")
+        _lib.check(lib.adamas_decode_forward(
+            self._handle, _ptr(q), _ptr(o), _ptr(lse), _ptr(paged_kv_data), _ptr(paged_kv_indices),
+            paged_kv_indices.stride(0), n_idx, unit, int(paged_kv_last_page_idx), int(paged_kv_last_page_len), tail,
+            1.0 / math.sqrt(head_dim), _stream()), "BatchDecodeWithPagedKVCache")
+
+
+def merge_states(o_parts: torch.Tensor, lse_parts: torch.Tensor, o: torch.Tensor,
+                 lse: Optional[torch.Tensor] = None) -> None:
+    """o_parts [P,H,D] fp32 normalised partial outputs, lse_parts [P,H] base-2 -> o [H,D] (or [1,H,D])."""
+    _check_input(o_parts, "o_parts", 3)
+    _check_input(lse_parts, "lse_parts", 2)
+    _check_input(o, "o")
+    p, h, d = o_parts.shape
+    _require(o_parts.dtype == torch.float32 and lse_parts.dtype == torch.float32, "partials must be float32")
+    _require(tuple(lse_parts.shape) == (p, h) and o.numel() == h * d, "shape mismatch")
+    _lib.check(lib.adamas_merge_states(_ptr(o_parts), _ptr(lse_parts), p, h, d, _ptr(o), _ptr(lse),
+                                       _dtype_code(o.dtype, "merge_states"), _stream()), "merge_states")

@@ -1,0 +1,490 @@
+// C ABI of the B200 Adamas decode path (see include/adamas_b200.h for the contract of every
+// entry point and the reference interface each one replaces).  Host side only: argument checks,
+// launch geometry, error reporting.  Kernels live in the .cuh files next to this one.
+#include "../../include/adamas_b200.h"
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "common.cuh"
+#include "estimate.cuh"
+#include "hadamard_append.cuh"
+#include "sparse_decode.cuh"
+#include "topk.cuh"
+
+using namespace adamas;
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define ADAMAS_REQUIRE(cond, ...) \
+  do {                            \
+    if (!(cond)) return fail(ADAMAS_ERR_INVALID, __VA_ARGS__); \
+  } while (0)
+
+#define ADAMAS_CUDA(expr)                                                                   \
+  do {                                                                                      \
+    cudaError_t e_ = (expr);                                                                \
+    if (e_ != cudaSuccess)                                                                  \
+      return fail(ADAMAS_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e_));         \
+  } while (0)
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(ADAMAS_ERR_CUDA, "%s launch failed: %s", what, cudaGetErrorString(e));
+  return ADAMAS_OK;
+}
+
+inline cudaStream_t to_stream(adamas_stream_t s) { return static_cast<cudaStream_t>(s); }
+
+Thresholds make_thresholds(const float* t) {
+  Thresholds th;
+  if (t) {
+    th.t0 = t[0]; th.t1 = t[1]; th.t2 = t[2];
+  } else {
+    th.t0 = -10.f; th.t1 = 0.f; th.t2 = 10.f;
+  }
+  return th;
+}
+
+int check_common(int num_heads, int head_dim, int page_size, int dtype) {
+  ADAMAS_REQUIRE(head_dim == kHeadDim, "head_dim must be 128 (got %d)", head_dim);
+  ADAMAS_REQUIRE(num_heads >= 1 && num_heads <= 1024, "num_heads out of range (%d)", num_heads);
+  ADAMAS_REQUIRE(page_size >= 1, "page_size must be >= 1 (got %d)", page_size);
+  ADAMAS_REQUIRE(dtype == ADAMAS_F16 || dtype == ADAMAS_BF16, "unsupported dtype %d", dtype);
+  return ADAMAS_OK;
+}
+
+inline unsigned rows_to_blocks(int64_t rows) { return static_cast<unsigned>((rows * 16 + 255) / 256); }
+
+}  // namespace
+
+extern "C" {
+
+int adamas_abi_version(void) { return ADAMAS_ABI_VERSION; }
+const char* adamas_last_error(void) { return g_err; }
+
+// ---------------------------------------------------------------------------------------------
+int adamas_hadamard_transform(const void* x, void* y, int64_t rows, int head_dim, float scale,
+                              int dtype, adamas_stream_t stream) {
+  ADAMAS_REQUIRE(head_dim == kHeadDim, "head_dim must be 128 (got %d)", head_dim);
+  ADAMAS_REQUIRE(dtype == ADAMAS_F16 || dtype == ADAMAS_BF16, "unsupported dtype %d", dtype);
+  ADAMAS_REQUIRE(rows >= 0, "rows must be >= 0");
+  if (rows == 0) return ADAMAS_OK;
+  ADAMAS_REQUIRE(x && y, "null pointer");
+  ADAMAS_REQUIRE(rows < (int64_t(1) << 31) * 16, "too many rows");
+  const unsigned blocks = rows_to_blocks(rows);
+  if (dtype == ADAMAS_F16)
+    hadamard_kernel<__half><<<blocks, 256, 0, to_stream(stream)>>>(
+        static_cast<const __half*>(x), static_cast<__half*>(y), rows, scale);
+  else
+    hadamard_kernel<__nv_bfloat16><<<blocks, 256, 0, to_stream(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), rows, scale);
+  return check_launch("hadamard_kernel");
+}
+
+int adamas_bucketize_pack(const void* h, void* codes, int64_t rows, int head_dim,
+                          const float* thresholds3_host, int dtype, adamas_stream_t stream) {
+  ADAMAS_REQUIRE(head_dim == kHeadDim, "head_dim must be 128 (got %d)", head_dim);
+  ADAMAS_REQUIRE(dtype == ADAMAS_F16 || dtype == ADAMAS_BF16, "unsupported dtype %d", dtype);
+  ADAMAS_REQUIRE(rows >= 0, "rows must be >= 0");
+  if (rows == 0) return ADAMAS_OK;
+  ADAMAS_REQUIRE(h && codes, "null pointer");
+  const Thresholds th = make_thresholds(thresholds3_host);
+  const unsigned blocks = rows_to_blocks(rows);
+  if (dtype == ADAMAS_F16)
+    bucketize_pack_kernel<__half><<<blocks, 256, 0, to_stream(stream)>>>(
+        static_cast<const __half*>(h), static_cast<uint16_t*>(codes), rows, th);
+  else
+    bucketize_pack_kernel<__nv_bfloat16><<<blocks, 256, 0, to_stream(stream)>>>(
+        static_cast<const __nv_bfloat16*>(h), static_cast<uint16_t*>(codes), rows, th);
+  return check_launch("bucketize_pack_kernel");
+}
+
+static int append_decode_impl(const void* k, const void* v, const void* qh, const void* kh, bool fused,
+                              void* q_code_out, void* kv_data, const int32_t* kv_page_table,
+                              int kv_num_pages, int kv_last_page_len, void* code_data,
+                              const int32_t* code_page_table, int code_num_pages,
+                              int code_last_page_len, int num_heads, int head_dim, int page_size,
+                              float scale, const float* thresholds3_host, int dtype,
+                              adamas_stream_t stream) {
+  if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
+  ADAMAS_REQUIRE(k && v && qh && kh && q_code_out && kv_data && code_data && kv_page_table &&
+                     code_page_table, "null pointer");
+  ADAMAS_REQUIRE(kv_num_pages >= 1 && code_num_pages >= 1, "page tables must not be empty");
+  ADAMAS_REQUIRE(kv_last_page_len >= 1 && kv_last_page_len <= page_size, "kv_last_page_len out of range");
+  ADAMAS_REQUIRE(code_last_page_len >= 1 && code_last_page_len <= page_size,
+                 "code_last_page_len out of range");
+  PagedTarget tgt{kv_data, kv_page_table, static_cast<uint16_t*>(code_data), code_page_table, page_size,
+                  num_heads};
+  const Thresholds th = make_thresholds(thresholds3_host);
+  const unsigned blocks = rows_to_blocks(num_heads);
+  cudaStream_t st = to_stream(stream);
+#define LAUNCH_AD(T, F)                                                                         \
+  append_decode_kernel<T, F><<<blocks, 256, 0, st>>>(                                           \
+      static_cast<const T*>(k), static_cast<const T*>(v), static_cast<const T*>(qh),            \
+      static_cast<const T*>(kh), static_cast<uint16_t*>(q_code_out), tgt, kv_num_pages - 1,     \
+      kv_last_page_len - 1, code_num_pages - 1, code_last_page_len - 1, scale, th)
+  if (dtype == ADAMAS_F16) {
+    if (fused) LAUNCH_AD(__half, true); else LAUNCH_AD(__half, false);
+  } else {
+    if (fused) LAUNCH_AD(__nv_bfloat16, true); else LAUNCH_AD(__nv_bfloat16, false);
+  }
+#undef LAUNCH_AD
+  return check_launch("append_decode_kernel");
+}
+
+int adamas_append_decode(const void* k, const void* v, const void* h, void* q_code_out, void* kv_data,
+                         const int32_t* kv_page_table, int kv_num_pages, int kv_last_page_len,
+                         void* code_data, const int32_t* code_page_table, int code_num_pages,
+                         int code_last_page_len, int num_heads, int head_dim, int page_size,
+                         const float* thresholds3_host, int dtype, adamas_stream_t stream) {
+  ADAMAS_REQUIRE(h, "null pointer");
+  ADAMAS_REQUIRE(num_heads >= 1, "num_heads out of range");
+  const size_t row_bytes = static_cast<size_t>(num_heads) * kHeadDim * 2;
+  return append_decode_impl(k, v, h, static_cast<const uint8_t*>(h) + row_bytes, false, q_code_out,
+                            kv_data, kv_page_table, kv_num_pages, kv_last_page_len, code_data,
+                            code_page_table, code_num_pages, code_last_page_len, num_heads, head_dim,
+                            page_size, 1.f, thresholds3_host, dtype, stream);
+}
+
+int adamas_append_decode_fused(const void* q, const void* k, const void* v, void* q_code_out,
+                               void* kv_data, const int32_t* kv_page_table, int kv_num_pages,
+                               int kv_last_page_len, void* code_data,
+                               const int32_t* code_page_table, int code_num_pages,
+                               int code_last_page_len, int num_heads, int head_dim, int page_size,
+                               float scale, const float* thresholds3_host, int dtype,
+                               adamas_stream_t stream) {
+  return append_decode_impl(k, v, q, k, true, q_code_out, kv_data, kv_page_table, kv_num_pages,
+                            kv_last_page_len, code_data, code_page_table, code_num_pages,
+                            code_last_page_len, num_heads, head_dim, page_size, scale,
+                            thresholds3_host, dtype, stream);
+}
+
+int adamas_append_prefill(const void* k, const void* v, const void* h, int64_t n_tokens, void* kv_data,
+                          const int32_t* kv_page_table, int kv_num_pages, int kv_last_page_len,
+                          void* code_data, const int32_t* code_page_table, int code_num_pages,
+                          int code_last_page_len, int num_heads, int head_dim, int page_size,
+                          float scale, const float* thresholds3_host, int dtype,
+                          adamas_stream_t stream) {
+  if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
+  ADAMAS_REQUIRE(n_tokens >= 0, "n_tokens must be >= 0");
+  if (n_tokens == 0) return ADAMAS_OK;
+  ADAMAS_REQUIRE(k && v && kv_data && code_data && kv_page_table && code_page_table, "null pointer");
+  ADAMAS_REQUIRE(kv_num_pages >= 1 && code_num_pages >= 1, "page tables must not be empty");
+  ADAMAS_REQUIRE(kv_last_page_len >= 1 && kv_last_page_len <= page_size, "kv_last_page_len out of range");
+  ADAMAS_REQUIRE(code_last_page_len >= 1 && code_last_page_len <= page_size,
+                 "code_last_page_len out of range");
+  const int64_t seq_len = static_cast<int64_t>(kv_num_pages - 1) * page_size + kv_last_page_len;
+  const int64_t code_len = static_cast<int64_t>(code_num_pages - 1) * page_size + code_last_page_len;
+  ADAMAS_REQUIRE(seq_len == code_len, "KV cache holds %lld tokens but the code cache %lld",
+                 static_cast<long long>(seq_len), static_cast<long long>(code_len));
+  ADAMAS_REQUIRE(n_tokens <= seq_len, "n_tokens (%lld) exceeds the sequence length (%lld)",
+                 static_cast<long long>(n_tokens), static_cast<long long>(seq_len));
+  const int64_t rows = n_tokens * num_heads;
+  ADAMAS_REQUIRE(rows < (int64_t(1) << 31) * 16, "too many rows");
+  PagedTarget tgt{kv_data, kv_page_table, static_cast<uint16_t*>(code_data), code_page_table, page_size,
+                  num_heads};
+  const Thresholds th = make_thresholds(thresholds3_host);
+  const unsigned blocks = rows_to_blocks(rows);
+  const int64_t start = seq_len - n_tokens;
+  cudaStream_t st = to_stream(stream);
+#define LAUNCH_AP(T, F)                                                                            \
+  append_prefill_kernel<T, F><<<blocks, 256, 0, st>>>(static_cast<const T*>(k),                    \
+                                                      static_cast<const T*>(v),                    \
+                                                      static_cast<const T*>(h), rows, start, tgt,  \
+                                                      scale, th)
+  if (dtype == ADAMAS_F16) {
+    if (h) LAUNCH_AP(__half, false); else LAUNCH_AP(__half, true);
+  } else {
+    if (h) LAUNCH_AP(__nv_bfloat16, false); else LAUNCH_AP(__nv_bfloat16, true);
+  }
+#undef LAUNCH_AP
+  return check_launch("append_prefill_kernel");
+}
+
+// ---------------------------------------------------------------------------------------------
+int adamas_estimate(const void* q_code, const void* code_data, const int32_t* code_page_table,
+                    int code_num_pages, int code_last_page_len, int page_size, int num_heads,
+                    int head_dim, void* out, int64_t out_stride, int out_format, int metric,
+                    adamas_stream_t stream) {
+  if (int rc = check_common(num_heads, head_dim, page_size, ADAMAS_F16)) return rc;
+  ADAMAS_REQUIRE(code_num_pages >= 1, "page table must not be empty");
+  ADAMAS_REQUIRE(code_last_page_len >= 1 && code_last_page_len <= page_size,
+                 "code_last_page_len out of range");
+  ADAMAS_REQUIRE(out_format == ADAMAS_VAL_F16 || out_format == ADAMAS_VAL_U16, "bad out_format %d",
+                 out_format);
+  ADAMAS_REQUIRE(metric == ADAMAS_METRIC_L1 || metric == ADAMAS_METRIC_XOR, "bad metric %d", metric);
+  const int64_t n64 = static_cast<int64_t>(code_num_pages - 1) * page_size + code_last_page_len - 1;
+  ADAMAS_REQUIRE(n64 < (int64_t(1) << 31) - kEstTile, "sequence too long");
+  const int n = static_cast<int>(n64);
+  if (n == 0) return ADAMAS_OK;
+  ADAMAS_REQUIRE(q_code && code_data && code_page_table && out, "null pointer");
+  ADAMAS_REQUIRE(out_stride >= n, "out_stride (%lld) smaller than the row length (%d)",
+                 static_cast<long long>(out_stride), n);
+  ADAMAS_REQUIRE((reinterpret_cast<uintptr_t>(q_code) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(code_data) & 15) == 0,
+                 "q_code and code_data must be 16-byte aligned");
+  const unsigned blocks = (n + kEstTile - 1) / kEstTile;
+  const size_t smem = static_cast<size_t>(num_heads) * (kEstTile + 2) * sizeof(uint16_t);
+  ADAMAS_REQUIRE(smem <= 48 * 1024, "num_heads too large for the estimate kernel");
+  cudaStream_t st = to_stream(stream);
+  const uint4* codes = static_cast<const uint4*>(code_data);
+  const uint4* qc = static_cast<const uint4*>(q_code);
+#define LAUNCH_EST(M, OT)                                                                   \
+  estimate_kernel<M, OT><<<blocks, kEstThreads, smem, st>>>(codes, code_page_table, qc,      \
+                                                            static_cast<OT*>(out), out_stride, n, \
+                                                            num_heads, page_size)
+  if (metric == ADAMAS_METRIC_L1) {
+    if (out_format == ADAMAS_VAL_F16) LAUNCH_EST(0, __half); else LAUNCH_EST(0, uint16_t);
+  } else {
+    if (out_format == ADAMAS_VAL_F16) LAUNCH_EST(1, __half); else LAUNCH_EST(1, uint16_t);
+  }
+#undef LAUNCH_EST
+  return check_launch("estimate_kernel");
+}
+
+// ---------------------------------------------------------------------------------------------
+int adamas_topk(const void* values, int value_format, int64_t value_stride, int n,
+                const int32_t* in_idx, int64_t in_idx_stride, int idx_page_size, int num_rows, int k,
+                void* out_values, int32_t* out_idx, int64_t out_stride, adamas_stream_t stream) {
+  ADAMAS_REQUIRE(value_format == ADAMAS_VAL_F16 || value_format == ADAMAS_VAL_U16,
+                 "bad value_format %d", value_format);
+  ADAMAS_REQUIRE(num_rows >= 0, "num_rows must be >= 0");
+  if (num_rows == 0) return ADAMAS_OK;
+  ADAMAS_REQUIRE(values && out_idx, "null pointer");
+  ADAMAS_REQUIRE(n >= 1 && n < (1 << 30), "n out of range (%d)", n);
+  ADAMAS_REQUIRE(k >= 1 && k <= n, "k must satisfy 1 <= k <= n (k=%d, n=%d)", k, n);
+  ADAMAS_REQUIRE(value_stride >= n || num_rows == 1, "value_stride smaller than n");
+  ADAMAS_REQUIRE(out_stride >= k || num_rows == 1, "out_stride smaller than k");
+  ADAMAS_REQUIRE(idx_page_size >= 1, "idx_page_size must be >= 1");
+  ADAMAS_REQUIRE((reinterpret_cast<uintptr_t>(values) & 1) == 0, "values must be 2-byte aligned");
+  // stage the row in shared memory when it fits (one extra granule for a misaligned row start)
+  static int max_smem = -1;
+  if (max_smem < 0) {
+    int dev = 0, v = 0;
+    ADAMAS_CUDA(cudaGetDevice(&dev));
+    ADAMAS_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    ADAMAS_CUDA(cudaFuncSetAttribute(topk_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     v - 4096));
+    ADAMAS_CUDA(cudaFuncSetAttribute(topk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     v - 4096));
+    max_smem = v - 4096;
+  }
+  const int granules = (n + 7) / 8 + 1;
+  int smem_granules = 0;
+  size_t smem = 0;
+  if (static_cast<size_t>(granules) * 16 <= static_cast<size_t>(max_smem)) {
+    smem_granules = granules;
+    smem = static_cast<size_t>(granules) * 16;
+  }
+  cudaStream_t st = to_stream(stream);
+  const uint16_t* vals = static_cast<const uint16_t*>(values);
+  uint16_t* ov = static_cast<uint16_t*>(out_values);
+  if (value_format == ADAMAS_VAL_F16)
+    topk_kernel<0><<<num_rows, kTopkThreads, smem, st>>>(vals, value_stride, n, in_idx, in_idx_stride,
+                                                         idx_page_size, k, ov, out_idx, out_stride,
+                                                         smem_granules);
+  else
+    topk_kernel<1><<<num_rows, kTopkThreads, smem, st>>>(vals, value_stride, n, in_idx, in_idx_stride,
+                                                         idx_page_size, k, ov, out_idx, out_stride,
+                                                         smem_granules);
+  return check_launch("topk_kernel");
+}
+
+// ---------------------------------------------------------------------------------------------
+struct adamas_decode_handler {
+  void* scratch = nullptr;        // partial_o | partial_ml | counters
+  size_t scratch_bytes = 0;
+  int64_t cap_units = 0;          // H * max_splits the scratch was sized for
+  int cap_heads = 0;
+  int num_sms = 0;
+  int device = -1;
+  bool forward_started = false;
+  int num_heads = 0, page_size = 0, dtype = 0;
+  bool smem_configured = false;
+};
+
+namespace {
+
+struct SplitPlan {
+  int tiles_per_block;
+  int num_splits;
+};
+
+// Aim at ~4 resident blocks per SM over all heads; never more splits than tiles.
+SplitPlan plan_splits(int64_t n_tokens, int num_heads, int num_sms) {
+  const int64_t tiles = (n_tokens + kDecTile - 1) / kDecTile;
+  int64_t want = (static_cast<int64_t>(num_sms) * 4 + num_heads - 1) / num_heads;
+  if (want < 1) want = 1;
+  if (want > tiles) want = tiles;
+  SplitPlan p;
+  p.tiles_per_block = static_cast<int>((tiles + want - 1) / want);
+  p.num_splits = static_cast<int>((tiles + p.tiles_per_block - 1) / p.tiles_per_block);
+  return p;
+}
+
+size_t scratch_layout(int64_t units, int heads, size_t* off_ml, size_t* off_cnt) {
+  size_t o = static_cast<size_t>(units) * kHeadDim * sizeof(float);
+  *off_ml = o;
+  o += static_cast<size_t>(units) * 2 * sizeof(float);
+  o = (o + 255) & ~static_cast<size_t>(255);
+  *off_cnt = o;
+  o += static_cast<size_t>(heads) * sizeof(unsigned);
+  return (o + 255) & ~static_cast<size_t>(255);
+}
+
+}  // namespace
+
+int adamas_decode_handler_create(adamas_decode_handler_t** handler) {
+  ADAMAS_REQUIRE(handler, "null pointer");
+  adamas_decode_handler* h = new (std::nothrow) adamas_decode_handler();
+  ADAMAS_REQUIRE(h, "out of host memory");
+  *handler = h;
+  return ADAMAS_OK;
+}
+
+int adamas_decode_handler_destroy(adamas_decode_handler_t* handler) {
+  if (!handler) return ADAMAS_OK;
+  if (handler->scratch) cudaFree(handler->scratch);
+  delete handler;
+  return ADAMAS_OK;
+}
+
+int adamas_decode_begin_forward(adamas_decode_handler_t* handler, int64_t max_tokens, int num_heads,
+                                int head_dim, int page_size, int dtype, adamas_stream_t stream) {
+  ADAMAS_REQUIRE(handler, "null handler");
+  if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
+  ADAMAS_REQUIRE(max_tokens >= 1 && max_tokens < (int64_t(1) << 31) - kDecTile, "max_tokens out of range");
+  int dev = 0;
+  ADAMAS_CUDA(cudaGetDevice(&dev));
+  if (handler->device != dev) {
+    ADAMAS_REQUIRE(handler->scratch == nullptr, "handler was planned on another device");
+    ADAMAS_CUDA(cudaDeviceGetAttribute(&handler->num_sms, cudaDevAttrMultiProcessorCount, dev));
+    handler->device = dev;
+  }
+  if (!handler->smem_configured) {
+    ADAMAS_CUDA(cudaFuncSetAttribute(sparse_decode_kernel<__half>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kDecStageBytes));
+    ADAMAS_CUDA(cudaFuncSetAttribute(sparse_decode_kernel<__nv_bfloat16>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kDecStageBytes));
+    handler->smem_configured = true;
+  }
+  const SplitPlan p = plan_splits(max_tokens, num_heads, handler->num_sms);
+  const int64_t units = static_cast<int64_t>(num_heads) * p.num_splits;
+  if (units > handler->cap_units || num_heads > handler->cap_heads) {
+    size_t off_ml, off_cnt;
+    const int64_t new_units = units > handler->cap_units ? units : handler->cap_units;
+    const int new_heads = num_heads > handler->cap_heads ? num_heads : handler->cap_heads;
+    const size_t bytes = scratch_layout(new_units, new_heads, &off_ml, &off_cnt);
+    if (handler->scratch) {
+      // earlier launches on this stream may still use the old buffer
+      ADAMAS_CUDA(cudaStreamSynchronize(to_stream(stream)));
+      ADAMAS_CUDA(cudaFree(handler->scratch));
+      handler->scratch = nullptr;
+      handler->cap_units = 0;
+      handler->cap_heads = 0;
+    }
+    ADAMAS_CUDA(cudaMalloc(&handler->scratch, bytes));
+    ADAMAS_CUDA(cudaMemsetAsync(handler->scratch, 0, bytes, to_stream(stream)));
+    handler->scratch_bytes = bytes;
+    handler->cap_units = new_units;
+    handler->cap_heads = new_heads;
+  }
+  handler->forward_started = true;
+  handler->num_heads = num_heads;
+  handler->page_size = page_size;
+  handler->dtype = dtype;
+  return ADAMAS_OK;
+}
+
+int adamas_decode_end_forward(adamas_decode_handler_t* handler) {
+  ADAMAS_REQUIRE(handler, "null handler");
+  handler->forward_started = false;
+  return ADAMAS_OK;
+}
+
+int adamas_decode_forward(adamas_decode_handler_t* handler, const void* q, void* o, float* lse,
+                          const void* kv_data, const int32_t* indices, int64_t idx_stride, int n_idx,
+                          int idx_unit, int last_page_idx, int last_page_len, int tail_len,
+                          float sm_scale, adamas_stream_t stream) {
+  ADAMAS_REQUIRE(handler, "null handler");
+  if (!handler->forward_started)
+    return fail(ADAMAS_ERR_STATE, "decode forward called before begin_forward");
+  ADAMAS_REQUIRE(q && o && kv_data, "null pointer");
+  ADAMAS_REQUIRE(n_idx >= 0 && (n_idx == 0 || indices), "indices missing");
+  const int ps = handler->page_size;
+  ADAMAS_REQUIRE(idx_unit == 1 || idx_unit == ps, "idx_unit must be 1 or page_size");
+  ADAMAS_REQUIRE(tail_len >= 0 && tail_len <= last_page_len && last_page_len <= ps,
+                 "tail_len / last_page_len out of range");
+  ADAMAS_REQUIRE(last_page_idx >= 0, "last_page_idx must be >= 0");
+  const int64_t n_tokens = static_cast<int64_t>(n_idx) * idx_unit + tail_len;
+  ADAMAS_REQUIRE(n_tokens >= 1, "nothing to attend to");
+  ADAMAS_REQUIRE(n_tokens < (int64_t(1) << 31) - kDecTile, "too many tokens");
+  ADAMAS_REQUIRE(idx_stride == 0 || idx_stride >= n_idx || handler->num_heads == 1,
+                 "idx_stride must be 0 (shared row) or >= n_idx");
+  const int H = handler->num_heads;
+  const SplitPlan p = plan_splits(n_tokens, H, handler->num_sms);
+  if (static_cast<int64_t>(H) * p.num_splits > handler->cap_units)
+    return fail(ADAMAS_ERR_STATE,
+                "decode forward needs %d splits per head but begin_forward planned for fewer tokens",
+                p.num_splits);
+  size_t off_ml, off_cnt;
+  scratch_layout(handler->cap_units, handler->cap_heads, &off_ml, &off_cnt);
+  DecodeParams prm;
+  prm.q = q;
+  prm.o = o;
+  prm.lse = lse;
+  prm.kv = kv_data;
+  prm.indices = indices ? indices : reinterpret_cast<const int32_t*>(kv_data);
+  prm.idx_stride = idx_stride;
+  prm.n_idx = n_idx;
+  prm.idx_unit = idx_unit;
+  prm.page_size = ps;
+  prm.H = H;
+  prm.tail_slot0 = static_cast<int64_t>(last_page_idx) * ps + (last_page_len - tail_len);
+  prm.n_tokens = static_cast<int>(n_tokens);
+  prm.tiles_per_block = p.tiles_per_block;
+  prm.num_splits = p.num_splits;
+  uint8_t* base = static_cast<uint8_t*>(handler->scratch);
+  prm.partial_o = reinterpret_cast<float*>(base);
+  prm.partial_ml = reinterpret_cast<float*>(base + off_ml);
+  prm.counters = reinterpret_cast<unsigned*>(base + off_cnt);
+  prm.scale_log2 = sm_scale * 1.4426950408889634f;
+  const size_t smem = static_cast<size_t>(p.tiles_per_block > 1 ? 2 : 1) * kDecStageBytes;
+  dim3 grid(p.num_splits, H);
+  if (handler->dtype == ADAMAS_F16)
+    sparse_decode_kernel<__half><<<grid, kDecThreads, smem, to_stream(stream)>>>(prm);
+  else
+    sparse_decode_kernel<__nv_bfloat16><<<grid, kDecThreads, smem, to_stream(stream)>>>(prm);
+  return check_launch("sparse_decode_kernel");
+}
+
+int adamas_merge_states(const float* o_parts, const float* lse_parts, int num_parts, int num_heads,
+                        int head_dim, void* o, float* lse, int dtype, adamas_stream_t stream) {
+  ADAMAS_REQUIRE(head_dim == kHeadDim, "head_dim must be 128 (got %d)", head_dim);
+  ADAMAS_REQUIRE(dtype == ADAMAS_F16 || dtype == ADAMAS_BF16, "unsupported dtype %d", dtype);
+  ADAMAS_REQUIRE(num_parts >= 1 && num_heads >= 1, "num_parts and num_heads must be >= 1");
+  ADAMAS_REQUIRE(o_parts && lse_parts && o, "null pointer");
+  if (dtype == ADAMAS_F16)
+    merge_states_kernel<__half><<<num_heads, kHeadDim, 0, to_stream(stream)>>>(
+        o_parts, lse_parts, num_parts, num_heads, static_cast<__half*>(o), lse);
+  else
+    merge_states_kernel<__nv_bfloat16><<<num_heads, kHeadDim, 0, to_stream(stream)>>>(
+        o_parts, lse_parts, num_parts, num_heads, static_cast<__nv_bfloat16*>(o), lse);
+  return check_launch("merge_states_kernel");
+}
+
+}  // extern "C"

@@ -1,0 +1,86 @@
+// Shared device helpers for the Adamas decode-path kernels (sm_100a only).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace adamas {
+
+constexpr int kHeadDim = 128;           // the only head dimension the path supports
+constexpr int kCodeWords = kHeadDim / 8;  // 16-bit words per (token, head) code = 32 bytes
+
+// ---- 16-byte global loads / stores ---------------------------------------------------------
+// Streaming read of data that is read once (code cache): bypass L1 allocation.
+__device__ __forceinline__ uint4 ld_stream_16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 ld_16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ void st_16(void* p, uint4 v) { *reinterpret_cast<uint4*>(p) = v; }
+
+// ---- cp.async (16 B, L2 only) --------------------------------------------------------------
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
+  unsigned s = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem_src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N));
+}
+
+// ---- element conversion: 8 x 16-bit storage <-> 8 x fp32 -----------------------------------
+template <typename T>
+struct Elem;
+template <>
+struct Elem<__half> {
+  static __device__ __forceinline__ float2 to_f2(uint32_t u) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&u));
+  }
+  static __device__ __forceinline__ uint32_t from_f2(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  static __device__ __forceinline__ float round(float a) { return __half2float(__float2half_rn(a)); }
+};
+template <>
+struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float2 to_f2(uint32_t u) {
+    // bf16 -> fp32 is a 16-bit shift
+    return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+  }
+  static __device__ __forceinline__ uint32_t from_f2(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+  static __device__ __forceinline__ float round(float a) {
+    return __bfloat162float(__float2bfloat16_rn(a));
+  }
+};
+
+template <typename T>
+__device__ __forceinline__ void unpack8(uint4 v, float (&x)[8]) {
+  float2 a = Elem<T>::to_f2(v.x), b = Elem<T>::to_f2(v.y), c = Elem<T>::to_f2(v.z),
+         d = Elem<T>::to_f2(v.w);
+  x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+  x[4] = c.x; x[5] = c.y; x[6] = d.x; x[7] = d.y;
+}
+template <typename T>
+__device__ __forceinline__ uint4 pack8(const float (&x)[8]) {
+  uint4 v;
+  v.x = Elem<T>::from_f2(x[0], x[1]);
+  v.y = Elem<T>::from_f2(x[2], x[3]);
+  v.z = Elem<T>::from_f2(x[4], x[5]);
+  v.w = Elem<T>::from_f2(x[6], x[7]);
+  return v;
+}
+
+struct Thresholds {
+  float t0, t1, t2;
+};
+
+}  // namespace adamas

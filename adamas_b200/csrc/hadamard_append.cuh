@@ -1,0 +1,184 @@
+// Stage 1 of the decode path: 128-point Walsh-Hadamard transform, 2-bit bucketize, pack, and the
+// append of new keys/values/codes to the paged caches.
+//
+// Work decomposition: one half-warp (16 lanes) per 128-element row, 8 elements (16 bytes) per lane.
+// Butterfly strides 1,2,4 run inside a lane's registers, strides 8..64 through shfl.xor with lane
+// masks 1,2,4,8.  Arithmetic is fp32 add/sub in a fixed order plus one multiply, then a round to
+// the storage type, so the result is bit-identical to the CPU restatement.  After the transform
+// lane w holds dimensions 8w..8w+7, which is exactly packed code word w.
+#pragma once
+#include "common.cuh"
+
+namespace adamas {
+
+// In-place 128-point WHT over the 16 lanes of a half-warp. `l16` = lane index within the half-warp.
+__device__ __forceinline__ void wht128_halfwarp(float (&x)[8], unsigned l16) {
+#pragma unroll
+  for (int s = 1; s < 8; s <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if ((i & s) == 0) {
+        float a = x[i], b = x[i + s];
+        x[i] = __fadd_rn(a, b);
+        x[i + s] = __fsub_rn(a, b);
+      }
+    }
+  }
+#pragma unroll
+  for (unsigned m = 1; m < 16; m <<= 1) {
+    const bool upper = (l16 & m) != 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float other = __shfl_xor_sync(0xffffffffu, x[i], m);
+      // lower lane holds a and receives b: a + b; upper lane holds b and receives a: a - b
+      x[i] = upper ? __fsub_rn(other, x[i]) : __fadd_rn(x[i], other);
+    }
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void scale_round(float (&x)[8], float scale) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) x[i] = Elem<T>::round(__fmul_rn(x[i], scale));
+}
+
+// 8 values -> one packed word: value i at bits [2i, 2i+1]; bucket = #thresholds strictly below.
+__device__ __forceinline__ uint16_t bucketize_pack8(const float (&x)[8], Thresholds th) {
+  unsigned w = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    unsigned b = (x[i] > th.t0) + (x[i] > th.t1) + (x[i] > th.t2);
+    w |= b << (2 * i);
+  }
+  return static_cast<uint16_t>(w);
+}
+
+// y = round(scale * WHT(x)), rows x 128.
+template <typename T>
+__global__ void __launch_bounds__(256) hadamard_kernel(const T* __restrict__ x, T* __restrict__ y,
+                                                       int64_t rows, float scale) {
+  const unsigned l16 = threadIdx.x & 15;
+  const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
+  const bool valid = row < rows;
+  float v[8];
+  uint4 raw = make_uint4(0, 0, 0, 0);
+  if (valid) raw = ld_16(x + row * kHeadDim + l16 * 8);
+  unpack8<T>(raw, v);
+  wht128_halfwarp(v, l16);
+  scale_round<T>(v, scale);
+  if (valid) st_16(y + row * kHeadDim + l16 * 8, pack8<T>(v));
+}
+
+// codes[row, w] = pack(bucketize(h[row, 8w..8w+7]))
+template <typename T>
+__global__ void __launch_bounds__(256) bucketize_pack_kernel(const T* __restrict__ h,
+                                                             uint16_t* __restrict__ codes,
+                                                             int64_t rows, Thresholds th) {
+  const unsigned l16 = threadIdx.x & 15;
+  const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
+  if (row >= rows) return;
+  float v[8];
+  unpack8<T>(ld_16(h + row * kHeadDim + l16 * 8), v);
+  codes[row * kCodeWords + l16] = bucketize_pack8(v, th);
+}
+
+struct PagedTarget {
+  void* kv_data;
+  const int32_t* kv_table;
+  uint16_t* code_data;
+  const int32_t* code_table;
+  int page_size;
+  int num_heads;
+};
+
+// Decode append: one half-warp per head.  FUSED: qh = q, kh = k and the transform runs here;
+// otherwise qh/kh point at rows 0/1 of the pre-transformed h.
+template <typename T, bool FUSED>
+__global__ void __launch_bounds__(256)
+append_decode_kernel(const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ qh,
+                     const T* __restrict__ kh, uint16_t* __restrict__ q_code_out, PagedTarget tgt,
+                     int kv_last_page, int kv_entry, int code_last_page, int code_entry, float scale,
+                     Thresholds th) {
+  // physical pages of the slot being written: last entries of the two page tables
+  const int kv_page = __ldg(tgt.kv_table + kv_last_page);
+  const int code_page = __ldg(tgt.code_table + code_last_page);
+  const unsigned l16 = threadIdx.x & 15;
+  const int head = (blockIdx.x * blockDim.x + threadIdx.x) >> 4;
+  const int H = tgt.num_heads;
+  const bool valid = head < H;
+  const int hh = valid ? head : 0;
+  const int64_t in_off = static_cast<int64_t>(hh) * kHeadDim + l16 * 8;
+
+  // copy K and V rows into the page slot
+  T* kv = static_cast<T*>(tgt.kv_data);
+  const int64_t k_off =
+      ((static_cast<int64_t>(kv_page) * 2 * tgt.page_size + kv_entry) * H + hh) * kHeadDim + l16 * 8;
+  const int64_t v_delta = static_cast<int64_t>(tgt.page_size) * H * kHeadDim;
+  uint4 kraw = ld_16(k + in_off);
+  uint4 vraw = ld_16(v + in_off);
+  if (valid) {
+    st_16(kv + k_off, kraw);
+    st_16(kv + k_off + v_delta, vraw);
+  }
+
+  float a[8], b[8];
+  unpack8<T>(ld_16(qh + in_off), a);
+  if (FUSED) {
+    unpack8<T>(kraw, b);
+    wht128_halfwarp(a, l16);
+    wht128_halfwarp(b, l16);
+    scale_round<T>(a, scale);
+    scale_round<T>(b, scale);
+  } else {
+    unpack8<T>(ld_16(kh + in_off), b);
+  }
+  if (valid) {
+    q_code_out[hh * kCodeWords + l16] = bucketize_pack8(a, th);
+    const int64_t c_off =
+        ((static_cast<int64_t>(code_page) * tgt.page_size + code_entry) * H + hh) * kCodeWords + l16;
+    tgt.code_data[c_off] = bucketize_pack8(b, th);
+  }
+}
+
+// Prefill append: one half-warp per (token, head) row; token n sits at position start_pos + n.
+template <typename T, bool FUSED>
+__global__ void __launch_bounds__(256)
+append_prefill_kernel(const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ h,
+                      int64_t rows, int64_t start_pos, PagedTarget tgt, float scale, Thresholds th) {
+  const unsigned l16 = threadIdx.x & 15;
+  const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
+  const bool valid = row < rows;
+  const int64_t r = valid ? row : 0;
+  const int H = tgt.num_heads;
+  const int64_t n = r / H;
+  const int head = static_cast<int>(r - n * H);
+  const int64_t pos = start_pos + n;
+  const int64_t lp = pos / tgt.page_size;
+  const int e = static_cast<int>(pos - lp * tgt.page_size);
+  const int64_t in_off = r * kHeadDim + l16 * 8;
+
+  uint4 kraw = ld_stream_16(k + in_off);
+  uint4 vraw = ld_stream_16(v + in_off);
+  const int64_t kv_page = tgt.kv_table[lp];
+  T* kv = static_cast<T*>(tgt.kv_data);
+  const int64_t k_off = ((kv_page * 2 * tgt.page_size + e) * H + head) * kHeadDim + l16 * 8;
+  if (valid) {
+    st_16(kv + k_off, kraw);
+    st_16(kv + k_off + static_cast<int64_t>(tgt.page_size) * H * kHeadDim, vraw);
+  }
+  float x[8];
+  if (FUSED) {
+    unpack8<T>(kraw, x);
+    wht128_halfwarp(x, l16);
+    scale_round<T>(x, scale);
+  } else {
+    unpack8<T>(ld_stream_16(h + in_off), x);
+  }
+  if (valid) {
+    const int64_t code_page = tgt.code_table[lp];
+    tgt.code_data[((code_page * tgt.page_size + e) * H + head) * kCodeWords + l16] =
+        bucketize_pack8(x, th);
+  }
+}
+
+}  // namespace adamas

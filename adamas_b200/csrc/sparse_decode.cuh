@@ -1,0 +1,284 @@
+// Stage 4 of the decode path: decode attention of one query row per head over a per-head list of
+// selected token slots (plus an always-attended tail) in the paged KV cache.
+//
+// grid = (num_splits, H).  A thread block walks its share of the head's token list in tiles of
+// kDecTile tokens.  For each tile it resolves the token slots from the index list, gathers the
+// 256-byte K and V rows into shared memory with 16-byte cp.async (double buffered across tiles),
+// computes the logits with two threads per token, runs an online softmax in base 2, and accumulates
+// P.V with one thread per (token group, 8-dim chunk).  Rows are stored with an XOR swizzle of the
+// 16-byte chunk position so that both access patterns are bank-conflict free.
+//
+// With more than one split per head each block writes an unnormalised partial (o, m, l) to global
+// scratch, and the block that arrives last at the head's counter merges the partials and writes the
+// output (no block ever waits for another).  The counter is left at zero for the next launch.
+#pragma once
+#include "common.cuh"
+
+namespace adamas {
+
+constexpr int kDecTile = 64;       // tokens per tile
+constexpr int kDecThreads = 128;
+constexpr int kDecStageBytes = 2 * kDecTile * kHeadDim * 2;  // K + V rows of one tile (32 KB)
+
+struct DecodeParams {
+  const void* q;          // [H, 128]
+  void* o;                // [H, 128]
+  float* lse;             // [H] or null (base-2 log-sum-exp of the scaled logits)
+  const void* kv;         // [pages, 2, page_size, H, 128]
+  const int32_t* indices; // [H, idx_stride]
+  int64_t idx_stride;
+  int n_idx;              // indices used per head
+  int idx_unit;           // token slots covered by one index
+  int page_size;
+  int H;
+  int64_t tail_slot0;     // physical token slot of the first tail token
+  int n_tokens;           // n_idx * idx_unit + tail_len
+  int tiles_per_block;
+  int num_splits;
+  float* partial_o;       // [H, num_splits, 128]
+  float* partial_ml;      // [H, num_splits, 2]
+  unsigned* counters;     // [H], zero on entry and on exit
+  float scale_log2;       // sm_scale * log2(e)
+};
+
+__device__ __forceinline__ float ld_cg_f32(const float* p) {
+  float v;
+  asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kDecThreads) sparse_decode_kernel(DecodeParams prm) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  __shared__ float s_logit[kDecTile];
+  __shared__ float s_p[kDecTile];
+  __shared__ float s_red[4];
+  __shared__ float s_sum[4];
+  __shared__ float s_o[8][kHeadDim];
+  __shared__ unsigned s_last;
+
+  const int split = blockIdx.x;
+  const int head = blockIdx.y;
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int H = prm.H;
+
+  const int tok_begin = split * prm.tiles_per_block * kDecTile;
+  const int tok_end = min(prm.n_tokens, tok_begin + prm.tiles_per_block * kDecTile);
+  const int n_tiles = (tok_end - tok_begin + kDecTile - 1) / kDecTile;
+  const int n_listed = prm.n_idx * prm.idx_unit;
+
+  const T* kvp = static_cast<const T*>(prm.kv);
+  const int32_t* idx_row = prm.indices + static_cast<int64_t>(head) * prm.idx_stride;
+  const int64_t v_delta = static_cast<int64_t>(prm.page_size) * H * kHeadDim;
+
+  // ---- gather one tile into a stage --------------------------------------------------------------
+  // thread -> chunk c = tid % 16 of tokens tl = tid / 16 + 8 * i
+  auto issue_tile = [&](int tile, int stage) {
+    uint8_t* sk = smem + stage * kDecStageBytes;
+    uint8_t* sv = sk + kDecTile * kHeadDim * 2;
+    const int c = tid & 15;
+    const int t0 = tok_begin + tile * kDecTile;
+    int64_t slot[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int tl = (tid >> 4) + 8 * i;
+      const int j = t0 + tl;
+      slot[i] = -1;
+      if (j < tok_end) {
+        if (j < n_listed) {
+          const int item = j / prm.idx_unit;
+          const int off = j - item * prm.idx_unit;
+          slot[i] = static_cast<int64_t>(__ldg(idx_row + item)) * prm.idx_unit + off;
+        } else {
+          slot[i] = prm.tail_slot0 + (j - n_listed);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int tl = (tid >> 4) + 8 * i;
+      if (slot[i] >= 0) {
+        const int64_t page = slot[i] / prm.page_size;
+        const int64_t e = slot[i] - page * prm.page_size;
+        const T* kp = kvp + ((page * 2 * prm.page_size + e) * H + head) * kHeadDim + c * 8;
+        const int phys = c ^ (tl & 3);
+        cp_async_16(sk + tl * 256 + phys * 16, kp);
+        cp_async_16(sv + tl * 256 + phys * 16, kp + v_delta);
+      }
+    }
+    cp_async_commit();
+  };
+
+  issue_tile(0, 0);
+
+  // ---- query: 64 dims per thread, in the order the thread walks its chunks ---------------------
+  // thread pair (tl = tid / 2, half = tid % 2); step i reads logical chunk half*8 + (i ^ half*4)
+  const int qk_tl = tid >> 1;
+  const int half = tid & 1;
+  float qreg[8][8];
+  {
+    const T* qp = static_cast<const T*>(prm.q) + static_cast<int64_t>(head) * kHeadDim;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int lc = half * 8 + (i ^ (half * 4));
+      unpack8<T>(ld_16(qp + lc * 8), qreg[i]);
+#pragma unroll
+      for (int d = 0; d < 8; ++d) qreg[i][d] *= prm.scale_log2;
+    }
+  }
+
+  float m_run = -INFINITY, l_run = 0.f;
+  float o_acc[8];
+#pragma unroll
+  for (int d = 0; d < 8; ++d) o_acc[d] = 0.f;
+  const int pv_g = tid >> 4;   // token group: tokens pv_g*8 .. pv_g*8+7 of the tile
+  const int pv_c = tid & 15;   // 8-dim chunk
+
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    const int stage = tile & 1;
+    if (tile + 1 < n_tiles) {
+      issue_tile(tile + 1, stage ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const uint8_t* sk = smem + stage * kDecStageBytes;
+    const uint8_t* sv = sk + kDecTile * kHeadDim * 2;
+    const int tile_tokens = min(kDecTile, tok_end - (tok_begin + tile * kDecTile));
+
+    // logits
+    float acc = 0.f;
+    if (qk_tl < tile_tokens) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int lc = half * 8 + (i ^ (half * 4));
+        const int phys = lc ^ (qk_tl & 3);
+        float kf[8];
+        unpack8<T>(*reinterpret_cast<const uint4*>(sk + qk_tl * 256 + phys * 16), kf);
+#pragma unroll
+        for (int d = 0; d < 8; ++d) acc = fmaf(qreg[i][d], kf[d], acc);
+      }
+    }
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    const float logit = (qk_tl < tile_tokens) ? acc : -INFINITY;
+    if (half == 0) s_logit[qk_tl] = logit;
+    float wmax = logit;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, o));
+    if (lane == 0) s_red[warp] = wmax;
+    __syncthreads();
+
+    const float m_tile = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+    const float m_new = fmaxf(m_run, m_tile);
+    const float rescale = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
+    float psum = 0.f;
+    if (tid < kDecTile) {
+      const float p = exp2f(s_logit[tid] - m_new);  // exp2(-inf) = 0 for masked tokens
+      s_p[tid] = p;
+      psum = p;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
+    if (lane == 0) s_sum[warp] = psum;
+    __syncthreads();
+    l_run = l_run * rescale + (s_sum[0] + s_sum[1]);
+    m_run = m_new;
+
+    // P.V for this thread's token group and chunk
+#pragma unroll
+    for (int d = 0; d < 8; ++d) o_acc[d] *= rescale;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int tl = pv_g * 8 + i;
+      const float p = s_p[tl];
+      if (tl < tile_tokens) {
+        const int phys = pv_c ^ (tl & 3);
+        float vf[8];
+        unpack8<T>(*reinterpret_cast<const uint4*>(sv + tl * 256 + phys * 16), vf);
+#pragma unroll
+        for (int d = 0; d < 8; ++d) o_acc[d] = fmaf(p, vf[d], o_acc[d]);
+      }
+    }
+    __syncthreads();  // the stage is free for the tile after next; s_logit / s_p reusable
+  }
+
+  // ---- reduce the 8 token groups ----------------------------------------------------------------
+#pragma unroll
+  for (int d = 0; d < 8; ++d) s_o[pv_g][pv_c * 8 + d] = o_acc[d];
+  __syncthreads();
+  float od = 0.f;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) od += s_o[g][tid];
+
+  T* op = static_cast<T*>(prm.o) + static_cast<int64_t>(head) * kHeadDim;
+  if (prm.num_splits == 1) {
+    const float r = od / l_run;
+    // pairs of threads share a 32-bit store
+    const float r1 = __shfl_down_sync(0xffffffffu, r, 1);
+    if ((tid & 1) == 0) reinterpret_cast<uint32_t*>(op)[tid >> 1] = Elem<T>::from_f2(r, r1);
+    if (tid == 0 && prm.lse) prm.lse[head] = m_run + log2f(l_run);
+    return;
+  }
+
+  const int64_t pidx = static_cast<int64_t>(head) * prm.num_splits + split;
+  prm.partial_o[pidx * kHeadDim + tid] = od;
+  if (tid == 0) {
+    prm.partial_ml[pidx * 2] = m_run;
+    prm.partial_ml[pidx * 2 + 1] = l_run;
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned ticket = atomicAdd(prm.counters + head, 1u);
+    s_last = (ticket == static_cast<unsigned>(prm.num_splits - 1));
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+
+  const int64_t p0 = static_cast<int64_t>(head) * prm.num_splits;
+  float M = -INFINITY;
+  for (int s = 0; s < prm.num_splits; ++s) M = fmaxf(M, ld_cg_f32(prm.partial_ml + (p0 + s) * 2));
+  float accd = 0.f, L = 0.f;
+  for (int s = 0; s < prm.num_splits; ++s) {
+    const float w = exp2f(ld_cg_f32(prm.partial_ml + (p0 + s) * 2) - M);
+    L += w * ld_cg_f32(prm.partial_ml + (p0 + s) * 2 + 1);
+    accd += w * ld_cg_f32(prm.partial_o + (p0 + s) * kHeadDim + tid);
+  }
+  const float r = accd / L;
+  const float r1 = __shfl_down_sync(0xffffffffu, r, 1);
+  if ((tid & 1) == 0) reinterpret_cast<uint32_t*>(op)[tid >> 1] = Elem<T>::from_f2(r, r1);
+  if (tid == 0) {
+    if (prm.lse) prm.lse[head] = M + log2f(L);
+    prm.counters[head] = 0;
+  }
+}
+
+// Merge P already-normalised partial results (o_parts [P,H,128] fp32, lse_parts [P,H] base 2).
+template <typename T>
+__global__ void __launch_bounds__(kHeadDim)
+merge_states_kernel(const float* __restrict__ o_parts, const float* __restrict__ lse_parts, int P,
+                    int H, T* __restrict__ o, float* __restrict__ lse) {
+  const int head = blockIdx.x;
+  const int d = threadIdx.x;
+  float M = -INFINITY;
+  for (int p = 0; p < P; ++p) M = fmaxf(M, lse_parts[static_cast<int64_t>(p) * H + head]);
+  float acc = 0.f, den = 0.f;
+  for (int p = 0; p < P; ++p) {
+    const float l = lse_parts[static_cast<int64_t>(p) * H + head];
+    const float w = (l == -INFINITY) ? 0.f : exp2f(l - M);
+    den += w;
+    acc += w * o_parts[(static_cast<int64_t>(p) * H + head) * kHeadDim + d];
+  }
+  const float r = acc / den;
+  const float r1 = __shfl_down_sync(0xffffffffu, r, 1);
+  if ((d & 1) == 0)
+    reinterpret_cast<uint32_t*>(o + static_cast<int64_t>(head) * kHeadDim)[d >> 1] =
+        Elem<T>::from_f2(r, r1);
+  if (d == 0 && lse) lse[head] = M + log2f(den);
+}
+
+}  // namespace adamas

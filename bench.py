@@ -1,0 +1,420 @@
+#!/usr/bin/env python
+"""Benchmark of the Adamas decode hot path on B200.
+
+A "step" is one decode token's pass through the attention hot path of every layer of a
+Llama-2-7B-shaped stack (32 layers, 32 heads x 128) at a 32K-token context with a token budget of
+1024 and page size 16: per layer, fused append (Hadamard + 2-bit code + KV write), distance
+estimate over the layer's code cache, top-k, sparse paged attention.  Every layer has its own KV
+and code cache, so one step streams ~1.6 GB of distinct data (inputs far larger than L2).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N > 1 is launched by torch.distributed.run; each rank owns the same number of KV heads of a model
+N times as wide (head sharding, no collective inside the path; the per-step gather of the layer
+outputs is included in the timed region).  Rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "sparse_attn_decode_hbm_GBps_at_32k"
+UNIT = "GB/s"
+
+
+# --------------------------------------------------------------------------------------------
+# algorithmic bytes of one layer-step (read + written bytes each stage cannot avoid)
+# --------------------------------------------------------------------------------------------
+def stage_bytes(L: int, H: int, B: int, b: int = 1) -> dict:
+    n = L - 1
+    est = b * H * (n * 32 + 32 + n * 2)            # codes + query code in, 16-bit distances out
+    topk = b * H * (n * 2 + (B - 1) * 4)           # distances in, indices out
+    attn = b * H * (B * 512 + (B - 1) * 4 + 256 + 256)   # K,V rows + indices + q in, o out
+    return dict(estimate=est, topk=topk, attention=attn, total=est + topk + attn)
+
+
+# --------------------------------------------------------------------------------------------
+# clocks during the timed region (NVML, read-only)
+# --------------------------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {
+        0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+        0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting",
+        0x100: "display_clock_setting", 0x10: "sync_boost",
+    }
+
+    def __init__(self, index: int, period_s: float = 0.02):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        self._h = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._h = None
+        self._period = period_s
+
+    def _once(self):
+        nv = self._nv
+        try:
+            self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+            try:
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+            except Exception:
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+            for bit, name in self.REASONS.items():
+                if mask & bit:
+                    self.reasons.add(name)
+        except Exception:
+            pass
+
+    def _run(self):
+        while not self._stop.is_set():
+            self._once()
+            self._stop.wait(self._period)
+
+    def start(self):
+        if self._h is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self) -> dict:
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join()
+            self._once()
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# --------------------------------------------------------------------------------------------
+# CPU arm: the reference's PyTorch decode path restated (oracle), timed on the host cores
+# --------------------------------------------------------------------------------------------
+def cpu_layer_step_setup(L, H, B, seed=0):
+    from oracle import adamas_ref as ref
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(H, 128, generator=g).to(torch.float16).float()
+    k = torch.randn(H, L, 128, generator=g).to(torch.float16).float()
+    v = torch.randn(H, L, 128, generator=g).to(torch.float16).float()
+    thresholds = torch.tensor([-10, 0, 10])
+    k_code = torch.bucketize(torch.from_numpy(ref.fwht(k.numpy())), thresholds, out_int32=True)
+    return ref, q, k, v, k_code
+
+
+def time_cpu_reference(L, H, B, steps, warmup, budget_s=25.0):
+    """Times one layer-step of the reference's PyTorch path (bucketize of the query ->
+    pairwise_distance(p=1) against cached key codes -> topk(largest=False) -> masked fp32 softmax
+    -> @V) with all host threads.  Returns (seconds per layer-step, number of timed runs)."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    ref, q, k, v, k_code = cpu_layer_step_setup(L, H, B)
+    for _ in range(max(1, warmup)):
+        ref.literal_reference_decode(q, k, v, B, k_code=k_code)
+    times = []
+    t_begin = time.perf_counter()
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        ref.literal_reference_decode(q, k, v, B, k_code=k_code)
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() - t_begin > budget_s:
+            break
+    return sum(times) / len(times), len(times)
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    L, H, B = args.ctx, args.heads, args.budget
+    sec, n = time_cpu_reference(L, H, B, args.steps, args.warmup, budget_s=120.0)
+    by = stage_bytes(L, H, B)
+    value = by["total"] / sec / 1e9
+    cores = torch.get_num_threads()
+    sample = (f"{n} timed runs of ONE layer-step (1 of {args.layers} layers) of the reference PyTorch decode path "
+              f"(cached key codes), ctx {L}, budget {B}, {H} heads, fp32, torch CPU")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": n, "warmup": max(1, args.warmup), "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "us_per_layer": sec * 1e6,
+        "config": workload_config(args, extra={"arm": "oracle port of evaluation/adamas_attention.py:214-241 on host cores"}),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, extra=None):
+    cfg = {
+        "workload": (f"llama2-7b-shaped attention stack: {args.layers} layers x {args.heads} heads x 128, "
+                     f"ctx {args.ctx}, token budget {args.budget}, page size {args.page_size}, batch 1; "
+                     "per layer: fused append + estimate + top-k + sparse paged attention"),
+        "layers": args.layers, "heads_per_gpu": args.heads, "ctx": args.ctx, "budget": args.budget,
+        "page_size": args.page_size, "parallelism": f"head-sharded x{args.gpus}" if args.gpus > 1 else "single GPU",
+        "l2": "inputs larger than L2 (each layer has its own caches; ~1.6 GB touched per step)",
+        "launch": "CUDA graph of the step" if not args.eager else "eager",
+    }
+    if extra:
+        cfg.update(extra)
+    return cfg
+
+
+# --------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------
+class Workload:
+    def __init__(self, args, dev):
+        import adamas_b200.utils as U
+        self.U = U
+        self.args = args
+        self.dev = dev
+        L, H, ps, B, layers = args.ctx, args.heads, args.page_size, args.budget, args.layers
+        dtype = torch.float16
+        self.c = c = U.InferenceController(layers, H, 128, ps, B // ps, L, dtype, dev)
+        gen = torch.Generator(device=dev).manual_seed(1234 + int(os.environ.get("RANK", "0")))
+        c.prepare_hadamard(L - 1)
+        c.begin_forward(L - 1)
+        for layer in range(layers):
+            k = torch.randn(L - 1, H, 128, device=dev, dtype=dtype, generator=gen)
+            v = torch.randn(L - 1, H, 128, device=dev, dtype=dtype, generator=gen)
+            U.append_kvh(k, v, None, c, layer)
+            del k, v
+        c.end_forward()
+        c.prepare_hadamard(1)
+        c.begin_forward(1)
+        assert c.need_estimate()
+        # this step's projections: pinned host copies (end-to-end path) and device copies
+        hg = torch.Generator().manual_seed(99)
+        self.h_qkv = torch.randn(3, layers, 1, H, 128, generator=hg).to(dtype).pin_memory()
+        self.d_qkv = self.h_qkv.to(dev)
+        self.d_out = torch.zeros(layers, 1, H, 128, dtype=dtype, device=dev)
+        self.h_out = torch.zeros(layers, 1, H, 128, dtype=dtype).pin_memory()
+        self.q_code = torch.zeros(layers, 1, H, 16, dtype=dtype, device=dev)
+        self.graph = None
+
+    def layer_step(self, layer):
+        U, c = self.U, self.c
+        q, k, v = self.d_qkv[0, layer], self.d_qkv[1, layer], self.d_qkv[2, layer]
+        q_code = U.append_qkv_fused(q, k, v, c, layer, out=self.q_code[layer])
+        est = U.decode_estimate(q_code, c, layer)
+        U.decode_topk(est, c)
+        U.decode_sparse_attn(q, c, layer, c.topk_dindices_buffer, out=self.d_out[layer])
+
+    def step_eager(self):
+        for layer in range(self.args.layers):
+            self.layer_step(layer)
+
+    def capture(self):
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                self.step_eager()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.step_eager()
+
+    def step(self):
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.step_eager()
+
+    def step_e2e(self):
+        """Host buffers in, host buffers out: H2D of this step's q/k/v, the step, D2H of the outputs."""
+        self.d_qkv.copy_(self.h_qkv, non_blocking=True)
+        self.step()
+        self.h_out.copy_(self.d_out, non_blocking=True)
+
+    # one kernel class alone, for the roofline entry
+    def capture_estimate_only(self):
+        U, c = self.U, self.c
+        g = torch.cuda.CUDAGraph()
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for layer in range(self.args.layers):
+                U.decode_estimate(self.q_code[layer], c, layer)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g):
+            for layer in range(self.args.layers):
+                U.decode_estimate(self.q_code[layer], c, layer)
+        return g
+
+
+def timed(fn, steps, dist_on, dev):
+    """barrier + synchronize, CUDA events around exactly `steps` calls, max over ranks (ms)."""
+    import torch.distributed as dist
+    if dist_on:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if dist_on:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.barrier()
+        ms = float(t.item())
+    return ms
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist_on = world > 1
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the product path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if dist_on:
+        dist.init_process_group("nccl", device_id=dev)
+    wl = Workload(args, dev)
+    gather_buf = None
+    if dist_on:
+        gather_buf = torch.empty(world, *wl.d_out.shape, dtype=wl.d_out.dtype, device=dev)
+
+    def step_dev():
+        wl.step()
+        if dist_on:
+            dist.all_gather_into_tensor(gather_buf, wl.d_out)
+
+    def step_e2e():
+        wl.step_e2e()
+        if dist_on:
+            dist.all_gather_into_tensor(gather_buf, wl.d_out)
+
+    if not args.eager:
+        wl.capture()
+    for _ in range(max(3, args.warmup)):
+        step_dev()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms = timed(step_dev, args.steps, dist_on, dev)
+    clocks = sampler.stop()
+
+    for _ in range(3):
+        step_e2e()
+    ms_e2e = timed(step_e2e, args.steps, dist_on, dev)
+
+    # eager (no graph) end to end, for information
+    saved = wl.graph
+    wl.graph = None
+    for _ in range(2):
+        step_e2e()
+    ms_eager = timed(step_e2e, max(1, min(args.steps, 20)), dist_on, dev)
+    wl.graph = saved
+
+    # dominant kernel alone (estimate), one launch per layer so the data comes from HBM
+    g_est = wl.capture_estimate_only()
+    for _ in range(3):
+        g_est.replay()
+    ms_est = timed(g_est.replay, args.steps, False, dev)
+    est_us = ms_est * 1e3 / args.steps / args.layers
+
+    if rank != 0:
+        if dist_on:
+            dist.destroy_process_group()
+        return
+
+    L, H, B = args.ctx, args.heads, args.budget
+    by = stage_bytes(L, H, B)
+    step_bytes = by["total"] * args.layers * world
+    ms_per_step = ms / args.steps
+    value = step_bytes / (ms_per_step * 1e-3) / 1e9
+    e2e_value = step_bytes / (ms_e2e / args.steps * 1e-3) / 1e9
+    peak, peak_src = measured_peak()
+    est_gbs = by["estimate"] / (est_us * 1e-6) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "us_per_layer": ms_per_step * 1e3 / args.layers,
+        "us_per_layer_e2e": ms_e2e / args.steps * 1e3 / args.layers,
+        "us_per_layer_e2e_eager": ms_eager / max(1, min(args.steps, 20)) * 1e3 / args.layers,
+        "path_roofline_frac": value / world / peak,
+        "config": workload_config(args),
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": UNIT,
+                "h2d_bytes_per_step": wl.h_qkv.numel() * wl.h_qkv.element_size(),
+                "d2h_bytes_per_step": wl.h_out.numel() * wl.h_out.element_size()},
+        "gpu_launches": args.steps * args.layers * 4,
+        "roofline": {"kernel": "estimate_kernel", "bound": "hbm", "achieved": est_gbs, "peak": peak,
+                     "unit": "GB/s", "frac": est_gbs / peak, "traffic": args.traffic,
+                     "peak_source": peak_src, "us_per_launch": est_us,
+                     "algorithmic_bytes_per_launch": by["estimate"]},
+        "stage_bytes_per_layer": by,
+    }
+    if not args.no_cpu and world >= 1:
+        sec, n = time_cpu_reference(L, H, B, steps=20, warmup=1, budget_s=20.0)
+        line["cpu_baseline"] = {
+            "value": by["total"] / sec / 1e9, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": (f"{n} timed runs of one layer-step (1 of {args.layers} layers) of the reference PyTorch "
+                       f"decode path with cached key codes, ctx {L}, budget {B}, fp32 torch CPU; {sec * 1e3:.1f} ms each"),
+        }
+    print(json.dumps(line), flush=True)
+    if dist_on:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ctx", type=int, default=32768)
+    ap.add_argument("--budget", type=int, default=1024)
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--heads", type=int, default=32, help="KV heads per GPU")
+    ap.add_argument("--page-size", dest="page_size", type=int, default=16)
+    ap.add_argument("--eager", action="store_true", help="no CUDA graph")
+    ap.add_argument("--no-cpu", dest="no_cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--traffic", type=float, default=None,
+                    help="DRAM bytes per estimate launch from an ncu capture (profiles/), if known")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,178 @@
+/*
+ * adamas_b200 -- C ABI of the B200 (sm_100a) implementation of the Adamas decode hot path.
+ *
+ * Every entry point takes raw device pointers, plain integers and a CUDA stream, and returns an
+ * int status (0 = ADAMAS_OK).  No entry point synchronises the stream.  On failure a
+ * human-readable message is available from adamas_last_error() (thread-local).
+ *
+ * Each declaration cites the reference interface it replaces as <file>:<line> relative to the
+ * root of the FibonaccciYan/Adamas checkout.
+ *
+ * Memory layouts (identical to the reference's KvPool, adamas/utils/kv_cache.py:21-24, layout NHD):
+ *   KV cache of one layer    [pages, 2, page_size, H, D]   fp16 or bf16   (item 0 = K, item 1 = V)
+ *   code cache of one layer  [pages, 1, page_size, H, D/8] 16-bit words   (2-bit codes, 32 B per key)
+ * A page table is an int32 array of physical page numbers in logical order.  Token t of a
+ * sequence lives at page page_table[t / page_size], entry t % page_size.
+ * Packed code word w of a (token, head) holds dimensions 8w..8w+7, dimension 8w+i at bits
+ * [2i, 2i+1] (kernels/include/decode/decode_page.cuh:380-398).
+ */
+#ifndef ADAMAS_B200_H_
+#define ADAMAS_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ADAMAS_ABI_VERSION 1
+
+/* status codes */
+#define ADAMAS_OK 0
+#define ADAMAS_ERR_INVALID 1     /* bad argument (null pointer, unsupported shape, size out of range) */
+#define ADAMAS_ERR_CUDA 2        /* a CUDA runtime call or kernel launch failed */
+#define ADAMAS_ERR_STATE 3       /* call order violated (forward before begin_forward) */
+
+/* element types of q/k/v and the KV cache (the reference dispatches fp16 only,
+ * adamas/ops/csrc/pytorch_extension_utils.h:25-35; bf16 is an extension) */
+#define ADAMAS_F16 0
+#define ADAMAS_BF16 1
+
+/* distance metric of the estimate */
+#define ADAMAS_METRIC_L1 0       /* sum |qc - kc|: evaluation/adamas_attention.py:222 */
+#define ADAMAS_METRIC_XOR 1      /* lowbit + 2*highbit of qc^kc: kernels/include/decode/decode_attn.cuh:192-193 */
+
+/* value formats of distances / top-k keys */
+#define ADAMAS_VAL_F16 0         /* IEEE fp16 (the reference's format) */
+#define ADAMAS_VAL_U16 1         /* unsigned 16-bit integer */
+
+typedef void* adamas_stream_t;   /* a cudaStream_t */
+
+int adamas_abi_version(void);
+const char* adamas_last_error(void);
+
+/* ---- stage 1: Hadamard transform, bucketize, pack, append -------------------------------- */
+
+/* y[r, :] = round_to_dtype(scale * WHT_D(x[r, :])) for r < rows; D = head_dim = 128; x == y allowed.
+ * Replaces faster_hadamard_transform.hadamard_transform(x, inplace) (external module;
+ * call sites adamas/models/Adamas.py:120,150). */
+int adamas_hadamard_transform(const void* x, void* y, int64_t rows, int head_dim, float scale,
+                              int dtype, adamas_stream_t stream);
+
+/* Bucketize (thresholds[3], strict >) and pack rows of already-transformed values:
+ * h [rows, D] -> codes [rows, D/8] 16-bit words.
+ * Replaces pack_2bit / vec_bucketize_and_pack_2bit (kernels/include/decode/decode_page.cuh:380-398;
+ * reference test helper adamas/tests/test_estimate.py:12-24). */
+int adamas_bucketize_pack(const void* h, void* codes, int64_t rows, int head_dim,
+                          const float* thresholds3_host, int dtype, adamas_stream_t stream);
+
+/* Decode append of one token.  k, v [1,H,D]; h [2,H,D] with row 0 = transformed q, row 1 =
+ * transformed k; q_code_out [1,H,D/8].  The token's position is
+ * (kv_num_pages-1)*page_size + kv_last_page_len - 1; its code goes to entry code_last_page_len-1
+ * of the last code page.
+ * Replaces append_kv_cache_decode (adamas/ops/csrc/page.cu:6-109,
+ * kernels/include/decode/decode_page.cuh:415-469,566-590). */
+int adamas_append_decode(const void* k, const void* v, const void* h, void* q_code_out,
+                         void* kv_data, const int32_t* kv_page_table, int kv_num_pages,
+                         int kv_last_page_len,
+                         void* code_data, const int32_t* code_page_table, int code_num_pages,
+                         int code_last_page_len,
+                         int num_heads, int head_dim, int page_size,
+                         const float* thresholds3_host, int dtype, adamas_stream_t stream);
+
+/* Same, with the Hadamard transform done inside: takes q and k (after RoPE) instead of h.
+ * Replaces the torch.cat + hadamard_transform + append_kvh sequence of
+ * adamas/models/Adamas.py:145-161 with one launch. */
+int adamas_append_decode_fused(const void* q, const void* k, const void* v, void* q_code_out,
+                               void* kv_data, const int32_t* kv_page_table, int kv_num_pages,
+                               int kv_last_page_len,
+                               void* code_data, const int32_t* code_page_table, int code_num_pages,
+                               int code_last_page_len,
+                               int num_heads, int head_dim, int page_size, float scale,
+                               const float* thresholds3_host, int dtype, adamas_stream_t stream);
+
+/* Prefill append of n_tokens tokens ending at the current sequence end.  k, v, h [n_tokens,H,D];
+ * h holds transformed keys.  If h is NULL the transform of k is computed inside (scale used).
+ * Replaces append_kv_cache_prefill (adamas/ops/csrc/page.cu:111-226,
+ * kernels/include/decode/decode_page.cuh:486-548,607-640) and, with h == NULL, also the
+ * hadamard_transform call of adamas/models/Adamas.py:120. */
+int adamas_append_prefill(const void* k, const void* v, const void* h, int64_t n_tokens,
+                          void* kv_data, const int32_t* kv_page_table, int kv_num_pages,
+                          int kv_last_page_len,
+                          void* code_data, const int32_t* code_page_table, int code_num_pages,
+                          int code_last_page_len,
+                          int num_heads, int head_dim, int page_size, float scale,
+                          const float* thresholds3_host, int dtype, adamas_stream_t stream);
+
+/* ---- stage 2: distance estimate ----------------------------------------------------------- */
+
+/* out[h * out_stride + t] = distance(q_code[h], code of token t, head h) for t < n_tokens, where
+ * n_tokens = (code_num_pages-1)*page_size + code_last_page_len - 1 (the newest token is excluded).
+ * q_code [H, D/8]; out_format ADAMAS_VAL_F16 (reference) or ADAMAS_VAL_U16.
+ * Replaces estimate_attn_score (adamas/ops/csrc/estimate.cu:6-84,
+ * kernels/include/decode/decode_attn.cuh:287-443,1144-1211). */
+int adamas_estimate(const void* q_code, const void* code_data, const int32_t* code_page_table,
+                    int code_num_pages, int code_last_page_len, int page_size, int num_heads,
+                    int head_dim, void* out, int64_t out_stride, int out_format, int metric,
+                    adamas_stream_t stream);
+
+/* ---- stage 3: top-k ------------------------------------------------------------------------ */
+
+/* For each of num_rows rows select the k smallest of n values; equal values are taken in order of
+ * position (lower position first); results are written in ascending position order:
+ *   out_values[row*out_stride + j] = value at the j-th selected position p_j,
+ *   out_idx[row*out_stride + j]    = in_idx ? in_idx[row*in_idx_stride + p_j/idx_page_size]*idx_page_size
+ *                                              + p_j % idx_page_size
+ *                                           : p_j.
+ * in_idx_stride may be 0 (one index row shared by all rows).  out_values may be NULL.
+ * Requires 1 <= k <= n.
+ * Replaces topk_filtering (adamas/ops/csrc/topk.cu:7-46, kernels/include/topk/decode_select_k.cuh:25-62,
+ * raft radix_topk_one_block_kernel); the reference leaves the tie order undefined. */
+int adamas_topk(const void* values, int value_format, int64_t value_stride, int n,
+                const int32_t* in_idx, int64_t in_idx_stride, int idx_page_size,
+                int num_rows, int k, void* out_values, int32_t* out_idx, int64_t out_stride,
+                adamas_stream_t stream);
+
+/* ---- stage 4: sparse paged decode attention ------------------------------------------------ */
+
+typedef struct adamas_decode_handler adamas_decode_handler_t;
+
+/* Handler lifecycle: replaces flashinfer::BatchDecodeHandler and the class
+ * BatchDecodeWithPagedKVCachePyTorchWrapper (adamas/ops/csrc/bsk_ops.h:95-124,
+ * adamas/ops/csrc/approx_attn.cu:27-151, kernels/include/decode/decode_handler.cuh:39-244). */
+int adamas_decode_handler_create(adamas_decode_handler_t** handler);
+int adamas_decode_handler_destroy(adamas_decode_handler_t* handler);
+
+/* Plans the split of max_tokens attended tokens per head over thread blocks and makes sure the
+ * handler's device scratch (partial outputs) is large enough (allocates on first use or growth).
+ * Replaces BeginForward (kernels/include/decode/decode_handler.cuh:73-121). */
+int adamas_decode_begin_forward(adamas_decode_handler_t* handler, int64_t max_tokens, int num_heads,
+                                int head_dim, int page_size, int dtype, adamas_stream_t stream);
+/* Replaces EndForward (decode_handler.cuh:123-136).  Scratch is kept for reuse until destroy. */
+int adamas_decode_end_forward(adamas_decode_handler_t* handler);
+
+/* o[h,:] = softmax(sm_scale * q[h,:] . K_sel^T) V_sel over, for head h, the tokens covered by
+ * indices[h*idx_stride + i], i < n_idx, followed by the tail.  Each index covers idx_unit
+ * consecutive token slots starting at index*idx_unit (idx_unit = 1: physical token slots
+ * page*page_size+entry; idx_unit = page_size: whole pages, the reference's meaning).  The tail is the
+ * last tail_len filled entries of page last_page_idx, i.e. entries
+ * [last_page_len - tail_len, last_page_len).  q, o [H, D]; lse (optional, may be NULL) [H] receives
+ * log2(sum exp2(sm_scale*log2(e)*logit)) style base-2 log-sum-exp of the scaled logits.
+ * Replaces BatchDecodeWithPagedKVCachePyTorchWrapper::Forward (adamas/ops/csrc/approx_attn.cu:68-151,
+ * kernels/include/decode/decode_attn.cuh:469-702,952-1127). */
+int adamas_decode_forward(adamas_decode_handler_t* handler, const void* q, void* o, float* lse,
+                          const void* kv_data, const int32_t* indices, int64_t idx_stride,
+                          int n_idx, int idx_unit, int last_page_idx, int last_page_len,
+                          int tail_len, float sm_scale, adamas_stream_t stream);
+
+/* Merge P partial results over disjoint token sets: o_parts [P, H, D] fp32 (each already
+ * normalised), lse_parts [P, H] base-2; writes o [H, D] in dtype and, optionally, lse [H].
+ * Replaces VariableLengthMergeStates (called at kernels/include/decode/decode_attn.cuh:1050-1059);
+ * also the merge step of sequence-sharded decoding. */
+int adamas_merge_states(const float* o_parts, const float* lse_parts, int num_parts, int num_heads,
+                        int head_dim, void* o, float* lse, int dtype, adamas_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ADAMAS_B200_H_ */

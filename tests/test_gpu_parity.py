@@ -1,0 +1,490 @@
+"""Parity of the CUDA path (called through the C ABI) with the CPU oracle on the same seeded
+inputs.  Integer results (codes, distances, selected indices) must be bit-exact; attention outputs
+must agree within 2e-3 relative (fp16 / bf16), the tolerance the task states.
+
+Shape lists follow the reference's own tests: adamas/tests/test_estimate.py:66,
+adamas/tests/test_topk.py:22, adamas/tests/test_approx_attention.py:100,
+kernels/src/test/test_batch_decode.cu:215-257.
+"""
+import functools
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import adamas_ref as ref
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+REL_TOL = 2e-3
+
+
+def _mods():
+    import adamas_b200
+    from adamas_b200 import _kernels, utils
+    return adamas_b200, _kernels, utils
+
+
+def _randn(shape, seed, dtype=torch.float16, sigma=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * sigma).to(dtype)
+
+
+def _assert_attn_close(got: torch.Tensor, want: torch.Tensor):
+    got = got.detach().float().cpu()
+    want = want.detach().float().cpu()
+    atol = REL_TOL * float(want.abs().max())
+    torch.testing.assert_close(got, want, rtol=REL_TOL, atol=atol)
+
+
+def _codes_of(buf: torch.Tensor) -> np.ndarray:
+    return buf.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+class State:
+    """A sequence pushed through the host API the way the reference's tests do it: prefill of
+    L-1 tokens (append_kvh), then one decode append."""
+
+    def __init__(self, L, H=32, ps=1, dtype=torch.float16, seed=0, sigma=1.0, scale=None, budget_pages=64,
+                 fused=False, layers=1, max_seq_len=None):
+        _, K, U = _mods()
+        self.L, self.H, self.ps, self.dtype, self.scale = L, H, ps, dtype, scale
+        self.q = _randn((1, H, 128), seed, dtype, sigma)
+        self.k = _randn((L, H, 128), seed + 1, dtype, sigma)
+        self.v = _randn((L, H, 128), seed + 2, dtype)
+        cap = max_seq_len or (L + 3 * ps + 5)
+        self.c = U.InferenceController(layers, H, 128, ps, budget_pages, cap, dtype, DEV)
+        # hand out physical pages in a shuffled order
+        rng = np.random.default_rng(seed)
+        for cache in (self.c.kv_cache, self.c.hadamard_cache):
+            pool = cache.pool
+            rng.shuffle(pool._free)
+            pool.alloc_block = functools.partial(_pop_random, pool)
+        qd, kd, vd = self.q.to(DEV), self.k.to(DEV), self.v.to(DEV)
+        c = self.c
+        if L > 1:
+            c.prepare_hadamard(L - 1)
+            c.begin_forward(max(L - 1, 2))      # prefill-style set-up even for a single token
+            if L - 1 > 1:
+                h = None if fused else K.hadamard_transform(kd[: L - 1], scale=scale)
+                if fused and scale is not None:
+                    K.append_kv_cache_prefill(kd[: L - 1].contiguous(), vd[: L - 1].contiguous(), None,
+                                              c.kv_cache.buf_layer(0), c.kv_indices_with_last, None,
+                                              c.kv_cache.last_page_len, c.kv_last_page_idx,
+                                              c.hadamard_cache.buf_layer(0), c.hadamard_indices, None,
+                                              c.hadamard_cache.last_page_len, c.hadamard_last_page_idx, c.layout,
+                                              scale=scale)
+                else:
+                    U.append_kvh(kd[: L - 1].contiguous(), vd[: L - 1].contiguous(), h, c, 0)
+            else:
+                # a single prefill token goes through the decode append
+                h = K.hadamard_transform(torch.cat((qd, kd[:1]), 0), scale=scale)
+                U.append_kvh(kd[:1].contiguous(), vd[:1].contiguous(), h, c, 0)
+            c.end_forward()
+        c.prepare_hadamard(1)
+        c.begin_forward(1)
+        if fused:
+            self.q_code = U.append_qkv_fused(qd, kd[L - 1:].contiguous(), vd[L - 1:].contiguous(), c, 0, scale=scale)
+        else:
+            h = K.hadamard_transform(torch.cat((qd, kd[L - 1:]), 0), scale=scale)
+            self.q_code = U.append_kvh(kd[L - 1:].contiguous(), vd[L - 1:].contiguous(), h, c, 0)
+        self.qd = qd
+
+    def oracle_codes(self):
+        return ref.encode(self.q[0], self.scale), ref.encode(self.k, self.scale)
+
+    def cached_codes(self) -> np.ndarray:
+        """[L, H, 16] uint16 read back from the paged code cache."""
+        c = self.c
+        buf = _codes_of(c.hadamard_cache.buf_layer(0))            # [P, 1, ps, H, 16]
+        table = np.asarray(c.hadamard_cache.indicies)
+        t = np.arange(self.L)
+        return buf[table[t // self.ps], 0, t % self.ps]
+
+    def cached_kv(self):
+        c = self.c
+        buf = c.kv_cache.buf_layer(0).cpu()
+        table = torch.tensor(c.kv_cache.indicies)
+        t = torch.arange(self.L)
+        return buf[table[t // self.ps], 0, t % self.ps], buf[table[t // self.ps], 1, t % self.ps]
+
+
+def _pop_random(pool):
+    idx = pool._free.pop()
+    pool._in_use.add(idx)
+    return idx
+
+
+# ------------------------------------------------------------------------------------------------
+# stage 1
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,sigma,scale", [(1, 1.0, None), (37, 1.0, None), (64 * 33 + 5, 3.0, 1.0), (4096, 11.0, None)])
+def test_hadamard_transform_bit_exact(dtype, rows, sigma, scale):
+    _, K, _ = _mods()
+    x = _randn((rows, 128), 11 + rows, dtype, sigma)
+    y = K.hadamard_transform(x.to(DEV), scale=scale)
+    want = ref.hadamard_transform(x, scale)
+    assert torch.equal(y.cpu().view(torch.int16), want.view(torch.int16))
+    # in place, 3-D input
+    x3 = x[: (rows // 2) * 2].reshape(-1, 2, 128).contiguous().to(DEV) if rows >= 2 else x.reshape(1, 1, 128).to(DEV)
+    ref3 = ref.hadamard_transform(x3.cpu(), scale)
+    out = K.hadamard_transform(x3, inplace=True, scale=scale)
+    assert out.data_ptr() == x3.data_ptr()
+    assert torch.equal(x3.cpu().view(torch.int16), ref3.view(torch.int16))
+
+
+def test_bucketize_pack_all_buckets_and_boundaries():
+    _, K, _ = _mods()
+    vals = torch.tensor([-65504.0, -11.0, -10.0, -9.99, -0.0, 0.0, 6e-8, 9.99, 10.0, 10.01, 65504.0, 1.0, -1.0, 5.0, -5.0, 0.5])
+    h = vals.repeat(8).reshape(1, 1, 128).to(torch.float16)
+    h = torch.cat([h, _randn((6, 1, 128), 3, torch.float16, 9.0)], 0)
+    o = torch.zeros(7, 1, 16, dtype=torch.int16, device=DEV)
+    K.bucketize_pack(h.to(DEV), o)
+    want = ref.pack_2bit(ref.bucketize(h.float().numpy()))
+    np.testing.assert_array_equal(_codes_of(o), want)
+    # custom thresholds
+    K.bucketize_pack(h.to(DEV), o, thresholds=(-1.0, 0.25, 2.0))
+    want = ref.pack_2bit(ref.bucketize(h.float().numpy(), (-1.0, 0.25, 2.0)))
+    np.testing.assert_array_equal(_codes_of(o), want)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("L,H,ps,sigma,scale", [
+    (2, 32, 1, 1.0, None), (27, 32, 1, 1.0, None), (61, 8, 16, 1.0, None), (113, 32, 3, 3.0, 1.0),
+    (577, 32, 16, 3.0, 1.0), (1110, 4, 7, 1.0, None), (3330, 32, 1, 1.0, None), (2049, 40, 32, 3.0, 1.0),
+])
+def test_append_codes_and_kv_bit_exact(dtype, fused, L, H, ps, sigma, scale):
+    st = State(L, H, ps, dtype, seed=L, sigma=sigma, scale=scale, fused=fused)
+    q_code, k_codes = st.oracle_codes()
+    np.testing.assert_array_equal(_codes_of(st.q_code)[0], q_code)
+    np.testing.assert_array_equal(st.cached_codes(), k_codes)
+    kk, vv = st.cached_kv()
+    assert torch.equal(kk.view(torch.int16), st.k.view(torch.int16))
+    assert torch.equal(vv.view(torch.int16), st.v.view(torch.int16))
+    if sigma > 1.0:
+        assert set(np.unique(ref.unpack_2bit(k_codes))) == {0, 1, 2, 3}
+
+
+# ------------------------------------------------------------------------------------------------
+# stage 2
+# ------------------------------------------------------------------------------------------------
+EST_LENS = [27, 61, 113, 482, 577, 1110, 1541, 2047, 3330]   # adamas/tests/test_estimate.py:66
+
+
+@pytest.mark.parametrize("kv_len", EST_LENS + [2, 3, 33, 4096])
+@pytest.mark.parametrize("ps", [1, 16])
+def test_estimate_bit_exact(kv_len, ps):
+    _, K, U = _mods()
+    wide = kv_len % 2 == 1
+    st = State(kv_len, 32, ps, seed=kv_len, sigma=3.0 if wide else 1.0, scale=1.0 if wide else None)
+    q_code, k_codes = st.oracle_codes()
+    for metric in ("l1", "xor"):
+        want = ref.code_distance(q_code, k_codes[:-1], metric)
+        got = U.decode_estimate(st.q_code, st.c, 0, metric=metric)
+        assert got.dtype == torch.float16 and tuple(got.shape) == (32, kv_len - 1)
+        np.testing.assert_array_equal(got.float().cpu().numpy().astype(np.int32), want)
+        # integer output format
+        o16 = torch.full((32, kv_len - 1), -1, dtype=torch.int16, device=DEV)
+        K.estimate_attn_score(st.q_code, o16, st.c.hadamard_cache.buf_layer(0), st.c.hadamard_indices, None,
+                              st.c.hadamard_cache.last_page_len, st.c.hadamard_last_page_idx, 0, metric)
+        np.testing.assert_array_equal(o16.cpu().numpy().astype(np.int32), want)
+    if wide:
+        assert (ref.code_distance(q_code, k_codes[:-1], "xor") != ref.code_distance(q_code, k_codes[:-1], "l1")).any()
+
+
+@pytest.mark.parametrize("H", [1, 4, 8, 40, 64])
+def test_estimate_other_head_counts(H):
+    _, _, U = _mods()
+    st = State(300, H, 16, seed=H, sigma=3.0, scale=1.0)
+    q_code, k_codes = st.oracle_codes()
+    got = U.decode_estimate(st.q_code, st.c, 0)
+    np.testing.assert_array_equal(got.float().cpu().numpy().astype(np.int32),
+                                  ref.code_distance(q_code, k_codes[:-1], "l1"))
+
+
+def test_estimate_golden_reference_vectors():
+    """Distances for the fixtures produced by the reference's own _ref_cpu_estimate."""
+    _, K, U = _mods()
+    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "ref_python_path.npz"))
+    for name in sorted({k.split(".")[0] for k in gold.files}):
+        f16 = lambda a: torch.from_numpy(a.copy()).view(torch.float16)
+        q, k, v = f16(gold[name + ".q"]), f16(gold[name + ".k"]), f16(gold[name + ".v"])
+        scale = None if gold[name + ".scale"] < 0 else float(gold[name + ".scale"])
+        L, H, _ = k.shape
+        c = U.InferenceController(1, H, 128, 1, 8, L + 8, torch.float16, DEV)
+        c.prepare_hadamard(L - 1); c.begin_forward(L - 1)
+        U.append_kvh(k[: L - 1].to(DEV), v[: L - 1].to(DEV), K.hadamard_transform(k[: L - 1].to(DEV), scale=scale), c, 0)
+        c.end_forward()
+        c.prepare_hadamard(1); c.begin_forward(1)
+        h = K.hadamard_transform(torch.cat((q, k[L - 1:]), 0).to(DEV), scale=scale)
+        q_code = U.append_kvh(k[L - 1:].to(DEV), v[L - 1:].to(DEV), h, c, 0)
+        assert torch.equal(q_code.cpu().view(torch.int16), torch.from_numpy(gold[name + ".q_code"].copy()))
+        est = U.decode_estimate(q_code, c, 0)
+        assert torch.equal(est.cpu().view(torch.int16), torch.from_numpy(gold[name + ".est"].copy()))
+        c.end_forward()
+
+
+# ------------------------------------------------------------------------------------------------
+# stage 3
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("kv_len", [13, 24, 51, 77, 244, 311, 502, 1110])      # adamas/tests/test_topk.py:22
+@pytest.mark.parametrize("k_budget", [2, 5, 7, 19, 31, 69, 111, 251])
+def test_topk_reference_shapes(kv_len, k_budget):
+    if k_budget > kv_len:
+        pytest.skip("k should be less than kv_len")
+    _, K, _ = _mods()
+    q = _randn((32, 1, 128), kv_len, torch.float16)
+    k = _randn((32, kv_len, 128), kv_len + 1, torch.float16)
+    attn = (torch.matmul(q.float(), k.float().transpose(1, 2)) / math.sqrt(128)).squeeze(1).to(torch.float16)
+    vals = attn.to(DEV).contiguous()
+    in_idx = (torch.arange(kv_len, dtype=torch.int32) * 3 + 1).repeat(32, 1).to(DEV)
+    d_out = torch.zeros(32, k_budget, dtype=torch.float16, device=DEV)
+    i_out = torch.zeros(32, k_budget, dtype=torch.int32, device=DEV)
+    buf = torch.zeros(32, 1024, dtype=torch.float16, device=DEV)
+    K.topk_filtering(vals, in_idx, d_out, i_out, buf, k_budget)
+    want = ref.select_topk(attn.numpy(), k_budget)
+    np.testing.assert_array_equal(i_out.cpu().numpy(), want * 3 + 1)
+    np.testing.assert_array_equal(d_out.cpu().numpy().view(np.uint16),
+                                  np.take_along_axis(attn.numpy(), want, 1).view(np.uint16))
+    # the reference's own check: sum of the selected values equals torch.topk's
+    tsum = torch.topk(attn.float(), k=k_budget, dim=-1, largest=False).values.sum(-1)
+    torch.testing.assert_close(d_out.float().cpu().sum(-1), tsum, rtol=5e-3, atol=5e-3)
+
+
+@pytest.mark.parametrize("n,k", [(1, 1), (7, 7), (8, 1), (4095, 255), (4096, 4095), (32767, 1023), (32767, 63),
+                                 (131071, 2047), (250000, 4095)])
+@pytest.mark.parametrize("fmt", ["dist_f16", "dist_u16"])
+def test_topk_distances_with_ties(n, k, fmt):
+    """Binomial-like integer distances (the real input of this stage): massive ties at the cut."""
+    _, K, _ = _mods()
+    rng = np.random.default_rng(n + k)
+    rows = 5 if n > 100000 else 32
+    d = rng.binomial(128, 0.5, size=(rows, n)).astype(np.int32)
+    if fmt == "dist_f16":
+        vals = torch.from_numpy(d.astype(np.float16))
+    else:
+        vals = torch.from_numpy(d.astype(np.int16))
+    # odd row stride: rows start at 2-byte-aligned addresses only
+    store = torch.zeros(rows, n + 3, dtype=vals.dtype, device=DEV)
+    store[:, 1:n + 1] = vals.to(DEV)
+    view = store[:, 1:n + 1]
+    i_out = torch.full((rows, k), -1, dtype=torch.int32, device=DEV)
+    v_out = torch.zeros((rows, k), dtype=vals.dtype, device=DEV)
+    K.topk_select(view, k, i_out, v_out)
+    want = ref.select_topk(d, k)
+    np.testing.assert_array_equal(i_out.cpu().numpy(), want)
+    np.testing.assert_array_equal(v_out.cpu().numpy().astype(np.int32), np.take_along_axis(d, want, 1))
+    # determinism: a second run gives the same bytes
+    i2 = torch.full((rows, k), -1, dtype=torch.int32, device=DEV)
+    K.topk_select(view, k, i2)
+    assert torch.equal(i2, i_out)
+
+
+def test_topk_adversarial_values():
+    _, K, _ = _mods()
+    rows = [
+        np.full(1000, 7.0),                                   # all ties
+        np.concatenate([np.zeros(500), -np.zeros(500)]),      # +0 / -0 are equal
+        np.linspace(-100, 100, 1000),                          # negatives, ascending
+        np.linspace(100, -100, 1000),                          # descending
+        np.concatenate([np.full(999, 65504.0), [-65504.0]]),   # extreme values, winner last
+    ]
+    a = np.stack(rows).astype(np.float16)
+    vals = torch.from_numpy(a).to(DEV)
+    for k in (1, 2, 499, 500, 501, 999, 1000):
+        i_out = torch.zeros((len(rows), k), dtype=torch.int32, device=DEV)
+        K.topk_select(vals, k, i_out)
+        np.testing.assert_array_equal(i_out.cpu().numpy(), ref.select_topk(a, k))
+
+
+def test_topk_maps_positions_through_page_table():
+    _, K, _ = _mods()
+    n, ps, k = 1000, 16, 100
+    d = np.random.default_rng(5).integers(0, 384, size=(4, n)).astype(np.int16)
+    table = torch.from_numpy(np.random.default_rng(6).permutation(200)[: (n + ps - 1) // ps].astype(np.int32))
+    i_out = torch.zeros((4, k), dtype=torch.int32, device=DEV)
+    K.topk_select(torch.from_numpy(d).to(DEV), k, i_out, page_table=table.to(DEV), page_size=ps)
+    want = ref.select_topk(d.astype(np.int32), k)
+    np.testing.assert_array_equal(i_out.cpu().numpy(), table.numpy()[want // ps] * ps + want % ps)
+
+
+def test_topk_rejects_bad_arguments():
+    _, K, _ = _mods()
+    vals = torch.zeros(2, 10, dtype=torch.float16, device=DEV)
+    out = torch.zeros(2, 11, dtype=torch.int32, device=DEV)
+    with pytest.raises(RuntimeError):
+        K.topk_select(vals, 11, out)
+    with pytest.raises(RuntimeError):
+        K.topk_select(vals, 0, out)
+    with pytest.raises(RuntimeError):
+        K.topk_select(vals.to(torch.bfloat16), 3, out)
+
+
+# ------------------------------------------------------------------------------------------------
+# stage 4
+# ------------------------------------------------------------------------------------------------
+def _attend(st, idx_tokens):
+    """oracle output for per-head token positions idx_tokens [H, m]"""
+    return ref.sparse_attention(st.q[0], st.k, st.v, idx_tokens)
+
+
+@pytest.mark.parametrize("kv_len", [27, 61, 113, 482, 577, 1011, 1541])       # test_approx_attention.py:100
+@pytest.mark.parametrize("token_budget", [64, 112, 240, 496, 880, 1136])
+def test_sparse_attention_reference_shapes(kv_len, token_budget):
+    """Page size 1, indices taken from the oracle's top-k, as the reference's test feeds its kernel."""
+    _, K, U = _mods()
+    st = State(kv_len, 32, 1, seed=kv_len + token_budget, budget_pages=token_budget)
+    r = ref.decode_step(st.q[0], st.k, st.v, token_budget)
+    c = st.c
+    if not c.need_estimate():
+        assert kv_len <= token_budget
+        o = U.decode_sparse_attn(st.qd, c, 0, c.kv_indices_without_last)
+    else:
+        table = np.asarray(c.kv_cache.indicies)
+        idx = torch.from_numpy(table[r["sel"]].astype(np.int32)).to(DEV)
+        o = U.decode_sparse_attn(st.qd, c, 0, idx)
+    _assert_attn_close(o[0], r["out"])
+
+
+@pytest.mark.parametrize("seq_len", [63, 129, 1024, 7777, 28837])     # test_batch_decode.cu:215-257
+@pytest.mark.parametrize("ps", [1, 3, 7, 16, 32])
+@pytest.mark.parametrize("page_budget", [16, 128])
+def test_sparse_attention_page_granular(seq_len, ps, page_budget):
+    """Random per-head page lists plus the forced last page (the reference kernel's meaning of
+    the index list), every page attended in full."""
+    _, K, U = _mods()
+    H = 8
+    st = State(seq_len, H, ps, seed=seq_len + ps, budget_pages=page_budget)
+    c = st.c
+    n_pages = len(c.kv_cache.indicies)
+    rng = np.random.default_rng(seq_len * 31 + ps)
+    n_sel = min(page_budget - 1, n_pages - 1)
+    if n_sel < 1:
+        pytest.skip("needs at least two pages")
+    logical = np.stack([np.sort(rng.choice(n_pages - 1, size=n_sel, replace=False)) for _ in range(H)])
+    table = np.asarray(c.kv_cache.indicies)
+    idx = torch.from_numpy(table[logical].astype(np.int32)).to(DEV)
+    o = torch.empty_like(st.qd)
+    lse = torch.zeros(H, dtype=torch.float32, device=DEV)
+    c._decode_handler.forward(st.qd, o, c.kv_cache.buf_layer(0), idx, None, c.kv_cache.last_page_len,
+                              c.kv_last_page_idx, lse=lse)
+    tok = (logical[:, :, None] * ps + np.arange(ps)[None, None, :]).reshape(H, -1)
+    last = np.arange((n_pages - 1) * ps, seq_len)
+    tok = np.concatenate([tok, np.tile(last, (H, 1))], axis=1)
+    want, want_lse = ref.sparse_attention(st.q[0], st.k, st.v, tok, return_lse=True)
+    _assert_attn_close(o[0], want)
+    torch.testing.assert_close(lse.cpu() * math.log(2.0), want_lse, rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("L,ps,budget", [(300, 16, 64), (4096, 16, 256), (5000, 16, 1024), (9000, 32, 4096)])
+def test_full_step_token_granular(dtype, L, ps, budget):
+    """append -> estimate -> top-k -> sparse attention through the host API at page_size > 1."""
+    _, K, U = _mods()
+    H = 32
+    st = State(L, H, ps, dtype, seed=L, budget_pages=budget // ps, fused=True)
+    c = st.c
+    assert c.need_estimate()
+    r = ref.decode_step(st.q[0], st.k, st.v, budget)
+    est = U.decode_estimate(st.q_code, c, 0)
+    np.testing.assert_array_equal(est.cpu().numpy().astype(np.int32) if est.dtype == torch.int16
+                                  else est.float().cpu().numpy().astype(np.int32), r["dist"])
+    U.decode_topk(est, c)
+    table = np.asarray(c.kv_cache.indicies)
+    want_slots = table[r["sel"] // ps] * ps + r["sel"] % ps
+    np.testing.assert_array_equal(c.topk_dindices_buffer.cpu().numpy(), want_slots)
+    o = U.decode_sparse_attn(st.qd, c, 0, c.topk_dindices_buffer)
+    _assert_attn_close(o[0], r["out"])
+    # bytes are reproducible
+    o2 = U.decode_sparse_attn(st.qd, c, 0, c.topk_dindices_buffer)
+    assert torch.equal(o, o2)
+
+
+def test_dense_layer_page_size_16():
+    _, K, U = _mods()
+    st = State(1000, 32, 16, seed=9, budget_pages=1 << 20)
+    c = st.c
+    assert not c.need_estimate()
+    o = U.decode_sparse_attn(st.qd, c, 0, c.kv_indices_without_last)
+    want = ref.sparse_attention(st.q[0], st.k, st.v, np.tile(np.arange(1000), (32, 1)))
+    _assert_attn_close(o[0], want)
+
+
+def test_config1_single_layer_decode_step():
+    """batch 1, 32 heads, head_dim 128, KV length 4096, page size 16, budget 256, seed 0, N(0,1)
+    fp16 inputs: codes and selected indices bit-exact, output vs attention restricted to the
+    selection."""
+    _, K, U = _mods()
+    g = torch.Generator().manual_seed(0)
+    L, H, ps, B = 4096, 32, 16, 256
+    q = torch.randn(1, H, 128, generator=g, dtype=torch.float16)
+    k = torch.randn(L, H, 128, generator=g, dtype=torch.float16)
+    v = torch.randn(L, H, 128, generator=g, dtype=torch.float16)
+    c = U.InferenceController(1, H, 128, ps, B // ps, L, torch.float16, DEV)
+    c.prepare_hadamard(L - 1); c.begin_forward(L - 1)
+    U.append_kvh(k[: L - 1].to(DEV), v[: L - 1].to(DEV), None, c, 0)
+    c.end_forward()
+    c.prepare_hadamard(1); c.begin_forward(1)
+    q_code = U.append_qkv_fused(q.to(DEV), k[L - 1:].to(DEV), v[L - 1:].to(DEV), c, 0)
+    r = ref.decode_step(q[0], k, v, B)
+    np.testing.assert_array_equal(_codes_of(q_code)[0], r["q_code"])
+    est = U.decode_estimate(q_code, c, 0)
+    np.testing.assert_array_equal(est.float().cpu().numpy().astype(np.int32), r["dist"])
+    U.decode_topk(est, c)
+    table = np.asarray(c.kv_cache.indicies)
+    np.testing.assert_array_equal(c.topk_dindices_buffer.cpu().numpy(), table[r["sel"] // ps] * ps + r["sel"] % ps)
+    o = U.decode_sparse_attn(q.to(DEV), c, 0, c.topk_dindices_buffer)
+    _assert_attn_close(o[0], r["out"])
+    # ties at the cut were really exercised
+    tau = np.take_along_axis(r["dist"], r["sel"], 1).max(1)
+    assert ((r["dist"] == tau[:, None]).sum(1) > (np.take_along_axis(r["dist"], r["sel"], 1) == tau[:, None]).sum(1)).any()
+
+
+def test_headline_size_properties_32k():
+    """32K context, budget 1024, page size 16 (the benchmark's workload): full parity on the integer
+    stages (the oracle takes a few seconds at this size) and the attention tolerance."""
+    _, K, U = _mods()
+    L, H, ps, B = 32768, 32, 16, 1024
+    st = State(L, H, ps, seed=77, budget_pages=B // ps, fused=True, max_seq_len=L)
+    c = st.c
+    r = ref.decode_step(st.q[0], st.k, st.v, B)
+    np.testing.assert_array_equal(st.cached_codes(), r["k_codes"])
+    est = U.decode_estimate(st.q_code, c, 0)
+    np.testing.assert_array_equal(est.float().cpu().numpy().astype(np.int32), r["dist"])
+    U.decode_topk(est, c)
+    table = np.asarray(c.kv_cache.indicies)
+    np.testing.assert_array_equal(c.topk_dindices_buffer.cpu().numpy(), table[r["sel"] // ps] * ps + r["sel"] % ps)
+    o = U.decode_sparse_attn(st.qd, c, 0, c.topk_dindices_buffer)
+    _assert_attn_close(o[0], r["out"])
+
+
+def test_merge_states_matches_oracle():
+    _, K, _ = _mods()
+    g = torch.Generator().manual_seed(3)
+    P, H = 5, 32
+    o_parts = torch.randn(P, H, 128, generator=g)
+    lse = torch.randn(P, H, generator=g) * 3
+    lse[2, 5] = -float("inf")                      # an empty shard
+    want_o, want_lse = ref.merge_states(o_parts, lse * math.log(2.0))
+    o = torch.zeros(H, 128, dtype=torch.float16, device=DEV)
+    out_lse = torch.zeros(H, dtype=torch.float32, device=DEV)
+    K.merge_states(o_parts.to(DEV), lse.to(DEV), o, out_lse)
+    _assert_attn_close(o, want_o)
+    torch.testing.assert_close(out_lse.cpu() * math.log(2.0), want_lse, rtol=1e-4, atol=1e-4)
+
+
+def test_forward_before_begin_forward_raises():
+    _, K, U = _mods()
+    w = U.BatchDecodeWithPagedKVCacheWrapper("NHD")
+    q = torch.zeros(1, 4, 128, dtype=torch.float16, device=DEV)
+    kv = torch.zeros(4, 2, 1, 4, 128, dtype=torch.float16, device=DEV)
+    idx = torch.zeros(4, 2, dtype=torch.int32, device=DEV)
+    with pytest.raises(RuntimeError):
+        w.forward(q, torch.empty_like(q), kv, idx, None, 1, 3)
+    with pytest.raises(KeyError):
+        U.BatchDecodeWithPagedKVCacheWrapper("XYZ")
