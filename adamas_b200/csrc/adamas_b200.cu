@@ -3,6 +3,7 @@
 // launch geometry, error reporting.  Kernels live in the .cuh files next to this one.
 #include "../../include/adamas_b200.h"
 
+#include <algorithm>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -64,6 +65,48 @@ int check_common(int num_heads, int head_dim, int page_size, int dtype) {
   ADAMAS_REQUIRE(num_heads >= 1 && num_heads <= 1024, "num_heads out of range (%d)", num_heads);
   ADAMAS_REQUIRE(page_size >= 1, "page_size must be >= 1 (got %d)", page_size);
   ADAMAS_REQUIRE(dtype == ADAMAS_F16 || dtype == ADAMAS_BF16, "unsupported dtype %d", dtype);
+  return ADAMAS_OK;
+}
+
+// Per-device facts and one-time kernel attributes.
+struct DeviceInfo {
+  bool ready = false;
+  int num_sms = 0;
+  int max_smem_optin = 0;
+  int topk_dyn_smem = 0;
+};
+
+int get_device_info(const DeviceInfo** out) {
+  static DeviceInfo infos[64];
+  int dev = 0;
+  ADAMAS_CUDA(cudaGetDevice(&dev));
+  ADAMAS_REQUIRE(dev >= 0 && dev < 64, "device ordinal out of range");
+  DeviceInfo& d = infos[dev];
+  if (!d.ready) {
+    ADAMAS_CUDA(cudaDeviceGetAttribute(&d.num_sms, cudaDevAttrMultiProcessorCount, dev));
+    ADAMAS_CUDA(cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    d.topk_dyn_smem = d.max_smem_optin - static_cast<int>(sizeof(TopkShared)) - 1024;
+    ADAMAS_CUDA(cudaFuncSetAttribute(topk_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, d.topk_dyn_smem));
+    ADAMAS_CUDA(cudaFuncSetAttribute(topk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, d.topk_dyn_smem));
+    const int est_max = d.max_smem_optin - 1024;
+#define EST_ATTR(M, OT, F, R)                                                                      \
+  ADAMAS_CUDA(cudaFuncSetAttribute(estimate_kernel<M, OT, F, R>,                                   \
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, est_max))
+#define EST_ATTR_ALL(M, OT) \
+  EST_ATTR(M, OT, true, 4); \
+  EST_ATTR(M, OT, true, 0); \
+  EST_ATTR(M, OT, false, 0)
+    EST_ATTR_ALL(0, __half);
+    EST_ATTR_ALL(0, uint16_t);
+    EST_ATTR_ALL(1, __half);
+    EST_ATTR_ALL(1, uint16_t);
+#undef EST_ATTR_ALL
+#undef EST_ATTR
+    ADAMAS_CUDA(cudaFuncSetAttribute(sparse_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kDecStageBytes));
+    ADAMAS_CUDA(cudaFuncSetAttribute(sparse_decode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kDecStageBytes));
+    d.ready = true;
+  }
+  *out = &d;
   return ADAMAS_OK;
 }
 
@@ -237,16 +280,46 @@ int adamas_estimate(const void* q_code, const void* code_data, const int32_t* co
   ADAMAS_REQUIRE((reinterpret_cast<uintptr_t>(q_code) & 15) == 0 &&
                      (reinterpret_cast<uintptr_t>(code_data) & 15) == 0,
                  "q_code and code_data must be 16-byte aligned");
-  const unsigned blocks = (n + kEstTile - 1) / kEstTile;
-  const size_t smem = static_cast<size_t>(num_heads) * (kEstTile + 2) * sizeof(uint16_t);
-  ADAMAS_REQUIRE(smem <= 48 * 1024, "num_heads too large for the estimate kernel");
+  const DeviceInfo* di = nullptr;
+  if (int rc = get_device_info(&di)) return rc;
+  const int num_tiles = (n + kEstTile - 1) / kEstTile;
+  const int rounds = (kEstTile * 2 * num_heads + kEstThreads - 1) / kEstThreads;
+  const size_t smem = static_cast<size_t>(kEstStages) * rounds * kEstThreads * 16 +
+                      2 * static_cast<size_t>(num_heads) * (kEstTile + 2) * sizeof(uint16_t);
+  ADAMAS_REQUIRE(smem <= static_cast<size_t>(di->max_smem_optin - 1024),
+                 "num_heads (%d) too large for the estimate kernel", num_heads);
+  const int per_sm = smem * 2 <= static_cast<size_t>(di->max_smem_optin) ? 2 : 1;
+  const unsigned blocks = static_cast<unsigned>(std::min(num_tiles, di->num_sms * per_sm));
+  auto log2_exact = [](int v) {
+    if (v <= 0 || (v & (v - 1)) != 0) return -1;
+    int s = 0;
+    while ((1 << s) < v) ++s;
+    return s;
+  };
+  EstimateParams prm;
+  prm.codes = static_cast<const uint4*>(code_data);
+  prm.page_table = code_page_table;
+  prm.q_code = static_cast<const uint4*>(q_code);
+  prm.out = out;
+  prm.out_stride = out_stride;
+  prm.n_tokens = n;
+  prm.H = num_heads;
+  prm.page_size = page_size;
+  prm.ps_shift = log2_exact(page_size);
+  prm.cpt_shift = log2_exact(2 * num_heads);
+  prm.num_tiles = num_tiles;
+  prm.rounds = rounds;
+  const bool fast = prm.ps_shift >= 0 && prm.cpt_shift >= 0 && 2 * num_heads <= kEstThreads;
   cudaStream_t st = to_stream(stream);
-  const uint4* codes = static_cast<const uint4*>(code_data);
-  const uint4* qc = static_cast<const uint4*>(q_code);
-#define LAUNCH_EST(M, OT)                                                                   \
-  estimate_kernel<M, OT><<<blocks, kEstThreads, smem, st>>>(codes, code_page_table, qc,      \
-                                                            static_cast<OT*>(out), out_stride, n, \
-                                                            num_heads, page_size)
+#define LAUNCH_EST(M, OT)                                                                      \
+  do {                                                                                         \
+    if (fast && rounds == 4)                                                                   \
+      estimate_kernel<M, OT, true, 4><<<blocks, kEstThreads, smem, st>>>(prm);                 \
+    else if (fast)                                                                             \
+      estimate_kernel<M, OT, true, 0><<<blocks, kEstThreads, smem, st>>>(prm);                 \
+    else                                                                                       \
+      estimate_kernel<M, OT, false, 0><<<blocks, kEstThreads, smem, st>>>(prm);                \
+  } while (0)
   if (metric == ADAMAS_METRIC_L1) {
     if (out_format == ADAMAS_VAL_F16) LAUNCH_EST(0, __half); else LAUNCH_EST(0, uint16_t);
   } else {
@@ -271,18 +344,70 @@ int adamas_topk(const void* values, int value_format, int64_t value_stride, int 
   ADAMAS_REQUIRE(out_stride >= k || num_rows == 1, "out_stride smaller than k");
   ADAMAS_REQUIRE(idx_page_size >= 1, "idx_page_size must be >= 1");
   ADAMAS_REQUIRE((reinterpret_cast<uintptr_t>(values) & 1) == 0, "values must be 2-byte aligned");
-  // stage the row in shared memory when it fits (one extra granule for a misaligned row start)
-  static int max_smem = -1;
-  if (max_smem < 0) {
-    int dev = 0, v = 0;
-    ADAMAS_CUDA(cudaGetDevice(&dev));
-    ADAMAS_CUDA(cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-    ADAMAS_CUDA(cudaFuncSetAttribute(topk_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     v - 4096));
-    ADAMAS_CUDA(cudaFuncSetAttribute(topk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     v - 4096));
-    max_smem = v - 4096;
+  cudaStream_t st = to_stream(stream);
+  const uint16_t* vals = static_cast<const uint16_t*>(values);
+  uint16_t* ov = static_cast<uint16_t*>(out_values);
+
+  // Rows that all start on a 16-byte boundary need ceil(n/8) granules, others up to one more.
+  const bool aligned = (reinterpret_cast<uintptr_t>(values) & 15) == 0 &&
+                       (num_rows == 1 || (value_stride * 2) % 16 == 0);
+  const int g_max = aligned ? (n + 7) / 8 : (n + 14) / 8;
+  int cl = 0, items = 0;
+  static const int kShapes[6][2] = {{1, 1}, {2, 1}, {4, 1}, {8, 1}, {8, 2}, {8, 4}};
+  for (const auto& sh : kShapes) {
+    if (static_cast<int64_t>(sh[0]) * sh[1] * kTopkThreads >= g_max) {
+      cl = sh[0];
+      items = sh[1];
+      break;
+    }
   }
+  if (cl > 0) {
+    TopkParams prm;
+    prm.values = vals;
+    prm.value_stride = value_stride;
+    prm.n = n;
+    prm.in_idx = in_idx;
+    prm.in_idx_stride = in_idx_stride;
+    prm.idx_page_size = idx_page_size;
+    prm.idx_ps_shift = -1;
+    if ((idx_page_size & (idx_page_size - 1)) == 0) {
+      prm.idx_ps_shift = 0;
+      while ((1 << prm.idx_ps_shift) < idx_page_size) ++prm.idx_ps_shift;
+    }
+    prm.k = k;
+    prm.out_values = ov;
+    prm.out_idx = out_idx;
+    prm.out_stride = out_stride;
+    prm.granules_per_block = (g_max + cl - 1) / cl;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(num_rows) * cl);
+    cfg.blockDim = dim3(kTopkThreads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cl;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaSuccess;
+#define LAUNCH_TK(F, I) e = cudaLaunchKernelEx(&cfg, topk_cluster_kernel<F, I>, prm)
+    if (value_format == ADAMAS_VAL_F16) {
+      if (items == 1) LAUNCH_TK(0, 1); else if (items == 2) LAUNCH_TK(0, 2); else LAUNCH_TK(0, 4);
+    } else {
+      if (items == 1) LAUNCH_TK(1, 1); else if (items == 2) LAUNCH_TK(1, 2); else LAUNCH_TK(1, 4);
+    }
+#undef LAUNCH_TK
+    if (e != cudaSuccess)
+      return fail(ADAMAS_ERR_CUDA, "topk_cluster_kernel launch failed: %s", cudaGetErrorString(e));
+    return check_launch("topk_cluster_kernel");
+  }
+
+  // long rows: one block per row, staged in shared memory when it fits
+  const DeviceInfo* di = nullptr;
+  if (int rc = get_device_info(&di)) return rc;
+  const int max_smem = di->topk_dyn_smem;
   const int granules = (n + 7) / 8 + 1;
   int smem_granules = 0;
   size_t smem = 0;
@@ -290,9 +415,6 @@ int adamas_topk(const void* values, int value_format, int64_t value_stride, int 
     smem_granules = granules;
     smem = static_cast<size_t>(granules) * 16;
   }
-  cudaStream_t st = to_stream(stream);
-  const uint16_t* vals = static_cast<const uint16_t*>(values);
-  uint16_t* ov = static_cast<uint16_t*>(out_values);
   if (value_format == ADAMAS_VAL_F16)
     topk_kernel<0><<<num_rows, kTopkThreads, smem, st>>>(vals, value_stride, n, in_idx, in_idx_stride,
                                                          idx_page_size, k, ov, out_idx, out_stride,
@@ -314,7 +436,6 @@ struct adamas_decode_handler {
   int device = -1;
   bool forward_started = false;
   int num_heads = 0, page_size = 0, dtype = 0;
-  bool smem_configured = false;
 };
 
 namespace {
@@ -370,17 +491,12 @@ int adamas_decode_begin_forward(adamas_decode_handler_t* handler, int64_t max_to
   ADAMAS_REQUIRE(max_tokens >= 1 && max_tokens < (int64_t(1) << 31) - kDecTile, "max_tokens out of range");
   int dev = 0;
   ADAMAS_CUDA(cudaGetDevice(&dev));
+  const DeviceInfo* di = nullptr;
+  if (int rc = get_device_info(&di)) return rc;
   if (handler->device != dev) {
     ADAMAS_REQUIRE(handler->scratch == nullptr, "handler was planned on another device");
-    ADAMAS_CUDA(cudaDeviceGetAttribute(&handler->num_sms, cudaDevAttrMultiProcessorCount, dev));
+    handler->num_sms = di->num_sms;
     handler->device = dev;
-  }
-  if (!handler->smem_configured) {
-    ADAMAS_CUDA(cudaFuncSetAttribute(sparse_decode_kernel<__half>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kDecStageBytes));
-    ADAMAS_CUDA(cudaFuncSetAttribute(sparse_decode_kernel<__nv_bfloat16>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kDecStageBytes));
-    handler->smem_configured = true;
   }
   const SplitPlan p = plan_splits(max_tokens, num_heads, handler->num_sms);
   const int64_t units = static_cast<int64_t>(num_heads) * p.num_splits;
@@ -454,7 +570,14 @@ int adamas_decode_forward(adamas_decode_handler_t* handler, const void* q, void*
   prm.idx_unit = idx_unit;
   prm.page_size = ps;
   prm.H = H;
-  prm.tail_slot0 = static_cast<int64_t>(last_page_idx) * ps + (last_page_len - tail_len);
+  const int64_t tail0 = static_cast<int64_t>(last_page_idx) * ps + (last_page_len - tail_len);
+  ADAMAS_REQUIRE(tail0 + tail_len < (int64_t(1) << 31), "token slots must be below 2^31");
+  prm.tail_slot0 = static_cast<unsigned>(tail0);
+  prm.ps_shift = -1;
+  if ((ps & (ps - 1)) == 0) {
+    prm.ps_shift = 0;
+    while ((1 << prm.ps_shift) < ps) ++prm.ps_shift;
+  }
   prm.n_tokens = static_cast<int>(n_tokens);
   prm.tiles_per_block = p.tiles_per_block;
   prm.num_splits = p.num_splits;

@@ -31,7 +31,8 @@ struct DecodeParams {
   int idx_unit;           // token slots covered by one index
   int page_size;
   int H;
-  int64_t tail_slot0;     // physical token slot of the first tail token
+  unsigned tail_slot0;    // physical token slot of the first tail token
+  int ps_shift;           // log2(page_size) or -1
   int n_tokens;           // n_idx * idx_unit + tail_len
   int tiles_per_block;
   int num_splits;
@@ -41,14 +42,8 @@ struct DecodeParams {
   float scale_log2;       // sm_scale * log2(e)
 };
 
-__device__ __forceinline__ float ld_cg_f32(const float* p) {
-  float v;
-  asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
-  return v;
-}
-
 template <typename T>
-__global__ void __launch_bounds__(kDecThreads) sparse_decode_kernel(DecodeParams prm) {
+__global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodeParams prm) {
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ float s_logit[kDecTile];
   __shared__ float s_p[kDecTile];
@@ -74,35 +69,56 @@ __global__ void __launch_bounds__(kDecThreads) sparse_decode_kernel(DecodeParams
   const int64_t v_delta = static_cast<int64_t>(prm.page_size) * H * kHeadDim;
 
   // ---- gather one tile into a stage --------------------------------------------------------------
-  // thread -> chunk c = tid % 16 of tokens tl = tid / 16 + 8 * i
+  // thread -> chunk c = tid % 16 of tokens tl = tid / 16 + 8 * i.  Slots are < 2^31 (checked on the
+  // host), so the index arithmetic is 32-bit; only the final element offset is 64-bit.
   auto issue_tile = [&](int tile, int stage) {
     uint8_t* sk = smem + stage * kDecStageBytes;
     uint8_t* sv = sk + kDecTile * kHeadDim * 2;
     const int c = tid & 15;
     const int t0 = tok_begin + tile * kDecTile;
-    int64_t slot[8];
+    const unsigned ps = static_cast<unsigned>(prm.page_size);
+    unsigned slot[8];
+    bool ok[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int tl = (tid >> 4) + 8 * i;
       const int j = t0 + tl;
-      slot[i] = -1;
-      if (j < tok_end) {
+      ok[i] = j < tok_end;
+      slot[i] = 0;
+      if (ok[i]) {
         if (j < n_listed) {
-          const int item = j / prm.idx_unit;
-          const int off = j - item * prm.idx_unit;
-          slot[i] = static_cast<int64_t>(__ldg(idx_row + item)) * prm.idx_unit + off;
+          if (prm.idx_unit == 1) {
+            slot[i] = static_cast<unsigned>(__ldg(idx_row + j));
+          } else {  // page-granular list: idx_unit == page_size
+            unsigned item, off;
+            if (prm.ps_shift >= 0) {
+              item = static_cast<unsigned>(j) >> prm.ps_shift;
+              off = static_cast<unsigned>(j) & (ps - 1);
+            } else {
+              item = static_cast<unsigned>(j) / ps;
+              off = static_cast<unsigned>(j) - item * ps;
+            }
+            slot[i] = static_cast<unsigned>(__ldg(idx_row + item)) * ps + off;
+          }
         } else {
-          slot[i] = prm.tail_slot0 + (j - n_listed);
+          slot[i] = prm.tail_slot0 + static_cast<unsigned>(j - n_listed);
         }
       }
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int tl = (tid >> 4) + 8 * i;
-      if (slot[i] >= 0) {
-        const int64_t page = slot[i] / prm.page_size;
-        const int64_t e = slot[i] - page * prm.page_size;
-        const T* kp = kvp + ((page * 2 * prm.page_size + e) * H + head) * kHeadDim + c * 8;
+      if (ok[i]) {
+        unsigned page, e;
+        if (prm.ps_shift >= 0) {
+          page = slot[i] >> prm.ps_shift;
+          e = slot[i] & (ps - 1);
+        } else {
+          page = slot[i] / ps;
+          e = slot[i] - page * ps;
+        }
+        const int64_t row = static_cast<int64_t>(page) * (2 * ps) + e;
+        const T* kp = kvp + (row * H + head) * kHeadDim + c * 8;
         const int phys = c ^ (tl & 3);
         cp_async_16(sk + tl * 256 + phys * 16, kp);
         cp_async_16(sv + tl * 256 + phys * 16, kp + v_delta);
@@ -239,20 +255,46 @@ __global__ void __launch_bounds__(kDecThreads) sparse_decode_kernel(DecodeParams
   if (!s_last) return;
   __threadfence();
 
+  // ---- merge by the last block of the head ---------------------------------------------------
+  // (m, l) of every split -> shared memory (the stage buffers are free now), then one pass per dim.
   const int64_t p0 = static_cast<int64_t>(head) * prm.num_splits;
-  float M = -INFINITY;
-  for (int s = 0; s < prm.num_splits; ++s) M = fmaxf(M, ld_cg_f32(prm.partial_ml + (p0 + s) * 2));
-  float accd = 0.f, L = 0.f;
-  for (int s = 0; s < prm.num_splits; ++s) {
-    const float w = exp2f(ld_cg_f32(prm.partial_ml + (p0 + s) * 2) - M);
-    L += w * ld_cg_f32(prm.partial_ml + (p0 + s) * 2 + 1);
-    accd += w * ld_cg_f32(prm.partial_o + (p0 + s) * kHeadDim + tid);
+  float* s_w = reinterpret_cast<float*>(smem);       // num_splits weights (fits: checked on the host)
+  float mloc = -INFINITY;
+  for (int s = tid; s < prm.num_splits; s += kDecThreads)
+    mloc = fmaxf(mloc, __ldcg(prm.partial_ml + (p0 + s) * 2));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, o));
+  if (lane == 0) s_red[warp] = mloc;
+  __syncthreads();
+  const float M = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+  float lloc = 0.f;
+  for (int s = tid; s < prm.num_splits; s += kDecThreads) {
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(prm.partial_ml + (p0 + s) * 2));
+    const float w = exp2f(ml.x - M);
+    s_w[s] = w;
+    lloc += w * ml.y;
   }
-  const float r = accd / L;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) lloc += __shfl_xor_sync(0xffffffffu, lloc, o);
+  if (lane == 0) s_sum[warp] = lloc;
+  __syncthreads();
+  const float Lsum = (s_sum[0] + s_sum[1]) + (s_sum[2] + s_sum[3]);
+  float accd = 0.f;
+  const float* po = prm.partial_o + p0 * kHeadDim + tid;
+  int s = 0;
+  for (; s + 8 <= prm.num_splits; s += 8) {
+    float t[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) t[u] = __ldcg(po + static_cast<int64_t>(s + u) * kHeadDim);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) accd = fmaf(s_w[s + u], t[u], accd);
+  }
+  for (; s < prm.num_splits; ++s) accd = fmaf(s_w[s], __ldcg(po + static_cast<int64_t>(s) * kHeadDim), accd);
+  const float r = accd / Lsum;
   const float r1 = __shfl_down_sync(0xffffffffu, r, 1);
   if ((tid & 1) == 0) reinterpret_cast<uint32_t*>(op)[tid >> 1] = Elem<T>::from_f2(r, r1);
   if (tid == 0) {
-    if (prm.lse) prm.lse[head] = M + log2f(L);
+    if (prm.lse) prm.lse[head] = M + log2f(Lsum);
     prm.counters[head] = 0;
   }
 }

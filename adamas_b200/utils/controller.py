@@ -150,8 +150,9 @@ class InferenceController:
         vdtype = self.dtype if self.dtype == torch.float16 else torch.int16
         if self._estimate_store is None or self._estimate_store.size(1) < n:
             cap = max(n, 1) if self._estimate_store is None else max(n, 2 * self._estimate_store.size(1))
-            cap = min(cap, self.kv_cache.pool.capacity * self.page_size)
-            self._estimate_store = torch.empty((self.num_heads, max(cap, n)), dtype=torch.int16, device=self.device)
+            cap = max(min(cap, self.kv_cache.pool.capacity * self.page_size), n)
+            cap = (cap + 7) // 8 * 8     # rows start on 16-byte boundaries (the top-k kernel's fast layout)
+            self._estimate_store = torch.empty((self.num_heads, cap), dtype=torch.int16, device=self.device)
         return self._estimate_store.view(vdtype)[:, :n]
 
     def clean_states(self):
