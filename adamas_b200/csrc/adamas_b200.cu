@@ -352,13 +352,15 @@ int adamas_topk(const void* values, int value_format, int64_t value_stride, int 
   const bool aligned = (reinterpret_cast<uintptr_t>(values) & 15) == 0 &&
                        (num_rows == 1 || (value_stride * 2) % 16 == 0);
   const int g_max = aligned ? (n + 7) / 8 : (n + 14) / 8;
+  // smallest ITEMS (granules per thread) that lets a cluster of up to 8 blocks cover the row
   int cl = 0, items = 0;
-  static const int kShapes[6][2] = {{1, 1}, {2, 1}, {4, 1}, {8, 1}, {8, 2}, {8, 4}};
-  for (const auto& sh : kShapes) {
-    if (static_cast<int64_t>(sh[0]) * sh[1] * kTopkThreads >= g_max) {
-      cl = sh[0];
-      items = sh[1];
-      break;
+  for (int it = 1; it <= 16 && cl == 0; it *= 2) {
+    for (int c = 1; c <= 8; c *= 2) {
+      if (static_cast<int64_t>(c) * it * kTopkClThreads >= g_max) {
+        cl = c;
+        items = it;
+        break;
+      }
     }
   }
   if (cl > 0) {
@@ -381,7 +383,7 @@ int adamas_topk(const void* values, int value_format, int64_t value_stride, int 
     prm.granules_per_block = (g_max + cl - 1) / cl;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(num_rows) * cl);
-    cfg.blockDim = dim3(kTopkThreads);
+    cfg.blockDim = dim3(kTopkClThreads);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -393,11 +395,20 @@ int adamas_topk(const void* values, int value_format, int64_t value_stride, int 
     cfg.numAttrs = 1;
     cudaError_t e = cudaSuccess;
 #define LAUNCH_TK(F, I) e = cudaLaunchKernelEx(&cfg, topk_cluster_kernel<F, I>, prm)
+#define LAUNCH_TK_ITEMS(F)                  \
+  switch (items) {                          \
+    case 1: LAUNCH_TK(F, 1); break;         \
+    case 2: LAUNCH_TK(F, 2); break;         \
+    case 4: LAUNCH_TK(F, 4); break;         \
+    case 8: LAUNCH_TK(F, 8); break;         \
+    default: LAUNCH_TK(F, 16); break;       \
+  }
     if (value_format == ADAMAS_VAL_F16) {
-      if (items == 1) LAUNCH_TK(0, 1); else if (items == 2) LAUNCH_TK(0, 2); else LAUNCH_TK(0, 4);
+      LAUNCH_TK_ITEMS(0)
     } else {
-      if (items == 1) LAUNCH_TK(1, 1); else if (items == 2) LAUNCH_TK(1, 2); else LAUNCH_TK(1, 4);
+      LAUNCH_TK_ITEMS(1)
     }
+#undef LAUNCH_TK_ITEMS
 #undef LAUNCH_TK
     if (e != cudaSuccess)
       return fail(ADAMAS_ERR_CUDA, "topk_cluster_kernel launch failed: %s", cudaGetErrorString(e));

@@ -269,24 +269,29 @@ topk_kernel(const uint16_t* __restrict__ values, int64_t value_stride, int n,
 // -------------------------------------------------------------------------------------------------
 // Cluster kernel.  A row is split over the CL thread blocks of a cluster (CL = 1, 2, 4 or 8); block
 // `cr` owns a contiguous range of 16-byte granules and every thread holds ITEMS consecutive
-// granules (8 values each) in registers for the whole kernel.
-//   1. histogram of the top 12 key bits in shared memory (4096 bins); cluster barrier; every block
-//      sums the CL histograms through distributed shared memory and scans them to find the bin that
-//      holds the k-th smallest key;
-//   2. histogram of the low 4 key bits inside that bin (16 bins); cluster barrier; same reduction:
-//      the exact cut key and the number of cut-valued elements to take;
-//   3. per-thread counts of (key < cut) and (key == cut), warp scan, block scan, cluster barrier,
-//      sum of the totals of the lower-ranked blocks: every thread knows the output position of each
-//      of its winners and writes them (ascending position order, lower position wins ties).
-// A final cluster barrier keeps every block's shared memory alive until its peers have read it.
+// granules (8 values each) in registers for the whole kernel, together with their sort keys.
+// Blocks never read each other's shared memory (remote loads are slow); they push:
+//   0. every block zeroes its accumulators; cluster barrier (all blocks have started);
+//   1. local histogram of the high key byte; the non-zero bins are added into the `total` array of
+//      EVERY block of the cluster with remote shared-memory reductions; cluster barrier; now each
+//      block holds the row's histogram and finds the bin of the k-th smallest key by itself;
+//   2. the same for the low key byte of the elements inside that bin: the exact cut key and the
+//      number of cut-valued elements to take;
+//   3. per-thread counts of (key < cut) and (key == cut), warp scan, block scan; every block adds
+//      its totals to the `base` of the higher-ranked blocks; cluster barrier; every thread knows the
+//      output position of each of its winners and writes them (ascending position order, lower
+//      position wins ties).
 // -------------------------------------------------------------------------------------------------
+constexpr int kTopkClThreads = 256;
+constexpr int kTopkClWarps = kTopkClThreads / 32;
+
 struct TopkClusterShared {
-  unsigned hist[4096];
-  unsigned hist2[16];
-  unsigned warp_a[kTopkWarps];
-  unsigned warp_b[kTopkWarps];
-  unsigned tot_lt;
-  unsigned tot_eq;
+  unsigned local[256];      // this block's histogram of the current pass
+  unsigned total[2][256];   // row histogram of pass 0 / pass 1 (filled by all blocks of the cluster)
+  unsigned warp_a[kTopkClWarps];
+  unsigned warp_b[kTopkClWarps];
+  unsigned base_lt;         // winners below the cut in lower-ranked blocks (filled by them)
+  unsigned base_eq;
   unsigned bucket;
   unsigned before;
 };
@@ -306,11 +311,58 @@ struct TopkParams {
   int granules_per_block;
 };
 
+// two packed 16-bit values -> two packed sort keys
+template <int FORMAT>
+__device__ __forceinline__ uint32_t to_key2(uint32_t w) {
+  if (FORMAT == 0) {
+    if ((w & 0xffffu) == 0x8000u) w &= 0xffff0000u;          // -0 -> +0
+    if ((w >> 16) == 0x8000u) w &= 0x0000ffffu;
+    const uint32_t neg = ((w >> 15) & 0x00010001u) * 0xffffu;  // 0xffff in the lanes with the sign set
+    return w ^ (neg | 0x80008000u);
+  }
+  return w;
+}
+
+// Executed by warp 0 on a 256-bin histogram in shared memory: smallest bin b with
+// sum(hist[0..b]) >= want; stores the bin and the count strictly before it.
+__device__ __forceinline__ void find_bin256(const unsigned* hist, unsigned want, unsigned* bucket,
+                                            unsigned* before) {
+  const unsigned lane = threadIdx.x & 31;
+  unsigned c[8];
+  unsigned s = 0;
+  const uint4 a = reinterpret_cast<const uint4*>(hist)[lane * 2];
+  const uint4 b = reinterpret_cast<const uint4*>(hist)[lane * 2 + 1];
+  c[0] = a.x; c[1] = a.y; c[2] = a.z; c[3] = a.w; c[4] = b.x; c[5] = b.y; c[6] = b.z; c[7] = b.w;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s += c[i];
+  unsigned incl = s;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  const unsigned hit = __ballot_sync(0xffffffffu, incl >= want);
+  const unsigned first = __ffs(hit) - 1;   // hit != 0: the histogram holds at least `want` elements
+  if (lane == first) {
+    unsigned run = incl - s;
+    int bsel = 7;
+    bool found = false;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (!found) {
+        if (run + c[i] >= want) { bsel = i; found = true; } else { run += c[i]; }
+      }
+    }
+    *bucket = lane * 8 + bsel;
+    *before = run;
+  }
+}
+
 template <int FORMAT, int ITEMS>
-__global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkParams p) {
+__global__ void __launch_bounds__(kTopkClThreads) topk_cluster_kernel(const TopkParams p) {
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
-  __shared__ TopkClusterShared sh;
+  __shared__ __align__(16) TopkClusterShared sh;
 
   const unsigned CL = cluster.num_blocks();
   const unsigned cr = cluster.block_rank();
@@ -318,6 +370,12 @@ __global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkPa
   const int tid = threadIdx.x;
   const unsigned lane = tid & 31;
   const unsigned warp = tid >> 5;
+
+  // zero the accumulators that peers will add into, then make sure every block has done so
+  sh.local[tid] = 0;
+  sh.total[0][tid] = 0;
+  sh.total[1][tid] = 0;
+  if (tid == 0) { sh.base_lt = 0; sh.base_eq = 0; }
 
   const uint16_t* rowp = p.values + static_cast<int64_t>(row) * p.value_stride;
   const uintptr_t addr = reinterpret_cast<uintptr_t>(rowp);
@@ -330,113 +388,75 @@ __global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkPa
   const int blk_first = cr * p.granules_per_block;
   const int blk_end = min(G, blk_first + p.granules_per_block);
   const int g0 = blk_first + tid * ITEMS;
-  uint4 v[ITEMS];
+  uint32_t raw[ITEMS][4];
+  uint32_t key[ITEMS][4];
+  unsigned vmask[ITEMS];   // bit j: element j of the granule belongs to the row
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
-    v[i] = make_uint4(0, 0, 0, 0);
-    if (g0 + i < blk_end) v[i] = ld_16(gbase + g0 + i);
-  }
-  for (int i = tid; i < 4096; i += kTopkThreads) sh.hist[i] = 0;
-  if (tid < 16) sh.hist2[tid] = 0;
-  __syncthreads();
-
-  // element accessors
-  auto raw_of = [&](int i, int j) -> unsigned {
-    const uint32_t w = (j >> 1) == 0 ? v[i].x : (j >> 1) == 1 ? v[i].y : (j >> 1) == 2 ? v[i].z : v[i].w;
-    return (w >> ((j & 1) * 16)) & 0xffffu;
-  };
-  auto valid = [&](int i, int j) -> bool {
-    const int e = (g0 + i) * 8 + j;
-    return (g0 + i < blk_end) && e >= lead && e < end;
-  };
-
-  // ---- pass 1: top 12 bits ------------------------------------------------------------------
-#pragma unroll
-  for (int i = 0; i < ITEMS; ++i) {
-    // a whole warp holding one single value (degenerate inputs) adds it with one update
-    const bool full = (g0 + i < blk_end) && (g0 + i) * 8 >= lead && (g0 + i) * 8 + 8 <= end;
-    const bool same = full && v[i].x == v[i].y && v[i].y == v[i].z && v[i].z == v[i].w &&
-                      (v[i].x >> 16) == (v[i].x & 0xffffu);
-    const unsigned first = __shfl_sync(0xffffffffu, v[i].x, 0);
-    if (__all_sync(0xffffffffu, same && v[i].x == first)) {
-      if (lane == 0) atomicAdd(&sh.hist[to_key<FORMAT>(first & 0xffffu) >> 4], 256u);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (valid(i, j)) atomicAdd(&sh.hist[to_key<FORMAT>(raw_of(i, j)) >> 4], 1u);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    unsigned m = 0;
+    const int g = g0 + i;
+    if (g < blk_end) {
+      v = ld_16(gbase + g);
+      const int e0 = g * 8;
+      m = 0xffu;
+      if (e0 < lead) m &= 0xffu << (lead - e0);
+      if (e0 + 8 > end) m &= 0xffu >> (e0 + 8 - end);
     }
+    raw[i][0] = v.x; raw[i][1] = v.y; raw[i][2] = v.z; raw[i][3] = v.w;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) key[i][q] = to_key2<FORMAT>(raw[i][q]);
+    vmask[i] = m;
   }
   cluster.sync();
 
-  // cluster-wide histogram of this thread's 4 bins, block scan, locate the k-th key's bin
-  {
-    unsigned c[4] = {0, 0, 0, 0};
-    for (unsigned r = 0; r < CL; ++r) {
-      const unsigned* rh = cluster.map_shared_rank(sh.hist, r);
-      const uint4 t = *reinterpret_cast<const uint4*>(rh + tid * 4);
-      c[0] += t.x; c[1] += t.y; c[2] += t.z; c[3] += t.w;
-    }
-    const unsigned s = c[0] + c[1] + c[2] + c[3];
-    unsigned incl = s;
+  unsigned prefix = 0;                              // key bits decided so far
+  unsigned want = static_cast<unsigned>(p.k);
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += t;
-    }
-    if (lane == 31) sh.warp_a[warp] = incl;
-    __syncthreads();
-    unsigned wbase = 0;
-    for (unsigned w2 = 0; w2 < warp; ++w2) wbase += sh.warp_a[w2];
-    const unsigned excl = wbase + incl - s;
-    const unsigned want = static_cast<unsigned>(p.k);
-    if (excl < want && excl + s >= want) {   // exactly one thread
-      unsigned run = excl;
-      int b = 3;
-      bool found = false;
+  for (int pass = 0; pass < 2; ++pass) {
+    // local histogram of the pass's byte
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        if (!found) {
-          if (run + c[i] >= want) { b = i; found = true; } else { run += c[i]; }
+    for (int i = 0; i < ITEMS; ++i) {
+      if (pass == 0) {
+        // a whole warp holding one single value (degenerate inputs) adds it with one update
+        const bool same = vmask[i] == 0xffu && key[i][0] == key[i][1] && key[i][1] == key[i][2] &&
+                          key[i][2] == key[i][3] && (key[i][0] >> 16) == (key[i][0] & 0xffffu);
+        const unsigned first = __shfl_sync(0xffffffffu, key[i][0], 0);
+        if (__all_sync(0xffffffffu, same && key[i][0] == first)) {
+          if (lane == 0) atomicAdd(&sh.local[(first >> 8) & 0xffu], 256u);
+          continue;
         }
       }
-      sh.bucket = tid * 4 + b;
-      sh.before = run;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const unsigned k16 = (key[i][j >> 1] >> ((j & 1) * 16)) & 0xffffu;
+        bool ok = (vmask[i] >> j) & 1u;
+        unsigned bin = k16 >> 8;
+        if (pass == 1) {
+          ok = ok && bin == prefix;
+          bin = k16 & 0xffu;
+        }
+        if (ok) atomicAdd(&sh.local[bin], 1u);
+      }
     }
     __syncthreads();
-  }
-  const unsigned bucket12 = sh.bucket;
-  unsigned want = static_cast<unsigned>(p.k) - sh.before;
-
-  // ---- pass 2: low 4 bits inside the bin ----------------------------------------------------------
-#pragma unroll
-  for (int i = 0; i < ITEMS; ++i) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const unsigned key = to_key<FORMAT>(raw_of(i, j));
-      if (valid(i, j) && (key >> 4) == bucket12) atomicAdd(&sh.hist2[key & 15u], 1u);
+    // push the non-zero bins to every block of the cluster (including this one)
+    {
+      const unsigned c = sh.local[tid];
+      if (c != 0) {
+        for (unsigned r = 0; r < CL; ++r) atomicAdd(cluster.map_shared_rank(&sh.total[pass][tid], r), c);
+      }
+      sh.local[tid] = 0;
     }
+    cluster.sync();
+    if (warp == 0) find_bin256(sh.total[pass], want, &sh.bucket, &sh.before);
+    __syncthreads();
+    prefix = (prefix << 8) | sh.bucket;
+    want -= sh.before;
+    __syncthreads();   // bucket / before are rewritten in the next pass
   }
-  cluster.sync();
-  if (warp == 0) {
-    unsigned c = 0;
-    if (lane < 16)
-      for (unsigned r = 0; r < CL; ++r) c += cluster.map_shared_rank(sh.hist2, r)[lane];
-    unsigned incl = c;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += t;
-    }
-    const unsigned hit = __ballot_sync(0xffffffffu, incl >= want);
-    const unsigned firstl = __ffs(hit) - 1;
-    if (lane == firstl) {
-      sh.bucket = (bucket12 << 4) | lane;
-      sh.before = incl - c;
-    }
-  }
-  __syncthreads();
-  const unsigned cut = sh.bucket;
-  const unsigned need_eq = want - sh.before;
+  const unsigned cut = prefix;
+  const unsigned need_eq = want;
 
   // ---- counts, scans ---------------------------------------------------------------------------------
   unsigned c_lt = 0, c_eq = 0;
@@ -444,10 +464,10 @@ __global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkPa
   for (int i = 0; i < ITEMS; ++i) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const unsigned key = to_key<FORMAT>(raw_of(i, j));
-      const bool ok = valid(i, j);
-      c_lt += (ok && key < cut);
-      c_eq += (ok && key == cut);
+      const unsigned k16 = (key[i][j >> 1] >> ((j & 1) * 16)) & 0xffffu;
+      const bool ok = (vmask[i] >> j) & 1u;
+      c_lt += (ok && k16 < cut);
+      c_eq += (ok && k16 == cut);
     }
   }
   unsigned i_lt = c_lt, i_eq = c_eq;
@@ -457,23 +477,25 @@ __global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkPa
     const unsigned b = __shfl_up_sync(0xffffffffu, i_eq, o);
     if (lane >= o) { i_lt += a; i_eq += b; }
   }
-  __syncthreads();   // warp_a is reused
   if (lane == 31) { sh.warp_a[warp] = i_lt; sh.warp_b[warp] = i_eq; }
   __syncthreads();
   unsigned base_lt = 0, base_eq = 0, blk_lt = 0, blk_eq = 0;
-  for (unsigned w2 = 0; w2 < kTopkWarps; ++w2) {
+#pragma unroll
+  for (unsigned w2 = 0; w2 < kTopkClWarps; ++w2) {
     const unsigned a = sh.warp_a[w2], b = sh.warp_b[w2];
     if (w2 < warp) { base_lt += a; base_eq += b; }
     blk_lt += a; blk_eq += b;
   }
-  if (tid == 0) { sh.tot_lt = blk_lt; sh.tot_eq = blk_eq; }
-  cluster.sync();
-  for (unsigned r = 0; r < cr; ++r) {
-    base_lt += *cluster.map_shared_rank(&sh.tot_lt, r);
-    base_eq += *cluster.map_shared_rank(&sh.tot_eq, r);
+  // this block's totals go to the bases of all higher-ranked blocks
+  if (tid < 2) {
+    const unsigned v = tid == 0 ? blk_lt : blk_eq;
+    if (v != 0)
+      for (unsigned r = cr + 1; r < CL; ++r)
+        atomicAdd(cluster.map_shared_rank(tid == 0 ? &sh.base_lt : &sh.base_eq, r), v);
   }
-  unsigned run_lt = base_lt + i_lt - c_lt;
-  unsigned run_eq = base_eq + i_eq - c_eq;
+  cluster.sync();
+  unsigned run_lt = sh.base_lt + base_lt + i_lt - c_lt;
+  unsigned run_eq = sh.base_eq + base_eq + i_eq - c_eq;
 
   // ---- emit -------------------------------------------------------------------------------------------
   if (c_lt | c_eq) {
@@ -484,11 +506,10 @@ __global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkPa
     for (int i = 0; i < ITEMS; ++i) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const unsigned raw = raw_of(i, j);
-        const unsigned key = to_key<FORMAT>(raw);
-        if (valid(i, j) && key <= cut) {
+        const unsigned k16 = (key[i][j >> 1] >> ((j & 1) * 16)) & 0xffffu;
+        if (((vmask[i] >> j) & 1u) && k16 <= cut) {
           int pos = -1;
-          if (key < cut) {
+          if (k16 < cut) {
             pos = static_cast<int>(run_lt + min(run_eq, need_eq));
             ++run_lt;
           } else {
@@ -510,13 +531,12 @@ __global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkPa
               id = __ldg(idx_row + pg) * p.idx_page_size + off;
             }
             oi[pos] = id;
-            if (ov) ov[pos] = static_cast<uint16_t>(raw);
+            if (ov) ov[pos] = static_cast<uint16_t>((raw[i][j >> 1] >> ((j & 1) * 16)) & 0xffffu);
           }
         }
       }
     }
   }
-  cluster.sync();   // peers may still be reading this block's totals
 }
 
 }  // namespace adamas
