@@ -44,6 +44,7 @@ SIGNATURES = {
     "adamas_decode_end_forward": [_P],
     "adamas_decode_forward": [_P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _P],
     "adamas_merge_states": [_P, _P, _I, _I, _I, _P, _P, _I, _P],
+    "adamas_device_error": [POINTER(ctypes.c_uint), _I],
 }
 
 for _name, _args in SIGNATURES.items():
@@ -69,6 +70,13 @@ def check(status: int, what: str) -> None:
     raise through TORCH_CHECK (adamas/ops/csrc/estimate.cu:77-83)."""
     if status != OK:
         raise RuntimeError(f"{what} failed: {last_error()}")
+
+
+def device_error(clear: bool = True) -> int:
+    """Error flags raised by kernels on the current device (0 = none); synchronises."""
+    flags = ctypes.c_uint(0)
+    check(lib.adamas_device_error(ctypes.byref(flags), int(clear)), "adamas_device_error")
+    return flags.value
 
 
 def thresholds_arg(thresholds):

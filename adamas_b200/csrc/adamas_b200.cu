@@ -117,6 +117,16 @@ inline unsigned rows_to_blocks(int64_t rows) { return static_cast<unsigned>((row
 extern "C" {
 
 int adamas_abi_version(void) { return ADAMAS_ABI_VERSION; }
+
+int adamas_device_error(unsigned* flags, int clear) {
+  ADAMAS_REQUIRE(flags, "null pointer");
+  ADAMAS_CUDA(cudaMemcpyFromSymbol(flags, g_adamas_error, sizeof(unsigned)));
+  if (clear && *flags) {
+    const unsigned zero = 0;
+    ADAMAS_CUDA(cudaMemcpyToSymbol(g_adamas_error, &zero, sizeof(unsigned)));
+  }
+  return ADAMAS_OK;
+}
 const char* adamas_last_error(void) { return g_err; }
 
 // ---------------------------------------------------------------------------------------------
@@ -284,7 +294,7 @@ int adamas_estimate(const void* q_code, const void* code_data, const int32_t* co
   if (int rc = get_device_info(&di)) return rc;
   const int num_tiles = (n + kEstTile - 1) / kEstTile;
   const int rounds = (kEstTile * 2 * num_heads + kEstThreads - 1) / kEstThreads;
-  const size_t smem = static_cast<size_t>(kEstStages) * rounds * kEstThreads * 16 +
+  const size_t smem = static_cast<size_t>(kEstStages) * kEstTile * 2 * num_heads * 16 +
                       2 * static_cast<size_t>(num_heads) * (kEstTile + 2) * sizeof(uint16_t);
   ADAMAS_REQUIRE(smem <= static_cast<size_t>(di->max_smem_optin - 1024),
                  "num_heads (%d) too large for the estimate kernel", num_heads);
@@ -309,7 +319,8 @@ int adamas_estimate(const void* q_code, const void* code_data, const int32_t* co
   prm.cpt_shift = log2_exact(2 * num_heads);
   prm.num_tiles = num_tiles;
   prm.rounds = rounds;
-  const bool fast = prm.ps_shift >= 0 && prm.cpt_shift >= 0 && 2 * num_heads <= kEstThreads;
+  prm.out_pairs_aligned = ((reinterpret_cast<uintptr_t>(out) & 3) == 0 && out_stride % 2 == 0) ? 1 : 0;
+  const bool fast = prm.cpt_shift >= 4 && 2 * num_heads <= kEstThreads;
   cudaStream_t st = to_stream(stream);
 #define LAUNCH_EST(M, OT)                                                                      \
   do {                                                                                         \

@@ -33,6 +33,49 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N));
 }
 
+// ---- mbarrier + bulk (TMA) copy, global -> shared ---------------------------------------------
+__device__ __forceinline__ unsigned smem_u32(const void* p) {
+  return static_cast<unsigned>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after `limit` polls (each poll may itself suspend for a while) and reports
+// failure instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity, unsigned limit) {
+  for (unsigned spin = 0; spin < limit; ++spin)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+// 1-D bulk copy of `bytes` (multiple of 16; src and dst 16-byte aligned); completion is signalled on
+// `bar` as transaction bytes.
+__device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gmem_src, unsigned bytes,
+                                              uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
 // ---- element conversion: 8 x 16-bit storage <-> 8 x fp32 -----------------------------------
 template <typename T>
 struct Elem;
@@ -78,6 +121,11 @@ __device__ __forceinline__ uint4 pack8(const float (&x)[8]) {
   v.w = Elem<T>::from_f2(x[6], x[7]);
   return v;
 }
+
+// Device-side error flags, readable through adamas_device_error().  A kernel that gives up on a
+// bounded wait sets a bit here and finishes normally.
+__device__ unsigned g_adamas_error = 0;
+constexpr unsigned kErrEstimateTimeout = 1u;
 
 struct Thresholds {
   float t0, t1, t2;

@@ -51,6 +51,12 @@ typedef void* adamas_stream_t;   /* a cudaStream_t */
 int adamas_abi_version(void);
 const char* adamas_last_error(void);
 
+/* Reads (and optionally clears) the current device's error flags.  Kernels never spin without a
+ * limit: one that gives up on a wait (bit 0: the estimate kernel's copy pipeline) sets a flag here and
+ * finishes, leaving wrong results behind.  Synchronises with the device.  No counterpart in the
+ * reference, whose kernels have no waits of this kind. */
+int adamas_device_error(unsigned* flags, int clear);
+
 /* ---- stage 1: Hadamard transform, bucketize, pack, append -------------------------------- */
 
 /* y[r, :] = round_to_dtype(scale * WHT_D(x[r, :])) for r < rows; D = head_dim = 128; x == y allowed.

@@ -463,6 +463,15 @@ def test_headline_size_properties_32k():
     _assert_attn_close(o[0], r["out"])
 
 
+def test_no_kernel_gave_up_on_a_wait():
+    """Runs after the estimate tests above: no bounded wait in a kernel has timed out."""
+    from adamas_b200 import _lib
+    st = State(5000, 32, 16, seed=5)
+    _, _, U = _mods()
+    U.decode_estimate(st.q_code, st.c, 0)
+    assert _lib.device_error(clear=False) == 0
+
+
 def test_merge_states_matches_oracle():
     _, K, _ = _mods()
     g = torch.Generator().manual_seed(3)
