@@ -1,6 +1,9 @@
 """Builds libadamas_b200.so (sm_100a only) next to this file with nvcc.
 
-    python -m adamas_b200.build [--force]
+    python adamas_b200/build.py [--force] [-v]
+
+(run it as a script: `python -m adamas_b200.build` imports the package first, which refuses to load
+when the library is missing or stale)
 """
 from __future__ import annotations
 
