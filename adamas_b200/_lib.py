@@ -18,7 +18,7 @@ VAL_F16, VAL_U16 = 0, 1
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
-        f"{LIB_PATH} is missing. Build it with `python -m adamas_b200.build` (needs nvcc); "
+        f"{LIB_PATH} is missing. Build it with `python adamas_b200/build.py` (needs nvcc); "
         "adamas_b200 has no fallback implementation.")
 
 lib = ctypes.CDLL(LIB_PATH)
@@ -43,12 +43,17 @@ SIGNATURES = {
     "adamas_decode_begin_forward": [_P, _L, _I, _I, _I, _I, _P],
     "adamas_decode_end_forward": [_P],
     "adamas_decode_forward": [_P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _P],
+    "adamas_decode_forward_static": [_P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P],
     "adamas_merge_states": [_P, _P, _I, _I, _I, _P, _P, _I, _P],
     "adamas_device_error": [POINTER(ctypes.c_uint), _I],
 }
 
 for _name, _args in SIGNATURES.items():
-    _fn = getattr(lib, _name)          # AttributeError here = stale library: rebuild
+    try:
+        _fn = getattr(lib, _name)
+    except AttributeError as exc:
+        raise ImportError(f"{LIB_PATH} does not export {_name}: it is stale, rebuild it with "
+                          "`python adamas_b200/build.py --force`") from exc
     _fn.argtypes = _args
     _fn.restype = c_int
 lib.adamas_abi_version.argtypes = []

@@ -617,6 +617,100 @@ int adamas_decode_forward(adamas_decode_handler_t* handler, const void* q, void*
   return check_launch("sparse_decode_kernel");
 }
 
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the sparse decode.  Its split-KV scratch (partial outputs, running
+// max / sum pairs and the per-head arrival counters) lives in the fixed array below instead of a
+// handler-owned cudaMalloc buffer.  Every device that loads this library keeps the array until
+// the process exits; all calls on a device share it.
+constexpr int kStaticMaxUnits = 2048;   // heads x splits
+constexpr int kStaticMaxHeads = 256;
+constexpr size_t kStaticOffMl = static_cast<size_t>(kStaticMaxUnits) * kHeadDim * sizeof(float);
+constexpr size_t kStaticOffCnt = kStaticOffMl + static_cast<size_t>(kStaticMaxUnits) * 2 * sizeof(float);
+constexpr size_t kStaticBytes = kStaticOffCnt + static_cast<size_t>(kStaticMaxHeads) * sizeof(unsigned);
+static __device__ __align__(256) unsigned char g_static_decode_scratch[kStaticBytes];
+
+int adamas_decode_forward_static(const void* q, void* o, float* lse, const void* kv_data,
+                                 const int32_t* indices, int64_t idx_stride, int n_idx, int idx_unit,
+                                 int num_heads, int head_dim, int page_size, int dtype,
+                                 int last_page_idx, int last_page_len, int tail_len, float sm_scale,
+                                 adamas_stream_t stream) {
+  if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
+  ADAMAS_REQUIRE(q && o && kv_data, "null pointer");
+  ADAMAS_REQUIRE(n_idx >= 0 && (n_idx == 0 || indices), "indices missing");
+  ADAMAS_REQUIRE(idx_unit == 1 || idx_unit == page_size, "idx_unit must be 1 or page_size");
+  ADAMAS_REQUIRE(tail_len >= 0 && tail_len <= last_page_len && last_page_len <= page_size,
+                 "tail_len / last_page_len out of range");
+  ADAMAS_REQUIRE(last_page_idx >= 0, "last_page_idx must be >= 0");
+  const int64_t n_tokens = static_cast<int64_t>(n_idx) * idx_unit + tail_len;
+  ADAMAS_REQUIRE(n_tokens >= 1, "nothing to attend to");
+  ADAMAS_REQUIRE(n_tokens < (int64_t(1) << 31) - kDecTile, "too many tokens");
+  ADAMAS_REQUIRE(idx_stride == 0 || idx_stride >= n_idx || num_heads == 1,
+                 "idx_stride must be 0 (shared row) or >= n_idx");
+
+  // Per-device set-up on the first call with that device current: the name of a __device__ array is
+  // only a host-side handle, so the address the kernel needs is looked up once and kept.
+  static void* scratch_ptr[64] = {};
+  int dev = 0;
+  ADAMAS_CUDA(cudaGetDevice(&dev));
+  ADAMAS_REQUIRE(dev >= 0 && dev < 64, "device ordinal out of range");
+  const DeviceInfo* di = nullptr;
+  if (int rc = get_device_info(&di)) return rc;
+  if (scratch_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    ADAMAS_CUDA(cudaGetSymbolAddress(&ptr, g_static_decode_scratch));
+    ADAMAS_REQUIRE(ptr != nullptr, "cudaGetSymbolAddress returned a null address");
+    scratch_ptr[dev] = ptr;
+  }
+
+  const SplitPlan p = plan_splits(n_tokens, num_heads, di->num_sms);
+  ADAMAS_REQUIRE(num_heads <= kStaticMaxHeads,
+                 "adamas_decode_forward_static supports at most %d heads (got %d)", kStaticMaxHeads,
+                 num_heads);
+  ADAMAS_REQUIRE(static_cast<int64_t>(num_heads) * p.num_splits <= kStaticMaxUnits,
+                 "adamas_decode_forward_static: %d heads x %d splits exceeds the fixed scratch of %d "
+                 "(head, split) units; use the handler-based adamas_decode_forward",
+                 num_heads, p.num_splits, kStaticMaxUnits);
+
+  uint8_t* base = static_cast<uint8_t*>(scratch_ptr[dev]);
+  cudaStream_t st = to_stream(stream);
+  // the arrival counters must start at zero whatever an earlier (possibly failed) call left behind
+  ADAMAS_CUDA(cudaMemsetAsync(base + kStaticOffCnt, 0, static_cast<size_t>(num_heads) * sizeof(unsigned), st));
+
+  DecodeParams prm;
+  prm.q = q;
+  prm.o = o;
+  prm.lse = lse;
+  prm.kv = kv_data;
+  prm.indices = indices ? indices : reinterpret_cast<const int32_t*>(kv_data);
+  prm.idx_stride = idx_stride;
+  prm.n_idx = n_idx;
+  prm.idx_unit = idx_unit;
+  prm.page_size = page_size;
+  prm.H = num_heads;
+  const int64_t tail0 = static_cast<int64_t>(last_page_idx) * page_size + (last_page_len - tail_len);
+  ADAMAS_REQUIRE(tail0 + tail_len < (int64_t(1) << 31), "token slots must be below 2^31");
+  prm.tail_slot0 = static_cast<unsigned>(tail0);
+  prm.ps_shift = -1;
+  if ((page_size & (page_size - 1)) == 0) {
+    prm.ps_shift = 0;
+    while ((1 << prm.ps_shift) < page_size) ++prm.ps_shift;
+  }
+  prm.n_tokens = static_cast<int>(n_tokens);
+  prm.tiles_per_block = p.tiles_per_block;
+  prm.num_splits = p.num_splits;
+  prm.partial_o = reinterpret_cast<float*>(base);
+  prm.partial_ml = reinterpret_cast<float*>(base + kStaticOffMl);
+  prm.counters = reinterpret_cast<unsigned*>(base + kStaticOffCnt);
+  prm.scale_log2 = sm_scale * 1.4426950408889634f;
+  const size_t smem = static_cast<size_t>(p.tiles_per_block > 1 ? 2 : 1) * kDecStageBytes;
+  dim3 grid(p.num_splits, num_heads);
+  if (dtype == ADAMAS_F16)
+    sparse_decode_kernel<__half><<<grid, kDecThreads, smem, st>>>(prm);
+  else
+    sparse_decode_kernel<__nv_bfloat16><<<grid, kDecThreads, smem, st>>>(prm);
+  return check_launch("sparse_decode_kernel (static scratch)");
+}
+
 int adamas_merge_states(const float* o_parts, const float* lse_parts, int num_parts, int num_heads,
                         int head_dim, void* o, float* lse, int dtype, adamas_stream_t stream) {
   ADAMAS_REQUIRE(head_dim == kHeadDim, "head_dim must be 128 (got %d)", head_dim);

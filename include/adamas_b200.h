@@ -171,6 +171,27 @@ int adamas_decode_forward(adamas_decode_handler_t* handler, const void* q, void*
                           int n_idx, int idx_unit, int last_page_idx, int last_page_len,
                           int tail_len, float sm_scale, adamas_stream_t stream);
 
+/* The same attention as adamas_decode_forward for callers that must not allocate device memory: code
+ * that runs while the process is not allowed to call cudaMalloc or cudaFree (a serving process whose
+ * memory manager has already claimed the whole device, a thread that cannot afford the device-wide
+ * synchronisation those calls imply).
+ * It needs no handler and no begin_forward: the split-KV scratch is a fixed array inside the library
+ * (about 1.1 MB of device memory, held by every GPU that loads the library until the process exits).
+ * Limits: num_heads <= 256 and num_heads * splits <= 2048 (head, split) units, where splits is the
+ * number of thread blocks the planner gives each head; larger requests are rejected with
+ * ADAMAS_ERR_INVALID and a message, and should use the handler-based call.
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress) and sets
+ * kernel attributes; make that first call outside any stream capture.  All calls on a device share
+ * the one array: two calls whose kernels may overlap on the GPU (different streams, no dependency)
+ * race on it; calls on one stream are safe.  Arguments as for adamas_decode_forward, plus the cache
+ * geometry that the handler otherwise carries.
+ * This entry point has no counterpart in the reference. */
+int adamas_decode_forward_static(const void* q, void* o, float* lse, const void* kv_data,
+                                 const int32_t* indices, int64_t idx_stride, int n_idx, int idx_unit,
+                                 int num_heads, int head_dim, int page_size, int dtype,
+                                 int last_page_idx, int last_page_len, int tail_len, float sm_scale,
+                                 adamas_stream_t stream);
+
 /* Merge P partial results over disjoint token sets: o_parts [P, H, D] fp32 (each already
  * normalised), lse_parts [P, H] base-2; writes o [H, D] in dtype and, optionally, lse [H].
  * Replaces VariableLengthMergeStates (called at kernels/include/decode/decode_attn.cuh:1050-1059);
