@@ -89,13 +89,14 @@ int get_device_info(const DeviceInfo** out) {
     ADAMAS_CUDA(cudaFuncSetAttribute(topk_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, d.topk_dyn_smem));
     ADAMAS_CUDA(cudaFuncSetAttribute(topk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, d.topk_dyn_smem));
     const int est_max = d.max_smem_optin - 1024;
-#define EST_ATTR(M, OT, F, R)                                                                      \
-  ADAMAS_CUDA(cudaFuncSetAttribute(estimate_kernel<M, OT, F, R>,                                   \
+#define EST_ATTR(M, OT, HPW)                                                                       \
+  ADAMAS_CUDA(cudaFuncSetAttribute(estimate_kernel<M, OT, HPW>,                                    \
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, est_max))
 #define EST_ATTR_ALL(M, OT) \
-  EST_ATTR(M, OT, true, 4); \
-  EST_ATTR(M, OT, true, 0); \
-  EST_ATTR(M, OT, false, 0)
+  EST_ATTR(M, OT, 0);       \
+  EST_ATTR(M, OT, 1);       \
+  EST_ATTR(M, OT, 2);       \
+  EST_ATTR(M, OT, 4)
     EST_ATTR_ALL(0, __half);
     EST_ATTR_ALL(0, uint16_t);
     EST_ATTR_ALL(1, __half);
@@ -293,19 +294,14 @@ int adamas_estimate(const void* q_code, const void* code_data, const int32_t* co
   const DeviceInfo* di = nullptr;
   if (int rc = get_device_info(&di)) return rc;
   const int num_tiles = (n + kEstTile - 1) / kEstTile;
-  const int rounds = (kEstTile * 2 * num_heads + kEstThreads - 1) / kEstThreads;
-  const size_t smem = static_cast<size_t>(kEstStages) * kEstTile * 2 * num_heads * 16 +
-                      2 * static_cast<size_t>(num_heads) * (kEstTile + 2) * sizeof(uint16_t);
+  const int hpw = (num_heads % kEstConsumerWarps == 0) ? num_heads / kEstConsumerWarps : 0;
+  const bool in_regs = hpw == 1 || hpw == 2 || hpw == 4;
+  const size_t smem = static_cast<size_t>(kEstStages) * kEstTile * (2 * num_heads + 1) * 16 +
+                      (in_regs ? 0 : static_cast<size_t>(2 * num_heads) * sizeof(QPlanes));
   ADAMAS_REQUIRE(smem <= static_cast<size_t>(di->max_smem_optin - 1024),
                  "num_heads (%d) too large for the estimate kernel", num_heads);
-  const int per_sm = smem * 2 <= static_cast<size_t>(di->max_smem_optin) ? 2 : 1;
+  const int per_sm = (smem + 1024) * 2 <= static_cast<size_t>(di->max_smem_optin) ? 2 : 1;
   const unsigned blocks = static_cast<unsigned>(std::min(num_tiles, di->num_sms * per_sm));
-  auto log2_exact = [](int v) {
-    if (v <= 0 || (v & (v - 1)) != 0) return -1;
-    int s = 0;
-    while ((1 << s) < v) ++s;
-    return s;
-  };
   EstimateParams prm;
   prm.codes = static_cast<const uint4*>(code_data);
   prm.page_table = code_page_table;
@@ -315,21 +311,23 @@ int adamas_estimate(const void* q_code, const void* code_data, const int32_t* co
   prm.n_tokens = n;
   prm.H = num_heads;
   prm.page_size = page_size;
-  prm.ps_shift = log2_exact(page_size);
-  prm.cpt_shift = log2_exact(2 * num_heads);
+  prm.ps_shift = -1;
+  if ((page_size & (page_size - 1)) == 0) {
+    prm.ps_shift = 0;
+    while ((1 << prm.ps_shift) < page_size) ++prm.ps_shift;
+  }
   prm.num_tiles = num_tiles;
-  prm.rounds = rounds;
-  prm.out_pairs_aligned = ((reinterpret_cast<uintptr_t>(out) & 3) == 0 && out_stride % 2 == 0) ? 1 : 0;
-  const bool fast = prm.cpt_shift >= 4 && 2 * num_heads <= kEstThreads;
   cudaStream_t st = to_stream(stream);
 #define LAUNCH_EST(M, OT)                                                                      \
   do {                                                                                         \
-    if (fast && rounds == 4)                                                                   \
-      estimate_kernel<M, OT, true, 4><<<blocks, kEstThreads, smem, st>>>(prm);                 \
-    else if (fast)                                                                             \
-      estimate_kernel<M, OT, true, 0><<<blocks, kEstThreads, smem, st>>>(prm);                 \
+    if (in_regs && hpw == 1)                                                                   \
+      estimate_kernel<M, OT, 1><<<blocks, kEstThreads, smem, st>>>(prm);                       \
+    else if (in_regs && hpw == 2)                                                              \
+      estimate_kernel<M, OT, 2><<<blocks, kEstThreads, smem, st>>>(prm);                       \
+    else if (in_regs && hpw == 4)                                                              \
+      estimate_kernel<M, OT, 4><<<blocks, kEstThreads, smem, st>>>(prm);                       \
     else                                                                                       \
-      estimate_kernel<M, OT, false, 0><<<blocks, kEstThreads, smem, st>>>(prm);                \
+      estimate_kernel<M, OT, 0><<<blocks, kEstThreads, smem, st>>>(prm);                       \
   } while (0)
   if (metric == ADAMAS_METRIC_L1) {
     if (out_format == ADAMAS_VAL_F16) LAUNCH_EST(0, __half); else LAUNCH_EST(0, uint16_t);

@@ -2,19 +2,18 @@
 //
 // The code of (token t, head h) is 32 bytes at ((page*page_size + entry)*H + h)*32 in the code
 // cache, so one token's codes for all heads are H*32 contiguous bytes.  The kernel is persistent:
-// gridDim.x blocks walk the token tiles round-robin.  A tile is kEstTile consecutive tokens, i.e. a
-// flat list of 16-byte chunks (2 per code).  Warp 0 is the producer: each of its lanes issues one
-// bulk (TMA) copy per token of the tile (the token's H codes, contiguous) into a kEstStages-deep
-// shared-memory ring, completion counted on one mbarrier per ring slot, so that several tiles are in
-// flight per block while one is being reduced.  All warps consume: every thread owns fixed chunk
-// positions of the tile; the two halves of a code sit in adjacent lanes and are summed with one
-// shfl.xor.  Waits on the mbarriers are bounded (a timeout sets a device error flag).  Distances are transposed through a small
-// double-buffered shared array so that the [H, n] output is written in runs along the token axis.
-//
-// The kernel is bound by integer instruction issue as much as by HBM, so index arithmetic is kept
-// out of the inner loops: in the FAST variant (2H a power of two between 16 and the block size) a
-// thread's chunk position inside a code is fixed and its token advances by a constant per round.
-//
+// gridDim.x blocks walk tiles of kEstTile = 32 consecutive tokens round-robin.
+//   * One producer warp: each lane issues one bulk (TMA) copy per token of the tile (the token's H
+//     codes) into a kEstStages-deep shared-memory ring; rows are padded by 16 bytes.  A "full"
+//     mbarrier per slot counts the bytes, an "empty" mbarrier per slot collects one arrival per
+//     consumer warp before the slot is refilled.
+//   * 16 consumer warps: lane l owns token l of the tile, a warp owns a set of heads.  A lane reads
+//     the two 16-byte halves of a code (the row padding makes the 32 lanes hit 32 different bank
+//     groups), reduces them in registers and stores the distance: the 32 lanes of a warp write 32
+//     consecutive tokens of one head, so the [H, n] output needs no transpose, no shuffle and no
+//     block barrier; the warps run decoupled from one another.
+// All mbarrier waits are bounded; a wait that runs out sets a device error flag and the kernel
+// finishes (with wrong results, which the flag reports).
 // The distance arithmetic on packed 2-bit codes is described at chunk_distance().
 #pragma once
 #include "common.cuh"
@@ -22,7 +21,8 @@
 namespace adamas {
 
 constexpr int kEstTile = 32;      // tokens per tile
-constexpr int kEstThreads = 512;
+constexpr int kEstConsumerWarps = 16;
+constexpr int kEstThreads = (kEstConsumerWarps + 1) * 32;   // 16 consumer warps + 1 producer warp
 constexpr int kEstStages = 3;     // ring depth (tiles in flight per block: kEstStages - 1)
 
 struct QPlanes {
@@ -91,43 +91,58 @@ struct EstimateParams {
   int H;
   int page_size;
   int ps_shift;     // log2(page_size) or -1
-  int cpt_shift;    // log2(2H) or -1
   int num_tiles;
-  int rounds;       // ceil(kEstTile * 2H / kEstThreads)
-  int out_pairs_aligned;  // out rows start on 4-byte boundaries (stride even, base aligned)
 };
 
-// Dynamic shared memory: kEstStages * kEstTile * H * 32 (ring) + 2 * H * (kEstTile + 2) * 2.
-// FAST requires cpt_shift >= 4 (H >= 8) and 2H <= kEstThreads.  ROUNDS > 0 makes the number of chunks per
-// thread and tile a compile-time constant (it must then equal p.rounds).
-template <int METRIC, typename OutT, bool FAST, int ROUNDS>
+// Dynamic shared memory: kEstStages * kEstTile * (2H + 1) * 16 bytes (ring), plus 2H * 32 bytes of
+// query planes when HPW == 0.
+// HPW > 0: H == kEstConsumerWarps * HPW and warp w keeps the query planes of heads w*HPW .. in
+// registers.  HPW == 0: any H, warp w handles heads w, w + 16, ... with the planes in shared memory.
+template <int METRIC, typename OutT, int HPW>
 __global__ void __launch_bounds__(kEstThreads) estimate_kernel(const EstimateParams p) {
   extern __shared__ uint4 est_smem[];
-  __shared__ __align__(8) uint64_t bars[kEstStages];
-  constexpr int PAD = kEstTile + 2;
+  __shared__ __align__(8) uint64_t full_bar[kEstStages];
+  __shared__ __align__(8) uint64_t empty_bar[kEstStages];
   const int tid = threadIdx.x;
   const int lane = tid & 31;
+  const int warp = tid >> 5;
   const int H = p.H;
-  const int cpt = 2 * H;  // 16-byte chunks per token
-  const int rounds = ROUNDS > 0 ? ROUNDS : p.rounds;
-  const int stage_chunks = kEstTile * cpt;
-  uint16_t* sdist = reinterpret_cast<uint16_t*>(est_smem + kEstStages * stage_chunks);
+  const int cpt = 2 * H;                      // 16-byte chunks per token
+  const int row_chunks = cpt + 1;             // padded row: lanes reading one chunk position of 32
+                                              // consecutive tokens hit 32 different bank groups
+  const int stage_chunks = kEstTile * row_chunks;
   OutT* out = static_cast<OutT*>(p.out);
 
   if (tid == 0) {
 #pragma unroll
-    for (int s = 0; s < kEstStages; ++s) mbar_init(&bars[s], 1);
+    for (int s = 0; s < kEstStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], kEstConsumerWarps);
+    }
     mbar_fence_init();
+  }
+  QPlanes* sq = reinterpret_cast<QPlanes*>(est_smem + kEstStages * stage_chunks);
+  if (HPW == 0) {
+    for (int c = tid; c < cpt; c += kEstThreads) sq[c] = make_qplanes<METRIC>(__ldg(p.q_code + c));
   }
   __syncthreads();
 
-  // Producer (warp 0, one lane per token of the tile): one bulk copy of the token's H codes.
-  auto produce = [&](int tile, int slot) {
-    if (tile < p.num_tiles) {
-      const int tile0 = tile * kEstTile;
+  const int my_tiles = (p.num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                       static_cast<int>(gridDim.x);
+
+  if (warp == kEstConsumerWarps) {
+    // ---- producer warp: one bulk copy per token (its H codes) into the padded ring slot -----------
+    const unsigned token_bytes = static_cast<unsigned>(cpt) * 16u;
+    int slot = 0;
+    unsigned parity = 0;   // parity of the previous use of the slot, for the empty barrier
+    for (int j = 0; j < my_tiles; ++j) {
+      const int tile0 = (blockIdx.x + j * gridDim.x) * kEstTile;
       const int tile_tokens = min(kEstTile, p.n_tokens - tile0);
-      const unsigned token_bytes = static_cast<unsigned>(cpt) * 16u;
-      if (lane == 0) mbar_arrive_expect_tx(&bars[slot], static_cast<unsigned>(tile_tokens) * token_bytes);
+      if (j >= kEstStages) {
+        // every consumer warp has finished reading the tile that used this slot before
+        if (!mbar_wait_bounded(&empty_bar[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
+      }
+      if (lane == 0) mbar_arrive_expect_tx(&full_bar[slot], static_cast<unsigned>(tile_tokens) * token_bytes);
       __syncwarp();
       if (lane < tile_tokens) {
         const int t = tile0 + lane;
@@ -140,93 +155,56 @@ __global__ void __launch_bounds__(kEstThreads) estimate_kernel(const EstimatePar
           e = t - lp * p.page_size;
         }
         const int64_t tok = static_cast<int64_t>(__ldg(p.page_table + lp)) * p.page_size + e;
-        bulk_copy_g2s(est_smem + slot * stage_chunks + lane * cpt, p.codes + tok * cpt, token_bytes,
-                      &bars[slot]);
+        bulk_copy_g2s(est_smem + slot * stage_chunks + lane * row_chunks, p.codes + tok * cpt, token_bytes,
+                      &full_bar[slot]);
+      }
+      if (++slot == kEstStages) {
+        slot = 0;
+        if (j >= kEstStages) parity ^= 1u;
       }
     }
-  };
-
-  // FAST: chunk position inside a code is fixed per thread, the token advances by tl_step per round
-  const int c_fixed = FAST ? (tid & (cpt - 1)) : 0;
-  const int tl_first = FAST ? (tid >> p.cpt_shift) : 0;
-  const int tl_step = FAST ? (kEstThreads >> p.cpt_shift) : 0;
-  const QPlanes qfix = make_qplanes<METRIC>(__ldg(p.q_code + c_fixed));
-  const int sd_base = (c_fixed >> 1) * PAD + tl_first;  // FAST: transpose slot of round 0
-
-  int tile = blockIdx.x;
-  if (tid < 32) {
-#pragma unroll
-    for (int s = 0; s < kEstStages - 1; ++s) produce(tile + s * gridDim.x, s);
+    return;
   }
 
-  int it = 0;
+  // ---- consumer warps: lane = token of the tile, a warp covers its heads -------------------------
+  QPlanes qp[HPW > 0 ? HPW : 1][2];
+  if (HPW > 0) {
+#pragma unroll
+    for (int hh = 0; hh < HPW; ++hh) {
+      qp[hh][0] = make_qplanes<METRIC>(__ldg(p.q_code + 2 * (warp * HPW + hh)));
+      qp[hh][1] = make_qplanes<METRIC>(__ldg(p.q_code + 2 * (warp * HPW + hh) + 1));
+    }
+  }
   int slot = 0;
   unsigned parity = 0;
-  for (; tile < p.num_tiles; tile += gridDim.x, ++it) {
-    int nslot = slot + (kEstStages - 1);
-    if (nslot >= kEstStages) nslot -= kEstStages;
-    if (tid < 32) produce(tile + (kEstStages - 1) * gridDim.x, nslot);
-
-    // bounded wait for this tile's bytes; on failure flag the error and carry on (results are
-    // then wrong, which the flag reports, but nothing spins forever)
-    if (!mbar_wait_bounded(&bars[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
-
-    const int tile0 = tile * kEstTile;
+  for (int j = 0; j < my_tiles; ++j) {
+    const int tile0 = (blockIdx.x + j * gridDim.x) * kEstTile;
     const int tile_tokens = min(kEstTile, p.n_tokens - tile0);
-    const uint4* srcp = est_smem + slot * stage_chunks + tid;
-    uint16_t* sd = sdist + (it & 1) * H * PAD;
-    if (FAST) {
-      unsigned d[ROUNDS > 0 ? ROUNDS : 1];
-      if (ROUNDS > 0) {
+    // bounded wait for this tile's bytes; on failure flag the error and carry on (results are then
+    // wrong, which the flag reports, but nothing spins forever)
+    if (!mbar_wait_bounded(&full_bar[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
+    const uint4* row = est_smem + slot * stage_chunks + lane * row_chunks;
+    OutT* o = out + tile0 + lane;
+    if (HPW > 0) {
+      unsigned d[HPW > 0 ? HPW : 1];
 #pragma unroll
-        for (int r = 0; r < ROUNDS; ++r) d[r] = chunk_distance<METRIC>(srcp[r * kEstThreads], qfix);
+      for (int hh = 0; hh < HPW; ++hh) {
+        const int h = warp * HPW + hh;
+        d[hh] = chunk_distance<METRIC>(row[2 * h], qp[hh][0]) + chunk_distance<METRIC>(row[2 * h + 1], qp[hh][1]);
+      }
+      if (lane < tile_tokens) {
 #pragma unroll
-        for (int r = 0; r < ROUNDS; ++r) d[r] += __shfl_xor_sync(0xffffffffu, d[r], 1);
-        if ((tid & 1) == 0) {
-#pragma unroll
-          for (int r = 0; r < ROUNDS; ++r) sd[sd_base + r * tl_step] = static_cast<uint16_t>(d[r]);
-        }
-      } else {
-        for (int r = 0; r < rounds; ++r) {
-          unsigned dd = chunk_distance<METRIC>(srcp[r * kEstThreads], qfix);
-          dd += __shfl_xor_sync(0xffffffffu, dd, 1);
-          if ((tid & 1) == 0) sd[sd_base + r * tl_step] = static_cast<uint16_t>(dd);
-        }
+        for (int hh = 0; hh < HPW; ++hh)
+          o[static_cast<int64_t>(warp * HPW + hh) * p.out_stride] = dist_to_out<OutT>(d[hh]);
       }
     } else {
-      const int total = kEstTile * cpt;
-      for (int r = 0; r < rounds; ++r) {
-        const int f = r * kEstThreads + tid;
-        const bool live = f < total;
-        const int tl = f / cpt;
-        const int c = f - tl * cpt;
-        uint4 kc = make_uint4(0, 0, 0, 0);
-        if (live) kc = srcp[r * kEstThreads];
-        const QPlanes qp = make_qplanes<METRIC>(__ldg(p.q_code + (live ? c : 0)));
-        unsigned d = chunk_distance<METRIC>(kc, qp);
-        d += __shfl_xor_sync(0xffffffffu, d, 1);
-        if (live && (c & 1) == 0) sd[(c >> 1) * PAD + tl] = static_cast<uint16_t>(d);
+      for (int h = warp; h < H; h += kEstConsumerWarps) {
+        const unsigned d = chunk_distance<METRIC>(row[2 * h], sq[2 * h]) + chunk_distance<METRIC>(row[2 * h + 1], sq[2 * h + 1]);
+        if (lane < tile_tokens) o[static_cast<int64_t>(h) * p.out_stride] = dist_to_out<OutT>(d);
       }
     }
-    __syncthreads();
-    // write out[h, tile0 + tl]: one thread per pair of tokens, consecutive threads -> consecutive
-    // pairs (tokens past the end of a partial tile hold stale bytes and are skipped)
-    for (int i = tid; i < H * (kEstTile / 2); i += kEstThreads) {
-      const int h = i / (kEstTile / 2);
-      const int tl = (i & (kEstTile / 2 - 1)) * 2;
-      const uint32_t two = *reinterpret_cast<const uint32_t*>(sd + h * PAD + tl);
-      OutT* o = out + static_cast<int64_t>(h) * p.out_stride + tile0 + tl;
-      const OutT lo = dist_to_out<OutT>(two & 0xffffu), hi = dist_to_out<OutT>(two >> 16);
-      if (p.out_pairs_aligned && tl + 1 < tile_tokens) {
-        uint32_t packed;
-        const uint16_t lo16 = *reinterpret_cast<const uint16_t*>(&lo), hi16 = *reinterpret_cast<const uint16_t*>(&hi);
-        packed = static_cast<uint32_t>(lo16) | (static_cast<uint32_t>(hi16) << 16);
-        *reinterpret_cast<uint32_t*>(o) = packed;
-      } else {
-        if (tl < tile_tokens) o[0] = lo;
-        if (tl + 1 < tile_tokens) o[1] = hi;
-      }
-    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[slot]);
     if (++slot == kEstStages) {
       slot = 0;
       parity ^= 1u;
