@@ -46,6 +46,7 @@ SIGNATURES = {
     "adamas_decode_forward_static": [_P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P],
     "adamas_merge_states": [_P, _P, _I, _I, _I, _P, _P, _I, _P],
     "adamas_device_error": [POINTER(ctypes.c_uint), _I],
+    "adamas_set_pdl": [_I],
 }
 
 for _name, _args in SIGNATURES.items():

@@ -6,6 +6,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdarg>
+#include <cstdlib>
 #include <cstdio>
 #include <cstring>
 #include <new>
@@ -111,6 +112,50 @@ int get_device_info(const DeviceInfo** out) {
   return ADAMAS_OK;
 }
 
+// Programmatic dependent launch of the hot kernels (on unless ADAMAS_PDL=0 or adamas_set_pdl(0)).
+int g_pdl = -1;
+bool pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* e = std::getenv("ADAMAS_PDL");
+    g_pdl = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_pdl != 0;
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                          int cluster, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  unsigned n = 0;
+  if (pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
+#define ADAMAS_LAUNCH(what, ...)                                                              \
+  do {                                                                                        \
+    cudaError_t le_ = launch_kernel(__VA_ARGS__);                                             \
+    if (le_ != cudaSuccess)                                                                   \
+      return fail(ADAMAS_ERR_CUDA, "%s launch failed: %s", what, cudaGetErrorString(le_));    \
+  } while (0)
+
 inline unsigned rows_to_blocks(int64_t rows) { return static_cast<unsigned>((rows * 16 + 255) / 256); }
 
 }  // namespace
@@ -118,6 +163,11 @@ inline unsigned rows_to_blocks(int64_t rows) { return static_cast<unsigned>((row
 extern "C" {
 
 int adamas_abi_version(void) { return ADAMAS_ABI_VERSION; }
+
+int adamas_set_pdl(int enable) {
+  g_pdl = enable ? 1 : 0;
+  return ADAMAS_OK;
+}
 
 int adamas_device_error(unsigned* flags, int clear) {
   ADAMAS_REQUIRE(flags, "null pointer");
@@ -187,10 +237,11 @@ static int append_decode_impl(const void* k, const void* v, const void* qh, cons
   const unsigned blocks = rows_to_blocks(num_heads);
   cudaStream_t st = to_stream(stream);
 #define LAUNCH_AD(T, F)                                                                         \
-  append_decode_kernel<T, F><<<blocks, 256, 0, st>>>(                                           \
-      static_cast<const T*>(k), static_cast<const T*>(v), static_cast<const T*>(qh),            \
-      static_cast<const T*>(kh), static_cast<uint16_t*>(q_code_out), tgt, kv_num_pages - 1,     \
-      kv_last_page_len - 1, code_num_pages - 1, code_last_page_len - 1, scale, th)
+  ADAMAS_LAUNCH("append_decode_kernel", append_decode_kernel<T, F>, dim3(blocks), dim3(256), 0, st, 1, \
+                static_cast<const T*>(k), static_cast<const T*>(v), static_cast<const T*>(qh),  \
+                static_cast<const T*>(kh), static_cast<uint16_t*>(q_code_out), tgt,             \
+                kv_num_pages - 1, kv_last_page_len - 1, code_num_pages - 1,                     \
+                code_last_page_len - 1, scale, th)
   if (dtype == ADAMAS_F16) {
     if (fused) LAUNCH_AD(__half, true); else LAUNCH_AD(__half, false);
   } else {
@@ -321,13 +372,13 @@ int adamas_estimate(const void* q_code, const void* code_data, const int32_t* co
 #define LAUNCH_EST(M, OT)                                                                      \
   do {                                                                                         \
     if (in_regs && hpw == 1)                                                                   \
-      estimate_kernel<M, OT, 1><<<blocks, kEstThreads, smem, st>>>(prm);                       \
+      ADAMAS_LAUNCH("estimate_kernel", estimate_kernel<M, OT, 1>, dim3(blocks), dim3(kEstThreads), smem, st, 1, prm);                       \
     else if (in_regs && hpw == 2)                                                              \
-      estimate_kernel<M, OT, 2><<<blocks, kEstThreads, smem, st>>>(prm);                       \
+      ADAMAS_LAUNCH("estimate_kernel", estimate_kernel<M, OT, 2>, dim3(blocks), dim3(kEstThreads), smem, st, 1, prm);                       \
     else if (in_regs && hpw == 4)                                                              \
-      estimate_kernel<M, OT, 4><<<blocks, kEstThreads, smem, st>>>(prm);                       \
+      ADAMAS_LAUNCH("estimate_kernel", estimate_kernel<M, OT, 4>, dim3(blocks), dim3(kEstThreads), smem, st, 1, prm);                       \
     else                                                                                       \
-      estimate_kernel<M, OT, 0><<<blocks, kEstThreads, smem, st>>>(prm);                       \
+      ADAMAS_LAUNCH("estimate_kernel", estimate_kernel<M, OT, 0>, dim3(blocks), dim3(kEstThreads), smem, st, 1, prm);                       \
   } while (0)
   if (metric == ADAMAS_METRIC_L1) {
     if (out_format == ADAMAS_VAL_F16) LAUNCH_EST(0, __half); else LAUNCH_EST(0, uint16_t);
@@ -390,20 +441,10 @@ int adamas_topk(const void* values, int value_format, int64_t value_stride, int 
     prm.out_idx = out_idx;
     prm.out_stride = out_stride;
     prm.granules_per_block = (g_max + cl - 1) / cl;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(num_rows) * cl);
-    cfg.blockDim = dim3(kTopkClThreads);
-    cfg.dynamicSmemBytes = 0;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = cl;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaSuccess;
-#define LAUNCH_TK(F, I) e = cudaLaunchKernelEx(&cfg, topk_cluster_kernel<F, I>, prm)
+    const dim3 tgrid(static_cast<unsigned>(num_rows) * cl);
+#define LAUNCH_TK(F, I)                                                                         \
+  ADAMAS_LAUNCH("topk_cluster_kernel", topk_cluster_kernel<F, I>, tgrid, dim3(kTopkClThreads), 0, st, \
+                cl, prm)
 #define LAUNCH_TK_ITEMS(F)                  \
   switch (items) {                          \
     case 1: LAUNCH_TK(F, 1); break;         \
@@ -419,8 +460,6 @@ int adamas_topk(const void* values, int value_format, int64_t value_stride, int 
     }
 #undef LAUNCH_TK_ITEMS
 #undef LAUNCH_TK
-    if (e != cudaSuccess)
-      return fail(ADAMAS_ERR_CUDA, "topk_cluster_kernel launch failed: %s", cudaGetErrorString(e));
     return check_launch("topk_cluster_kernel");
   }
 
@@ -609,9 +648,11 @@ int adamas_decode_forward(adamas_decode_handler_t* handler, const void* q, void*
   const size_t smem = static_cast<size_t>(p.tiles_per_block > 1 ? 2 : 1) * kDecStageBytes;
   dim3 grid(p.num_splits, H);
   if (handler->dtype == ADAMAS_F16)
-    sparse_decode_kernel<__half><<<grid, kDecThreads, smem, to_stream(stream)>>>(prm);
+    ADAMAS_LAUNCH("sparse_decode_kernel", sparse_decode_kernel<__half>, grid, dim3(kDecThreads), smem,
+                  to_stream(stream), 1, prm);
   else
-    sparse_decode_kernel<__nv_bfloat16><<<grid, kDecThreads, smem, to_stream(stream)>>>(prm);
+    ADAMAS_LAUNCH("sparse_decode_kernel", sparse_decode_kernel<__nv_bfloat16>, grid, dim3(kDecThreads), smem,
+                  to_stream(stream), 1, prm);
   return check_launch("sparse_decode_kernel");
 }
 

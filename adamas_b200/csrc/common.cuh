@@ -33,6 +33,17 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N));
 }
 
+// ---- programmatic dependent launch -----------------------------------------------------------
+// A kernel launched with the programmatic-serialization attribute may start while its predecessor in
+// the stream is still running.  grid_dependency_wait() returns once the predecessor has completed
+// and its writes are visible; everything before it may only touch data that was final before the
+// predecessor started.  grid_launch_dependents() lets the successor's blocks be scheduled as this
+// grid's blocks retire.  Both are no-ops for a normal launch.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---- mbarrier + bulk (TMA) copy, global -> shared ---------------------------------------------
 __device__ __forceinline__ unsigned smem_u32(const void* p) {
   return static_cast<unsigned>(__cvta_generic_to_shared(p));

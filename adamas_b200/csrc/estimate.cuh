@@ -123,6 +123,9 @@ __global__ void __launch_bounds__(kEstThreads) estimate_kernel(const EstimatePar
   }
   QPlanes* sq = reinterpret_cast<QPlanes*>(est_smem + kEstStages * stage_chunks);
   if (HPW == 0) {
+    // generic path: the query planes go through shared memory, so the query code (written by the
+    // preceding append kernel) is needed before the block barrier
+    grid_dependency_wait();
     for (int c = tid; c < cpt; c += kEstThreads) sq[c] = make_qplanes<METRIC>(__ldg(p.q_code + c));
   }
   __syncthreads();
@@ -163,10 +166,15 @@ __global__ void __launch_bounds__(kEstThreads) estimate_kernel(const EstimatePar
         if (j >= kEstStages) parity ^= 1u;
       }
     }
+    grid_launch_dependents();
     return;
   }
 
   // ---- consumer warps: lane = token of the tile, a warp covers its heads -------------------------
+  // The cached codes the producer streams were final before the preceding kernel started; the query
+  // code is that kernel's output, so the consumers wait for it here (the producer does not).
+  grid_dependency_wait();
+  grid_launch_dependents();
   QPlanes qp[HPW > 0 ? HPW : 1][2];
   if (HPW > 0) {
 #pragma unroll

@@ -99,6 +99,8 @@ append_decode_kernel(const T* __restrict__ k, const T* __restrict__ v, const T* 
                      const T* __restrict__ kh, uint16_t* __restrict__ q_code_out, PagedTarget tgt,
                      int kv_last_page, int kv_entry, int code_last_page, int code_entry, float scale,
                      Thresholds th) {
+  grid_dependency_wait();
+  grid_launch_dependents();
   // physical pages of the slot being written: last entries of the two page tables
   const int kv_page = __ldg(tgt.kv_table + kv_last_page);
   const int code_page = __ldg(tgt.code_table + code_last_page);

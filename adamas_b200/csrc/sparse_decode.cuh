@@ -127,8 +127,6 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
     cp_async_commit();
   };
 
-  issue_tile(0, 0);
-
   // ---- query: 64 dims per thread, in the order the thread walks its chunks ---------------------
   // thread pair (tl = tid / 2, half = tid % 2); step i reads logical chunk half*8 + (i ^ half*4)
   const int qk_tl = tid >> 1;
@@ -144,6 +142,11 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
       for (int d = 0; d < 8; ++d) qreg[i][d] *= prm.scale_log2;
     }
   }
+
+  // the index list is the preceding kernel's output
+  grid_dependency_wait();
+  grid_launch_dependents();
+  issue_tile(0, 0);
 
   float m_run = -INFINITY, l_run = 0.f;
   float o_acc[8];

@@ -371,7 +371,8 @@ __global__ void __launch_bounds__(kTopkClThreads) topk_cluster_kernel(const Topk
   const unsigned lane = tid & 31;
   const unsigned warp = tid >> 5;
 
-  // zero the accumulators that peers will add into, then make sure every block has done so
+  // zero the accumulators that peers will add into, then make sure every block has done so; all of
+  // this can run while the kernel that produces `values` is still finishing
   sh.local[tid] = 0;
   sh.total[0][tid] = 0;
   sh.total[1][tid] = 0;
@@ -383,11 +384,14 @@ __global__ void __launch_bounds__(kTopkClThreads) topk_cluster_kernel(const Topk
   const uint4* gbase = reinterpret_cast<const uint4*>(addr & ~static_cast<uintptr_t>(15));
   const int G = (lead + p.n + 7) >> 3;
   const int end = lead + p.n;
-
-  // this thread's granules: g0 .. g0 + ITEMS - 1 (inside the block's range and the row)
   const int blk_first = cr * p.granules_per_block;
   const int blk_end = min(G, blk_first + p.granules_per_block);
   const int g0 = blk_first + tid * ITEMS;
+  cluster.sync();
+  grid_dependency_wait();
+  grid_launch_dependents();
+
+  // this thread's granules: g0 .. g0 + ITEMS - 1 (inside the block's range and the row)
   uint32_t raw[ITEMS][4];
   uint32_t key[ITEMS][4];
   unsigned vmask[ITEMS];   // bit j: element j of the granule belongs to the row
@@ -408,7 +412,6 @@ __global__ void __launch_bounds__(kTopkClThreads) topk_cluster_kernel(const Topk
     for (int q = 0; q < 4; ++q) key[i][q] = to_key2<FORMAT>(raw[i][q]);
     vmask[i] = m;
   }
-  cluster.sync();
 
   unsigned prefix = 0;                              // key bits decided so far
   unsigned want = static_cast<unsigned>(p.k);

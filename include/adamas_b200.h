@@ -57,6 +57,13 @@ const char* adamas_last_error(void);
  * reference, whose kernels have no waits of this kind. */
 int adamas_device_error(unsigned* flags, int clear);
 
+/* Turns programmatic dependent launch of the decode-step kernels (append, estimate, top-k, sparse
+ * decode) on or off for this process; on by default, ADAMAS_PDL=0 in the environment turns it off.
+ * With it a kernel's set-up overlaps the tail of the kernel before it on the same stream; every
+ * kernel still waits for its predecessor to complete before it reads that kernel's results.  The
+ * reference launches everything on the legacy default stream (e.g. adamas/ops/csrc/page.cu:99). */
+int adamas_set_pdl(int enable);
+
 /* ---- stage 1: Hadamard transform, bucketize, pack, append -------------------------------- */
 
 /* y[r, :] = round_to_dtype(scale * WHT_D(x[r, :])) for r < rows; D = head_dim = 128; x == y allowed.
