@@ -185,10 +185,11 @@ def append_kv_cache_prefill(k, v, h, kv_data, kv_indices, kv_indptr, kv_last_pag
 # stage 2
 # ----------------------------------------------------------------------------------------------
 def estimate_attn_score(q, o, metadata_data, metadata_indices, metadata_indptr, metadata_last_page_len,
-                        metadata_last_page_idx, layout, metric: str = "l1") -> None:
+                        metadata_last_page_idx, layout, metric: str = "l1", exclude_last: bool = True) -> None:
     """adamas/ops/csrc/estimate.cu:6-84.  q [1,H,D/8] packed query code; o [H, n] with
     n = (pages-1)*page_size + last_page_len - 1 (newest token excluded); o.dtype float16 stores the
-    distances as fp16 (reference), int16 as integers."""
+    distances as fp16 (reference), int16 as integers.  exclude_last=False covers every cached token
+    (a sequence shard that does not hold the newest token)."""
     _nhd_only(layout)
     _check_input(q, "q", 3)
     _check_rows(o, "o")
@@ -201,13 +202,14 @@ def estimate_attn_score(q, o, metadata_data, metadata_indices, metadata_indptr, 
     _require(metadata_data.size(3) == num_heads and metadata_data.size(4) == code_words and code_words == 16,
              "hadamard_data must be [pages, 1, page_size, num_heads, 16]")
     _require(q.element_size() == 2 and metadata_data.element_size() == 2, "codes must be 16-bit words")
-    n = (metadata_indices.numel() - 1) * page_size + int(metadata_last_page_len) - 1
+    n = (metadata_indices.numel() - 1) * page_size + int(metadata_last_page_len) - (1 if exclude_last else 0)
     _require(o.size(0) == num_heads and o.size(1) == n, f"o must be [{num_heads}, {n}]")
     _lib.check(lib.adamas_estimate(
         _ptr(q), _ptr(metadata_data), _ptr(metadata_indices), metadata_indices.numel(),
         int(metadata_last_page_len), page_size, num_heads, code_words * 8, _ptr(o), o.stride(0),
         _value_format(o.dtype, "Estimate_attn_score"),
-        {"l1": _lib.METRIC_L1, "xor": _lib.METRIC_XOR}[metric], _stream()), "Estimate_attn_score")
+        {"l1": _lib.METRIC_L1, "xor": _lib.METRIC_XOR}[metric], 1 if exclude_last else 0, _stream()),
+        "Estimate_attn_score")
 
 
 # ----------------------------------------------------------------------------------------------
@@ -296,20 +298,25 @@ class BatchDecodeWithPagedKVCachePyTorchWrapper:
 
     def forward(self, q, o, paged_kv_data, paged_kv_indices, paged_kv_indptr, paged_kv_last_page_len,
                 paged_kv_last_page_idx, rope_scale=1.0, rope_theta=1e4, token_granular: bool = False,
-                lse: Optional[torch.Tensor] = None) -> None:
+                lse: Optional[torch.Tensor] = None, tail_len: Optional[int] = None,
+                o_f32: Optional[torch.Tensor] = None) -> None:
         """q, o [1,H,D]; paged_kv_indices [H, n] per-head page ids (the reference's meaning: each
         page is attended in full, then the last page's last_page_len entries).  With
         token_granular=True the entries are physical token slots (page*page_size + entry) and only
-        the newest token is appended."""
+        the newest token is appended; negative entries are holes.  `tail_len` overrides the number of
+        trailing entries of the last page that are always attended (0: none, for a shard that does
+        not hold the newest token).  With `o_f32` (float32 [H, D], needs `lse`) the result is written
+        there unrounded instead of into `o` (partial result of a sequence shard)."""
         if not self._started:
             raise RuntimeError("BatchDecodeWithPagedKVCache failed with error: forward called before begin_forward")
         _check_input(q, "q", 3)
-        _check_input(o, "o", 3)
+        if o_f32 is None:
+            _check_input(o, "o", 3)
         _check_input(paged_kv_data, "paged_kv_data", 5)
         _check_rows(paged_kv_indices, "paged_kv_indices")
         num_heads, head_dim, page_size, dt = self._cfg
         _require(q.size(0) == 1 and q.size(1) == num_heads and q.size(2) == head_dim, "q must be [1, H, D]")
-        _require(tuple(o.shape) == tuple(q.shape) and o.dtype == q.dtype, "o must match q")
+        _require(o_f32 is not None or (tuple(o.shape) == tuple(q.shape) and o.dtype == q.dtype), "o must match q")
         _require(paged_kv_data.size(1) == 2 and paged_kv_data.size(2) == page_size
                  and paged_kv_data.size(3) == num_heads and paged_kv_data.size(4) == head_dim,
                  "paged_kv_data must be [pages, 2, page_size, H, D]")
@@ -320,6 +327,8 @@ class BatchDecodeWithPagedKVCachePyTorchWrapper:
         n_idx = paged_kv_indices.size(1)
         unit = 1 if token_granular else page_size
         tail = 1 if token_granular else int(paged_kv_last_page_len)
+        if tail_len is not None:
+            tail = int(tail_len)
         n_tokens = n_idx * unit + tail
         if n_tokens > self._planned_tokens:
             _lib.check(lib.adamas_decode_begin_forward(self._handle, n_tokens, num_heads, head_dim, page_size, dt,
@@ -328,6 +337,14 @@ class BatchDecodeWithPagedKVCachePyTorchWrapper:
         if lse is not None:
             _require(lse.is_cuda and lse.dtype == torch.float32 and lse.numel() == num_heads and lse.is_contiguous(),
                      "lse must be a contiguous float32 CUDA tensor of H elements")
+        if o_f32 is not None:
+            _require(lse is not None and o_f32.is_cuda and o_f32.dtype == torch.float32 and o_f32.is_contiguous()
+                     and o_f32.numel() == num_heads * head_dim, "o_f32 must be float32 [H, D] and lse given")
+            _lib.check(lib.adamas_decode_forward_partial(
+                self._handle, _ptr(q), _ptr(o_f32), _ptr(lse), _ptr(paged_kv_data), _ptr(paged_kv_indices),
+                paged_kv_indices.stride(0), n_idx, unit, int(paged_kv_last_page_idx), int(paged_kv_last_page_len),
+                tail, 1.0 / math.sqrt(head_dim), _stream()), "BatchDecodeWithPagedKVCache")
+            return
         _lib.check(lib.adamas_decode_forward(
             self._handle, _ptr(q), _ptr(o), _ptr(lse), _ptr(paged_kv_data), _ptr(paged_kv_indices),
             paged_kv_indices.stride(0), n_idx, unit, int(paged_kv_last_page_idx), int(paged_kv_last_page_len), tail,

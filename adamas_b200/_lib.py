@@ -36,13 +36,14 @@ SIGNATURES = {
     "adamas_append_decode": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _FP, _I, _P],
     "adamas_append_decode_fused": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _FP, _I, _P],
     "adamas_append_prefill": [_P, _P, _P, _L, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _FP, _I, _P],
-    "adamas_estimate": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _L, _I, _I, _P],
+    "adamas_estimate": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _L, _I, _I, _I, _P],
     "adamas_topk": [_P, _I, _L, _I, _P, _L, _I, _I, _I, _P, _P, _L, _P],
     "adamas_decode_handler_create": [POINTER(c_void_p)],
     "adamas_decode_handler_destroy": [_P],
     "adamas_decode_begin_forward": [_P, _L, _I, _I, _I, _I, _P],
     "adamas_decode_end_forward": [_P],
     "adamas_decode_forward": [_P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _P],
+    "adamas_decode_forward_partial": [_P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _P],
     "adamas_decode_forward_static": [_P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P],
     "adamas_merge_states": [_P, _P, _I, _I, _I, _P, _P, _I, _P],
     "adamas_device_error": [POINTER(ctypes.c_uint), _I],

@@ -324,7 +324,7 @@ int adamas_append_prefill(const void* k, const void* v, const void* h, int64_t n
 int adamas_estimate(const void* q_code, const void* code_data, const int32_t* code_page_table,
                     int code_num_pages, int code_last_page_len, int page_size, int num_heads,
                     int head_dim, void* out, int64_t out_stride, int out_format, int metric,
-                    adamas_stream_t stream) {
+                    int exclude_last, adamas_stream_t stream) {
   if (int rc = check_common(num_heads, head_dim, page_size, ADAMAS_F16)) return rc;
   ADAMAS_REQUIRE(code_num_pages >= 1, "page table must not be empty");
   ADAMAS_REQUIRE(code_last_page_len >= 1 && code_last_page_len <= page_size,
@@ -332,7 +332,9 @@ int adamas_estimate(const void* q_code, const void* code_data, const int32_t* co
   ADAMAS_REQUIRE(out_format == ADAMAS_VAL_F16 || out_format == ADAMAS_VAL_U16, "bad out_format %d",
                  out_format);
   ADAMAS_REQUIRE(metric == ADAMAS_METRIC_L1 || metric == ADAMAS_METRIC_XOR, "bad metric %d", metric);
-  const int64_t n64 = static_cast<int64_t>(code_num_pages - 1) * page_size + code_last_page_len - 1;
+  ADAMAS_REQUIRE(exclude_last == 0 || exclude_last == 1, "exclude_last must be 0 or 1");
+  const int64_t n64 =
+      static_cast<int64_t>(code_num_pages - 1) * page_size + code_last_page_len - exclude_last;
   ADAMAS_REQUIRE(n64 < (int64_t(1) << 31) - kEstTile, "sequence too long");
   const int n = static_cast<int>(n64);
   if (n == 0) return ADAMAS_OK;
@@ -591,14 +593,15 @@ int adamas_decode_end_forward(adamas_decode_handler_t* handler) {
   return ADAMAS_OK;
 }
 
-int adamas_decode_forward(adamas_decode_handler_t* handler, const void* q, void* o, float* lse,
-                          const void* kv_data, const int32_t* indices, int64_t idx_stride, int n_idx,
-                          int idx_unit, int last_page_idx, int last_page_len, int tail_len,
-                          float sm_scale, adamas_stream_t stream) {
+static int decode_forward_impl(adamas_decode_handler_t* handler, const void* q, void* o, float* o_f32,
+                               float* lse, const void* kv_data, const int32_t* indices,
+                               int64_t idx_stride, int n_idx, int idx_unit, int last_page_idx,
+                               int last_page_len, int tail_len, float sm_scale,
+                               adamas_stream_t stream) {
   ADAMAS_REQUIRE(handler, "null handler");
   if (!handler->forward_started)
     return fail(ADAMAS_ERR_STATE, "decode forward called before begin_forward");
-  ADAMAS_REQUIRE(q && o && kv_data, "null pointer");
+  ADAMAS_REQUIRE(q && (o || o_f32) && kv_data, "null pointer");
   ADAMAS_REQUIRE(n_idx >= 0 && (n_idx == 0 || indices), "indices missing");
   const int ps = handler->page_size;
   ADAMAS_REQUIRE(idx_unit == 1 || idx_unit == ps, "idx_unit must be 1 or page_size");
@@ -621,6 +624,7 @@ int adamas_decode_forward(adamas_decode_handler_t* handler, const void* q, void*
   DecodeParams prm;
   prm.q = q;
   prm.o = o;
+  prm.o_f32 = o_f32;
   prm.lse = lse;
   prm.kv = kv_data;
   prm.indices = indices ? indices : reinterpret_cast<const int32_t*>(kv_data);
@@ -654,6 +658,23 @@ int adamas_decode_forward(adamas_decode_handler_t* handler, const void* q, void*
     ADAMAS_LAUNCH("sparse_decode_kernel", sparse_decode_kernel<__nv_bfloat16>, grid, dim3(kDecThreads), smem,
                   to_stream(stream), 1, prm);
   return check_launch("sparse_decode_kernel");
+}
+
+int adamas_decode_forward(adamas_decode_handler_t* handler, const void* q, void* o, float* lse,
+                          const void* kv_data, const int32_t* indices, int64_t idx_stride, int n_idx,
+                          int idx_unit, int last_page_idx, int last_page_len, int tail_len,
+                          float sm_scale, adamas_stream_t stream) {
+  return decode_forward_impl(handler, q, o, nullptr, lse, kv_data, indices, idx_stride, n_idx, idx_unit,
+                             last_page_idx, last_page_len, tail_len, sm_scale, stream);
+}
+
+int adamas_decode_forward_partial(adamas_decode_handler_t* handler, const void* q, float* o_f32,
+                                  float* lse, const void* kv_data, const int32_t* indices,
+                                  int64_t idx_stride, int n_idx, int idx_unit, int last_page_idx,
+                                  int last_page_len, int tail_len, float sm_scale,
+                                  adamas_stream_t stream) {
+  return decode_forward_impl(handler, q, nullptr, o_f32, lse, kv_data, indices, idx_stride, n_idx,
+                             idx_unit, last_page_idx, last_page_len, tail_len, sm_scale, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -718,6 +739,7 @@ int adamas_decode_forward_static(const void* q, void* o, float* lse, const void*
   DecodeParams prm;
   prm.q = q;
   prm.o = o;
+  prm.o_f32 = nullptr;
   prm.lse = lse;
   prm.kv = kv_data;
   prm.indices = indices ? indices : reinterpret_cast<const int32_t*>(kv_data);

@@ -22,7 +22,8 @@ constexpr int kDecStageBytes = 2 * kDecTile * kHeadDim * 2;  // K + V rows of on
 
 struct DecodeParams {
   const void* q;          // [H, 128]
-  void* o;                // [H, 128]
+  void* o;                // [H, 128] in the cache's element type, or null
+  float* o_f32;           // [H, 128] fp32 output (partial results of a sequence shard), or null
   float* lse;             // [H] or null (base-2 log-sum-exp of the scaled logits)
   const void* kv;         // [pages, 2, page_size, H, 128]
   const int32_t* indices; // [H, idx_stride]
@@ -46,6 +47,7 @@ template <typename T>
 __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodeParams prm) {
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ float s_logit[kDecTile];
+  __shared__ unsigned char s_skip[2][kDecTile];   // per stage: token masked out (negative index)
   __shared__ float s_p[kDecTile];
   __shared__ float s_red[4];
   __shared__ float s_sum[4];
@@ -88,7 +90,9 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
       if (ok[i]) {
         if (j < n_listed) {
           if (prm.idx_unit == 1) {
-            slot[i] = static_cast<unsigned>(__ldg(idx_row + j));
+            const int32_t id = __ldg(idx_row + j);
+            ok[i] = id >= 0;   // a negative entry is a hole in the list: the token is skipped
+            slot[i] = static_cast<unsigned>(id);
           } else {  // page-granular list: idx_unit == page_size
             unsigned item, off;
             if (prm.ps_shift >= 0) {
@@ -108,6 +112,7 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int tl = (tid >> 4) + 8 * i;
+      if (c == 0) s_skip[stage][tl] = ok[i] ? 0 : 1;
       if (ok[i]) {
         unsigned page, e;
         if (prm.ps_shift >= 0) {
@@ -170,7 +175,8 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
 
     // logits
     float acc = 0.f;
-    if (qk_tl < tile_tokens) {
+    const bool qk_live = qk_tl < tile_tokens && s_skip[stage][qk_tl] == 0;
+    if (qk_live) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int lc = half * 8 + (i ^ (half * 4));
@@ -182,7 +188,7 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
       }
     }
     acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-    const float logit = (qk_tl < tile_tokens) ? acc : -INFINITY;
+    const float logit = qk_live ? acc : -INFINITY;
     if (half == 0) s_logit[qk_tl] = logit;
     float wmax = logit;
 #pragma unroll
@@ -195,7 +201,8 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
     const float rescale = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
     float psum = 0.f;
     if (tid < kDecTile) {
-      const float p = exp2f(s_logit[tid] - m_new);  // exp2(-inf) = 0 for masked tokens
+      const float lg = s_logit[tid];
+      const float p = (lg == -INFINITY) ? 0.f : exp2f(lg - m_new);   // masked tokens weigh nothing
       s_p[tid] = p;
       psum = p;
     }
@@ -213,7 +220,7 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
     for (int i = 0; i < 8; ++i) {
       const int tl = pv_g * 8 + i;
       const float p = s_p[tl];
-      if (tl < tile_tokens) {
+      if (p != 0.f) {   // masked or absent tokens: their rows in shared memory are stale
         const int phys = pv_c ^ (tl & 3);
         float vf[8];
         unpack8<T>(*reinterpret_cast<const uint4*>(sv + tl * 256 + phys * 16), vf);
@@ -234,11 +241,12 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
 
   T* op = static_cast<T*>(prm.o) + static_cast<int64_t>(head) * kHeadDim;
   if (prm.num_splits == 1) {
-    const float r = od / l_run;
+    const float r = l_run > 0.f ? od / l_run : 0.f;   // nothing attended: zeros and lse = -inf
     // pairs of threads share a 32-bit store
     const float r1 = __shfl_down_sync(0xffffffffu, r, 1);
-    if ((tid & 1) == 0) reinterpret_cast<uint32_t*>(op)[tid >> 1] = Elem<T>::from_f2(r, r1);
-    if (tid == 0 && prm.lse) prm.lse[head] = m_run + log2f(l_run);
+    if (prm.o_f32) prm.o_f32[static_cast<int64_t>(head) * kHeadDim + tid] = r;
+    if (prm.o && (tid & 1) == 0) reinterpret_cast<uint32_t*>(op)[tid >> 1] = Elem<T>::from_f2(r, r1);
+    if (tid == 0 && prm.lse) prm.lse[head] = l_run > 0.f ? m_run + log2f(l_run) : -INFINITY;
     return;
   }
 
@@ -273,7 +281,7 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
   float lloc = 0.f;
   for (int s = tid; s < prm.num_splits; s += kDecThreads) {
     const float2 ml = __ldcg(reinterpret_cast<const float2*>(prm.partial_ml + (p0 + s) * 2));
-    const float w = exp2f(ml.x - M);
+    const float w = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - M);
     s_w[s] = w;
     lloc += w * ml.y;
   }
@@ -293,11 +301,12 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
     for (int u = 0; u < 8; ++u) accd = fmaf(s_w[s + u], t[u], accd);
   }
   for (; s < prm.num_splits; ++s) accd = fmaf(s_w[s], __ldcg(po + static_cast<int64_t>(s) * kHeadDim), accd);
-  const float r = accd / Lsum;
+  const float r = Lsum > 0.f ? accd / Lsum : 0.f;
   const float r1 = __shfl_down_sync(0xffffffffu, r, 1);
-  if ((tid & 1) == 0) reinterpret_cast<uint32_t*>(op)[tid >> 1] = Elem<T>::from_f2(r, r1);
+  if (prm.o_f32) prm.o_f32[static_cast<int64_t>(head) * kHeadDim + tid] = r;
+  if (prm.o && (tid & 1) == 0) reinterpret_cast<uint32_t*>(op)[tid >> 1] = Elem<T>::from_f2(r, r1);
   if (tid == 0) {
-    if (prm.lse) prm.lse[head] = M + log2f(Lsum);
+    if (prm.lse) prm.lse[head] = Lsum > 0.f ? M + log2f(Lsum) : -INFINITY;
     prm.counters[head] = 0;
   }
 }

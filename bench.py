@@ -244,20 +244,31 @@ class Workload:
         self.step()
         self.h_out.copy_(self.d_out, non_blocking=True)
 
-    # one kernel class alone, for the roofline entry
-    def capture_estimate_only(self):
+    # one kernel class alone (a graph with one launch per layer, so the data comes from HBM)
+    def capture_stage_only(self, stage):
         U, c = self.U, self.c
+
+        def body():
+            for layer in range(self.args.layers):
+                q, k, v = self.d_qkv[0, layer], self.d_qkv[1, layer], self.d_qkv[2, layer]
+                if stage == "append":
+                    U.append_qkv_fused(q, k, v, c, layer, out=self.q_code[layer])
+                elif stage == "estimate":
+                    U.decode_estimate(self.q_code[layer], c, layer)
+                elif stage == "topk":
+                    U.decode_topk(c.estimate_buffer(c.hadamard_cache.seqlen - 1), c)
+                elif stage == "attention":
+                    U.decode_sparse_attn(q, c, layer, c.topk_dindices_buffer, out=self.d_out[layer])
+
         g = torch.cuda.CUDAGraph()
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
-            for layer in range(self.args.layers):
-                U.decode_estimate(self.q_code[layer], c, layer)
+            body()
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
         with torch.cuda.graph(g):
-            for layer in range(self.args.layers):
-                U.decode_estimate(self.q_code[layer], c, layer)
+            body()
         return g
 
 
@@ -343,11 +354,14 @@ def run_ours(args):
     wl.graph = saved
 
     # dominant kernel alone (estimate), one launch per layer so the data comes from HBM
-    g_est = wl.capture_estimate_only()
-    for _ in range(3):
-        g_est.replay()
-    ms_est = timed(g_est.replay, args.steps, False, dev)
-    est_us = ms_est * 1e3 / args.steps / args.layers
+    stage_us = {}
+    for stage in ("estimate", "append", "topk", "attention"):
+        g_st = wl.capture_stage_only(stage)
+        for _ in range(3):
+            g_st.replay()
+        stage_us[stage] = timed(g_st.replay, args.steps, False, dev) * 1e3 / args.steps / args.layers
+        del g_st
+    est_us = stage_us["estimate"]
 
     if rank != 0:
         if dist_on:
@@ -381,6 +395,8 @@ def run_ours(args):
                      "peak_source": peak_src, "us_per_launch": est_us,
                      "algorithmic_bytes_per_launch": by["estimate"]},
         "stage_bytes_per_layer": by,
+        "stage_us_alone": stage_us,
+        "stage_gbs_alone": {k: by[k] / (stage_us[k] * 1e-6) / 1e9 for k in ("estimate", "topk", "attention")},
     }
     if not args.no_cpu and world >= 1:
         sec, n = time_cpu_reference(L, H, B, steps=20, warmup=1, budget_s=20.0)

@@ -120,14 +120,15 @@ int adamas_append_prefill(const void* k, const void* v, const void* h, int64_t n
 /* ---- stage 2: distance estimate ----------------------------------------------------------- */
 
 /* out[h * out_stride + t] = distance(q_code[h], code of token t, head h) for t < n_tokens, where
- * n_tokens = (code_num_pages-1)*page_size + code_last_page_len - 1 (the newest token is excluded).
+ * n_tokens = (code_num_pages-1)*page_size + code_last_page_len - exclude_last; exclude_last = 1 leaves
+ * the newest token out, as the reference does; 0 is for a sequence shard that does not hold it.
  * q_code [H, D/8]; out_format ADAMAS_VAL_F16 (reference) or ADAMAS_VAL_U16.
  * Replaces estimate_attn_score (adamas/ops/csrc/estimate.cu:6-84,
  * kernels/include/decode/decode_attn.cuh:287-443,1144-1211). */
 int adamas_estimate(const void* q_code, const void* code_data, const int32_t* code_page_table,
                     int code_num_pages, int code_last_page_len, int page_size, int num_heads,
                     int head_dim, void* out, int64_t out_stride, int out_format, int metric,
-                    adamas_stream_t stream);
+                    int exclude_last, adamas_stream_t stream);
 
 /* ---- stage 3: top-k ------------------------------------------------------------------------ */
 
@@ -167,7 +168,9 @@ int adamas_decode_end_forward(adamas_decode_handler_t* handler);
 /* o[h,:] = softmax(sm_scale * q[h,:] . K_sel^T) V_sel over, for head h, the tokens covered by
  * indices[h*idx_stride + i], i < n_idx, followed by the tail.  Each index covers idx_unit
  * consecutive token slots starting at index*idx_unit (idx_unit = 1: physical token slots
- * page*page_size+entry; idx_unit = page_size: whole pages, the reference's meaning).  The tail is the
+ * page*page_size+entry, a negative entry is a hole that is skipped; idx_unit = page_size: whole
+ * pages, the reference's meaning).  A head whose list and tail are empty gets zeros and lse = -inf.
+ * The tail is the
  * last tail_len filled entries of page last_page_idx, i.e. entries
  * [last_page_len - tail_len, last_page_len).  q, o [H, D]; lse (optional, may be NULL) [H] receives
  * log2(sum exp2(sm_scale*log2(e)*logit)) style base-2 log-sum-exp of the scaled logits.
@@ -177,6 +180,16 @@ int adamas_decode_forward(adamas_decode_handler_t* handler, const void* q, void*
                           const void* kv_data, const int32_t* indices, int64_t idx_stride,
                           int n_idx, int idx_unit, int last_page_idx, int last_page_len,
                           int tail_len, float sm_scale, adamas_stream_t stream);
+
+/* Same as adamas_decode_forward with the output kept in fp32 (o_f32 [H, D]) and lse mandatory: the
+ * partial result of one sequence shard, to be combined with adamas_merge_states without an
+ * intermediate rounding.  Replaces the (o, lse) partial written by the reference's split-KV kernel
+ * (kernels/include/decode/decode_attn.cuh:672-700). */
+int adamas_decode_forward_partial(adamas_decode_handler_t* handler, const void* q, float* o_f32,
+                                  float* lse, const void* kv_data, const int32_t* indices,
+                                  int64_t idx_stride, int n_idx, int idx_unit, int last_page_idx,
+                                  int last_page_len, int tail_len, float sm_scale,
+                                  adamas_stream_t stream);
 
 /* The same attention as adamas_decode_forward for callers that must not allocate device memory: code
  * that runs while the process is not allowed to call cudaMalloc or cudaFree (a serving process whose
