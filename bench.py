@@ -424,8 +424,11 @@ def main():
     ap.add_argument("--eager", action="store_true", help="no CUDA graph")
     ap.add_argument("--no-cpu", dest="no_cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--traffic", type=float, default=None,
-                    help="DRAM bytes per estimate launch from an ncu capture (profiles/), if known")
+                    help="DRAM bytes per estimate launch from an ncu capture; default: the figure in "
+                         "profiles/estimate_topk_decode_kernels_32k_ncu.md when the workload matches it")
     args = ap.parse_args()
+    if args.traffic is None and (args.ctx, args.heads, args.page_size) == (32768, 32, 16):
+        args.traffic = 33.58e6 + 1.0e3     # dram__bytes_read.sum + dram__bytes_write.sum, one launch
     if args.impl == "reference":
         run_reference_arm(args)
     else:
