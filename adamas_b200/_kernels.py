@@ -351,6 +351,71 @@ class BatchDecodeWithPagedKVCachePyTorchWrapper:
             1.0 / math.sqrt(head_dim), _stream()), "BatchDecodeWithPagedKVCache")
 
 
+def select_attend(dist: torch.Tensor, k: int, q: torch.Tensor, o: torch.Tensor, kv_data: torch.Tensor,
+                  kv_indices: torch.Tensor, last_page_len: int, last_page_idx: int,
+                  indices_out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None) -> None:
+    """Top-k and sparse attention in one launch (replaces topk_filtering + the decode wrapper's
+    forward, adamas/models/Adamas.py:185-200).  dist int16 [H, n] integer distances with rows on
+    16-byte boundaries; q, o [1,H,D]; kv_indices int32 page table; indices_out optional int32
+    [H, >=k] receiving the winners' token slots."""
+    _check_rows(dist, "dist")
+    _check_input(q, "q", 3)
+    _check_input(o, "o", 3)
+    _check_input(kv_data, "kv_data", 5)
+    _check_input(kv_indices, "kv_indices", 1)
+    _require(dist.dtype in (torch.int16, torch.uint16), "dist must hold 16-bit integer distances")
+    h, n = dist.shape
+    _require(q.size(0) == 1 and q.size(1) == h and q.size(2) == 128 and tuple(o.shape) == tuple(q.shape)
+             and o.dtype == q.dtype, "q and o must be [1, H, 128]")
+    page_size = kv_data.size(2)
+    _require(kv_data.size(1) == 2 and kv_data.size(3) == h and kv_data.size(4) == 128 and kv_data.dtype == q.dtype,
+             "kv_data must be [pages, 2, page_size, H, 128] in q.dtype")
+    _require(kv_indices.dtype == torch.int32 and kv_indices.numel() * page_size >= n, "page table too short")
+    out_stride = 0
+    if indices_out is not None:
+        _check_rows(indices_out, "indices_out")
+        _require(indices_out.dtype == torch.int32 and indices_out.size(0) == h and indices_out.size(1) >= k,
+                 "indices_out must be int32 [H, >=k]")
+        out_stride = indices_out.stride(0)
+    if lse is not None:
+        _require(lse.is_cuda and lse.dtype == torch.float32 and lse.numel() == h and lse.is_contiguous(),
+                 "lse must be a contiguous float32 CUDA tensor of H elements")
+    _lib.check(lib.adamas_select_attend(
+        _ptr(dist), dist.stride(0), n, int(k), _ptr(q), _ptr(o), _ptr(lse), _ptr(kv_data), _ptr(kv_indices),
+        page_size, h, 128, _dtype_code(q.dtype, "select_attend"), int(last_page_idx), int(last_page_len),
+        _ptr(indices_out), out_stride, 1.0 / math.sqrt(128.0), _stream()), "select_attend")
+
+
+def decode_step(q, k, v, o, q_code, kv_data, kv_indices, kv_last_page_len, kv_last_page_idx, hadamard_data,
+                hadamard_indices, hadamard_last_page_len, budget: int, dist_scratch: torch.Tensor,
+                indices_out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
+                scale: Optional[float] = None, thresholds=None) -> None:
+    """One layer's decode step in one call: fused append, estimate, select + attend (three launches
+    for what adamas/models/Adamas.py:145-200 does with seven).  Needs context > budget."""
+    num_heads, head_dim, page_size = _check_append(k, v, kv_data, kv_indices, hadamard_data, hadamard_indices, NHD)
+    _check_input(q, "q", 3)
+    _check_input(o, "o", 3)
+    _check_input(q_code, "q_code", 3)
+    _check_rows(dist_scratch, "dist_scratch")
+    _require(tuple(q.shape) == tuple(k.shape) == tuple(o.shape) and k.size(0) == 1, "q, k, v, o must be [1, H, D]")
+    _require(q_code.element_size() == 2 and q_code.numel() == num_heads * head_dim // 8, "q_code must be [1, H, D/8] 16-bit")
+    _require(dist_scratch.element_size() == 2 and dist_scratch.size(0) == num_heads, "dist_scratch must be 16-bit [H, n]")
+    out_stride = 0
+    if indices_out is not None:
+        _check_rows(indices_out, "indices_out")
+        _require(indices_out.dtype == torch.int32 and indices_out.size(0) == num_heads
+                 and indices_out.size(1) >= budget - 1, "indices_out must be int32 [H, >=budget-1]")
+        out_stride = indices_out.stride(0)
+    s = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)
+    _lib.check(lib.adamas_decode_step(
+        _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(q_code),
+        _ptr(kv_data), _ptr(kv_indices), kv_indices.numel(), int(kv_last_page_len), int(kv_last_page_idx),
+        _ptr(hadamard_data), _ptr(hadamard_indices), hadamard_indices.numel(), int(hadamard_last_page_len),
+        num_heads, head_dim, page_size, _dtype_code(k.dtype, "decode_step"), int(budget),
+        _ptr(dist_scratch), dist_scratch.stride(0), _ptr(indices_out), out_stride, s,
+        _lib.thresholds_arg(thresholds), 1.0 / math.sqrt(head_dim), _stream()), "decode_step")
+
+
 def merge_states(o_parts: torch.Tensor, lse_parts: torch.Tensor, o: torch.Tensor,
                  lse: Optional[torch.Tensor] = None) -> None:
     """o_parts [P,H,D] fp32 normalised partial outputs, lse_parts [P,H] base-2 -> o [H,D] (or [1,H,D])."""

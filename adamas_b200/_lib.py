@@ -45,6 +45,9 @@ SIGNATURES = {
     "adamas_decode_forward": [_P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _P],
     "adamas_decode_forward_partial": [_P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _P],
     "adamas_decode_forward_static": [_P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P],
+    "adamas_select_attend": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _L, _F, _P],
+    "adamas_decode_step": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I,
+                           _P, _L, _P, _L, _F, _FP, _F, _P],
     "adamas_merge_states": [_P, _P, _I, _I, _I, _P, _P, _I, _P],
     "adamas_device_error": [POINTER(ctypes.c_uint), _I],
     "adamas_set_pdl": [_I],

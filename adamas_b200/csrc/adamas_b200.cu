@@ -14,6 +14,7 @@
 #include "common.cuh"
 #include "estimate.cuh"
 #include "hadamard_append.cuh"
+#include "select_attend.cuh"
 #include "sparse_decode.cuh"
 #include "topk.cuh"
 
@@ -106,6 +107,39 @@ int get_device_info(const DeviceInfo** out) {
 #undef EST_ATTR
     ADAMAS_CUDA(cudaFuncSetAttribute(sparse_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kDecStageBytes));
     ADAMAS_CUDA(cudaFuncSetAttribute(sparse_decode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kDecStageBytes));
+    // One shared-memory carve-out for every kernel of the decode step: a kernel that asks for a
+    // different L1 / shared split than its predecessor cannot start until the SMs have drained.
+#define SET_CARVEOUT(kern) \
+  ADAMAS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared))
+    SET_CARVEOUT((append_decode_kernel<__half, true>));
+    SET_CARVEOUT((append_decode_kernel<__half, false>));
+    SET_CARVEOUT((append_decode_kernel<__nv_bfloat16, true>));
+    SET_CARVEOUT((append_decode_kernel<__nv_bfloat16, false>));
+    SET_CARVEOUT((estimate_kernel<0, __half, 0>));
+    SET_CARVEOUT((estimate_kernel<0, __half, 1>));
+    SET_CARVEOUT((estimate_kernel<0, __half, 2>));
+    SET_CARVEOUT((estimate_kernel<0, __half, 4>));
+    SET_CARVEOUT((estimate_kernel<0, uint16_t, 0>));
+    SET_CARVEOUT((estimate_kernel<0, uint16_t, 1>));
+    SET_CARVEOUT((estimate_kernel<0, uint16_t, 2>));
+    SET_CARVEOUT((estimate_kernel<0, uint16_t, 4>));
+    SET_CARVEOUT((topk_cluster_kernel<0, 1>));
+    SET_CARVEOUT((topk_cluster_kernel<0, 2>));
+    SET_CARVEOUT((topk_cluster_kernel<0, 4>));
+    SET_CARVEOUT((topk_cluster_kernel<1, 1>));
+    SET_CARVEOUT((topk_cluster_kernel<1, 2>));
+    SET_CARVEOUT((topk_cluster_kernel<1, 4>));
+    SET_CARVEOUT((sparse_decode_kernel<__half>));
+    SET_CARVEOUT((sparse_decode_kernel<__nv_bfloat16>));
+    SET_CARVEOUT((select_attend_kernel<__half, 1>));
+    SET_CARVEOUT((select_attend_kernel<__half, 2>));
+    SET_CARVEOUT((select_attend_kernel<__half, 4>));
+    SET_CARVEOUT((select_attend_kernel<__half, 8>));
+    SET_CARVEOUT((select_attend_kernel<__nv_bfloat16, 1>));
+    SET_CARVEOUT((select_attend_kernel<__nv_bfloat16, 2>));
+    SET_CARVEOUT((select_attend_kernel<__nv_bfloat16, 4>));
+    SET_CARVEOUT((select_attend_kernel<__nv_bfloat16, 8>));
+#undef SET_CARVEOUT
     d.ready = true;
   }
   *out = &d;
@@ -236,6 +270,10 @@ static int append_decode_impl(const void* k, const void* v, const void* qh, cons
   const Thresholds th = make_thresholds(thresholds3_host);
   const unsigned blocks = rows_to_blocks(num_heads);
   cudaStream_t st = to_stream(stream);
+  {
+    const DeviceInfo* di = nullptr;
+    if (int rc = get_device_info(&di)) return rc;
+  }
 #define LAUNCH_AD(T, F)                                                                         \
   ADAMAS_LAUNCH("append_decode_kernel", append_decode_kernel<T, F>, dim3(blocks), dim3(256), 0, st, 1, \
                 static_cast<const T*>(k), static_cast<const T*>(v), static_cast<const T*>(qh),  \
@@ -770,6 +808,138 @@ int adamas_decode_forward_static(const void* q, void* o, float* lse, const void*
   else
     sparse_decode_kernel<__nv_bfloat16><<<grid, kDecThreads, smem, st>>>(prm);
   return check_launch("sparse_decode_kernel (static scratch)");
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+int log2_exact(int v) {
+  if (v <= 0 || (v & (v - 1)) != 0) return -1;
+  int s = 0;
+  while ((1 << s) < v) ++s;
+  return s;
+}
+
+template <typename T>
+int launch_select_attend(const SelectAttendParams& prm, int items, int cl, int num_heads, size_t smem,
+                         cudaStream_t st) {
+  const dim3 grid(static_cast<unsigned>(num_heads) * cl);
+#define SA_CASE(I)                                                                                  \
+  case I: {                                                                                         \
+    static bool configured[64] = {};                                                                \
+    int dev = 0;                                                                                    \
+    ADAMAS_CUDA(cudaGetDevice(&dev));                                                               \
+    if (!configured[dev & 63]) {                                                                    \
+      ADAMAS_CUDA(cudaFuncSetAttribute(select_attend_kernel<T, I>,                                  \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));   \
+      configured[dev & 63] = true;                                                                  \
+    }                                                                                               \
+    ADAMAS_LAUNCH("select_attend_kernel", select_attend_kernel<T, I>, grid, dim3(kSaThreads), smem, st, \
+                  cl, prm);                                                                         \
+    break;                                                                                          \
+  }
+  switch (items) {
+    SA_CASE(1)
+    SA_CASE(2)
+    SA_CASE(4)
+    SA_CASE(8)
+    default:
+      return fail(ADAMAS_ERR_INVALID, "unsupported row length for select_attend");
+  }
+#undef SA_CASE
+  return check_launch("select_attend_kernel");
+}
+
+}  // namespace
+
+extern "C" {
+
+int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, const void* q, void* o,
+                         float* lse, const void* kv_data, const int32_t* kv_page_table, int page_size,
+                         int num_heads, int head_dim, int dtype, int last_page_idx, int last_page_len,
+                         int32_t* out_idx, int64_t out_stride, float sm_scale, adamas_stream_t stream) {
+  if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
+  ADAMAS_REQUIRE(dist && q && o && kv_data && kv_page_table, "null pointer");
+  ADAMAS_REQUIRE(n >= 1 && k >= 1 && k <= n, "need 1 <= k <= n (k=%d, n=%d)", k, n);
+  ADAMAS_REQUIRE((reinterpret_cast<uintptr_t>(dist) & 15) == 0 && (num_heads == 1 || (dist_stride * 2) % 16 == 0),
+                 "distance rows must start on 16-byte boundaries");
+  ADAMAS_REQUIRE(dist_stride >= n || num_heads == 1, "dist_stride smaller than n");
+  ADAMAS_REQUIRE(last_page_idx >= 0 && last_page_len >= 1 && last_page_len <= page_size,
+                 "last page out of range");
+  ADAMAS_REQUIRE(out_idx == nullptr || out_stride >= k || num_heads == 1, "out_stride smaller than k");
+  const int64_t tail = static_cast<int64_t>(last_page_idx) * page_size + last_page_len - 1;
+  ADAMAS_REQUIRE(tail < (int64_t(1) << 31), "token slots must be below 2^31");
+  const int g_total = (n + 7) / 8;
+  int cl = 0, items = 0;
+  for (int it = 1; it <= 8 && cl == 0; it *= 2) {
+    for (int c = 1; c <= kSaMaxCluster; c *= 2) {
+      if (static_cast<int64_t>(c) * it * kSaThreads >= g_total) {
+        cl = c;
+        items = it;
+        break;
+      }
+    }
+  }
+  ADAMAS_REQUIRE(cl > 0, "select_attend supports at most %d distances per head (got %d)",
+                 kSaMaxCluster * 8 * kSaThreads * 8, n);
+  SelectAttendParams prm;
+  prm.dist = static_cast<const uint16_t*>(dist);
+  prm.dist_stride = dist_stride;
+  prm.n = n;
+  prm.k = k;
+  prm.q = q;
+  prm.o = o;
+  prm.lse = lse;
+  prm.kv = kv_data;
+  prm.kv_table = kv_page_table;
+  prm.page_size = page_size;
+  prm.ps_shift = log2_exact(page_size);
+  prm.H = num_heads;
+  prm.tail_slot = static_cast<unsigned>(tail);
+  prm.out_idx = out_idx;
+  prm.out_stride = out_stride;
+  prm.granules_per_block = (g_total + cl - 1) / cl;
+  const int slice_tokens = std::min(n, prm.granules_per_block * 8);
+  prm.list_capacity = std::min(k, slice_tokens) + 1;
+  prm.scale_log2 = sm_scale * 1.4426950408889634f;
+  const size_t smem = static_cast<size_t>(2) * kSaTile * 256 + static_cast<size_t>(prm.list_capacity) * 4;
+  ADAMAS_REQUIRE(smem <= 160 * 1024, "winner list too long for select_attend (k=%d)", k);
+  if (dtype == ADAMAS_F16)
+    return launch_select_attend<__half>(prm, items, cl, num_heads, smem, to_stream(stream));
+  return launch_select_attend<__nv_bfloat16>(prm, items, cl, num_heads, smem, to_stream(stream));
+}
+
+int adamas_decode_step(const void* q, const void* k, const void* v, void* o, float* lse, void* q_code,
+                       void* kv_data, const int32_t* kv_page_table, int kv_num_pages,
+                       int kv_last_page_len, int kv_last_page_idx, void* code_data,
+                       const int32_t* code_page_table, int code_num_pages, int code_last_page_len,
+                       int num_heads, int head_dim, int page_size, int dtype, int budget,
+                       void* dist_scratch, int64_t dist_stride, int32_t* out_idx, int64_t out_stride,
+                       float hadamard_scale, const float* thresholds3_host, float sm_scale,
+                       adamas_stream_t stream) {
+  ADAMAS_REQUIRE(kv_num_pages >= 1 && kv_page_table, "page table missing");
+  ADAMAS_REQUIRE(page_size >= 1, "page_size must be >= 1");
+  const int64_t seq_len = static_cast<int64_t>(kv_num_pages - 1) * page_size + kv_last_page_len;
+  ADAMAS_REQUIRE(budget >= 2 && seq_len > budget,
+                 "adamas_decode_step needs budget >= 2 and a context longer than the budget (%lld vs %d); "
+                 "shorter contexts attend to every page through adamas_decode_forward",
+                 static_cast<long long>(seq_len), budget);
+  ADAMAS_REQUIRE(seq_len - 1 < (int64_t(1) << 31), "sequence too long");
+  ADAMAS_REQUIRE(dist_scratch && q_code, "null pointer");
+  if (int rc = adamas_append_decode_fused(q, k, v, q_code, kv_data, kv_page_table, kv_num_pages,
+                                          kv_last_page_len, code_data, code_page_table, code_num_pages,
+                                          code_last_page_len, num_heads, head_dim, page_size,
+                                          hadamard_scale, thresholds3_host, dtype, stream))
+    return rc;
+  if (int rc = adamas_estimate(q_code, code_data, code_page_table, code_num_pages, code_last_page_len,
+                               page_size, num_heads, head_dim, dist_scratch, dist_stride, ADAMAS_VAL_U16,
+                               ADAMAS_METRIC_L1, 1, stream))
+    return rc;
+  return adamas_select_attend(dist_scratch, dist_stride, static_cast<int>(seq_len - 1), budget - 1, q, o,
+                              lse, kv_data, kv_page_table, page_size, num_heads, head_dim, dtype,
+                              kv_last_page_idx, kv_last_page_len, out_idx, out_stride, sm_scale, stream);
 }
 
 int adamas_merge_states(const float* o_parts, const float* lse_parts, int num_parts, int num_heads,

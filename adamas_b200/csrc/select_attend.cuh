@@ -1,0 +1,413 @@
+// Stages 3 + 4 of the decode path in one kernel: per head, pick the k smallest of n integer distances
+// (ties to the lower position) and run the decode attention over the picked tokens plus the newest
+// token.  Used by the fused decode step; the separate top-k and decode kernels remain for callers
+// that want the stages one by one.
+//
+// One thread-block cluster (CL <= 8 blocks x 256 threads) per head.  Block `cr` owns a contiguous
+// slice of the head's distance row, keeps it in registers, and later attends over the winners that
+// lie in its own slice, so the selected indices never travel between blocks:
+//   pre   zero the exchange buffers, load the query row, cluster barrier (peers have started);
+//         all of this may overlap the tail of the estimate kernel (programmatic dependent launch);
+//   1     histogram of the block's distances (values < 512: a distance is at most 3 * 128);
+//         the non-zero bins are STORED into slot `cr` of every peer's per-source table; cluster
+//         barrier.  Every block now holds all CL histograms and derives by itself: the cut distance,
+//         how many cut-valued elements are taken in all, how many of them and how many smaller
+//         elements lie in lower-ranked slices (= its tie quota and its offset in the output list);
+//   2     ordered compaction of the block's winners into a shared-memory list (and, optionally, to
+//         the global index list at the right offset);
+//   3     attention over the list in tiles of 128 tokens: slot look-up through the page table, K/V
+//         rows gathered with 16-byte cp.async into XOR-swizzled shared memory, two threads per token
+//         for q.K, online softmax in base 2, one thread per (token group, 8-dim chunk) for P.V;
+//   4     the partial (o, m, l) is stored into slot `cr` of rank 0's shared memory; cluster barrier;
+//         rank 0 merges the CL partials and writes the head's output.
+// Only two cluster barriers sit on the critical path after the start-up one.
+#pragma once
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace adamas {
+
+constexpr int kSaThreads = 256;
+constexpr int kSaWarps = kSaThreads / 32;
+constexpr int kSaBins = 512;
+constexpr int kSaTile = 128;          // tokens per attention tile
+constexpr int kSaMaxCluster = 8;
+
+struct SelectAttendParams {
+  const uint16_t* dist;     // [H, dist_stride] u16 distances, rows 16-byte aligned
+  int64_t dist_stride;
+  int n;                    // distances per head (tokens 0 .. n-1)
+  int k;                    // winners per head, 1 <= k <= n
+  const void* q;            // [H, 128]
+  void* o;                  // [H, 128]
+  float* lse;               // [H] or null (base 2)
+  const void* kv;           // [pages, 2, page_size, H, 128]
+  const int32_t* kv_table;  // logical page -> physical page
+  int page_size;
+  int ps_shift;             // log2(page_size) or -1
+  int H;
+  unsigned tail_slot;       // physical slot of the newest token (always attended)
+  int32_t* out_idx;         // optional [H, out_stride]: physical slots of the winners, ascending position
+  int64_t out_stride;
+  int granules_per_block;   // 16-byte granules (8 distances) of a row per block
+  int list_capacity;        // entries of the shared-memory winner list
+  float scale_log2;
+};
+
+struct SaShared {
+  unsigned local[kSaBins];
+  unsigned per_src[kSaMaxCluster][kSaBins];
+  float part_o[kSaMaxCluster][kHeadDim];     // rank 0 only: partial outputs of the blocks
+  float part_ml[kSaMaxCluster][2];
+  float s_o[16][kHeadDim];
+  float s_logit[kSaTile];
+  float s_p[kSaTile];
+  float s_red[kSaWarps];
+  float s_sum[kSaWarps];
+  unsigned warp_a[kSaWarps];
+  unsigned cut, before, lt_before, eq_before;
+};
+
+// Dynamic shared memory: K tile (32 KB) | V tile (32 KB) | winner list (list_capacity * 4 bytes).
+template <typename T, int ITEMS>
+__global__ void __launch_bounds__(kSaThreads) select_attend_kernel(const SelectAttendParams p) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  extern __shared__ __align__(16) uint8_t sa_smem[];
+  __shared__ __align__(16) SaShared sh;
+
+  const unsigned CL = cluster.num_blocks();
+  const unsigned cr = cluster.block_rank();
+  const int head = blockIdx.x / CL;
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int H = p.H;
+
+  uint8_t* sk = sa_smem;
+  uint8_t* sv = sa_smem + kSaTile * 256;
+  int32_t* s_list = reinterpret_cast<int32_t*>(sa_smem + 2 * kSaTile * 256);
+
+  // ---- pre: buffers, query, start-up barrier --------------------------------------------------------
+  for (int i = tid; i < kSaBins; i += kSaThreads) sh.local[i] = 0;
+  for (int i = tid; i < kSaMaxCluster * kSaBins; i += kSaThreads) (&sh.per_src[0][0])[i] = 0;
+
+  // q.K mapping: thread pair (tl = tid / 2, half = tid % 2); step i reads logical chunk half*8 + (i ^ half*4)
+  const int qk_tl = tid >> 1;
+  const int half = tid & 1;
+  float qreg[8][8];
+  {
+    const T* qp = static_cast<const T*>(p.q) + static_cast<int64_t>(head) * kHeadDim;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int lc = half * 8 + (i ^ (half * 4));
+      unpack8<T>(ld_16(qp + lc * 8), qreg[i]);
+#pragma unroll
+      for (int d = 0; d < 8; ++d) qreg[i][d] *= p.scale_log2;
+    }
+  }
+  cluster.sync();
+  grid_dependency_wait();
+  grid_launch_dependents();
+
+  // ---- 1: this block's slice of the row, histogram, exchange --------------------------------------
+  const uint16_t* rowp = p.dist + static_cast<int64_t>(head) * p.dist_stride;
+  const uint4* gbase = reinterpret_cast<const uint4*>(rowp);
+  const int G = (p.n + 7) >> 3;
+  const int blk_first = cr * p.granules_per_block;
+  const int blk_end = min(G, blk_first + p.granules_per_block);
+  const int g0 = blk_first + tid * ITEMS;
+  uint32_t raw[ITEMS][4];
+  unsigned vmask[ITEMS];
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    uint4 v = make_uint4(0, 0, 0, 0);
+    unsigned m = 0;
+    const int g = g0 + i;
+    if (g < blk_end) {
+      v = ld_16(gbase + g);
+      m = 0xffu;
+      if (g * 8 + 8 > p.n) m = 0xffu >> (g * 8 + 8 - p.n);
+    }
+    raw[i][0] = v.x; raw[i][1] = v.y; raw[i][2] = v.z; raw[i][3] = v.w;
+    vmask[i] = m;
+  }
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const unsigned d = (raw[i][j >> 1] >> ((j & 1) * 16)) & 0xffffu;
+      if ((vmask[i] >> j) & 1u) atomicAdd(&sh.local[min(d, static_cast<unsigned>(kSaBins - 1))], 1u);
+    }
+  }
+  __syncthreads();
+  for (int b = tid; b < kSaBins; b += kSaThreads) {
+    const unsigned c = sh.local[b];
+    if (c != 0)
+      for (unsigned r = 0; r < CL; ++r) *cluster.map_shared_rank(&sh.per_src[cr][b], r) = c;
+  }
+  cluster.sync();
+
+  // every block: total histogram, cut, counts in lower-ranked slices
+  {
+    unsigned tot[2] = {0, 0}, low[2] = {0, 0};
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int b = tid * 2 + u;
+      for (unsigned r = 0; r < CL; ++r) {
+        const unsigned c = sh.per_src[r][b];
+        tot[u] += c;
+        if (r < cr) low[u] += c;
+      }
+    }
+    const unsigned s = tot[0] + tot[1];
+    unsigned incl = s;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    if (lane == 31) sh.warp_a[warp] = incl;
+    if (tid == 0) { sh.lt_before = 0; sh.eq_before = 0; }
+    __syncthreads();
+    unsigned wbase = 0;
+#pragma unroll
+    for (int w2 = 0; w2 < kSaWarps; ++w2) wbase += (w2 < warp) ? sh.warp_a[w2] : 0u;
+    const unsigned excl = wbase + incl - s;
+    const unsigned want = static_cast<unsigned>(p.k);
+    if (excl < want && excl + s >= want) {   // exactly one thread
+      const bool first = excl + tot[0] >= want;
+      sh.cut = tid * 2 + (first ? 0 : 1);
+      sh.before = first ? excl : excl + tot[0];
+    }
+    __syncthreads();
+    const unsigned cutb = sh.cut;
+    unsigned lt = 0, eq = 0;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const unsigned b = tid * 2 + u;
+      if (b < cutb) lt += low[u];
+      if (b == cutb) eq += low[u];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      lt += __shfl_xor_sync(0xffffffffu, lt, o);
+      eq += __shfl_xor_sync(0xffffffffu, eq, o);
+    }
+    if (lane == 0) {
+      if (lt) atomicAdd(&sh.lt_before, lt);
+      if (eq) atomicAdd(&sh.eq_before, eq);
+    }
+    __syncthreads();
+  }
+  const unsigned cut = sh.cut;
+  const unsigned need_eq = static_cast<unsigned>(p.k) - sh.before;       // cut-valued winners in all
+  const unsigned eq_before = sh.eq_before;
+  const unsigned take_eq = need_eq > eq_before ? need_eq - eq_before : 0u;  // this slice's tie quota
+  const unsigned out_base = sh.lt_before + min(eq_before, need_eq);      // winners in lower slices
+
+  // ---- 2: ordered compaction of this block's winners ------------------------------------------------
+  unsigned c_lt = 0, c_eq = 0;
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const unsigned d = (raw[i][j >> 1] >> ((j & 1) * 16)) & 0xffffu;
+      const bool ok = (vmask[i] >> j) & 1u;
+      c_lt += (ok && d < cut);
+      c_eq += (ok && d == cut);
+    }
+  }
+  const unsigned packed = c_lt | (c_eq << 16);
+  unsigned incl = packed;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) sh.warp_a[warp] = incl;
+  __syncthreads();
+  unsigned wbase = 0, blk_tot = 0;
+#pragma unroll
+  for (int w2 = 0; w2 < kSaWarps; ++w2) {
+    const unsigned a = sh.warp_a[w2];
+    wbase += (w2 < warp) ? a : 0u;
+    blk_tot += a;
+  }
+  const unsigned excl = wbase + incl - packed;
+  unsigned run_lt = excl & 0xffffu, run_eq = excl >> 16;
+  const unsigned blk_lt = blk_tot & 0xffffu, blk_eq = blk_tot >> 16;
+  int n_loc = static_cast<int>(blk_lt + min(blk_eq, take_eq));
+  int32_t* oi = p.out_idx ? p.out_idx + static_cast<int64_t>(head) * p.out_stride + out_base : nullptr;
+  if (c_lt | c_eq) {
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const unsigned d = (raw[i][j >> 1] >> ((j & 1) * 16)) & 0xffffu;
+        if (((vmask[i] >> j) & 1u) && d <= cut) {
+          int pos = -1;
+          if (d < cut) {
+            pos = static_cast<int>(run_lt + min(run_eq, take_eq));
+            ++run_lt;
+          } else {
+            if (run_eq < take_eq) pos = static_cast<int>(run_lt + run_eq);
+            ++run_eq;
+          }
+          if (pos >= 0) {
+            const unsigned t = static_cast<unsigned>((g0 + i) * 8 + j);   // logical token position
+            unsigned pg, e;
+            if (p.ps_shift >= 0) {
+              pg = t >> p.ps_shift;
+              e = t & (p.page_size - 1);
+            } else {
+              pg = t / p.page_size;
+              e = t - pg * p.page_size;
+            }
+            const int32_t slot = __ldg(p.kv_table + pg) * p.page_size + static_cast<int32_t>(e);
+            if (pos < p.list_capacity) s_list[pos] = slot;
+            if (oi) oi[pos] = slot;
+          }
+        }
+      }
+    }
+  }
+  if (cr == CL - 1) {   // the newest token rides with the last slice
+    if (tid == 0 && n_loc < p.list_capacity) s_list[n_loc] = static_cast<int32_t>(p.tail_slot);
+    n_loc += 1;
+  }
+  n_loc = min(n_loc, p.list_capacity);
+  __syncthreads();
+
+  // ---- 3: attention over the block's winners ------------------------------------------------------------
+  const T* kvp = static_cast<const T*>(p.kv);
+  const int64_t v_delta = static_cast<int64_t>(p.page_size) * H * kHeadDim;
+  float m_run = -INFINITY, l_run = 0.f;
+  float o_acc[8];
+#pragma unroll
+  for (int d = 0; d < 8; ++d) o_acc[d] = 0.f;
+  const int pv_g = tid >> 4;   // token group: tokens pv_g*8 .. pv_g*8+7 of the tile
+  const int pv_c = tid & 15;   // 8-dim chunk
+  const unsigned ps = static_cast<unsigned>(p.page_size);
+
+  for (int t0 = 0; t0 < n_loc; t0 += kSaTile) {
+    const int tile_tokens = min(kSaTile, n_loc - t0);
+    // gather: thread -> chunk c = tid % 16 of tokens tl = tid / 16 + 16 * i
+    {
+      const int c = tid & 15;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int tl = (tid >> 4) + 16 * i;
+        if (tl < tile_tokens) {
+          const unsigned slot = static_cast<unsigned>(s_list[t0 + tl]);
+          unsigned page, e;
+          if (p.ps_shift >= 0) {
+            page = slot >> p.ps_shift;
+            e = slot & (ps - 1);
+          } else {
+            page = slot / ps;
+            e = slot - page * ps;
+          }
+          const int64_t row = static_cast<int64_t>(page) * (2 * ps) + e;
+          const T* kp = kvp + (row * H + head) * kHeadDim + c * 8;
+          const int phys = c ^ (tl & 3);
+          cp_async_16(sk + tl * 256 + phys * 16, kp);
+          cp_async_16(sv + tl * 256 + phys * 16, kp + v_delta);
+        }
+      }
+      cp_async_commit();
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+
+    float acc = 0.f;
+    const bool live = qk_tl < tile_tokens;
+    if (live) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int lc = half * 8 + (i ^ (half * 4));
+        const int phys = lc ^ (qk_tl & 3);
+        float kf[8];
+        unpack8<T>(*reinterpret_cast<const uint4*>(sk + qk_tl * 256 + phys * 16), kf);
+#pragma unroll
+        for (int d = 0; d < 8; ++d) acc = fmaf(qreg[i][d], kf[d], acc);
+      }
+    }
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    const float logit = live ? acc : -INFINITY;
+    if (half == 0) sh.s_logit[qk_tl] = logit;
+    float wmax = logit;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, o));
+    if (lane == 0) sh.s_red[warp] = wmax;
+    __syncthreads();
+    float m_tile = sh.s_red[0];
+#pragma unroll
+    for (int w2 = 1; w2 < kSaWarps; ++w2) m_tile = fmaxf(m_tile, sh.s_red[w2]);
+    const float m_new = fmaxf(m_run, m_tile);
+    const float rescale = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
+    float psum = 0.f;
+    if (tid < kSaTile) {
+      const float lg = sh.s_logit[tid];
+      const float pr = (lg == -INFINITY) ? 0.f : exp2f(lg - m_new);
+      sh.s_p[tid] = pr;
+      psum = pr;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
+    if (lane == 0) sh.s_sum[warp] = psum;
+    __syncthreads();
+    l_run = l_run * rescale + ((sh.s_sum[0] + sh.s_sum[1]) + (sh.s_sum[2] + sh.s_sum[3]));
+    m_run = m_new;
+#pragma unroll
+    for (int d = 0; d < 8; ++d) o_acc[d] *= rescale;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int tl = pv_g * 8 + i;
+      const float pr = sh.s_p[tl];
+      if (pr != 0.f) {
+        const int phys = pv_c ^ (tl & 3);
+        float vf[8];
+        unpack8<T>(*reinterpret_cast<const uint4*>(sv + tl * 256 + phys * 16), vf);
+#pragma unroll
+        for (int d = 0; d < 8; ++d) o_acc[d] = fmaf(pr, vf[d], o_acc[d]);
+      }
+    }
+    __syncthreads();
+  }
+
+  // ---- 4: partial to rank 0, merge -----------------------------------------------------------------------
+#pragma unroll
+  for (int d = 0; d < 8; ++d) sh.s_o[pv_g][pv_c * 8 + d] = o_acc[d];
+  __syncthreads();
+  if (tid < kHeadDim) {
+    float od = 0.f;
+#pragma unroll
+    for (int g = 0; g < 16; ++g) od += sh.s_o[g][tid];
+    *cluster.map_shared_rank(&sh.part_o[cr][tid], 0) = od;
+  }
+  if (tid == 0) {
+    float* ml = cluster.map_shared_rank(&sh.part_ml[cr][0], 0);
+    ml[0] = m_run;
+    ml[1] = l_run;
+  }
+  cluster.sync();
+  if (cr != 0 || tid >= kHeadDim) return;
+  float M = -INFINITY;
+  for (unsigned r = 0; r < CL; ++r) M = fmaxf(M, sh.part_ml[r][0]);
+  float accd = 0.f, L = 0.f;
+  for (unsigned r = 0; r < CL; ++r) {
+    const float m = sh.part_ml[r][0];
+    const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
+    L += w * sh.part_ml[r][1];
+    accd += w * sh.part_o[r][tid];
+  }
+  const float res = L > 0.f ? accd / L : 0.f;
+  const float res1 = __shfl_down_sync(0xffffffffu, res, 1);
+  T* op = static_cast<T*>(p.o) + static_cast<int64_t>(head) * kHeadDim;
+  if ((tid & 1) == 0) reinterpret_cast<uint32_t*>(op)[tid >> 1] = Elem<T>::from_f2(res, res1);
+  if (tid == 0 && p.lse) p.lse[head] = L > 0.f ? M + log2f(L) : -INFINITY;
+}
+
+}  // namespace adamas

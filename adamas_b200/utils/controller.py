@@ -155,6 +155,11 @@ class InferenceController:
             self._estimate_store = torch.empty((self.num_heads, cap), dtype=torch.int16, device=self.device)
         return self._estimate_store.view(vdtype)[:, :n]
 
+    def distance_scratch(self, n: int) -> torch.Tensor:
+        """[H, n] int16 view of the same buffer, rows on 16-byte boundaries (fused decode step)."""
+        self.estimate_buffer(n)
+        return self._estimate_store[:, :n]
+
     def clean_states(self):
         self.kv_cache.release()
         self.hadamard_cache.release()

@@ -164,7 +164,8 @@ def workload_config(args, extra=None):
     cfg = {
         "workload": (f"llama2-7b-shaped attention stack: {args.layers} layers x {args.heads} heads x 128, "
                      f"ctx {args.ctx}, token budget {args.budget}, page size {args.page_size}, batch 1; "
-                     "per layer: fused append + estimate + top-k + sparse paged attention"),
+                     "per layer: fused append + estimate + top-k + sparse paged attention "
+                     + ("(4 launches)" if args.unfused else "(decode_step: 3 launches, top-k and attention in one kernel)")),
         "layers": args.layers, "heads_per_gpu": args.heads, "ctx": args.ctx, "budget": args.budget,
         "page_size": args.page_size, "parallelism": f"head-sharded x{args.gpus}" if args.gpus > 1 else "single GPU",
         "l2": "inputs larger than L2 (each layer has its own caches; ~1.6 GB touched per step)",
@@ -211,6 +212,10 @@ class Workload:
     def layer_step(self, layer):
         U, c = self.U, self.c
         q, k, v = self.d_qkv[0, layer], self.d_qkv[1, layer], self.d_qkv[2, layer]
+        if not self.args.unfused:
+            # public fused API: append + estimate + select/attend, three launches
+            U.decode_step(q, k, v, c, layer, out=self.d_out[layer], record_indices=False)
+            return
         q_code = U.append_qkv_fused(q, k, v, c, layer, out=self.q_code[layer])
         est = U.decode_estimate(q_code, c, layer)
         U.decode_topk(est, c)
@@ -247,6 +252,7 @@ class Workload:
     # one kernel class alone (a graph with one launch per layer, so the data comes from HBM)
     def capture_stage_only(self, stage):
         U, c = self.U, self.c
+        from adamas_b200 import _kernels as K
 
         def body():
             for layer in range(self.args.layers):
@@ -259,6 +265,11 @@ class Workload:
                     U.decode_topk(c.estimate_buffer(c.hadamard_cache.seqlen - 1), c)
                 elif stage == "attention":
                     U.decode_sparse_attn(q, c, layer, c.topk_dindices_buffer, out=self.d_out[layer])
+                elif stage == "select_attend":
+                    n = c.hadamard_cache.seqlen - 1
+                    K.select_attend(c.distance_scratch(n), c.inference_token_budget - 1, q, self.d_out[layer],
+                                    c.kv_cache.buf_layer(layer), c.kv_indices_with_last, c.kv_cache.last_page_len,
+                                    c.kv_last_page_idx)
 
         g = torch.cuda.CUDAGraph()
         s = torch.cuda.Stream()
@@ -355,7 +366,10 @@ def run_ours(args):
 
     # dominant kernel alone (estimate), one launch per layer so the data comes from HBM
     stage_us = {}
-    for stage in ("estimate", "append", "topk", "attention"):
+    # leave integer distances of the last layer in the scratch for the select/attend stage
+    wl.U.decode_step(wl.d_qkv[0, 0], wl.d_qkv[1, 0], wl.d_qkv[2, 0], wl.c, 0, out=wl.d_out[0], record_indices=True)
+    stage_list = ("estimate", "append", "select_attend") if not args.unfused else ("estimate", "append", "topk", "attention")
+    for stage in stage_list:
         g_st = wl.capture_stage_only(stage)
         for _ in range(3):
             g_st.replay()
@@ -389,14 +403,14 @@ def run_ours(args):
         "e2e": {"value": e2e_value, "unit": UNIT,
                 "h2d_bytes_per_step": wl.h_qkv.numel() * wl.h_qkv.element_size(),
                 "d2h_bytes_per_step": wl.h_out.numel() * wl.h_out.element_size()},
-        "gpu_launches": args.steps * args.layers * 4,
+        "gpu_launches": args.steps * args.layers * (4 if args.unfused else 3),
         "roofline": {"kernel": "estimate_kernel", "bound": "hbm", "achieved": est_gbs, "peak": peak,
                      "unit": "GB/s", "frac": est_gbs / peak, "traffic": args.traffic,
                      "peak_source": peak_src, "us_per_launch": est_us,
                      "algorithmic_bytes_per_launch": by["estimate"]},
         "stage_bytes_per_layer": by,
         "stage_us_alone": stage_us,
-        "stage_gbs_alone": {k: by[k] / (stage_us[k] * 1e-6) / 1e9 for k in ("estimate", "topk", "attention")},
+        "stage_gbs_alone": {k: by[k] / (stage_us[k] * 1e-6) / 1e9 for k in ("estimate", "topk", "attention") if k in stage_us},
     }
     if not args.no_cpu and world >= 1:
         sec, n = time_cpu_reference(L, H, B, steps=20, warmup=1, budget_s=20.0)
@@ -422,6 +436,8 @@ def main():
     ap.add_argument("--heads", type=int, default=32, help="KV heads per GPU")
     ap.add_argument("--page-size", dest="page_size", type=int, default=16)
     ap.add_argument("--eager", action="store_true", help="no CUDA graph")
+    ap.add_argument("--unfused", action="store_true",
+                    help="four launches per layer (append, estimate, top-k, sparse decode) instead of the fused step")
     ap.add_argument("--no-cpu", dest="no_cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per estimate launch from an ncu capture; default: the figure in "

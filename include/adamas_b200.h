@@ -212,6 +212,32 @@ int adamas_decode_forward_static(const void* q, void* o, float* lse, const void*
                                  int last_page_idx, int last_page_len, int tail_len, float sm_scale,
                                  adamas_stream_t stream);
 
+/* Stages 3 and 4 in one launch: per head, the k smallest of n distances (ADAMAS_VAL_U16 values below
+ * 512, rows on 16-byte boundaries; ties to the lower position) are selected and attended together with
+ * the newest token (entry last_page_len-1 of page last_page_idx).  Token t of the row is looked up as
+ * kv_page_table[t / page_size] * page_size + t % page_size.  out_idx (optional, [H, out_stride])
+ * receives the winners' physical token slots in ascending position order, exactly what adamas_topk
+ * would write.  Replaces the topk_filtering + BatchDecodeWithPagedKVCachePyTorchWrapper::Forward pair
+ * (adamas/models/Adamas.py:185-200) for n up to 131072. */
+int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, const void* q, void* o,
+                         float* lse, const void* kv_data, const int32_t* kv_page_table, int page_size,
+                         int num_heads, int head_dim, int dtype, int last_page_idx, int last_page_len,
+                         int32_t* out_idx, int64_t out_stride, float sm_scale, adamas_stream_t stream);
+
+/* One layer's whole decode step in one call (three launches: fused append, estimate, select+attend):
+ * what adamas/models/Adamas.py:145-200 does with seven launches.  q, k, v, o [1,H,D]; q_code
+ * [1,H,D/8] scratch/output; dist_scratch [H, dist_stride] 16-bit, rows on 16-byte boundaries,
+ * dist_stride >= context - 1.  Requires context > budget (otherwise every page is attended: use
+ * adamas_decode_forward).  kv_last_page_idx is the physical number of the last KV page. */
+int adamas_decode_step(const void* q, const void* k, const void* v, void* o, float* lse, void* q_code,
+                       void* kv_data, const int32_t* kv_page_table, int kv_num_pages,
+                       int kv_last_page_len, int kv_last_page_idx, void* code_data,
+                       const int32_t* code_page_table, int code_num_pages, int code_last_page_len,
+                       int num_heads, int head_dim, int page_size, int dtype, int budget,
+                       void* dist_scratch, int64_t dist_stride, int32_t* out_idx, int64_t out_stride,
+                       float hadamard_scale, const float* thresholds3_host, float sm_scale,
+                       adamas_stream_t stream);
+
 /* Merge P partial results over disjoint token sets: o_parts [P, H, D] fp32 (each already
  * normalised), lse_parts [P, H] base-2; writes o [H, D] in dtype and, optionally, lse [H].
  * Replaces VariableLengthMergeStates (called at kernels/include/decode/decode_attn.cuh:1050-1059);

@@ -405,6 +405,39 @@ def test_full_step_token_granular(dtype, L, ps, budget):
     assert torch.equal(o, o2)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("L,ps,budget,H", [
+    (70, 16, 8, 32), (300, 16, 64, 32), (2049, 16, 33, 8), (4096, 16, 256, 32), (5000, 1, 1024, 32),
+    (9001, 32, 4096, 4), (32768, 16, 1024, 32), (70000, 16, 2048, 2),
+])
+def test_fused_decode_step(dtype, L, ps, budget, H):
+    """decode_step (append + estimate + select/attend in one call) against the oracle: codes and
+    selected slots bit-exact, output within tolerance, and equal winners to the separate kernels."""
+    _, K, U = _mods()
+    st = State(L - 1, H, ps, dtype, seed=L + H, budget_pages=max(1, budget // ps), fused=True, max_seq_len=L + ps)
+    # State holds L-1 tokens (its last one appended by a decode step); append one more with decode_step
+    c = st.c
+    c.end_forward()
+    q = _randn((1, H, 128), 901 + L, dtype)
+    k_new = _randn((1, H, 128), 902 + L, dtype)
+    v_new = _randn((1, H, 128), 903 + L, dtype)
+    c.prepare_hadamard(1)
+    c.begin_forward(1)
+    if ps > 1:
+        assert c.inference_token_budget == min(max(1, budget // ps) * ps, L)
+    bud = c.inference_token_budget
+    o = U.decode_step(q.to(DEV), k_new.to(DEV), v_new.to(DEV), c, 0)
+    k_all = torch.cat([st.k, k_new], 0)
+    v_all = torch.cat([st.v, v_new], 0)
+    r = ref.decode_step(q[0], k_all, v_all, bud)
+    table = np.asarray(c.kv_cache.indicies)
+    want_slots = table[r["sel"] // ps] * ps + r["sel"] % ps
+    np.testing.assert_array_equal(c.topk_dindices_buffer.cpu().numpy(), want_slots)
+    _assert_attn_close(o[0], r["out"])
+    from adamas_b200 import _lib
+    assert _lib.device_error(clear=False) == 0
+
+
 def test_dense_layer_page_size_16():
     _, K, U = _mods()
     st = State(1000, 32, 16, seed=9, budget_pages=1 << 20)
