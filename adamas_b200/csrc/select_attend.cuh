@@ -3,7 +3,7 @@
 // token.  Used by the fused decode step; the separate top-k and decode kernels remain for callers
 // that want the stages one by one.
 //
-// One thread-block cluster (CL <= 8 blocks x 256 threads) per head.  Block `cr` owns a contiguous
+// One thread-block cluster (CL <= 8 blocks x 512 threads) per head.  Block `cr` owns a contiguous
 // slice of the head's distance row, keeps it in registers, and later attends over the winners that
 // lie in its own slice, so the selected indices never travel between blocks:
 //   pre   zero the exchange buffers, load the query row, cluster barrier (peers have started);
@@ -15,9 +15,9 @@
 //         elements lie in lower-ranked slices (= its tie quota and its offset in the output list);
 //   2     ordered compaction of the block's winners into a shared-memory list (and, optionally, to
 //         the global index list at the right offset);
-//   3     attention over the list in tiles of 128 tokens: slot look-up through the page table, K/V
-//         rows gathered with 16-byte cp.async into XOR-swizzled shared memory, two threads per token
-//         for q.K, online softmax in base 2, one thread per (token group, 8-dim chunk) for P.V;
+//   3     attention over the list in tiles of 128 tokens: K/V rows gathered with 16-byte cp.async
+//         into XOR-swizzled shared memory, four threads per token for q.K, online softmax in base
+//         2, one thread per (group of 4 tokens, 8-dim chunk) for P.V;
 //   4     the partial (o, m, l) is stored into slot `cr` of rank 0's shared memory; cluster barrier;
 //         rank 0 merges the CL partials and writes the head's output.
 // Only two cluster barriers sit on the critical path after the start-up one.
@@ -28,7 +28,7 @@
 
 namespace adamas {
 
-constexpr int kSaThreads = 256;
+constexpr int kSaThreads = 512;
 constexpr int kSaWarps = kSaThreads / 32;
 constexpr int kSaBins = 512;
 constexpr int kSaTile = 128;          // tokens per attention tile
@@ -55,12 +55,14 @@ struct SelectAttendParams {
   float scale_log2;
 };
 
+static_assert(kSaBins == kSaThreads, "one histogram bin per thread");
+
 struct SaShared {
   unsigned local[kSaBins];
   unsigned per_src[kSaMaxCluster][kSaBins];
   float part_o[kSaMaxCluster][kHeadDim];     // rank 0 only: partial outputs of the blocks
   float part_ml[kSaMaxCluster][2];
-  float s_o[16][kHeadDim];
+  float s_o[16][kHeadDim];                   // partial outputs of the 16 warps
   float s_logit[kSaTile];
   float s_p[kSaTile];
   float s_red[kSaWarps];
@@ -71,7 +73,7 @@ struct SaShared {
 
 // Dynamic shared memory: K tile (32 KB) | V tile (32 KB) | winner list (list_capacity * 4 bytes).
 template <typename T, int ITEMS>
-__global__ void __launch_bounds__(kSaThreads) select_attend_kernel(const SelectAttendParams p) {
+__global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const SelectAttendParams p) {
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
   extern __shared__ __align__(16) uint8_t sa_smem[];
@@ -90,22 +92,20 @@ __global__ void __launch_bounds__(kSaThreads) select_attend_kernel(const SelectA
   int32_t* s_list = reinterpret_cast<int32_t*>(sa_smem + 2 * kSaTile * 256);
 
   // ---- pre: buffers, query, start-up barrier --------------------------------------------------------
-  for (int i = tid; i < kSaBins; i += kSaThreads) sh.local[i] = 0;
-  for (int i = tid; i < kSaMaxCluster * kSaBins; i += kSaThreads) (&sh.per_src[0][0])[i] = 0;
-
-  // q.K mapping: thread pair (tl = tid / 2, half = tid % 2); step i reads logical chunk half*8 + (i ^ half*4)
-  const int qk_tl = tid >> 1;
-  const int half = tid & 1;
-  float qreg[8][8];
+  {
+    uint4* z = reinterpret_cast<uint4*>(&sh.local[0]);   // local[] and per_src[] are contiguous
+    for (int i = tid; i < (kSaBins + kSaMaxCluster * kSaBins) / 4; i += kSaThreads) z[i] = make_uint4(0, 0, 0, 0);
+  }
+  // q.K mapping: four threads per token (tl = tid / 4, quarter = tid % 4); step i of a thread reads
+  // logical chunk 4*quarter + ((i + quarter) & 3), which keeps the 8 lanes of a quarter-warp on 8
+  // different 16-byte bank groups.  The query chunks stay packed in registers.
+  const int qk_tl = tid >> 2;
+  const int quarter = tid & 3;
+  uint4 qpk[4];
   {
     const T* qp = static_cast<const T*>(p.q) + static_cast<int64_t>(head) * kHeadDim;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int lc = half * 8 + (i ^ (half * 4));
-      unpack8<T>(ld_16(qp + lc * 8), qreg[i]);
-#pragma unroll
-      for (int d = 0; d < 8; ++d) qreg[i][d] *= p.scale_log2;
-    }
+    for (int i = 0; i < 4; ++i) qpk[i] = ld_16(qp + (4 * quarter + ((i + quarter) & 3)) * 8);
   }
   cluster.sync();
   grid_dependency_wait();
@@ -133,6 +133,15 @@ __global__ void __launch_bounds__(kSaThreads) select_attend_kernel(const SelectA
     raw[i][0] = v.x; raw[i][1] = v.y; raw[i][2] = v.z; raw[i][3] = v.w;
     vmask[i] = m;
   }
+  // With pages of 8 tokens or more (a power of two) a granule lies inside one page: fetch its
+  // physical page number now, long before the winners are known.
+  const bool page_per_granule = p.ps_shift >= 3;
+  int granule_page[ITEMS];
+#pragma unroll
+  for (int i = 0; i < ITEMS; ++i) {
+    granule_page[i] = 0;
+    if (page_per_granule && g0 + i < blk_end) granule_page[i] = __ldg(p.kv_table + (((g0 + i) * 8) >> p.ps_shift));
+  }
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
 #pragma unroll
@@ -142,27 +151,22 @@ __global__ void __launch_bounds__(kSaThreads) select_attend_kernel(const SelectA
     }
   }
   __syncthreads();
-  for (int b = tid; b < kSaBins; b += kSaThreads) {
-    const unsigned c = sh.local[b];
+  {
+    const unsigned c = sh.local[tid];   // kSaBins == kSaThreads: one bin per thread
     if (c != 0)
-      for (unsigned r = 0; r < CL; ++r) *cluster.map_shared_rank(&sh.per_src[cr][b], r) = c;
+      for (unsigned r = 0; r < CL; ++r) *cluster.map_shared_rank(&sh.per_src[cr][tid], r) = c;
   }
   cluster.sync();
 
-  // every block: total histogram, cut, counts in lower-ranked slices
+  // every block: total histogram, cut, counts in lower-ranked slices (one bin per thread)
   {
-    unsigned tot[2] = {0, 0}, low[2] = {0, 0};
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int b = tid * 2 + u;
-      for (unsigned r = 0; r < CL; ++r) {
-        const unsigned c = sh.per_src[r][b];
-        tot[u] += c;
-        if (r < cr) low[u] += c;
-      }
+    unsigned tot = 0, low = 0;
+    for (unsigned r = 0; r < CL; ++r) {
+      const unsigned c = sh.per_src[r][tid];
+      tot += c;
+      if (r < cr) low += c;
     }
-    const unsigned s = tot[0] + tot[1];
-    unsigned incl = s;
+    unsigned incl = tot;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
@@ -174,31 +178,19 @@ __global__ void __launch_bounds__(kSaThreads) select_attend_kernel(const SelectA
     unsigned wbase = 0;
 #pragma unroll
     for (int w2 = 0; w2 < kSaWarps; ++w2) wbase += (w2 < warp) ? sh.warp_a[w2] : 0u;
-    const unsigned excl = wbase + incl - s;
+    const unsigned excl = wbase + incl - tot;
     const unsigned want = static_cast<unsigned>(p.k);
-    if (excl < want && excl + s >= want) {   // exactly one thread
-      const bool first = excl + tot[0] >= want;
-      sh.cut = tid * 2 + (first ? 0 : 1);
-      sh.before = first ? excl : excl + tot[0];
+    if (excl < want && excl + tot >= want) {   // exactly one thread
+      sh.cut = tid;
+      sh.before = excl;
     }
     __syncthreads();
     const unsigned cutb = sh.cut;
-    unsigned lt = 0, eq = 0;
+    unsigned lt = (static_cast<unsigned>(tid) < cutb) ? low : 0u;
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const unsigned b = tid * 2 + u;
-      if (b < cutb) lt += low[u];
-      if (b == cutb) eq += low[u];
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      lt += __shfl_xor_sync(0xffffffffu, lt, o);
-      eq += __shfl_xor_sync(0xffffffffu, eq, o);
-    }
-    if (lane == 0) {
-      if (lt) atomicAdd(&sh.lt_before, lt);
-      if (eq) atomicAdd(&sh.eq_before, eq);
-    }
+    for (int o = 16; o > 0; o >>= 1) lt += __shfl_xor_sync(0xffffffffu, lt, o);
+    if (lane == 0 && lt) atomicAdd(&sh.lt_before, lt);
+    if (static_cast<unsigned>(tid) == cutb) sh.eq_before = low;
     __syncthreads();
   }
   const unsigned cut = sh.cut;
@@ -257,15 +249,20 @@ __global__ void __launch_bounds__(kSaThreads) select_attend_kernel(const SelectA
           }
           if (pos >= 0) {
             const unsigned t = static_cast<unsigned>((g0 + i) * 8 + j);   // logical token position
-            unsigned pg, e;
-            if (p.ps_shift >= 0) {
-              pg = t >> p.ps_shift;
-              e = t & (p.page_size - 1);
+            int32_t slot;
+            if (page_per_granule) {
+              slot = granule_page[i] * p.page_size + static_cast<int32_t>(t & (p.page_size - 1));
             } else {
-              pg = t / p.page_size;
-              e = t - pg * p.page_size;
+              unsigned pg, e;
+              if (p.ps_shift >= 0) {
+                pg = t >> p.ps_shift;
+                e = t & (p.page_size - 1);
+              } else {
+                pg = t / p.page_size;
+                e = t - pg * p.page_size;
+              }
+              slot = __ldg(p.kv_table + pg) * p.page_size + static_cast<int32_t>(e);
             }
-            const int32_t slot = __ldg(p.kv_table + pg) * p.page_size + static_cast<int32_t>(e);
             if (pos < p.list_capacity) s_list[pos] = slot;
             if (oi) oi[pos] = slot;
           }
@@ -287,18 +284,18 @@ __global__ void __launch_bounds__(kSaThreads) select_attend_kernel(const SelectA
   float o_acc[8];
 #pragma unroll
   for (int d = 0; d < 8; ++d) o_acc[d] = 0.f;
-  const int pv_g = tid >> 4;   // token group: tokens pv_g*8 .. pv_g*8+7 of the tile
+  const int pv_g = tid >> 4;   // token group: tokens pv_g*4 .. pv_g*4+3 of the tile (32 groups)
   const int pv_c = tid & 15;   // 8-dim chunk
   const unsigned ps = static_cast<unsigned>(p.page_size);
 
   for (int t0 = 0; t0 < n_loc; t0 += kSaTile) {
     const int tile_tokens = min(kSaTile, n_loc - t0);
-    // gather: thread -> chunk c = tid % 16 of tokens tl = tid / 16 + 16 * i
+    // gather: thread -> chunk c = tid % 16 of tokens tl = tid / 16 + 32 * i
     {
       const int c = tid & 15;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int tl = (tid >> 4) + 16 * i;
+      for (int i = 0; i < 4; ++i) {
+        const int tl = (tid >> 4) + 32 * i;
         if (tl < tile_tokens) {
           const unsigned slot = static_cast<unsigned>(s_list[t0 + tl]);
           unsigned page, e;
@@ -325,18 +322,20 @@ __global__ void __launch_bounds__(kSaThreads) select_attend_kernel(const SelectA
     const bool live = qk_tl < tile_tokens;
     if (live) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int lc = half * 8 + (i ^ (half * 4));
+      for (int i = 0; i < 4; ++i) {
+        const int lc = 4 * quarter + ((i + quarter) & 3);
         const int phys = lc ^ (qk_tl & 3);
-        float kf[8];
+        float kf[8], qf[8];
         unpack8<T>(*reinterpret_cast<const uint4*>(sk + qk_tl * 256 + phys * 16), kf);
+        unpack8<T>(qpk[i], qf);
 #pragma unroll
-        for (int d = 0; d < 8; ++d) acc = fmaf(qreg[i][d], kf[d], acc);
+        for (int d = 0; d < 8; ++d) acc = fmaf(qf[d], kf[d], acc);
       }
     }
     acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-    const float logit = live ? acc : -INFINITY;
-    if (half == 0) sh.s_logit[qk_tl] = logit;
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    const float logit = live ? acc * p.scale_log2 : -INFINITY;
+    if (quarter == 0) sh.s_logit[qk_tl] = logit;
     float wmax = logit;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, o));
@@ -354,17 +353,19 @@ __global__ void __launch_bounds__(kSaThreads) select_attend_kernel(const SelectA
       sh.s_p[tid] = pr;
       psum = pr;
     }
+    if (tid < kSaTile) {   // warps 0..3
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
-    if (lane == 0) sh.s_sum[warp] = psum;
+      for (int o = 16; o > 0; o >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
+      if (lane == 0) sh.s_sum[warp] = psum;
+    }
     __syncthreads();
     l_run = l_run * rescale + ((sh.s_sum[0] + sh.s_sum[1]) + (sh.s_sum[2] + sh.s_sum[3]));
     m_run = m_new;
 #pragma unroll
     for (int d = 0; d < 8; ++d) o_acc[d] *= rescale;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int tl = pv_g * 8 + i;
+    for (int i = 0; i < 4; ++i) {
+      const int tl = pv_g * 4 + i;
       const float pr = sh.s_p[tl];
       if (pr != 0.f) {
         const int phys = pv_c ^ (tl & 3);
@@ -379,7 +380,11 @@ __global__ void __launch_bounds__(kSaThreads) select_attend_kernel(const SelectA
 
   // ---- 4: partial to rank 0, merge -----------------------------------------------------------------------
 #pragma unroll
-  for (int d = 0; d < 8; ++d) sh.s_o[pv_g][pv_c * 8 + d] = o_acc[d];
+  for (int d = 0; d < 8; ++d) o_acc[d] += __shfl_xor_sync(0xffffffffu, o_acc[d], 16);   // the warp's two groups
+  if (lane < 16) {
+#pragma unroll
+    for (int d = 0; d < 8; ++d) sh.s_o[warp][pv_c * 8 + d] = o_acc[d];
+  }
   __syncthreads();
   if (tid < kHeadDim) {
     float od = 0.f;

@@ -259,8 +259,13 @@ class Workload:
                 q, k, v = self.d_qkv[0, layer], self.d_qkv[1, layer], self.d_qkv[2, layer]
                 if stage == "append":
                     U.append_qkv_fused(q, k, v, c, layer, out=self.q_code[layer])
-                elif stage == "estimate":
+                elif stage == "estimate" and self.args.unfused:
                     U.decode_estimate(self.q_code[layer], c, layer)
+                elif stage == "estimate":      # fused step: integer distances, as decode_step asks for
+                    n = c.hadamard_cache.seqlen - 1
+                    K.estimate_attn_score(self.q_code[layer], c.distance_scratch(n), c.hadamard_cache.buf_layer(layer),
+                                          c.hadamard_indices, None, c.hadamard_cache.last_page_len,
+                                          c.hadamard_last_page_idx, c.layout)
                 elif stage == "topk":
                     U.decode_topk(c.estimate_buffer(c.hadamard_cache.seqlen - 1), c)
                 elif stage == "attention":
@@ -368,6 +373,8 @@ def run_ours(args):
     stage_us = {}
     # leave integer distances of the last layer in the scratch for the select/attend stage
     wl.U.decode_step(wl.d_qkv[0, 0], wl.d_qkv[1, 0], wl.d_qkv[2, 0], wl.c, 0, out=wl.d_out[0], record_indices=True)
+    for layer in range(args.layers):   # query codes of every layer, for the estimate stage run alone
+        wl.U.append_qkv_fused(wl.d_qkv[0, layer], wl.d_qkv[1, layer], wl.d_qkv[2, layer], wl.c, layer, out=wl.q_code[layer])
     stage_list = ("estimate", "append", "select_attend") if not args.unfused else ("estimate", "append", "topk", "attention")
     for stage in stage_list:
         g_st = wl.capture_stage_only(stage)
