@@ -92,6 +92,20 @@ def hadamard_transform(x: torch.Tensor, inplace: bool = False, scale: Optional[f
     return y
 
 
+def apply_rope_in_place(q: torch.Tensor, k: torch.Tensor, past_kv_len: int, rope_scale: float = 1.0,
+                        rope_theta: float = 1e4) -> None:
+    """adamas/ops/csrc/page.cu:228-269.  q [N,Hq,D], k [N,Hk,D] rotated in place; token s has
+    position past_kv_len + s; linear position scaling by rope_scale."""
+    _check_input(q, "q", 3)
+    _check_input(k, "k", 3)
+    _require(q.size(0) == k.size(0) and q.size(2) == k.size(2) == 128 and q.dtype == k.dtype,
+             "q and k must be [N, H, 128] of one dtype")
+    _lib.check(lib.adamas_apply_rope_in_place(_ptr(q), _ptr(k), q.size(0), q.size(1), k.size(1), 128,
+                                              int(past_kv_len), float(rope_scale), float(rope_theta),
+                                              _dtype_code(q.dtype, "apply_rope_in_place"), _stream()),
+               "apply_rope_in_place")
+
+
 def bucketize_pack(h: torch.Tensor, o: torch.Tensor, thresholds=None) -> None:
     """o[..., w] = packed 2-bit buckets of h[..., 8w:8w+8] (kernels/include/decode/decode_page.cuh:380-398)."""
     _check_input(h, "h")
@@ -146,15 +160,24 @@ def append_kv_cache_decode(k, v, h, o, kv_data, kv_indices, kv_indptr, kv_last_p
 
 def append_kv_cache_decode_fused(q, k, v, o, kv_data, kv_indices, kv_last_page_len, hadamard_data,
                                  hadamard_indices, hadamard_last_page_len, layout=NHD, scale=None,
-                                 thresholds=None) -> None:
+                                 thresholds=None, rope=None) -> None:
     """One launch for torch.cat((q, k)) + hadamard_transform + append_kv_cache_decode
-    (adamas/models/Adamas.py:145-161)."""
+    (adamas/models/Adamas.py:145-161).  With rope=(rope_scale, rope_theta) q and k arrive
+    un-rotated and are rotated in place first (also replaces apply_rope_in_place, Adamas.py:113)."""
     num_heads, head_dim, page_size = _check_append(k, v, kv_data, kv_indices, hadamard_data, hadamard_indices, layout)
     _check_input(q, "q", 3)
     _check_input(o, "o", 3)
     _require(tuple(q.shape) == tuple(k.shape) and q.dtype == k.dtype and k.size(0) == 1, "q, k, v must be [1, H, D]")
     _require(o.size(1) == num_heads and o.size(2) == head_dim // 8 and o.element_size() == 2, "o must be [1, H, D/8] 16-bit")
     s = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)
+    if rope is not None:
+        _lib.check(lib.adamas_append_decode_rope_fused(
+            _ptr(q), _ptr(k), _ptr(v), _ptr(o),
+            _ptr(kv_data), _ptr(kv_indices), kv_indices.numel(), int(kv_last_page_len),
+            _ptr(hadamard_data), _ptr(hadamard_indices), hadamard_indices.numel(), int(hadamard_last_page_len),
+            num_heads, head_dim, page_size, s, _lib.thresholds_arg(thresholds), float(rope[0]), float(rope[1]),
+            _dtype_code(k.dtype, "append_kv_cache_decode_rope_fused"), _stream()), "append_kv_cache_decode_rope_fused")
+        return
     _lib.check(lib.adamas_append_decode_fused(
         _ptr(q), _ptr(k), _ptr(v), _ptr(o),
         _ptr(kv_data), _ptr(kv_indices), kv_indices.numel(), int(kv_last_page_len),

@@ -35,6 +35,8 @@ SIGNATURES = {
     "adamas_bucketize_pack": [_P, _P, _L, _I, _FP, _I, _P],
     "adamas_append_decode": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _FP, _I, _P],
     "adamas_append_decode_fused": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _FP, _I, _P],
+    "adamas_apply_rope_in_place": [_P, _P, _L, _I, _I, _I, _L, _F, _F, _I, _P],
+    "adamas_append_decode_rope_fused": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _FP, _F, _F, _I, _P],
     "adamas_append_prefill": [_P, _P, _P, _L, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _FP, _I, _P],
     "adamas_estimate": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _L, _I, _I, _I, _P],
     "adamas_topk": [_P, _I, _L, _I, _P, _L, _I, _I, _I, _P, _P, _L, _P],

@@ -115,6 +115,8 @@ int get_device_info(const DeviceInfo** out) {
     SET_CARVEOUT((append_decode_kernel<__half, false>));
     SET_CARVEOUT((append_decode_kernel<__nv_bfloat16, true>));
     SET_CARVEOUT((append_decode_kernel<__nv_bfloat16, false>));
+    SET_CARVEOUT((append_decode_kernel<__half, true, true>));
+    SET_CARVEOUT((append_decode_kernel<__nv_bfloat16, true, true>));
     SET_CARVEOUT((estimate_kernel<0, __half, 0>));
     SET_CARVEOUT((estimate_kernel<0, __half, 1>));
     SET_CARVEOUT((estimate_kernel<0, __half, 2>));
@@ -257,10 +259,12 @@ static int append_decode_impl(const void* k, const void* v, const void* qh, cons
                               const int32_t* code_page_table, int code_num_pages,
                               int code_last_page_len, int num_heads, int head_dim, int page_size,
                               float scale, const float* thresholds3_host, int dtype,
-                              adamas_stream_t stream) {
+                              adamas_stream_t stream, bool rope = false, float rope_scale = 1.f,
+                              float rope_theta = 1e4f) {
   if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
   ADAMAS_REQUIRE(k && v && qh && kh && q_code_out && kv_data && code_data && kv_page_table &&
                      code_page_table, "null pointer");
+  ADAMAS_REQUIRE(!rope || (rope_scale > 0.f && rope_theta > 0.f), "rope_scale and rope_theta must be positive");
   ADAMAS_REQUIRE(kv_num_pages >= 1 && code_num_pages >= 1, "page tables must not be empty");
   ADAMAS_REQUIRE(kv_last_page_len >= 1 && kv_last_page_len <= page_size, "kv_last_page_len out of range");
   ADAMAS_REQUIRE(code_last_page_len >= 1 && code_last_page_len <= page_size,
@@ -279,7 +283,20 @@ static int append_decode_impl(const void* k, const void* v, const void* qh, cons
                 static_cast<const T*>(k), static_cast<const T*>(v), static_cast<const T*>(qh),  \
                 static_cast<const T*>(kh), static_cast<uint16_t*>(q_code_out), tgt,             \
                 kv_num_pages - 1, kv_last_page_len - 1, code_num_pages - 1,                     \
-                code_last_page_len - 1, scale, th)
+                code_last_page_len - 1, scale, th, 0.f, RopeParams{1.f, 1e4f})
+  if (rope) {
+    // position of the token being appended
+    const float pos = static_cast<float>(static_cast<int64_t>(kv_num_pages - 1) * page_size + kv_last_page_len - 1);
+    const RopeParams rp{1.0f / rope_scale, rope_theta};
+#define LAUNCH_AD_ROPE(T)                                                                            \
+  ADAMAS_LAUNCH("append_decode_kernel", (append_decode_kernel<T, true, true>), dim3(blocks), dim3(256), 0, \
+                st, 1, static_cast<const T*>(k), static_cast<const T*>(v), static_cast<const T*>(qh), \
+                static_cast<const T*>(kh), static_cast<uint16_t*>(q_code_out), tgt, kv_num_pages - 1, \
+                kv_last_page_len - 1, code_num_pages - 1, code_last_page_len - 1, scale, th, pos, rp)
+    if (dtype == ADAMAS_F16) LAUNCH_AD_ROPE(__half); else LAUNCH_AD_ROPE(__nv_bfloat16);
+#undef LAUNCH_AD_ROPE
+    return check_launch("append_decode_kernel");
+  }
   if (dtype == ADAMAS_F16) {
     if (fused) LAUNCH_AD(__half, true); else LAUNCH_AD(__half, false);
   } else {
@@ -314,6 +331,43 @@ int adamas_append_decode_fused(const void* q, const void* k, const void* v, void
                             kv_last_page_len, code_data, code_page_table, code_num_pages,
                             code_last_page_len, num_heads, head_dim, page_size, scale,
                             thresholds3_host, dtype, stream);
+}
+
+int adamas_append_decode_rope_fused(void* q, void* k, const void* v, void* q_code_out, void* kv_data,
+                                    const int32_t* kv_page_table, int kv_num_pages, int kv_last_page_len,
+                                    void* code_data, const int32_t* code_page_table, int code_num_pages,
+                                    int code_last_page_len, int num_heads, int head_dim, int page_size,
+                                    float scale, const float* thresholds3_host, float rope_scale,
+                                    float rope_theta, int dtype, adamas_stream_t stream) {
+  return append_decode_impl(k, v, q, k, true, q_code_out, kv_data, kv_page_table, kv_num_pages,
+                            kv_last_page_len, code_data, code_page_table, code_num_pages,
+                            code_last_page_len, num_heads, head_dim, page_size, scale,
+                            thresholds3_host, dtype, stream, true, rope_scale, rope_theta);
+}
+
+int adamas_apply_rope_in_place(void* q, void* k, int64_t seq_len, int num_q_heads, int num_kv_heads,
+                               int head_dim, int64_t past_kv_len, float rope_scale, float rope_theta,
+                               int dtype, adamas_stream_t stream) {
+  ADAMAS_REQUIRE(head_dim == kHeadDim, "head_dim must be 128 (got %d)", head_dim);
+  ADAMAS_REQUIRE(dtype == ADAMAS_F16 || dtype == ADAMAS_BF16, "unsupported dtype %d", dtype);
+  ADAMAS_REQUIRE(seq_len >= 0 && num_q_heads >= 1 && num_kv_heads >= 1, "bad shape");
+  ADAMAS_REQUIRE(rope_scale > 0.f && rope_theta > 0.f, "rope_scale and rope_theta must be positive");
+  ADAMAS_REQUIRE(past_kv_len >= 0 && past_kv_len + seq_len < (int64_t(1) << 24),
+                 "positions must stay below 2^24 (exact in fp32)");
+  if (seq_len == 0) return ADAMAS_OK;
+  ADAMAS_REQUIRE(q && k, "null pointer");
+  const int64_t rows_q = seq_len * num_q_heads, rows_k = seq_len * num_kv_heads;
+  const unsigned blocks = rows_to_blocks(rows_q + rows_k);
+  const RopeParams rp{1.0f / rope_scale, rope_theta};
+  if (dtype == ADAMAS_F16)
+    rope_kernel<__half><<<blocks, 256, 0, to_stream(stream)>>>(static_cast<__half*>(q), static_cast<__half*>(k),
+                                                              rows_q, rows_k, num_q_heads, num_kv_heads,
+                                                              static_cast<int>(past_kv_len), rp);
+  else
+    rope_kernel<__nv_bfloat16><<<blocks, 256, 0, to_stream(stream)>>>(
+        static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k), rows_q, rows_k, num_q_heads,
+        num_kv_heads, static_cast<int>(past_kv_len), rp);
+  return check_launch("rope_kernel");
 }
 
 int adamas_append_prefill(const void* k, const void* v, const void* h, int64_t n_tokens, void* kv_data,

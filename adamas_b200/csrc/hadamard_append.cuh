@@ -53,6 +53,53 @@ __device__ __forceinline__ uint16_t bucketize_pack8(const float (&x)[8], Thresho
   return static_cast<uint16_t>(w);
 }
 
+// Llama rotary embedding (rotate-half form) of one 128-dim row spread over a half-warp: element e of
+// the first half pairs with e + 64, which lives in lane l16 ^ 8.  angle = pos * inv_freq(e % 64) with
+// inv_freq(j) = (1 / rope_scale) / theta^(2j/128), all in fp32 as the reference's kernel and the HF
+// module compute it (kernels/include/decode/decode_page.cuh:642-690).  The result is rounded to the
+// storage type, as the in-place reference operator leaves it.
+struct RopeParams {
+  float rcp_scale;
+  float theta;
+};
+
+template <typename T>
+__device__ __forceinline__ void rope_halfwarp(float (&x)[8], unsigned l16, float pos, RopeParams rp) {
+  const bool upper = (l16 & 8) != 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float other = __shfl_xor_sync(0xffffffffu, x[i], 8);
+    const int j = static_cast<int>(l16 & 7) * 8 + i;
+    const float inv_freq = rp.rcp_scale / powf(rp.theta, static_cast<float>(2 * j) * (1.0f / kHeadDim));
+    float sn, cs;
+    sincosf(pos * inv_freq, &sn, &cs);
+    // lower half: x*cos - partner*sin; upper half: x*cos + partner*sin
+    const float r = upper ? fmaf(other, sn, x[i] * cs) : fmaf(-other, sn, x[i] * cs);
+    x[i] = Elem<T>::round(r);
+  }
+}
+
+// In-place rotary embedding of q [seq, Hq, 128] and k [seq, Hk, 128]; token s has position past_len + s.
+template <typename T>
+__global__ void __launch_bounds__(256) rope_kernel(T* __restrict__ q, T* __restrict__ k, int64_t rows_q,
+                                                   int64_t rows_k, int hq, int hk, int past_len,
+                                                   RopeParams rp) {
+  const unsigned l16 = threadIdx.x & 15;
+  const int64_t row = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;
+  const bool valid = row < rows_q + rows_k;
+  const bool is_k = row >= rows_q;
+  const int64_t r = valid ? (is_k ? row - rows_q : row) : 0;
+  T* base = (is_k && valid) ? k : q;
+  const int heads = (is_k && valid) ? hk : hq;
+  const float pos = static_cast<float>(past_len + r / heads);
+  float v[8];
+  uint4 raw = make_uint4(0, 0, 0, 0);
+  if (valid) raw = ld_16(base + r * kHeadDim + l16 * 8);
+  unpack8<T>(raw, v);
+  rope_halfwarp<T>(v, l16, pos, rp);
+  if (valid) st_16(base + r * kHeadDim + l16 * 8, pack8<T>(v));
+}
+
 // y = round(scale * WHT(x)), rows x 128.
 template <typename T>
 __global__ void __launch_bounds__(256) hadamard_kernel(const T* __restrict__ x, T* __restrict__ y,
@@ -92,13 +139,15 @@ struct PagedTarget {
 };
 
 // Decode append: one half-warp per head.  FUSED: qh = q, kh = k and the transform runs here;
-// otherwise qh/kh point at rows 0/1 of the pre-transformed h.
-template <typename T, bool FUSED>
+// otherwise qh/kh point at rows 0/1 of the pre-transformed h.  ROPE (needs FUSED): q and k arrive
+// un-rotated; they are rotated for position `pos`, written back in place (the attention reads the
+// rotated q, the caller's k stays consistent with the cache) and then coded.
+template <typename T, bool FUSED, bool ROPE = false>
 __global__ void __launch_bounds__(256)
 append_decode_kernel(const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ qh,
                      const T* __restrict__ kh, uint16_t* __restrict__ q_code_out, PagedTarget tgt,
                      int kv_last_page, int kv_entry, int code_last_page, int code_entry, float scale,
-                     Thresholds th) {
+                     Thresholds th, float pos = 0.f, RopeParams rp = RopeParams{1.f, 1e4f}) {
   grid_dependency_wait();
   grid_launch_dependents();
   // physical pages of the slot being written: last entries of the two page tables
@@ -118,13 +167,23 @@ append_decode_kernel(const T* __restrict__ k, const T* __restrict__ v, const T* 
   const int64_t v_delta = static_cast<int64_t>(tgt.page_size) * H * kHeadDim;
   uint4 kraw = ld_16(k + in_off);
   uint4 vraw = ld_16(v + in_off);
+  float a[8], b[8];
+  unpack8<T>(ld_16(qh + in_off), a);
+  if (ROPE) {
+    unpack8<T>(kraw, b);
+    rope_halfwarp<T>(a, l16, pos, rp);
+    rope_halfwarp<T>(b, l16, pos, rp);
+    kraw = pack8<T>(b);
+    if (valid) {
+      st_16(const_cast<T*>(qh) + in_off, pack8<T>(a));
+      st_16(const_cast<T*>(k) + in_off, kraw);
+    }
+  }
   if (valid) {
     st_16(kv + k_off, kraw);
     st_16(kv + k_off + v_delta, vraw);
   }
 
-  float a[8], b[8];
-  unpack8<T>(ld_16(qh + in_off), a);
   if (FUSED) {
     unpack8<T>(kraw, b);
     wht128_halfwarp(a, l16);

@@ -15,6 +15,7 @@ __all__ = [
     "KvCache",
     "InferenceController",
     "BatchDecodeWithPagedKVCacheWrapper",
+    "apply_rope_in_place",
     "append_kvh",
     "append_qkv_fused",
     "decode_estimate",
@@ -22,6 +23,13 @@ __all__ = [
     "decode_sparse_attn",
     "decode_step",
 ]
+
+
+def apply_rope_in_place(q: torch.Tensor, k: torch.Tensor, past_kv_len: int, rope_scale: Optional[float] = None,
+                        rope_theta: Optional[float] = None):
+    """Rotary embedding of q, k [N,H,D] in place (adamas/utils/__init__.py:26-53)."""
+    _kernels.apply_rope_in_place(q, k, past_kv_len, 1.0 if rope_scale is None else rope_scale,
+                                 1e4 if rope_theta is None else rope_theta)
 
 
 def append_kvh(k: torch.Tensor, v: torch.Tensor, h: Optional[torch.Tensor], iController: InferenceController,
@@ -54,16 +62,17 @@ def append_kvh(k: torch.Tensor, v: torch.Tensor, h: Optional[torch.Tensor], iCon
 
 def append_qkv_fused(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, iController: InferenceController,
                      layer_idx: int, scale: Optional[float] = None,
-                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     out: Optional[torch.Tensor] = None, rope=None) -> torch.Tensor:
     """Decode-step append with the Hadamard transform inside: replaces torch.cat((q, k)),
     hadamard_transform and append_kvh (adamas/models/Adamas.py:145-161) with one launch.
-    Returns the packed query code [1,H,D/8] (written into `out` when given)."""
+    Returns the packed query code [1,H,D/8] (written into `out` when given).  rope=(rope_scale,
+    rope_theta): q and k are un-rotated and get rotated in place inside the same launch."""
     c = iController
     o = out if out is not None else torch.empty(1, k.size(1), k.size(2) // 8, dtype=k.dtype, device=k.device)
     _kernels.append_kv_cache_decode_fused(
         q, k, v, o, c.kv_cache.buf_layer(layer_idx), c.kv_indices_with_last, c.kv_cache.last_page_len,
         c.hadamard_cache.buf_layer(layer_idx), c.hadamard_indices, c.hadamard_cache.last_page_len,
-        c.layout, scale)
+        c.layout, scale, rope=rope)
     return o
 
 

@@ -104,6 +104,25 @@ int adamas_append_decode_fused(const void* q, const void* k, const void* v, void
                                int num_heads, int head_dim, int page_size, float scale,
                                const float* thresholds3_host, int dtype, adamas_stream_t stream);
 
+/* In-place rotary position embedding (Llama rotate-half form, linear position scaling) of
+ * q [seq_len, num_q_heads, D] and k [seq_len, num_kv_heads, D]; token s has position past_kv_len + s.
+ * Replaces apply_rope_in_place (adamas/ops/csrc/page.cu:228-269,
+ * kernels/include/decode/decode_page.cuh:642-726). */
+int adamas_apply_rope_in_place(void* q, void* k, int64_t seq_len, int num_q_heads, int num_kv_heads,
+                               int head_dim, int64_t past_kv_len, float rope_scale, float rope_theta,
+                               int dtype, adamas_stream_t stream);
+
+/* adamas_append_decode_fused with the rotary embedding in front: q and k [1,H,D] arrive un-rotated,
+ * are rotated in place for the position of the token being appended, and are then transformed, coded
+ * and stored.  One launch for apply_rope_in_place + torch.cat + hadamard_transform + append_kvh
+ * (adamas/models/Adamas.py:113,145-161). */
+int adamas_append_decode_rope_fused(void* q, void* k, const void* v, void* q_code_out, void* kv_data,
+                                    const int32_t* kv_page_table, int kv_num_pages, int kv_last_page_len,
+                                    void* code_data, const int32_t* code_page_table, int code_num_pages,
+                                    int code_last_page_len, int num_heads, int head_dim, int page_size,
+                                    float scale, const float* thresholds3_host, float rope_scale,
+                                    float rope_theta, int dtype, adamas_stream_t stream);
+
 /* Prefill append of n_tokens tokens ending at the current sequence end.  k, v, h [n_tokens,H,D];
  * h holds transformed keys.  If h is NULL the transform of k is computed inside (scale used).
  * Replaces append_kv_cache_prefill (adamas/ops/csrc/page.cu:111-226,

@@ -126,6 +126,22 @@ def encode(x: torch.Tensor, scale: Optional[float] = None,
     return pack_2bit(bucketize(h, thresholds))
 
 
+def rope(x: torch.Tensor, past_len: int, rope_scale: float = 1.0, rope_theta: float = 1e4) -> torch.Tensor:
+    """Llama rotary embedding with linear position scaling of x [N, H, D]; token s has position
+    past_len + s.  Same arithmetic as the HF module the reference's test compares against
+    (adamas/tests/test_rope.py:17-31): fp32 inverse frequencies theta^(-2j/D), angle = position /
+    rope_scale * inv_freq, out = x * cos + rotate_half(x) * sin; result in x.dtype."""
+    n, h, d = x.shape
+    inv_freq = 1.0 / (torch.tensor(rope_theta, dtype=torch.float32) ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    pos = torch.arange(past_len, past_len + n, dtype=torch.float32) / rope_scale
+    freqs = torch.outer(pos, inv_freq)
+    emb = torch.cat((freqs, freqs), dim=-1)
+    cos, sin = emb.cos()[:, None, :], emb.sin()[:, None, :]
+    xf = x.to(torch.float32)
+    rot = torch.cat((-xf[..., d // 2:], xf[..., : d // 2]), dim=-1)
+    return (xf * cos + rot * sin).to(x.dtype)
+
+
 # --------------------------------------------------------------------------
 # stage 2: distance estimate
 # --------------------------------------------------------------------------

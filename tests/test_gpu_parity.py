@@ -170,6 +170,48 @@ def test_append_codes_and_kv_bit_exact(dtype, fused, L, H, ps, sigma, scale):
         assert set(np.unique(ref.unpack_2bit(k_codes))) == {0, 1, 2, 3}
 
 
+@pytest.mark.parametrize("past_kv_len", [13, 24, 51, 77, 244, 311, 502, 1110, 32760])   # adamas/tests/test_rope.py:33
+@pytest.mark.parametrize("seq_len", [1, 2, 5, 19, 69, 251])
+def test_rope_in_place(past_kv_len, seq_len):
+    _, K, U = _mods()
+    scale = 8.0 if past_kv_len > 2000 else 1.0
+    q = _randn((seq_len, 32, 128), past_kv_len + seq_len, torch.float16)
+    k = _randn((seq_len, 32, 128), past_kv_len + seq_len + 1, torch.float16)
+    qd, kd = q.to(DEV), k.to(DEV)
+    U.apply_rope_in_place(qd, kd, past_kv_len, rope_scale=scale)
+    # the reference's tolerance for this operator (adamas/tests/test_rope.py:10-15)
+    torch.testing.assert_close(qd.cpu().float(), ref.rope(q, past_kv_len, scale).float(), rtol=5e-3, atol=5e-3)
+    torch.testing.assert_close(kd.cpu().float(), ref.rope(k, past_kv_len, scale).float(), rtol=5e-3, atol=5e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_rope_fused_append_equals_separate_launches(dtype):
+    """rope + cat + hadamard + append in one launch gives the same bits as the separate operators."""
+    _, K, U = _mods()
+    L, H, ps = 500, 32, 16
+    outs = []
+    for fused in (False, True):
+        st = State(L - 1, H, ps, dtype, seed=4, fused=True, max_seq_len=L + ps)
+        c = st.c
+        c.end_forward()
+        q = _randn((1, H, 128), 71, dtype).to(DEV)
+        k = _randn((1, H, 128), 72, dtype).to(DEV)
+        v = _randn((1, H, 128), 73, dtype).to(DEV)
+        c.prepare_hadamard(1)
+        c.begin_forward(1)
+        if fused:
+            code = U.append_qkv_fused(q, k, v, c, 0, rope=(8.0, 1e4))
+        else:
+            U.apply_rope_in_place(q, k, L - 1, rope_scale=8.0)
+            code = U.append_qkv_fused(q, k, v, c, 0)
+        table = c.kv_cache.indicies
+        kv = c.kv_cache.buf_layer(0)[table[-1], :, (L - 1) % ps].clone()
+        codes = c.hadamard_cache.buf_layer(0)[c.hadamard_cache.indicies[-1], 0, (L - 1) % ps].clone()
+        outs.append((q.clone(), k.clone(), code.clone(), kv, codes))
+    for a, b in zip(*outs):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
 # ------------------------------------------------------------------------------------------------
 # stage 2
 # ------------------------------------------------------------------------------------------------
@@ -408,7 +450,7 @@ def test_full_step_token_granular(dtype, L, ps, budget):
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("L,ps,budget,H", [
     (70, 16, 8, 32), (300, 16, 64, 32), (2049, 16, 33, 8), (4096, 16, 256, 32), (5000, 1, 1024, 32),
-    (9001, 32, 4096, 4), (32768, 16, 1024, 32), (70000, 16, 2048, 2),
+    (9001, 32, 4096, 4), (32768, 16, 1024, 32), (70000, 16, 2048, 2), (131072, 16, 2048, 4),
 ])
 def test_fused_decode_step(dtype, L, ps, budget, H):
     """decode_step (append + estimate + select/attend in one call) against the oracle: codes and

@@ -139,3 +139,21 @@ def test_topk_edge_cases():
     np.testing.assert_array_equal(ref.select_topk(d, 4), [[0, 1, 3, 4]])
     f = np.array([[0.5, -0.0, 0.0, -1.0, 2.0]], dtype=np.float16)
     np.testing.assert_array_equal(ref.select_topk(f, 2), [[1, 3]])
+
+
+def test_rope_matches_hf_apply_rotary_pos_emb():
+    """The rotate-half structure against transformers' own helper (the reference's test_rope.py uses it)."""
+    from transformers.models.llama.modeling_llama import apply_rotary_pos_emb
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(7, 4, 128, generator=g)
+    k = torch.randn(7, 4, 128, generator=g)
+    past, theta = 13, 1e4
+    inv_freq = 1.0 / (theta ** (torch.arange(0, 128, 2, dtype=torch.float32) / 128))
+    pos = torch.arange(past, past + 7, dtype=torch.float32)
+    emb = torch.cat((torch.outer(pos, inv_freq),) * 2, dim=-1)
+    cos, sin = emb.cos()[None], emb.sin()[None]                    # [1, N, D]
+    qh, kh = apply_rotary_pos_emb(q.transpose(0, 1)[None], k.transpose(0, 1)[None], cos, sin)
+    torch.testing.assert_close(ref.rope(q, past), qh[0].transpose(0, 1), rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(ref.rope(k, past), kh[0].transpose(0, 1), rtol=1e-5, atol=1e-5)
+    # position scaling divides the position
+    torch.testing.assert_close(ref.rope(q[:1], 16, rope_scale=8.0), ref.rope(q[:1], 2), rtol=1e-5, atol=1e-5)
