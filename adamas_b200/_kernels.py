@@ -302,8 +302,11 @@ class BatchDecodeWithPagedKVCachePyTorchWrapper:
 
     def __del__(self):
         h = getattr(self, "_handle", None)
-        if h:
-            lib.adamas_decode_handler_destroy(h)
+        if h and lib is not None:          # `lib` is already gone when the interpreter shuts down
+            try:
+                lib.adamas_decode_handler_destroy(h)
+            except Exception:
+                pass
             self._handle = None
 
     def begin_forward(self, indptr, num_qo_heads, num_kv_heads, head_dim, page_size, empty_data) -> None:

@@ -125,12 +125,12 @@ int get_device_info(const DeviceInfo** out) {
     SET_CARVEOUT((estimate_kernel<0, uint16_t, 1>));
     SET_CARVEOUT((estimate_kernel<0, uint16_t, 2>));
     SET_CARVEOUT((estimate_kernel<0, uint16_t, 4>));
-    SET_CARVEOUT((topk_cluster_kernel<0, 1>));
-    SET_CARVEOUT((topk_cluster_kernel<0, 2>));
-    SET_CARVEOUT((topk_cluster_kernel<0, 4>));
-    SET_CARVEOUT((topk_cluster_kernel<1, 1>));
-    SET_CARVEOUT((topk_cluster_kernel<1, 2>));
-    SET_CARVEOUT((topk_cluster_kernel<1, 4>));
+    SET_CARVEOUT((topk_cluster_kernel<0, 1, 256>));
+    SET_CARVEOUT((topk_cluster_kernel<0, 2, 256>));
+    SET_CARVEOUT((topk_cluster_kernel<0, 4, 256>));
+    SET_CARVEOUT((topk_cluster_kernel<1, 1, 256>));
+    SET_CARVEOUT((topk_cluster_kernel<1, 2, 256>));
+    SET_CARVEOUT((topk_cluster_kernel<1, 4, 256>));
     SET_CARVEOUT((sparse_decode_kernel<__half>));
     SET_CARVEOUT((sparse_decode_kernel<__nv_bfloat16>));
     SET_CARVEOUT((select_attend_kernel<__half, 1>));
@@ -506,14 +506,24 @@ int adamas_topk(const void* values, int value_format, int64_t value_stride, int 
   const bool aligned = (reinterpret_cast<uintptr_t>(values) & 15) == 0 &&
                        (num_rows == 1 || (value_stride * 2) % 16 == 0);
   const int g_max = aligned ? (n + 7) / 8 : (n + 14) / 8;
-  // smallest ITEMS (granules per thread) that lets a cluster of up to 8 blocks cover the row
-  int cl = 0, items = 0;
-  for (int it = 1; it <= 16 && cl == 0; it *= 2) {
+  // smallest ITEMS (granules per thread) that lets a cluster of up to 8 blocks of 256 threads cover
+  // the row; rows beyond 65536 values use blocks of 1024 threads with 2 or 4 granules per thread
+  int cl = 0, items = 0, nt = kTopkClThreads;
+  for (int it = 1; it <= 4 && cl == 0; it *= 2) {
     for (int c = 1; c <= 8; c *= 2) {
       if (static_cast<int64_t>(c) * it * kTopkClThreads >= g_max) {
         cl = c;
         items = it;
         break;
+      }
+    }
+  }
+  if (cl == 0) {
+    for (int it = 2; it <= 4 && cl == 0; it *= 2) {
+      if (static_cast<int64_t>(8) * it * 1024 >= g_max) {
+        cl = 8;
+        items = it;
+        nt = 1024;
       }
     }
   }
@@ -536,16 +546,17 @@ int adamas_topk(const void* values, int value_format, int64_t value_stride, int 
     prm.out_stride = out_stride;
     prm.granules_per_block = (g_max + cl - 1) / cl;
     const dim3 tgrid(static_cast<unsigned>(num_rows) * cl);
-#define LAUNCH_TK(F, I)                                                                         \
-  ADAMAS_LAUNCH("topk_cluster_kernel", topk_cluster_kernel<F, I>, tgrid, dim3(kTopkClThreads), 0, st, \
-                cl, prm)
-#define LAUNCH_TK_ITEMS(F)                  \
-  switch (items) {                          \
-    case 1: LAUNCH_TK(F, 1); break;         \
-    case 2: LAUNCH_TK(F, 2); break;         \
-    case 4: LAUNCH_TK(F, 4); break;         \
-    case 8: LAUNCH_TK(F, 8); break;         \
-    default: LAUNCH_TK(F, 16); break;       \
+#define LAUNCH_TK(F, I, N)                                                                      \
+  ADAMAS_LAUNCH("topk_cluster_kernel", (topk_cluster_kernel<F, I, N>), tgrid, dim3(N), 0, st, cl, prm)
+#define LAUNCH_TK_ITEMS(F)                                  \
+  if (nt == 1024) {                                         \
+    if (items == 2) LAUNCH_TK(F, 2, 1024); else LAUNCH_TK(F, 4, 1024); \
+  } else {                                                  \
+    switch (items) {                                        \
+      case 1: LAUNCH_TK(F, 1, 256); break;                  \
+      case 2: LAUNCH_TK(F, 2, 256); break;                  \
+      default: LAUNCH_TK(F, 4, 256); break;                 \
+    }                                                       \
   }
     if (value_format == ADAMAS_VAL_F16) {
       LAUNCH_TK_ITEMS(0)
@@ -598,14 +609,19 @@ struct SplitPlan {
   int num_splits;
 };
 
-// Aim at ~4 resident blocks per SM over all heads; never more splits than tiles.
+// One wave of resident blocks: up to 4 single-tile blocks per SM (32 KB of shared memory each) or 3
+// double-buffered multi-tile blocks (64 KB each), over all heads; never more splits than tiles.
 SplitPlan plan_splits(int64_t n_tokens, int num_heads, int num_sms) {
   const int64_t tiles = (n_tokens + kDecTile - 1) / kDecTile;
-  int64_t want = (static_cast<int64_t>(num_sms) * 4 + num_heads - 1) / num_heads;
-  if (want < 1) want = 1;
-  if (want > tiles) want = tiles;
+  const int64_t cap1 = std::max<int64_t>(1, (static_cast<int64_t>(num_sms) * 4 + num_heads - 1) / num_heads);
   SplitPlan p;
-  p.tiles_per_block = static_cast<int>((tiles + want - 1) / want);
+  if (tiles <= cap1) {
+    p.tiles_per_block = 1;
+    p.num_splits = static_cast<int>(tiles);
+    return p;
+  }
+  const int64_t cap2 = std::max<int64_t>(1, static_cast<int64_t>(num_sms) * 3 / num_heads);
+  p.tiles_per_block = static_cast<int>((tiles + cap2 - 1) / cap2);
   p.num_splits = static_cast<int>((tiles + p.tiles_per_block - 1) / p.tiles_per_block);
   return p;
 }

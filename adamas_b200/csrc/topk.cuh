@@ -282,14 +282,14 @@ topk_kernel(const uint16_t* __restrict__ values, int64_t value_stride, int n,
 //      output position of each of its winners and writes them (ascending position order, lower
 //      position wins ties).
 // -------------------------------------------------------------------------------------------------
-constexpr int kTopkClThreads = 256;
-constexpr int kTopkClWarps = kTopkClThreads / 32;
+constexpr int kTopkClThreads = 256;          // default block size; long rows use 1024
+constexpr int kTopkClMaxWarps = 32;
 
 struct TopkClusterShared {
   unsigned local[256];      // this block's histogram of the current pass
   unsigned total[2][256];   // row histogram of pass 0 / pass 1 (filled by all blocks of the cluster)
-  unsigned warp_a[kTopkClWarps];
-  unsigned warp_b[kTopkClWarps];
+  unsigned warp_a[kTopkClMaxWarps];
+  unsigned warp_b[kTopkClMaxWarps];
   unsigned base_lt;         // winners below the cut in lower-ranked blocks (filled by them)
   unsigned base_eq;
   unsigned bucket;
@@ -358,8 +358,9 @@ __device__ __forceinline__ void find_bin256(const unsigned* hist, unsigned want,
   }
 }
 
-template <int FORMAT, int ITEMS>
-__global__ void __launch_bounds__(kTopkClThreads) topk_cluster_kernel(const TopkParams p) {
+template <int FORMAT, int ITEMS, int NT = kTopkClThreads>
+__global__ void __launch_bounds__(NT) topk_cluster_kernel(const TopkParams p) {
+  constexpr int kWarps = NT / 32;
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
   __shared__ __align__(16) TopkClusterShared sh;
@@ -373,9 +374,11 @@ __global__ void __launch_bounds__(kTopkClThreads) topk_cluster_kernel(const Topk
 
   // zero the accumulators that peers will add into, then make sure every block has done so; all of
   // this can run while the kernel that produces `values` is still finishing
-  sh.local[tid] = 0;
-  sh.total[0][tid] = 0;
-  sh.total[1][tid] = 0;
+  if (tid < 256) {
+    sh.local[tid] = 0;
+    sh.total[0][tid] = 0;
+    sh.total[1][tid] = 0;
+  }
   if (tid == 0) { sh.base_lt = 0; sh.base_eq = 0; }
 
   const uint16_t* rowp = p.values + static_cast<int64_t>(row) * p.value_stride;
@@ -444,7 +447,7 @@ __global__ void __launch_bounds__(kTopkClThreads) topk_cluster_kernel(const Topk
     }
     __syncthreads();
     // push the non-zero bins to every block of the cluster (including this one)
-    {
+    if (tid < 256) {
       const unsigned c = sh.local[tid];
       if (c != 0) {
         for (unsigned r = 0; r < CL; ++r) atomicAdd(cluster.map_shared_rank(&sh.total[pass][tid], r), c);
@@ -484,7 +487,7 @@ __global__ void __launch_bounds__(kTopkClThreads) topk_cluster_kernel(const Topk
   __syncthreads();
   unsigned base_lt = 0, base_eq = 0, blk_lt = 0, blk_eq = 0;
 #pragma unroll
-  for (unsigned w2 = 0; w2 < kTopkClWarps; ++w2) {
+  for (unsigned w2 = 0; w2 < kWarps; ++w2) {
     const unsigned a = sh.warp_a[w2], b = sh.warp_b[w2];
     if (w2 < warp) { base_lt += a; base_eq += b; }
     blk_lt += a; blk_eq += b;

@@ -431,6 +431,45 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_sweep(args):
+    """Per-operator sweep (one GPU): context x budget, each stage timed alone in a CUDA graph with
+    one launch per layer (distinct caches, so data comes from HBM).  Prints one JSON line per point.
+    Batch > 1 in the reference's terms is b independent sequences, each with its own page table and
+    caches, i.e. b times these launches."""
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    for ctx in args.sweep_ctx:
+        layers = max(4, min(32, int(6e9 // (ctx * args.heads * 544))))   # keep the caches under ~6 GB
+        for budget in args.sweep_budget:
+            if budget >= ctx:
+                continue
+            a = argparse.Namespace(**vars(args))
+            a.ctx, a.budget, a.layers, a.unfused = ctx, budget, layers, True
+            wl = Workload(a, dev)
+            wl.step_eager()
+            torch.cuda.synchronize()
+            by = stage_bytes(ctx, args.heads, budget)
+            out = {"sweep": True, "ctx": ctx, "budget": budget, "heads": args.heads, "page_size": args.page_size,
+                   "layers_rotated": layers}
+            for stage in ("estimate", "topk", "attention", "select_attend", "append"):
+                if stage == "select_attend":
+                    a.unfused = False
+                    wl.U.decode_step(wl.d_qkv[0, 0], wl.d_qkv[1, 0], wl.d_qkv[2, 0], wl.c, 0, out=wl.d_out[0])
+                g = wl.capture_stage_only(stage)
+                for _ in range(3):
+                    g.replay()
+                us = timed(g.replay, args.steps, False, dev) * 1e3 / args.steps / layers
+                a.unfused = True
+                out[stage + "_us"] = round(us, 2)
+                if stage in by:
+                    out[stage + "_GBps"] = round(by[stage] / (us * 1e-6) / 1e9, 1)
+                del g
+            out["select_attend_GBps"] = round((by["topk"] + by["attention"]) / (out["select_attend_us"] * 1e-6) / 1e9, 1)
+            print(json.dumps(out), flush=True)
+            del wl
+            torch.cuda.empty_cache()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -449,7 +488,13 @@ def main():
     ap.add_argument("--traffic", type=float, default=None,
                     help="DRAM bytes per estimate launch from an ncu capture; default: the figure in "
                          "profiles/estimate_topk_decode_kernels_32k_ncu.md when the workload matches it")
+    ap.add_argument("--sweep", action="store_true", help="per-operator sweep over context x budget (one GPU)")
+    ap.add_argument("--sweep-ctx", dest="sweep_ctx", type=int, nargs="+", default=[8192, 32768, 131072])
+    ap.add_argument("--sweep-budget", dest="sweep_budget", type=int, nargs="+", default=[64, 128, 512, 2048])
     args = ap.parse_args()
+    if args.sweep:
+        run_sweep(args)
+        return
     if args.traffic is None and (args.ctx, args.heads, args.page_size) == (32768, 32, 16):
         args.traffic = 33.58e6 + 1.0e3     # dram__bytes_read.sum + dram__bytes_write.sum, one launch
     if args.impl == "reference":

@@ -480,6 +480,25 @@ def test_fused_decode_step(dtype, L, ps, budget, H):
     assert _lib.device_error(clear=False) == 0
 
 
+@pytest.mark.parametrize("ps", [1, 16])
+def test_decode_step_dense_when_context_fits_budget(ps):
+    """decode_step with a budget that covers the whole context (the reference's first two layers):
+    append, then attention over every page."""
+    _, K, U = _mods()
+    L, H = 200, 32
+    st = State(L - 1, H, ps, seed=12, budget_pages=1 << 20, fused=True, max_seq_len=L + ps)
+    c = st.c
+    c.end_forward()
+    q, k_new, v_new = _randn((1, H, 128), 1), _randn((1, H, 128), 2), _randn((1, H, 128), 3)
+    c.prepare_hadamard(1)
+    c.begin_forward(1)
+    assert not c.need_estimate()
+    o = U.decode_step(q.to(DEV), k_new.to(DEV), v_new.to(DEV), c, 0)
+    k_all, v_all = torch.cat([st.k, k_new], 0), torch.cat([st.v, v_new], 0)
+    want = ref.sparse_attention(q[0], k_all, v_all, np.tile(np.arange(L), (H, 1)))
+    _assert_attn_close(o[0], want)
+
+
 def test_dense_layer_page_size_16():
     _, K, U = _mods()
     st = State(1000, 32, 16, seed=9, budget_pages=1 << 20)
