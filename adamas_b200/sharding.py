@@ -93,9 +93,16 @@ def sequence_sharded_step(ops, q: torch.Tensor, budget: int, group=None):
     cand = ops.local_candidates(k)
     h = cand.values.size(0)
 
-    gathered = [torch.empty_like(cand.values) for _ in range(world)]
-    dist.all_gather(gathered, cand.values.contiguous(), group=group)
+    # 16-bit integers travel as fp16 bit patterns (all-gather only copies; NCCL has no int16 type)
+    wire = cand.values.contiguous()
+    as_int = wire.dtype in (torch.int16, torch.uint16)
+    if as_int:
+        wire = wire.view(torch.float16)
+    gathered = [torch.empty_like(wire) for _ in range(world)]
+    dist.all_gather(gathered, wire, group=group)
     table = torch.stack(gathered, dim=1).reshape(h, world * k)        # rank-major candidate table
+    if as_int:
+        table = table.view(cand.values.dtype)
     sel = ops.select(table, k).to(torch.int64)                        # [H, k] positions in the table
 
     slots = winners_of_rank(sel, cand.slots, rank)

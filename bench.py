@@ -186,7 +186,7 @@ class Workload:
         self.args = args
         self.dev = dev
         L, H, ps, B, layers = args.ctx, args.heads, args.page_size, args.budget, args.layers
-        dtype = torch.float16
+        dtype = torch.bfloat16 if getattr(args, "dtype", "f16") == "bf16" else torch.float16
         self.c = c = U.InferenceController(layers, H, 128, ps, B // ps, L, dtype, dev)
         gen = torch.Generator(device=dev).manual_seed(1234 + int(os.environ.get("RANK", "0")))
         c.prepare_hadamard(L - 1)
@@ -400,7 +400,7 @@ def run_ours(args):
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None, "dtype": getattr(args, "dtype", "f16"), "data": "synthetic",
         "us_per_layer": ms_per_step * 1e3 / args.layers,
         "us_per_layer_e2e": ms_e2e / args.steps * 1e3 / args.layers,
         "us_per_layer_e2e_eager": ms_eager / max(1, min(args.steps, 20)) * 1e3 / args.layers,
@@ -470,6 +470,76 @@ def run_sweep(args):
             torch.cuda.empty_cache()
 
 
+def run_seqshard(args):
+    """Sequence-sharded decode of one long context over the ranks (million-token configuration):
+    rank g holds tokens [g*L/G, (g+1)*L/G) of every head and layer; per layer-step the ranks run the
+    local estimate and candidate selection, all-gather the candidate distances, pick the global
+    winners, attend over their own winners and merge the partial results (adamas_b200.sharding).
+    Eager launches (NCCL collectives between the kernels).  Prints one JSON line on rank 0."""
+    import torch.distributed as dist
+    from adamas_b200 import _kernels as K, sharding
+    import adamas_b200.utils as U
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float16
+    L, H, ps, B, layers = args.ctx, args.heads, args.page_size, args.budget, args.layers
+    t0, t1 = sharding.token_range(L, world, rank, ps)
+    n_local = t1 - t0
+    owns_tail = t1 == L
+    c = U.InferenceController(layers, H, 128, ps, 1 << 24, n_local + ps, dtype, dev)
+    gen = torch.Generator(device=dev).manual_seed(4321 + rank)
+    n_pre = n_local - 1 if owns_tail else n_local
+    c.prepare_hadamard(n_pre)
+    c.begin_forward(n_pre)
+    chunk = 1 << 15
+    for layer in range(layers):
+        k = torch.randn(n_pre, H, 128, device=dev, dtype=dtype, generator=gen)
+        v = torch.randn(n_pre, H, 128, device=dev, dtype=dtype, generator=gen)
+        U.append_kvh(k, v, None, c, layer)
+        del k, v
+    c.end_forward()
+    if owns_tail:
+        c.prepare_hadamard(1)
+        c.begin_forward(1)
+    hg = torch.Generator().manual_seed(77)          # the same new token on every rank
+    qkv = torch.randn(3, layers, 1, H, 128, generator=hg).to(dtype).to(dev)
+    out = torch.zeros(layers, H, 128, dtype=dtype, device=dev)
+    q_code = torch.empty(1, H, 16, dtype=dtype, device=dev)
+
+    def step():
+        for layer in range(layers):
+            q, k, v = qkv[0, layer], qkv[1, layer], qkv[2, layer]
+            if owns_tail:
+                U.append_qkv_fused(q, k, v, c, layer, out=q_code)
+            else:
+                K.bucketize_pack(K.hadamard_transform(q), q_code)
+            ops = sharding.CudaOps(c, layer, q_code, owns_tail)
+            o, _ = sharding.sequence_sharded_step(ops, q, B)
+            out[layer].copy_(o)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    ms = timed(step, args.steps, True, dev)
+    if rank == 0:
+        per_layer_us = ms * 1e3 / args.steps / layers
+        by = stage_bytes(L, H, B)
+        print(json.dumps({
+            "mode": "sequence-sharded", "metric": METRIC, "value": by["total"] / (per_layer_us * 1e-6) / 1e9,
+            "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": ms / args.steps, "us_per_layer": per_layer_us, "higher_is_better": True,
+            "scaling": "strong", "dtype": args.dtype, "data": "synthetic",
+            "config": {"workload": f"one sequence of {L} tokens split over {world} GPUs, {layers} layers x {H} heads x 128, "
+                                   f"budget {B}, page size {ps}; eager launches, 3 NCCL all-gathers per layer",
+                       "tokens_per_gpu": n_local}}), flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -491,7 +561,13 @@ def main():
     ap.add_argument("--sweep", action="store_true", help="per-operator sweep over context x budget (one GPU)")
     ap.add_argument("--sweep-ctx", dest="sweep_ctx", type=int, nargs="+", default=[8192, 32768, 131072])
     ap.add_argument("--sweep-budget", dest="sweep_budget", type=int, nargs="+", default=[64, 128, 512, 2048])
+    ap.add_argument("--seq-sharded", dest="seq_sharded", action="store_true",
+                    help="one long sequence split over the ranks (torchrun); see run_seqshard")
+    ap.add_argument("--dtype", default="f16", choices=["f16", "bf16"])
     args = ap.parse_args()
+    if args.seq_sharded:
+        run_seqshard(args)
+        return
     if args.sweep:
         run_sweep(args)
         return
