@@ -420,7 +420,7 @@ def run_ours(args):
         "stage_gbs_alone": {k: by[k] / (stage_us[k] * 1e-6) / 1e9 for k in ("estimate", "topk", "attention") if k in stage_us},
     }
     if not args.no_cpu and world >= 1:
-        sec, n = time_cpu_reference(L, H, B, steps=20, warmup=1, budget_s=20.0)
+        sec, n = time_cpu_reference(L, H, B, steps=60, warmup=2, budget_s=15.0)
         line["cpu_baseline"] = {
             "value": by["total"] / sec / 1e9, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
             "sample": (f"{n} timed runs of one layer-step (1 of {args.layers} layers) of the reference PyTorch "
