@@ -9,6 +9,7 @@
 #include <cstdlib>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <new>
 
 #include "common.cuh"
@@ -78,11 +79,14 @@ struct DeviceInfo {
   int topk_dyn_smem = 0;
 };
 
+std::mutex g_init_mutex;   // first-use set-up may be reached from several host threads at once
+
 int get_device_info(const DeviceInfo** out) {
   static DeviceInfo infos[64];
   int dev = 0;
   ADAMAS_CUDA(cudaGetDevice(&dev));
   ADAMAS_REQUIRE(dev >= 0 && dev < 64, "device ordinal out of range");
+  std::lock_guard<std::mutex> lock(g_init_mutex);
   DeviceInfo& d = infos[dev];
   if (!d.ready) {
     ADAMAS_CUDA(cudaDeviceGetAttribute(&d.num_sms, cudaDevAttrMultiProcessorCount, dev));
@@ -823,12 +827,14 @@ int adamas_decode_forward_static(const void* q, void* o, float* lse, const void*
   ADAMAS_REQUIRE(dev >= 0 && dev < 64, "device ordinal out of range");
   const DeviceInfo* di = nullptr;
   if (int rc = get_device_info(&di)) return rc;
+  std::unique_lock<std::mutex> init_lock(g_init_mutex);
   if (scratch_ptr[dev] == nullptr) {
     void* ptr = nullptr;
     ADAMAS_CUDA(cudaGetSymbolAddress(&ptr, g_static_decode_scratch));
     ADAMAS_REQUIRE(ptr != nullptr, "cudaGetSymbolAddress returned a null address");
     scratch_ptr[dev] = ptr;
   }
+  init_lock.unlock();
 
   const SplitPlan p = plan_splits(n_tokens, num_heads, di->num_sms);
   ADAMAS_REQUIRE(num_heads <= kStaticMaxHeads,
@@ -901,10 +907,13 @@ int launch_select_attend(const SelectAttendParams& prm, int items, int cl, int n
     static bool configured[64] = {};                                                                \
     int dev = 0;                                                                                    \
     ADAMAS_CUDA(cudaGetDevice(&dev));                                                               \
-    if (!configured[dev & 63]) {                                                                    \
-      ADAMAS_CUDA(cudaFuncSetAttribute(select_attend_kernel<T, I>,                                  \
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));   \
-      configured[dev & 63] = true;                                                                  \
+    {                                                                                               \
+      std::lock_guard<std::mutex> lock(g_init_mutex);                                               \
+      if (!configured[dev & 63]) {                                                                  \
+        ADAMAS_CUDA(cudaFuncSetAttribute(select_attend_kernel<T, I>,                                \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024)); \
+        configured[dev & 63] = true;                                                                \
+      }                                                                                             \
     }                                                                                               \
     ADAMAS_LAUNCH("select_attend_kernel", select_attend_kernel<T, I>, grid, dim3(kSaThreads), smem, st, \
                   cl, prm);                                                                         \

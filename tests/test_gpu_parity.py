@@ -299,7 +299,7 @@ def test_topk_reference_shapes(kv_len, k_budget):
 
 
 @pytest.mark.parametrize("n,k", [(1, 1), (7, 7), (8, 1), (4095, 255), (4096, 4095), (32767, 1023), (32767, 63),
-                                 (131071, 2047), (250000, 4095)])
+                                 (131071, 2047), (250000, 4095), (300001, 1000)])
 @pytest.mark.parametrize("fmt", ["dist_f16", "dist_u16"])
 def test_topk_distances_with_ties(n, k, fmt):
     """Binomial-like integer distances (the real input of this stage): massive ties at the cut."""
@@ -449,7 +449,7 @@ def test_full_step_token_granular(dtype, L, ps, budget):
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("L,ps,budget,H", [
-    (70, 16, 8, 32), (300, 16, 64, 32), (2049, 16, 33, 8), (4096, 16, 256, 32), (5000, 1, 1024, 32),
+    (70, 16, 8, 32), (300, 16, 64, 32), (700, 16, 128, 16), (700, 1, 128, 64), (2049, 16, 33, 8), (4096, 16, 256, 32), (5000, 1, 1024, 32),
     (9001, 32, 4096, 4), (32768, 16, 1024, 32), (70000, 16, 2048, 2), (131072, 16, 2048, 4),
 ])
 def test_fused_decode_step(dtype, L, ps, budget, H):
