@@ -415,9 +415,10 @@ def select_attend(dist: torch.Tensor, k: int, q: torch.Tensor, o: torch.Tensor, 
 def decode_step(q, k, v, o, q_code, kv_data, kv_indices, kv_last_page_len, kv_last_page_idx, hadamard_data,
                 hadamard_indices, hadamard_last_page_len, budget: int, dist_scratch: torch.Tensor,
                 indices_out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
-                scale: Optional[float] = None, thresholds=None) -> None:
+                scale: Optional[float] = None, thresholds=None, rope=None) -> None:
     """One layer's decode step in one call: fused append, estimate, select + attend (three launches
-    for what adamas/models/Adamas.py:145-200 does with seven).  Needs context > budget."""
+    for what adamas/models/Adamas.py:145-200 does with seven).  Needs context > budget.  With
+    rope=(rope_scale, rope_theta) q and k arrive un-rotated and are rotated in place first."""
     num_heads, head_dim, page_size = _check_append(k, v, kv_data, kv_indices, hadamard_data, hadamard_indices, NHD)
     _check_input(q, "q", 3)
     _check_input(o, "o", 3)
@@ -439,7 +440,8 @@ def decode_step(q, k, v, o, q_code, kv_data, kv_indices, kv_last_page_len, kv_la
         _ptr(hadamard_data), _ptr(hadamard_indices), hadamard_indices.numel(), int(hadamard_last_page_len),
         num_heads, head_dim, page_size, _dtype_code(k.dtype, "decode_step"), int(budget),
         _ptr(dist_scratch), dist_scratch.stride(0), _ptr(indices_out), out_stride, s,
-        _lib.thresholds_arg(thresholds), 1.0 / math.sqrt(head_dim), _stream()), "decode_step")
+        _lib.thresholds_arg(thresholds), float(rope[0]) if rope is not None else 0.0,
+        float(rope[1]) if rope is not None else 0.0, 1.0 / math.sqrt(head_dim), _stream()), "decode_step")
 
 
 def merge_states(o_parts: torch.Tensor, lse_parts: torch.Tensor, o: torch.Tensor,

@@ -49,7 +49,7 @@ SIGNATURES = {
     "adamas_decode_forward_static": [_P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P],
     "adamas_select_attend": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _L, _F, _P],
     "adamas_decode_step": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I,
-                           _P, _L, _P, _L, _F, _FP, _F, _P],
+                           _P, _L, _P, _L, _F, _FP, _F, _F, _F, _P],
     "adamas_merge_states": [_P, _P, _I, _I, _I, _P, _P, _I, _P],
     "adamas_device_error": [POINTER(ctypes.c_uint), _I],
     "adamas_set_pdl": [_I],
@@ -68,7 +68,7 @@ lib.adamas_abi_version.restype = c_int
 lib.adamas_last_error.argtypes = []
 lib.adamas_last_error.restype = c_char_p
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 if lib.adamas_abi_version() != ABI_VERSION:
     raise ImportError(f"{LIB_PATH} has ABI version {lib.adamas_abi_version()}, expected {ABI_VERSION}; rebuild it")
 

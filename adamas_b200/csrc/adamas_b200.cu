@@ -990,14 +990,14 @@ int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, co
   return launch_select_attend<__nv_bfloat16>(prm, items, cl, num_heads, smem, to_stream(stream));
 }
 
-int adamas_decode_step(const void* q, const void* k, const void* v, void* o, float* lse, void* q_code,
+int adamas_decode_step(void* q, void* k, const void* v, void* o, float* lse, void* q_code,
                        void* kv_data, const int32_t* kv_page_table, int kv_num_pages,
                        int kv_last_page_len, int kv_last_page_idx, void* code_data,
                        const int32_t* code_page_table, int code_num_pages, int code_last_page_len,
                        int num_heads, int head_dim, int page_size, int dtype, int budget,
                        void* dist_scratch, int64_t dist_stride, int32_t* out_idx, int64_t out_stride,
-                       float hadamard_scale, const float* thresholds3_host, float sm_scale,
-                       adamas_stream_t stream) {
+                       float hadamard_scale, const float* thresholds3_host, float rope_scale,
+                       float rope_theta, float sm_scale, adamas_stream_t stream) {
   ADAMAS_REQUIRE(kv_num_pages >= 1 && kv_page_table, "page table missing");
   ADAMAS_REQUIRE(page_size >= 1, "page_size must be >= 1");
   const int64_t seq_len = static_cast<int64_t>(kv_num_pages - 1) * page_size + kv_last_page_len;
@@ -1007,10 +1007,16 @@ int adamas_decode_step(const void* q, const void* k, const void* v, void* o, flo
                  static_cast<long long>(seq_len), budget);
   ADAMAS_REQUIRE(seq_len - 1 < (int64_t(1) << 31), "sequence too long");
   ADAMAS_REQUIRE(dist_scratch && q_code, "null pointer");
-  if (int rc = adamas_append_decode_fused(q, k, v, q_code, kv_data, kv_page_table, kv_num_pages,
-                                          kv_last_page_len, code_data, code_page_table, code_num_pages,
-                                          code_last_page_len, num_heads, head_dim, page_size,
-                                          hadamard_scale, thresholds3_host, dtype, stream))
+  if (int rc = rope_scale > 0.f
+                   ? adamas_append_decode_rope_fused(q, k, v, q_code, kv_data, kv_page_table, kv_num_pages,
+                                                     kv_last_page_len, code_data, code_page_table,
+                                                     code_num_pages, code_last_page_len, num_heads, head_dim,
+                                                     page_size, hadamard_scale, thresholds3_host, rope_scale,
+                                                     rope_theta, dtype, stream)
+                   : adamas_append_decode_fused(q, k, v, q_code, kv_data, kv_page_table, kv_num_pages,
+                                                kv_last_page_len, code_data, code_page_table, code_num_pages,
+                                                code_last_page_len, num_heads, head_dim, page_size,
+                                                hadamard_scale, thresholds3_host, dtype, stream))
     return rc;
   if (int rc = adamas_estimate(q_code, code_data, code_page_table, code_num_pages, code_last_page_len,
                                page_size, num_heads, head_dim, dist_scratch, dist_stride, ADAMAS_VAL_U16,

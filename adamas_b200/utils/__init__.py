@@ -115,18 +115,19 @@ def decode_sparse_attn(q: torch.Tensor, iController: InferenceController, layer_
 
 def decode_step(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, iController: InferenceController,
                 layer_idx: int, out: Optional[torch.Tensor] = None, record_indices: bool = True,
-                scale: Optional[float] = None) -> torch.Tensor:
+                scale: Optional[float] = None, rope=None) -> torch.Tensor:
     """The whole decode branch of the attention module (adamas/models/Adamas.py:145-200: cat,
     Hadamard, append, estimate, top-k, sparse attention) in one call and three launches.
 
-    q, k, v [1,H,D] after RoPE.  Returns o [1,H,D].  When the context still fits in the budget
+    q, k, v [1,H,D] after RoPE, or before it with rope=(rope_scale, rope_theta): q and k are then
+    rotated in place by the append launch (apply_rope_in_place, Adamas.py:113).  Returns o [1,H,D].  When the context still fits in the budget
     (iController.need_estimate() is False, e.g. the dense first layers) it appends and attends to
     every page instead.  With record_indices the selected token slots are also written to
     iController.topk_dindices_buffer, as decode_topk would."""
     c = iController
     o = out if out is not None else torch.empty_like(q)
     if not c.need_estimate():
-        append_qkv_fused(q, k, v, c, layer_idx, scale=scale)
+        append_qkv_fused(q, k, v, c, layer_idx, scale=scale, rope=rope)
         return decode_sparse_attn(q, c, layer_idx, c.kv_indices_without_last, out=o)
     q_code = torch.empty(1, k.size(1), k.size(2) // 8, dtype=k.dtype, device=k.device)
     n = c.hadamard_cache.seqlen - 1
@@ -134,5 +135,5 @@ def decode_step(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, iController: 
         q, k, v, o, q_code, c.kv_cache.buf_layer(layer_idx), c.kv_indices_with_last, c.kv_cache.last_page_len,
         c.kv_last_page_idx, c.hadamard_cache.buf_layer(layer_idx), c.hadamard_indices,
         c.hadamard_cache.last_page_len, c.inference_token_budget, c.distance_scratch(n),
-        indices_out=c.topk_dindices_buffer if record_indices else None, scale=scale)
+        indices_out=c.topk_dindices_buffer if record_indices else None, scale=scale, rope=rope)
     return o

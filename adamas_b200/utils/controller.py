@@ -120,7 +120,9 @@ class InferenceController:
 
         # top-k outputs: values and indices share one row stride; reused across steps
         if self._topk_store is None or self._topk_store[0].size(1) < k or self._topk_store[0].size(0) != self.num_heads:
-            cap = max(k, 1)
+            # grows geometrically: in the dense first layers k is the whole context, one more each step
+            cap = max(k, 1) if self._topk_store is None else max(k, 2 * self._topk_store[0].size(1))
+            cap = max(min(cap, self.kv_cache.pool.capacity * self.page_size), k, 1)
             vals = torch.zeros((self.num_heads, cap), dtype=torch.int16, device=self.device)
             idx = torch.zeros((self.num_heads, cap), dtype=torch.int32, device=self.device)
             self._topk_store = (vals, idx)

@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define ADAMAS_ABI_VERSION 1
+#define ADAMAS_ABI_VERSION 2
 
 /* status codes */
 #define ADAMAS_OK 0
@@ -247,14 +247,17 @@ int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, co
  * what adamas/models/Adamas.py:145-200 does with seven launches.  q, k, v, o [1,H,D]; q_code
  * [1,H,D/8] scratch/output; dist_scratch [H, dist_stride] 16-bit, rows on 16-byte boundaries,
  * dist_stride >= context - 1.  Requires context > budget (otherwise every page is attended: use
- * adamas_decode_forward).  kv_last_page_idx is the physical number of the last KV page. */
-int adamas_decode_step(const void* q, const void* k, const void* v, void* o, float* lse, void* q_code,
+ * adamas_decode_forward).  kv_last_page_idx is the physical number of the last KV page.  With
+ * rope_scale > 0, q and k arrive un-rotated and the append launch rotates them in place first
+ * (apply_rope_in_place, adamas/models/Adamas.py:113); rope_scale <= 0: q and k are already rotated. */
+int adamas_decode_step(void* q, void* k, const void* v, void* o, float* lse, void* q_code,
                        void* kv_data, const int32_t* kv_page_table, int kv_num_pages,
                        int kv_last_page_len, int kv_last_page_idx, void* code_data,
                        const int32_t* code_page_table, int code_num_pages, int code_last_page_len,
                        int num_heads, int head_dim, int page_size, int dtype, int budget,
                        void* dist_scratch, int64_t dist_stride, int32_t* out_idx, int64_t out_stride,
-                       float hadamard_scale, const float* thresholds3_host, float sm_scale,
+                       float hadamard_scale, const float* thresholds3_host, float rope_scale,
+                       float rope_theta, float sm_scale,
                        adamas_stream_t stream);
 
 /* Merge P partial results over disjoint token sets: o_parts [P, H, D] fp32 (each already
