@@ -377,6 +377,13 @@ class BatchDecodeWithPagedKVCachePyTorchWrapper:
             1.0 / math.sqrt(head_dim), _stream()), "BatchDecodeWithPagedKVCache")
 
 
+def set_max_cluster(blocks: int) -> None:
+    """Upper bound (1, 2, 4, 8) on the thread blocks that share one head in select_attend /
+    decode_step: 8 is fastest for a single sequence, smaller values let calls of several sequences
+    on different streams overlap."""
+    _lib.check(lib.adamas_set_max_cluster(int(blocks)), "set_max_cluster")
+
+
 def select_attend(dist: torch.Tensor, k: int, q: torch.Tensor, o: torch.Tensor, kv_data: torch.Tensor,
                   kv_indices: torch.Tensor, last_page_len: int, last_page_idx: int,
                   indices_out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None) -> None:

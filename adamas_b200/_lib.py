@@ -53,6 +53,7 @@ SIGNATURES = {
     "adamas_merge_states": [_P, _P, _I, _I, _I, _P, _P, _I, _P],
     "adamas_device_error": [POINTER(ctypes.c_uint), _I],
     "adamas_set_pdl": [_I],
+    "adamas_set_max_cluster": [_I],
 }
 
 for _name, _args in SIGNATURES.items():

@@ -162,6 +162,17 @@ bool pdl_enabled() {
   return g_pdl != 0;
 }
 
+// Upper bound on the cluster size of select_attend (adamas_set_max_cluster / ADAMAS_MAX_CLUSTER).
+int g_max_cluster = -1;
+int max_cluster() {
+  if (g_max_cluster < 0) {
+    const char* e = std::getenv("ADAMAS_MAX_CLUSTER");
+    const int v = e ? std::atoi(e) : kSaMaxCluster;
+    g_max_cluster = (v >= 1 && v <= kSaMaxCluster) ? v : kSaMaxCluster;
+  }
+  return g_max_cluster;
+}
+
 template <typename... KArgs, typename... Args>
 cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
                           int cluster, Args... args) {
@@ -206,6 +217,13 @@ int adamas_abi_version(void) { return ADAMAS_ABI_VERSION; }
 
 int adamas_set_pdl(int enable) {
   g_pdl = enable ? 1 : 0;
+  return ADAMAS_OK;
+}
+
+int adamas_set_max_cluster(int blocks) {
+  ADAMAS_REQUIRE(blocks >= 1 && blocks <= kSaMaxCluster && (blocks & (blocks - 1)) == 0,
+                 "cluster size must be a power of two between 1 and %d (got %d)", kSaMaxCluster, blocks);
+  g_max_cluster = blocks;
   return ADAMAS_OK;
 }
 
@@ -952,8 +970,9 @@ int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, co
   ADAMAS_REQUIRE(tail < (int64_t(1) << 31), "token slots must be below 2^31");
   const int g_total = (n + 7) / 8;
   int cl = 0, items = 0;
+  const int cl_limit = max_cluster();
   for (int it = 1; it <= 8 && cl == 0; it *= 2) {
-    for (int c = 1; c <= kSaMaxCluster; c *= 2) {
+    for (int c = 1; c <= cl_limit; c *= 2) {
       if (static_cast<int64_t>(c) * it * kSaThreads >= g_total) {
         cl = c;
         items = it;
@@ -961,8 +980,17 @@ int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, co
       }
     }
   }
-  ADAMAS_REQUIRE(cl > 0, "select_attend supports at most %d distances per head (got %d)",
-                 kSaMaxCluster * 8 * kSaThreads * 8, n);
+  ADAMAS_REQUIRE(cl > 0, "select_attend supports at most %d distances per head at cluster size %d (got %d)",
+                 cl_limit * 8 * kSaThreads * 8, cl_limit, n);
+  {
+    // a large budget on a short row: more blocks per head than the scan needs, so that each block
+    // attends to about one tile of winners, as long as all blocks stay resident at once
+    const DeviceInfo* di = nullptr;
+    if (int rc = get_device_info(&di)) return rc;
+    while (cl < cl_limit && k > cl * kSaTile && 2 * cl * num_heads <= 2 * di->num_sms &&
+           (g_total + 2 * cl - 1) / (2 * cl) >= 1)
+      cl *= 2;
+  }
   SelectAttendParams prm;
   prm.dist = static_cast<const uint16_t*>(dist);
   prm.dist_stride = dist_stride;

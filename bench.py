@@ -180,7 +180,7 @@ def workload_config(args, extra=None):
 # GPU arm
 # --------------------------------------------------------------------------------------------
 class Workload:
-    def __init__(self, args, dev):
+    def __init__(self, args, dev, seed_offset=0):
         import adamas_b200.utils as U
         self.U = U
         self.args = args
@@ -188,7 +188,7 @@ class Workload:
         L, H, ps, B, layers = args.ctx, args.heads, args.page_size, args.budget, args.layers
         dtype = torch.bfloat16 if getattr(args, "dtype", "f16") == "bf16" else torch.float16
         self.c = c = U.InferenceController(layers, H, 128, ps, B // ps, L, dtype, dev)
-        gen = torch.Generator(device=dev).manual_seed(1234 + int(os.environ.get("RANK", "0")))
+        gen = torch.Generator(device=dev).manual_seed(1234 + int(os.environ.get("RANK", "0")) + 1000 * seed_offset)
         c.prepare_hadamard(L - 1)
         c.begin_forward(L - 1)
         for layer in range(layers):
@@ -201,7 +201,7 @@ class Workload:
         c.begin_forward(1)
         assert c.need_estimate()
         # this step's projections: pinned host copies (end-to-end path) and device copies
-        hg = torch.Generator().manual_seed(99)
+        hg = torch.Generator().manual_seed(99 + seed_offset)
         self.h_qkv = torch.randn(3, layers, 1, H, 128, generator=hg).to(dtype).pin_memory()
         self.d_qkv = self.h_qkv.to(dev)
         self.d_out = torch.zeros(layers, 1, H, 128, dtype=dtype, device=dev)
@@ -249,43 +249,72 @@ class Workload:
         self.step()
         self.h_out.copy_(self.d_out, non_blocking=True)
 
-    # one kernel class alone (a graph with one launch per layer, so the data comes from HBM)
-    def capture_stage_only(self, stage):
+    def stage_op(self, stage, layer):
+        """One kernel class of one layer ("step": the whole layer step)."""
         U, c = self.U, self.c
         from adamas_b200 import _kernels as K
+        q, k, v = self.d_qkv[0, layer], self.d_qkv[1, layer], self.d_qkv[2, layer]
+        if stage == "step":
+            self.layer_step(layer)
+        elif stage == "append":
+            U.append_qkv_fused(q, k, v, c, layer, out=self.q_code[layer])
+        elif stage == "estimate" and self.args.unfused:
+            U.decode_estimate(self.q_code[layer], c, layer)
+        elif stage == "estimate":      # fused step: integer distances, as decode_step asks for
+            n = c.hadamard_cache.seqlen - 1
+            K.estimate_attn_score(self.q_code[layer], c.distance_scratch(n), c.hadamard_cache.buf_layer(layer),
+                                  c.hadamard_indices, None, c.hadamard_cache.last_page_len,
+                                  c.hadamard_last_page_idx, c.layout)
+        elif stage == "topk":
+            U.decode_topk(c.estimate_buffer(c.hadamard_cache.seqlen - 1), c)
+        elif stage == "attention":
+            U.decode_sparse_attn(q, c, layer, c.topk_dindices_buffer, out=self.d_out[layer])
+        elif stage == "select_attend":
+            n = c.hadamard_cache.seqlen - 1
+            K.select_attend(c.distance_scratch(n), c.inference_token_budget - 1, q, self.d_out[layer],
+                            c.kv_cache.buf_layer(layer), c.kv_indices_with_last, c.kv_cache.last_page_len,
+                            c.kv_last_page_idx)
+        else:
+            raise ValueError(stage)
 
-        def body():
-            for layer in range(self.args.layers):
-                q, k, v = self.d_qkv[0, layer], self.d_qkv[1, layer], self.d_qkv[2, layer]
-                if stage == "append":
-                    U.append_qkv_fused(q, k, v, c, layer, out=self.q_code[layer])
-                elif stage == "estimate" and self.args.unfused:
-                    U.decode_estimate(self.q_code[layer], c, layer)
-                elif stage == "estimate":      # fused step: integer distances, as decode_step asks for
-                    n = c.hadamard_cache.seqlen - 1
-                    K.estimate_attn_score(self.q_code[layer], c.distance_scratch(n), c.hadamard_cache.buf_layer(layer),
-                                          c.hadamard_indices, None, c.hadamard_cache.last_page_len,
-                                          c.hadamard_last_page_idx, c.layout)
-                elif stage == "topk":
-                    U.decode_topk(c.estimate_buffer(c.hadamard_cache.seqlen - 1), c)
-                elif stage == "attention":
-                    U.decode_sparse_attn(q, c, layer, c.topk_dindices_buffer, out=self.d_out[layer])
-                elif stage == "select_attend":
-                    n = c.hadamard_cache.seqlen - 1
-                    K.select_attend(c.distance_scratch(n), c.inference_token_budget - 1, q, self.d_out[layer],
-                                    c.kv_cache.buf_layer(layer), c.kv_indices_with_last, c.kv_cache.last_page_len,
-                                    c.kv_last_page_idx)
+    # one kernel class alone (a graph with one launch per layer, so the data comes from HBM)
+    def capture_stage_only(self, stage):
+        return capture_batch([self], stage)
 
-        g = torch.cuda.CUDAGraph()
-        s = torch.cuda.Stream()
-        s.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(s):
-            body()
-        torch.cuda.current_stream().wait_stream(s)
-        torch.cuda.synchronize()
-        with torch.cuda.graph(g):
-            body()
-        return g
+
+def capture_batch(wls, stage):
+    """CUDA graph of `stage` for every layer of every sequence in `wls`.  The sequences are
+    independent (each has its own controller, page tables and caches); within a layer they run on
+    one stream each, forked from and joined to the capturing stream, the way a batched model step
+    proceeds layer by layer."""
+    layers = wls[0].args.layers
+
+    def body(main, streams):
+        for layer in range(layers):
+            if len(wls) == 1:
+                wls[0].stage_op(stage, layer)
+                continue
+            fork = torch.cuda.Event()
+            fork.record(main)
+            for wl, st in zip(wls, streams):
+                st.wait_event(fork)
+                with torch.cuda.stream(st):
+                    wl.stage_op(stage, layer)
+                join = torch.cuda.Event()
+                join.record(st)
+                main.wait_event(join)
+
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    streams = [torch.cuda.Stream() for _ in wls] if len(wls) > 1 else []
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        body(s, streams)
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    with torch.cuda.graph(g, stream=s):
+        body(s, streams)
+    return g
 
 
 def timed(fn, steps, dist_on, dev):
@@ -434,40 +463,54 @@ def run_ours(args):
 def run_sweep(args):
     """Per-operator sweep (one GPU): context x budget, each stage timed alone in a CUDA graph with
     one launch per layer (distinct caches, so data comes from HBM).  Prints one JSON line per point.
-    Batch > 1 in the reference's terms is b independent sequences, each with its own page table and
-    caches, i.e. b times these launches."""
+    Batch > 1 (--sweep-batch) is b independent sequences, each with its own controller, page table
+    and caches (the reference is batch-1 only): their launches run on one stream per sequence inside
+    the graph, joined after every layer; GB/s figures are aggregates over the b sequences."""
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
     for ctx in args.sweep_ctx:
-        layers = max(4, min(32, int(6e9 // (ctx * args.heads * 544))))   # keep the caches under ~6 GB
-        for budget in args.sweep_budget:
-            if budget >= ctx:
-                continue
-            a = argparse.Namespace(**vars(args))
-            a.ctx, a.budget, a.layers, a.unfused = ctx, budget, layers, True
-            wl = Workload(a, dev)
-            wl.step_eager()
-            torch.cuda.synchronize()
-            by = stage_bytes(ctx, args.heads, budget)
-            out = {"sweep": True, "ctx": ctx, "budget": budget, "heads": args.heads, "page_size": args.page_size,
-                   "layers_rotated": layers}
-            for stage in ("estimate", "topk", "attention", "select_attend", "append"):
-                if stage == "select_attend":
-                    a.unfused = False
-                    wl.U.decode_step(wl.d_qkv[0, 0], wl.d_qkv[1, 0], wl.d_qkv[2, 0], wl.c, 0, out=wl.d_out[0])
-                g = wl.capture_stage_only(stage)
-                for _ in range(3):
-                    g.replay()
-                us = timed(g.replay, args.steps, False, dev) * 1e3 / args.steps / layers
-                a.unfused = True
-                out[stage + "_us"] = round(us, 2)
-                if stage in by:
-                    out[stage + "_GBps"] = round(by[stage] / (us * 1e-6) / 1e9, 1)
-                del g
-            out["select_attend_GBps"] = round((by["topk"] + by["attention"]) / (out["select_attend_us"] * 1e-6) / 1e9, 1)
-            print(json.dumps(out), flush=True)
-            del wl
-            torch.cuda.empty_cache()
+        for batch in args.sweep_batch:
+            # caches of all sequences and rotated layers stay under ~48 GB and well above L2
+            layers = max(1, min(32, int(48e9 // (batch * ctx * args.heads * 544))))
+            if batch == 1:
+                layers = max(4, min(layers, int(6e9 // (ctx * args.heads * 544))))
+            for budget in args.sweep_budget:
+                if budget >= ctx:
+                    continue
+                a = argparse.Namespace(**vars(args))
+                a.ctx, a.budget, a.layers, a.unfused = ctx, budget, layers, True
+                from adamas_b200 import _kernels as K
+                # several sequences in flight: fewer blocks per head so that their kernels overlap
+                cluster = 8 if batch == 1 else 4      # measured: 4 is best from two sequences up
+                if args.sweep_cluster:
+                    cluster = args.sweep_cluster
+                K.set_max_cluster(cluster)
+                wls = [Workload(a, dev, seed_offset=i) for i in range(batch)]
+                for wl in wls:
+                    wl.step_eager()
+                torch.cuda.synchronize()
+                by = stage_bytes(ctx, args.heads, budget, batch)
+                out = {"sweep": True, "batch": batch, "ctx": ctx, "budget": budget, "heads": args.heads,
+                       "page_size": args.page_size, "layers_rotated": layers, "max_cluster": cluster}
+                for stage in ("estimate", "topk", "attention", "select_attend", "append", "step"):
+                    if stage in ("select_attend", "step"):
+                        a.unfused = False      # the estimate must have left integer distances
+                        for wl in wls:
+                            wl.U.decode_step(wl.d_qkv[0, 0], wl.d_qkv[1, 0], wl.d_qkv[2, 0], wl.c, 0, out=wl.d_out[0])
+                    g = capture_batch(wls, stage)
+                    for _ in range(3):
+                        g.replay()
+                    us = timed(g.replay, args.steps, False, dev) * 1e3 / args.steps / layers
+                    a.unfused = True
+                    out[stage + "_us"] = round(us, 2)
+                    if stage in by:
+                        out[stage + "_GBps"] = round(by[stage] / (us * 1e-6) / 1e9, 1)
+                    del g
+                out["select_attend_GBps"] = round((by["topk"] + by["attention"]) / (out["select_attend_us"] * 1e-6) / 1e9, 1)
+                out["step_GBps"] = round(by["total"] / (out["step_us"] * 1e-6) / 1e9, 1)
+                print(json.dumps(out), flush=True)
+                del wls, wl
+                torch.cuda.empty_cache()
 
 
 def run_seqshard(args):
@@ -627,6 +670,10 @@ def main():
     ap.add_argument("--sweep", action="store_true", help="per-operator sweep over context x budget (one GPU)")
     ap.add_argument("--sweep-ctx", dest="sweep_ctx", type=int, nargs="+", default=[8192, 32768, 131072])
     ap.add_argument("--sweep-budget", dest="sweep_budget", type=int, nargs="+", default=[64, 128, 512, 2048])
+    ap.add_argument("--sweep-cluster", dest="sweep_cluster", type=int, default=0,
+                    help="force the select_attend cluster bound (default: 8 for one sequence, else 4)")
+    ap.add_argument("--sweep-batch", dest="sweep_batch", type=int, nargs="+", default=[1],
+                    help="independent sequences per step, one stream each inside the graph")
     ap.add_argument("--seq-sharded", dest="seq_sharded", action="store_true",
                     help="one long sequence split over the ranks (torchrun); see run_seqshard")
     ap.add_argument("--dtype", default="f16", choices=["f16", "bf16"])

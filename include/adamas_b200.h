@@ -64,6 +64,13 @@ int adamas_device_error(unsigned* flags, int clear);
  * reference launches everything on the legacy default stream (e.g. adamas/ops/csrc/page.cu:99). */
 int adamas_set_pdl(int enable);
 
+/* Upper bound (1, 2, 4 or 8; default 8, or ADAMAS_MAX_CLUSTER in the environment) on the number of
+ * thread blocks that share one head in adamas_select_attend / adamas_decode_step.  Eight blocks per
+ * head give the shortest single call; a smaller cluster takes longer per call but leaves room on the
+ * GPU for calls of other sequences running on other streams (a batch of independent sequences).  Rows
+ * longer than 32768 x the bound are rejected.  No counterpart in the reference (batch 1 only). */
+int adamas_set_max_cluster(int blocks);
+
 /* ---- stage 1: Hadamard transform, bucketize, pack, append -------------------------------- */
 
 /* y[r, :] = round_to_dtype(scale * WHT_D(x[r, :])) for r < rows; D = head_dim = 128; x == y allowed.

@@ -450,7 +450,7 @@ def test_full_step_token_granular(dtype, L, ps, budget):
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("L,ps,budget,H", [
     (70, 16, 8, 32), (300, 16, 64, 32), (700, 16, 128, 16), (700, 1, 128, 64), (2049, 16, 33, 8), (4096, 16, 256, 32), (5000, 1, 1024, 32),
-    (9001, 32, 4096, 4), (32768, 16, 1024, 32), (70000, 16, 2048, 2), (131072, 16, 2048, 4),
+    (9001, 32, 4096, 4), (8192, 16, 2048, 32), (32768, 16, 1024, 32), (70000, 16, 2048, 2), (131072, 16, 2048, 4),
 ])
 def test_fused_decode_step(dtype, L, ps, budget, H):
     """decode_step (append + estimate + select/attend in one call) against the oracle: codes and
@@ -478,6 +478,33 @@ def test_fused_decode_step(dtype, L, ps, budget, H):
     _assert_attn_close(o[0], r["out"])
     from adamas_b200 import _lib
     assert _lib.device_error(clear=False) == 0
+
+
+@pytest.mark.parametrize("blocks", [1, 2, 4])
+@pytest.mark.parametrize("L,budget,H", [(32768, 1024, 8), (6000, 640, 32)])
+def test_decode_step_with_smaller_clusters(blocks, L, budget, H):
+    """set_max_cluster only changes how a head's row is split over thread blocks: same winners, same
+    output (to tolerance) against the oracle for every bound."""
+    _, K, U = _mods()
+    ps = 16
+    st = State(L - 1, H, ps, seed=L + blocks, budget_pages=budget // ps, fused=True, max_seq_len=L + ps)
+    c = st.c
+    c.end_forward()
+    q, k_new, v_new = _randn((1, H, 128), 11 + L), _randn((1, H, 128), 12 + L), _randn((1, H, 128), 13 + L)
+    c.prepare_hadamard(1)
+    c.begin_forward(1)
+    K.set_max_cluster(blocks)
+    try:
+        o = U.decode_step(q.to(DEV), k_new.to(DEV), v_new.to(DEV), c, 0)
+        torch.cuda.synchronize()
+    finally:
+        K.set_max_cluster(8)
+    r = ref.decode_step(q[0], torch.cat([st.k, k_new], 0), torch.cat([st.v, v_new], 0), c.inference_token_budget)
+    table = np.asarray(c.kv_cache.indicies)
+    np.testing.assert_array_equal(c.topk_dindices_buffer.cpu().numpy(), table[r["sel"] // ps] * ps + r["sel"] % ps)
+    _assert_attn_close(o[0], r["out"])
+    with pytest.raises(RuntimeError):
+        K.set_max_cluster(3)
 
 
 @pytest.mark.parametrize("ps", [1, 16])

@@ -39,6 +39,9 @@ def test_argument_validation_without_gpu():
     assert lib.adamas_decode_handler_destroy(h) == 0
     with pytest.raises(RuntimeError):
         _lib.check(rc, "decode")
+    assert lib.adamas_set_max_cluster(3) == _lib.ERR_INVALID and "power of two" in _lib.last_error()
+    assert lib.adamas_set_max_cluster(16) == _lib.ERR_INVALID
+    assert lib.adamas_set_max_cluster(8) == 0
 
 
 def test_ops_reject_cpu_tensors():
