@@ -9,7 +9,8 @@ import os
 from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p, POINTER
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG_DIR, "libadamas_b200.so")
+# ADAMAS_B200_LIBRARY names a library built elsewhere (e.g. a build with extra compile flags)
+LIB_PATH = os.environ.get("ADAMAS_B200_LIBRARY") or os.path.join(_PKG_DIR, "libadamas_b200.so")
 
 OK, ERR_INVALID, ERR_CUDA, ERR_STATE = 0, 1, 2, 3
 F16, BF16 = 0, 1
@@ -50,10 +51,13 @@ SIGNATURES = {
     "adamas_select_attend": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _L, _F, _P],
     "adamas_decode_step": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I,
                            _P, _L, _P, _L, _F, _FP, _F, _F, _F, _P],
+    "adamas_append_estimate": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _L, _F, _FP,
+                               _F, _F, _P],
     "adamas_merge_states": [_P, _P, _I, _I, _I, _P, _P, _I, _P],
     "adamas_device_error": [POINTER(ctypes.c_uint), _I],
     "adamas_set_pdl": [_I],
     "adamas_set_max_cluster": [_I],
+    "adamas_set_fused_append": [_I],
 }
 
 for _name, _args in SIGNATURES.items():

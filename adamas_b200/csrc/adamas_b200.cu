@@ -109,6 +109,22 @@ int get_device_info(const DeviceInfo** out) {
     EST_ATTR_ALL(1, uint16_t);
 #undef EST_ATTR_ALL
 #undef EST_ATTR
+#define ESTA_ATTR(T, HPW, R)                                                                           \
+  ADAMAS_CUDA(cudaFuncSetAttribute(estimate_append_kernel<T, HPW, R>,                                  \
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, est_max));            \
+  ADAMAS_CUDA(cudaFuncSetAttribute(estimate_append_kernel<T, HPW, R>,                                  \
+                                   cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared))
+#define ESTA_ATTR_ALL(T) \
+  ESTA_ATTR(T, 1, false); \
+  ESTA_ATTR(T, 1, true);  \
+  ESTA_ATTR(T, 2, false); \
+  ESTA_ATTR(T, 2, true);  \
+  ESTA_ATTR(T, 4, false); \
+  ESTA_ATTR(T, 4, true)
+    ESTA_ATTR_ALL(__half);
+    ESTA_ATTR_ALL(__nv_bfloat16);
+#undef ESTA_ATTR_ALL
+#undef ESTA_ATTR
     ADAMAS_CUDA(cudaFuncSetAttribute(sparse_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kDecStageBytes));
     ADAMAS_CUDA(cudaFuncSetAttribute(sparse_decode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kDecStageBytes));
     // One shared-memory carve-out for every kernel of the decode step: a kernel that asks for a
@@ -162,6 +178,17 @@ bool pdl_enabled() {
   return g_pdl != 0;
 }
 
+// Whether adamas_decode_step folds the append into the estimate launch (off unless
+// ADAMAS_FUSED_APPEND=1 or adamas_set_fused_append(1)).
+int g_fused_append = -1;
+bool fused_append_enabled() {
+  if (g_fused_append < 0) {
+    const char* e = std::getenv("ADAMAS_FUSED_APPEND");
+    g_fused_append = (e && e[0] == '1') ? 1 : 0;
+  }
+  return g_fused_append != 0;
+}
+
 // Upper bound on the cluster size of select_attend (adamas_set_max_cluster / ADAMAS_MAX_CLUSTER).
 int g_max_cluster = -1;
 int max_cluster() {
@@ -181,8 +208,18 @@ cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[2];
+  cudaLaunchAttribute attr[3];
   unsigned n = 0;
+  if (cluster > 1) {
+    // By default the hardware spreads the blocks of a cluster over as many different SMs of a GPC.  With
+    // two resident blocks per SM and nearly as many clusters as fit, blocks placed while the preceding
+    // kernel drains then leave a GPC with enough free slots on too few SMs, and the last cluster
+    // waits for another to finish (measured: a third of the select_attend launches took 9 us
+    // longer).  Load balancing lets blocks of one cluster share an SM.
+    attr[n].id = cudaLaunchAttributeClusterSchedulingPolicyPreference;
+    attr[n].val.clusterSchedulingPolicyPreference = cudaClusterSchedulingPolicyLoadBalancing;
+    ++n;
+  }
   if (pdl_enabled()) {
     attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[n].val.programmaticStreamSerializationAllowed = 1;
@@ -220,6 +257,11 @@ int adamas_set_pdl(int enable) {
   return ADAMAS_OK;
 }
 
+int adamas_set_fused_append(int enable) {
+  g_fused_append = enable ? 1 : 0;
+  return ADAMAS_OK;
+}
+
 int adamas_set_max_cluster(int blocks) {
   ADAMAS_REQUIRE(blocks >= 1 && blocks <= kSaMaxCluster && (blocks & (blocks - 1)) == 0,
                  "cluster size must be a power of two between 1 and %d (got %d)", kSaMaxCluster, blocks);
@@ -237,6 +279,43 @@ int adamas_device_error(unsigned* flags, int clear) {
   return ADAMAS_OK;
 }
 const char* adamas_last_error(void) { return g_err; }
+
+#ifdef ADAMAS_PHASE_TIMING
+// Debug builds only: copies the phase-timing table ([2 kernels][512 blocks][16 slots] of nanosecond
+// stamps) to `out`.
+int adamas_debug_read_timing(unsigned long long* out) {
+  ADAMAS_REQUIRE(out, "null pointer");
+  ADAMAS_CUDA(cudaMemcpyFromSymbol(out, g_phase_timing, sizeof(unsigned long long) * 2 * kTimingBlocks * kTimingSlots));
+  return ADAMAS_OK;
+}
+int adamas_debug_read_chain(unsigned long long* out, unsigned* seq) {
+  ADAMAS_CUDA(cudaMemcpyFromSymbol(out, g_chain, sizeof(unsigned long long) * 3 * kChainDepth * 4));
+  ADAMAS_CUDA(cudaMemcpyFromSymbol(seq, g_chain_seq, sizeof(unsigned) * 3));
+  return ADAMAS_OK;
+}
+int adamas_debug_read_trace(unsigned long long* out) {
+  ADAMAS_CUDA(cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * 2 * 64 * 320 * 3));
+  return ADAMAS_OK;
+}
+// Debug builds only: how many clusters of `cluster` select_attend blocks with `smem` bytes of dynamic
+// shared memory can be resident at once.
+int adamas_debug_max_clusters(int cluster, int smem, int grid_blocks, int* out) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid_blocks);
+  cfg.blockDim = dim3(kSaThreads);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  ADAMAS_CUDA(cudaFuncSetAttribute(select_attend_kernel<__half, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+  ADAMAS_CUDA(cudaOccupancyMaxActiveClusters(out, select_attend_kernel<__half, 1>, &cfg));
+  return ADAMAS_OK;
+}
+#endif
 
 // ---------------------------------------------------------------------------------------------
 int adamas_hadamard_transform(const void* x, void* y, int64_t rows, int head_dim, float scale,
@@ -484,6 +563,13 @@ int adamas_estimate(const void* q_code, const void* code_data, const int32_t* co
     while ((1 << prm.ps_shift) < page_size) ++prm.ps_shift;
   }
   prm.num_tiles = num_tiles;
+  prm.trace_tag = 0;
+#ifdef ADAMAS_PHASE_TIMING
+  {
+    static int est_launches = 0;
+    prm.trace_tag = (est_launches++) & 63;
+  }
+#endif
   cudaStream_t st = to_stream(stream);
 #define LAUNCH_EST(M, OT)                                                                      \
   do {                                                                                         \
@@ -916,47 +1002,46 @@ int log2_exact(int v) {
   return s;
 }
 
+template <typename T, int I>
+int launch_select_attend_one(const SelectAttendParams& prm, int cl, int num_heads, size_t smem, cudaStream_t st) {
+  static bool configured[64] = {};
+  int dev = 0;
+  ADAMAS_CUDA(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lock(g_init_mutex);
+    if (!configured[dev & 63]) {
+      ADAMAS_CUDA(cudaFuncSetAttribute(select_attend_kernel<T, I>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       160 * 1024));
+      configured[dev & 63] = true;
+    }
+  }
+  const dim3 grid(static_cast<unsigned>(num_heads) * cl);
+  ADAMAS_LAUNCH("select_attend_kernel", (select_attend_kernel<T, I>), grid, dim3(kSaThreads), smem, st, cl, prm);
+  return check_launch("select_attend_kernel");
+}
+
 template <typename T>
 int launch_select_attend(const SelectAttendParams& prm, int items, int cl, int num_heads, size_t smem,
                          cudaStream_t st) {
-  const dim3 grid(static_cast<unsigned>(num_heads) * cl);
-#define SA_CASE(I)                                                                                  \
-  case I: {                                                                                         \
-    static bool configured[64] = {};                                                                \
-    int dev = 0;                                                                                    \
-    ADAMAS_CUDA(cudaGetDevice(&dev));                                                               \
-    {                                                                                               \
-      std::lock_guard<std::mutex> lock(g_init_mutex);                                               \
-      if (!configured[dev & 63]) {                                                                  \
-        ADAMAS_CUDA(cudaFuncSetAttribute(select_attend_kernel<T, I>,                                \
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024)); \
-        configured[dev & 63] = true;                                                                \
-      }                                                                                             \
-    }                                                                                               \
-    ADAMAS_LAUNCH("select_attend_kernel", select_attend_kernel<T, I>, grid, dim3(kSaThreads), smem, st, \
-                  cl, prm);                                                                         \
-    break;                                                                                          \
-  }
   switch (items) {
-    SA_CASE(1)
-    SA_CASE(2)
-    SA_CASE(4)
-    SA_CASE(8)
-    default:
-      return fail(ADAMAS_ERR_INVALID, "unsupported row length for select_attend");
+    case 1: return launch_select_attend_one<T, 1>(prm, cl, num_heads, smem, st);
+    case 2: return launch_select_attend_one<T, 2>(prm, cl, num_heads, smem, st);
+    case 4: return launch_select_attend_one<T, 4>(prm, cl, num_heads, smem, st);
+    case 8: return launch_select_attend_one<T, 8>(prm, cl, num_heads, smem, st);
+    default: break;
   }
-#undef SA_CASE
-  return check_launch("select_attend_kernel");
+  return fail(ADAMAS_ERR_INVALID, "unsupported row length for select_attend");
 }
 
 }  // namespace
 
 extern "C" {
 
-int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, const void* q, void* o,
-                         float* lse, const void* kv_data, const int32_t* kv_page_table, int page_size,
-                         int num_heads, int head_dim, int dtype, int last_page_idx, int last_page_len,
-                         int32_t* out_idx, int64_t out_stride, float sm_scale, adamas_stream_t stream) {
+static int select_attend_impl(const void* dist, int64_t dist_stride, int n, int k, const void* q,
+                              void* q_writeback, void* o, float* lse, const void* kv_data,
+                              const int32_t* kv_page_table, int page_size, int num_heads, int head_dim,
+                              int dtype, int last_page_idx, int last_page_len, int32_t* out_idx,
+                              int64_t out_stride, float sm_scale, adamas_stream_t stream) {
   if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
   ADAMAS_REQUIRE(dist && q && o && kv_data && kv_page_table, "null pointer");
   ADAMAS_REQUIRE(n >= 1 && k >= 1 && k <= n, "need 1 <= k <= n (k=%d, n=%d)", k, n);
@@ -982,11 +1067,11 @@ int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, co
   }
   ADAMAS_REQUIRE(cl > 0, "select_attend supports at most %d distances per head at cluster size %d (got %d)",
                  cl_limit * 8 * kSaThreads * 8, cl_limit, n);
+  const DeviceInfo* di = nullptr;
+  if (int rc = get_device_info(&di)) return rc;
   {
     // a large budget on a short row: more blocks per head than the scan needs, so that each block
     // attends to about one tile of winners, as long as all blocks stay resident at once
-    const DeviceInfo* di = nullptr;
-    if (int rc = get_device_info(&di)) return rc;
     while (cl < cl_limit && k > cl * kSaTile && 2 * cl * num_heads <= 2 * di->num_sms &&
            (g_total + 2 * cl - 1) / (2 * cl) >= 1)
       cl *= 2;
@@ -997,6 +1082,7 @@ int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, co
   prm.n = n;
   prm.k = k;
   prm.q = q;
+  prm.q_writeback = q_writeback;
   prm.o = o;
   prm.lse = lse;
   prm.kv = kv_data;
@@ -1010,12 +1096,132 @@ int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, co
   prm.granules_per_block = (g_total + cl - 1) / cl;
   const int slice_tokens = std::min(n, prm.granules_per_block * 8);
   prm.list_capacity = std::min(k, slice_tokens) + 1;
+  // Attention tile: the winners spread over the cl slices about evenly (binomially for unordered
+  // data); a tile with room for the mean plus four standard deviations makes a second, serial tile
+  // pass rare.  Lists that exceed the tile are still handled, tile after tile.
+  {
+    const int unit = kSaThreads / 8;   // tile sizes: unit (2 tokens per P.V group), 2 * unit, 3 * unit
+    const int mean = (k + cl - 1) / cl + 1;
+    const int want = std::min(prm.list_capacity, mean + static_cast<int>(4.0 * std::sqrt(static_cast<double>(mean))) + 8);
+    prm.tile_cap = want <= unit ? unit : (want <= 2 * unit ? 2 * unit : 3 * unit);
+  }
   prm.scale_log2 = sm_scale * 1.4426950408889634f;
-  const size_t smem = static_cast<size_t>(2) * kSaTile * 256 + static_cast<size_t>(prm.list_capacity) * 4;
+  prm.trace_tag = 0;
+#ifdef ADAMAS_PHASE_TIMING
+  {
+    static int sa_launches = 0;
+    prm.trace_tag = (sa_launches++) & 63;
+  }
+#endif
+  const size_t smem = static_cast<size_t>(2) * prm.tile_cap * 256 + static_cast<size_t>(prm.list_capacity) * 4;
   ADAMAS_REQUIRE(smem <= 160 * 1024, "winner list too long for select_attend (k=%d)", k);
   if (dtype == ADAMAS_F16)
     return launch_select_attend<__half>(prm, items, cl, num_heads, smem, to_stream(stream));
   return launch_select_attend<__nv_bfloat16>(prm, items, cl, num_heads, smem, to_stream(stream));
+}
+
+int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, const void* q, void* o,
+                         float* lse, const void* kv_data, const int32_t* kv_page_table, int page_size,
+                         int num_heads, int head_dim, int dtype, int last_page_idx, int last_page_len,
+                         int32_t* out_idx, int64_t out_stride, float sm_scale, adamas_stream_t stream) {
+  return select_attend_impl(dist, dist_stride, n, k, q, nullptr, o, lse, kv_data, kv_page_table, page_size,
+                            num_heads, head_dim, dtype, last_page_idx, last_page_len, out_idx, out_stride,
+                            sm_scale, stream);
+}
+
+// Stages 1 + 2 of a decode step in one launch (estimate_append_kernel); the caller has checked that
+// num_heads is 16, 32 or 64.
+static int estimate_append_launch(const void* q, void* q_rot_out, void* k, const void* v, void* q_code,
+                                  void* kv_data, const int32_t* kv_page_table, int kv_num_pages,
+                                  int kv_last_page_len, void* code_data, const int32_t* code_page_table,
+                                  int code_num_pages, int code_last_page_len, int num_heads, int page_size,
+                                  int dtype, void* dist, int64_t dist_stride, float hadamard_scale,
+                                  const float* thresholds3_host, float rope_scale, float rope_theta,
+                                  adamas_stream_t stream) {
+  ADAMAS_REQUIRE(q && k && v && q_code && kv_data && code_data && kv_page_table && code_page_table && dist,
+                 "null pointer");
+  ADAMAS_REQUIRE(kv_num_pages >= 1 && code_num_pages >= 1, "page tables must not be empty");
+  ADAMAS_REQUIRE(kv_last_page_len >= 1 && kv_last_page_len <= page_size, "kv_last_page_len out of range");
+  ADAMAS_REQUIRE(code_last_page_len >= 1 && code_last_page_len <= page_size,
+                 "code_last_page_len out of range");
+  const bool rope = rope_scale > 0.f;
+  ADAMAS_REQUIRE(!rope || rope_theta > 0.f, "rope_theta must be positive");
+  const int64_t n64 = static_cast<int64_t>(code_num_pages - 1) * page_size + code_last_page_len - 1;
+  ADAMAS_REQUIRE(n64 >= 1 && n64 < (int64_t(1) << 31) - kEstTile, "sequence length out of range");
+  const int n = static_cast<int>(n64);
+  ADAMAS_REQUIRE(dist_stride >= n, "dist_stride (%lld) smaller than the row length (%d)",
+                 static_cast<long long>(dist_stride), n);
+  ADAMAS_REQUIRE((reinterpret_cast<uintptr_t>(code_data) & 15) == 0 && (reinterpret_cast<uintptr_t>(q) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(k) & 15) == 0 && (reinterpret_cast<uintptr_t>(v) & 15) == 0,
+                 "q, k, v and code_data must be 16-byte aligned");
+  const DeviceInfo* di = nullptr;
+  if (int rc = get_device_info(&di)) return rc;
+  const int num_tiles = (n + kEstTile - 1) / kEstTile;
+  const int hpw = num_heads / kEstConsumerWarps;
+  const size_t smem = static_cast<size_t>(kEstStages) * kEstTile * (2 * num_heads + 1) * 16;
+  ADAMAS_REQUIRE(smem <= static_cast<size_t>(di->max_smem_optin - 1024), "num_heads (%d) too large", num_heads);
+  const int per_sm = (smem + 1024) * 2 <= static_cast<size_t>(di->max_smem_optin) ? 2 : 1;
+  const unsigned blocks = static_cast<unsigned>(std::min(num_tiles, di->num_sms * per_sm));
+  EstimateParams prm;
+  prm.codes = static_cast<const uint4*>(code_data);
+  prm.page_table = code_page_table;
+  prm.q_code = nullptr;
+  prm.out = dist;
+  prm.out_stride = dist_stride;
+  prm.n_tokens = n;
+  prm.H = num_heads;
+  prm.page_size = page_size;
+  prm.ps_shift = log2_exact(page_size);
+  prm.num_tiles = num_tiles;
+  prm.trace_tag = 0;
+  StepAppend ap;
+  ap.q = q;
+  ap.q_rot_out = q_rot_out;
+  ap.k = k;
+  ap.v = v;
+  ap.q_code_out = static_cast<uint16_t*>(q_code);
+  ap.tgt = PagedTarget{kv_data, kv_page_table, static_cast<uint16_t*>(code_data), code_page_table, page_size,
+                       num_heads};
+  ap.kv_last_page = kv_num_pages - 1;
+  ap.kv_entry = kv_last_page_len - 1;
+  ap.code_last_page = code_num_pages - 1;
+  ap.code_entry = code_last_page_len - 1;
+  ap.scale = hadamard_scale;
+  ap.th = make_thresholds(thresholds3_host);
+  ap.pos = static_cast<float>(static_cast<int64_t>(kv_num_pages - 1) * page_size + kv_last_page_len - 1);
+  ap.rp = RopeParams{rope ? 1.0f / rope_scale : 1.f, rope ? rope_theta : 1e4f};
+  cudaStream_t st = to_stream(stream);
+#define LAUNCH_ESTA(T, HPW, R)                                                                        \
+  ADAMAS_LAUNCH("estimate_append_kernel", (estimate_append_kernel<T, HPW, R>), dim3(blocks),          \
+                dim3(kEstThreads), smem, st, 1, prm, ap)
+#define LAUNCH_ESTA_T(T)                                                              \
+  do {                                                                                \
+    if (hpw == 1) { if (rope) LAUNCH_ESTA(T, 1, true); else LAUNCH_ESTA(T, 1, false); } \
+    else if (hpw == 2) { if (rope) LAUNCH_ESTA(T, 2, true); else LAUNCH_ESTA(T, 2, false); } \
+    else { if (rope) LAUNCH_ESTA(T, 4, true); else LAUNCH_ESTA(T, 4, false); }          \
+  } while (0)
+  if (dtype == ADAMAS_F16) LAUNCH_ESTA_T(__half); else LAUNCH_ESTA_T(__nv_bfloat16);
+#undef LAUNCH_ESTA_T
+#undef LAUNCH_ESTA
+  return check_launch("estimate_append_kernel");
+}
+
+int adamas_append_estimate(const void* q, void* q_rot_out, void* k, const void* v, void* q_code,
+                           void* kv_data, const int32_t* kv_page_table, int kv_num_pages,
+                           int kv_last_page_len, void* code_data, const int32_t* code_page_table,
+                           int code_num_pages, int code_last_page_len, int num_heads, int head_dim,
+                           int page_size, int dtype, void* dist, int64_t dist_stride, float hadamard_scale,
+                           const float* thresholds3_host, float rope_scale, float rope_theta,
+                           adamas_stream_t stream) {
+  if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
+  ADAMAS_REQUIRE(num_heads == 16 || num_heads == 32 || num_heads == 64,
+                 "adamas_append_estimate supports 16, 32 or 64 heads (got %d); use adamas_append_decode_fused "
+                 "and adamas_estimate", num_heads);
+  ADAMAS_REQUIRE(rope_scale <= 0.f || q_rot_out, "q_rot_out is required with rope_scale > 0");
+  return estimate_append_launch(q, q_rot_out, k, v, q_code, kv_data, kv_page_table, kv_num_pages,
+                                kv_last_page_len, code_data, code_page_table, code_num_pages,
+                                code_last_page_len, num_heads, page_size, dtype, dist, dist_stride,
+                                hadamard_scale, thresholds3_host, rope_scale, rope_theta, stream);
 }
 
 int adamas_decode_step(void* q, void* k, const void* v, void* o, float* lse, void* q_code,
@@ -1035,6 +1241,24 @@ int adamas_decode_step(void* q, void* k, const void* v, void* o, float* lse, voi
                  static_cast<long long>(seq_len), budget);
   ADAMAS_REQUIRE(seq_len - 1 < (int64_t(1) << 31), "sequence too long");
   ADAMAS_REQUIRE(dist_scratch && q_code, "null pointer");
+  if (fused_append_enabled() && (num_heads == 16 || num_heads == 32 || num_heads == 64) &&
+      head_dim == kHeadDim && (dtype == ADAMAS_F16 || dtype == ADAMAS_BF16)) {
+    // two launches: estimate with the append inside, then select + attend.  With RoPE the rotated
+    // query travels through `o` (select_attend reads it there before it writes the result) and is
+    // copied back over q by select_attend, so that q ends up rotated in place as documented.
+    ADAMAS_REQUIRE(q && o, "null pointer");
+    const bool rope = rope_scale > 0.f;
+    if (int rc = estimate_append_launch(q, o, k, v, q_code, kv_data, kv_page_table, kv_num_pages,
+                                        kv_last_page_len, code_data, code_page_table, code_num_pages,
+                                        code_last_page_len, num_heads, page_size, dtype, dist_scratch,
+                                        dist_stride, hadamard_scale, thresholds3_host, rope_scale, rope_theta,
+                                        stream))
+      return rc;
+    return select_attend_impl(dist_scratch, dist_stride, static_cast<int>(seq_len - 1), budget - 1,
+                              rope ? o : q, rope ? q : nullptr, o, lse, kv_data, kv_page_table, page_size,
+                              num_heads, head_dim, dtype, kv_last_page_idx, kv_last_page_len, out_idx,
+                              out_stride, sm_scale, stream);
+  }
   if (int rc = rope_scale > 0.f
                    ? adamas_append_decode_rope_fused(q, k, v, q_code, kv_data, kv_page_table, kv_num_pages,
                                                      kv_last_page_len, code_data, code_page_table,

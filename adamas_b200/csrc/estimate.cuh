@@ -17,6 +17,7 @@
 // The distance arithmetic on packed 2-bit codes is described at chunk_distance().
 #pragma once
 #include "common.cuh"
+#include "hadamard_append.cuh"
 
 namespace adamas {
 
@@ -92,97 +93,69 @@ struct EstimateParams {
   int page_size;
   int ps_shift;     // log2(page_size) or -1
   int num_tiles;
+  int trace_tag;    // launch number, used by builds with phase timing only
 };
 
-// Dynamic shared memory: kEstStages * kEstTile * (2H + 1) * 16 bytes (ring), plus 2H * 32 bytes of
-// query planes when HPW == 0.
-// HPW > 0: H == kEstConsumerWarps * HPW and warp w keeps the query planes of heads w*HPW .. in
-// registers.  HPW == 0: any H, warp w handles heads w, w + 16, ... with the planes in shared memory.
+// ---- the two halves of the copy pipeline, shared by the kernels below --------------------------------
+// Geometry of the ring for H heads: a token's codes are 2H 16-byte chunks, padded by one chunk so
+// that lanes reading one chunk position of 32 consecutive tokens hit 32 different bank groups.
+struct EstRing {
+  uint4* base;
+  uint64_t* full_bar;
+  uint64_t* empty_bar;
+  int cpt;            // 16-byte chunks per token (2H)
+  int row_chunks;     // padded row
+  int stage_chunks;   // chunks per ring slot
+};
+
+__device__ __forceinline__ int est_tiles_of_block(const EstimateParams& p) {
+  return (p.num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+         static_cast<int>(gridDim.x);
+}
+
+// Producer warp: one bulk copy per token (its H codes) into the padded ring slot.
+__device__ __forceinline__ void est_produce(const EstimateParams& p, const EstRing& r, int my_tiles, int lane) {
+  const unsigned token_bytes = static_cast<unsigned>(r.cpt) * 16u;
+  int slot = 0;
+  unsigned parity = 0;   // parity of the previous use of the slot, for the empty barrier
+  for (int j = 0; j < my_tiles; ++j) {
+    const int tile0 = (blockIdx.x + j * gridDim.x) * kEstTile;
+    const int tile_tokens = min(kEstTile, p.n_tokens - tile0);
+    if (j >= kEstStages) {
+      // every consumer warp has finished reading the tile that used this slot before
+      if (!mbar_wait_bounded(&r.empty_bar[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
+    }
+    if (lane == 0) mbar_arrive_expect_tx(&r.full_bar[slot], static_cast<unsigned>(tile_tokens) * token_bytes);
+    __syncwarp();
+    if (lane < tile_tokens) {
+      const int t = tile0 + lane;
+      int lp, e;
+      if (p.ps_shift >= 0) {
+        lp = t >> p.ps_shift;
+        e = t & (p.page_size - 1);
+      } else {
+        lp = t / p.page_size;
+        e = t - lp * p.page_size;
+      }
+      const int64_t tok = static_cast<int64_t>(__ldg(p.page_table + lp)) * p.page_size + e;
+      bulk_copy_g2s(r.base + slot * r.stage_chunks + lane * r.row_chunks, p.codes + tok * r.cpt, token_bytes,
+                    &r.full_bar[slot]);
+    }
+    if (++slot == kEstStages) {
+      slot = 0;
+      if (j >= kEstStages) parity ^= 1u;
+    }
+  }
+}
+
+// Consumer warp: lane = token of the tile; the warp covers heads warp*HPW .. (query planes in
+// registers, HPW > 0) or heads warp, warp + 16, ... (planes `sq` in shared memory, HPW == 0).
 template <int METRIC, typename OutT, int HPW>
-__global__ void __launch_bounds__(kEstThreads) estimate_kernel(const EstimateParams p) {
-  extern __shared__ uint4 est_smem[];
-  __shared__ __align__(8) uint64_t full_bar[kEstStages];
-  __shared__ __align__(8) uint64_t empty_bar[kEstStages];
-  const int tid = threadIdx.x;
-  const int lane = tid & 31;
-  const int warp = tid >> 5;
-  const int H = p.H;
-  const int cpt = 2 * H;                      // 16-byte chunks per token
-  const int row_chunks = cpt + 1;             // padded row: lanes reading one chunk position of 32
-                                              // consecutive tokens hit 32 different bank groups
-  const int stage_chunks = kEstTile * row_chunks;
+__device__ __forceinline__ void est_consume(const EstimateParams& p, const EstRing& r, int my_tiles, int lane,
+                                            int warp, const QPlanes (&qp)[HPW > 0 ? HPW : 1][2],
+                                            const QPlanes* sq) {
   OutT* out = static_cast<OutT*>(p.out);
-
-  if (tid == 0) {
-#pragma unroll
-    for (int s = 0; s < kEstStages; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], kEstConsumerWarps);
-    }
-    mbar_fence_init();
-  }
-  QPlanes* sq = reinterpret_cast<QPlanes*>(est_smem + kEstStages * stage_chunks);
-  if (HPW == 0) {
-    // generic path: the query planes go through shared memory, so the query code (written by the
-    // preceding append kernel) is needed before the block barrier
-    grid_dependency_wait();
-    for (int c = tid; c < cpt; c += kEstThreads) sq[c] = make_qplanes<METRIC>(__ldg(p.q_code + c));
-  }
-  __syncthreads();
-
-  const int my_tiles = (p.num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
-                       static_cast<int>(gridDim.x);
-
-  if (warp == kEstConsumerWarps) {
-    // ---- producer warp: one bulk copy per token (its H codes) into the padded ring slot -----------
-    const unsigned token_bytes = static_cast<unsigned>(cpt) * 16u;
-    int slot = 0;
-    unsigned parity = 0;   // parity of the previous use of the slot, for the empty barrier
-    for (int j = 0; j < my_tiles; ++j) {
-      const int tile0 = (blockIdx.x + j * gridDim.x) * kEstTile;
-      const int tile_tokens = min(kEstTile, p.n_tokens - tile0);
-      if (j >= kEstStages) {
-        // every consumer warp has finished reading the tile that used this slot before
-        if (!mbar_wait_bounded(&empty_bar[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
-      }
-      if (lane == 0) mbar_arrive_expect_tx(&full_bar[slot], static_cast<unsigned>(tile_tokens) * token_bytes);
-      __syncwarp();
-      if (lane < tile_tokens) {
-        const int t = tile0 + lane;
-        int lp, e;
-        if (p.ps_shift >= 0) {
-          lp = t >> p.ps_shift;
-          e = t & (p.page_size - 1);
-        } else {
-          lp = t / p.page_size;
-          e = t - lp * p.page_size;
-        }
-        const int64_t tok = static_cast<int64_t>(__ldg(p.page_table + lp)) * p.page_size + e;
-        bulk_copy_g2s(est_smem + slot * stage_chunks + lane * row_chunks, p.codes + tok * cpt, token_bytes,
-                      &full_bar[slot]);
-      }
-      if (++slot == kEstStages) {
-        slot = 0;
-        if (j >= kEstStages) parity ^= 1u;
-      }
-    }
-    grid_launch_dependents();
-    return;
-  }
-
-  // ---- consumer warps: lane = token of the tile, a warp covers its heads -------------------------
-  // The cached codes the producer streams were final before the preceding kernel started; the query
-  // code is that kernel's output, so the consumers wait for it here (the producer does not).
-  grid_dependency_wait();
-  grid_launch_dependents();
-  QPlanes qp[HPW > 0 ? HPW : 1][2];
-  if (HPW > 0) {
-#pragma unroll
-    for (int hh = 0; hh < HPW; ++hh) {
-      qp[hh][0] = make_qplanes<METRIC>(__ldg(p.q_code + 2 * (warp * HPW + hh)));
-      qp[hh][1] = make_qplanes<METRIC>(__ldg(p.q_code + 2 * (warp * HPW + hh) + 1));
-    }
-  }
+  const int H = p.H;
   int slot = 0;
   unsigned parity = 0;
   for (int j = 0; j < my_tiles; ++j) {
@@ -190,8 +163,8 @@ __global__ void __launch_bounds__(kEstThreads) estimate_kernel(const EstimatePar
     const int tile_tokens = min(kEstTile, p.n_tokens - tile0);
     // bounded wait for this tile's bytes; on failure flag the error and carry on (results are then
     // wrong, which the flag reports, but nothing spins forever)
-    if (!mbar_wait_bounded(&full_bar[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
-    const uint4* row = est_smem + slot * stage_chunks + lane * row_chunks;
+    if (!mbar_wait_bounded(&r.full_bar[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
+    const uint4* row = r.base + slot * r.stage_chunks + lane * r.row_chunks;
     OutT* o = out + tile0 + lane;
     if (HPW > 0) {
       unsigned d[HPW > 0 ? HPW : 1];
@@ -212,12 +185,200 @@ __global__ void __launch_bounds__(kEstThreads) estimate_kernel(const EstimatePar
       }
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(&empty_bar[slot]);
+    if (lane == 0) mbar_arrive(&r.empty_bar[slot]);
     if (++slot == kEstStages) {
       slot = 0;
       parity ^= 1u;
     }
   }
+}
+
+__device__ __forceinline__ EstRing est_ring_init(uint4* smem, uint64_t* full_bar, uint64_t* empty_bar, int H,
+                                                 int tid) {
+  EstRing r;
+  r.base = smem;
+  r.full_bar = full_bar;
+  r.empty_bar = empty_bar;
+  r.cpt = 2 * H;
+  r.row_chunks = r.cpt + 1;
+  r.stage_chunks = kEstTile * r.row_chunks;
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < kEstStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], kEstConsumerWarps);
+    }
+    mbar_fence_init();
+  }
+  return r;
+}
+
+// Dynamic shared memory: kEstStages * kEstTile * (2H + 1) * 16 bytes (ring), plus 2H * 32 bytes of
+// query planes when HPW == 0.
+// HPW > 0: H == kEstConsumerWarps * HPW and warp w keeps the query planes of heads w*HPW .. in
+// registers.  HPW == 0: any H, warp w handles heads w, w + 16, ... with the planes in shared memory.
+template <int METRIC, typename OutT, int HPW>
+__global__ void __launch_bounds__(kEstThreads) estimate_kernel(const EstimateParams p) {
+  extern __shared__ uint4 est_smem[];
+  __shared__ __align__(8) uint64_t full_bar[kEstStages];
+  __shared__ __align__(8) uint64_t empty_bar[kEstStages];
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const EstRing ring = est_ring_init(est_smem, full_bar, empty_bar, p.H, tid);
+  QPlanes* sq = reinterpret_cast<QPlanes*>(est_smem + kEstStages * ring.stage_chunks);
+  if (HPW == 0) {
+    // generic path: the query planes go through shared memory, so the query code (written by the
+    // preceding append kernel) is needed before the block barrier
+    grid_dependency_wait();
+    for (int c = tid; c < ring.cpt; c += kEstThreads) sq[c] = make_qplanes<METRIC>(__ldg(p.q_code + c));
+  }
+  __syncthreads();
+  const int my_tiles = est_tiles_of_block(p);
+
+  ADAMAS_STAMP(0, 0, tid == 0);
+  ADAMAS_TRACE(0, p.trace_tag, 0, tid == 0);
+  ADAMAS_CHAIN(1, 0, false, blockIdx.x == 0 && tid == 0);
+  if (warp == kEstConsumerWarps) {
+    est_produce(p, ring, my_tiles, lane);
+    grid_launch_dependents();
+    ADAMAS_STAMP(0, 4, lane == 0);
+    return;
+  }
+  // The cached codes the producer streams were final before the preceding kernel started; the query
+  // code is that kernel's output, so the consumers wait for it here (the producer does not).
+  grid_dependency_wait();
+  grid_launch_dependents();
+  ADAMAS_STAMP(0, 1, tid == 0);
+  ADAMAS_CHAIN(1, 1, false, blockIdx.x == 0 && tid == 0);
+  QPlanes qp[HPW > 0 ? HPW : 1][2];
+  if (HPW > 0) {
+#pragma unroll
+    for (int hh = 0; hh < HPW; ++hh) {
+      qp[hh][0] = make_qplanes<METRIC>(__ldg(p.q_code + 2 * (warp * HPW + hh)));
+      qp[hh][1] = make_qplanes<METRIC>(__ldg(p.q_code + 2 * (warp * HPW + hh) + 1));
+    }
+  }
+  ADAMAS_STAMP(0, 2, tid == 0);
+  est_consume<METRIC, OutT, HPW>(p, ring, my_tiles, lane, warp, qp, sq);
+  ADAMAS_STAMP(0, 3, tid == 0);
+  ADAMAS_TRACE(0, p.trace_tag, 1, tid == 0);
+  ADAMAS_CHAIN(1, 2, true, blockIdx.x == 0 && tid == 0);
+}
+
+// ---- estimate with the decode append inside (stages 1 + 2 of a decode step in one launch) -------------
+// Same pipeline; the consumer warps do not read a query code from memory but make it themselves: warp w
+// loads the query rows of its HPW heads (one half-warp per row), rotates them (ROPE), transforms,
+// buckets and packs them, and spreads the 16 code words of each head over the warp with shuffles.
+// Every block does this redundantly (H rows of 256 bytes from L2), so no block waits for another.
+// The last block (it has the fewest tiles) also does the append proper for the new token: K and V rows
+// into the page slot, the key's code into the code cache, the query code to q_code_out, and with ROPE
+// the rotated k back in place and the rotated q into q_rot_out (not in place: the other blocks still
+// read the un-rotated q).  None of this is read by the scan, which leaves the newest token out; the
+// kernel after this one finds all of it complete.
+struct StepAppend {
+  const void* q;           // [H,128]
+  void* q_rot_out;         // [H,128]: receives the rotated q when ROPE
+  void* k;                 // [H,128]; rotated in place when ROPE
+  const void* v;           // [H,128]
+  uint16_t* q_code_out;    // [H,16]
+  PagedTarget tgt;
+  int kv_last_page, kv_entry, code_last_page, code_entry;
+  float scale;
+  Thresholds th;
+  float pos;
+  RopeParams rp;
+};
+
+template <typename T, int HPW, bool ROPE>
+__global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const EstimateParams p, const StepAppend a) {
+  static_assert(HPW == 1 || HPW == 2 || HPW == 4, "heads per warp");
+  extern __shared__ uint4 est_smem[];
+  __shared__ __align__(8) uint64_t full_bar[kEstStages];
+  __shared__ __align__(8) uint64_t empty_bar[kEstStages];
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const EstRing ring = est_ring_init(est_smem, full_bar, empty_bar, p.H, tid);
+  __syncthreads();
+  const int my_tiles = est_tiles_of_block(p);
+
+  if (warp == kEstConsumerWarps) {
+    // the cached codes were final before the preceding kernel started: stream them right away
+    est_produce(p, ring, my_tiles, lane);
+    grid_launch_dependents();
+    return;
+  }
+  // q, k, v are the preceding kernel's output
+  grid_dependency_wait();
+  grid_launch_dependents();
+
+  const bool appender = blockIdx.x == gridDim.x - 1;
+  const unsigned l16 = lane & 15;
+  const int half = lane >> 4;
+  const int H = p.H;
+  QPlanes qp[HPW][2];
+#pragma unroll
+  for (int pass = 0; pass < (HPW + 1) / 2; ++pass) {
+    // this half-warp's row: head warp*HPW + 2*pass + half (HPW == 1: both halves take the one head)
+    const int hh_mine = (HPW == 1) ? 0 : 2 * pass + half;
+    const int head = warp * HPW + hh_mine;
+    const int64_t in_off = static_cast<int64_t>(head) * kHeadDim + l16 * 8;
+    const bool writer = appender && (HPW > 1 || half == 0);
+    float x[8];
+    unpack8<T>(ld_16(static_cast<const T*>(a.q) + in_off), x);
+    if (ROPE) {
+      rope_halfwarp<T>(x, l16, a.pos, a.rp);
+      if (writer) st_16(static_cast<T*>(a.q_rot_out) + in_off, pack8<T>(x));
+    }
+    wht128_halfwarp(x, l16);
+    scale_round<T>(x, a.scale);
+    const unsigned word = bucketize_pack8(x, a.th);   // code word l16 of `head`
+    if (writer) a.q_code_out[head * kCodeWords + l16] = static_cast<uint16_t>(word);
+#pragma unroll
+    for (int s = 0; s < (HPW == 1 ? 1 : 2); ++s) {
+      uint32_t cw[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const unsigned lo = __shfl_sync(0xffffffffu, word, s * 16 + 2 * j);
+        const unsigned hi = __shfl_sync(0xffffffffu, word, s * 16 + 2 * j + 1);
+        cw[j] = lo | (hi << 16);
+      }
+      const int hh = (HPW == 1) ? 0 : 2 * pass + s;
+      qp[hh][0] = make_qplanes<0>(make_uint4(cw[0], cw[1], cw[2], cw[3]));
+      qp[hh][1] = make_qplanes<0>(make_uint4(cw[4], cw[5], cw[6], cw[7]));
+    }
+    if (appender) {   // block-uniform
+      const int kv_page = __ldg(a.tgt.kv_table + a.kv_last_page);
+      const int code_page = __ldg(a.tgt.code_table + a.code_last_page);
+      const int ps = a.tgt.page_size;
+      T* kv = static_cast<T*>(a.tgt.kv_data);
+      const int64_t k_off =
+          ((static_cast<int64_t>(kv_page) * 2 * ps + a.kv_entry) * H + head) * kHeadDim + l16 * 8;
+      const int64_t v_delta = static_cast<int64_t>(ps) * H * kHeadDim;
+      uint4 kraw = ld_16(static_cast<const T*>(a.k) + in_off);
+      const uint4 vraw = ld_16(static_cast<const T*>(a.v) + in_off);
+      float b[8];
+      unpack8<T>(kraw, b);
+      if (ROPE) {
+        rope_halfwarp<T>(b, l16, a.pos, a.rp);
+        kraw = pack8<T>(b);
+        if (writer) st_16(static_cast<T*>(a.k) + in_off, kraw);
+      }
+      if (writer) {
+        st_16(kv + k_off, kraw);
+        st_16(kv + k_off + v_delta, vraw);
+      }
+      wht128_halfwarp(b, l16);
+      scale_round<T>(b, a.scale);
+      if (writer) {
+        const int64_t c_off =
+            ((static_cast<int64_t>(code_page) * ps + a.code_entry) * H + head) * kCodeWords + l16;
+        a.tgt.code_data[c_off] = bucketize_pack8(b, a.th);
+      }
+    }
+  }
+  est_consume<0, uint16_t, HPW>(p, ring, my_tiles, lane, warp, qp, nullptr);
 }
 
 }  // namespace adamas

@@ -148,8 +148,10 @@ append_decode_kernel(const T* __restrict__ k, const T* __restrict__ v, const T* 
                      const T* __restrict__ kh, uint16_t* __restrict__ q_code_out, PagedTarget tgt,
                      int kv_last_page, int kv_entry, int code_last_page, int code_entry, float scale,
                      Thresholds th, float pos = 0.f, RopeParams rp = RopeParams{1.f, 1e4f}) {
+  ADAMAS_CHAIN(0, 0, false, blockIdx.x == 0 && threadIdx.x == 0);
   grid_dependency_wait();
   grid_launch_dependents();
+  ADAMAS_CHAIN(0, 1, false, blockIdx.x == 0 && threadIdx.x == 0);
   // physical pages of the slot being written: last entries of the two page tables
   const int kv_page = __ldg(tgt.kv_table + kv_last_page);
   const int code_page = __ldg(tgt.code_table + code_last_page);
@@ -199,6 +201,7 @@ append_decode_kernel(const T* __restrict__ k, const T* __restrict__ v, const T* 
         ((static_cast<int64_t>(code_page) * tgt.page_size + code_entry) * H + hh) * kCodeWords + l16;
     tgt.code_data[c_off] = bucketize_pack8(b, th);
   }
+  ADAMAS_CHAIN(0, 2, true, blockIdx.x == 0 && threadIdx.x == 0);
 }
 
 // Prefill append: one half-warp per (token, head) row; token n sits at position start_pos + n.

@@ -6,21 +6,26 @@
 // One thread-block cluster (CL <= 8 blocks x 512 threads) per head.  Block `cr` owns a contiguous
 // slice of the head's distance row, keeps it in registers, and later attends over the winners that
 // lie in its own slice, so the selected indices never travel between blocks:
-//   pre   zero the exchange buffers, load the query row, cluster barrier (peers have started);
-//         all of this may overlap the tail of the estimate kernel (programmatic dependent launch);
-//   1     histogram of the block's distances (values < 512: a distance is at most 3 * 128);
-//         the non-zero bins are STORED into slot `cr` of every peer's per-source table; cluster
-//         barrier.  Every block now holds all CL histograms and derives by itself: the cut distance,
-//         how many cut-valued elements are taken in all, how many of them and how many smaller
-//         elements lie in lower-ranked slices (= its tie quota and its offset in the output list);
+//   pre   clear the local histogram and ARRIVE at a cluster barrier without waiting ("I have
+//         started"); all of this may overlap the tail of the estimate kernel (programmatic dependent
+//         launch);
+//   1     histogram of the block's distances (values < 512: a distance is at most 3 * 128); the wait
+//         half of the start-up barrier (every peer is running by now); the whole histogram, packed
+//         to 16-bit counts, is STORED into slot `cr` of every peer's per-source table with one
+//         16-byte remote store per thread (nothing has to be zeroed); cluster barrier.  Every block
+//         now holds all CL histograms and derives by itself: the cut distance, how many cut-valued
+//         elements are taken in all, how many of them and how many smaller elements lie in
+//         lower-ranked slices (= its tie quota and its offset in the output list);
 //   2     ordered compaction of the block's winners into a shared-memory list (and, optionally, to
 //         the global index list at the right offset);
-//   3     attention over the list in tiles of 128 tokens: K/V rows gathered with 16-byte cp.async
+//   3     attention over the list in tiles of `tile_cap` (64, 128 or 192) tokens, chosen by the host so
+//         that a block's winners almost always fit one tile: K/V rows gathered with 16-byte cp.async
 //         into XOR-swizzled shared memory, four threads per token for q.K, online softmax in base
-//         2, one thread per (group of 4 tokens, 8-dim chunk) for P.V;
+//         2, one thread per (group of tile_cap/32 tokens, 8-dim chunk) for P.V;
 //   4     the partial (o, m, l) is stored into slot `cr` of rank 0's shared memory; cluster barrier;
 //         rank 0 merges the CL partials and writes the head's output.
-// Only two cluster barriers sit on the critical path after the start-up one.
+// Only two cluster barriers sit on the critical path.  The histogram tables and the per-warp partial
+// outputs live in the K/V tile memory, which is idle before and after phase 3.
 #pragma once
 #include <cooperative_groups.h>
 
@@ -29,9 +34,11 @@
 namespace adamas {
 
 constexpr int kSaThreads = 512;
-constexpr int kSaWarps = kSaThreads / 32;
+constexpr int kSaMaxWarps = kSaThreads / 32;
 constexpr int kSaBins = 512;
-constexpr int kSaTile = 128;          // tokens per attention tile
+constexpr int kSaTile = 128;          // planning unit of the host (winners per block it aims for)
+constexpr int kSaMaxTpg = 6;          // tokens per P.V group at most
+constexpr int kSaTileMax = kSaMaxTpg * kSaThreads / 16;   // largest attention tile: 192 tokens
 constexpr int kSaMaxCluster = 8;
 
 struct SelectAttendParams {
@@ -39,7 +46,8 @@ struct SelectAttendParams {
   int64_t dist_stride;
   int n;                    // distances per head (tokens 0 .. n-1)
   int k;                    // winners per head, 1 <= k <= n
-  const void* q;            // [H, 128]
+  const void* q;            // [H, 128]; read after the preceding kernel has completed
+  void* q_writeback;        // optional [H, 128]: receives a copy of q (the rotated query of a fused step)
   void* o;                  // [H, 128]
   float* lse;               // [H] or null (base 2)
   const void* kv;           // [pages, 2, page_size, H, 128]
@@ -52,28 +60,42 @@ struct SelectAttendParams {
   int64_t out_stride;
   int granules_per_block;   // 16-byte granules (8 distances) of a row per block
   int list_capacity;        // entries of the shared-memory winner list
+  int tile_cap;             // tokens per attention tile: 64, 128 or 192
+  int trace_tag;            // launch number, used by builds with phase timing only
   float scale_log2;
 };
 
-static_assert(kSaBins == kSaThreads, "one histogram bin per thread");
-
 struct SaShared {
-  unsigned local[kSaBins];
-  unsigned per_src[kSaMaxCluster][kSaBins];
   float part_o[kSaMaxCluster][kHeadDim];     // rank 0 only: partial outputs of the blocks
   float part_ml[kSaMaxCluster][2];
-  float s_o[16][kHeadDim];                   // partial outputs of the 16 warps
-  float s_logit[kSaTile];
-  float s_p[kSaTile];
-  float s_red[kSaWarps];
-  float s_sum[kSaWarps];
-  unsigned warp_a[kSaWarps];
+  float s_logit[kSaTileMax];
+  float s_p[kSaTileMax];
+  float s_red[kSaMaxWarps];
+  float s_sum[kSaTileMax / 32];
+  unsigned warp_a[kSaMaxWarps];
+  unsigned warp_b[kSaMaxWarps];
   unsigned cut, before, lt_before, eq_before;
 };
 
-// Dynamic shared memory: K tile (32 KB) | V tile (32 KB) | winner list (list_capacity * 4 bytes).
+// The two halves of a cluster barrier (all threads of all blocks of the cluster execute both).
+__device__ __forceinline__ void cluster_arrive_release() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_acquire() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Dynamic shared memory: K tile (tile_cap * 256 B) | V tile (same) | winner list (list_capacity * 4 B).
+// The first 10 KB double as the histogram tables (local: 512 x u32; per source block: 8 x 512 x u16)
+// until phase 3 starts, the first 8 KB as the warps' partial outputs after it has ended.
 template <typename T, int ITEMS>
 __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const SelectAttendParams p) {
+  constexpr int NT = kSaThreads;
+  static_assert(NT >= kSaBins, "one histogram bin per thread");
+  constexpr int kWarps = NT / 32;
+  constexpr int kGroups = NT / 16;        // P.V token groups per tile
+  constexpr int kQkTokens = NT / 4;       // tokens per q.K pass
+  constexpr int kCapMax = kSaMaxTpg * kGroups;
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
   extern __shared__ __align__(16) uint8_t sa_smem[];
@@ -86,16 +108,27 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   const int lane = tid & 31;
   const int warp = tid >> 5;
   const int H = p.H;
+  const int cap = p.tile_cap;
 
   uint8_t* sk = sa_smem;
-  uint8_t* sv = sa_smem + kSaTile * 256;
-  int32_t* s_list = reinterpret_cast<int32_t*>(sa_smem + 2 * kSaTile * 256);
+  uint8_t* sv = sa_smem + cap * 256;
+  int32_t* s_list = reinterpret_cast<int32_t*>(sa_smem + 2 * cap * 256);
+  unsigned* h_local = reinterpret_cast<unsigned*>(sa_smem);
+  uint16_t* h_src = reinterpret_cast<uint16_t*>(sa_smem + kSaBins * 4);
+  float(*s_o)[kHeadDim] = reinterpret_cast<float(*)[kHeadDim]>(sa_smem);
 
-  // ---- pre: buffers, query, start-up barrier --------------------------------------------------------
-  {
-    uint4* z = reinterpret_cast<uint4*>(&sh.local[0]);   // local[] and per_src[] are contiguous
-    for (int i = tid; i < (kSaBins + kSaMaxCluster * kSaBins) / 4; i += kSaThreads) z[i] = make_uint4(0, 0, 0, 0);
-  }
+  // ---- pre ------------------------------------------------------------------------------------------
+  ADAMAS_STAMP(1, 0, tid == 0);
+  ADAMAS_TRACE(1, p.trace_tag, 0, tid == 0);
+  ADAMAS_CHAIN(2, 0, false, blockIdx.x == 0 && tid == 0);
+  if (tid < kSaBins) h_local[tid] = 0;
+  cluster_arrive_release();   // start-up barrier, first half: this block is running
+  __syncthreads();
+  grid_dependency_wait();
+  grid_launch_dependents();
+  ADAMAS_STAMP(1, 1, tid == 0);
+  ADAMAS_CHAIN(2, 1, false, blockIdx.x == 0 && tid == 0);
+
   // q.K mapping: four threads per token (tl = tid / 4, quarter = tid % 4); step i of a thread reads
   // logical chunk 4*quarter + ((i + quarter) & 3), which keeps the 8 lanes of a quarter-warp on 8
   // different 16-byte bank groups.  The query chunks stay packed in registers.
@@ -106,10 +139,12 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
     const T* qp = static_cast<const T*>(p.q) + static_cast<int64_t>(head) * kHeadDim;
 #pragma unroll
     for (int i = 0; i < 4; ++i) qpk[i] = ld_16(qp + (4 * quarter + ((i + quarter) & 3)) * 8);
+    if (p.q_writeback != nullptr && cr == 0 && tid < 4) {
+      T* wb = static_cast<T*>(p.q_writeback) + static_cast<int64_t>(head) * kHeadDim;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) st_16(wb + (4 * quarter + ((i + quarter) & 3)) * 8, qpk[i]);
+    }
   }
-  cluster.sync();
-  grid_dependency_wait();
-  grid_launch_dependents();
 
   // ---- 1: this block's slice of the row, histogram, exchange --------------------------------------
   const uint16_t* rowp = p.dist + static_cast<int64_t>(head) * p.dist_stride;
@@ -147,53 +182,71 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const unsigned d = (raw[i][j >> 1] >> ((j & 1) * 16)) & 0xffffu;
-      if ((vmask[i] >> j) & 1u) atomicAdd(&sh.local[min(d, static_cast<unsigned>(kSaBins - 1))], 1u);
+      if ((vmask[i] >> j) & 1u) atomicAdd(&h_local[min(d, static_cast<unsigned>(kSaBins - 1))], 1u);
     }
   }
   __syncthreads();
+  cluster_wait_acquire();     // start-up barrier, second half: every peer is running
+  ADAMAS_STAMP(1, 2, tid == 0);
   {
-    const unsigned c = sh.local[tid];   // kSaBins == kSaThreads: one bin per thread
-    if (c != 0)
-      for (unsigned r = 0; r < CL; ++r) *cluster.map_shared_rank(&sh.per_src[cr][tid], r) = c;
+    // thread -> (8 bins, peer): a block's count of one bin is at most 8 * 512 * ITEMS <= 32768
+    const int vec = tid & 63;
+    const unsigned peer = static_cast<unsigned>(tid) >> 6;
+    if (peer < CL) {
+      const uint4 a = *reinterpret_cast<const uint4*>(h_local + 8 * vec);
+      const uint4 b = *reinterpret_cast<const uint4*>(h_local + 8 * vec + 4);
+      const uint4 pk = make_uint4(a.x | (a.y << 16), a.z | (a.w << 16), b.x | (b.y << 16), b.z | (b.w << 16));
+      uint16_t* dst = cluster.map_shared_rank(h_src + cr * kSaBins + 8 * vec, peer);
+      *reinterpret_cast<uint4*>(dst) = pk;
+    }
   }
-  cluster.sync();
+  cluster_arrive_release();
+  cluster_wait_acquire();
+  ADAMAS_STAMP(1, 3, tid == 0);
 
   // every block: total histogram, cut, counts in lower-ranked slices (one bin per thread)
   {
     unsigned tot = 0, low = 0;
-    for (unsigned r = 0; r < CL; ++r) {
-      const unsigned c = sh.per_src[r][tid];
-      tot += c;
-      if (r < cr) low += c;
+    if (tid < kSaBins) {
+      for (unsigned r = 0; r < CL; ++r) {
+        const unsigned c = h_src[r * kSaBins + tid];
+        tot += c;
+        if (r < cr) low += c;
+      }
     }
-    unsigned incl = tot;
+    unsigned it = tot, il = low;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += t;
+      const unsigned t = __shfl_up_sync(0xffffffffu, it, o);
+      const unsigned u = __shfl_up_sync(0xffffffffu, il, o);
+      if (lane >= o) {
+        it += t;
+        il += u;
+      }
     }
-    if (lane == 31) sh.warp_a[warp] = incl;
-    if (tid == 0) { sh.lt_before = 0; sh.eq_before = 0; }
+    if (lane == 31) {
+      sh.warp_a[warp] = it;
+      sh.warp_b[warp] = il;
+    }
     __syncthreads();
-    unsigned wbase = 0;
+    unsigned wa = 0, wb = 0;
 #pragma unroll
-    for (int w2 = 0; w2 < kSaWarps; ++w2) wbase += (w2 < warp) ? sh.warp_a[w2] : 0u;
-    const unsigned excl = wbase + incl - tot;
+    for (int w2 = 0; w2 < kWarps; ++w2) {
+      wa += (w2 < warp) ? sh.warp_a[w2] : 0u;
+      wb += (w2 < warp) ? sh.warp_b[w2] : 0u;
+    }
+    const unsigned excl = wa + it - tot;
     const unsigned want = static_cast<unsigned>(p.k);
     if (excl < want && excl + tot >= want) {   // exactly one thread
       sh.cut = tid;
       sh.before = excl;
+      sh.lt_before = wb + il - low;            // smaller-valued elements in lower-ranked slices
+      sh.eq_before = low;                      // cut-valued elements in lower-ranked slices
     }
-    __syncthreads();
-    const unsigned cutb = sh.cut;
-    unsigned lt = (static_cast<unsigned>(tid) < cutb) ? low : 0u;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) lt += __shfl_xor_sync(0xffffffffu, lt, o);
-    if (lane == 0 && lt) atomicAdd(&sh.lt_before, lt);
-    if (static_cast<unsigned>(tid) == cutb) sh.eq_before = low;
     __syncthreads();
   }
   const unsigned cut = sh.cut;
+  ADAMAS_STAMP(1, 4, tid == 0);
   const unsigned need_eq = static_cast<unsigned>(p.k) - sh.before;       // cut-valued winners in all
   const unsigned eq_before = sh.eq_before;
   const unsigned take_eq = need_eq > eq_before ? need_eq - eq_before : 0u;  // this slice's tie quota
@@ -222,7 +275,7 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   __syncthreads();
   unsigned wbase = 0, blk_tot = 0;
 #pragma unroll
-  for (int w2 = 0; w2 < kSaWarps; ++w2) {
+  for (int w2 = 0; w2 < kWarps; ++w2) {
     const unsigned a = sh.warp_a[w2];
     wbase += (w2 < warp) ? a : 0u;
     blk_tot += a;
@@ -276,6 +329,7 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   }
   n_loc = min(n_loc, p.list_capacity);
   __syncthreads();
+  ADAMAS_STAMP(1, 5, tid == 0);
 
   // ---- 3: attention over the block's winners ------------------------------------------------------------
   const T* kvp = static_cast<const T*>(p.kv);
@@ -284,18 +338,19 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   float o_acc[8];
 #pragma unroll
   for (int d = 0; d < 8; ++d) o_acc[d] = 0.f;
-  const int pv_g = tid >> 4;   // token group: tokens pv_g*4 .. pv_g*4+3 of the tile (32 groups)
+  const int tpg = cap / kGroups;   // tokens per P.V group
+  const int pv_g = tid >> 4;   // token group: tokens pv_g*tpg .. pv_g*tpg+tpg-1 of the tile
   const int pv_c = tid & 15;   // 8-dim chunk
   const unsigned ps = static_cast<unsigned>(p.page_size);
 
-  for (int t0 = 0; t0 < n_loc; t0 += kSaTile) {
-    const int tile_tokens = min(kSaTile, n_loc - t0);
-    // gather: thread -> chunk c = tid % 16 of tokens tl = tid / 16 + 32 * i
+  for (int t0 = 0; t0 < n_loc; t0 += cap) {
+    const int tile_tokens = min(cap, n_loc - t0);
+    // gather: thread -> chunk c = tid % 16 of tokens tl = tid / 16 + kGroups * i
     {
       const int c = tid & 15;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int tl = (tid >> 4) + 32 * i;
+      for (int i = 0; i < kSaMaxTpg; ++i) {
+        const int tl = (tid >> 4) + kGroups * i;
         if (tl < tile_tokens) {
           const unsigned slot = static_cast<unsigned>(s_list[t0 + tl]);
           unsigned page, e;
@@ -317,79 +372,98 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
       cp_async_wait<0>();
     }
     __syncthreads();
+    ADAMAS_STAMP(1, 6, tid == 0 && t0 == 0);
+    ADAMAS_STAMP(1, 10, tid == 0 && t0 != 0);
 
-    float acc = 0.f;
-    const bool live = qk_tl < tile_tokens;
-    if (live) {
+    // q.K: tokens qk_tl (all threads) and NT/4 + qk_tl (tiles of more than NT/4 tokens)
+    float wmax = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int lc = 4 * quarter + ((i + quarter) & 3);
-        const int phys = lc ^ (qk_tl & 3);
-        float kf[8], qf[8];
-        unpack8<T>(*reinterpret_cast<const uint4*>(sk + qk_tl * 256 + phys * 16), kf);
-        unpack8<T>(qpk[i], qf);
+    for (int pass = 0; pass < 2; ++pass) {
+      if (pass == 1 && tile_tokens <= kQkTokens) break;   // block-uniform
+      const int tl = qk_tl + kQkTokens * pass;
+      float acc = 0.f;
+      const bool live = tl < tile_tokens;
+      if (live) {
 #pragma unroll
-        for (int d = 0; d < 8; ++d) acc = fmaf(qf[d], kf[d], acc);
+        for (int i = 0; i < 4; ++i) {
+          const int lc = 4 * quarter + ((i + quarter) & 3);
+          const int phys = lc ^ (tl & 3);
+          float kf[8], qf[8];
+          unpack8<T>(*reinterpret_cast<const uint4*>(sk + tl * 256 + phys * 16), kf);
+          unpack8<T>(qpk[i], qf);
+#pragma unroll
+          for (int d = 0; d < 8; ++d) acc = fmaf(qf[d], kf[d], acc);
+        }
       }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      const float logit = live ? acc * p.scale_log2 : -INFINITY;
+      if (quarter == 0 && tl < kCapMax) sh.s_logit[tl] = logit;
+      wmax = fmaxf(wmax, logit);
     }
-    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-    const float logit = live ? acc * p.scale_log2 : -INFINITY;
-    if (quarter == 0) sh.s_logit[qk_tl] = logit;
-    float wmax = logit;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, o));
     if (lane == 0) sh.s_red[warp] = wmax;
     __syncthreads();
     float m_tile = sh.s_red[0];
 #pragma unroll
-    for (int w2 = 1; w2 < kSaWarps; ++w2) m_tile = fmaxf(m_tile, sh.s_red[w2]);
+    for (int w2 = 1; w2 < kWarps; ++w2) m_tile = fmaxf(m_tile, sh.s_red[w2]);
     const float m_new = fmaxf(m_run, m_tile);
     const float rescale = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
-    float psum = 0.f;
-    if (tid < kSaTile) {
-      const float lg = sh.s_logit[tid];
-      const float pr = (lg == -INFINITY) ? 0.f : exp2f(lg - m_new);
-      sh.s_p[tid] = pr;
-      psum = pr;
-    }
-    if (tid < kSaTile) {   // warps 0..3
+    if (tid < kCapMax) {   // the first kCapMax / 32 warps
+      float psum = 0.f;
+      if (tid < tile_tokens) {
+        const float lg = sh.s_logit[tid];
+        const float pr = (lg == -INFINITY) ? 0.f : exp2f(lg - m_new);
+        sh.s_p[tid] = pr;
+        psum = pr;
+      } else {
+        sh.s_p[tid] = 0.f;
+      }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
       if (lane == 0) sh.s_sum[warp] = psum;
     }
     __syncthreads();
-    l_run = l_run * rescale + ((sh.s_sum[0] + sh.s_sum[1]) + (sh.s_sum[2] + sh.s_sum[3]));
+    {
+      float tile_sum = 0.f;
+#pragma unroll
+      for (int w2 = 0; w2 < kCapMax / 32; ++w2) tile_sum += sh.s_sum[w2];
+      l_run = l_run * rescale + tile_sum;
+    }
     m_run = m_new;
 #pragma unroll
     for (int d = 0; d < 8; ++d) o_acc[d] *= rescale;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int tl = pv_g * 4 + i;
-      const float pr = sh.s_p[tl];
-      if (pr != 0.f) {
-        const int phys = pv_c ^ (tl & 3);
-        float vf[8];
-        unpack8<T>(*reinterpret_cast<const uint4*>(sv + tl * 256 + phys * 16), vf);
+    for (int i = 0; i < kSaMaxTpg; ++i) {
+      if (i < tpg) {
+        const int tl = pv_g * tpg + i;
+        const float pr = sh.s_p[tl];
+        if (pr != 0.f) {
+          const int phys = pv_c ^ (tl & 3);
+          float vf[8];
+          unpack8<T>(*reinterpret_cast<const uint4*>(sv + tl * 256 + phys * 16), vf);
 #pragma unroll
-        for (int d = 0; d < 8; ++d) o_acc[d] = fmaf(pr, vf[d], o_acc[d]);
+          for (int d = 0; d < 8; ++d) o_acc[d] = fmaf(pr, vf[d], o_acc[d]);
+        }
       }
     }
     __syncthreads();
   }
 
   // ---- 4: partial to rank 0, merge -----------------------------------------------------------------------
+  ADAMAS_STAMP(1, 7, tid == 0);
 #pragma unroll
   for (int d = 0; d < 8; ++d) o_acc[d] += __shfl_xor_sync(0xffffffffu, o_acc[d], 16);   // the warp's two groups
   if (lane < 16) {
 #pragma unroll
-    for (int d = 0; d < 8; ++d) sh.s_o[warp][pv_c * 8 + d] = o_acc[d];
+    for (int d = 0; d < 8; ++d) s_o[warp][pv_c * 8 + d] = o_acc[d];
   }
   __syncthreads();
   if (tid < kHeadDim) {
     float od = 0.f;
 #pragma unroll
-    for (int g = 0; g < 16; ++g) od += sh.s_o[g][tid];
+    for (int g = 0; g < kWarps; ++g) od += s_o[g][tid];
     *cluster.map_shared_rank(&sh.part_o[cr][tid], 0) = od;
   }
   if (tid == 0) {
@@ -397,7 +471,13 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
     ml[0] = m_run;
     ml[1] = l_run;
   }
-  cluster.sync();
+  cluster_arrive_release();
+  cluster_wait_acquire();
+  ADAMAS_STAMP(1, 8, tid == 0);
+  ADAMAS_TRACE(1, p.trace_tag, 1, tid == 0);
+#ifdef ADAMAS_PHASE_TIMING
+  if (tid == 0 && blockIdx.x < kTimingBlocks) g_phase_timing[1][blockIdx.x][11] = static_cast<unsigned long long>(n_loc);
+#endif
   if (cr != 0 || tid >= kHeadDim) return;
   float M = -INFINITY;
   for (unsigned r = 0; r < CL; ++r) M = fmaxf(M, sh.part_ml[r][0]);
@@ -413,6 +493,11 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   T* op = static_cast<T*>(p.o) + static_cast<int64_t>(head) * kHeadDim;
   if ((tid & 1) == 0) reinterpret_cast<uint32_t*>(op)[tid >> 1] = Elem<T>::from_f2(res, res1);
   if (tid == 0 && p.lse) p.lse[head] = L > 0.f ? M + log2f(L) : -INFINITY;
+  ADAMAS_STAMP(1, 9, tid == 0);
+  ADAMAS_CHAIN(2, 2, true, blockIdx.x == 0 && tid == 0);
+#ifdef ADAMAS_PHASE_TIMING
+  if (tid == 0 && blockIdx.x < kTimingBlocks) g_phase_timing[1][blockIdx.x][11] = static_cast<unsigned long long>(n_loc);
+#endif
 }
 
 }  // namespace adamas

@@ -117,7 +117,7 @@ def decode_step(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, iController: 
                 layer_idx: int, out: Optional[torch.Tensor] = None, record_indices: bool = True,
                 scale: Optional[float] = None, rope=None) -> torch.Tensor:
     """The whole decode branch of the attention module (adamas/models/Adamas.py:145-200: cat,
-    Hadamard, append, estimate, top-k, sparse attention) in one call and three launches.
+    Hadamard, append, estimate, top-k, sparse attention) in one call and two or three launches.
 
     q, k, v [1,H,D] after RoPE, or before it with rope=(rope_scale, rope_theta): q and k are then
     rotated in place by the append launch (apply_rope_in_place, Adamas.py:113).  Returns o [1,H,D].  When the context still fits in the budget

@@ -480,6 +480,53 @@ def test_fused_decode_step(dtype, L, ps, budget, H):
     assert _lib.device_error(clear=False) == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rope", [None, (8.0, 1e4)])
+@pytest.mark.parametrize("L,ps,budget,H", [(300, 16, 64, 32), (1500, 1, 128, 16), (2100, 16, 256, 64),
+                                           (5000, 16, 1024, 32), (32768, 16, 1024, 32)])
+def test_two_launch_step_equals_three_launch_step(dtype, rope, L, ps, budget, H):
+    """decode_step with the append folded into the estimate launch writes the same bits as the
+    three-launch step: rotated q and k, the new token's K/V rows and code, the query code, the
+    distances, the selected slots and the output."""
+    _, K, U = _mods()
+    results = []
+    for fused_append in (False, True):
+        st = State(L - 1, H, ps, dtype, seed=L + 7, budget_pages=max(1, budget // ps), fused=True,
+                   max_seq_len=L + ps)
+        c = st.c
+        c.end_forward()
+        q = _randn((1, H, 128), 31 + L, dtype).to(DEV)
+        k_new = _randn((1, H, 128), 32 + L, dtype).to(DEV)
+        v_new = _randn((1, H, 128), 33 + L, dtype).to(DEV)
+        c.prepare_hadamard(1)
+        c.begin_forward(1)
+        o = torch.full_like(q, float("nan"))
+        q_code = torch.zeros(1, H, 16, dtype=dtype, device=DEV)
+        n = c.hadamard_cache.seqlen - 1
+        dist = c.distance_scratch(n)
+        K.set_fused_append(fused_append)
+        try:
+            K.decode_step(q, k_new, v_new, o, q_code, c.kv_cache.buf_layer(0), c.kv_indices_with_last,
+                          c.kv_cache.last_page_len, c.kv_last_page_idx, c.hadamard_cache.buf_layer(0),
+                          c.hadamard_indices, c.hadamard_cache.last_page_len, c.inference_token_budget, dist,
+                          indices_out=c.topk_dindices_buffer, rope=rope)
+            torch.cuda.synchronize()
+        finally:
+            K.set_fused_append(False)
+        page = c.kv_cache.indicies[-1]
+        kv_rows = c.kv_cache.buf_layer(0)[page, :, (L - 1) % ps].clone()
+        code = c.hadamard_cache.buf_layer(0)[c.hadamard_cache.indicies[-1], 0, (L - 1) % ps].clone()
+        results.append((q.clone(), k_new.clone(), kv_rows, code, q_code.clone(), dist[:, :n].clone(),
+                        c.topk_dindices_buffer[:, : c.inference_token_budget - 1].clone(), o.clone()))
+    names = ["q", "k", "kv rows", "key code", "query code", "distances", "selected slots", "output"]
+    for name, a, b in zip(names, *results):
+        a16 = a.view(torch.int16) if a.element_size() == 2 else a
+        b16 = b.view(torch.int16) if b.element_size() == 2 else b
+        assert torch.equal(a16, b16), name
+    from adamas_b200 import _lib
+    assert _lib.device_error(clear=False) == 0
+
+
 @pytest.mark.parametrize("blocks", [1, 2, 4])
 @pytest.mark.parametrize("L,budget,H", [(32768, 1024, 8), (6000, 640, 32)])
 def test_decode_step_with_smaller_clusters(blocks, L, budget, H):
