@@ -71,6 +71,8 @@ int check_common(int num_heads, int head_dim, int page_size, int dtype) {
   return ADAMAS_OK;
 }
 
+constexpr int kEstAppendStatic = 1280;   // static shared memory of estimate_append_kernel, rounded up
+
 // Per-device facts and one-time kernel attributes.
 struct DeviceInfo {
   bool ready = false;
@@ -111,7 +113,7 @@ int get_device_info(const DeviceInfo** out) {
 #undef EST_ATTR
 #define ESTA_ATTR(T, HPW, R)                                                                           \
   ADAMAS_CUDA(cudaFuncSetAttribute(estimate_append_kernel<T, HPW, R>,                                  \
-                                   cudaFuncAttributeMaxDynamicSharedMemorySize, est_max));            \
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, est_max - kEstAppendStatic)); \
   ADAMAS_CUDA(cudaFuncSetAttribute(estimate_append_kernel<T, HPW, R>,                                  \
                                    cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared))
 #define ESTA_ATTR_ALL(T) \
@@ -178,13 +180,13 @@ bool pdl_enabled() {
   return g_pdl != 0;
 }
 
-// Whether adamas_decode_step folds the append into the estimate launch (off unless
-// ADAMAS_FUSED_APPEND=1 or adamas_set_fused_append(1)).
+// Whether adamas_decode_step folds the append into the estimate launch (on unless
+// ADAMAS_FUSED_APPEND=0 or adamas_set_fused_append(0)).
 int g_fused_append = -1;
 bool fused_append_enabled() {
   if (g_fused_append < 0) {
     const char* e = std::getenv("ADAMAS_FUSED_APPEND");
-    g_fused_append = (e && e[0] == '1') ? 1 : 0;
+    g_fused_append = (e && e[0] == '0') ? 0 : 1;
   }
   return g_fused_append != 0;
 }
@@ -1159,8 +1161,9 @@ static int estimate_append_launch(const void* q, void* q_rot_out, void* k, const
   const int num_tiles = (n + kEstTile - 1) / kEstTile;
   const int hpw = num_heads / kEstConsumerWarps;
   const size_t smem = static_cast<size_t>(kEstStages) * kEstTile * (2 * num_heads + 1) * 16;
-  ADAMAS_REQUIRE(smem <= static_cast<size_t>(di->max_smem_optin - 1024), "num_heads (%d) too large", num_heads);
-  const int per_sm = (smem + 1024) * 2 <= static_cast<size_t>(di->max_smem_optin) ? 2 : 1;
+  ADAMAS_REQUIRE(smem <= static_cast<size_t>(di->max_smem_optin - 1024 - kEstAppendStatic),
+                 "num_heads (%d) too large", num_heads);
+  const int per_sm = (smem + 1024 + kEstAppendStatic) * 2 <= static_cast<size_t>(di->max_smem_optin) ? 2 : 1;
   const unsigned blocks = static_cast<unsigned>(std::min(num_tiles, di->num_sms * per_sm));
   EstimateParams prm;
   prm.codes = static_cast<const uint4*>(code_data);

@@ -296,6 +296,7 @@ __global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const Esti
   extern __shared__ uint4 est_smem[];
   __shared__ __align__(8) uint64_t full_bar[kEstStages];
   __shared__ __align__(8) uint64_t empty_bar[kEstStages];
+  __shared__ __align__(16) uint16_t s_code[kEstConsumerWarps][32];   // a warp's two rows of code words
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
@@ -335,18 +336,17 @@ __global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const Esti
     scale_round<T>(x, a.scale);
     const unsigned word = bucketize_pack8(x, a.th);   // code word l16 of `head`
     if (writer) a.q_code_out[head * kCodeWords + l16] = static_cast<uint16_t>(word);
+    // spread the 16 code words of each row over the warp: through shared memory (one 2-byte store per
+    // lane, two 16-byte broadcast loads per head)
+    __syncwarp();
+    s_code[warp][lane] = static_cast<uint16_t>(word);
+    __syncwarp();
 #pragma unroll
     for (int s = 0; s < (HPW == 1 ? 1 : 2); ++s) {
-      uint32_t cw[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const unsigned lo = __shfl_sync(0xffffffffu, word, s * 16 + 2 * j);
-        const unsigned hi = __shfl_sync(0xffffffffu, word, s * 16 + 2 * j + 1);
-        cw[j] = lo | (hi << 16);
-      }
+      const uint4* cw = reinterpret_cast<const uint4*>(&s_code[warp][16 * s]);
       const int hh = (HPW == 1) ? 0 : 2 * pass + s;
-      qp[hh][0] = make_qplanes<0>(make_uint4(cw[0], cw[1], cw[2], cw[3]));
-      qp[hh][1] = make_qplanes<0>(make_uint4(cw[4], cw[5], cw[6], cw[7]));
+      qp[hh][0] = make_qplanes<0>(cw[0]);
+      qp[hh][1] = make_qplanes<0>(cw[1]);
     }
     if (appender) {   // block-uniform
       const int kv_page = __ldg(a.tgt.kv_table + a.kv_last_page);

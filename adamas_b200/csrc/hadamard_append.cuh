@@ -26,12 +26,14 @@ __device__ __forceinline__ void wht128_halfwarp(float (&x)[8], unsigned l16) {
   }
 #pragma unroll
   for (unsigned m = 1; m < 16; m <<= 1) {
-    const bool upper = (l16 & m) != 0;
+    // lower lane holds a and receives b: a + b; upper lane holds b and receives a: a - b.  Written as
+    // one fused multiply-add with a factor of +-1: the product is exact, so the single rounding is that
+    // of the plain add or subtract.
+    const float sgn = (l16 & m) != 0 ? -1.0f : 1.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      float other = __shfl_xor_sync(0xffffffffu, x[i], m);
-      // lower lane holds a and receives b: a + b; upper lane holds b and receives a: a - b
-      x[i] = upper ? __fsub_rn(other, x[i]) : __fadd_rn(x[i], other);
+      const float other = __shfl_xor_sync(0xffffffffu, x[i], m);
+      x[i] = __fmaf_rn(x[i], sgn, other);
     }
   }
 }

@@ -64,12 +64,10 @@ int adamas_device_error(unsigned* flags, int clear);
  * reference launches everything on the legacy default stream (e.g. adamas/ops/csrc/page.cu:99). */
 int adamas_set_pdl(int enable);
 
-/* Chooses how adamas_decode_step launches a step whose head count is 16, 32 or 64: as three launches
- * (append, estimate, select+attend; the default) or with the append folded into the estimate launch
- * (two launches; ADAMAS_FUSED_APPEND=1 in the environment selects it).  Results are identical.  Two
- * launches cost less host time per step; in the three-launch chain the append overlaps the start of
- * the estimate, which is faster once launches are replayed from a CUDA graph.  No counterpart in the
- * reference. */
+/* Chooses how adamas_decode_step launches a step whose head count is 16, 32 or 64: with the append
+ * folded into the estimate launch (two launches; the default) or as three launches (append, estimate,
+ * select+attend; ADAMAS_FUSED_APPEND=0 in the environment selects it).  Results are identical.  No
+ * counterpart in the reference. */
 int adamas_set_fused_append(int enable);
 
 /* Upper bound (1, 2, 4 or 8; default 8, or ADAMAS_MAX_CLUSTER in the environment) on the number of
@@ -275,8 +273,8 @@ int adamas_append_estimate(const void* q, void* q_rot_out, void* k, const void* 
                            const float* thresholds3_host, float rope_scale, float rope_theta,
                            adamas_stream_t stream);
 
-/* One layer's whole decode step in one call: three launches (fused append, estimate, select+attend),
- * or two (the estimate with the append inside, then select+attend) after adamas_set_fused_append(1):
+/* One layer's whole decode step in one call: two launches (the estimate with the append inside, then
+ * select+attend) for 16, 32 or 64 heads, three (fused append, estimate, select+attend) otherwise:
  * what adamas/models/Adamas.py:145-200 does with seven launches.  q, k, v, o [1,H,D]; q_code
  * [1,H,D/8] scratch/output; dist_scratch [H, dist_stride] 16-bit, rows on 16-byte boundaries,
  * dist_stride >= context - 1.  Requires context > budget (otherwise every page is attended: use

@@ -512,7 +512,7 @@ def test_two_launch_step_equals_three_launch_step(dtype, rope, L, ps, budget, H)
                           indices_out=c.topk_dindices_buffer, rope=rope)
             torch.cuda.synchronize()
         finally:
-            K.set_fused_append(False)
+            K.set_fused_append(True)
         page = c.kv_cache.indicies[-1]
         kv_rows = c.kv_cache.buf_layer(0)[page, :, (L - 1) % ps].clone()
         code = c.hadamard_cache.buf_layer(0)[c.hadamard_cache.indicies[-1], 0, (L - 1) % ps].clone()
