@@ -430,7 +430,8 @@ def decode_step(q, k, v, o, q_code, kv_data, kv_indices, kv_last_page_len, kv_la
                 indices_out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
                 scale: Optional[float] = None, thresholds=None, rope=None) -> None:
     """One layer's decode step in one call: append + estimate, select + attend (two launches for 16, 32
-    or 64 heads, else three, for what adamas/models/Adamas.py:145-200 does with seven).  Needs context > budget.  With
+    or 64 heads and already rotated q/k, else three, for what adamas/models/Adamas.py:145-200 does with
+    seven).  Needs context > budget.  With
     rope=(rope_scale, rope_theta) q and k arrive un-rotated and are rotated in place first."""
     num_heads, head_dim, page_size = _check_append(k, v, kv_data, kv_indices, hadamard_data, hadamard_indices, NHD)
     _check_input(q, "q", 3)
@@ -458,12 +459,11 @@ def decode_step(q, k, v, o, q_code, kv_data, kv_indices, kv_last_page_len, kv_la
 
 
 def append_estimate(q, k, v, q_code, kv_data, kv_indices, kv_last_page_len, hadamard_data, hadamard_indices,
-                    hadamard_last_page_len, dist: torch.Tensor, q_rot_out: Optional[torch.Tensor] = None,
-                    scale: Optional[float] = None, thresholds=None, rope=None) -> None:
-    """Decode append and distance estimate in one launch (16, 32 or 64 heads): what
+                    hadamard_last_page_len, dist: torch.Tensor, scale: Optional[float] = None,
+                    thresholds=None) -> None:
+    """Decode append and distance estimate in one launch (16, 32 or 64 heads; q and k after RoPE): what
     append_kv_cache_decode_fused followed by estimate_attn_score do, with integer (16-bit) distances
-    in `dist` [H, >= context-1].  With rope=(rope_scale, rope_theta) k is rotated in place and the
-    rotated q goes to q_rot_out."""
+    in `dist` [H, >= context-1]."""
     num_heads, head_dim, page_size = _check_append(k, v, kv_data, kv_indices, hadamard_data, hadamard_indices, NHD)
     _check_input(q, "q", 3)
     _check_input(q_code, "q_code", 3)
@@ -471,18 +471,13 @@ def append_estimate(q, k, v, q_code, kv_data, kv_indices, kv_last_page_len, hada
     _require(tuple(q.shape) == tuple(k.shape) and k.size(0) == 1, "q, k, v must be [1, H, D]")
     _require(q_code.element_size() == 2 and q_code.numel() == num_heads * head_dim // 8, "q_code must be [1, H, D/8] 16-bit")
     _require(dist.element_size() == 2 and dist.size(0) == num_heads, "dist must be 16-bit [H, n]")
-    if rope is not None:
-        _require(q_rot_out is not None and tuple(q_rot_out.shape) == tuple(q.shape) and q_rot_out.dtype == q.dtype
-                 and q_rot_out.is_contiguous(), "q_rot_out must be a contiguous tensor shaped like q")
     s = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)
     _lib.check(lib.adamas_append_estimate(
-        _ptr(q), _ptr(q_rot_out), _ptr(k), _ptr(v), _ptr(q_code),
+        _ptr(q), _ptr(k), _ptr(v), _ptr(q_code),
         _ptr(kv_data), _ptr(kv_indices), kv_indices.numel(), int(kv_last_page_len),
         _ptr(hadamard_data), _ptr(hadamard_indices), hadamard_indices.numel(), int(hadamard_last_page_len),
         num_heads, head_dim, page_size, _dtype_code(k.dtype, "append_estimate"),
-        _ptr(dist), dist.stride(0), s, _lib.thresholds_arg(thresholds),
-        float(rope[0]) if rope is not None else 0.0, float(rope[1]) if rope is not None else 0.0, _stream()),
-        "append_estimate")
+        _ptr(dist), dist.stride(0), s, _lib.thresholds_arg(thresholds), _stream()), "append_estimate")
 
 
 def merge_states(o_parts: torch.Tensor, lse_parts: torch.Tensor, o: torch.Tensor,

@@ -51,8 +51,7 @@ SIGNATURES = {
     "adamas_select_attend": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _L, _F, _P],
     "adamas_decode_step": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I,
                            _P, _L, _P, _L, _F, _FP, _F, _F, _F, _P],
-    "adamas_append_estimate": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _L, _F, _FP,
-                               _F, _F, _P],
+    "adamas_append_estimate": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _L, _F, _FP, _P],
     "adamas_merge_states": [_P, _P, _I, _I, _I, _P, _P, _I, _P],
     "adamas_device_error": [POINTER(ctypes.c_uint), _I],
     "adamas_set_pdl": [_I],

@@ -111,18 +111,15 @@ int get_device_info(const DeviceInfo** out) {
     EST_ATTR_ALL(1, uint16_t);
 #undef EST_ATTR_ALL
 #undef EST_ATTR
-#define ESTA_ATTR(T, HPW, R)                                                                           \
-  ADAMAS_CUDA(cudaFuncSetAttribute(estimate_append_kernel<T, HPW, R>,                                  \
+#define ESTA_ATTR(T, HPW)                                                                              \
+  ADAMAS_CUDA(cudaFuncSetAttribute(estimate_append_kernel<T, HPW>,                                     \
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, est_max - kEstAppendStatic)); \
-  ADAMAS_CUDA(cudaFuncSetAttribute(estimate_append_kernel<T, HPW, R>,                                  \
+  ADAMAS_CUDA(cudaFuncSetAttribute(estimate_append_kernel<T, HPW>,                                     \
                                    cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared))
 #define ESTA_ATTR_ALL(T) \
-  ESTA_ATTR(T, 1, false); \
-  ESTA_ATTR(T, 1, true);  \
-  ESTA_ATTR(T, 2, false); \
-  ESTA_ATTR(T, 2, true);  \
-  ESTA_ATTR(T, 4, false); \
-  ESTA_ATTR(T, 4, true)
+  ESTA_ATTR(T, 1);       \
+  ESTA_ATTR(T, 2);       \
+  ESTA_ATTR(T, 4)
     ESTA_ATTR_ALL(__half);
     ESTA_ATTR_ALL(__nv_bfloat16);
 #undef ESTA_ATTR_ALL
@@ -530,7 +527,7 @@ int adamas_estimate(const void* q_code, const void* code_data, const int32_t* co
   ADAMAS_REQUIRE(exclude_last == 0 || exclude_last == 1, "exclude_last must be 0 or 1");
   const int64_t n64 =
       static_cast<int64_t>(code_num_pages - 1) * page_size + code_last_page_len - exclude_last;
-  ADAMAS_REQUIRE(n64 < (int64_t(1) << 31) - kEstTile, "sequence too long");
+  ADAMAS_REQUIRE(n64 < (int64_t(1) << 31) - kEstTile * kEstConsumerWarps, "sequence too long");
   const int n = static_cast<int>(n64);
   if (n == 0) return ADAMAS_OK;
   ADAMAS_REQUIRE(q_code && code_data && code_page_table && out, "null pointer");
@@ -541,10 +538,14 @@ int adamas_estimate(const void* q_code, const void* code_data, const int32_t* co
                  "q_code and code_data must be 16-byte aligned");
   const DeviceInfo* di = nullptr;
   if (int rc = get_device_info(&di)) return rc;
-  const int num_tiles = (n + kEstTile - 1) / kEstTile;
   const int hpw = (num_heads % kEstConsumerWarps == 0) ? num_heads / kEstConsumerWarps : 0;
   const bool in_regs = hpw == 1 || hpw == 2 || hpw == 4;
-  const size_t smem = static_cast<size_t>(kEstStages) * kEstTile * (2 * num_heads + 1) * 16 +
+  // fewer than 16 heads: a tile holds 16 / H groups of 32 tokens, so that all 16 consumer warps work
+  const int groups = (num_heads < kEstConsumerWarps && kEstConsumerWarps % num_heads == 0)
+                         ? kEstConsumerWarps / num_heads : 1;
+  const int tile_span = kEstTile * groups;
+  const int num_tiles = (n + tile_span - 1) / tile_span;
+  const size_t smem = static_cast<size_t>(kEstStages) * tile_span * (2 * num_heads + 1) * 16 +
                       (in_regs ? 0 : static_cast<size_t>(2 * num_heads) * sizeof(QPlanes));
   ADAMAS_REQUIRE(smem <= static_cast<size_t>(di->max_smem_optin - 1024),
                  "num_heads (%d) too large for the estimate kernel", num_heads);
@@ -564,6 +565,7 @@ int adamas_estimate(const void* q_code, const void* code_data, const int32_t* co
     prm.ps_shift = 0;
     while ((1 << prm.ps_shift) < page_size) ++prm.ps_shift;
   }
+  prm.groups = groups;
   prm.num_tiles = num_tiles;
   prm.trace_tag = 0;
 #ifdef ADAMAS_PHASE_TIMING
@@ -1039,11 +1041,10 @@ int launch_select_attend(const SelectAttendParams& prm, int items, int cl, int n
 
 extern "C" {
 
-static int select_attend_impl(const void* dist, int64_t dist_stride, int n, int k, const void* q,
-                              void* q_writeback, void* o, float* lse, const void* kv_data,
-                              const int32_t* kv_page_table, int page_size, int num_heads, int head_dim,
-                              int dtype, int last_page_idx, int last_page_len, int32_t* out_idx,
-                              int64_t out_stride, float sm_scale, adamas_stream_t stream) {
+int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, const void* q, void* o,
+                         float* lse, const void* kv_data, const int32_t* kv_page_table, int page_size,
+                         int num_heads, int head_dim, int dtype, int last_page_idx, int last_page_len,
+                         int32_t* out_idx, int64_t out_stride, float sm_scale, adamas_stream_t stream) {
   if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
   ADAMAS_REQUIRE(dist && q && o && kv_data && kv_page_table, "null pointer");
   ADAMAS_REQUIRE(n >= 1 && k >= 1 && k <= n, "need 1 <= k <= n (k=%d, n=%d)", k, n);
@@ -1084,7 +1085,6 @@ static int select_attend_impl(const void* dist, int64_t dist_stride, int n, int 
   prm.n = n;
   prm.k = k;
   prm.q = q;
-  prm.q_writeback = q_writeback;
   prm.o = o;
   prm.lse = lse;
   prm.kv = kv_data;
@@ -1122,23 +1122,13 @@ static int select_attend_impl(const void* dist, int64_t dist_stride, int n, int 
   return launch_select_attend<__nv_bfloat16>(prm, items, cl, num_heads, smem, to_stream(stream));
 }
 
-int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, const void* q, void* o,
-                         float* lse, const void* kv_data, const int32_t* kv_page_table, int page_size,
-                         int num_heads, int head_dim, int dtype, int last_page_idx, int last_page_len,
-                         int32_t* out_idx, int64_t out_stride, float sm_scale, adamas_stream_t stream) {
-  return select_attend_impl(dist, dist_stride, n, k, q, nullptr, o, lse, kv_data, kv_page_table, page_size,
-                            num_heads, head_dim, dtype, last_page_idx, last_page_len, out_idx, out_stride,
-                            sm_scale, stream);
-}
-
 // Stages 1 + 2 of a decode step in one launch (estimate_append_kernel); the caller has checked that
 // num_heads is 16, 32 or 64.
-static int estimate_append_launch(const void* q, void* q_rot_out, void* k, const void* v, void* q_code,
-                                  void* kv_data, const int32_t* kv_page_table, int kv_num_pages,
-                                  int kv_last_page_len, void* code_data, const int32_t* code_page_table,
-                                  int code_num_pages, int code_last_page_len, int num_heads, int page_size,
-                                  int dtype, void* dist, int64_t dist_stride, float hadamard_scale,
-                                  const float* thresholds3_host, float rope_scale, float rope_theta,
+static int estimate_append_launch(const void* q, const void* k, const void* v, void* q_code, void* kv_data,
+                                  const int32_t* kv_page_table, int kv_num_pages, int kv_last_page_len,
+                                  void* code_data, const int32_t* code_page_table, int code_num_pages,
+                                  int code_last_page_len, int num_heads, int page_size, int dtype, void* dist,
+                                  int64_t dist_stride, float hadamard_scale, const float* thresholds3_host,
                                   adamas_stream_t stream) {
   ADAMAS_REQUIRE(q && k && v && q_code && kv_data && code_data && kv_page_table && code_page_table && dist,
                  "null pointer");
@@ -1146,8 +1136,6 @@ static int estimate_append_launch(const void* q, void* q_rot_out, void* k, const
   ADAMAS_REQUIRE(kv_last_page_len >= 1 && kv_last_page_len <= page_size, "kv_last_page_len out of range");
   ADAMAS_REQUIRE(code_last_page_len >= 1 && code_last_page_len <= page_size,
                  "code_last_page_len out of range");
-  const bool rope = rope_scale > 0.f;
-  ADAMAS_REQUIRE(!rope || rope_theta > 0.f, "rope_theta must be positive");
   const int64_t n64 = static_cast<int64_t>(code_num_pages - 1) * page_size + code_last_page_len - 1;
   ADAMAS_REQUIRE(n64 >= 1 && n64 < (int64_t(1) << 31) - kEstTile, "sequence length out of range");
   const int n = static_cast<int>(n64);
@@ -1175,11 +1163,11 @@ static int estimate_append_launch(const void* q, void* q_rot_out, void* k, const
   prm.H = num_heads;
   prm.page_size = page_size;
   prm.ps_shift = log2_exact(page_size);
+  prm.groups = 1;
   prm.num_tiles = num_tiles;
   prm.trace_tag = 0;
   StepAppend ap;
   ap.q = q;
-  ap.q_rot_out = q_rot_out;
   ap.k = k;
   ap.v = v;
   ap.q_code_out = static_cast<uint16_t*>(q_code);
@@ -1191,17 +1179,15 @@ static int estimate_append_launch(const void* q, void* q_rot_out, void* k, const
   ap.code_entry = code_last_page_len - 1;
   ap.scale = hadamard_scale;
   ap.th = make_thresholds(thresholds3_host);
-  ap.pos = static_cast<float>(static_cast<int64_t>(kv_num_pages - 1) * page_size + kv_last_page_len - 1);
-  ap.rp = RopeParams{rope ? 1.0f / rope_scale : 1.f, rope ? rope_theta : 1e4f};
   cudaStream_t st = to_stream(stream);
-#define LAUNCH_ESTA(T, HPW, R)                                                                        \
-  ADAMAS_LAUNCH("estimate_append_kernel", (estimate_append_kernel<T, HPW, R>), dim3(blocks),          \
+#define LAUNCH_ESTA(T, HPW)                                                                        \
+  ADAMAS_LAUNCH("estimate_append_kernel", (estimate_append_kernel<T, HPW>), dim3(blocks),          \
                 dim3(kEstThreads), smem, st, 1, prm, ap)
-#define LAUNCH_ESTA_T(T)                                                              \
-  do {                                                                                \
-    if (hpw == 1) { if (rope) LAUNCH_ESTA(T, 1, true); else LAUNCH_ESTA(T, 1, false); } \
-    else if (hpw == 2) { if (rope) LAUNCH_ESTA(T, 2, true); else LAUNCH_ESTA(T, 2, false); } \
-    else { if (rope) LAUNCH_ESTA(T, 4, true); else LAUNCH_ESTA(T, 4, false); }          \
+#define LAUNCH_ESTA_T(T)                  \
+  do {                                    \
+    if (hpw == 1) LAUNCH_ESTA(T, 1);      \
+    else if (hpw == 2) LAUNCH_ESTA(T, 2); \
+    else LAUNCH_ESTA(T, 4);               \
   } while (0)
   if (dtype == ADAMAS_F16) LAUNCH_ESTA_T(__half); else LAUNCH_ESTA_T(__nv_bfloat16);
 #undef LAUNCH_ESTA_T
@@ -1209,22 +1195,19 @@ static int estimate_append_launch(const void* q, void* q_rot_out, void* k, const
   return check_launch("estimate_append_kernel");
 }
 
-int adamas_append_estimate(const void* q, void* q_rot_out, void* k, const void* v, void* q_code,
-                           void* kv_data, const int32_t* kv_page_table, int kv_num_pages,
-                           int kv_last_page_len, void* code_data, const int32_t* code_page_table,
-                           int code_num_pages, int code_last_page_len, int num_heads, int head_dim,
-                           int page_size, int dtype, void* dist, int64_t dist_stride, float hadamard_scale,
-                           const float* thresholds3_host, float rope_scale, float rope_theta,
-                           adamas_stream_t stream) {
+int adamas_append_estimate(const void* q, const void* k, const void* v, void* q_code, void* kv_data,
+                           const int32_t* kv_page_table, int kv_num_pages, int kv_last_page_len,
+                           void* code_data, const int32_t* code_page_table, int code_num_pages,
+                           int code_last_page_len, int num_heads, int head_dim, int page_size, int dtype,
+                           void* dist, int64_t dist_stride, float hadamard_scale,
+                           const float* thresholds3_host, adamas_stream_t stream) {
   if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
   ADAMAS_REQUIRE(num_heads == 16 || num_heads == 32 || num_heads == 64,
                  "adamas_append_estimate supports 16, 32 or 64 heads (got %d); use adamas_append_decode_fused "
                  "and adamas_estimate", num_heads);
-  ADAMAS_REQUIRE(rope_scale <= 0.f || q_rot_out, "q_rot_out is required with rope_scale > 0");
-  return estimate_append_launch(q, q_rot_out, k, v, q_code, kv_data, kv_page_table, kv_num_pages,
-                                kv_last_page_len, code_data, code_page_table, code_num_pages,
-                                code_last_page_len, num_heads, page_size, dtype, dist, dist_stride,
-                                hadamard_scale, thresholds3_host, rope_scale, rope_theta, stream);
+  return estimate_append_launch(q, k, v, q_code, kv_data, kv_page_table, kv_num_pages, kv_last_page_len,
+                                code_data, code_page_table, code_num_pages, code_last_page_len, num_heads,
+                                page_size, dtype, dist, dist_stride, hadamard_scale, thresholds3_host, stream);
 }
 
 int adamas_decode_step(void* q, void* k, const void* v, void* o, float* lse, void* q_code,
@@ -1244,23 +1227,19 @@ int adamas_decode_step(void* q, void* k, const void* v, void* o, float* lse, voi
                  static_cast<long long>(seq_len), budget);
   ADAMAS_REQUIRE(seq_len - 1 < (int64_t(1) << 31), "sequence too long");
   ADAMAS_REQUIRE(dist_scratch && q_code, "null pointer");
-  if (fused_append_enabled() && (num_heads == 16 || num_heads == 32 || num_heads == 64) &&
+  if (fused_append_enabled() && rope_scale <= 0.f && (num_heads == 16 || num_heads == 32 || num_heads == 64) &&
       head_dim == kHeadDim && (dtype == ADAMAS_F16 || dtype == ADAMAS_BF16)) {
-    // two launches: estimate with the append inside, then select + attend.  With RoPE the rotated
-    // query travels through `o` (select_attend reads it there before it writes the result) and is
-    // copied back over q by select_attend, so that q ends up rotated in place as documented.
+    // two launches: the estimate with the append inside, then select + attend.  Not with RoPE: every
+    // block of the estimate would repeat the rotation, which costs more than the append launch.
     ADAMAS_REQUIRE(q && o, "null pointer");
-    const bool rope = rope_scale > 0.f;
-    if (int rc = estimate_append_launch(q, o, k, v, q_code, kv_data, kv_page_table, kv_num_pages,
-                                        kv_last_page_len, code_data, code_page_table, code_num_pages,
-                                        code_last_page_len, num_heads, page_size, dtype, dist_scratch,
-                                        dist_stride, hadamard_scale, thresholds3_host, rope_scale, rope_theta,
-                                        stream))
+    if (int rc = estimate_append_launch(q, k, v, q_code, kv_data, kv_page_table, kv_num_pages, kv_last_page_len,
+                                        code_data, code_page_table, code_num_pages, code_last_page_len,
+                                        num_heads, page_size, dtype, dist_scratch, dist_stride, hadamard_scale,
+                                        thresholds3_host, stream))
       return rc;
-    return select_attend_impl(dist_scratch, dist_stride, static_cast<int>(seq_len - 1), budget - 1,
-                              rope ? o : q, rope ? q : nullptr, o, lse, kv_data, kv_page_table, page_size,
-                              num_heads, head_dim, dtype, kv_last_page_idx, kv_last_page_len, out_idx,
-                              out_stride, sm_scale, stream);
+    return adamas_select_attend(dist_scratch, dist_stride, static_cast<int>(seq_len - 1), budget - 1, q, o, lse,
+                                kv_data, kv_page_table, page_size, num_heads, head_dim, dtype, kv_last_page_idx,
+                                kv_last_page_len, out_idx, out_stride, sm_scale, stream);
   }
   if (int rc = rope_scale > 0.f
                    ? adamas_append_decode_rope_fused(q, k, v, q_code, kv_data, kv_page_table, kv_num_pages,

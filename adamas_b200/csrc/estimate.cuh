@@ -92,6 +92,7 @@ struct EstimateParams {
   int H;
   int page_size;
   int ps_shift;     // log2(page_size) or -1
+  int groups;       // token groups of 32 per tile: 1, or 16 / H for H < 16 (generic kernel only)
   int num_tiles;
   int trace_tag;    // launch number, used by builds with phase timing only
 };
@@ -113,22 +114,25 @@ __device__ __forceinline__ int est_tiles_of_block(const EstimateParams& p) {
          static_cast<int>(gridDim.x);
 }
 
-// Producer warp: one bulk copy per token (its H codes) into the padded ring slot.
+// Producer warp: one bulk copy per token (its H codes) into the padded ring slot.  GROUPED: a tile
+// holds p.groups groups of 32 tokens and a lane issues one copy per group.
+template <bool GROUPED>
 __device__ __forceinline__ void est_produce(const EstimateParams& p, const EstRing& r, int my_tiles, int lane) {
   const unsigned token_bytes = static_cast<unsigned>(r.cpt) * 16u;
+  const int tile_span = GROUPED ? kEstTile * p.groups : kEstTile;
   int slot = 0;
   unsigned parity = 0;   // parity of the previous use of the slot, for the empty barrier
   for (int j = 0; j < my_tiles; ++j) {
-    const int tile0 = (blockIdx.x + j * gridDim.x) * kEstTile;
-    const int tile_tokens = min(kEstTile, p.n_tokens - tile0);
+    const int tile0 = (blockIdx.x + j * gridDim.x) * tile_span;
+    const int tile_tokens = min(tile_span, p.n_tokens - tile0);
     if (j >= kEstStages) {
       // every consumer warp has finished reading the tile that used this slot before
       if (!mbar_wait_bounded(&r.empty_bar[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
     }
     if (lane == 0) mbar_arrive_expect_tx(&r.full_bar[slot], static_cast<unsigned>(tile_tokens) * token_bytes);
     __syncwarp();
-    if (lane < tile_tokens) {
-      const int t = tile0 + lane;
+    for (int tl = lane; tl < (GROUPED ? tile_tokens : min(tile_tokens, kEstTile)); tl += 32) {
+      const int t = tile0 + tl;
       int lp, e;
       if (p.ps_shift >= 0) {
         lp = t >> p.ps_shift;
@@ -138,7 +142,7 @@ __device__ __forceinline__ void est_produce(const EstimateParams& p, const EstRi
         e = t - lp * p.page_size;
       }
       const int64_t tok = static_cast<int64_t>(__ldg(p.page_table + lp)) * p.page_size + e;
-      bulk_copy_g2s(r.base + slot * r.stage_chunks + lane * r.row_chunks, p.codes + tok * r.cpt, token_bytes,
+      bulk_copy_g2s(r.base + slot * r.stage_chunks + tl * r.row_chunks, p.codes + tok * r.cpt, token_bytes,
                     &r.full_bar[slot]);
     }
     if (++slot == kEstStages) {
@@ -156,11 +160,12 @@ __device__ __forceinline__ void est_consume(const EstimateParams& p, const EstRi
                                             const QPlanes* sq) {
   OutT* out = static_cast<OutT*>(p.out);
   const int H = p.H;
+  const int tile_span = (HPW == 0) ? kEstTile * p.groups : kEstTile;
   int slot = 0;
   unsigned parity = 0;
   for (int j = 0; j < my_tiles; ++j) {
-    const int tile0 = (blockIdx.x + j * gridDim.x) * kEstTile;
-    const int tile_tokens = min(kEstTile, p.n_tokens - tile0);
+    const int tile0 = (blockIdx.x + j * gridDim.x) * tile_span;
+    const int tile_tokens = min(tile_span, p.n_tokens - tile0);
     // bounded wait for this tile's bytes; on failure flag the error and carry on (results are then
     // wrong, which the flag reports, but nothing spins forever)
     if (!mbar_wait_bounded(&r.full_bar[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
@@ -178,6 +183,13 @@ __device__ __forceinline__ void est_consume(const EstimateParams& p, const EstRi
         for (int hh = 0; hh < HPW; ++hh)
           o[static_cast<int64_t>(warp * HPW + hh) * p.out_stride] = dist_to_out<OutT>(d[hh]);
       }
+    } else if (p.groups > 1) {
+      // fewer than 16 heads: H * groups == 16, warp w takes head w % H of token group w / H
+      const int h = warp % H;
+      const int tl = (warp / H) * kEstTile + lane;
+      const uint4* grow = r.base + slot * r.stage_chunks + tl * r.row_chunks;
+      const unsigned d = chunk_distance<METRIC>(grow[2 * h], sq[2 * h]) + chunk_distance<METRIC>(grow[2 * h + 1], sq[2 * h + 1]);
+      if (tl < tile_tokens) out[static_cast<int64_t>(h) * p.out_stride + tile0 + tl] = dist_to_out<OutT>(d);
     } else {
       for (int h = warp; h < H; h += kEstConsumerWarps) {
         const unsigned d = chunk_distance<METRIC>(row[2 * h], sq[2 * h]) + chunk_distance<METRIC>(row[2 * h + 1], sq[2 * h + 1]);
@@ -194,14 +206,14 @@ __device__ __forceinline__ void est_consume(const EstimateParams& p, const EstRi
 }
 
 __device__ __forceinline__ EstRing est_ring_init(uint4* smem, uint64_t* full_bar, uint64_t* empty_bar, int H,
-                                                 int tid) {
+                                                 int tid, int groups = 1) {
   EstRing r;
   r.base = smem;
   r.full_bar = full_bar;
   r.empty_bar = empty_bar;
   r.cpt = 2 * H;
   r.row_chunks = r.cpt + 1;
-  r.stage_chunks = kEstTile * r.row_chunks;
+  r.stage_chunks = kEstTile * groups * r.row_chunks;
   if (tid == 0) {
 #pragma unroll
     for (int s = 0; s < kEstStages; ++s) {
@@ -213,8 +225,8 @@ __device__ __forceinline__ EstRing est_ring_init(uint4* smem, uint64_t* full_bar
   return r;
 }
 
-// Dynamic shared memory: kEstStages * kEstTile * (2H + 1) * 16 bytes (ring), plus 2H * 32 bytes of
-// query planes when HPW == 0.
+// Dynamic shared memory: kEstStages * kEstTile * groups * (2H + 1) * 16 bytes (ring), plus 2H * 32 bytes
+// of query planes when HPW == 0.
 // HPW > 0: H == kEstConsumerWarps * HPW and warp w keeps the query planes of heads w*HPW .. in
 // registers.  HPW == 0: any H, warp w handles heads w, w + 16, ... with the planes in shared memory.
 template <int METRIC, typename OutT, int HPW>
@@ -225,7 +237,7 @@ __global__ void __launch_bounds__(kEstThreads) estimate_kernel(const EstimatePar
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  const EstRing ring = est_ring_init(est_smem, full_bar, empty_bar, p.H, tid);
+  const EstRing ring = est_ring_init(est_smem, full_bar, empty_bar, p.H, tid, HPW == 0 ? p.groups : 1);
   QPlanes* sq = reinterpret_cast<QPlanes*>(est_smem + kEstStages * ring.stage_chunks);
   if (HPW == 0) {
     // generic path: the query planes go through shared memory, so the query code (written by the
@@ -240,7 +252,7 @@ __global__ void __launch_bounds__(kEstThreads) estimate_kernel(const EstimatePar
   ADAMAS_TRACE(0, p.trace_tag, 0, tid == 0);
   ADAMAS_CHAIN(1, 0, false, blockIdx.x == 0 && tid == 0);
   if (warp == kEstConsumerWarps) {
-    est_produce(p, ring, my_tiles, lane);
+    est_produce<HPW == 0>(p, ring, my_tiles, lane);
     grid_launch_dependents();
     ADAMAS_STAMP(0, 4, lane == 0);
     return;
@@ -268,29 +280,26 @@ __global__ void __launch_bounds__(kEstThreads) estimate_kernel(const EstimatePar
 
 // ---- estimate with the decode append inside (stages 1 + 2 of a decode step in one launch) -------------
 // Same pipeline; the consumer warps do not read a query code from memory but make it themselves: warp w
-// loads the query rows of its HPW heads (one half-warp per row), rotates them (ROPE), transforms,
-// buckets and packs them, and spreads the 16 code words of each head over the warp with shuffles.
+// loads the query rows of its HPW heads (one half-warp per row), transforms, buckets and packs them,
+// and spreads the 16 code words of each head over the warp through shared memory.
 // Every block does this redundantly (H rows of 256 bytes from L2), so no block waits for another.
 // The last block (it has the fewest tiles) also does the append proper for the new token: K and V rows
-// into the page slot, the key's code into the code cache, the query code to q_code_out, and with ROPE
-// the rotated k back in place and the rotated q into q_rot_out (not in place: the other blocks still
-// read the un-rotated q).  None of this is read by the scan, which leaves the newest token out; the
-// kernel after this one finds all of it complete.
+// into the page slot, the key's code into the code cache, the query code to q_code_out.  None of this
+// is read by the scan, which leaves the newest token out; the kernel after this one finds all of it
+// complete.  q and k arrive rotated: a rotary embedding in here would be repeated by every block (a
+// power and a sine/cosine per element), which costs far more than the append launch this kernel saves.
 struct StepAppend {
   const void* q;           // [H,128]
-  void* q_rot_out;         // [H,128]: receives the rotated q when ROPE
-  void* k;                 // [H,128]; rotated in place when ROPE
+  const void* k;           // [H,128]
   const void* v;           // [H,128]
   uint16_t* q_code_out;    // [H,16]
   PagedTarget tgt;
   int kv_last_page, kv_entry, code_last_page, code_entry;
   float scale;
   Thresholds th;
-  float pos;
-  RopeParams rp;
 };
 
-template <typename T, int HPW, bool ROPE>
+template <typename T, int HPW>
 __global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const EstimateParams p, const StepAppend a) {
   static_assert(HPW == 1 || HPW == 2 || HPW == 4, "heads per warp");
   extern __shared__ uint4 est_smem[];
@@ -306,7 +315,7 @@ __global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const Esti
 
   if (warp == kEstConsumerWarps) {
     // the cached codes were final before the preceding kernel started: stream them right away
-    est_produce(p, ring, my_tiles, lane);
+    est_produce<false>(p, ring, my_tiles, lane);
     grid_launch_dependents();
     return;
   }
@@ -328,10 +337,6 @@ __global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const Esti
     const bool writer = appender && (HPW > 1 || half == 0);
     float x[8];
     unpack8<T>(ld_16(static_cast<const T*>(a.q) + in_off), x);
-    if (ROPE) {
-      rope_halfwarp<T>(x, l16, a.pos, a.rp);
-      if (writer) st_16(static_cast<T*>(a.q_rot_out) + in_off, pack8<T>(x));
-    }
     wht128_halfwarp(x, l16);
     scale_round<T>(x, a.scale);
     const unsigned word = bucketize_pack8(x, a.th);   // code word l16 of `head`
@@ -356,15 +361,10 @@ __global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const Esti
       const int64_t k_off =
           ((static_cast<int64_t>(kv_page) * 2 * ps + a.kv_entry) * H + head) * kHeadDim + l16 * 8;
       const int64_t v_delta = static_cast<int64_t>(ps) * H * kHeadDim;
-      uint4 kraw = ld_16(static_cast<const T*>(a.k) + in_off);
+      const uint4 kraw = ld_16(static_cast<const T*>(a.k) + in_off);
       const uint4 vraw = ld_16(static_cast<const T*>(a.v) + in_off);
       float b[8];
       unpack8<T>(kraw, b);
-      if (ROPE) {
-        rope_halfwarp<T>(b, l16, a.pos, a.rp);
-        kraw = pack8<T>(b);
-        if (writer) st_16(static_cast<T*>(a.k) + in_off, kraw);
-      }
       if (writer) {
         st_16(kv + k_off, kraw);
         st_16(kv + k_off + v_delta, vraw);

@@ -47,7 +47,6 @@ struct SelectAttendParams {
   int n;                    // distances per head (tokens 0 .. n-1)
   int k;                    // winners per head, 1 <= k <= n
   const void* q;            // [H, 128]; read after the preceding kernel has completed
-  void* q_writeback;        // optional [H, 128]: receives a copy of q (the rotated query of a fused step)
   void* o;                  // [H, 128]
   float* lse;               // [H] or null (base 2)
   const void* kv;           // [pages, 2, page_size, H, 128]
@@ -128,23 +127,6 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   grid_launch_dependents();
   ADAMAS_STAMP(1, 1, tid == 0);
   ADAMAS_CHAIN(2, 1, false, blockIdx.x == 0 && tid == 0);
-
-  // q.K mapping: four threads per token (tl = tid / 4, quarter = tid % 4); step i of a thread reads
-  // logical chunk 4*quarter + ((i + quarter) & 3), which keeps the 8 lanes of a quarter-warp on 8
-  // different 16-byte bank groups.  The query chunks stay packed in registers.
-  const int qk_tl = tid >> 2;
-  const int quarter = tid & 3;
-  uint4 qpk[4];
-  {
-    const T* qp = static_cast<const T*>(p.q) + static_cast<int64_t>(head) * kHeadDim;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) qpk[i] = ld_16(qp + (4 * quarter + ((i + quarter) & 3)) * 8);
-    if (p.q_writeback != nullptr && cr == 0 && tid < 4) {
-      T* wb = static_cast<T*>(p.q_writeback) + static_cast<int64_t>(head) * kHeadDim;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) st_16(wb + (4 * quarter + ((i + quarter) & 3)) * 8, qpk[i]);
-    }
-  }
 
   // ---- 1: this block's slice of the row, histogram, exchange --------------------------------------
   const uint16_t* rowp = p.dist + static_cast<int64_t>(head) * p.dist_stride;
@@ -332,6 +314,18 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   ADAMAS_STAMP(1, 5, tid == 0);
 
   // ---- 3: attention over the block's winners ------------------------------------------------------------
+  // q.K mapping: four threads per token (tl = tid / 4, quarter = tid % 4); step i of a thread reads
+  // logical chunk 4*quarter + ((i + quarter) & 3), which keeps the 8 lanes of a quarter-warp on 8
+  // different 16-byte bank groups.  The query chunks stay packed in registers; they are fetched only
+  // now, so that the selection phases above have those registers for the distances.
+  const int qk_tl = tid >> 2;
+  const int quarter = tid & 3;
+  uint4 qpk[4];
+  {
+    const T* qp = static_cast<const T*>(p.q) + static_cast<int64_t>(head) * kHeadDim;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) qpk[i] = ld_16(qp + (4 * quarter + ((i + quarter) & 3)) * 8);
+  }
   const T* kvp = static_cast<const T*>(p.kv);
   const int64_t v_delta = static_cast<int64_t>(p.page_size) * H * kHeadDim;
   float m_run = -INFINITY, l_run = 0.f;

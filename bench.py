@@ -685,8 +685,8 @@ def main():
                     help="four launches per layer (append, estimate, top-k, sparse decode) instead of the fused step")
     ap.add_argument("--no-cpu", dest="no_cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--traffic", type=float, default=None,
-                    help="DRAM bytes per estimate launch from an ncu capture; default: the figure in "
-                         "profiles/estimate_topk_decode_kernels_32k_ncu.md when the workload matches it")
+                    help="DRAM bytes per launch of the dominant kernel from an ncu capture; default: the figure in "
+                         "profiles/fused_step_kernels_32k_b1024_ncu.md when the workload matches it")
     ap.add_argument("--sweep", action="store_true", help="per-operator sweep over context x budget (one GPU)")
     ap.add_argument("--sweep-ctx", dest="sweep_ctx", type=int, nargs="+", default=[8192, 32768, 131072])
     ap.add_argument("--sweep-budget", dest="sweep_budget", type=int, nargs="+", default=[64, 128, 512, 2048])
@@ -711,7 +711,10 @@ def main():
         run_sweep(args)
         return
     if args.traffic is None and (args.ctx, args.heads, args.page_size) == (32768, 32, 16):
-        args.traffic = 33.58e6 + 1.0e3     # dram__bytes_read.sum + dram__bytes_write.sum, one launch
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel (ncu, 32K
+        # context, 32 heads): 33.62 MB for the estimate with the append inside
+        # (profiles/fused_step_kernels_32k_b1024_ncu.md), 33.58 MB for the plain estimate
+        args.traffic = 33.62e6 if two_launch_step(args) else 33.58e6 + 1.0e3
     if args.impl == "reference":
         run_reference_arm(args)
     else:

@@ -64,10 +64,10 @@ int adamas_device_error(unsigned* flags, int clear);
  * reference launches everything on the legacy default stream (e.g. adamas/ops/csrc/page.cu:99). */
 int adamas_set_pdl(int enable);
 
-/* Chooses how adamas_decode_step launches a step whose head count is 16, 32 or 64: with the append
- * folded into the estimate launch (two launches; the default) or as three launches (append, estimate,
- * select+attend; ADAMAS_FUSED_APPEND=0 in the environment selects it).  Results are identical.  No
- * counterpart in the reference. */
+/* Chooses how adamas_decode_step launches a step whose head count is 16, 32 or 64 and whose q and k
+ * are already rotated: with the append folded into the estimate launch (two launches; the default) or
+ * as three launches (append, estimate, select+attend; ADAMAS_FUSED_APPEND=0 in the environment selects
+ * it).  Results are identical.  No counterpart in the reference. */
 int adamas_set_fused_append(int enable);
 
 /* Upper bound (1, 2, 4 or 8; default 8, or ADAMAS_MAX_CLUSTER in the environment) on the number of
@@ -257,24 +257,22 @@ int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, co
                          int32_t* out_idx, int64_t out_stride, float sm_scale, adamas_stream_t stream);
 
 /* Stages 1 and 2 of a decode step in one launch, for 16, 32 or 64 heads: the append of
- * adamas_append_decode_fused / adamas_append_decode_rope_fused (new token's K, V and code into the
- * caches, query code to q_code) and the estimate of adamas_estimate with ADAMAS_VAL_U16 output, the L1
- * metric and exclude_last = 1 (dist [H, dist_stride], rows on 16-byte boundaries, dist_stride >=
- * context - 1).  Every thread block derives the query code from q by itself, so the scan does not wait
- * for an append launch.  With rope_scale > 0, q and k arrive un-rotated: k is rotated in place, the
- * rotated q is written to q_rot_out [1,H,D] (q itself is left as it is); rope_scale <= 0: q and k are
- * already rotated and q_rot_out is ignored.
- * Replaces hadamard_transform + append_kvh + decode_estimate of adamas/models/Adamas.py:145-180. */
-int adamas_append_estimate(const void* q, void* q_rot_out, void* k, const void* v, void* q_code,
-                           void* kv_data, const int32_t* kv_page_table, int kv_num_pages,
-                           int kv_last_page_len, void* code_data, const int32_t* code_page_table,
-                           int code_num_pages, int code_last_page_len, int num_heads, int head_dim,
-                           int page_size, int dtype, void* dist, int64_t dist_stride, float hadamard_scale,
-                           const float* thresholds3_host, float rope_scale, float rope_theta,
-                           adamas_stream_t stream);
+ * adamas_append_decode_fused (new token's K, V and code into the caches, query code to q_code; q and k
+ * already rotated) and the estimate of adamas_estimate with ADAMAS_VAL_U16 output, the L1 metric and
+ * exclude_last = 1 (dist [H, dist_stride], rows on 16-byte boundaries, dist_stride >= context - 1).
+ * Every thread block derives the query code from q by itself, so the scan does not wait for an append
+ * launch.  Replaces hadamard_transform + append_kvh + decode_estimate of
+ * adamas/models/Adamas.py:145-180. */
+int adamas_append_estimate(const void* q, const void* k, const void* v, void* q_code, void* kv_data,
+                           const int32_t* kv_page_table, int kv_num_pages, int kv_last_page_len,
+                           void* code_data, const int32_t* code_page_table, int code_num_pages,
+                           int code_last_page_len, int num_heads, int head_dim, int page_size, int dtype,
+                           void* dist, int64_t dist_stride, float hadamard_scale,
+                           const float* thresholds3_host, adamas_stream_t stream);
 
 /* One layer's whole decode step in one call: two launches (the estimate with the append inside, then
- * select+attend) for 16, 32 or 64 heads, three (fused append, estimate, select+attend) otherwise:
+ * select+attend) for 16, 32 or 64 heads and rotated inputs, three (fused append, estimate,
+ * select+attend) otherwise:
  * what adamas/models/Adamas.py:145-200 does with seven launches.  q, k, v, o [1,H,D]; q_code
  * [1,H,D/8] scratch/output; dist_scratch [H, dist_stride] 16-bit, rows on 16-byte boundaries,
  * dist_stride >= context - 1.  Requires context > budget (otherwise every page is attended: use
