@@ -62,7 +62,13 @@ def _value_format(dtype: torch.dtype, what: str) -> int:
     raise RuntimeError(f"{what} failed to dispatch with dtype {dtype}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> ctypes.c_void_p:
+    """The current CUDA stream of the current device as a raw handle."""
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 

@@ -128,6 +128,22 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   ADAMAS_STAMP(1, 1, tid == 0);
   ADAMAS_CHAIN(2, 1, false, blockIdx.x == 0 && tid == 0);
 
+  // q.K mapping: four threads per token (tl = tid / 4, quarter = tid % 4); step i of a thread reads
+  // logical chunk 4*quarter + ((i + quarter) & 3), which keeps the 8 lanes of a quarter-warp on 8
+  // different 16-byte bank groups.  The query chunks stay packed in registers.  Short rows fetch them
+  // now (the latency hides behind the selection); long rows hold 16 to 64 distances per thread through
+  // the selection phases and fetch the query after them, so that it does not push distances out of the
+  // registers.
+  const int qk_tl = tid >> 2;
+  const int quarter = tid & 3;
+  uint4 qpk[4];
+  auto load_query = [&]() {
+    const T* qp = static_cast<const T*>(p.q) + static_cast<int64_t>(head) * kHeadDim;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) qpk[i] = ld_16(qp + (4 * quarter + ((i + quarter) & 3)) * 8);
+  };
+  if (ITEMS == 1) load_query();
+
   // ---- 1: this block's slice of the row, histogram, exchange --------------------------------------
   const uint16_t* rowp = p.dist + static_cast<int64_t>(head) * p.dist_stride;
   const uint4* gbase = reinterpret_cast<const uint4*>(rowp);
@@ -314,18 +330,7 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   ADAMAS_STAMP(1, 5, tid == 0);
 
   // ---- 3: attention over the block's winners ------------------------------------------------------------
-  // q.K mapping: four threads per token (tl = tid / 4, quarter = tid % 4); step i of a thread reads
-  // logical chunk 4*quarter + ((i + quarter) & 3), which keeps the 8 lanes of a quarter-warp on 8
-  // different 16-byte bank groups.  The query chunks stay packed in registers; they are fetched only
-  // now, so that the selection phases above have those registers for the distances.
-  const int qk_tl = tid >> 2;
-  const int quarter = tid & 3;
-  uint4 qpk[4];
-  {
-    const T* qp = static_cast<const T*>(p.q) + static_cast<int64_t>(head) * kHeadDim;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) qpk[i] = ld_16(qp + (4 * quarter + ((i + quarter) & 3)) * 8);
-  }
+  if (ITEMS > 1) load_query();
   const T* kvp = static_cast<const T*>(p.kv);
   const int64_t v_delta = static_cast<int64_t>(p.page_size) * H * kHeadDim;
   float m_run = -INFINITY, l_run = 0.f;

@@ -58,6 +58,12 @@ class KvCache:
         self._indicies = []
         self._seqlen = 0
         self._table = torch.zeros(self._pool.capacity, dtype=torch.int32, device=device)
+        # host mirror of the table; pinned when the table lives on a GPU, so that new entries travel
+        # with an asynchronous copy (a copy from pageable memory would wait for the stream to drain,
+        # i.e. for the decode steps already queued, every time a sequence grows by a page)
+        self._host_table = torch.zeros(self._pool.capacity, dtype=torch.int32)
+        if self._table.is_cuda:
+            self._host_table = self._host_table.pin_memory()
         self._uploaded = 0
 
     pool = property(lambda self: self._pool)
@@ -89,8 +95,9 @@ class KvCache:
         persistent buffer; only entries added since the last call are copied to the device)."""
         n = len(self._indicies)
         if self._uploaded < n:
-            new = torch.tensor(self._indicies[self._uploaded:n], dtype=torch.int32)
-            self._table[self._uploaded:n].copy_(new, non_blocking=False)
+            # every entry of the mirror is written once, before the copy that reads it is queued
+            self._host_table[self._uploaded:n] = torch.tensor(self._indicies[self._uploaded:n], dtype=torch.int32)
+            self._table[self._uploaded:n].copy_(self._host_table[self._uploaded:n], non_blocking=True)
             self._uploaded = n
         return self._table[:n]
 
@@ -100,4 +107,6 @@ class KvCache:
         for idx in self._indicies:
             self._pool.free_block(idx)
         self._indicies.clear()
+        if self._table.is_cuda and self._uploaded:
+            torch.cuda.current_stream(self._table.device).synchronize()   # copies out of the mirror have landed
         self._uploaded = 0
