@@ -73,30 +73,26 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
   // ---- gather one tile into a stage --------------------------------------------------------------
   // thread -> chunk c = tid % 16 of tokens tl = tid / 16 + 8 * i.  Slots are < 2^31 (checked on the
   // host), so the index arithmetic is 32-bit; only the final element offset is 64-bit.
-  // Two steps, software-pipelined by the caller: the token slots of a tile are read from the index
-  // list one tile ahead of the copies that use them, so that the copies are not issued behind a
-  // dependent global load.
-  const unsigned ps = static_cast<unsigned>(prm.page_size);
-  struct TileSlots {
-    unsigned slot[8];
-    unsigned ok;   // bit i: token i of this thread is attended
-  };
-  auto load_slots = [&](int tile) {
-    TileSlots ts;
-    ts.ok = 0;
+  auto issue_tile = [&](int tile, int stage) {
+    uint8_t* sk = smem + stage * kDecStageBytes;
+    uint8_t* sv = sk + kDecTile * kHeadDim * 2;
+    const int c = tid & 15;
     const int t0 = tok_begin + tile * kDecTile;
+    const unsigned ps = static_cast<unsigned>(prm.page_size);
+    unsigned slot[8];
+    bool ok[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int tl = (tid >> 4) + 8 * i;
       const int j = t0 + tl;
-      bool ok = j < tok_end;
-      ts.slot[i] = 0;
-      if (ok) {
+      ok[i] = j < tok_end;
+      slot[i] = 0;
+      if (ok[i]) {
         if (j < n_listed) {
           if (prm.idx_unit == 1) {
             const int32_t id = __ldg(idx_row + j);
-            ok = id >= 0;   // a negative entry is a hole in the list: the token is skipped
-            ts.slot[i] = static_cast<unsigned>(id);
+            ok[i] = id >= 0;   // a negative entry is a hole in the list: the token is skipped
+            slot[i] = static_cast<unsigned>(id);
           } else {  // page-granular list: idx_unit == page_size
             unsigned item, off;
             if (prm.ps_shift >= 0) {
@@ -106,33 +102,25 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
               item = static_cast<unsigned>(j) / ps;
               off = static_cast<unsigned>(j) - item * ps;
             }
-            ts.slot[i] = static_cast<unsigned>(__ldg(idx_row + item)) * ps + off;
+            slot[i] = static_cast<unsigned>(__ldg(idx_row + item)) * ps + off;
           }
         } else {
-          ts.slot[i] = prm.tail_slot0 + static_cast<unsigned>(j - n_listed);
+          slot[i] = prm.tail_slot0 + static_cast<unsigned>(j - n_listed);
         }
       }
-      ts.ok |= (ok ? 1u : 0u) << i;
     }
-    return ts;
-  };
-  auto issue_copies = [&](const TileSlots& ts, int stage) {
-    uint8_t* sk = smem + stage * kDecStageBytes;
-    uint8_t* sv = sk + kDecTile * kHeadDim * 2;
-    const int c = tid & 15;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int tl = (tid >> 4) + 8 * i;
-      const bool ok = (ts.ok >> i) & 1u;
-      if (c == 0) s_skip[stage][tl] = ok ? 0 : 1;
-      if (ok) {
+      if (c == 0) s_skip[stage][tl] = ok[i] ? 0 : 1;
+      if (ok[i]) {
         unsigned page, e;
         if (prm.ps_shift >= 0) {
-          page = ts.slot[i] >> prm.ps_shift;
-          e = ts.slot[i] & (ps - 1);
+          page = slot[i] >> prm.ps_shift;
+          e = slot[i] & (ps - 1);
         } else {
-          page = ts.slot[i] / ps;
-          e = ts.slot[i] - page * ps;
+          page = slot[i] / ps;
+          e = slot[i] - page * ps;
         }
         const int64_t row = static_cast<int64_t>(page) * (2 * ps) + e;
         const T* kp = kvp + (row * H + head) * kHeadDim + c * 8;
@@ -163,11 +151,7 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
   // the index list is the preceding kernel's output
   grid_dependency_wait();
   grid_launch_dependents();
-  ADAMAS_STAMP(0, 0, tid == 0 && blockIdx.y == 0);
-  TileSlots next_slots = load_slots(0);
-  issue_copies(next_slots, 0);
-  if (n_tiles > 1) next_slots = load_slots(1);
-  ADAMAS_STAMP(0, 1, tid == 0 && blockIdx.y == 0);
+  issue_tile(0, 0);
 
   float m_run = -INFINITY, l_run = 0.f;
   float o_acc[8];
@@ -179,14 +163,12 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
   for (int tile = 0; tile < n_tiles; ++tile) {
     const int stage = tile & 1;
     if (tile + 1 < n_tiles) {
-      issue_copies(next_slots, stage ^ 1);
-      if (tile + 2 < n_tiles) next_slots = load_slots(tile + 2);   // in flight during this tile's math
+      issue_tile(tile + 1, stage ^ 1);
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
     __syncthreads();
-    ADAMAS_STAMP(0, 2 + 4 * tile, tid == 0 && blockIdx.y == 0 && tile < 3);
     const uint8_t* sk = smem + stage * kDecStageBytes;
     const uint8_t* sv = sk + kDecTile * kHeadDim * 2;
     const int tile_tokens = min(kDecTile, tok_end - (tok_begin + tile * kDecTile));
@@ -213,7 +195,6 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
     for (int o = 16; o > 0; o >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, o));
     if (lane == 0) s_red[warp] = wmax;
     __syncthreads();
-    ADAMAS_STAMP(0, 3 + 4 * tile, tid == 0 && blockIdx.y == 0 && tile < 3);
 
     const float m_tile = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
     const float m_new = fmaxf(m_run, m_tile);
@@ -229,7 +210,6 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
     for (int o = 16; o > 0; o >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
     if (lane == 0) s_sum[warp] = psum;
     __syncthreads();
-    ADAMAS_STAMP(0, 4 + 4 * tile, tid == 0 && blockIdx.y == 0 && tile < 3);
     l_run = l_run * rescale + (s_sum[0] + s_sum[1]);
     m_run = m_new;
 
@@ -249,9 +229,7 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
       }
     }
     __syncthreads();  // the stage is free for the tile after next; s_logit / s_p reusable
-    ADAMAS_STAMP(0, 5 + 4 * tile, tid == 0 && blockIdx.y == 0 && tile < 3);
   }
-  ADAMAS_STAMP(0, 14, tid == 0 && blockIdx.y == 0);
 
   // ---- reduce the 8 token groups ----------------------------------------------------------------
 #pragma unroll
