@@ -527,6 +527,45 @@ def test_two_launch_step_equals_three_launch_step(dtype, rope, L, ps, budget, H)
     assert _lib.device_error(clear=False) == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("L,ps,H", [(500, 16, 32), (1300, 1, 16), (4100, 16, 64)])
+def test_append_estimate_equals_separate_operators(dtype, L, ps, H):
+    """append_estimate (one launch) leaves the same bits as append_kv_cache_decode_fused followed by
+    estimate_attn_score: the new token's K/V rows and code, the query code and the integer distances."""
+    _, K, U = _mods()
+    results = []
+    for one_launch in (False, True):
+        st = State(L - 1, H, ps, dtype, seed=L + 3, fused=True, max_seq_len=L + ps)
+        c = st.c
+        c.end_forward()
+        q = _randn((1, H, 128), 41 + L, dtype).to(DEV)
+        k_new = _randn((1, H, 128), 42 + L, dtype).to(DEV)
+        v_new = _randn((1, H, 128), 43 + L, dtype).to(DEV)
+        c.prepare_hadamard(1)
+        c.begin_forward(1)
+        n = c.hadamard_cache.seqlen - 1
+        dist = c.distance_scratch(n)
+        dist.fill_(-1)
+        q_code = torch.zeros(1, H, 16, dtype=dtype, device=DEV)
+        if one_launch:
+            K.append_estimate(q, k_new, v_new, q_code, c.kv_cache.buf_layer(0), c.kv_indices_with_last,
+                              c.kv_cache.last_page_len, c.hadamard_cache.buf_layer(0), c.hadamard_indices,
+                              c.hadamard_cache.last_page_len, dist)
+        else:
+            U.append_qkv_fused(q, k_new, v_new, c, 0, out=q_code)
+            K.estimate_attn_score(q_code, dist, c.hadamard_cache.buf_layer(0), c.hadamard_indices, None,
+                                  c.hadamard_cache.last_page_len, c.hadamard_last_page_idx, c.layout)
+        torch.cuda.synchronize()
+        kv_rows = c.kv_cache.buf_layer(0)[c.kv_cache.indicies[-1], :, (L - 1) % ps].clone()
+        code = c.hadamard_cache.buf_layer(0)[c.hadamard_cache.indicies[-1], 0, (L - 1) % ps].clone()
+        results.append((kv_rows, code, q_code.clone(), dist[:, :n].clone()))
+    for name, a, b in zip(["kv rows", "key code", "query code", "distances"], *results):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16)), name
+    # and the distances are the oracle's
+    r = ref.decode_step(q[0].cpu(), torch.cat([st.k, k_new.cpu()], 0), torch.cat([st.v, v_new.cpu()], 0), 2)
+    np.testing.assert_array_equal(results[1][3].cpu().numpy().astype(np.int32), r["dist"])
+
+
 @pytest.mark.parametrize("blocks", [1, 2, 4])
 @pytest.mark.parametrize("L,budget,H", [(32768, 1024, 8), (6000, 640, 32)])
 def test_decode_step_with_smaller_clusters(blocks, L, budget, H):
