@@ -390,6 +390,12 @@ def set_max_cluster(blocks: int) -> None:
     _lib.check(lib.adamas_set_max_cluster(int(blocks)), "set_max_cluster")
 
 
+def set_estimate_blocks_per_sm(blocks: int) -> None:
+    """1 or 2 (default) resident blocks of the estimate kernel per SM; 1 leaves room for kernels of other
+    sequences running on other streams."""
+    _lib.check(lib.adamas_set_estimate_blocks_per_sm(int(blocks)), "set_estimate_blocks_per_sm")
+
+
 def set_fused_append(enable: bool) -> None:
     """decode_step with the append folded into the estimate launch (two launches, the default for 16,
     32 or 64 heads) or as three launches; the results are identical."""

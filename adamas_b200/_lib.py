@@ -57,6 +57,7 @@ SIGNATURES = {
     "adamas_set_pdl": [_I],
     "adamas_set_max_cluster": [_I],
     "adamas_set_fused_append": [_I],
+    "adamas_set_estimate_blocks_per_sm": [_I],
 }
 
 for _name, _args in SIGNATURES.items():

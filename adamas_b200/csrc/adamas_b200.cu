@@ -188,6 +188,18 @@ bool fused_append_enabled() {
   return g_fused_append != 0;
 }
 
+// Upper bound on the estimate kernel's resident blocks per SM (adamas_set_estimate_blocks_per_sm /
+// ADAMAS_EST_BLOCKS_PER_SM): 2 by default, 1 leaves half of every SM to kernels of other streams.
+int g_est_blocks_per_sm = -1;
+int est_blocks_per_sm() {
+  if (g_est_blocks_per_sm < 0) {
+    const char* e = std::getenv("ADAMAS_EST_BLOCKS_PER_SM");
+    const int v = e ? std::atoi(e) : 2;
+    g_est_blocks_per_sm = (v == 1) ? 1 : 2;
+  }
+  return g_est_blocks_per_sm;
+}
+
 // Upper bound on the cluster size of select_attend (adamas_set_max_cluster / ADAMAS_MAX_CLUSTER).
 int g_max_cluster = -1;
 int max_cluster() {
@@ -258,6 +270,12 @@ int adamas_set_pdl(int enable) {
 
 int adamas_set_fused_append(int enable) {
   g_fused_append = enable ? 1 : 0;
+  return ADAMAS_OK;
+}
+
+int adamas_set_estimate_blocks_per_sm(int blocks) {
+  ADAMAS_REQUIRE(blocks == 1 || blocks == 2, "blocks per SM must be 1 or 2 (got %d)", blocks);
+  g_est_blocks_per_sm = blocks;
   return ADAMAS_OK;
 }
 
@@ -549,7 +567,7 @@ int adamas_estimate(const void* q_code, const void* code_data, const int32_t* co
                       (in_regs ? 0 : static_cast<size_t>(2 * num_heads) * sizeof(QPlanes));
   ADAMAS_REQUIRE(smem <= static_cast<size_t>(di->max_smem_optin - 1024),
                  "num_heads (%d) too large for the estimate kernel", num_heads);
-  const int per_sm = (smem + 1024) * 2 <= static_cast<size_t>(di->max_smem_optin) ? 2 : 1;
+  const int per_sm = std::min(est_blocks_per_sm(), (smem + 1024) * 2 <= static_cast<size_t>(di->max_smem_optin) ? 2 : 1);
   const unsigned blocks = static_cast<unsigned>(std::min(num_tiles, di->num_sms * per_sm));
   EstimateParams prm;
   prm.codes = static_cast<const uint4*>(code_data);
@@ -1151,7 +1169,8 @@ static int estimate_append_launch(const void* q, const void* k, const void* v, v
   const size_t smem = static_cast<size_t>(kEstStages) * kEstTile * (2 * num_heads + 1) * 16;
   ADAMAS_REQUIRE(smem <= static_cast<size_t>(di->max_smem_optin - 1024 - kEstAppendStatic),
                  "num_heads (%d) too large", num_heads);
-  const int per_sm = (smem + 1024 + kEstAppendStatic) * 2 <= static_cast<size_t>(di->max_smem_optin) ? 2 : 1;
+  const int per_sm = std::min(est_blocks_per_sm(),
+                              (smem + 1024 + kEstAppendStatic) * 2 <= static_cast<size_t>(di->max_smem_optin) ? 2 : 1);
   const unsigned blocks = static_cast<unsigned>(std::min(num_tiles, di->num_sms * per_sm));
   EstimateParams prm;
   prm.codes = static_cast<const uint4*>(code_data);

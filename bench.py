@@ -505,13 +505,17 @@ def run_sweep(args):
                 if args.sweep_cluster:
                     cluster = args.sweep_cluster
                 K.set_max_cluster(cluster)
+                # several sequences: one estimate block per SM, so that other sequences' select+attend
+                # blocks find room while an estimate streams
+                K.set_estimate_blocks_per_sm(args.sweep_est_blocks or (1 if batch > 1 else 2))
                 wls = [Workload(a, dev, seed_offset=i) for i in range(batch)]
                 for wl in wls:
                     wl.step_eager()
                 torch.cuda.synchronize()
                 by = stage_bytes(ctx, args.heads, budget, batch)
                 out = {"sweep": True, "batch": batch, "ctx": ctx, "budget": budget, "heads": args.heads,
-                       "page_size": args.page_size, "layers_rotated": layers, "max_cluster": cluster}
+                       "page_size": args.page_size, "layers_rotated": layers, "max_cluster": cluster,
+                       "est_blocks_per_sm": args.sweep_est_blocks or (1 if batch > 1 else 2)}
                 for stage in ("estimate", "topk", "attention", "select_attend", "append", "step"):
                     if stage in ("select_attend", "step"):
                         a.unfused = False      # the estimate must have left integer distances
@@ -692,6 +696,8 @@ def main():
     ap.add_argument("--sweep-budget", dest="sweep_budget", type=int, nargs="+", default=[64, 128, 512, 2048])
     ap.add_argument("--sweep-cluster", dest="sweep_cluster", type=int, default=0,
                     help="force the select_attend cluster bound (default: 8 for one sequence, else 4)")
+    ap.add_argument("--sweep-est-blocks", dest="sweep_est_blocks", type=int, default=0,
+                    help="force the estimate's blocks per SM in the sweep (default: 2 for one sequence, else 1)")
     ap.add_argument("--sweep-batch", dest="sweep_batch", type=int, nargs="+", default=[1],
                     help="independent sequences per step, one stream each inside the graph")
     ap.add_argument("--seq-sharded", dest="seq_sharded", action="store_true",

@@ -70,6 +70,13 @@ int adamas_set_pdl(int enable);
  * it).  Results are identical.  No counterpart in the reference. */
 int adamas_set_fused_append(int enable);
 
+/* How many blocks of the estimate kernel may be resident per SM: 2 (default; fastest for one sequence)
+ * or 1, which leaves half of every SM's registers and shared memory to kernels running on other
+ * streams, so that the select+attend of one sequence overlaps the estimate of another (a batch of
+ * independent sequences, one stream each).  ADAMAS_EST_BLOCKS_PER_SM in the environment sets the initial
+ * value.  No counterpart in the reference (batch 1 only). */
+int adamas_set_estimate_blocks_per_sm(int blocks);
+
 /* Upper bound (1, 2, 4 or 8; default 8, or ADAMAS_MAX_CLUSTER in the environment) on the number of
  * thread blocks that share one head in adamas_select_attend / adamas_decode_step.  Eight blocks per
  * head give the shortest single call; a smaller cluster takes longer per call but leaves room on the
