@@ -42,6 +42,9 @@ def test_argument_validation_without_gpu():
     assert lib.adamas_set_max_cluster(3) == _lib.ERR_INVALID and "power of two" in _lib.last_error()
     assert lib.adamas_set_max_cluster(16) == _lib.ERR_INVALID
     assert lib.adamas_set_max_cluster(8) == 0
+    assert lib.adamas_set_estimate_blocks_per_sm(3) == _lib.ERR_INVALID and "1 or 2" in _lib.last_error()
+    assert lib.adamas_set_estimate_blocks_per_sm(2) == 0
+    assert lib.adamas_set_fused_append(1) == 0
 
 
 def test_ops_reject_cpu_tensors():
