@@ -739,8 +739,8 @@ struct SplitPlan {
   int num_splits;
 };
 
-// One wave of resident blocks: up to 4 single-tile blocks per SM (32 KB of shared memory each) or 3
-// double-buffered multi-tile blocks (64 KB each), over all heads; never more splits than tiles.
+// One wave of resident blocks: up to 4 single-tile blocks per SM (34 KB of shared memory each) or 3
+// double-buffered multi-tile blocks (68 KB each), over all heads; never more splits than tiles.
 SplitPlan plan_splits(int64_t n_tokens, int num_heads, int num_sms) {
   const int64_t tiles = (n_tokens + kDecTile - 1) / kDecTile;
   const int64_t cap1 = std::max<int64_t>(1, (static_cast<int64_t>(num_sms) * 4 + num_heads - 1) / num_heads);

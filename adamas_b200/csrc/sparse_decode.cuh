@@ -3,10 +3,11 @@
 //
 // grid = (num_splits, H).  A thread block walks its share of the head's token list in tiles of
 // kDecTile tokens.  For each tile it resolves the token slots from the index list, gathers the
-// 256-byte K and V rows into shared memory with 16-byte cp.async (double buffered across tiles),
-// computes the logits with two threads per token, runs an online softmax in base 2, and accumulates
-// P.V with one thread per (token group, 8-dim chunk).  Rows are stored with an XOR swizzle of the
-// 16-byte chunk position so that both access patterns are bank-conflict free.
+// 256-byte K and V rows into shared memory with one bulk (TMA) copy per row (double buffered across
+// tiles, one mbarrier per stage counting the bytes; waits are bounded), computes the logits with two
+// threads per token, runs an online softmax in base 2, and accumulates P.V with one thread per (token
+// group, 8-dim chunk).  Rows are padded to 272 bytes so that both access patterns are bank-conflict
+// free.
 //
 // With more than one split per head each block writes an unnormalised partial (o, m, l) to global
 // scratch, and the block that arrives last at the head's counter merges the partials and writes the
@@ -18,7 +19,9 @@ namespace adamas {
 
 constexpr int kDecTile = 64;       // tokens per tile
 constexpr int kDecThreads = 128;
-constexpr int kDecStageBytes = 2 * kDecTile * kHeadDim * 2;  // K + V rows of one tile (32 KB)
+constexpr int kDecRowBytes = kHeadDim * 2 + 16;             // a row plus 16 bytes of padding
+constexpr int kDecStageBytes = 2 * kDecTile * kDecRowBytes;  // K + V rows of one tile (34 KB)
+constexpr unsigned kErrDecodeTimeout = 2u;
 
 struct DecodeParams {
   const void* q;          // [H, 128]
@@ -53,6 +56,7 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
   __shared__ float s_sum[4];
   __shared__ float s_o[8][kHeadDim];
   __shared__ unsigned s_last;
+  __shared__ __align__(8) uint64_t full_bar[2];
 
   const int split = blockIdx.x;
   const int head = blockIdx.y;
@@ -71,65 +75,63 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
   const int64_t v_delta = static_cast<int64_t>(prm.page_size) * H * kHeadDim;
 
   // ---- gather one tile into a stage --------------------------------------------------------------
-  // thread -> chunk c = tid % 16 of tokens tl = tid / 16 + 8 * i.  Slots are < 2^31 (checked on the
-  // host), so the index arithmetic is 32-bit; only the final element offset is 64-bit.
+  // thread -> (token tl = tid / 2, K or V row): one 256-byte bulk copy each.  Every thread arrives at
+  // the stage's barrier once, with the bytes it has asked for (none for a skipped or absent token).
+  // Slots are < 2^31 (checked on the host), so the index arithmetic is 32-bit; only the final element
+  // offset is 64-bit.
+  if (tid == 0) {
+    mbar_init(&full_bar[0], kDecThreads);
+    mbar_init(&full_bar[1], kDecThreads);
+    mbar_fence_init();
+  }
+  __syncthreads();
   auto issue_tile = [&](int tile, int stage) {
     uint8_t* sk = smem + stage * kDecStageBytes;
-    uint8_t* sv = sk + kDecTile * kHeadDim * 2;
-    const int c = tid & 15;
-    const int t0 = tok_begin + tile * kDecTile;
+    uint8_t* sv = sk + kDecTile * kDecRowBytes;
+    const int tl = tid >> 1;
+    const int is_v = tid & 1;
+    const int j = tok_begin + tile * kDecTile + tl;
     const unsigned ps = static_cast<unsigned>(prm.page_size);
-    unsigned slot[8];
-    bool ok[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int tl = (tid >> 4) + 8 * i;
-      const int j = t0 + tl;
-      ok[i] = j < tok_end;
-      slot[i] = 0;
-      if (ok[i]) {
-        if (j < n_listed) {
-          if (prm.idx_unit == 1) {
-            const int32_t id = __ldg(idx_row + j);
-            ok[i] = id >= 0;   // a negative entry is a hole in the list: the token is skipped
-            slot[i] = static_cast<unsigned>(id);
-          } else {  // page-granular list: idx_unit == page_size
-            unsigned item, off;
-            if (prm.ps_shift >= 0) {
-              item = static_cast<unsigned>(j) >> prm.ps_shift;
-              off = static_cast<unsigned>(j) & (ps - 1);
-            } else {
-              item = static_cast<unsigned>(j) / ps;
-              off = static_cast<unsigned>(j) - item * ps;
-            }
-            slot[i] = static_cast<unsigned>(__ldg(idx_row + item)) * ps + off;
+    bool ok = j < tok_end;
+    unsigned slot = 0;
+    if (ok) {
+      if (j < n_listed) {
+        if (prm.idx_unit == 1) {
+          const int32_t id = __ldg(idx_row + j);
+          ok = id >= 0;   // a negative entry is a hole in the list: the token is skipped
+          slot = static_cast<unsigned>(id);
+        } else {  // page-granular list: idx_unit == page_size
+          unsigned item, off;
+          if (prm.ps_shift >= 0) {
+            item = static_cast<unsigned>(j) >> prm.ps_shift;
+            off = static_cast<unsigned>(j) & (ps - 1);
+          } else {
+            item = static_cast<unsigned>(j) / ps;
+            off = static_cast<unsigned>(j) - item * ps;
           }
-        } else {
-          slot[i] = prm.tail_slot0 + static_cast<unsigned>(j - n_listed);
+          slot = static_cast<unsigned>(__ldg(idx_row + item)) * ps + off;
         }
+      } else {
+        slot = prm.tail_slot0 + static_cast<unsigned>(j - n_listed);
       }
     }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int tl = (tid >> 4) + 8 * i;
-      if (c == 0) s_skip[stage][tl] = ok[i] ? 0 : 1;
-      if (ok[i]) {
-        unsigned page, e;
-        if (prm.ps_shift >= 0) {
-          page = slot[i] >> prm.ps_shift;
-          e = slot[i] & (ps - 1);
-        } else {
-          page = slot[i] / ps;
-          e = slot[i] - page * ps;
-        }
-        const int64_t row = static_cast<int64_t>(page) * (2 * ps) + e;
-        const T* kp = kvp + (row * H + head) * kHeadDim + c * 8;
-        const int phys = c ^ (tl & 3);
-        cp_async_16(sk + tl * 256 + phys * 16, kp);
-        cp_async_16(sv + tl * 256 + phys * 16, kp + v_delta);
+    if (is_v == 0) s_skip[stage][tl] = ok ? 0 : 1;
+    if (ok) {
+      unsigned page, e;
+      if (prm.ps_shift >= 0) {
+        page = slot >> prm.ps_shift;
+        e = slot & (ps - 1);
+      } else {
+        page = slot / ps;
+        e = slot - page * ps;
       }
+      const int64_t row = static_cast<int64_t>(page) * (2 * ps) + e;
+      const T* src = kvp + (row * H + head) * kHeadDim + (is_v ? v_delta : 0);
+      mbar_arrive_expect_tx(&full_bar[stage], kHeadDim * 2);
+      bulk_copy_g2s((is_v ? sv : sk) + tl * kDecRowBytes, src, kHeadDim * 2, &full_bar[stage]);
+    } else {
+      mbar_arrive(&full_bar[stage]);
     }
-    cp_async_commit();
   };
 
   // ---- query: 64 dims per thread, in the order the thread walks its chunks ---------------------
@@ -162,15 +164,12 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
 
   for (int tile = 0; tile < n_tiles; ++tile) {
     const int stage = tile & 1;
-    if (tile + 1 < n_tiles) {
-      issue_tile(tile + 1, stage ^ 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
+    if (tile + 1 < n_tiles) issue_tile(tile + 1, stage ^ 1);
+    // bounded wait for this tile's bytes (a stage is used every other tile: its phase parity follows)
+    if (!mbar_wait_bounded(&full_bar[stage], (tile >> 1) & 1, 1u << 22)) atomicOr(&g_adamas_error, kErrDecodeTimeout);
+    __syncthreads();   // s_skip of this stage is visible to all threads
     const uint8_t* sk = smem + stage * kDecStageBytes;
-    const uint8_t* sv = sk + kDecTile * kHeadDim * 2;
+    const uint8_t* sv = sk + kDecTile * kDecRowBytes;
     const int tile_tokens = min(kDecTile, tok_end - (tok_begin + tile * kDecTile));
 
     // logits
@@ -180,9 +179,8 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int lc = half * 8 + (i ^ (half * 4));
-        const int phys = lc ^ (qk_tl & 3);
         float kf[8];
-        unpack8<T>(*reinterpret_cast<const uint4*>(sk + qk_tl * 256 + phys * 16), kf);
+        unpack8<T>(*reinterpret_cast<const uint4*>(sk + qk_tl * kDecRowBytes + lc * 16), kf);
 #pragma unroll
         for (int d = 0; d < 8; ++d) acc = fmaf(qreg[i][d], kf[d], acc);
       }
@@ -221,9 +219,8 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
       const int tl = pv_g * 8 + i;
       const float p = s_p[tl];
       if (p != 0.f) {   // masked or absent tokens: their rows in shared memory are stale
-        const int phys = pv_c ^ (tl & 3);
         float vf[8];
-        unpack8<T>(*reinterpret_cast<const uint4*>(sv + tl * 256 + phys * 16), vf);
+        unpack8<T>(*reinterpret_cast<const uint4*>(sv + tl * kDecRowBytes + pv_c * 16), vf);
 #pragma unroll
         for (int d = 0; d < 8; ++d) o_acc[d] = fmaf(p, vf[d], o_acc[d]);
       }
