@@ -140,6 +140,8 @@ __device__ __forceinline__ uint4 pack8(const float (&x)[8]) {
 // bounded wait sets a bit here and finishes normally.
 __device__ unsigned g_adamas_error = 0;
 constexpr unsigned kErrEstimateTimeout = 1u;
+constexpr unsigned kErrDecodeTimeout = 2u;
+constexpr unsigned kErrGatherTimeout = 4u;
 
 // ---- optional phase timing (compile with -DADAMAS_PHASE_TIMING; off in the product build) --------
 // One thread per block stamps the global nanosecond timer at phase boundaries into a fixed table that

@@ -19,9 +19,11 @@
 //   2     ordered compaction of the block's winners into a shared-memory list (and, optionally, to
 //         the global index list at the right offset);
 //   3     attention over the list in tiles of `tile_cap` (64, 128 or 192) tokens, chosen by the host so
-//         that a block's winners almost always fit one tile: K/V rows gathered with 16-byte cp.async
-//         into XOR-swizzled shared memory, four threads per token for q.K, online softmax in base
-//         2, one thread per (group of tile_cap/32 tokens, 8-dim chunk) for P.V;
+//         that a block's winners almost always fit one tile: K/V rows gathered with one 256-byte
+//         bulk (TMA) copy per row, counted by an mbarrier (bounded wait), four threads per token
+//         for q.K (odd and even tokens walk their chunks in different orders, which keeps the
+//         un-padded rows free of bank conflicts), online softmax in base 2, one thread per (group
+//         of tile_cap/32 tokens, 8-dim chunk) for P.V;
 //   4     the partial (o, m, l) is stored into slot `cr` of rank 0's shared memory; cluster barrier;
 //         rank 0 merges the CL partials and writes the head's output.
 // Only two cluster barriers sit on the critical path.  The histogram tables and the per-warp partial
@@ -99,6 +101,7 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   cg::cluster_group cluster = cg::this_cluster();
   extern __shared__ __align__(16) uint8_t sa_smem[];
   __shared__ __align__(16) SaShared sh;
+  __shared__ __align__(8) uint64_t gather_bar;
 
   const unsigned CL = cluster.num_blocks();
   const unsigned cr = cluster.block_rank();
@@ -121,6 +124,10 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   ADAMAS_TRACE(1, p.trace_tag, 0, tid == 0);
   ADAMAS_CHAIN(2, 0, false, blockIdx.x == 0 && tid == 0);
   if (tid < kSaBins) h_local[tid] = 0;
+  if (tid == 0) {
+    mbar_init(&gather_bar, NT);
+    mbar_fence_init();
+  }
   cluster_arrive_release();   // start-up barrier, first half: this block is running
   __syncthreads();
   grid_dependency_wait();
@@ -129,8 +136,10 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   ADAMAS_CHAIN(2, 1, false, blockIdx.x == 0 && tid == 0);
 
   // q.K mapping: four threads per token (tl = tid / 4, quarter = tid % 4); step i of a thread reads
-  // logical chunk 4*quarter + ((i + quarter) & 3), which keeps the 8 lanes of a quarter-warp on 8
-  // different 16-byte bank groups.  The query chunks stay packed in registers.  Short rows fetch them
+  // chunk 4*quarter + ((i + quarter + tl) & 3).  A quarter-warp covers an even and an odd token; the
+  // rows are 256 bytes apart (the same banks), and with this order the two tokens' four chunks fall
+  // on complementary 16-byte bank groups, so the 8 lanes hit 8 different ones.  The query chunks stay
+  // packed in registers, in the thread's own order.  Short rows fetch them
   // now (the latency hides behind the selection); long rows hold 16 to 64 distances per thread through
   // the selection phases and fetch the query after them, so that it does not push distances out of the
   // registers.
@@ -140,7 +149,7 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   auto load_query = [&]() {
     const T* qp = static_cast<const T*>(p.q) + static_cast<int64_t>(head) * kHeadDim;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) qpk[i] = ld_16(qp + (4 * quarter + ((i + quarter) & 3)) * 8);
+    for (int i = 0; i < 4; ++i) qpk[i] = ld_16(qp + (4 * quarter + ((i + quarter + qk_tl) & 3)) * 8);
   };
   if (ITEMS == 1) load_query();
 
@@ -342,35 +351,37 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   const int pv_c = tid & 15;   // 8-dim chunk
   const unsigned ps = static_cast<unsigned>(p.page_size);
 
+  // The tile memory held the histogram tables, written through the generic proxy (by this block and
+  // by its peers); the bulk copies write it through the async proxy.
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  unsigned gather_parity = 0;
   for (int t0 = 0; t0 < n_loc; t0 += cap) {
     const int tile_tokens = min(cap, n_loc - t0);
-    // gather: thread -> chunk c = tid % 16 of tokens tl = tid / 16 + kGroups * i
+    // gather: thread -> (token tl = tid / 2, K or V row), one 256-byte bulk copy each; every thread
+    // arrives at the barrier once, with the bytes it asked for
     {
-      const int c = tid & 15;
-#pragma unroll
-      for (int i = 0; i < kSaMaxTpg; ++i) {
-        const int tl = (tid >> 4) + kGroups * i;
-        if (tl < tile_tokens) {
-          const unsigned slot = static_cast<unsigned>(s_list[t0 + tl]);
-          unsigned page, e;
-          if (p.ps_shift >= 0) {
-            page = slot >> p.ps_shift;
-            e = slot & (ps - 1);
-          } else {
-            page = slot / ps;
-            e = slot - page * ps;
-          }
-          const int64_t row = static_cast<int64_t>(page) * (2 * ps) + e;
-          const T* kp = kvp + (row * H + head) * kHeadDim + c * 8;
-          const int phys = c ^ (tl & 3);
-          cp_async_16(sk + tl * 256 + phys * 16, kp);
-          cp_async_16(sv + tl * 256 + phys * 16, kp + v_delta);
+      const int tl = tid >> 1;
+      const int is_v = tid & 1;
+      if (tl < tile_tokens) {
+        const unsigned slot = static_cast<unsigned>(s_list[t0 + tl]);
+        unsigned page, e;
+        if (p.ps_shift >= 0) {
+          page = slot >> p.ps_shift;
+          e = slot & (ps - 1);
+        } else {
+          page = slot / ps;
+          e = slot - page * ps;
         }
+        const int64_t row = static_cast<int64_t>(page) * (2 * ps) + e;
+        const T* src = kvp + (row * H + head) * kHeadDim + (is_v ? v_delta : 0);
+        mbar_arrive_expect_tx(&gather_bar, kHeadDim * 2);
+        bulk_copy_g2s((is_v ? sv : sk) + tl * 256, src, kHeadDim * 2, &gather_bar);
+      } else {
+        mbar_arrive(&gather_bar);
       }
-      cp_async_commit();
-      cp_async_wait<0>();
+      if (!mbar_wait_bounded(&gather_bar, gather_parity, 1u << 22)) atomicOr(&g_adamas_error, kErrGatherTimeout);
+      gather_parity ^= 1u;
     }
-    __syncthreads();
     ADAMAS_STAMP(1, 6, tid == 0 && t0 == 0);
     ADAMAS_STAMP(1, 10, tid == 0 && t0 != 0);
 
@@ -385,10 +396,9 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
       if (live) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int lc = 4 * quarter + ((i + quarter) & 3);
-          const int phys = lc ^ (tl & 3);
+          const int lc = 4 * quarter + ((i + quarter + qk_tl) & 3);   // tl and qk_tl have the same parity
           float kf[8], qf[8];
-          unpack8<T>(*reinterpret_cast<const uint4*>(sk + tl * 256 + phys * 16), kf);
+          unpack8<T>(*reinterpret_cast<const uint4*>(sk + tl * 256 + lc * 16), kf);
           unpack8<T>(qpk[i], qf);
 #pragma unroll
           for (int d = 0; d < 8; ++d) acc = fmaf(qf[d], kf[d], acc);
@@ -439,9 +449,8 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
         const int tl = pv_g * tpg + i;
         const float pr = sh.s_p[tl];
         if (pr != 0.f) {
-          const int phys = pv_c ^ (tl & 3);
           float vf[8];
-          unpack8<T>(*reinterpret_cast<const uint4*>(sv + tl * 256 + phys * 16), vf);
+          unpack8<T>(*reinterpret_cast<const uint4*>(sv + tl * 256 + pv_c * 16), vf);
 #pragma unroll
           for (int d = 0; d < 8; ++d) o_acc[d] = fmaf(pr, vf[d], o_acc[d]);
         }

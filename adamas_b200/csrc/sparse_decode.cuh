@@ -21,7 +21,6 @@ constexpr int kDecTile = 64;       // tokens per tile
 constexpr int kDecThreads = 128;
 constexpr int kDecRowBytes = kHeadDim * 2 + 16;             // a row plus 16 bytes of padding
 constexpr int kDecStageBytes = 2 * kDecTile * kDecRowBytes;  // K + V rows of one tile (34 KB)
-constexpr unsigned kErrDecodeTimeout = 2u;
 
 struct DecodeParams {
   const void* q;          // [H, 128]

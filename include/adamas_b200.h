@@ -53,7 +53,7 @@ const char* adamas_last_error(void);
 
 /* Reads (and optionally clears) the current device's error flags.  Kernels never spin without a
  * limit: one that gives up on a wait (bit 0: the estimate kernel's copy pipeline; bit 1: the decode
- * kernel's) sets a flag here and
+ * kernel's; bit 2: the gather of select+attend) sets a flag here and
  * finishes, leaving wrong results behind.  Synchronises with the device.  No counterpart in the
  * reference, whose kernels have no waits of this kind. */
 int adamas_device_error(unsigned* flags, int clear);
