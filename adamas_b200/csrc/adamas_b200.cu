@@ -545,7 +545,7 @@ int adamas_estimate(const void* q_code, const void* code_data, const int32_t* co
   ADAMAS_REQUIRE(exclude_last == 0 || exclude_last == 1, "exclude_last must be 0 or 1");
   const int64_t n64 =
       static_cast<int64_t>(code_num_pages - 1) * page_size + code_last_page_len - exclude_last;
-  ADAMAS_REQUIRE(n64 < (int64_t(1) << 31) - kEstTile * kEstConsumerWarps, "sequence too long");
+  ADAMAS_REQUIRE(n64 < (int64_t(1) << 31) - kEstTile * kEstConsumerWarps * 2, "sequence too long");
   const int n = static_cast<int>(n64);
   if (n == 0) return ADAMAS_OK;
   ADAMAS_REQUIRE(q_code && code_data && code_page_table && out, "null pointer");
@@ -556,11 +556,64 @@ int adamas_estimate(const void* q_code, const void* code_data, const int32_t* co
                  "q_code and code_data must be 16-byte aligned");
   const DeviceInfo* di = nullptr;
   if (int rc = get_device_info(&di)) return rc;
+  cudaStream_t st = to_stream(stream);
+  if (num_heads <= 16 && 32 % (2 * num_heads) == 0 && page_size * num_heads * 32 >= 512) {
+    // few heads (a head-sharded model): whole pages per copy, one chunk per lane
+    const int page_bytes = page_size * num_heads * 32;
+    const int ppt = std::max(1, std::min(32, 32768 / page_bytes));
+    const int pages = (n + page_size - 1) / page_size;
+    const int num_tiles = (pages + ppt - 1) / ppt;
+    // spare bytes: a partial last unit reads up to 8 tokens past the valid ones
+    const size_t smem = static_cast<size_t>(kEstStages) * ppt * page_bytes + 4096 + 512;
+    constexpr int kPagesStatic = 8448;   // static shared memory of estimate_pages_kernel, rounded up
+    ADAMAS_REQUIRE(smem <= static_cast<size_t>(di->max_smem_optin - 1024 - kPagesStatic),
+                   "page too large for the estimate kernel");
+    const int per_sm = std::min(est_blocks_per_sm(),
+                                (smem + 1024 + kPagesStatic) * 2 <= static_cast<size_t>(di->max_smem_optin) ? 2 : 1);
+    const unsigned blocks = static_cast<unsigned>(std::min(num_tiles, di->num_sms * per_sm));
+    EstimatePagesParams pp;
+    pp.codes = static_cast<const uint4*>(code_data);
+    pp.page_table = code_page_table;
+    pp.q_code = static_cast<const uint4*>(q_code);
+    pp.out = out;
+    pp.out_stride = out_stride;
+    pp.n_tokens = n;
+    pp.H = num_heads;
+    pp.page_size = page_size;
+    pp.pages_per_tile = ppt;
+    pp.num_tiles = num_tiles;
+    pp.stage_out = num_heads >= 16 ? 1 : 0;
+#define LAUNCH_ESTP(M, OT)                                                                              \
+  do {                                                                                                  \
+    static bool configured[64] = {};                                                                    \
+    int dev = 0;                                                                                        \
+    ADAMAS_CUDA(cudaGetDevice(&dev));                                                                   \
+    {                                                                                                   \
+      std::lock_guard<std::mutex> lock(g_init_mutex);                                                   \
+      if (!configured[dev & 63]) {                                                                      \
+        ADAMAS_CUDA(cudaFuncSetAttribute(estimate_pages_kernel<M, OT>,                                  \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, di->max_smem_optin - 1024 - kPagesStatic)); \
+        ADAMAS_CUDA(cudaFuncSetAttribute(estimate_pages_kernel<M, OT>,                                  \
+                                         cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared)); \
+        configured[dev & 63] = true;                                                                    \
+      }                                                                                                 \
+    }                                                                                                   \
+    ADAMAS_LAUNCH("estimate_pages_kernel", (estimate_pages_kernel<M, OT>), dim3(blocks), dim3(kEstThreads), smem, st, 1, pp); \
+  } while (0)
+    if (metric == ADAMAS_METRIC_L1) {
+      if (out_format == ADAMAS_VAL_F16) LAUNCH_ESTP(0, __half); else LAUNCH_ESTP(0, uint16_t);
+    } else {
+      if (out_format == ADAMAS_VAL_F16) LAUNCH_ESTP(1, __half); else LAUNCH_ESTP(1, uint16_t);
+    }
+#undef LAUNCH_ESTP
+    return check_launch("estimate_pages_kernel");
+  }
   const int hpw = (num_heads % kEstConsumerWarps == 0) ? num_heads / kEstConsumerWarps : 0;
   const bool in_regs = hpw == 1 || hpw == 2 || hpw == 4;
-  // fewer than 16 heads: a tile holds 16 / H groups of 32 tokens, so that all 16 consumer warps work
+  // fewer than 16 heads: a tile holds 32 / H groups of 32 tokens, so that all 16 consumer warps work,
+  // each on one head of two token groups
   const int groups = (num_heads < kEstConsumerWarps && kEstConsumerWarps % num_heads == 0)
-                         ? kEstConsumerWarps / num_heads : 1;
+                         ? 2 * kEstConsumerWarps / num_heads : 1;
   const int tile_span = kEstTile * groups;
   const int num_tiles = (n + tile_span - 1) / tile_span;
   const size_t smem = static_cast<size_t>(kEstStages) * tile_span * (2 * num_heads + 1) * 16 +
@@ -592,8 +645,7 @@ int adamas_estimate(const void* q_code, const void* code_data, const int32_t* co
     prm.trace_tag = (est_launches++) & 63;
   }
 #endif
-  cudaStream_t st = to_stream(stream);
-#define LAUNCH_EST(M, OT)                                                                      \
+  #define LAUNCH_EST(M, OT)                                                                      \
   do {                                                                                         \
     if (in_regs && hpw == 1)                                                                   \
       ADAMAS_LAUNCH("estimate_kernel", estimate_kernel<M, OT, 1>, dim3(blocks), dim3(kEstThreads), smem, st, 1, prm);                       \
@@ -1246,7 +1298,9 @@ int adamas_decode_step(void* q, void* k, const void* v, void* o, float* lse, voi
                  static_cast<long long>(seq_len), budget);
   ADAMAS_REQUIRE(seq_len - 1 < (int64_t(1) << 31), "sequence too long");
   ADAMAS_REQUIRE(dist_scratch && q_code, "null pointer");
-  if (fused_append_enabled() && rope_scale <= 0.f && (num_heads == 16 || num_heads == 32 || num_heads == 64) &&
+  // (16 heads: the page-copy estimate after a separate append is faster than the fused kernel's 512-byte
+  // copies per token)
+  if (fused_append_enabled() && rope_scale <= 0.f && (num_heads == 32 || num_heads == 64) &&
       head_dim == kHeadDim && (dtype == ADAMAS_F16 || dtype == ADAMAS_BF16)) {
     // two launches: the estimate with the append inside, then select + attend.  Not with RoPE: every
     // block of the estimate would repeat the rotation, which costs more than the append launch.

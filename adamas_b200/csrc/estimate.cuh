@@ -92,7 +92,8 @@ struct EstimateParams {
   int H;
   int page_size;
   int ps_shift;     // log2(page_size) or -1
-  int groups;       // token groups of 32 per tile: 1, or 16 / H for H < 16 (generic kernel only)
+  int groups;       // token groups of 32 per tile: 1, or 2 * 16 / H for H < 16 (generic kernel only): each
+                    // of the 16 consumer warps takes one head of two token groups
   int num_tiles;
   int trace_tag;    // launch number, used by builds with phase timing only
 };
@@ -184,12 +185,21 @@ __device__ __forceinline__ void est_consume(const EstimateParams& p, const EstRi
           o[static_cast<int64_t>(warp * HPW + hh) * p.out_stride] = dist_to_out<OutT>(d[hh]);
       }
     } else if (p.groups > 1) {
-      // fewer than 16 heads: H * groups == 16, warp w takes head w % H of token group w / H
+      // fewer than 16 heads: H * groups == 32; warp w takes head w % H of token groups w / H and
+      // w / H + groups / 2 (two independent distances per lane and tile, as with 32 heads)
       const int h = warp % H;
-      const int tl = (warp / H) * kEstTile + lane;
-      const uint4* grow = r.base + slot * r.stage_chunks + tl * r.row_chunks;
-      const unsigned d = chunk_distance<METRIC>(grow[2 * h], sq[2 * h]) + chunk_distance<METRIC>(grow[2 * h + 1], sq[2 * h + 1]);
-      if (tl < tile_tokens) out[static_cast<int64_t>(h) * p.out_stride + tile0 + tl] = dist_to_out<OutT>(d);
+      const QPlanes q0 = sq[2 * h], q1 = sq[2 * h + 1];
+      unsigned d[2];
+      int tl[2];
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        tl[rr] = (warp / H + rr * (p.groups >> 1)) * kEstTile + lane;
+        const uint4* grow = r.base + slot * r.stage_chunks + tl[rr] * r.row_chunks;
+        d[rr] = chunk_distance<METRIC>(grow[2 * h], q0) + chunk_distance<METRIC>(grow[2 * h + 1], q1);
+      }
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr)
+        if (tl[rr] < tile_tokens) out[static_cast<int64_t>(h) * p.out_stride + tile0 + tl[rr]] = dist_to_out<OutT>(d[rr]);
     } else {
       for (int h = warp; h < H; h += kEstConsumerWarps) {
         const unsigned d = chunk_distance<METRIC>(row[2 * h], sq[2 * h]) + chunk_distance<METRIC>(row[2 * h + 1], sq[2 * h + 1]);
@@ -379,6 +389,152 @@ __global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const Esti
     }
   }
   est_consume<0, uint16_t, HPW>(p, ring, my_tiles, lane, warp, qp, nullptr);
+}
+
+// ---- few heads per GPU: whole pages per copy, one 16-byte chunk per lane ---------------------------------
+// With H <= 16 heads (a head-sharded model) a token's codes are only H*32 bytes, and one bulk copy per
+// token leaves the producer warp issuing thousands of 128- to 512-byte copies.  A page of the code cache
+// is contiguous (page_size * H * 32 bytes), so this kernel copies whole pages and lays them out back to
+// back in shared memory.  Consumers take one 16-byte chunk per lane: 32 consecutive chunks per warp
+// step (conflict-free), lane l always holds half (l & 1) of head (l % 2H) / 2, so its query planes stay
+// in registers; the two halves of a (token, head) are joined by one shuffle.  Needs 2H | 32.  Partial
+// last units read a few chunks past the valid ones (the allocation has 512 spare bytes).
+struct EstimatePagesParams {
+  const uint4* codes;
+  const int32_t* page_table;
+  const uint4* q_code;
+  void* out;
+  int64_t out_stride;
+  int n_tokens;
+  int H;
+  int page_size;
+  int pages_per_tile;
+  int num_tiles;
+  int stage_out;    // gather the distances of 8 tokens per head in shared memory before writing them
+};
+
+template <int METRIC, typename OutT>
+__global__ void __launch_bounds__(kEstThreads, 2) estimate_pages_kernel(const EstimatePagesParams p) {
+  extern __shared__ uint4 est_smem[];
+  __shared__ __align__(8) uint64_t full_bar[kEstStages];
+  __shared__ __align__(8) uint64_t empty_bar[kEstStages];
+  __shared__ __align__(16) uint16_t s_stage[kEstConsumerWarps][16][16];   // per warp: [head][token of the unit]
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int H2 = 2 * p.H;                              // chunks per token
+  const int page_chunks = p.page_size * H2;
+  const int tile_chunks = p.pages_per_tile * page_chunks;
+  const int tile_span = p.pages_per_tile * p.page_size;   // tokens per tile
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < kEstStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], kEstConsumerWarps);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  const int my_tiles = (p.num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                       static_cast<int>(gridDim.x);
+
+  if (warp == kEstConsumerWarps) {
+    // ---- producer: one bulk copy per page of the tile (the last page of the row may be partial)
+    int slot = 0;
+    unsigned parity = 0;
+    for (int j = 0; j < my_tiles; ++j) {
+      const int tile = blockIdx.x + j * gridDim.x;
+      const int tok0 = tile * tile_span;
+      const int ntok = min(tile_span, p.n_tokens - tok0);
+      if (j >= kEstStages) {
+        if (!mbar_wait_bounded(&empty_bar[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
+      }
+      if (lane == 0) mbar_arrive_expect_tx(&full_bar[slot], static_cast<unsigned>(ntok) * H2 * 16u);
+      __syncwarp();
+      const int npages = (ntok + p.page_size - 1) / p.page_size;
+      for (int pg = lane; pg < npages; pg += 32) {
+        const int64_t phys = __ldg(p.page_table + tile * p.pages_per_tile + pg);
+        const int toks = min(p.page_size, ntok - pg * p.page_size);
+        bulk_copy_g2s(est_smem + slot * tile_chunks + pg * page_chunks, p.codes + phys * page_chunks,
+                      static_cast<unsigned>(toks) * H2 * 16u, &full_bar[slot]);
+      }
+      if (++slot == kEstStages) {
+        slot = 0;
+        if (j >= kEstStages) parity ^= 1u;
+      }
+    }
+    grid_launch_dependents();
+    return;
+  }
+
+  // ---- consumers ------------------------------------------------------------------------------------
+  grid_dependency_wait();
+  grid_launch_dependents();
+  const int half = lane & 1;
+  const int h = (lane % H2) >> 1;
+  const QPlanes qp = make_qplanes<METRIC>(__ldg(p.q_code + 2 * h + half));
+  const int toks_per_step = 32 / H2;
+  const int tok_in_step = lane / H2;
+  // A warp works in units of 8 consecutive tokens (16 for one head).  With stage_out its lanes drop
+  // their distances into a warp-private table [head][token], then one lane per head (and 8-token part)
+  // writes 16 contiguous bytes of the head's output row: with 16 heads a step covers one token, and
+  // isolated 2-byte stores to 16 different rows cost more than the scan itself.  With fewer heads a
+  // step already writes runs of 2 to 16 tokens per row, and direct stores are faster.
+  const int unit_tok = max(8, toks_per_step);
+  const int steps_per_unit = unit_tok / toks_per_step;
+  const int parts = unit_tok >> 3;
+  uint16_t(*stage)[16] = s_stage[warp];
+  OutT* out = static_cast<OutT*>(p.out);
+  const bool rows_aligned = ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) && ((p.out_stride * sizeof(OutT)) % 16 == 0);
+  int slot = 0;
+  unsigned parity = 0;
+  for (int j = 0; j < my_tiles; ++j) {
+    const int tile = blockIdx.x + j * gridDim.x;
+    const int tok0 = tile * tile_span;
+    const int ntok = min(tile_span, p.n_tokens - tok0);
+    if (!mbar_wait_bounded(&full_bar[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
+    const uint4* base = est_smem + slot * tile_chunks;
+    const int units = (ntok + unit_tok - 1) / unit_tok;
+    for (int u = warp; u < units; u += kEstConsumerWarps) {
+      const uint4* ubase = base + u * steps_per_unit * 32 + lane;
+#pragma unroll 4
+      for (int st = 0; st < steps_per_unit; ++st) {
+        unsigned d = chunk_distance<METRIC>(ubase[st * 32], qp);
+        d += __shfl_xor_sync(0xffffffffu, d, 1);
+        if (half == 0) {
+          const OutT v = dist_to_out<OutT>(d);
+          const int t = st * toks_per_step + tok_in_step;
+          if (p.stage_out) {
+            stage[h][t] = *reinterpret_cast<const uint16_t*>(&v);
+          } else if (u * unit_tok + t < ntok) {
+            out[static_cast<int64_t>(h) * p.out_stride + tok0 + u * unit_tok + t] = v;
+          }
+        }
+      }
+      if (!p.stage_out) continue;
+      __syncwarp();
+      if (lane < p.H * parts) {
+        const int row = lane / parts;
+        const int t_base = u * unit_tok + (lane % parts) * 8;
+        if (t_base < ntok) {
+          OutT* dst = out + static_cast<int64_t>(row) * p.out_stride + tok0 + t_base;
+          const uint16_t* src = &stage[row][(lane % parts) * 8];
+          if (rows_aligned && ((tok0 + t_base) & 7) == 0 && t_base + 8 <= ntok) {
+            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+          } else {
+            for (int k = 0; k < 8 && t_base + k < ntok; ++k) reinterpret_cast<uint16_t*>(dst)[k] = src[k];
+          }
+        }
+      }
+      __syncwarp();
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[slot]);
+    if (++slot == kEstStages) {
+      slot = 0;
+      parity ^= 1u;
+    }
+  }
 }
 
 }  // namespace adamas

@@ -161,8 +161,8 @@ def run_reference_arm(args):
 
 
 def two_launch_step(args) -> bool:
-    """decode_step folds the append into the estimate launch for 16, 32 or 64 heads."""
-    return (not args.unfused) and args.heads in (16, 32, 64) and os.environ.get("ADAMAS_FUSED_APPEND", "1") != "0"
+    """decode_step folds the append into the estimate launch for 32 or 64 heads."""
+    return (not args.unfused) and args.heads in (32, 64) and os.environ.get("ADAMAS_FUSED_APPEND", "1") != "0"
 
 
 def launches_per_layer(args) -> int:

@@ -65,7 +65,7 @@ int adamas_device_error(unsigned* flags, int clear);
  * reference launches everything on the legacy default stream (e.g. adamas/ops/csrc/page.cu:99). */
 int adamas_set_pdl(int enable);
 
-/* Chooses how adamas_decode_step launches a step whose head count is 16, 32 or 64 and whose q and k
+/* Chooses how adamas_decode_step launches a step whose head count is 32 or 64 and whose q and k
  * are already rotated: with the append folded into the estimate launch (two launches; the default) or
  * as three launches (append, estimate, select+attend; ADAMAS_FUSED_APPEND=0 in the environment selects
  * it).  Results are identical.  No counterpart in the reference. */
@@ -279,7 +279,7 @@ int adamas_append_estimate(const void* q, const void* k, const void* v, void* q_
                            const float* thresholds3_host, adamas_stream_t stream);
 
 /* One layer's whole decode step in one call: two launches (the estimate with the append inside, then
- * select+attend) for 16, 32 or 64 heads and rotated inputs, three (fused append, estimate,
+ * select+attend) for 32 or 64 heads and rotated inputs, three (fused append, estimate,
  * select+attend) otherwise:
  * what adamas/models/Adamas.py:145-200 does with seven launches.  q, k, v, o [1,H,D]; q_code
  * [1,H,D/8] scratch/output; dist_scratch [H, dist_stride] 16-bit, rows on 16-byte boundaries,

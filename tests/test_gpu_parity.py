@@ -249,6 +249,23 @@ def test_estimate_other_head_counts(H):
                                   ref.code_distance(q_code, k_codes[:-1], "l1"))
 
 
+@pytest.mark.parametrize("H", [1, 2, 4, 8, 16])
+@pytest.mark.parametrize("L,ps", [(2, 16), (17, 16), (530, 16), (4099, 16), (9000, 32), (700, 3), (1000, 1)])
+@pytest.mark.parametrize("metric", ["l1", "xor"])
+def test_estimate_few_heads_page_copies(H, L, ps, metric):
+    """Head-sharded shapes (16 heads or fewer): the estimate copies whole pages of codes when a page
+    is at least 512 bytes, and token by token otherwise; both against the oracle, including rows
+    that end inside a page and inside a tile."""
+    _, _, U = _mods()
+    st = State(L, H, ps, seed=3 * H + L, sigma=3.0, scale=1.0)
+    q_code, k_codes = st.oracle_codes()
+    got = U.decode_estimate(st.q_code, st.c, 0, metric=metric)
+    np.testing.assert_array_equal(got.float().cpu().numpy().astype(np.int32),
+                                  ref.code_distance(q_code, k_codes[:-1], metric))
+    from adamas_b200 import _lib
+    assert _lib.device_error(clear=False) == 0
+
+
 def test_estimate_golden_reference_vectors():
     """Distances for the fixtures produced by the reference's own _ref_cpu_estimate."""
     _, K, U = _mods()
