@@ -1086,12 +1086,50 @@ int launch_select_attend_one(const SelectAttendParams& prm, int cl, int num_head
     if (!configured[dev & 63]) {
       ADAMAS_CUDA(cudaFuncSetAttribute(select_attend_kernel<T, I>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        160 * 1024));
+      // clusters of 16 blocks (long rows of few heads) are beyond the portable size
+      ADAMAS_CUDA(cudaFuncSetAttribute(select_attend_kernel<T, I>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
       configured[dev & 63] = true;
     }
   }
   const dim3 grid(static_cast<unsigned>(num_heads) * cl);
   ADAMAS_LAUNCH("select_attend_kernel", (select_attend_kernel<T, I>), grid, dim3(kSaThreads), smem, st, cl, prm);
   return check_launch("select_attend_kernel");
+}
+
+// How many clusters of 16 select_attend blocks (one block per SM) the device holds at once; 0 if it
+// cannot launch them.  Queried once per device.
+int big_cluster_capacity(int* out) {
+  static int cap[64];
+  static bool known[64] = {};
+  int dev = 0;
+  ADAMAS_CUDA(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(g_init_mutex);
+  if (!known[dev & 63]) {
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kSaBigCluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cfg.gridDim = dim3(kSaBigCluster * 64);
+    cfg.blockDim = dim3(kSaThreads);
+    cfg.dynamicSmemBytes = 120 * 1024;
+    int n = 0;
+    cudaError_t e = cudaFuncSetAttribute(select_attend_kernel<__half, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(select_attend_kernel<__half, 2>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveClusters(&n, select_attend_kernel<__half, 2>, &cfg);
+    if (e != cudaSuccess) {
+      cudaGetLastError();   // not an error of the caller: big clusters are simply not used
+      n = 0;
+    }
+    cap[dev & 63] = n;
+    known[dev & 63] = true;
+  }
+  *out = cap[dev & 63];
+  return ADAMAS_OK;
 }
 
 template <typename T>
@@ -1142,6 +1180,17 @@ int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, co
                  cl_limit * 8 * kSaThreads * 8, cl_limit, n);
   const DeviceInfo* di = nullptr;
   if (int rc = get_device_info(&di)) return rc;
+  if (cl == kSaMaxCluster && items >= 2 && cl_limit == kSaMaxCluster) {
+    // A long row (16 or more distances per thread) of few heads (a head-sharded model): most SMs would
+    // idle while 8 blocks per head walk their slices.  Sixteen blocks per head halve the slices, as
+    // long as all clusters are resident at once (one cluster of 16 per GPC).
+    int big = 0;
+    if (int rc = big_cluster_capacity(&big)) return rc;
+    if (num_heads <= big) {
+      cl = kSaBigCluster;
+      items /= 2;
+    }
+  }
   {
     // a large budget on a short row: more blocks per head than the scan needs, so that each block
     // attends to about one tile of winners, as long as all blocks stay resident at once
@@ -1185,7 +1234,10 @@ int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, co
     prm.trace_tag = (sa_launches++) & 63;
   }
 #endif
-  const size_t smem = static_cast<size_t>(2) * prm.tile_cap * 256 + static_cast<size_t>(prm.list_capacity) * 4;
+  // K and V tile | winner list | rank 0's table of partial results
+  const size_t smem = static_cast<size_t>(2) * prm.tile_cap * 256 +
+                      ((static_cast<size_t>(prm.list_capacity) * 4 + 15) & ~static_cast<size_t>(15)) +
+                      static_cast<size_t>(cl) * (kHeadDim + 2) * sizeof(float);
   ADAMAS_REQUIRE(smem <= 160 * 1024, "winner list too long for select_attend (k=%d)", k);
   if (dtype == ADAMAS_F16)
     return launch_select_attend<__half>(prm, items, cl, num_heads, smem, to_stream(stream));

@@ -41,7 +41,8 @@ constexpr int kSaBins = 512;
 constexpr int kSaTile = 128;          // planning unit of the host (winners per block it aims for)
 constexpr int kSaMaxTpg = 6;          // tokens per P.V group at most
 constexpr int kSaTileMax = kSaMaxTpg * kSaThreads / 16;   // largest attention tile: 192 tokens
-constexpr int kSaMaxCluster = 8;
+constexpr int kSaMaxCluster = 8;      // portable cluster size
+constexpr int kSaBigCluster = 16;     // non-portable: long rows of few heads (see the host code)
 
 struct SelectAttendParams {
   const uint16_t* dist;     // [H, dist_stride] u16 distances, rows 16-byte aligned
@@ -67,8 +68,6 @@ struct SelectAttendParams {
 };
 
 struct SaShared {
-  float part_o[kSaMaxCluster][kHeadDim];     // rank 0 only: partial outputs of the blocks
-  float part_ml[kSaMaxCluster][2];
   float s_logit[kSaTileMax];
   float s_p[kSaTileMax];
   float s_red[kSaMaxWarps];
@@ -86,9 +85,10 @@ __device__ __forceinline__ void cluster_wait_acquire() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-// Dynamic shared memory: K tile (tile_cap * 256 B) | V tile (same) | winner list (list_capacity * 4 B).
-// The first 10 KB double as the histogram tables (local: 512 x u32; per source block: 8 x 512 x u16)
-// until phase 3 starts, the first 8 KB as the warps' partial outputs after it has ended.
+// Dynamic shared memory: K tile (tile_cap * 256 B) | V tile (same) | winner list (list_capacity * 4 B,
+// rounded up to 16) | rank 0's table of the blocks' partial results (CL * 130 floats).
+// The first 2 KB + CL KB double as the histogram tables (local: 512 x u32; per source block: CL x 512 x
+// u16) until phase 3 starts, the first 8 KB as the warps' partial outputs after it has ended.
 template <typename T, int ITEMS>
 __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const SelectAttendParams p) {
   constexpr int NT = kSaThreads;
@@ -115,6 +115,8 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   uint8_t* sk = sa_smem;
   uint8_t* sv = sa_smem + cap * 256;
   int32_t* s_list = reinterpret_cast<int32_t*>(sa_smem + 2 * cap * 256);
+  float* part_o = reinterpret_cast<float*>(sa_smem + 2 * cap * 256 + ((p.list_capacity * 4 + 15) & ~15));  // [CL][128]
+  float* part_ml = part_o + CL * kHeadDim;                                                                  // [CL][2]
   unsigned* h_local = reinterpret_cast<unsigned*>(sa_smem);
   uint16_t* h_src = reinterpret_cast<uint16_t*>(sa_smem + kSaBins * 4);
   float(*s_o)[kHeadDim] = reinterpret_cast<float(*)[kHeadDim]>(sa_smem);
@@ -198,11 +200,10 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   {
     // thread -> (8 bins, peer): a block's count of one bin is at most 8 * 512 * ITEMS <= 32768
     const int vec = tid & 63;
-    const unsigned peer = static_cast<unsigned>(tid) >> 6;
-    if (peer < CL) {
-      const uint4 a = *reinterpret_cast<const uint4*>(h_local + 8 * vec);
-      const uint4 b = *reinterpret_cast<const uint4*>(h_local + 8 * vec + 4);
-      const uint4 pk = make_uint4(a.x | (a.y << 16), a.z | (a.w << 16), b.x | (b.y << 16), b.z | (b.w << 16));
+    const uint4 a = *reinterpret_cast<const uint4*>(h_local + 8 * vec);
+    const uint4 b = *reinterpret_cast<const uint4*>(h_local + 8 * vec + 4);
+    const uint4 pk = make_uint4(a.x | (a.y << 16), a.z | (a.w << 16), b.x | (b.y << 16), b.z | (b.w << 16));
+    for (unsigned peer = static_cast<unsigned>(tid) >> 6; peer < CL; peer += NT / 64) {
       uint16_t* dst = cluster.map_shared_rank(h_src + cr * kSaBins + 8 * vec, peer);
       *reinterpret_cast<uint4*>(dst) = pk;
     }
@@ -472,10 +473,10 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
     float od = 0.f;
 #pragma unroll
     for (int g = 0; g < kWarps; ++g) od += s_o[g][tid];
-    *cluster.map_shared_rank(&sh.part_o[cr][tid], 0) = od;
+    *cluster.map_shared_rank(part_o + cr * kHeadDim + tid, 0) = od;
   }
   if (tid == 0) {
-    float* ml = cluster.map_shared_rank(&sh.part_ml[cr][0], 0);
+    float* ml = cluster.map_shared_rank(part_ml + cr * 2, 0);
     ml[0] = m_run;
     ml[1] = l_run;
   }
@@ -488,13 +489,13 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
 #endif
   if (cr != 0 || tid >= kHeadDim) return;
   float M = -INFINITY;
-  for (unsigned r = 0; r < CL; ++r) M = fmaxf(M, sh.part_ml[r][0]);
+  for (unsigned r = 0; r < CL; ++r) M = fmaxf(M, part_ml[r * 2]);
   float accd = 0.f, L = 0.f;
   for (unsigned r = 0; r < CL; ++r) {
-    const float m = sh.part_ml[r][0];
+    const float m = part_ml[r * 2];
     const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
-    L += w * sh.part_ml[r][1];
-    accd += w * sh.part_o[r][tid];
+    L += w * part_ml[r * 2 + 1];
+    accd += w * part_o[r * kHeadDim + tid];
   }
   const float res = L > 0.f ? accd / L : 0.f;
   const float res1 = __shfl_down_sync(0xffffffffu, res, 1);
