@@ -1096,15 +1096,16 @@ int launch_select_attend_one(const SelectAttendParams& prm, int cl, int num_head
   return check_launch("select_attend_kernel");
 }
 
-// How many clusters of 16 select_attend blocks (one block per SM) the device holds at once; 0 if it
-// cannot launch them.  Queried once per device.
-int big_cluster_capacity(int* out) {
-  static int cap[64];
-  static bool known[64] = {};
+// How many clusters of 16 select_attend blocks with `smem` bytes of dynamic shared memory the device
+// holds at once; 0 if it cannot launch them.  Queried once per device and shared-memory size (in KB).
+int big_cluster_capacity(size_t smem, int* out) {
+  static int cap[64][161];
+  static bool known[64][161] = {};
   int dev = 0;
   ADAMAS_CUDA(cudaGetDevice(&dev));
+  const int kb = static_cast<int>(std::min<size_t>((smem + 1023) / 1024, 160));
   std::lock_guard<std::mutex> lock(g_init_mutex);
-  if (!known[dev & 63]) {
+  if (!known[dev & 63][kb]) {
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1115,7 +1116,7 @@ int big_cluster_capacity(int* out) {
     cfg.numAttrs = 1;
     cfg.gridDim = dim3(kSaBigCluster * 64);
     cfg.blockDim = dim3(kSaThreads);
-    cfg.dynamicSmemBytes = 120 * 1024;
+    cfg.dynamicSmemBytes = static_cast<size_t>(kb) * 1024;
     int n = 0;
     cudaError_t e = cudaFuncSetAttribute(select_attend_kernel<__half, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
     if (e == cudaSuccess)
@@ -1125,11 +1126,35 @@ int big_cluster_capacity(int* out) {
       cudaGetLastError();   // not an error of the caller: big clusters are simply not used
       n = 0;
     }
-    cap[dev & 63] = n;
-    known[dev & 63] = true;
+    cap[dev & 63][kb] = n;
+    known[dev & 63][kb] = true;
   }
-  *out = cap[dev & 63];
+  *out = cap[dev & 63][kb];
   return ADAMAS_OK;
+}
+
+// Shape of a select_attend launch for cl blocks per head: winner-list capacity, attention tile and
+// dynamic shared memory (K and V tile | winner list | rank 0's table of partial results).
+struct SaShape {
+  int granules_per_block, list_capacity, tile_cap;
+  size_t smem;
+};
+SaShape sa_shape(int n, int k, int g_total, int cl) {
+  SaShape sh;
+  sh.granules_per_block = (g_total + cl - 1) / cl;
+  const int slice_tokens = std::min(n, sh.granules_per_block * 8);
+  sh.list_capacity = std::min(k, slice_tokens) + 1;
+  // Attention tile: the winners spread over the cl slices about evenly (binomially for unordered
+  // data); a tile with room for the mean plus four standard deviations makes a second, serial tile
+  // pass rare.  Lists that exceed the tile are still handled, tile after tile.
+  const int unit = kSaThreads / 8;   // tile sizes: unit (2 tokens per P.V group), 2 * unit, 3 * unit
+  const int mean = (k + cl - 1) / cl + 1;
+  const int want = std::min(sh.list_capacity, mean + static_cast<int>(4.0 * std::sqrt(static_cast<double>(mean))) + 8);
+  sh.tile_cap = want <= unit ? unit : (want <= 2 * unit ? 2 * unit : 3 * unit);
+  sh.smem = static_cast<size_t>(2) * sh.tile_cap * 256 +
+            ((static_cast<size_t>(sh.list_capacity) * 4 + 15) & ~static_cast<size_t>(15)) +
+            static_cast<size_t>(cl) * (kHeadDim + 2) * sizeof(float);
+  return sh;
 }
 
 template <typename T>
@@ -1183,9 +1208,9 @@ int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, co
   if (cl == kSaMaxCluster && items >= 2 && cl_limit == kSaMaxCluster) {
     // A long row (16 or more distances per thread) of few heads (a head-sharded model): most SMs would
     // idle while 8 blocks per head walk their slices.  Sixteen blocks per head halve the slices, as
-    // long as all clusters are resident at once (one cluster of 16 per GPC).
+    // long as all clusters are resident at once.
     int big = 0;
-    if (int rc = big_cluster_capacity(&big)) return rc;
+    if (int rc = big_cluster_capacity(sa_shape(n, k, g_total, kSaBigCluster).smem, &big)) return rc;
     if (num_heads <= big) {
       cl = kSaBigCluster;
       items /= 2;
@@ -1214,18 +1239,10 @@ int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, co
   prm.tail_slot = static_cast<unsigned>(tail);
   prm.out_idx = out_idx;
   prm.out_stride = out_stride;
-  prm.granules_per_block = (g_total + cl - 1) / cl;
-  const int slice_tokens = std::min(n, prm.granules_per_block * 8);
-  prm.list_capacity = std::min(k, slice_tokens) + 1;
-  // Attention tile: the winners spread over the cl slices about evenly (binomially for unordered
-  // data); a tile with room for the mean plus four standard deviations makes a second, serial tile
-  // pass rare.  Lists that exceed the tile are still handled, tile after tile.
-  {
-    const int unit = kSaThreads / 8;   // tile sizes: unit (2 tokens per P.V group), 2 * unit, 3 * unit
-    const int mean = (k + cl - 1) / cl + 1;
-    const int want = std::min(prm.list_capacity, mean + static_cast<int>(4.0 * std::sqrt(static_cast<double>(mean))) + 8);
-    prm.tile_cap = want <= unit ? unit : (want <= 2 * unit ? 2 * unit : 3 * unit);
-  }
+  const SaShape shape = sa_shape(n, k, g_total, cl);
+  prm.granules_per_block = shape.granules_per_block;
+  prm.list_capacity = shape.list_capacity;
+  prm.tile_cap = shape.tile_cap;
   prm.scale_log2 = sm_scale * 1.4426950408889634f;
   prm.trace_tag = 0;
 #ifdef ADAMAS_PHASE_TIMING
@@ -1234,10 +1251,7 @@ int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, co
     prm.trace_tag = (sa_launches++) & 63;
   }
 #endif
-  // K and V tile | winner list | rank 0's table of partial results
-  const size_t smem = static_cast<size_t>(2) * prm.tile_cap * 256 +
-                      ((static_cast<size_t>(prm.list_capacity) * 4 + 15) & ~static_cast<size_t>(15)) +
-                      static_cast<size_t>(cl) * (kHeadDim + 2) * sizeof(float);
+  const size_t smem = shape.smem;
   ADAMAS_REQUIRE(smem <= 160 * 1024, "winner list too long for select_attend (k=%d)", k);
   if (dtype == ADAMAS_F16)
     return launch_select_attend<__half>(prm, items, cl, num_heads, smem, to_stream(stream));
