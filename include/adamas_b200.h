@@ -258,7 +258,7 @@ int adamas_decode_forward_static(const void* q, void* o, float* lse, const void*
  * kv_page_table[t / page_size] * page_size + t % page_size.  out_idx (optional, [H, out_stride])
  * receives the winners' physical token slots in ascending position order, exactly what adamas_topk
  * would write.  Replaces the topk_filtering + BatchDecodeWithPagedKVCachePyTorchWrapper::Forward pair
- * (adamas/models/Adamas.py:185-200) for n up to 131072. */
+ * (adamas/models/Adamas.py:185-200) for n up to 262144 (32768 x the adamas_set_max_cluster bound). */
 int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, const void* q, void* o,
                          float* lse, const void* kv_data, const int32_t* kv_page_table, int page_size,
                          int num_heads, int head_dim, int dtype, int last_page_idx, int last_page_len,

@@ -468,6 +468,7 @@ def test_full_step_token_granular(dtype, L, ps, budget):
 @pytest.mark.parametrize("L,ps,budget,H", [
     (70, 16, 8, 32), (300, 16, 64, 32), (700, 16, 128, 16), (700, 1, 128, 64), (2049, 16, 33, 8), (4096, 16, 256, 32), (5000, 1, 1024, 32),
     (9001, 32, 4096, 4), (8192, 16, 2048, 32), (32768, 16, 1024, 32), (70000, 16, 2048, 2), (131072, 16, 2048, 4),
+    (150000, 16, 512, 1), (200000, 16, 1024, 8),      # 16-block clusters / 64 distances per thread
 ])
 def test_fused_decode_step(dtype, L, ps, budget, H):
     """decode_step (append + estimate + select/attend in one call) against the oracle: codes and
