@@ -323,15 +323,21 @@ __global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const Esti
   __syncthreads();
   const int my_tiles = est_tiles_of_block(p);
 
+  ADAMAS_STAMP(0, 0, tid == 0);
+  ADAMAS_TRACE(0, p.trace_tag, 0, tid == 0);
+  ADAMAS_CHAIN(1, 0, false, blockIdx.x == 0 && tid == 0);
   if (warp == kEstConsumerWarps) {
     // the cached codes were final before the preceding kernel started: stream them right away
     est_produce<false>(p, ring, my_tiles, lane);
     grid_launch_dependents();
+    ADAMAS_STAMP(0, 4, lane == 0);
     return;
   }
   // q, k, v are the preceding kernel's output
   grid_dependency_wait();
   grid_launch_dependents();
+  ADAMAS_STAMP(0, 1, tid == 0);
+  ADAMAS_CHAIN(1, 1, false, blockIdx.x == 0 && tid == 0);
 
   const bool appender = blockIdx.x == gridDim.x - 1;
   const unsigned l16 = lane & 15;
@@ -388,7 +394,11 @@ __global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const Esti
       }
     }
   }
+  ADAMAS_STAMP(0, 2, tid == 0);
   est_consume<0, uint16_t, HPW>(p, ring, my_tiles, lane, warp, qp, nullptr);
+  ADAMAS_STAMP(0, 3, tid == 0);
+  ADAMAS_TRACE(0, p.trace_tag, 1, tid == 0);
+  ADAMAS_CHAIN(1, 2, true, blockIdx.x == 0 && tid == 0);
 }
 
 // ---- few heads per GPU: whole pages per copy, one 16-byte chunk per lane ---------------------------------
