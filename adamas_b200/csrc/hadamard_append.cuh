@@ -151,8 +151,11 @@ append_decode_kernel(const T* __restrict__ k, const T* __restrict__ v, const T* 
                      int kv_last_page, int kv_entry, int code_last_page, int code_entry, float scale,
                      Thresholds th, float pos = 0.f, RopeParams rp = RopeParams{1.f, 1e4f}) {
   ADAMAS_CHAIN(0, 0, false, blockIdx.x == 0 && threadIdx.x == 0);
-  grid_dependency_wait();
+  // The kernel after this one (the estimate) may become resident right away: its producer warps only
+  // read the code cache as it was before this step, and its consumers wait for this grid to complete,
+  // which in turn waits for the grid before it.
   grid_launch_dependents();
+  grid_dependency_wait();
   ADAMAS_CHAIN(0, 1, false, blockIdx.x == 0 && threadIdx.x == 0);
   // physical pages of the slot being written: last entries of the two page tables
   const int kv_page = __ldg(tgt.kv_table + kv_last_page);
