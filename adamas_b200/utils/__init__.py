@@ -129,7 +129,12 @@ def decode_step(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, iController: 
     if not c.need_estimate():
         append_qkv_fused(q, k, v, c, layer_idx, scale=scale, rope=rope)
         return decode_sparse_attn(q, c, layer_idx, c.kv_indices_without_last, out=o)
-    q_code = torch.empty(1, k.size(1), k.size(2) // 8, dtype=k.dtype, device=k.device)
+    # the packed query code is scratch here (one buffer per controller: launches of one sequence are
+    # ordered on one stream)
+    q_code = getattr(c, "_q_code_scratch", None)
+    if q_code is None or q_code.dtype != k.dtype or q_code.device != k.device or q_code.size(1) != k.size(1):
+        q_code = torch.empty(1, k.size(1), k.size(2) // 8, dtype=k.dtype, device=k.device)
+        c._q_code_scratch = q_code
     n = c.hadamard_cache.seqlen - 1
     _kernels.decode_step(
         q, k, v, o, q_code, c.kv_cache.buf_layer(layer_idx), c.kv_indices_with_last, c.kv_cache.last_page_len,
