@@ -122,6 +122,35 @@ def bucketize_pack(h: torch.Tensor, o: torch.Tensor, thresholds=None) -> None:
                                          _dtype_code(h.dtype, "bucketize_pack"), _stream()), "bucketize_pack")
 
 
+def pack_2bit(h: torch.Tensor, o: torch.Tensor, past_kv_len: int = 0) -> None:
+    """adamas/ops/csrc/page.cu:271-298 under its reference name: o[..., w] = packed 2-bit codes of the
+    already transformed values h[..., 8w:8w+8] (default thresholds).  `past_kv_len` is accepted for
+    the reference's signature; the packing does not depend on it."""
+    bucketize_pack(h, o)
+
+
+def histogram_scratch(num_heads: int, device) -> torch.Tensor:
+    """A zeroed histogram table for decode_step / select_attend ([H, 16, 512] 32-bit counts).  Every
+    call that uses it leaves it all zero, so one table serves all steps of a sequence; calls that
+    may overlap on the GPU need separate tables."""
+    return torch.zeros(num_heads, 16, 512, dtype=torch.int32, device=device)
+
+
+def _check_hist(hist: Optional[torch.Tensor], num_heads: int) -> Optional[torch.Tensor]:
+    if hist is not None:
+        _require(hist.is_cuda and hist.is_contiguous() and hist.dtype == torch.int32
+                 and hist.numel() >= num_heads * _lib.HIST_WORDS_PER_HEAD,
+                 "hist must be a contiguous int32 CUDA tensor of H * 16 * 512 elements")
+    return hist
+
+
+def select_attend_slices(n: int, k: int, num_heads: int) -> int:
+    """Thread blocks per head (= histogram slices) select_attend uses for rows of n distances."""
+    out = ctypes.c_int(0)
+    _lib.check(lib.adamas_select_attend_slices(int(n), int(k), int(num_heads), ctypes.byref(out)), "select_attend_slices")
+    return out.value
+
+
 def _check_append(k, v, kv_data, kv_indices, hadamard_data, hadamard_indices, layout):
     _nhd_only(layout)
     _check_input(k, "k", 3)
@@ -214,11 +243,14 @@ def append_kv_cache_prefill(k, v, h, kv_data, kv_indices, kv_indptr, kv_last_pag
 # stage 2
 # ----------------------------------------------------------------------------------------------
 def estimate_attn_score(q, o, metadata_data, metadata_indices, metadata_indptr, metadata_last_page_len,
-                        metadata_last_page_idx, layout, metric: str = "l1", exclude_last: bool = True) -> None:
+                        metadata_last_page_idx, layout, metric: str = "l1", exclude_last: bool = True,
+                        hist: Optional[torch.Tensor] = None, hist_slices: int = 0) -> None:
     """adamas/ops/csrc/estimate.cu:6-84.  q [1,H,D/8] packed query code; o [H, n] with
     n = (pages-1)*page_size + last_page_len - 1 (newest token excluded); o.dtype float16 stores the
     distances as fp16 (reference), int16 as integers.  exclude_last=False covers every cached token
-    (a sequence shard that does not hold the newest token)."""
+    (a sequence shard that does not hold the newest token).  `hist` (a zeroed histogram_scratch(H))
+    additionally receives the per-slice counts that select_attend(..., hist_ready=True) reads;
+    hist_slices = select_attend_slices(n, k, H) of that call."""
     _nhd_only(layout)
     _check_input(q, "q", 3)
     _check_rows(o, "o")
@@ -237,7 +269,8 @@ def estimate_attn_score(q, o, metadata_data, metadata_indices, metadata_indptr, 
         _ptr(q), _ptr(metadata_data), _ptr(metadata_indices), metadata_indices.numel(),
         int(metadata_last_page_len), page_size, num_heads, code_words * 8, _ptr(o), o.stride(0),
         _value_format(o.dtype, "Estimate_attn_score"),
-        {"l1": _lib.METRIC_L1, "xor": _lib.METRIC_XOR}[metric], 1 if exclude_last else 0, _stream()),
+        {"l1": _lib.METRIC_L1, "xor": _lib.METRIC_XOR}[metric], 1 if exclude_last else 0,
+        _ptr(_check_hist(hist, num_heads)), int(hist_slices), _stream()),
         "Estimate_attn_score")
 
 
@@ -383,6 +416,37 @@ class BatchDecodeWithPagedKVCachePyTorchWrapper:
             1.0 / math.sqrt(head_dim), _stream()), "BatchDecodeWithPagedKVCache")
 
 
+    def dense_step_dev(self, q, k, v, o, q_code, kv_data, kv_indices, hadamard_data, hadamard_indices,
+                       seq_len: torch.Tensor, max_seq_len: int, scale: Optional[float] = None, thresholds=None,
+                       rope=None, lse: Optional[torch.Tensor] = None) -> None:
+        """The dense layers' decode step with the sequence length in device memory (see
+        decode_step_dev): fused append (with the rotary embedding when `rope` is given) and attention
+        over all seq_len tokens, shaped by max_seq_len only, so that it can be captured in a graph."""
+        if not self._started:
+            raise RuntimeError("BatchDecodeWithPagedKVCache failed with error: dense step called before begin_forward")
+        num_heads, head_dim, page_size = _check_append(k, v, kv_data, kv_indices, hadamard_data, hadamard_indices, NHD)
+        cfg_heads, cfg_dim, cfg_ps, dt = self._cfg
+        _require((num_heads, head_dim, page_size) == (cfg_heads, cfg_dim, cfg_ps)
+                 and _dtype_code(k.dtype, "dense_step_dev") == dt, "cache geometry differs from begin_forward")
+        _check_input(q, "q", 3)
+        _check_input(o, "o", 3)
+        _check_input(q_code, "q_code", 3)
+        _check_seq_len(seq_len)
+        _require(tuple(q.shape) == tuple(k.shape) == tuple(o.shape) and k.size(0) == 1, "q, k, v, o must be [1, H, D]")
+        _require(kv_indices.numel() * page_size >= max_seq_len, "the page table must have room for max_seq_len tokens")
+        if max_seq_len > self._planned_tokens:
+            _lib.check(lib.adamas_decode_begin_forward(self._handle, int(max_seq_len), num_heads, head_dim, page_size,
+                                                       dt, _stream()), "BatchDecodeWithPagedKVCache")
+            self._planned_tokens = int(max_seq_len)
+        s = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)
+        rs, rt, inv_freq, mscale = _rope_args(rope)
+        _lib.check(lib.adamas_dense_step_dev(
+            self._handle, _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(q_code), _ptr(kv_data),
+            _ptr(kv_indices), _ptr(hadamard_data), _ptr(hadamard_indices), _ptr(seq_len), int(max_seq_len),
+            num_heads, head_dim, page_size, dt, s, _lib.thresholds_arg(thresholds), rs, rt, _ptr(inv_freq), mscale,
+            1.0 / math.sqrt(head_dim), _stream()), "dense_step_dev")
+
+
 def set_max_cluster(blocks: int) -> None:
     """Upper bound (1, 2, 4, 8) on the thread blocks that share one head in select_attend /
     decode_step: 8 is fastest for a single sequence, smaller values let calls of several sequences
@@ -402,22 +466,30 @@ def set_fused_append(enable: bool) -> None:
     _lib.check(lib.adamas_set_fused_append(int(bool(enable))), "set_fused_append")
 
 
-def select_attend(dist: torch.Tensor, k: int, q: torch.Tensor, o: torch.Tensor, kv_data: torch.Tensor,
+def select_attend(dist: torch.Tensor, k: int, q: torch.Tensor, o: Optional[torch.Tensor], kv_data: torch.Tensor,
                   kv_indices: torch.Tensor, last_page_len: int, last_page_idx: int,
-                  indices_out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None) -> None:
+                  indices_out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
+                  hist: Optional[torch.Tensor] = None, hist_ready: bool = False,
+                  ext_cut: Optional[torch.Tensor] = None, o_f32: Optional[torch.Tensor] = None) -> None:
     """Top-k and sparse attention in one launch (replaces topk_filtering + the decode wrapper's
     forward, adamas/models/Adamas.py:185-200).  dist int16 [H, n] integer distances with rows on
     16-byte boundaries; q, o [1,H,D]; kv_indices int32 page table; indices_out optional int32
-    [H, >=k] receiving the winners' token slots."""
+    [H, >=k] receiving the winners' token slots.  last_page_len = 0: no newest token is attended.
+    hist: a histogram_scratch(H) (made for the call when None); hist_ready: an estimate call has
+    already counted the distances into it.  ext_cut int32 [H, 2]: cut distance and number of
+    cut-valued winners of this call per head, decided elsewhere.  o_f32 float32 [H, D] (+ lse):
+    unrounded partial result."""
     _check_rows(dist, "dist")
     _check_input(q, "q", 3)
-    _check_input(o, "o", 3)
+    if o is not None:
+        _check_input(o, "o", 3)
     _check_input(kv_data, "kv_data", 5)
     _check_input(kv_indices, "kv_indices", 1)
     _require(dist.dtype in (torch.int16, torch.uint16), "dist must hold 16-bit integer distances")
     h, n = dist.shape
-    _require(q.size(0) == 1 and q.size(1) == h and q.size(2) == 128 and tuple(o.shape) == tuple(q.shape)
-             and o.dtype == q.dtype, "q and o must be [1, H, 128]")
+    _require(q.size(0) == 1 and q.size(1) == h and q.size(2) == 128, "q must be [1, H, 128]")
+    _require(o is not None or o_f32 is not None, "o or o_f32 must be given")
+    _require(o is None or (tuple(o.shape) == tuple(q.shape) and o.dtype == q.dtype), "o must match q")
     page_size = kv_data.size(2)
     _require(kv_data.size(1) == 2 and kv_data.size(3) == h and kv_data.size(4) == 128 and kv_data.dtype == q.dtype,
              "kv_data must be [pages, 2, page_size, H, 128] in q.dtype")
@@ -431,19 +503,30 @@ def select_attend(dist: torch.Tensor, k: int, q: torch.Tensor, o: torch.Tensor, 
     if lse is not None:
         _require(lse.is_cuda and lse.dtype == torch.float32 and lse.numel() == h and lse.is_contiguous(),
                  "lse must be a contiguous float32 CUDA tensor of H elements")
+    if o_f32 is not None:
+        _require(lse is not None and o_f32.is_cuda and o_f32.dtype == torch.float32 and o_f32.is_contiguous()
+                 and o_f32.numel() == h * 128, "o_f32 must be float32 [H, 128] and lse given")
+    if ext_cut is not None:
+        _require(ext_cut.is_cuda and ext_cut.dtype == torch.int32 and ext_cut.is_contiguous()
+                 and tuple(ext_cut.shape) == (h, 2), "ext_cut must be a contiguous int32 CUDA tensor [H, 2]")
+    if hist is None:
+        _require(not hist_ready, "hist_ready needs the table an estimate call has filled")
+        hist = histogram_scratch(h, dist.device)
     _lib.check(lib.adamas_select_attend(
-        _ptr(dist), dist.stride(0), n, int(k), _ptr(q), _ptr(o), _ptr(lse), _ptr(kv_data), _ptr(kv_indices),
-        page_size, h, 128, _dtype_code(q.dtype, "select_attend"), int(last_page_idx), int(last_page_len),
+        _ptr(dist), dist.stride(0), n, int(k), _ptr(q), _ptr(o), _ptr(o_f32), _ptr(lse), _ptr(kv_data),
+        _ptr(kv_indices), page_size, h, 128, _dtype_code(q.dtype, "select_attend"), int(last_page_idx),
+        int(last_page_len), _ptr(_check_hist(hist, h)), 1 if hist_ready else 0, _ptr(ext_cut),
         _ptr(indices_out), out_stride, 1.0 / math.sqrt(128.0), _stream()), "select_attend")
 
 
 def decode_step(q, k, v, o, q_code, kv_data, kv_indices, kv_last_page_len, kv_last_page_idx, hadamard_data,
                 hadamard_indices, hadamard_last_page_len, budget: int, dist_scratch: torch.Tensor,
-                indices_out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
-                scale: Optional[float] = None, thresholds=None, rope=None) -> None:
+                hist: torch.Tensor, indices_out: Optional[torch.Tensor] = None,
+                lse: Optional[torch.Tensor] = None, scale: Optional[float] = None, thresholds=None,
+                rope=None) -> None:
     """One layer's decode step in one call: append + estimate, select + attend (two launches for 16, 32
     or 64 heads and already rotated q/k, else three, for what adamas/models/Adamas.py:145-200 does with
-    seven).  Needs context > budget.  With
+    seven).  Needs context > budget.  `hist`: a histogram_scratch(H), all zero between steps.  With
     rope=(rope_scale, rope_theta) q and k arrive un-rotated and are rotated in place first."""
     num_heads, head_dim, page_size = _check_append(k, v, kv_data, kv_indices, hadamard_data, hadamard_indices, NHD)
     _check_input(q, "q", 3)
@@ -465,14 +548,90 @@ def decode_step(q, k, v, o, q_code, kv_data, kv_indices, kv_last_page_len, kv_la
         _ptr(kv_data), _ptr(kv_indices), kv_indices.numel(), int(kv_last_page_len), int(kv_last_page_idx),
         _ptr(hadamard_data), _ptr(hadamard_indices), hadamard_indices.numel(), int(hadamard_last_page_len),
         num_heads, head_dim, page_size, _dtype_code(k.dtype, "decode_step"), int(budget),
-        _ptr(dist_scratch), dist_scratch.stride(0), _ptr(indices_out), out_stride, s,
+        _ptr(dist_scratch), dist_scratch.stride(0), _ptr(_check_hist(hist, num_heads)), _ptr(indices_out), out_stride, s,
         _lib.thresholds_arg(thresholds), float(rope[0]) if rope is not None else 0.0,
         float(rope[1]) if rope is not None else 0.0, 1.0 / math.sqrt(head_dim), _stream()), "decode_step")
 
 
+def _rope_args(rope):
+    """rope: None | (rope_scale, rope_theta) | {"inv_freq": float32 CUDA tensor [64], "mscale": float}."""
+    if rope is None:
+        return 0.0, 0.0, None, 1.0
+    if isinstance(rope, dict):
+        t = rope["inv_freq"]
+        _require(t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() and t.numel() == 64,
+                 "rope inv_freq must be a contiguous float32 CUDA tensor of 64 elements")
+        return 0.0, 0.0, t, float(rope.get("mscale", 1.0))
+    return float(rope[0]), float(rope[1]), None, 1.0
+
+
+def _check_seq_len(seq_len: torch.Tensor) -> None:
+    _require(isinstance(seq_len, torch.Tensor) and seq_len.is_cuda and seq_len.dtype == torch.int32
+             and seq_len.numel() == 1, "seq_len must be a one-element int32 CUDA tensor")
+
+
+def decode_step_dev(q, k, v, o, q_code, kv_data, kv_indices, hadamard_data, hadamard_indices,
+                    seq_len: torch.Tensor, max_seq_len: int, budget: int, dist_scratch: torch.Tensor,
+                    hist: torch.Tensor, indices_out: Optional[torch.Tensor] = None,
+                    lse: Optional[torch.Tensor] = None, scale: Optional[float] = None, thresholds=None,
+                    rope=None) -> None:
+    """decode_step with the sequence length (tokens in the caches, the new one included) in device
+    memory: the launches depend on max_seq_len only, so a CUDA graph captured once serves every token
+    (advance `seq_len` with seq_len_advance at the end of each token's work).  kv_indices /
+    hadamard_indices: the page tables, with an entry for every page the current length needs."""
+    num_heads, head_dim, page_size = _check_append(k, v, kv_data, kv_indices, hadamard_data, hadamard_indices, NHD)
+    _check_input(q, "q", 3)
+    _check_input(o, "o", 3)
+    _check_input(q_code, "q_code", 3)
+    _check_rows(dist_scratch, "dist_scratch")
+    _check_seq_len(seq_len)
+    _require(tuple(q.shape) == tuple(k.shape) == tuple(o.shape) and k.size(0) == 1, "q, k, v, o must be [1, H, D]")
+    _require(q_code.element_size() == 2 and q_code.numel() == num_heads * head_dim // 8, "q_code must be [1, H, D/8] 16-bit")
+    _require(dist_scratch.element_size() == 2 and dist_scratch.size(0) == num_heads
+             and dist_scratch.size(1) >= max_seq_len - 1, "dist_scratch must be 16-bit [H, >= max_seq_len - 1]")
+    _require(kv_indices.numel() * page_size >= max_seq_len and hadamard_indices.numel() * page_size >= max_seq_len,
+             "the page tables must have room for max_seq_len tokens")
+    out_stride = 0
+    if indices_out is not None:
+        _check_rows(indices_out, "indices_out")
+        _require(indices_out.dtype == torch.int32 and indices_out.size(0) == num_heads
+                 and indices_out.size(1) >= budget - 1, "indices_out must be int32 [H, >=budget-1]")
+        out_stride = indices_out.stride(0)
+    s = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)
+    rs, rt, inv_freq, mscale = _rope_args(rope)
+    _lib.check(lib.adamas_decode_step_dev(
+        _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(q_code), _ptr(kv_data), _ptr(kv_indices),
+        _ptr(hadamard_data), _ptr(hadamard_indices), _ptr(seq_len), int(max_seq_len), num_heads, head_dim,
+        page_size, _dtype_code(k.dtype, "decode_step_dev"), int(budget), _ptr(dist_scratch),
+        dist_scratch.stride(0), _ptr(_check_hist(hist, num_heads)), _ptr(indices_out), out_stride, s,
+        _lib.thresholds_arg(thresholds), rs, rt, _ptr(inv_freq), mscale, 1.0 / math.sqrt(head_dim), _stream()),
+        "decode_step_dev")
+
+
+def seq_len_advance(seq_len: torch.Tensor, delta: int = 1) -> None:
+    """seq_len += delta on the device, as one launch ordered against its neighbours in the stream."""
+    _check_seq_len(seq_len)
+    _lib.check(lib.adamas_seq_len_advance(_ptr(seq_len), int(delta), _stream()), "seq_len_advance")
+
+
+def apply_rope_table_in_place(q: torch.Tensor, k: torch.Tensor, past_kv_len: int, inv_freq: torch.Tensor,
+                              mscale: float = 1.0) -> None:
+    """apply_rope_in_place with a table of 64 rotation frequencies and a factor on the rotated values
+    (YaRN-scaled models) instead of (rope_scale, rope_theta)."""
+    _check_input(q, "q", 3)
+    _check_input(k, "k", 3)
+    _require(q.size(0) == k.size(0) and q.size(2) == k.size(2) == 128 and q.dtype == k.dtype,
+             "q and k must be [N, H, 128] of one dtype")
+    _, _, t, ms = _rope_args({"inv_freq": inv_freq, "mscale": mscale})
+    _lib.check(lib.adamas_apply_rope_table_in_place(_ptr(q), _ptr(k), q.size(0), q.size(1), k.size(1), 128,
+                                                    int(past_kv_len), _ptr(t), ms,
+                                                    _dtype_code(q.dtype, "apply_rope_table_in_place"), _stream()),
+               "apply_rope_table_in_place")
+
+
 def append_estimate(q, k, v, q_code, kv_data, kv_indices, kv_last_page_len, hadamard_data, hadamard_indices,
                     hadamard_last_page_len, dist: torch.Tensor, scale: Optional[float] = None,
-                    thresholds=None) -> None:
+                    thresholds=None, hist: Optional[torch.Tensor] = None, hist_slices: int = 0) -> None:
     """Decode append and distance estimate in one launch (16, 32 or 64 heads; q and k after RoPE): what
     append_kv_cache_decode_fused followed by estimate_attn_score do, with integer (16-bit) distances
     in `dist` [H, >= context-1]."""
@@ -489,7 +648,8 @@ def append_estimate(q, k, v, q_code, kv_data, kv_indices, kv_last_page_len, hada
         _ptr(kv_data), _ptr(kv_indices), kv_indices.numel(), int(kv_last_page_len),
         _ptr(hadamard_data), _ptr(hadamard_indices), hadamard_indices.numel(), int(hadamard_last_page_len),
         num_heads, head_dim, page_size, _dtype_code(k.dtype, "append_estimate"),
-        _ptr(dist), dist.stride(0), s, _lib.thresholds_arg(thresholds), _stream()), "append_estimate")
+        _ptr(dist), dist.stride(0), s, _lib.thresholds_arg(thresholds), _ptr(_check_hist(hist, num_heads)),
+        int(hist_slices), _stream()), "append_estimate")
 
 
 def merge_states(o_parts: torch.Tensor, lse_parts: torch.Tensor, o: torch.Tensor,

@@ -4,6 +4,7 @@
 #include "../../include/adamas_b200.h"
 
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdarg>
 #include <cstdlib>
@@ -72,6 +73,8 @@ int check_common(int num_heads, int head_dim, int page_size, int dtype) {
 }
 
 constexpr int kEstAppendStatic = 1280;   // static shared memory of estimate_append_kernel, rounded up
+constexpr int kEstPagesStatic = 8448;    // static shared memory of estimate_pages_kernel, rounded up
+constexpr int kSaMaxDynSmem = 160 * 1024;   // dynamic shared memory select_attend may ask for
 
 // Per-device facts and one-time kernel attributes.
 struct DeviceInfo {
@@ -130,10 +133,10 @@ int get_device_info(const DeviceInfo** out) {
     // different L1 / shared split than its predecessor cannot start until the SMs have drained.
 #define SET_CARVEOUT(kern) \
   ADAMAS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared))
-    SET_CARVEOUT((append_decode_kernel<__half, true>));
-    SET_CARVEOUT((append_decode_kernel<__half, false>));
-    SET_CARVEOUT((append_decode_kernel<__nv_bfloat16, true>));
-    SET_CARVEOUT((append_decode_kernel<__nv_bfloat16, false>));
+    SET_CARVEOUT((append_decode_kernel<__half, true, false>));
+    SET_CARVEOUT((append_decode_kernel<__half, false, false>));
+    SET_CARVEOUT((append_decode_kernel<__nv_bfloat16, true, false>));
+    SET_CARVEOUT((append_decode_kernel<__nv_bfloat16, false, false>));
     SET_CARVEOUT((append_decode_kernel<__half, true, true>));
     SET_CARVEOUT((append_decode_kernel<__nv_bfloat16, true, true>));
     SET_CARVEOUT((estimate_kernel<0, __half, 0>));
@@ -152,63 +155,69 @@ int get_device_info(const DeviceInfo** out) {
     SET_CARVEOUT((topk_cluster_kernel<1, 4, 256>));
     SET_CARVEOUT((sparse_decode_kernel<__half>));
     SET_CARVEOUT((sparse_decode_kernel<__nv_bfloat16>));
-    SET_CARVEOUT((select_attend_kernel<__half, 1>));
-    SET_CARVEOUT((select_attend_kernel<__half, 2>));
-    SET_CARVEOUT((select_attend_kernel<__half, 4>));
-    SET_CARVEOUT((select_attend_kernel<__half, 8>));
-    SET_CARVEOUT((select_attend_kernel<__nv_bfloat16, 1>));
-    SET_CARVEOUT((select_attend_kernel<__nv_bfloat16, 2>));
-    SET_CARVEOUT((select_attend_kernel<__nv_bfloat16, 4>));
-    SET_CARVEOUT((select_attend_kernel<__nv_bfloat16, 8>));
 #undef SET_CARVEOUT
+    // select+attend: large dynamic shared memory; clusters of 16 blocks (long rows of few heads) are
+    // beyond the portable size
+#define SA_ATTR(T, I)                                                                                          \
+  ADAMAS_CUDA(cudaFuncSetAttribute(select_attend_kernel<T, I>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                                   kSaMaxDynSmem));                                                            \
+  ADAMAS_CUDA(cudaFuncSetAttribute(select_attend_kernel<T, I>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1)); \
+  ADAMAS_CUDA(cudaFuncSetAttribute(select_attend_kernel<T, I>, cudaFuncAttributePreferredSharedMemoryCarveout, \
+                                   cudaSharedmemCarveoutMaxShared))
+#define SA_ATTR_ALL(T) \
+  SA_ATTR(T, 1);       \
+  SA_ATTR(T, 2);       \
+  SA_ATTR(T, 4);       \
+  SA_ATTR(T, 8)
+    SA_ATTR_ALL(__half);
+    SA_ATTR_ALL(__nv_bfloat16);
+#undef SA_ATTR_ALL
+#undef SA_ATTR
+#define ESTP_ATTR(M, OT)                                                                                      \
+  ADAMAS_CUDA(cudaFuncSetAttribute(estimate_pages_kernel<M, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                   d.max_smem_optin - 1024 - kEstPagesStatic));                               \
+  ADAMAS_CUDA(cudaFuncSetAttribute(estimate_pages_kernel<M, OT>, cudaFuncAttributePreferredSharedMemoryCarveout, \
+                                   cudaSharedmemCarveoutMaxShared))
+    ESTP_ATTR(0, __half);
+    ESTP_ATTR(0, uint16_t);
+    ESTP_ATTR(1, __half);
+    ESTP_ATTR(1, uint16_t);
+#undef ESTP_ATTR
     d.ready = true;
   }
   *out = &d;
   return ADAMAS_OK;
 }
 
-// Programmatic dependent launch of the hot kernels (on unless ADAMAS_PDL=0 or adamas_set_pdl(0)).
-int g_pdl = -1;
-bool pdl_enabled() {
-  if (g_pdl < 0) {
-    const char* e = std::getenv("ADAMAS_PDL");
-    g_pdl = (e && e[0] == '0') ? 0 : 1;
+// Process-wide settings.  Each is one atomic integer: a launch reads it once, so a change made by
+// another thread applies to whole launches, never to half of one.  -1 = not yet read from the
+// environment.
+int setting(std::atomic<int>& v, const char* env, int dflt, int lo, int hi) {
+  int cur = v.load(std::memory_order_relaxed);
+  if (cur < 0) {
+    const char* e = std::getenv(env);
+    cur = e ? std::atoi(e) : dflt;
+    if (cur < lo || cur > hi) cur = dflt;
+    v.store(cur, std::memory_order_relaxed);
   }
-  return g_pdl != 0;
+  return cur;
 }
-
+// Programmatic dependent launch of the hot kernels (on unless ADAMAS_PDL=0 or adamas_set_pdl(0)).
+std::atomic<int> g_pdl{-1};
+bool pdl_enabled() { return setting(g_pdl, "ADAMAS_PDL", 1, 0, 1) != 0; }
 // Whether adamas_decode_step folds the append into the estimate launch (on unless
 // ADAMAS_FUSED_APPEND=0 or adamas_set_fused_append(0)).
-int g_fused_append = -1;
-bool fused_append_enabled() {
-  if (g_fused_append < 0) {
-    const char* e = std::getenv("ADAMAS_FUSED_APPEND");
-    g_fused_append = (e && e[0] == '0') ? 0 : 1;
-  }
-  return g_fused_append != 0;
-}
-
+std::atomic<int> g_fused_append{-1};
+bool fused_append_enabled() { return setting(g_fused_append, "ADAMAS_FUSED_APPEND", 1, 0, 1) != 0; }
 // Upper bound on the estimate kernel's resident blocks per SM (adamas_set_estimate_blocks_per_sm /
 // ADAMAS_EST_BLOCKS_PER_SM): 2 by default, 1 leaves half of every SM to kernels of other streams.
-int g_est_blocks_per_sm = -1;
-int est_blocks_per_sm() {
-  if (g_est_blocks_per_sm < 0) {
-    const char* e = std::getenv("ADAMAS_EST_BLOCKS_PER_SM");
-    const int v = e ? std::atoi(e) : 2;
-    g_est_blocks_per_sm = (v == 1) ? 1 : 2;
-  }
-  return g_est_blocks_per_sm;
-}
-
+std::atomic<int> g_est_blocks_per_sm{-1};
+int est_blocks_per_sm() { return setting(g_est_blocks_per_sm, "ADAMAS_EST_BLOCKS_PER_SM", 2, 1, 2); }
 // Upper bound on the cluster size of select_attend (adamas_set_max_cluster / ADAMAS_MAX_CLUSTER).
-int g_max_cluster = -1;
+std::atomic<int> g_max_cluster{-1};
 int max_cluster() {
-  if (g_max_cluster < 0) {
-    const char* e = std::getenv("ADAMAS_MAX_CLUSTER");
-    const int v = e ? std::atoi(e) : kSaMaxCluster;
-    g_max_cluster = (v >= 1 && v <= kSaMaxCluster) ? v : kSaMaxCluster;
-  }
-  return g_max_cluster;
+  const int v = setting(g_max_cluster, "ADAMAS_MAX_CLUSTER", kSaMaxCluster, 1, kSaMaxCluster);
+  return (v & (v - 1)) == 0 ? v : kSaMaxCluster;
 }
 
 template <typename... KArgs, typename... Args>
@@ -231,7 +240,7 @@ cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
     attr[n].val.clusterSchedulingPolicyPreference = cudaClusterSchedulingPolicyLoadBalancing;
     ++n;
   }
-  if (pdl_enabled()) {
+  if (cluster >= 0 && pdl_enabled()) {   // cluster < 0: an ordinary, fully serialised launch
     attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[n].val.programmaticStreamSerializationAllowed = 1;
     ++n;
@@ -255,6 +264,13 @@ cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
       return fail(ADAMAS_ERR_CUDA, "%s launch failed: %s", what, cudaGetErrorString(le_));    \
   } while (0)
 
+int log2_exact(int v) {
+  if (v <= 0 || (v & (v - 1)) != 0) return -1;
+  int s = 0;
+  while ((1 << s) < v) ++s;
+  return s;
+}
+
 inline unsigned rows_to_blocks(int64_t rows) { return static_cast<unsigned>((rows * 16 + 255) / 256); }
 
 }  // namespace
@@ -264,25 +280,25 @@ extern "C" {
 int adamas_abi_version(void) { return ADAMAS_ABI_VERSION; }
 
 int adamas_set_pdl(int enable) {
-  g_pdl = enable ? 1 : 0;
+  g_pdl.store(enable ? 1 : 0);
   return ADAMAS_OK;
 }
 
 int adamas_set_fused_append(int enable) {
-  g_fused_append = enable ? 1 : 0;
+  g_fused_append.store(enable ? 1 : 0);
   return ADAMAS_OK;
 }
 
 int adamas_set_estimate_blocks_per_sm(int blocks) {
   ADAMAS_REQUIRE(blocks == 1 || blocks == 2, "blocks per SM must be 1 or 2 (got %d)", blocks);
-  g_est_blocks_per_sm = blocks;
+  g_est_blocks_per_sm.store(blocks);
   return ADAMAS_OK;
 }
 
 int adamas_set_max_cluster(int blocks) {
   ADAMAS_REQUIRE(blocks >= 1 && blocks <= kSaMaxCluster && (blocks & (blocks - 1)) == 0,
                  "cluster size must be a power of two between 1 and %d (got %d)", kSaMaxCluster, blocks);
-  g_max_cluster = blocks;
+  g_max_cluster.store(blocks);
   return ADAMAS_OK;
 }
 
@@ -296,43 +312,6 @@ int adamas_device_error(unsigned* flags, int clear) {
   return ADAMAS_OK;
 }
 const char* adamas_last_error(void) { return g_err; }
-
-#ifdef ADAMAS_PHASE_TIMING
-// Debug builds only: copies the phase-timing table ([2 kernels][512 blocks][16 slots] of nanosecond
-// stamps) to `out`.
-int adamas_debug_read_timing(unsigned long long* out) {
-  ADAMAS_REQUIRE(out, "null pointer");
-  ADAMAS_CUDA(cudaMemcpyFromSymbol(out, g_phase_timing, sizeof(unsigned long long) * 2 * kTimingBlocks * kTimingSlots));
-  return ADAMAS_OK;
-}
-int adamas_debug_read_chain(unsigned long long* out, unsigned* seq) {
-  ADAMAS_CUDA(cudaMemcpyFromSymbol(out, g_chain, sizeof(unsigned long long) * 3 * kChainDepth * 4));
-  ADAMAS_CUDA(cudaMemcpyFromSymbol(seq, g_chain_seq, sizeof(unsigned) * 3));
-  return ADAMAS_OK;
-}
-int adamas_debug_read_trace(unsigned long long* out) {
-  ADAMAS_CUDA(cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * 2 * 64 * 320 * 3));
-  return ADAMAS_OK;
-}
-// Debug builds only: how many clusters of `cluster` select_attend blocks with `smem` bytes of dynamic
-// shared memory can be resident at once.
-int adamas_debug_max_clusters(int cluster, int smem, int grid_blocks, int* out) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid_blocks);
-  cfg.blockDim = dim3(kSaThreads);
-  cfg.dynamicSmemBytes = smem;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = cluster;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  ADAMAS_CUDA(cudaFuncSetAttribute(select_attend_kernel<__half, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-  ADAMAS_CUDA(cudaOccupancyMaxActiveClusters(out, select_attend_kernel<__half, 1>, &cfg));
-  return ADAMAS_OK;
-}
-#endif
 
 // ---------------------------------------------------------------------------------------------
 int adamas_hadamard_transform(const void* x, void* y, int64_t rows, int head_dim, float scale,
@@ -371,22 +350,46 @@ int adamas_bucketize_pack(const void* h, void* codes, int64_t rows, int head_dim
   return check_launch("bucketize_pack_kernel");
 }
 
+// Rotary embedding of the append launch: off, the Llama form with linear position scaling, or a
+// caller-supplied table of 64 rotation frequencies plus a factor on the rotated values (YaRN).
+struct RopeSpec {
+  bool on = false;
+  float scale = 1.f, theta = 1e4f;
+  const float* inv_freq = nullptr;   // device, 64 floats
+  float mscale = 1.f;
+};
+
+// seq_len_dev (optional): the sequence length, new token included, lives on the device; the page
+// counts and last-page lengths are then not used (pass the capacity's) and the slot and the position
+// follow from the device value.
+static RopeSpec linear_rope(float rope_scale, float rope_theta) {
+  RopeSpec r;
+  r.on = true;
+  r.scale = rope_scale;
+  r.theta = rope_theta;
+  return r;
+}
+
 static int append_decode_impl(const void* k, const void* v, const void* qh, const void* kh, bool fused,
                               void* q_code_out, void* kv_data, const int32_t* kv_page_table,
                               int kv_num_pages, int kv_last_page_len, void* code_data,
                               const int32_t* code_page_table, int code_num_pages,
                               int code_last_page_len, int num_heads, int head_dim, int page_size,
                               float scale, const float* thresholds3_host, int dtype,
-                              adamas_stream_t stream, bool rope = false, float rope_scale = 1.f,
-                              float rope_theta = 1e4f) {
+                              adamas_stream_t stream, const RopeSpec& rope = RopeSpec(),
+                              const int32_t* seq_len_dev = nullptr) {
   if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
   ADAMAS_REQUIRE(k && v && qh && kh && q_code_out && kv_data && code_data && kv_page_table &&
                      code_page_table, "null pointer");
-  ADAMAS_REQUIRE(!rope || (rope_scale > 0.f && rope_theta > 0.f), "rope_scale and rope_theta must be positive");
-  ADAMAS_REQUIRE(kv_num_pages >= 1 && code_num_pages >= 1, "page tables must not be empty");
-  ADAMAS_REQUIRE(kv_last_page_len >= 1 && kv_last_page_len <= page_size, "kv_last_page_len out of range");
-  ADAMAS_REQUIRE(code_last_page_len >= 1 && code_last_page_len <= page_size,
-                 "code_last_page_len out of range");
+  ADAMAS_REQUIRE(!rope.on || rope.inv_freq || (rope.scale > 0.f && rope.theta > 0.f),
+                 "rope_scale and rope_theta must be positive");
+  ADAMAS_REQUIRE(!rope.on || fused, "the rotary embedding needs the fused append");
+  if (!seq_len_dev) {
+    ADAMAS_REQUIRE(kv_num_pages >= 1 && code_num_pages >= 1, "page tables must not be empty");
+    ADAMAS_REQUIRE(kv_last_page_len >= 1 && kv_last_page_len <= page_size, "kv_last_page_len out of range");
+    ADAMAS_REQUIRE(code_last_page_len >= 1 && code_last_page_len <= page_size,
+                   "code_last_page_len out of range");
+  }
   PagedTarget tgt{kv_data, kv_page_table, static_cast<uint16_t*>(code_data), code_page_table, page_size,
                   num_heads};
   const Thresholds th = make_thresholds(thresholds3_host);
@@ -396,29 +399,23 @@ static int append_decode_impl(const void* k, const void* v, const void* qh, cons
     const DeviceInfo* di = nullptr;
     if (int rc = get_device_info(&di)) return rc;
   }
-#define LAUNCH_AD(T, F)                                                                         \
-  ADAMAS_LAUNCH("append_decode_kernel", append_decode_kernel<T, F>, dim3(blocks), dim3(256), 0, st, 1, \
-                static_cast<const T*>(k), static_cast<const T*>(v), static_cast<const T*>(qh),  \
-                static_cast<const T*>(kh), static_cast<uint16_t*>(q_code_out), tgt,             \
-                kv_num_pages - 1, kv_last_page_len - 1, code_num_pages - 1,                     \
-                code_last_page_len - 1, scale, th, 0.f, RopeParams{1.f, 1e4f})
-  if (rope) {
-    // position of the token being appended
-    const float pos = static_cast<float>(static_cast<int64_t>(kv_num_pages - 1) * page_size + kv_last_page_len - 1);
-    const RopeParams rp{1.0f / rope_scale, rope_theta};
-#define LAUNCH_AD_ROPE(T)                                                                            \
-  ADAMAS_LAUNCH("append_decode_kernel", (append_decode_kernel<T, true, true>), dim3(blocks), dim3(256), 0, \
+  // position of the token being appended
+  const float pos = static_cast<float>(static_cast<int64_t>(kv_num_pages - 1) * page_size + kv_last_page_len - 1);
+  const RopeParams rp{rope.scale > 0.f ? 1.0f / rope.scale : 1.f, rope.theta, rope.inv_freq, rope.mscale};
+#define LAUNCH_AD(T, F, R)                                                                            \
+  ADAMAS_LAUNCH("append_decode_kernel", (append_decode_kernel<T, F, R>), dim3(blocks), dim3(256), 0,  \
                 st, 1, static_cast<const T*>(k), static_cast<const T*>(v), static_cast<const T*>(qh), \
                 static_cast<const T*>(kh), static_cast<uint16_t*>(q_code_out), tgt, kv_num_pages - 1, \
-                kv_last_page_len - 1, code_num_pages - 1, code_last_page_len - 1, scale, th, pos, rp)
-    if (dtype == ADAMAS_F16) LAUNCH_AD_ROPE(__half); else LAUNCH_AD_ROPE(__nv_bfloat16);
-#undef LAUNCH_AD_ROPE
-    return check_launch("append_decode_kernel");
-  }
+                kv_last_page_len - 1, code_num_pages - 1, code_last_page_len - 1, scale, th, pos, rp, \
+                seq_len_dev)
   if (dtype == ADAMAS_F16) {
-    if (fused) LAUNCH_AD(__half, true); else LAUNCH_AD(__half, false);
+    if (rope.on) LAUNCH_AD(__half, true, true);
+    else if (fused) LAUNCH_AD(__half, true, false);
+    else LAUNCH_AD(__half, false, false);
   } else {
-    if (fused) LAUNCH_AD(__nv_bfloat16, true); else LAUNCH_AD(__nv_bfloat16, false);
+    if (rope.on) LAUNCH_AD(__nv_bfloat16, true, true);
+    else if (fused) LAUNCH_AD(__nv_bfloat16, true, false);
+    else LAUNCH_AD(__nv_bfloat16, false, false);
   }
 #undef LAUNCH_AD
   return check_launch("append_decode_kernel");
@@ -460,7 +457,7 @@ int adamas_append_decode_rope_fused(void* q, void* k, const void* v, void* q_cod
   return append_decode_impl(k, v, q, k, true, q_code_out, kv_data, kv_page_table, kv_num_pages,
                             kv_last_page_len, code_data, code_page_table, code_num_pages,
                             code_last_page_len, num_heads, head_dim, page_size, scale,
-                            thresholds3_host, dtype, stream, true, rope_scale, rope_theta);
+                            thresholds3_host, dtype, stream, linear_rope(rope_scale, rope_theta));
 }
 
 int adamas_apply_rope_in_place(void* q, void* k, int64_t seq_len, int num_q_heads, int num_kv_heads,
@@ -476,7 +473,7 @@ int adamas_apply_rope_in_place(void* q, void* k, int64_t seq_len, int num_q_head
   ADAMAS_REQUIRE(q && k, "null pointer");
   const int64_t rows_q = seq_len * num_q_heads, rows_k = seq_len * num_kv_heads;
   const unsigned blocks = rows_to_blocks(rows_q + rows_k);
-  const RopeParams rp{1.0f / rope_scale, rope_theta};
+  const RopeParams rp{1.0f / rope_scale, rope_theta, nullptr, 1.f};
   if (dtype == ADAMAS_F16)
     rope_kernel<__half><<<blocks, 256, 0, to_stream(stream)>>>(static_cast<__half*>(q), static_cast<__half*>(k),
                                                               rows_q, rows_k, num_q_heads, num_kv_heads,
@@ -531,29 +528,18 @@ int adamas_append_prefill(const void* k, const void* v, const void* h, int64_t n
 }
 
 // ---------------------------------------------------------------------------------------------
-int adamas_estimate(const void* q_code, const void* code_data, const int32_t* code_page_table,
-                    int code_num_pages, int code_last_page_len, int page_size, int num_heads,
-                    int head_dim, void* out, int64_t out_stride, int out_format, int metric,
-                    int exclude_last, adamas_stream_t stream) {
-  if (int rc = check_common(num_heads, head_dim, page_size, ADAMAS_F16)) return rc;
-  ADAMAS_REQUIRE(code_num_pages >= 1, "page table must not be empty");
-  ADAMAS_REQUIRE(code_last_page_len >= 1 && code_last_page_len <= page_size,
-                 "code_last_page_len out of range");
-  ADAMAS_REQUIRE(out_format == ADAMAS_VAL_F16 || out_format == ADAMAS_VAL_U16, "bad out_format %d",
-                 out_format);
-  ADAMAS_REQUIRE(metric == ADAMAS_METRIC_L1 || metric == ADAMAS_METRIC_XOR, "bad metric %d", metric);
-  ADAMAS_REQUIRE(exclude_last == 0 || exclude_last == 1, "exclude_last must be 0 or 1");
-  const int64_t n64 =
-      static_cast<int64_t>(code_num_pages - 1) * page_size + code_last_page_len - exclude_last;
-  ADAMAS_REQUIRE(n64 < (int64_t(1) << 31) - kEstTile * kEstConsumerWarps * 2, "sequence too long");
-  const int n = static_cast<int>(n64);
-  if (n == 0) return ADAMAS_OK;
+// n: distances per head (host mode), or their upper bound when seq_len_dev gives the length on the
+// device (the grid is then sized for n and each block derives its share from the device value).
+static int estimate_impl(const void* q_code, const void* code_data, const int32_t* code_page_table, int n,
+                         int page_size, int num_heads, void* out, int64_t out_stride, int out_format, int metric,
+                         const int32_t* seq_len_dev, uint32_t* hist, int hist_cl, adamas_stream_t stream) {
   ADAMAS_REQUIRE(q_code && code_data && code_page_table && out, "null pointer");
   ADAMAS_REQUIRE(out_stride >= n, "out_stride (%lld) smaller than the row length (%d)",
                  static_cast<long long>(out_stride), n);
   ADAMAS_REQUIRE((reinterpret_cast<uintptr_t>(q_code) & 15) == 0 &&
                      (reinterpret_cast<uintptr_t>(code_data) & 15) == 0,
                  "q_code and code_data must be 16-byte aligned");
+  ADAMAS_REQUIRE(!hist || (hist_cl >= 1 && hist_cl <= kSaMaxSlices), "histogram slices out of range (%d)", hist_cl);
   const DeviceInfo* di = nullptr;
   if (int rc = get_device_info(&di)) return rc;
   cudaStream_t st = to_stream(stream);
@@ -565,11 +551,10 @@ int adamas_estimate(const void* q_code, const void* code_data, const int32_t* co
     const int num_tiles = (pages + ppt - 1) / ppt;
     // spare bytes: a partial last unit reads up to 8 tokens past the valid ones
     const size_t smem = static_cast<size_t>(kEstStages) * ppt * page_bytes + 4096 + 512;
-    constexpr int kPagesStatic = 8448;   // static shared memory of estimate_pages_kernel, rounded up
-    ADAMAS_REQUIRE(smem <= static_cast<size_t>(di->max_smem_optin - 1024 - kPagesStatic),
+    ADAMAS_REQUIRE(smem <= static_cast<size_t>(di->max_smem_optin - 1024 - kEstPagesStatic),
                    "page too large for the estimate kernel");
     const int per_sm = std::min(est_blocks_per_sm(),
-                                (smem + 1024 + kPagesStatic) * 2 <= static_cast<size_t>(di->max_smem_optin) ? 2 : 1);
+                                (smem + 1024 + kEstPagesStatic) * 2 <= static_cast<size_t>(di->max_smem_optin) ? 2 : 1);
     const unsigned blocks = static_cast<unsigned>(std::min(num_tiles, di->num_sms * per_sm));
     EstimatePagesParams pp;
     pp.codes = static_cast<const uint4*>(code_data);
@@ -583,23 +568,11 @@ int adamas_estimate(const void* q_code, const void* code_data, const int32_t* co
     pp.pages_per_tile = ppt;
     pp.num_tiles = num_tiles;
     pp.stage_out = num_heads >= 16 ? 1 : 0;
-#define LAUNCH_ESTP(M, OT)                                                                              \
-  do {                                                                                                  \
-    static bool configured[64] = {};                                                                    \
-    int dev = 0;                                                                                        \
-    ADAMAS_CUDA(cudaGetDevice(&dev));                                                                   \
-    {                                                                                                   \
-      std::lock_guard<std::mutex> lock(g_init_mutex);                                                   \
-      if (!configured[dev & 63]) {                                                                      \
-        ADAMAS_CUDA(cudaFuncSetAttribute(estimate_pages_kernel<M, OT>,                                  \
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, di->max_smem_optin - 1024 - kPagesStatic)); \
-        ADAMAS_CUDA(cudaFuncSetAttribute(estimate_pages_kernel<M, OT>,                                  \
-                                         cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared)); \
-        configured[dev & 63] = true;                                                                    \
-      }                                                                                                 \
-    }                                                                                                   \
-    ADAMAS_LAUNCH("estimate_pages_kernel", (estimate_pages_kernel<M, OT>), dim3(blocks), dim3(kEstThreads), smem, st, 1, pp); \
-  } while (0)
+    pp.seq_len_dev = seq_len_dev;
+    pp.hist = hist;
+    pp.hist_cl = hist_cl;
+#define LAUNCH_ESTP(M, OT) \
+  ADAMAS_LAUNCH("estimate_pages_kernel", (estimate_pages_kernel<M, OT>), dim3(blocks), dim3(kEstThreads), smem, st, 1, pp)
     if (metric == ADAMAS_METRIC_L1) {
       if (out_format == ADAMAS_VAL_F16) LAUNCH_ESTP(0, __half); else LAUNCH_ESTP(0, uint16_t);
     } else {
@@ -631,21 +604,13 @@ int adamas_estimate(const void* q_code, const void* code_data, const int32_t* co
   prm.n_tokens = n;
   prm.H = num_heads;
   prm.page_size = page_size;
-  prm.ps_shift = -1;
-  if ((page_size & (page_size - 1)) == 0) {
-    prm.ps_shift = 0;
-    while ((1 << prm.ps_shift) < page_size) ++prm.ps_shift;
-  }
+  prm.ps_shift = log2_exact(page_size);
   prm.groups = groups;
   prm.num_tiles = num_tiles;
-  prm.trace_tag = 0;
-#ifdef ADAMAS_PHASE_TIMING
-  {
-    static int est_launches = 0;
-    prm.trace_tag = (est_launches++) & 63;
-  }
-#endif
-  #define LAUNCH_EST(M, OT)                                                                      \
+  prm.seq_len_dev = seq_len_dev;
+  prm.hist = hist;
+  prm.hist_cl = hist_cl;
+#define LAUNCH_EST(M, OT)                                                                      \
   do {                                                                                         \
     if (in_regs && hpw == 1)                                                                   \
       ADAMAS_LAUNCH("estimate_kernel", estimate_kernel<M, OT, 1>, dim3(blocks), dim3(kEstThreads), smem, st, 1, prm);                       \
@@ -663,6 +628,26 @@ int adamas_estimate(const void* q_code, const void* code_data, const int32_t* co
   }
 #undef LAUNCH_EST
   return check_launch("estimate_kernel");
+}
+
+int adamas_estimate(const void* q_code, const void* code_data, const int32_t* code_page_table,
+                    int code_num_pages, int code_last_page_len, int page_size, int num_heads,
+                    int head_dim, void* out, int64_t out_stride, int out_format, int metric,
+                    int exclude_last, uint32_t* hist, int hist_slices, adamas_stream_t stream) {
+  if (int rc = check_common(num_heads, head_dim, page_size, ADAMAS_F16)) return rc;
+  ADAMAS_REQUIRE(code_num_pages >= 1, "page table must not be empty");
+  ADAMAS_REQUIRE(code_last_page_len >= 1 && code_last_page_len <= page_size,
+                 "code_last_page_len out of range");
+  ADAMAS_REQUIRE(out_format == ADAMAS_VAL_F16 || out_format == ADAMAS_VAL_U16, "bad out_format %d",
+                 out_format);
+  ADAMAS_REQUIRE(metric == ADAMAS_METRIC_L1 || metric == ADAMAS_METRIC_XOR, "bad metric %d", metric);
+  ADAMAS_REQUIRE(exclude_last == 0 || exclude_last == 1, "exclude_last must be 0 or 1");
+  const int64_t n64 =
+      static_cast<int64_t>(code_num_pages - 1) * page_size + code_last_page_len - exclude_last;
+  ADAMAS_REQUIRE(n64 < (int64_t(1) << 31) - kEstTile * kEstConsumerWarps * 2, "sequence too long");
+  if (n64 == 0) return ADAMAS_OK;
+  return estimate_impl(q_code, code_data, code_page_table, static_cast<int>(n64), page_size, num_heads, out,
+                       out_stride, out_format, metric, nullptr, hist, hist_slices, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -849,8 +834,10 @@ int adamas_decode_begin_forward(adamas_decode_handler_t* handler, int64_t max_to
     handler->num_sms = di->num_sms;
     handler->device = dev;
   }
-  const SplitPlan p = plan_splits(max_tokens, num_heads, handler->num_sms);
-  const int64_t units = static_cast<int64_t>(num_heads) * p.num_splits;
+  // The planner never gives a head more than ceil(4 * SMs / H) splits, so H * splits <= 4 * SMs + H
+  // whatever the length: sized once for that bound, the scratch never has to grow while the head count
+  // stays (a regrow costs a stream synchronisation and a cudaFree / cudaMalloc pair).
+  const int64_t units = static_cast<int64_t>(4) * handler->num_sms + num_heads;
   if (units > handler->cap_units || num_heads > handler->cap_heads) {
     size_t off_ml, off_cnt;
     const int64_t new_units = units > handler->cap_units ? units : handler->cap_units;
@@ -883,11 +870,14 @@ int adamas_decode_end_forward(adamas_decode_handler_t* handler) {
   return ADAMAS_OK;
 }
 
+// seq_len_dev (optional): attend to every token of a sequence whose length lives on the device; indices
+// is then the page table, n_idx / tail_len describe the LONGEST sequence (they size the grid), and the
+// kernel derives the actual lists from the device value.
 static int decode_forward_impl(adamas_decode_handler_t* handler, const void* q, void* o, float* o_f32,
                                float* lse, const void* kv_data, const int32_t* indices,
                                int64_t idx_stride, int n_idx, int idx_unit, int last_page_idx,
                                int last_page_len, int tail_len, float sm_scale,
-                               adamas_stream_t stream) {
+                               adamas_stream_t stream, const int32_t* seq_len_dev = nullptr) {
   ADAMAS_REQUIRE(handler, "null handler");
   if (!handler->forward_started)
     return fail(ADAMAS_ERR_STATE, "decode forward called before begin_forward");
@@ -939,7 +929,9 @@ static int decode_forward_impl(adamas_decode_handler_t* handler, const void* q, 
   prm.partial_ml = reinterpret_cast<float*>(base + off_ml);
   prm.counters = reinterpret_cast<unsigned*>(base + off_cnt);
   prm.scale_log2 = sm_scale * 1.4426950408889634f;
-  const size_t smem = static_cast<size_t>(p.tiles_per_block > 1 ? 2 : 1) * kDecStageBytes;
+  prm.seq_len_dev = seq_len_dev;
+  // (with the length on the device a block may get more than one tile later on: two stages)
+  const size_t smem = static_cast<size_t>(p.tiles_per_block > 1 || seq_len_dev ? 2 : 1) * kDecStageBytes;
   dim3 grid(p.num_splits, H);
   if (handler->dtype == ADAMAS_F16)
     ADAMAS_LAUNCH("sparse_decode_kernel", sparse_decode_kernel<__half>, grid, dim3(kDecThreads), smem,
@@ -1055,6 +1047,7 @@ int adamas_decode_forward_static(const void* q, void* o, float* lse, const void*
   prm.partial_ml = reinterpret_cast<float*>(base + kStaticOffMl);
   prm.counters = reinterpret_cast<unsigned*>(base + kStaticOffCnt);
   prm.scale_log2 = sm_scale * 1.4426950408889634f;
+  prm.seq_len_dev = nullptr;
   const size_t smem = static_cast<size_t>(p.tiles_per_block > 1 ? 2 : 1) * kDecStageBytes;
   dim3 grid(p.num_splits, num_heads);
   if (dtype == ADAMAS_F16)
@@ -1069,35 +1062,29 @@ int adamas_decode_forward_static(const void* q, void* o, float* lse, const void*
 // ---------------------------------------------------------------------------------------------
 namespace {
 
-int log2_exact(int v) {
-  if (v <= 0 || (v & (v - 1)) != 0) return -1;
-  int s = 0;
-  while ((1 << s) < v) ++s;
-  return s;
-}
-
 template <typename T, int I>
 int launch_select_attend_one(const SelectAttendParams& prm, int cl, int num_heads, size_t smem, cudaStream_t st) {
-  static bool configured[64] = {};
-  int dev = 0;
-  ADAMAS_CUDA(cudaGetDevice(&dev));
-  {
-    std::lock_guard<std::mutex> lock(g_init_mutex);
-    if (!configured[dev & 63]) {
-      ADAMAS_CUDA(cudaFuncSetAttribute(select_attend_kernel<T, I>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       160 * 1024));
-      // clusters of 16 blocks (long rows of few heads) are beyond the portable size
-      ADAMAS_CUDA(cudaFuncSetAttribute(select_attend_kernel<T, I>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
-      configured[dev & 63] = true;
-    }
-  }
   const dim3 grid(static_cast<unsigned>(num_heads) * cl);
   ADAMAS_LAUNCH("select_attend_kernel", (select_attend_kernel<T, I>), grid, dim3(kSaThreads), smem, st, cl, prm);
   return check_launch("select_attend_kernel");
 }
 
+template <typename T>
+int launch_select_attend(const SelectAttendParams& prm, int items, int cl, int num_heads, size_t smem,
+                         cudaStream_t st) {
+  switch (items) {
+    case 1: return launch_select_attend_one<T, 1>(prm, cl, num_heads, smem, st);
+    case 2: return launch_select_attend_one<T, 2>(prm, cl, num_heads, smem, st);
+    case 4: return launch_select_attend_one<T, 4>(prm, cl, num_heads, smem, st);
+    case 8: return launch_select_attend_one<T, 8>(prm, cl, num_heads, smem, st);
+    default: break;
+  }
+  return fail(ADAMAS_ERR_INVALID, "unsupported row length for select_attend");
+}
+
 // How many clusters of 16 select_attend blocks with `smem` bytes of dynamic shared memory the device
-// holds at once; 0 if it cannot launch them.  Queried once per device and shared-memory size (in KB).
+// holds at once; 0 if it cannot launch them.  Queried once per device and shared-memory size (in KB);
+// the kernel's attributes have been set by get_device_info.
 int big_cluster_capacity(size_t smem, int* out) {
   static int cap[64][161];
   static bool known[64][161] = {};
@@ -1118,11 +1105,7 @@ int big_cluster_capacity(size_t smem, int* out) {
     cfg.blockDim = dim3(kSaThreads);
     cfg.dynamicSmemBytes = static_cast<size_t>(kb) * 1024;
     int n = 0;
-    cudaError_t e = cudaFuncSetAttribute(select_attend_kernel<__half, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(select_attend_kernel<__half, 2>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-    if (e == cudaSuccess) e = cudaOccupancyMaxActiveClusters(&n, select_attend_kernel<__half, 2>, &cfg);
-    if (e != cudaSuccess) {
+    if (cudaOccupancyMaxActiveClusters(&n, select_attend_kernel<__half, 2>, &cfg) != cudaSuccess) {
       cudaGetLastError();   // not an error of the caller: big clusters are simply not used
       n = 0;
     }
@@ -1133,62 +1116,31 @@ int big_cluster_capacity(size_t smem, int* out) {
   return ADAMAS_OK;
 }
 
-// Shape of a select_attend launch for cl blocks per head: winner-list capacity, attention tile and
-// dynamic shared memory (K and V tile | winner list | rank 0's table of partial results).
-struct SaShape {
-  int granules_per_block, list_capacity, tile_cap;
+// Shape of a select_attend launch: blocks per head (= histogram slices), granules per thread, attention
+// tile, overflow list and dynamic shared memory (K and V tile | overflow list | rank 0's table of
+// partial results).  Planned for rows of up to n distances; shorter rows run in the same shape.
+struct SaPlan {
+  int cl, items, tile_cap, list_capacity;
   size_t smem;
 };
-SaShape sa_shape(int n, int k, int g_total, int cl) {
-  SaShape sh;
-  sh.granules_per_block = (g_total + cl - 1) / cl;
-  const int slice_tokens = std::min(n, sh.granules_per_block * 8);
-  sh.list_capacity = std::min(k, slice_tokens) + 1;
+
+void sa_shape(int n, int k, int cl, SaPlan* pl) {
+  const int slice_tokens = std::min(n, sa_granules_per_block(n, cl) * 8);
+  const int max_loc = std::min(k, slice_tokens) + 1;   // winners of one block at most, plus the newest token
   // Attention tile: the winners spread over the cl slices about evenly (binomially for unordered
-  // data); a tile with room for the mean plus four standard deviations makes a second, serial tile
-  // pass rare.  Lists that exceed the tile are still handled, tile after tile.
-  const int unit = kSaThreads / 8;   // tile sizes: unit (2 tokens per P.V group), 2 * unit, 3 * unit
+  // data); a tile with room for the mean plus four standard deviations makes a second, serial
+  // pass rare.  Lists that exceed the tile are still handled, pass after pass.
+  const int unit = 64;
   const int mean = (k + cl - 1) / cl + 1;
-  const int want = std::min(sh.list_capacity, mean + static_cast<int>(4.0 * std::sqrt(static_cast<double>(mean))) + 8);
-  sh.tile_cap = want <= unit ? unit : (want <= 2 * unit ? 2 * unit : 3 * unit);
-  sh.smem = static_cast<size_t>(2) * sh.tile_cap * 256 +
-            ((static_cast<size_t>(sh.list_capacity) * 4 + 15) & ~static_cast<size_t>(15)) +
-            static_cast<size_t>(cl) * (kHeadDim + 2) * sizeof(float);
-  return sh;
+  const int want = std::min(max_loc, mean + static_cast<int>(4.0 * std::sqrt(static_cast<double>(mean))) + 8);
+  pl->tile_cap = want <= unit ? unit : (want <= 2 * unit ? 2 * unit : 3 * unit);
+  pl->list_capacity = std::max(0, max_loc - pl->tile_cap);
+  pl->smem = static_cast<size_t>(2) * pl->tile_cap * 256 +
+             ((static_cast<size_t>(pl->list_capacity) * 4 + 15) & ~static_cast<size_t>(15)) +
+             static_cast<size_t>(cl) * (kHeadDim + 2) * sizeof(float);
 }
 
-template <typename T>
-int launch_select_attend(const SelectAttendParams& prm, int items, int cl, int num_heads, size_t smem,
-                         cudaStream_t st) {
-  switch (items) {
-    case 1: return launch_select_attend_one<T, 1>(prm, cl, num_heads, smem, st);
-    case 2: return launch_select_attend_one<T, 2>(prm, cl, num_heads, smem, st);
-    case 4: return launch_select_attend_one<T, 4>(prm, cl, num_heads, smem, st);
-    case 8: return launch_select_attend_one<T, 8>(prm, cl, num_heads, smem, st);
-    default: break;
-  }
-  return fail(ADAMAS_ERR_INVALID, "unsupported row length for select_attend");
-}
-
-}  // namespace
-
-extern "C" {
-
-int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, const void* q, void* o,
-                         float* lse, const void* kv_data, const int32_t* kv_page_table, int page_size,
-                         int num_heads, int head_dim, int dtype, int last_page_idx, int last_page_len,
-                         int32_t* out_idx, int64_t out_stride, float sm_scale, adamas_stream_t stream) {
-  if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
-  ADAMAS_REQUIRE(dist && q && o && kv_data && kv_page_table, "null pointer");
-  ADAMAS_REQUIRE(n >= 1 && k >= 1 && k <= n, "need 1 <= k <= n (k=%d, n=%d)", k, n);
-  ADAMAS_REQUIRE((reinterpret_cast<uintptr_t>(dist) & 15) == 0 && (num_heads == 1 || (dist_stride * 2) % 16 == 0),
-                 "distance rows must start on 16-byte boundaries");
-  ADAMAS_REQUIRE(dist_stride >= n || num_heads == 1, "dist_stride smaller than n");
-  ADAMAS_REQUIRE(last_page_idx >= 0 && last_page_len >= 1 && last_page_len <= page_size,
-                 "last page out of range");
-  ADAMAS_REQUIRE(out_idx == nullptr || out_stride >= k || num_heads == 1, "out_stride smaller than k");
-  const int64_t tail = static_cast<int64_t>(last_page_idx) * page_size + last_page_len - 1;
-  ADAMAS_REQUIRE(tail < (int64_t(1) << 31), "token slots must be below 2^31");
+int sa_plan(int n, int k, int num_heads, const DeviceInfo* di, SaPlan* pl) {
   const int g_total = (n + 7) / 8;
   int cl = 0, items = 0;
   const int cl_limit = max_cluster();
@@ -1203,83 +1155,147 @@ int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, co
   }
   ADAMAS_REQUIRE(cl > 0, "select_attend supports at most %d distances per head at cluster size %d (got %d)",
                  cl_limit * 8 * kSaThreads * 8, cl_limit, n);
-  const DeviceInfo* di = nullptr;
-  if (int rc = get_device_info(&di)) return rc;
   if (cl == kSaMaxCluster && items >= 2 && cl_limit == kSaMaxCluster) {
     // A long row (16 or more distances per thread) of few heads (a head-sharded model): most SMs would
     // idle while 8 blocks per head walk their slices.  Sixteen blocks per head halve the slices, as
     // long as all clusters are resident at once.
+    SaPlan big_shape;
+    sa_shape(n, k, kSaBigCluster, &big_shape);
     int big = 0;
-    if (int rc = big_cluster_capacity(sa_shape(n, k, g_total, kSaBigCluster).smem, &big)) return rc;
+    if (int rc = big_cluster_capacity(big_shape.smem, &big)) return rc;
     if (num_heads <= big) {
       cl = kSaBigCluster;
       items /= 2;
     }
   }
-  {
-    // a large budget on a short row: more blocks per head than the scan needs, so that each block
-    // attends to about one tile of winners, as long as all blocks stay resident at once
-    while (cl < cl_limit && k > cl * kSaTile && 2 * cl * num_heads <= 2 * di->num_sms &&
-           (g_total + 2 * cl - 1) / (2 * cl) >= 1)
-      cl *= 2;
-  }
+  // a large budget on a short row: more blocks per head than the scan needs, so that each block
+  // attends to about one tile of winners, as long as all blocks stay resident at once
+  while (cl < cl_limit && k > cl * kSaTile && 2 * cl * num_heads <= 2 * di->num_sms) cl *= 2;
+  pl->cl = cl;
+  pl->items = items;
+  sa_shape(n, k, cl, pl);
+  ADAMAS_REQUIRE(pl->smem <= static_cast<size_t>(kSaMaxDynSmem), "winner list too long for select_attend (k=%d)", k);
+  return ADAMAS_OK;
+}
+
+// n: distances per head, or their upper bound when seq_len_dev is given.
+int select_attend_impl(const void* dist, int64_t dist_stride, int n, int k, const void* q, void* o, float* o_f32,
+                       float* lse, const void* kv_data, const int32_t* kv_page_table, int page_size, int num_heads,
+                       int dtype, int tail_mode, unsigned tail_slot, uint32_t* hist, const int32_t* ext_cut,
+                       const int32_t* seq_len_dev, int32_t* out_idx, int64_t out_stride, float sm_scale,
+                       const SaPlan& pl, adamas_stream_t stream) {
   SelectAttendParams prm;
   prm.dist = static_cast<const uint16_t*>(dist);
   prm.dist_stride = dist_stride;
+  prm.hist = hist;
+  prm.ext_cut = reinterpret_cast<const int2*>(ext_cut);
+  prm.seq_len_dev = seq_len_dev;
   prm.n = n;
   prm.k = k;
   prm.q = q;
   prm.o = o;
+  prm.o_f32 = o_f32;
   prm.lse = lse;
   prm.kv = kv_data;
   prm.kv_table = kv_page_table;
   prm.page_size = page_size;
   prm.ps_shift = log2_exact(page_size);
   prm.H = num_heads;
-  prm.tail_slot = static_cast<unsigned>(tail);
+  prm.tail_mode = tail_mode;
+  prm.tail_slot = tail_slot;
   prm.out_idx = out_idx;
   prm.out_stride = out_stride;
-  const SaShape shape = sa_shape(n, k, g_total, cl);
-  prm.granules_per_block = shape.granules_per_block;
-  prm.list_capacity = shape.list_capacity;
-  prm.tile_cap = shape.tile_cap;
+  prm.list_capacity = pl.list_capacity;
+  prm.tile_cap = pl.tile_cap;
   prm.scale_log2 = sm_scale * 1.4426950408889634f;
-  prm.trace_tag = 0;
-#ifdef ADAMAS_PHASE_TIMING
-  {
-    static int sa_launches = 0;
-    prm.trace_tag = (sa_launches++) & 63;
-  }
-#endif
-  const size_t smem = shape.smem;
-  ADAMAS_REQUIRE(smem <= 160 * 1024, "winner list too long for select_attend (k=%d)", k);
   if (dtype == ADAMAS_F16)
-    return launch_select_attend<__half>(prm, items, cl, num_heads, smem, to_stream(stream));
-  return launch_select_attend<__nv_bfloat16>(prm, items, cl, num_heads, smem, to_stream(stream));
+    return launch_select_attend<__half>(prm, pl.items, pl.cl, num_heads, pl.smem, to_stream(stream));
+  return launch_select_attend<__nv_bfloat16>(prm, pl.items, pl.cl, num_heads, pl.smem, to_stream(stream));
+}
+
+size_t hist_bytes(int num_heads) {
+  return static_cast<size_t>(num_heads) * ADAMAS_HIST_WORDS_PER_HEAD * sizeof(uint32_t);
+}
+
+__global__ void seq_len_advance_kernel(int32_t* seq_len, int delta) { *seq_len += delta; }
+
+}  // namespace
+
+extern "C" {
+
+int adamas_select_attend_slices(int n, int k, int num_heads, int* slices) {
+  ADAMAS_REQUIRE(slices, "null pointer");
+  ADAMAS_REQUIRE(n >= 1 && k >= 1 && k <= n && num_heads >= 1, "need 1 <= k <= n (k=%d, n=%d)", k, n);
+  const DeviceInfo* di = nullptr;
+  if (int rc = get_device_info(&di)) return rc;
+  SaPlan pl;
+  if (int rc = sa_plan(n, k, num_heads, di, &pl)) return rc;
+  *slices = pl.cl;
+  return ADAMAS_OK;
+}
+
+int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, const void* q, void* o,
+                         float* o_f32, float* lse, const void* kv_data, const int32_t* kv_page_table,
+                         int page_size, int num_heads, int head_dim, int dtype, int last_page_idx,
+                         int last_page_len, uint32_t* hist, int hist_ready, const int32_t* ext_cut,
+                         int32_t* out_idx, int64_t out_stride, float sm_scale, adamas_stream_t stream) {
+  if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
+  ADAMAS_REQUIRE(dist && q && (o || o_f32) && kv_data && kv_page_table && hist, "null pointer");
+  ADAMAS_REQUIRE(!o_f32 || lse, "a partial result (o_f32) needs lse");
+  ADAMAS_REQUIRE(n >= 1 && k >= 1 && k <= n, "need 1 <= k <= n (k=%d, n=%d)", k, n);
+  ADAMAS_REQUIRE((reinterpret_cast<uintptr_t>(dist) & 15) == 0 && (num_heads == 1 || (dist_stride * 2) % 16 == 0),
+                 "distance rows must start on 16-byte boundaries");
+  ADAMAS_REQUIRE(dist_stride >= n || num_heads == 1, "dist_stride smaller than n");
+  ADAMAS_REQUIRE(last_page_idx >= 0 && last_page_len >= 0 && last_page_len <= page_size,
+                 "last page out of range");
+  ADAMAS_REQUIRE(out_idx == nullptr || out_stride >= k || num_heads == 1, "out_stride smaller than k");
+  ADAMAS_REQUIRE((reinterpret_cast<uintptr_t>(ext_cut) & 7) == 0, "ext_cut must be 8-byte aligned");
+  const int64_t tail = static_cast<int64_t>(last_page_idx) * page_size + last_page_len - 1;
+  ADAMAS_REQUIRE(tail < (int64_t(1) << 31), "token slots must be below 2^31");
+  const DeviceInfo* di = nullptr;
+  if (int rc = get_device_info(&di)) return rc;
+  SaPlan pl;
+  if (int rc = sa_plan(n, k, num_heads, di, &pl)) return rc;
+  if (!hist_ready) {
+    DistHistogramParams hp;
+    hp.dist = static_cast<const uint16_t*>(dist);
+    hp.dist_stride = dist_stride;
+    hp.hist = hist;
+    hp.n = n;
+    hp.cl = pl.cl;
+    ADAMAS_LAUNCH("dist_histogram_kernel", dist_histogram_kernel, dim3(pl.cl, num_heads), dim3(kSaThreads), 0,
+                  to_stream(stream), 1, hp);
+  }
+  return select_attend_impl(dist, dist_stride, n, k, q, o, o_f32, lse, kv_data, kv_page_table, page_size, num_heads,
+                            dtype, last_page_len > 0 ? 1 : 0, static_cast<unsigned>(std::max<int64_t>(tail, 0)), hist,
+                            ext_cut, nullptr, out_idx, out_stride, sm_scale, pl, stream);
+}
+
+int adamas_seq_len_advance(int32_t* seq_len_dev, int delta, adamas_stream_t stream) {
+  ADAMAS_REQUIRE(seq_len_dev, "null pointer");
+  // an ordinary launch: it completes before anything that follows it in the stream starts
+  ADAMAS_LAUNCH("seq_len_advance_kernel", seq_len_advance_kernel, dim3(1), dim3(1), 0, to_stream(stream), -1,
+                seq_len_dev, delta);
+  return check_launch("seq_len_advance_kernel");
 }
 
 // Stages 1 + 2 of a decode step in one launch (estimate_append_kernel); the caller has checked that
-// num_heads is 16, 32 or 64.
+// num_heads is 16, 32 or 64.  n: distances per head (host mode) or their upper bound (seq_len_dev).
 static int estimate_append_launch(const void* q, const void* k, const void* v, void* q_code, void* kv_data,
                                   const int32_t* kv_page_table, int kv_num_pages, int kv_last_page_len,
                                   void* code_data, const int32_t* code_page_table, int code_num_pages,
-                                  int code_last_page_len, int num_heads, int page_size, int dtype, void* dist,
+                                  int code_last_page_len, int n, int num_heads, int page_size, int dtype, void* dist,
                                   int64_t dist_stride, float hadamard_scale, const float* thresholds3_host,
-                                  adamas_stream_t stream) {
+                                  const int32_t* seq_len_dev, uint32_t* hist, int hist_cl, adamas_stream_t stream) {
   ADAMAS_REQUIRE(q && k && v && q_code && kv_data && code_data && kv_page_table && code_page_table && dist,
                  "null pointer");
-  ADAMAS_REQUIRE(kv_num_pages >= 1 && code_num_pages >= 1, "page tables must not be empty");
-  ADAMAS_REQUIRE(kv_last_page_len >= 1 && kv_last_page_len <= page_size, "kv_last_page_len out of range");
-  ADAMAS_REQUIRE(code_last_page_len >= 1 && code_last_page_len <= page_size,
-                 "code_last_page_len out of range");
-  const int64_t n64 = static_cast<int64_t>(code_num_pages - 1) * page_size + code_last_page_len - 1;
-  ADAMAS_REQUIRE(n64 >= 1 && n64 < (int64_t(1) << 31) - kEstTile, "sequence length out of range");
-  const int n = static_cast<int>(n64);
+  ADAMAS_REQUIRE(n >= 1 && n < 2147483647 - kEstTile, "sequence length out of range");
   ADAMAS_REQUIRE(dist_stride >= n, "dist_stride (%lld) smaller than the row length (%d)",
                  static_cast<long long>(dist_stride), n);
   ADAMAS_REQUIRE((reinterpret_cast<uintptr_t>(code_data) & 15) == 0 && (reinterpret_cast<uintptr_t>(q) & 15) == 0 &&
                      (reinterpret_cast<uintptr_t>(k) & 15) == 0 && (reinterpret_cast<uintptr_t>(v) & 15) == 0,
                  "q, k, v and code_data must be 16-byte aligned");
+  ADAMAS_REQUIRE(!hist || (hist_cl >= 1 && hist_cl <= kSaMaxSlices), "histogram slices out of range (%d)", hist_cl);
   const DeviceInfo* di = nullptr;
   if (int rc = get_device_info(&di)) return rc;
   const int num_tiles = (n + kEstTile - 1) / kEstTile;
@@ -1302,7 +1318,9 @@ static int estimate_append_launch(const void* q, const void* k, const void* v, v
   prm.ps_shift = log2_exact(page_size);
   prm.groups = 1;
   prm.num_tiles = num_tiles;
-  prm.trace_tag = 0;
+  prm.seq_len_dev = seq_len_dev;
+  prm.hist = hist;
+  prm.hist_cl = hist_cl;
   StepAppend ap;
   ap.q = q;
   ap.k = k;
@@ -1337,14 +1355,80 @@ int adamas_append_estimate(const void* q, const void* k, const void* v, void* q_
                            void* code_data, const int32_t* code_page_table, int code_num_pages,
                            int code_last_page_len, int num_heads, int head_dim, int page_size, int dtype,
                            void* dist, int64_t dist_stride, float hadamard_scale,
-                           const float* thresholds3_host, adamas_stream_t stream) {
+                           const float* thresholds3_host, uint32_t* hist, int hist_slices,
+                           adamas_stream_t stream) {
   if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
   ADAMAS_REQUIRE(num_heads == 16 || num_heads == 32 || num_heads == 64,
                  "adamas_append_estimate supports 16, 32 or 64 heads (got %d); use adamas_append_decode_fused "
                  "and adamas_estimate", num_heads);
+  ADAMAS_REQUIRE(kv_num_pages >= 1 && code_num_pages >= 1, "page tables must not be empty");
+  ADAMAS_REQUIRE(kv_last_page_len >= 1 && kv_last_page_len <= page_size, "kv_last_page_len out of range");
+  ADAMAS_REQUIRE(code_last_page_len >= 1 && code_last_page_len <= page_size,
+                 "code_last_page_len out of range");
+  const int64_t n64 = static_cast<int64_t>(code_num_pages - 1) * page_size + code_last_page_len - 1;
+  ADAMAS_REQUIRE(n64 >= 1 && n64 < (int64_t(1) << 31) - kEstTile, "sequence length out of range");
   return estimate_append_launch(q, k, v, q_code, kv_data, kv_page_table, kv_num_pages, kv_last_page_len,
-                                code_data, code_page_table, code_num_pages, code_last_page_len, num_heads,
-                                page_size, dtype, dist, dist_stride, hadamard_scale, thresholds3_host, stream);
+                                code_data, code_page_table, code_num_pages, code_last_page_len,
+                                static_cast<int>(n64), num_heads, page_size, dtype, dist, dist_stride,
+                                hadamard_scale, thresholds3_host, nullptr, hist, hist_slices, stream);
+}
+
+// One layer's decode step.  Host mode (seq_len_dev null): seq_len tokens are in the caches, the newest
+// included.  Device mode: *seq_len_dev holds that number and seq_len is its upper bound, which sizes the
+// launches.
+static int decode_step_impl(void* q, void* k, const void* v, void* o, float* lse, void* q_code, void* kv_data,
+                            const int32_t* kv_page_table, int kv_last_page_idx, void* code_data,
+                            const int32_t* code_page_table, int64_t seq_len, const int32_t* seq_len_dev,
+                            int num_heads, int head_dim, int page_size, int dtype, int budget, void* dist_scratch,
+                            int64_t dist_stride, uint32_t* hist, int32_t* out_idx, int64_t out_stride,
+                            float hadamard_scale, const float* thresholds3_host, const RopeSpec& rope,
+                            float sm_scale, adamas_stream_t stream) {
+  if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
+  ADAMAS_REQUIRE(kv_page_table && code_page_table, "page table missing");
+  ADAMAS_REQUIRE(budget >= 2 && seq_len > budget,
+                 "a decode step needs budget >= 2 and a context longer than the budget (%lld vs %d); "
+                 "shorter contexts attend to every page through adamas_decode_forward",
+                 static_cast<long long>(seq_len), budget);
+  ADAMAS_REQUIRE(seq_len - 1 < (int64_t(1) << 31) - kEstTile * kEstConsumerWarps * 2, "sequence too long");
+  ADAMAS_REQUIRE(q && o && dist_scratch && q_code && hist, "null pointer");
+  ADAMAS_REQUIRE((reinterpret_cast<uintptr_t>(dist_scratch) & 15) == 0 && (dist_stride * 2) % 16 == 0,
+                 "distance rows must start on 16-byte boundaries");
+  ADAMAS_REQUIRE(out_idx == nullptr || out_stride >= budget - 1 || num_heads == 1, "out_stride smaller than budget - 1");
+  const int n = static_cast<int>(seq_len - 1);
+  const int pages = static_cast<int>((seq_len + page_size - 1) / page_size);
+  const int last_len = static_cast<int>(seq_len - static_cast<int64_t>(pages - 1) * page_size);
+  const DeviceInfo* di = nullptr;
+  if (int rc = get_device_info(&di)) return rc;
+  SaPlan pl;
+  if (int rc = sa_plan(n, budget - 1, num_heads, di, &pl)) return rc;
+  int rc;
+  // (16 heads: the page-copy estimate after a separate append is faster than the fused kernel's 512-byte
+  // copies per token)
+  if (fused_append_enabled() && !rope.on && (num_heads == 32 || num_heads == 64)) {
+    // two launches: the estimate with the append inside, then select + attend.  Not with RoPE: every
+    // block of the estimate would repeat the rotation, which costs more than the append launch.
+    rc = estimate_append_launch(q, k, v, q_code, kv_data, kv_page_table, pages, last_len, code_data,
+                                code_page_table, pages, last_len, n, num_heads, page_size, dtype, dist_scratch,
+                                dist_stride, hadamard_scale, thresholds3_host, seq_len_dev, hist, pl.cl, stream);
+    if (rc) return rc;
+  } else {
+    rc = append_decode_impl(k, v, q, k, true, q_code, kv_data, kv_page_table, pages, last_len, code_data,
+                            code_page_table, pages, last_len, num_heads, head_dim, page_size, hadamard_scale,
+                            thresholds3_host, dtype, stream, rope, seq_len_dev);
+    if (rc) return rc;
+    rc = estimate_impl(q_code, code_data, code_page_table, n, page_size, num_heads, dist_scratch, dist_stride,
+                       ADAMAS_VAL_U16, ADAMAS_METRIC_L1, seq_len_dev, hist, pl.cl, stream);
+    if (rc) return rc;
+  }
+  const int64_t tail = static_cast<int64_t>(kv_last_page_idx) * page_size + last_len - 1;
+  rc = select_attend_impl(dist_scratch, dist_stride, n, budget - 1, q, o, nullptr, lse, kv_data, kv_page_table,
+                          page_size, num_heads, dtype, seq_len_dev ? 2 : 1, static_cast<unsigned>(tail), hist, nullptr,
+                          seq_len_dev, out_idx, out_stride, sm_scale, pl, stream);
+  if (rc) {
+    // the estimate has filled the histogram table and nothing will clear it: restore the all-zero state
+    cudaMemsetAsync(hist, 0, hist_bytes(num_heads), to_stream(stream));
+  }
+  return rc;
 }
 
 int adamas_decode_step(void* q, void* k, const void* v, void* o, float* lse, void* q_code,
@@ -1352,52 +1436,100 @@ int adamas_decode_step(void* q, void* k, const void* v, void* o, float* lse, voi
                        int kv_last_page_len, int kv_last_page_idx, void* code_data,
                        const int32_t* code_page_table, int code_num_pages, int code_last_page_len,
                        int num_heads, int head_dim, int page_size, int dtype, int budget,
-                       void* dist_scratch, int64_t dist_stride, int32_t* out_idx, int64_t out_stride,
-                       float hadamard_scale, const float* thresholds3_host, float rope_scale,
-                       float rope_theta, float sm_scale, adamas_stream_t stream) {
-  ADAMAS_REQUIRE(kv_num_pages >= 1 && kv_page_table, "page table missing");
+                       void* dist_scratch, int64_t dist_stride, uint32_t* hist_scratch, int32_t* out_idx,
+                       int64_t out_stride, float hadamard_scale, const float* thresholds3_host,
+                       float rope_scale, float rope_theta, float sm_scale, adamas_stream_t stream) {
+  ADAMAS_REQUIRE(kv_num_pages >= 1 && code_num_pages >= 1, "page tables must not be empty");
   ADAMAS_REQUIRE(page_size >= 1, "page_size must be >= 1");
+  ADAMAS_REQUIRE(kv_last_page_len >= 1 && kv_last_page_len <= page_size, "kv_last_page_len out of range");
+  ADAMAS_REQUIRE(kv_num_pages == code_num_pages && kv_last_page_len == code_last_page_len,
+                 "the KV cache and the code cache must hold the same number of tokens");
+  ADAMAS_REQUIRE(kv_last_page_idx >= 0, "kv_last_page_idx must be >= 0");
   const int64_t seq_len = static_cast<int64_t>(kv_num_pages - 1) * page_size + kv_last_page_len;
-  ADAMAS_REQUIRE(budget >= 2 && seq_len > budget,
-                 "adamas_decode_step needs budget >= 2 and a context longer than the budget (%lld vs %d); "
-                 "shorter contexts attend to every page through adamas_decode_forward",
-                 static_cast<long long>(seq_len), budget);
-  ADAMAS_REQUIRE(seq_len - 1 < (int64_t(1) << 31), "sequence too long");
-  ADAMAS_REQUIRE(dist_scratch && q_code, "null pointer");
-  // (16 heads: the page-copy estimate after a separate append is faster than the fused kernel's 512-byte
-  // copies per token)
-  if (fused_append_enabled() && rope_scale <= 0.f && (num_heads == 32 || num_heads == 64) &&
-      head_dim == kHeadDim && (dtype == ADAMAS_F16 || dtype == ADAMAS_BF16)) {
-    // two launches: the estimate with the append inside, then select + attend.  Not with RoPE: every
-    // block of the estimate would repeat the rotation, which costs more than the append launch.
-    ADAMAS_REQUIRE(q && o, "null pointer");
-    if (int rc = estimate_append_launch(q, k, v, q_code, kv_data, kv_page_table, kv_num_pages, kv_last_page_len,
-                                        code_data, code_page_table, code_num_pages, code_last_page_len,
-                                        num_heads, page_size, dtype, dist_scratch, dist_stride, hadamard_scale,
-                                        thresholds3_host, stream))
-      return rc;
-    return adamas_select_attend(dist_scratch, dist_stride, static_cast<int>(seq_len - 1), budget - 1, q, o, lse,
-                                kv_data, kv_page_table, page_size, num_heads, head_dim, dtype, kv_last_page_idx,
-                                kv_last_page_len, out_idx, out_stride, sm_scale, stream);
+  RopeSpec rope;
+  if (rope_scale > 0.f) rope = linear_rope(rope_scale, rope_theta);
+  return decode_step_impl(q, k, v, o, lse, q_code, kv_data, kv_page_table, kv_last_page_idx, code_data,
+                          code_page_table, seq_len, nullptr, num_heads, head_dim, page_size, dtype, budget,
+                          dist_scratch, dist_stride, hist_scratch, out_idx, out_stride, hadamard_scale,
+                          thresholds3_host, rope, sm_scale, stream);
+}
+
+static RopeSpec rope_from_args(float rope_scale, float rope_theta, const float* rope_inv_freq, float rope_mscale) {
+  RopeSpec rope;
+  if (rope_inv_freq) {
+    rope.on = true;
+    rope.inv_freq = rope_inv_freq;
+    rope.mscale = rope_mscale;
+  } else if (rope_scale > 0.f) {
+    rope = linear_rope(rope_scale, rope_theta);
   }
-  if (int rc = rope_scale > 0.f
-                   ? adamas_append_decode_rope_fused(q, k, v, q_code, kv_data, kv_page_table, kv_num_pages,
-                                                     kv_last_page_len, code_data, code_page_table,
-                                                     code_num_pages, code_last_page_len, num_heads, head_dim,
-                                                     page_size, hadamard_scale, thresholds3_host, rope_scale,
-                                                     rope_theta, dtype, stream)
-                   : adamas_append_decode_fused(q, k, v, q_code, kv_data, kv_page_table, kv_num_pages,
-                                                kv_last_page_len, code_data, code_page_table, code_num_pages,
-                                                code_last_page_len, num_heads, head_dim, page_size,
-                                                hadamard_scale, thresholds3_host, dtype, stream))
+  return rope;
+}
+
+int adamas_decode_step_dev(void* q, void* k, const void* v, void* o, float* lse, void* q_code, void* kv_data,
+                           const int32_t* kv_page_table, void* code_data, const int32_t* code_page_table,
+                           const int32_t* seq_len_dev, int max_seq_len, int num_heads, int head_dim,
+                           int page_size, int dtype, int budget, void* dist_scratch, int64_t dist_stride,
+                           uint32_t* hist_scratch, int32_t* out_idx, int64_t out_stride, float hadamard_scale,
+                           const float* thresholds3_host, float rope_scale, float rope_theta,
+                           const float* rope_inv_freq, float rope_mscale, float sm_scale,
+                           adamas_stream_t stream) {
+  ADAMAS_REQUIRE(seq_len_dev, "null pointer");
+  ADAMAS_REQUIRE(page_size >= 1 && max_seq_len >= 1, "page_size and max_seq_len must be >= 1");
+  return decode_step_impl(q, k, v, o, lse, q_code, kv_data, kv_page_table, 0, code_data, code_page_table,
+                          max_seq_len, seq_len_dev, num_heads, head_dim, page_size, dtype, budget, dist_scratch,
+                          dist_stride, hist_scratch, out_idx, out_stride, hadamard_scale, thresholds3_host,
+                          rope_from_args(rope_scale, rope_theta, rope_inv_freq, rope_mscale), sm_scale, stream);
+}
+
+int adamas_dense_step_dev(adamas_decode_handler_t* handler, void* q, void* k, const void* v, void* o, float* lse,
+                          void* q_code, void* kv_data, const int32_t* kv_page_table, void* code_data,
+                          const int32_t* code_page_table, const int32_t* seq_len_dev, int max_seq_len,
+                          int num_heads, int head_dim, int page_size, int dtype, float hadamard_scale,
+                          const float* thresholds3_host, float rope_scale, float rope_theta,
+                          const float* rope_inv_freq, float rope_mscale, float sm_scale,
+                          adamas_stream_t stream) {
+  ADAMAS_REQUIRE(handler && seq_len_dev, "null pointer");
+  if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
+  ADAMAS_REQUIRE(max_seq_len >= 1, "max_seq_len must be >= 1");
+  ADAMAS_REQUIRE(q && k && v && o && q_code, "null pointer");
+  if (!handler->forward_started)
+    return fail(ADAMAS_ERR_STATE, "dense step called before begin_forward");
+  ADAMAS_REQUIRE(handler->num_heads == num_heads && handler->page_size == page_size && handler->dtype == dtype,
+                 "the handler was planned for another cache geometry");
+  const int pages = (max_seq_len + page_size - 1) / page_size;
+  const int last_len = max_seq_len - (pages - 1) * page_size;
+  if (int rc = append_decode_impl(k, v, q, k, true, q_code, kv_data, kv_page_table, pages, last_len, code_data,
+                                  code_page_table, pages, last_len, num_heads, head_dim, page_size, hadamard_scale,
+                                  thresholds3_host, dtype, stream,
+                                  rope_from_args(rope_scale, rope_theta, rope_inv_freq, rope_mscale), seq_len_dev))
     return rc;
-  if (int rc = adamas_estimate(q_code, code_data, code_page_table, code_num_pages, code_last_page_len,
-                               page_size, num_heads, head_dim, dist_scratch, dist_stride, ADAMAS_VAL_U16,
-                               ADAMAS_METRIC_L1, 1, stream))
-    return rc;
-  return adamas_select_attend(dist_scratch, dist_stride, static_cast<int>(seq_len - 1), budget - 1, q, o,
-                              lse, kv_data, kv_page_table, page_size, num_heads, head_dim, dtype,
-                              kv_last_page_idx, kv_last_page_len, out_idx, out_stride, sm_scale, stream);
+  return decode_forward_impl(handler, q, o, nullptr, lse, kv_data, kv_page_table, 0, pages - 1, page_size, 0,
+                             last_len, last_len, sm_scale, stream, seq_len_dev);
+}
+
+int adamas_apply_rope_table_in_place(void* q, void* k, int64_t seq_len, int num_q_heads, int num_kv_heads,
+                                     int head_dim, int64_t past_kv_len, const float* inv_freq_dev, float mscale,
+                                     int dtype, adamas_stream_t stream) {
+  ADAMAS_REQUIRE(head_dim == kHeadDim, "head_dim must be 128 (got %d)", head_dim);
+  ADAMAS_REQUIRE(dtype == ADAMAS_F16 || dtype == ADAMAS_BF16, "unsupported dtype %d", dtype);
+  ADAMAS_REQUIRE(seq_len >= 0 && num_q_heads >= 1 && num_kv_heads >= 1, "bad shape");
+  ADAMAS_REQUIRE(past_kv_len >= 0 && past_kv_len + seq_len < (int64_t(1) << 24),
+                 "positions must stay below 2^24 (exact in fp32)");
+  if (seq_len == 0) return ADAMAS_OK;
+  ADAMAS_REQUIRE(q && k && inv_freq_dev, "null pointer");
+  const int64_t rows_q = seq_len * num_q_heads, rows_k = seq_len * num_kv_heads;
+  const unsigned blocks = rows_to_blocks(rows_q + rows_k);
+  const RopeParams rp{1.f, 1e4f, inv_freq_dev, mscale};
+  if (dtype == ADAMAS_F16)
+    rope_kernel<__half><<<blocks, 256, 0, to_stream(stream)>>>(static_cast<__half*>(q), static_cast<__half*>(k),
+                                                              rows_q, rows_k, num_q_heads, num_kv_heads,
+                                                              static_cast<int>(past_kv_len), rp);
+  else
+    rope_kernel<__nv_bfloat16><<<blocks, 256, 0, to_stream(stream)>>>(
+        static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k), rows_q, rows_k, num_q_heads,
+        num_kv_heads, static_cast<int>(past_kv_len), rp);
+  return check_launch("rope_kernel");
 }
 
 int adamas_merge_states(const float* o_parts, const float* lse_parts, int num_parts, int num_heads,

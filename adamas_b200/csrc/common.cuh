@@ -142,70 +142,7 @@ __device__ unsigned g_adamas_error = 0;
 constexpr unsigned kErrEstimateTimeout = 1u;
 constexpr unsigned kErrDecodeTimeout = 2u;
 constexpr unsigned kErrGatherTimeout = 4u;
-
-// ---- optional phase timing (compile with -DADAMAS_PHASE_TIMING; off in the product build) --------
-// One thread per block stamps the global nanosecond timer at phase boundaries into a fixed table that
-// adamas_debug_read_timing() copies out; each launch overwrites the last.  Used to see where a
-// latency-bound kernel spends its time without a profiler.
-#ifdef ADAMAS_PHASE_TIMING
-constexpr int kTimingBlocks = 512;
-constexpr int kTimingSlots = 16;
-__device__ unsigned long long g_phase_timing[2][kTimingBlocks][kTimingSlots];
-__device__ __forceinline__ void phase_stamp(int kernel_id, int slot) {
-  if (blockIdx.x < kTimingBlocks && slot < kTimingSlots) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_phase_timing[kernel_id][blockIdx.x][slot] = t;
-  }
-}
-#define ADAMAS_STAMP(kernel_id, slot, cond) \
-  do {                                      \
-    if (cond) phase_stamp(kernel_id, slot); \
-  } while (0)
-// Chain view: thread 0 of block 0 of each kernel keeps its stamps of the last 128 launches.
-constexpr int kChainDepth = 128;
-__device__ unsigned long long g_chain[3][kChainDepth][4];
-__device__ unsigned g_chain_seq[3];
-__device__ __forceinline__ void chain_stamp(int kernel_id, int slot, bool last) {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  const unsigned seq = g_chain_seq[kernel_id];
-  g_chain[kernel_id][seq % kChainDepth][slot] = t;
-  if (last) g_chain_seq[kernel_id] = seq + 1;
-}
-#define ADAMAS_CHAIN(kernel_id, slot, last, cond)   \
-  do {                                              \
-    if (cond) chain_stamp(kernel_id, slot, last);   \
-  } while (0)
-// Placement trace: per launch tag (< 64) and block (< 320): entry time, end time, SM id.
-__device__ unsigned long long g_trace[2][64][320][3];
-__device__ __forceinline__ void trace_stamp(int kernel_id, int tag, int slot) {
-  if (tag >= 0 && tag < 64 && blockIdx.x < 320) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_trace[kernel_id][tag][blockIdx.x][slot] = t;
-    if (slot == 0) {
-      unsigned smid;
-      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-      g_trace[kernel_id][tag][blockIdx.x][2] = smid;
-    }
-  }
-}
-#define ADAMAS_TRACE(kernel_id, tag, slot, cond)    \
-  do {                                              \
-    if (cond) trace_stamp(kernel_id, tag, slot);    \
-  } while (0)
-#else
-#define ADAMAS_TRACE(kernel_id, tag, slot, cond) \
-  do {                                           \
-  } while (0)
-#define ADAMAS_CHAIN(kernel_id, slot, last, cond) \
-  do {                                            \
-  } while (0)
-#define ADAMAS_STAMP(kernel_id, slot, cond) \
-  do {                                      \
-  } while (0)
-#endif
+constexpr unsigned kErrHistogram = 8u;   // select_attend found histograms that do not describe its row
 
 struct Thresholds {
   float t0, t1, t2;

@@ -18,6 +18,7 @@
 #pragma once
 #include "common.cuh"
 #include "hadamard_append.cuh"
+#include "select_attend.cuh"
 
 namespace adamas {
 
@@ -95,8 +96,39 @@ struct EstimateParams {
   int groups;       // token groups of 32 per tile: 1, or 2 * 16 / H for H < 16 (generic kernel only): each
                     // of the 16 consumer warps takes one head of two token groups
   int num_tiles;
-  int trace_tag;    // launch number, used by builds with phase timing only
+  // optional: the sequence length (tokens, the newest included) lives on the device; n_tokens is then
+  // *seq_len_dev - 1 and num_tiles follows from it (the host values above are upper bounds that size
+  // the grid).  Read before the kernel's dependency resolves: the value must be final before the
+  // kernel that precedes this one in the stream starts.
+  const int32_t* seq_len_dev;
+  // optional: per-slice histograms of the distance rows for select_attend, table [H][kSaMaxSlices][512]
+  // u32, zero on entry; slice = token / (8 * sa_granules_per_block(n_tokens, hist_cl))
+  uint32_t* hist;
+  int hist_cl;
 };
+
+// Lengths of this launch, from the host or from the device-resident sequence length.
+struct EstGeom {
+  int n_tokens;
+  int num_tiles;
+  int slice_tokens;   // tokens per histogram slice (a multiple of 32)
+};
+__device__ __forceinline__ EstGeom est_geom(const EstimateParams& p, int tile_span) {
+  EstGeom g;
+  g.n_tokens = p.n_tokens;
+  g.num_tiles = p.num_tiles;
+  if (p.seq_len_dev) {
+    g.n_tokens = __ldg(p.seq_len_dev) - 1;
+    g.num_tiles = (g.n_tokens + tile_span - 1) / tile_span;
+  }
+  g.slice_tokens = p.hist ? 8 * sa_granules_per_block(g.n_tokens, p.hist_cl) : 1;
+  return g;
+}
+
+__device__ __forceinline__ void hist_count(uint32_t* hist, int head, int slice, unsigned d) {
+  uint32_t* a = hist + ((static_cast<size_t>(head) * kSaMaxSlices + slice) << 9) + d;
+  asm volatile("red.global.add.u32 [%0], 1;" ::"l"(a) : "memory");
+}
 
 // ---- the two halves of the copy pipeline, shared by the kernels below --------------------------------
 // Geometry of the ring for H heads: a token's codes are 2H 16-byte chunks, padded by one chunk so
@@ -110,22 +142,23 @@ struct EstRing {
   int stage_chunks;   // chunks per ring slot
 };
 
-__device__ __forceinline__ int est_tiles_of_block(const EstimateParams& p) {
-  return (p.num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
-         static_cast<int>(gridDim.x);
+__device__ __forceinline__ int est_tiles_of_block(int num_tiles) {
+  return max(0, (num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                    static_cast<int>(gridDim.x));
 }
 
 // Producer warp: one bulk copy per token (its H codes) into the padded ring slot.  GROUPED: a tile
 // holds p.groups groups of 32 tokens and a lane issues one copy per group.
 template <bool GROUPED>
-__device__ __forceinline__ void est_produce(const EstimateParams& p, const EstRing& r, int my_tiles, int lane) {
+__device__ __forceinline__ void est_produce(const EstimateParams& p, const EstGeom& g, const EstRing& r, int my_tiles,
+                                            int lane) {
   const unsigned token_bytes = static_cast<unsigned>(r.cpt) * 16u;
   const int tile_span = GROUPED ? kEstTile * p.groups : kEstTile;
   int slot = 0;
   unsigned parity = 0;   // parity of the previous use of the slot, for the empty barrier
   for (int j = 0; j < my_tiles; ++j) {
     const int tile0 = (blockIdx.x + j * gridDim.x) * tile_span;
-    const int tile_tokens = min(tile_span, p.n_tokens - tile0);
+    const int tile_tokens = min(tile_span, g.n_tokens - tile0);
     if (j >= kEstStages) {
       // every consumer warp has finished reading the tile that used this slot before
       if (!mbar_wait_bounded(&r.empty_bar[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
@@ -156,8 +189,8 @@ __device__ __forceinline__ void est_produce(const EstimateParams& p, const EstRi
 // Consumer warp: lane = token of the tile; the warp covers heads warp*HPW .. (query planes in
 // registers, HPW > 0) or heads warp, warp + 16, ... (planes `sq` in shared memory, HPW == 0).
 template <int METRIC, typename OutT, int HPW>
-__device__ __forceinline__ void est_consume(const EstimateParams& p, const EstRing& r, int my_tiles, int lane,
-                                            int warp, const QPlanes (&qp)[HPW > 0 ? HPW : 1][2],
+__device__ __forceinline__ void est_consume(const EstimateParams& p, const EstGeom& g, const EstRing& r, int my_tiles,
+                                            int lane, int warp, const QPlanes (&qp)[HPW > 0 ? HPW : 1][2],
                                             const QPlanes* sq) {
   OutT* out = static_cast<OutT*>(p.out);
   const int H = p.H;
@@ -166,7 +199,8 @@ __device__ __forceinline__ void est_consume(const EstimateParams& p, const EstRi
   unsigned parity = 0;
   for (int j = 0; j < my_tiles; ++j) {
     const int tile0 = (blockIdx.x + j * gridDim.x) * tile_span;
-    const int tile_tokens = min(tile_span, p.n_tokens - tile0);
+    const int tile_tokens = min(tile_span, g.n_tokens - tile0);
+    const int slice = p.hist ? tile0 / g.slice_tokens : 0;   // a 32-token group never straddles two slices
     // bounded wait for this tile's bytes; on failure flag the error and carry on (results are then
     // wrong, which the flag reports, but nothing spins forever)
     if (!mbar_wait_bounded(&r.full_bar[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
@@ -183,6 +217,10 @@ __device__ __forceinline__ void est_consume(const EstimateParams& p, const EstRi
 #pragma unroll
         for (int hh = 0; hh < HPW; ++hh)
           o[static_cast<int64_t>(warp * HPW + hh) * p.out_stride] = dist_to_out<OutT>(d[hh]);
+        if (p.hist) {
+#pragma unroll
+          for (int hh = 0; hh < HPW; ++hh) hist_count(p.hist, warp * HPW + hh, slice, d[hh]);
+        }
       }
     } else if (p.groups > 1) {
       // fewer than 16 heads: H * groups == 32; warp w takes head w % H of token groups w / H and
@@ -199,11 +237,17 @@ __device__ __forceinline__ void est_consume(const EstimateParams& p, const EstRi
       }
 #pragma unroll
       for (int rr = 0; rr < 2; ++rr)
-        if (tl[rr] < tile_tokens) out[static_cast<int64_t>(h) * p.out_stride + tile0 + tl[rr]] = dist_to_out<OutT>(d[rr]);
+        if (tl[rr] < tile_tokens) {
+          out[static_cast<int64_t>(h) * p.out_stride + tile0 + tl[rr]] = dist_to_out<OutT>(d[rr]);
+          if (p.hist) hist_count(p.hist, h, (tile0 + tl[rr] - lane) / g.slice_tokens, d[rr]);
+        }
     } else {
       for (int h = warp; h < H; h += kEstConsumerWarps) {
         const unsigned d = chunk_distance<METRIC>(row[2 * h], sq[2 * h]) + chunk_distance<METRIC>(row[2 * h + 1], sq[2 * h + 1]);
-        if (lane < tile_tokens) o[static_cast<int64_t>(h) * p.out_stride] = dist_to_out<OutT>(d);
+        if (lane < tile_tokens) {
+          o[static_cast<int64_t>(h) * p.out_stride] = dist_to_out<OutT>(d);
+          if (p.hist) hist_count(p.hist, h, slice, d);
+        }
       }
     }
     __syncwarp();
@@ -256,23 +300,17 @@ __global__ void __launch_bounds__(kEstThreads) estimate_kernel(const EstimatePar
     for (int c = tid; c < ring.cpt; c += kEstThreads) sq[c] = make_qplanes<METRIC>(__ldg(p.q_code + c));
   }
   __syncthreads();
-  const int my_tiles = est_tiles_of_block(p);
-
-  ADAMAS_STAMP(0, 0, tid == 0);
-  ADAMAS_TRACE(0, p.trace_tag, 0, tid == 0);
-  ADAMAS_CHAIN(1, 0, false, blockIdx.x == 0 && tid == 0);
+  const EstGeom geom = est_geom(p, HPW == 0 ? kEstTile * p.groups : kEstTile);
+  const int my_tiles = est_tiles_of_block(geom.num_tiles);
   if (warp == kEstConsumerWarps) {
-    est_produce<HPW == 0>(p, ring, my_tiles, lane);
+    est_produce<HPW == 0>(p, geom, ring, my_tiles, lane);
     grid_launch_dependents();
-    ADAMAS_STAMP(0, 4, lane == 0);
     return;
   }
   // The cached codes the producer streams were final before the preceding kernel started; the query
   // code is that kernel's output, so the consumers wait for it here (the producer does not).
   grid_dependency_wait();
   grid_launch_dependents();
-  ADAMAS_STAMP(0, 1, tid == 0);
-  ADAMAS_CHAIN(1, 1, false, blockIdx.x == 0 && tid == 0);
   QPlanes qp[HPW > 0 ? HPW : 1][2];
   if (HPW > 0) {
 #pragma unroll
@@ -281,11 +319,7 @@ __global__ void __launch_bounds__(kEstThreads) estimate_kernel(const EstimatePar
       qp[hh][1] = make_qplanes<METRIC>(__ldg(p.q_code + 2 * (warp * HPW + hh) + 1));
     }
   }
-  ADAMAS_STAMP(0, 2, tid == 0);
-  est_consume<METRIC, OutT, HPW>(p, ring, my_tiles, lane, warp, qp, sq);
-  ADAMAS_STAMP(0, 3, tid == 0);
-  ADAMAS_TRACE(0, p.trace_tag, 1, tid == 0);
-  ADAMAS_CHAIN(1, 2, true, blockIdx.x == 0 && tid == 0);
+  est_consume<METRIC, OutT, HPW>(p, geom, ring, my_tiles, lane, warp, qp, sq);
 }
 
 // ---- estimate with the decode append inside (stages 1 + 2 of a decode step in one launch) -------------
@@ -321,25 +355,25 @@ __global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const Esti
   const int warp = tid >> 5;
   const EstRing ring = est_ring_init(est_smem, full_bar, empty_bar, p.H, tid);
   __syncthreads();
-  const int my_tiles = est_tiles_of_block(p);
-
-  ADAMAS_STAMP(0, 0, tid == 0);
-  ADAMAS_TRACE(0, p.trace_tag, 0, tid == 0);
-  ADAMAS_CHAIN(1, 0, false, blockIdx.x == 0 && tid == 0);
+  const EstGeom geom = est_geom(p, kEstTile);
+  const int my_tiles = est_tiles_of_block(geom.num_tiles);
   if (warp == kEstConsumerWarps) {
     // the cached codes were final before the preceding kernel started: stream them right away
-    est_produce<false>(p, ring, my_tiles, lane);
+    est_produce<false>(p, geom, ring, my_tiles, lane);
     grid_launch_dependents();
-    ADAMAS_STAMP(0, 4, lane == 0);
     return;
   }
   // q, k, v are the preceding kernel's output
   grid_dependency_wait();
   grid_launch_dependents();
-  ADAMAS_STAMP(0, 1, tid == 0);
-  ADAMAS_CHAIN(1, 1, false, blockIdx.x == 0 && tid == 0);
 
   const bool appender = blockIdx.x == gridDim.x - 1;
+  // slot of the new token: from the host, or from the device-resident sequence length (position n)
+  int kv_last_page = a.kv_last_page, kv_entry = a.kv_entry, code_last_page = a.code_last_page, code_entry = a.code_entry;
+  if (p.seq_len_dev) {
+    kv_last_page = code_last_page = geom.n_tokens / p.page_size;
+    kv_entry = code_entry = geom.n_tokens - kv_last_page * p.page_size;
+  }
   const unsigned l16 = lane & 15;
   const int half = lane >> 4;
   const int H = p.H;
@@ -370,12 +404,12 @@ __global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const Esti
       qp[hh][1] = make_qplanes<0>(cw[1]);
     }
     if (appender) {   // block-uniform
-      const int kv_page = __ldg(a.tgt.kv_table + a.kv_last_page);
-      const int code_page = __ldg(a.tgt.code_table + a.code_last_page);
+      const int kv_page = __ldg(a.tgt.kv_table + kv_last_page);
+      const int code_page = __ldg(a.tgt.code_table + code_last_page);
       const int ps = a.tgt.page_size;
       T* kv = static_cast<T*>(a.tgt.kv_data);
       const int64_t k_off =
-          ((static_cast<int64_t>(kv_page) * 2 * ps + a.kv_entry) * H + head) * kHeadDim + l16 * 8;
+          ((static_cast<int64_t>(kv_page) * 2 * ps + kv_entry) * H + head) * kHeadDim + l16 * 8;
       const int64_t v_delta = static_cast<int64_t>(ps) * H * kHeadDim;
       const uint4 kraw = ld_16(static_cast<const T*>(a.k) + in_off);
       const uint4 vraw = ld_16(static_cast<const T*>(a.v) + in_off);
@@ -389,16 +423,12 @@ __global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const Esti
       scale_round<T>(b, a.scale);
       if (writer) {
         const int64_t c_off =
-            ((static_cast<int64_t>(code_page) * ps + a.code_entry) * H + head) * kCodeWords + l16;
+            ((static_cast<int64_t>(code_page) * ps + code_entry) * H + head) * kCodeWords + l16;
         a.tgt.code_data[c_off] = bucketize_pack8(b, a.th);
       }
     }
   }
-  ADAMAS_STAMP(0, 2, tid == 0);
-  est_consume<0, uint16_t, HPW>(p, ring, my_tiles, lane, warp, qp, nullptr);
-  ADAMAS_STAMP(0, 3, tid == 0);
-  ADAMAS_TRACE(0, p.trace_tag, 1, tid == 0);
-  ADAMAS_CHAIN(1, 2, true, blockIdx.x == 0 && tid == 0);
+  est_consume<0, uint16_t, HPW>(p, geom, ring, my_tiles, lane, warp, qp, nullptr);
 }
 
 // ---- few heads per GPU: whole pages per copy, one 16-byte chunk per lane ---------------------------------
@@ -421,6 +451,9 @@ struct EstimatePagesParams {
   int pages_per_tile;
   int num_tiles;
   int stage_out;    // gather the distances of 8 tokens per head in shared memory before writing them
+  const int32_t* seq_len_dev;   // optional device-resident sequence length, as in EstimateParams
+  uint32_t* hist;               // optional per-slice histograms, as in EstimateParams
+  int hist_cl;
 };
 
 template <int METRIC, typename OutT>
@@ -445,8 +478,13 @@ __global__ void __launch_bounds__(kEstThreads, 2) estimate_pages_kernel(const Es
     mbar_fence_init();
   }
   __syncthreads();
-  const int my_tiles = (p.num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
-                       static_cast<int>(gridDim.x);
+  int n_tokens = p.n_tokens, num_tiles = p.num_tiles;
+  if (p.seq_len_dev) {
+    n_tokens = __ldg(p.seq_len_dev) - 1;
+    num_tiles = (n_tokens + tile_span - 1) / tile_span;
+  }
+  const int slice_tokens = p.hist ? 8 * sa_granules_per_block(n_tokens, p.hist_cl) : 1;
+  const int my_tiles = est_tiles_of_block(num_tiles);
 
   if (warp == kEstConsumerWarps) {
     // ---- producer: one bulk copy per page of the tile (the last page of the row may be partial)
@@ -455,7 +493,7 @@ __global__ void __launch_bounds__(kEstThreads, 2) estimate_pages_kernel(const Es
     for (int j = 0; j < my_tiles; ++j) {
       const int tile = blockIdx.x + j * gridDim.x;
       const int tok0 = tile * tile_span;
-      const int ntok = min(tile_span, p.n_tokens - tok0);
+      const int ntok = min(tile_span, n_tokens - tok0);
       if (j >= kEstStages) {
         if (!mbar_wait_bounded(&empty_bar[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
       }
@@ -501,7 +539,9 @@ __global__ void __launch_bounds__(kEstThreads, 2) estimate_pages_kernel(const Es
   for (int j = 0; j < my_tiles; ++j) {
     const int tile = blockIdx.x + j * gridDim.x;
     const int tok0 = tile * tile_span;
-    const int ntok = min(tile_span, p.n_tokens - tok0);
+    const int ntok = min(tile_span, n_tokens - tok0);
+    const int slice0 = p.hist ? tok0 / slice_tokens : 0;
+    const int off0 = tok0 - slice0 * slice_tokens;
     if (!mbar_wait_bounded(&full_bar[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
     const uint4* base = est_smem + slot * tile_chunks;
     const int units = (ntok + unit_tok - 1) / unit_tok;
@@ -518,6 +558,10 @@ __global__ void __launch_bounds__(kEstThreads, 2) estimate_pages_kernel(const Es
             stage[h][t] = *reinterpret_cast<const uint16_t*>(&v);
           } else if (u * unit_tok + t < ntok) {
             out[static_cast<int64_t>(h) * p.out_stride + tok0 + u * unit_tok + t] = v;
+          }
+          if (p.hist && u * unit_tok + t < ntok) {
+            const int off = off0 + u * unit_tok + t;
+            hist_count(p.hist, h, slice0 + (off >= slice_tokens ? off / slice_tokens : 0), d);
           }
         }
       }

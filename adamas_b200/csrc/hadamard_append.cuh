@@ -60,9 +60,14 @@ __device__ __forceinline__ uint16_t bucketize_pack8(const float (&x)[8], Thresho
 // inv_freq(j) = (1 / rope_scale) / theta^(2j/128), all in fp32 as the reference's kernel and the HF
 // module compute it (kernels/include/decode/decode_page.cuh:642-690).  The result is rounded to the
 // storage type, as the in-place reference operator leaves it.
+// With `inv_freq` (64 floats on the device: one rotation frequency per dimension pair, position scaling
+// already folded in) the angle is pos * inv_freq[j] and the rotated values are multiplied by `mscale`:
+// the form YaRN-scaled models use (per-dimension interpolation ramp, attention factor on cos and sin).
 struct RopeParams {
   float rcp_scale;
   float theta;
+  const float* inv_freq;
+  float mscale;
 };
 
 template <typename T>
@@ -72,11 +77,13 @@ __device__ __forceinline__ void rope_halfwarp(float (&x)[8], unsigned l16, float
   for (int i = 0; i < 8; ++i) {
     const float other = __shfl_xor_sync(0xffffffffu, x[i], 8);
     const int j = static_cast<int>(l16 & 7) * 8 + i;
-    const float inv_freq = rp.rcp_scale / powf(rp.theta, static_cast<float>(2 * j) * (1.0f / kHeadDim));
+    const float inv_freq = rp.inv_freq ? __ldg(rp.inv_freq + j)
+                                       : rp.rcp_scale / powf(rp.theta, static_cast<float>(2 * j) * (1.0f / kHeadDim));
     float sn, cs;
     sincosf(pos * inv_freq, &sn, &cs);
     // lower half: x*cos - partner*sin; upper half: x*cos + partner*sin
-    const float r = upper ? fmaf(other, sn, x[i] * cs) : fmaf(-other, sn, x[i] * cs);
+    float r = upper ? fmaf(other, sn, x[i] * cs) : fmaf(-other, sn, x[i] * cs);
+    if (rp.inv_freq) r *= rp.mscale;
     x[i] = Elem<T>::round(r);
   }
 }
@@ -149,14 +156,21 @@ __global__ void __launch_bounds__(256)
 append_decode_kernel(const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ qh,
                      const T* __restrict__ kh, uint16_t* __restrict__ q_code_out, PagedTarget tgt,
                      int kv_last_page, int kv_entry, int code_last_page, int code_entry, float scale,
-                     Thresholds th, float pos = 0.f, RopeParams rp = RopeParams{1.f, 1e4f}) {
-  ADAMAS_CHAIN(0, 0, false, blockIdx.x == 0 && threadIdx.x == 0);
+                     Thresholds th, float pos, RopeParams rp, const int32_t* seq_len_dev) {
   // The kernel after this one (the estimate) may become resident right away: its producer warps only
   // read the code cache as it was before this step, and its consumers wait for this grid to complete,
-  // which in turn waits for the grid before it.
+  // which in turn waits for the grid before it.  (Two appends to one cache back to back, followed by an
+  // estimate, are outside this reasoning: the estimate's early reads could then see the first append's
+  // slot unwritten.  A decode step appends once.)
   grid_launch_dependents();
   grid_dependency_wait();
-  ADAMAS_CHAIN(0, 1, false, blockIdx.x == 0 && threadIdx.x == 0);
+  if (seq_len_dev) {
+    // the token being appended sits at position *seq_len_dev - 1 of both caches
+    const int t = __ldg(seq_len_dev) - 1;
+    kv_last_page = code_last_page = t / tgt.page_size;
+    kv_entry = code_entry = t - kv_last_page * tgt.page_size;
+    pos = static_cast<float>(t);
+  }
   // physical pages of the slot being written: last entries of the two page tables
   const int kv_page = __ldg(tgt.kv_table + kv_last_page);
   const int code_page = __ldg(tgt.code_table + code_last_page);
@@ -206,7 +220,6 @@ append_decode_kernel(const T* __restrict__ k, const T* __restrict__ v, const T* 
         ((static_cast<int64_t>(code_page) * tgt.page_size + code_entry) * H + hh) * kCodeWords + l16;
     tgt.code_data[c_off] = bucketize_pack8(b, th);
   }
-  ADAMAS_CHAIN(0, 2, true, blockIdx.x == 0 && threadIdx.x == 0);
 }
 
 // Prefill append: one half-warp per (token, head) row; token n sits at position start_pos + n.

@@ -3,31 +3,30 @@
 // token.  Used by the fused decode step; the separate top-k and decode kernels remain for callers
 // that want the stages one by one.
 //
-// One thread-block cluster (CL <= 8 blocks x 512 threads) per head.  Block `cr` owns a contiguous
-// slice of the head's distance row, keeps it in registers, and later attends over the winners that
-// lie in its own slice, so the selected indices never travel between blocks:
-//   pre   clear the local histogram and ARRIVE at a cluster barrier without waiting ("I have
-//         started"); all of this may overlap the tail of the estimate kernel (programmatic dependent
-//         launch);
-//   1     histogram of the block's distances (values < 512: a distance is at most 3 * 128); the wait
-//         half of the start-up barrier (every peer is running by now); the whole histogram, packed
-//         to 16-bit counts, is STORED into slot `cr` of every peer's per-source table with one
-//         16-byte remote store per thread (nothing has to be zeroed); cluster barrier.  Every block
-//         now holds all CL histograms and derives by itself: the cut distance, how many cut-valued
-//         elements are taken in all, how many of them and how many smaller elements lie in
-//         lower-ranked slices (= its tie quota and its offset in the output list);
-//   2     ordered compaction of the block's winners into a shared-memory list (and, optionally, to
-//         the global index list at the right offset);
-//   3     attention over the list in tiles of `tile_cap` (64, 128 or 192) tokens, chosen by the host so
-//         that a block's winners almost always fit one tile: K/V rows gathered with one 256-byte
-//         bulk (TMA) copy per row, counted by an mbarrier (bounded wait), four threads per token
-//         for q.K (odd and even tokens walk their chunks in different orders, which keeps the
-//         un-padded rows free of bank conflicts), online softmax in base 2, one thread per (group
-//         of tile_cap/32 tokens, 8-dim chunk) for P.V;
-//   4     the partial (o, m, l) is stored into slot `cr` of rank 0's shared memory; cluster barrier;
-//         rank 0 merges the CL partials and writes the head's output.
-// Only two cluster barriers sit on the critical path.  The histogram tables and the per-warp partial
-// outputs live in the K/V tile memory, which is idle before and after phase 3.
+// The kernel does not count anything itself.  The estimate kernels (or dist_histogram_kernel, for a
+// caller that only has a distance row) leave, per head, one 512-bin histogram per SLICE of the row
+// in a global table [H][kSaMaxSlices][512] u32: slice r covers the granules (8 distances) that block
+// r of the head's cluster owns.  A distance is at most 3 * 128 = 384; larger values count as 511.
+//
+// One thread-block cluster (CL <= 16 blocks x 512 threads) per head.  Block `cr`:
+//   load   its slice of the distance row (registers), the head's CL histograms (one bin per thread)
+//          and the query chunks, all in flight together;
+//   cut    block-wide scan of the summed histogram: the cut distance, how many cut-valued elements
+//          are taken in all, how many of them and how many smaller elements lie in lower-ranked
+//          slices (= this slice's tie quota and its offset in the output list).  Every block
+//          derives this by itself from the same table: no cluster barrier;
+//   pick   ordered compaction: a thread that holds a winner computes its row in the tile and issues
+//          the two 256-byte bulk (TMA) copies of its K and V row right away; winner number `pos`
+//          goes to warp pos / tpw, which owns tpw = tile_cap / 16 consecutive rows and one mbarrier;
+//   attend every warp waits for its own rows only (bounded wait), computes q.K with four lanes per
+//          token, a softmax in base 2 over its tokens and P.V with four dimensions per lane: no
+//          block barrier inside the attention.  Winners beyond the tile (rare: the host sizes the
+//          tile for the mean plus four standard deviations) go through a list in shared memory and
+//          further passes;
+//   merge  the 16 warps' partial (o, m, l) are merged in shared memory, the block's partial is
+//          stored into slot `cr` of rank 0's shared memory; one cluster barrier; rank 0 merges the
+//          CL partials and writes the head's output; every block clears its own histogram row, so
+//          that the table is all zero again when the kernel ends.
 #pragma once
 #include <cooperative_groups.h>
 
@@ -36,45 +35,54 @@
 namespace adamas {
 
 constexpr int kSaThreads = 512;
-constexpr int kSaMaxWarps = kSaThreads / 32;
+constexpr int kSaWarps = kSaThreads / 32;
 constexpr int kSaBins = 512;
+constexpr int kSaMaxSlices = 16;      // histogram rows per head = largest cluster
 constexpr int kSaTile = 128;          // planning unit of the host (winners per block it aims for)
-constexpr int kSaMaxTpg = 6;          // tokens per P.V group at most
-constexpr int kSaTileMax = kSaMaxTpg * kSaThreads / 16;   // largest attention tile: 192 tokens
+constexpr int kSaTileMax = 192;       // largest attention tile (rows of K and of V in shared memory)
 constexpr int kSaMaxCluster = 8;      // portable cluster size
 constexpr int kSaBigCluster = 16;     // non-portable: long rows of few heads (see the host code)
+
+// Granules (8 distances) of a row that each of `cl` blocks owns: a multiple of 4, so that a slice
+// starts on a multiple of 32 tokens and no 32-token tile of an estimate kernel straddles two slices.
+__host__ __device__ __forceinline__ int sa_granules_per_block(int n, int cl) {
+  const int g = ((n + 7) >> 3);
+  return (((g + cl - 1) / cl) + 3) & ~3;
+}
 
 struct SelectAttendParams {
   const uint16_t* dist;     // [H, dist_stride] u16 distances, rows 16-byte aligned
   int64_t dist_stride;
-  int n;                    // distances per head (tokens 0 .. n-1)
+  uint32_t* hist;           // [H][kSaMaxSlices][512]: per-slice histograms of the rows; cleared on exit
+  const int2* ext_cut;      // optional [H]: (cut distance, cut-valued winners this call takes), decided
+                            // elsewhere (sequence shards); k is then unused
+  const int32_t* seq_len_dev;  // optional: n = *seq_len_dev - 1 and the newest token sits at position n
+  int n;                    // distances per head (tokens 0 .. n-1) when seq_len_dev is null
   int k;                    // winners per head, 1 <= k <= n
   const void* q;            // [H, 128]; read after the preceding kernel has completed
-  void* o;                  // [H, 128]
+  void* o;                  // [H, 128] in the cache's element type, or null
+  float* o_f32;             // [H, 128] fp32 (partial result of a sequence shard), or null
   float* lse;               // [H] or null (base 2)
   const void* kv;           // [pages, 2, page_size, H, 128]
   const int32_t* kv_table;  // logical page -> physical page
   int page_size;
   int ps_shift;             // log2(page_size) or -1
   int H;
-  unsigned tail_slot;       // physical slot of the newest token (always attended)
+  int tail_mode;            // 0: no newest token; 1: it is at tail_slot; 2: at logical position n
+  unsigned tail_slot;       // physical slot of the newest token (tail_mode 1)
   int32_t* out_idx;         // optional [H, out_stride]: physical slots of the winners, ascending position
   int64_t out_stride;
-  int granules_per_block;   // 16-byte granules (8 distances) of a row per block
-  int list_capacity;        // entries of the shared-memory winner list
-  int tile_cap;             // tokens per attention tile: 64, 128 or 192
-  int trace_tag;            // launch number, used by builds with phase timing only
+  int list_capacity;        // entries of the shared-memory overflow list (winners beyond the tile)
+  int tile_cap;             // rows per attention tile: 64, 128 or 192
   float scale_log2;
 };
 
 struct SaShared {
-  float s_logit[kSaTileMax];
-  float s_p[kSaTileMax];
-  float s_red[kSaMaxWarps];
-  float s_sum[kSaTileMax / 32];
-  unsigned warp_a[kSaMaxWarps];
-  unsigned warp_b[kSaMaxWarps];
-  unsigned cut, before, lt_before, eq_before;
+  float ml[kSaWarps][2];
+  unsigned warp_a[kSaWarps];
+  unsigned warp_b[kSaWarps];
+  unsigned cut, need_eq, lt_before, eq_before;
+  unsigned long long bar[kSaWarps];
 };
 
 // The two halves of a cluster barrier (all threads of all blocks of the cluster execute both).
@@ -85,23 +93,17 @@ __device__ __forceinline__ void cluster_wait_acquire() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-// Dynamic shared memory: K tile (tile_cap * 256 B) | V tile (same) | winner list (list_capacity * 4 B,
+// Dynamic shared memory: K tile (tile_cap * 256 B) | V tile (same) | overflow list (list_capacity * 4 B,
 // rounded up to 16) | rank 0's table of the blocks' partial results (CL * 130 floats).
-// The first 2 KB + CL KB double as the histogram tables (local: 512 x u32; per source block: CL x 512 x
-// u16) until phase 3 starts, the first 8 KB as the warps' partial outputs after it has ended.
+// After its last pass a warp parks its partial output in its own K rows.
 template <typename T, int ITEMS>
 __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const SelectAttendParams p) {
   constexpr int NT = kSaThreads;
   static_assert(NT >= kSaBins, "one histogram bin per thread");
-  constexpr int kWarps = NT / 32;
-  constexpr int kGroups = NT / 16;        // P.V token groups per tile
-  constexpr int kQkTokens = NT / 4;       // tokens per q.K pass
-  constexpr int kCapMax = kSaMaxTpg * kGroups;
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
   extern __shared__ __align__(16) uint8_t sa_smem[];
   __shared__ __align__(16) SaShared sh;
-  __shared__ __align__(8) uint64_t gather_bar;
 
   const unsigned CL = cluster.num_blocks();
   const unsigned cr = cluster.block_rank();
@@ -111,57 +113,35 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   const int warp = tid >> 5;
   const int H = p.H;
   const int cap = p.tile_cap;
+  const int tpw = cap / kSaWarps;     // rows per warp and pass: 4, 8 or 12
+  const unsigned tpw_rcp = 65536u / static_cast<unsigned>(tpw) + 1u;   // pos / tpw == (pos * tpw_rcp) >> 16 for pos < 192
 
   uint8_t* sk = sa_smem;
   uint8_t* sv = sa_smem + cap * 256;
   int32_t* s_list = reinterpret_cast<int32_t*>(sa_smem + 2 * cap * 256);
   float* part_o = reinterpret_cast<float*>(sa_smem + 2 * cap * 256 + ((p.list_capacity * 4 + 15) & ~15));  // [CL][128]
   float* part_ml = part_o + CL * kHeadDim;                                                                  // [CL][2]
-  unsigned* h_local = reinterpret_cast<unsigned*>(sa_smem);
-  uint16_t* h_src = reinterpret_cast<uint16_t*>(sa_smem + kSaBins * 4);
-  float(*s_o)[kHeadDim] = reinterpret_cast<float(*)[kHeadDim]>(sa_smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sh.bar);
 
-  // ---- pre ------------------------------------------------------------------------------------------
-  ADAMAS_STAMP(1, 0, tid == 0);
-  ADAMAS_TRACE(1, p.trace_tag, 0, tid == 0);
-  ADAMAS_CHAIN(2, 0, false, blockIdx.x == 0 && tid == 0);
-  if (tid < kSaBins) h_local[tid] = 0;
+  // ---- set-up that needs no input (overlaps the tail of the preceding kernel) -----------------------
   if (tid == 0) {
-    mbar_init(&gather_bar, NT);
+#pragma unroll
+    for (int w2 = 0; w2 < kSaWarps; ++w2) mbar_init(&bars[w2], 1);
+    sh.cut = 0xffffffffu;
     mbar_fence_init();
   }
-  cluster_arrive_release();   // start-up barrier, first half: this block is running
   __syncthreads();
   grid_dependency_wait();
   grid_launch_dependents();
-  ADAMAS_STAMP(1, 1, tid == 0);
-  ADAMAS_CHAIN(2, 1, false, blockIdx.x == 0 && tid == 0);
 
-  // q.K mapping: four threads per token (tl = tid / 4, quarter = tid % 4); step i of a thread reads
-  // chunk 4*quarter + ((i + quarter + tl) & 3).  A quarter-warp covers an even and an odd token; the
-  // rows are 256 bytes apart (the same banks), and with this order the two tokens' four chunks fall
-  // on complementary 16-byte bank groups, so the 8 lanes hit 8 different ones.  The query chunks stay
-  // packed in registers, in the thread's own order.  Short rows fetch them
-  // now (the latency hides behind the selection); long rows hold 16 to 64 distances per thread through
-  // the selection phases and fetch the query after them, so that it does not push distances out of the
-  // registers.
-  const int qk_tl = tid >> 2;
-  const int quarter = tid & 3;
-  uint4 qpk[4];
-  auto load_query = [&]() {
-    const T* qp = static_cast<const T*>(p.q) + static_cast<int64_t>(head) * kHeadDim;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) qpk[i] = ld_16(qp + (4 * quarter + ((i + quarter + qk_tl) & 3)) * 8);
-  };
-  if (ITEMS == 1) load_query();
-
-  // ---- 1: this block's slice of the row, histogram, exchange --------------------------------------
-  const uint16_t* rowp = p.dist + static_cast<int64_t>(head) * p.dist_stride;
-  const uint4* gbase = reinterpret_cast<const uint4*>(rowp);
-  const int G = (p.n + 7) >> 3;
-  const int blk_first = cr * p.granules_per_block;
-  const int blk_end = min(G, blk_first + p.granules_per_block);
+  // ---- loads: distances, histograms, query, page numbers --------------------------------------------
+  const int n = p.seq_len_dev ? (__ldg(p.seq_len_dev) - 1) : p.n;
+  const int G = (n + 7) >> 3;
+  const int gpb = sa_granules_per_block(n, static_cast<int>(CL));
+  const int blk_first = cr * gpb;
+  const int blk_end = min(G, blk_first + gpb);
   const int g0 = blk_first + tid * ITEMS;
+  const uint4* gbase = reinterpret_cast<const uint4*>(p.dist + static_cast<int64_t>(head) * p.dist_stride);
   uint32_t raw[ITEMS][4];
   unsigned vmask[ITEMS];
 #pragma unroll
@@ -172,10 +152,19 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
     if (g < blk_end) {
       v = ld_16(gbase + g);
       m = 0xffu;
-      if (g * 8 + 8 > p.n) m = 0xffu >> (g * 8 + 8 - p.n);
+      if (g * 8 + 8 > n) m = 0xffu >> (g * 8 + 8 - n);
     }
     raw[i][0] = v.x; raw[i][1] = v.y; raw[i][2] = v.z; raw[i][3] = v.w;
     vmask[i] = m;
+  }
+  unsigned tot = 0, low = 0;
+  {
+    const uint32_t* hrow = p.hist + (static_cast<size_t>(head) * kSaMaxSlices) * kSaBins + tid;
+    for (unsigned r = 0; r < CL; ++r) {
+      const unsigned c = __ldcg(hrow + r * kSaBins);
+      tot += c;
+      if (r < cr) low += c;
+    }
   }
   // With pages of 8 tokens or more (a power of two) a granule lies inside one page: fetch its
   // physical page number now, long before the winners are known.
@@ -186,42 +175,32 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
     granule_page[i] = 0;
     if (page_per_granule && g0 + i < blk_end) granule_page[i] = __ldg(p.kv_table + (((g0 + i) * 8) >> p.ps_shift));
   }
-#pragma unroll
-  for (int i = 0; i < ITEMS; ++i) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const unsigned d = (raw[i][j >> 1] >> ((j & 1) * 16)) & 0xffffu;
-      if ((vmask[i] >> j) & 1u) atomicAdd(&h_local[min(d, static_cast<unsigned>(kSaBins - 1))], 1u);
-    }
+  // the newest token rides with the last slice
+  const bool tail_here = p.tail_mode != 0 && cr == CL - 1;
+  unsigned tail_slot = p.tail_slot;
+  if (tail_here && tid == 0 && p.tail_mode == 2) {
+    const unsigned un = static_cast<unsigned>(n), ps = static_cast<unsigned>(p.page_size);
+    const unsigned pg = p.ps_shift >= 0 ? (un >> p.ps_shift) : (un / ps);
+    tail_slot = static_cast<unsigned>(__ldg(p.kv_table + pg)) * ps + (un - pg * ps);
   }
-  __syncthreads();
-  cluster_wait_acquire();     // start-up barrier, second half: every peer is running
-  ADAMAS_STAMP(1, 2, tid == 0);
-  {
-    // thread -> (8 bins, peer): a block's count of one bin is at most 8 * 512 * ITEMS <= 32768
-    const int vec = tid & 63;
-    const uint4 a = *reinterpret_cast<const uint4*>(h_local + 8 * vec);
-    const uint4 b = *reinterpret_cast<const uint4*>(h_local + 8 * vec + 4);
-    const uint4 pk = make_uint4(a.x | (a.y << 16), a.z | (a.w << 16), b.x | (b.y << 16), b.z | (b.w << 16));
-    for (unsigned peer = static_cast<unsigned>(tid) >> 6; peer < CL; peer += NT / 64) {
-      uint16_t* dst = cluster.map_shared_rank(h_src + cr * kSaBins + 8 * vec, peer);
-      *reinterpret_cast<uint4*>(dst) = pk;
-    }
-  }
-  cluster_arrive_release();
-  cluster_wait_acquire();
-  ADAMAS_STAMP(1, 3, tid == 0);
+  // q.K mapping: four lanes per token (tq = lane / 4, quarter = lane % 4); step i of a lane reads chunk
+  // 4*quarter + ((i + quarter + tq) & 3).  A quarter-warp covers an even and an odd token; the rows are
+  // 256 bytes apart (the same banks), and with this order the two tokens' four chunks fall on
+  // complementary 16-byte bank groups, so the 8 lanes hit 8 different ones.  The query chunks stay
+  // packed in registers, in the lane's own order (a warp's first row is a multiple of 4).
+  const int tq = lane >> 2;
+  const int quarter = lane & 3;
+  // They are fetched once the copies of the winners' rows are on their way: the latency hides behind
+  // the gather, and the selection keeps its registers.
+  uint4 qpk[4];
+  auto load_query = [&]() {
+    const T* qp = static_cast<const T*>(p.q) + static_cast<int64_t>(head) * kHeadDim;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) qpk[i] = ld_16(qp + (4 * quarter + ((i + quarter + tq) & 3)) * 8);
+  };
 
-  // every block: total histogram, cut, counts in lower-ranked slices (one bin per thread)
+  // ---- cut: one bin per thread ------------------------------------------------------------------------
   {
-    unsigned tot = 0, low = 0;
-    if (tid < kSaBins) {
-      for (unsigned r = 0; r < CL; ++r) {
-        const unsigned c = h_src[r * kSaBins + tid];
-        tot += c;
-        if (r < cr) low += c;
-      }
-    }
     unsigned it = tot, il = low;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -239,34 +218,50 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
     __syncthreads();
     unsigned wa = 0, wb = 0;
 #pragma unroll
-    for (int w2 = 0; w2 < kWarps; ++w2) {
+    for (int w2 = 0; w2 < kSaWarps; ++w2) {
       wa += (w2 < warp) ? sh.warp_a[w2] : 0u;
       wb += (w2 < warp) ? sh.warp_b[w2] : 0u;
     }
-    const unsigned excl = wa + it - tot;
-    const unsigned want = static_cast<unsigned>(p.k);
-    if (excl < want && excl + tot >= want) {   // exactly one thread
+    const unsigned excl = wa + it - tot;        // elements of smaller value, whole row
+    const unsigned excl_low = wb + il - low;    // ... in lower-ranked slices
+    bool mine;
+    unsigned need = 0;
+    if (p.ext_cut) {
+      const int2 e = __ldg(p.ext_cut + head);
+      mine = tid == e.x;
+      need = static_cast<unsigned>(e.y);
+    } else {
+      const unsigned want = static_cast<unsigned>(p.k);
+      mine = excl < want && excl + tot >= want;   // exactly one thread
+      need = want - excl;
+    }
+    if (mine) {
       sh.cut = tid;
-      sh.before = excl;
-      sh.lt_before = wb + il - low;            // smaller-valued elements in lower-ranked slices
-      sh.eq_before = low;                      // cut-valued elements in lower-ranked slices
+      sh.need_eq = need;               // cut-valued winners in all
+      sh.lt_before = excl_low;         // smaller-valued elements in lower-ranked slices
+      sh.eq_before = low;              // cut-valued elements in lower-ranked slices
     }
     __syncthreads();
   }
-  const unsigned cut = sh.cut;
-  ADAMAS_STAMP(1, 4, tid == 0);
-  const unsigned need_eq = static_cast<unsigned>(p.k) - sh.before;       // cut-valued winners in all
-  const unsigned eq_before = sh.eq_before;
-  const unsigned take_eq = need_eq > eq_before ? need_eq - eq_before : 0u;  // this slice's tie quota
-  const unsigned out_base = sh.lt_before + min(eq_before, need_eq);      // winners in lower slices
+  unsigned cut = sh.cut;
+  unsigned need_eq = sh.need_eq;
+  if (cut == 0xffffffffu) {
+    // the table does not describe this row (fewer than k entries): take nothing but the newest token
+    if (tid == 0) atomicOr(&g_adamas_error, kErrHistogram);
+    cut = 0;
+    need_eq = 0;
+  }
+  const unsigned eq_before = (sh.cut == 0xffffffffu) ? 0u : sh.eq_before;
+  const unsigned take_eq = need_eq > eq_before ? need_eq - eq_before : 0u;   // this slice's tie quota
+  const unsigned out_base = ((sh.cut == 0xffffffffu) ? 0u : sh.lt_before) + min(eq_before, need_eq);
 
-  // ---- 2: ordered compaction of this block's winners ------------------------------------------------
+  // ---- pick: ordered compaction of this block's winners -----------------------------------------------
   unsigned c_lt = 0, c_eq = 0;
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const unsigned d = (raw[i][j >> 1] >> ((j & 1) * 16)) & 0xffffu;
+      const unsigned d = min((raw[i][j >> 1] >> ((j & 1) * 16)) & 0xffffu, static_cast<unsigned>(kSaBins - 1));
       const bool ok = (vmask[i] >> j) & 1u;
       c_lt += (ok && d < cut);
       c_eq += (ok && d == cut);
@@ -279,11 +274,11 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
     const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
     if (lane >= o) incl += t;
   }
-  if (lane == 31) sh.warp_a[warp] = incl;
+  if (lane == 31) sh.warp_a[warp] = incl;   // (its readers of the cut phase are past a block barrier)
   __syncthreads();
   unsigned wbase = 0, blk_tot = 0;
 #pragma unroll
-  for (int w2 = 0; w2 < kWarps; ++w2) {
+  for (int w2 = 0; w2 < kSaWarps; ++w2) {
     const unsigned a = sh.warp_a[w2];
     wbase += (w2 < warp) ? a : 0u;
     blk_tot += a;
@@ -291,14 +286,49 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   const unsigned excl = wbase + incl - packed;
   unsigned run_lt = excl & 0xffffu, run_eq = excl >> 16;
   const unsigned blk_lt = blk_tot & 0xffffu, blk_eq = blk_tot >> 16;
-  int n_loc = static_cast<int>(blk_lt + min(blk_eq, take_eq));
+  const int n_win = static_cast<int>(blk_lt + min(blk_eq, take_eq));
+  const int n_loc = min(n_win + (tail_here ? 1 : 0), cap + p.list_capacity);
+
+  const T* kvp = static_cast<const T*>(p.kv);
+  const unsigned ps = static_cast<unsigned>(p.page_size);
+  const int64_t v_delta = static_cast<int64_t>(p.page_size) * H * kHeadDim;
+  // K row of a physical token slot
+  auto row_of = [&](unsigned slot) -> const T* {
+    unsigned page, e;
+    if (p.ps_shift >= 0) {
+      page = slot >> p.ps_shift;
+      e = slot & (ps - 1);
+    } else {
+      page = slot / ps;
+      e = slot - page * ps;
+    }
+    const int64_t row = static_cast<int64_t>(page) * (2 * ps) + e;
+    return kvp + (row * H + head) * kHeadDim;
+  };
+  // rows of pass `pass` (tile rows pass*cap ..) that warp `w` owns
+  auto rows_of_warp = [&](int pass, int w) -> int { return max(0, min(tpw, n_loc - pass * cap - w * tpw)); };
+  // winner number `pos` of the block lives at physical slot `slot`: copy its rows now (first tile) or
+  // remember it (later passes)
+  auto place = [&](int pos, unsigned slot) {
+    if (pos < cap) {
+      const T* src = row_of(slot);
+      uint64_t* bar = &bars[(static_cast<unsigned>(pos) * tpw_rcp) >> 16];
+      bulk_copy_g2s(sk + pos * 256, src, kHeadDim * 2, bar);
+      bulk_copy_g2s(sv + pos * 256, src + v_delta, kHeadDim * 2, bar);
+    } else if (pos - cap < p.list_capacity) {
+      s_list[pos - cap] = static_cast<int32_t>(slot);
+    }
+  };
+
+  // every warp announces the bytes of its rows of the first pass, then the copies are issued
+  if (lane == 0) mbar_arrive_expect_tx(&bars[warp], static_cast<unsigned>(rows_of_warp(0, warp)) * (2 * kHeadDim * 2));
   int32_t* oi = p.out_idx ? p.out_idx + static_cast<int64_t>(head) * p.out_stride + out_base : nullptr;
   if (c_lt | c_eq) {
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const unsigned d = (raw[i][j >> 1] >> ((j & 1) * 16)) & 0xffffu;
+        const unsigned d = min((raw[i][j >> 1] >> ((j & 1) * 16)) & 0xffffu, static_cast<unsigned>(kSaBins - 1));
         if (((vmask[i] >> j) & 1u) && d <= cut) {
           int pos = -1;
           if (d < cut) {
@@ -310,96 +340,60 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
           }
           if (pos >= 0) {
             const unsigned t = static_cast<unsigned>((g0 + i) * 8 + j);   // logical token position
-            int32_t slot;
+            unsigned slot;
             if (page_per_granule) {
-              slot = granule_page[i] * p.page_size + static_cast<int32_t>(t & (p.page_size - 1));
+              slot = static_cast<unsigned>(granule_page[i]) * ps + (t & (ps - 1));
             } else {
               unsigned pg, e;
               if (p.ps_shift >= 0) {
                 pg = t >> p.ps_shift;
-                e = t & (p.page_size - 1);
+                e = t & (ps - 1);
               } else {
-                pg = t / p.page_size;
-                e = t - pg * p.page_size;
+                pg = t / ps;
+                e = t - pg * ps;
               }
-              slot = __ldg(p.kv_table + pg) * p.page_size + static_cast<int32_t>(e);
+              slot = static_cast<unsigned>(__ldg(p.kv_table + pg)) * ps + e;
             }
-            if (pos < p.list_capacity) s_list[pos] = slot;
-            if (oi) oi[pos] = slot;
+            place(pos, slot);
+            if (oi) oi[pos] = static_cast<int32_t>(slot);
           }
         }
       }
     }
   }
-  if (cr == CL - 1) {   // the newest token rides with the last slice
-    if (tid == 0 && n_loc < p.list_capacity) s_list[n_loc] = static_cast<int32_t>(p.tail_slot);
-    n_loc += 1;
-  }
-  n_loc = min(n_loc, p.list_capacity);
-  __syncthreads();
-  ADAMAS_STAMP(1, 5, tid == 0);
+  if (tail_here && tid == 0) place(n_win, tail_slot);
+  load_query();
 
-  // ---- 3: attention over the block's winners ------------------------------------------------------------
-  if (ITEMS > 1) load_query();
-  const T* kvp = static_cast<const T*>(p.kv);
-  const int64_t v_delta = static_cast<int64_t>(p.page_size) * H * kHeadDim;
-  float m_run = -INFINITY, l_run = 0.f;
-  float o_acc[8];
-#pragma unroll
-  for (int d = 0; d < 8; ++d) o_acc[d] = 0.f;
-  const int tpg = cap / kGroups;   // tokens per P.V group
-  const int pv_g = tid >> 4;   // token group: tokens pv_g*tpg .. pv_g*tpg+tpg-1 of the tile
-  const int pv_c = tid & 15;   // 8-dim chunk
-  const unsigned ps = static_cast<unsigned>(p.page_size);
-
-  // The tile memory held the histogram tables, written through the generic proxy (by this block and
-  // by its peers); the bulk copies write it through the async proxy.
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  unsigned gather_parity = 0;
-  for (int t0 = 0; t0 < n_loc; t0 += cap) {
-    const int tile_tokens = min(cap, n_loc - t0);
-    // gather: thread -> (token tl = tid / 2, K or V row), one 256-byte bulk copy each; every thread
-    // arrives at the barrier once, with the bytes it asked for
-    {
+  // ---- attend: every warp over its own rows --------------------------------------------------------------
+  float m_run = -INFINITY, l_run = 0.f;   // l_run is kept by the lanes with quarter == 0
+  float o_acc[4] = {0.f, 0.f, 0.f, 0.f};  // dimensions 4*lane .. 4*lane+3
+  const int n_pass = (n_loc + cap - 1) / cap;
+  for (int pass = 0; pass < n_pass; ++pass) {
+    if (pass > 0) {
+      // the tile is refilled from the list: all warps have finished with the rows of the pass before
+      __syncthreads();
+      if (lane == 0)
+        mbar_arrive_expect_tx(&bars[warp], static_cast<unsigned>(rows_of_warp(pass, warp)) * (2 * kHeadDim * 2));
       const int tl = tid >> 1;
       const int is_v = tid & 1;
-      if (tl < tile_tokens) {
-        const unsigned slot = static_cast<unsigned>(s_list[t0 + tl]);
-        unsigned page, e;
-        if (p.ps_shift >= 0) {
-          page = slot >> p.ps_shift;
-          e = slot & (ps - 1);
-        } else {
-          page = slot / ps;
-          e = slot - page * ps;
-        }
-        const int64_t row = static_cast<int64_t>(page) * (2 * ps) + e;
-        const T* src = kvp + (row * H + head) * kHeadDim + (is_v ? v_delta : 0);
-        mbar_arrive_expect_tx(&gather_bar, kHeadDim * 2);
-        bulk_copy_g2s((is_v ? sv : sk) + tl * 256, src, kHeadDim * 2, &gather_bar);
-      } else {
-        mbar_arrive(&gather_bar);
+      for (int r = tl; r < min(cap, n_loc - pass * cap); r += NT / 2) {
+        const T* src = row_of(static_cast<unsigned>(s_list[(pass - 1) * cap + r]));
+        bulk_copy_g2s((is_v ? sv : sk) + r * 256, src + (is_v ? v_delta : 0), kHeadDim * 2, &bars[(static_cast<unsigned>(r) * tpw_rcp) >> 16]);
       }
-      if (!mbar_wait_bounded(&gather_bar, gather_parity, 1u << 22)) atomicOr(&g_adamas_error, kErrGatherTimeout);
-      gather_parity ^= 1u;
     }
-    ADAMAS_STAMP(1, 6, tid == 0 && t0 == 0);
-    ADAMAS_STAMP(1, 10, tid == 0 && t0 != 0);
-
-    // q.K: tokens qk_tl (all threads) and NT/4 + qk_tl (tiles of more than NT/4 tokens)
-    float wmax = -INFINITY;
-#pragma unroll
-    for (int pass = 0; pass < 2; ++pass) {
-      if (pass == 1 && tile_tokens <= kQkTokens) break;   // block-uniform
-      const int tl = qk_tl + kQkTokens * pass;
+    const int my_rows = rows_of_warp(pass, warp);
+    if (!mbar_wait_bounded(&bars[warp], static_cast<unsigned>(pass & 1), 1u << 22)) atomicOr(&g_adamas_error, kErrGatherTimeout);
+    for (int base = 0; base < my_rows; base += 8) {
+      const int r_in_warp = base + tq;
+      const bool live = r_in_warp < my_rows;
+      const int row = warp * tpw + r_in_warp;
       float acc = 0.f;
-      const bool live = tl < tile_tokens;
       if (live) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const int lc = 4 * quarter + ((i + quarter + qk_tl) & 3);   // tl and qk_tl have the same parity
+          const int lc = 4 * quarter + ((i + quarter + tq) & 3);
           float kf[8], qf[8];
-          unpack8<T>(*reinterpret_cast<const uint4*>(sk + tl * 256 + lc * 16), kf);
+          unpack8<T>(*reinterpret_cast<const uint4*>(sk + row * 256 + lc * 16), kf);
           unpack8<T>(qpk[i], qf);
 #pragma unroll
           for (int d = 0; d < 8; ++d) acc = fmaf(qf[d], kf[d], acc);
@@ -408,85 +402,66 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
       acc += __shfl_xor_sync(0xffffffffu, acc, 1);
       acc += __shfl_xor_sync(0xffffffffu, acc, 2);
       const float logit = live ? acc * p.scale_log2 : -INFINITY;
-      if (quarter == 0 && tl < kCapMax) sh.s_logit[tl] = logit;
-      wmax = fmaxf(wmax, logit);
-    }
+      float m_new = logit;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, o));
-    if (lane == 0) sh.s_red[warp] = wmax;
-    __syncthreads();
-    float m_tile = sh.s_red[0];
+      for (int o = 4; o < 32; o <<= 1) m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, o));
+      m_new = fmaxf(m_new, m_run);      // finite: the first row of a group is live
+      const float rescale = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
+      const float pr = live ? exp2f(logit - m_new) : 0.f;
+      float psum = quarter == 0 ? pr : 0.f;
 #pragma unroll
-    for (int w2 = 1; w2 < kWarps; ++w2) m_tile = fmaxf(m_tile, sh.s_red[w2]);
-    const float m_new = fmaxf(m_run, m_tile);
-    const float rescale = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
-    if (tid < kCapMax) {   // the first kCapMax / 32 warps
-      float psum = 0.f;
-      if (tid < tile_tokens) {
-        const float lg = sh.s_logit[tid];
-        const float pr = (lg == -INFINITY) ? 0.f : exp2f(lg - m_new);
-        sh.s_p[tid] = pr;
-        psum = pr;
-      } else {
-        sh.s_p[tid] = 0.f;
-      }
+      for (int o = 4; o < 32; o <<= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
+      l_run = l_run * rescale + psum;
+      m_run = m_new;
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
-      if (lane == 0) sh.s_sum[warp] = psum;
-    }
-    __syncthreads();
-    {
-      float tile_sum = 0.f;
+      for (int d = 0; d < 4; ++d) o_acc[d] *= rescale;
 #pragma unroll
-      for (int w2 = 0; w2 < kCapMax / 32; ++w2) tile_sum += sh.s_sum[w2];
-      l_run = l_run * rescale + tile_sum;
-    }
-    m_run = m_new;
-#pragma unroll
-    for (int d = 0; d < 8; ++d) o_acc[d] *= rescale;
-#pragma unroll
-    for (int i = 0; i < kSaMaxTpg; ++i) {
-      if (i < tpg) {
-        const int tl = pv_g * tpg + i;
-        const float pr = sh.s_p[tl];
-        if (pr != 0.f) {
-          float vf[8];
-          unpack8<T>(*reinterpret_cast<const uint4*>(sv + tl * 256 + pv_c * 16), vf);
-#pragma unroll
-          for (int d = 0; d < 8; ++d) o_acc[d] = fmaf(pr, vf[d], o_acc[d]);
+      for (int j = 0; j < 8; ++j) {
+        const float pj = __shfl_sync(0xffffffffu, pr, 4 * j);
+        if (pj != 0.f) {   // warp-uniform; rows past the end are stale
+          const uint2 vv = *reinterpret_cast<const uint2*>(sv + (warp * tpw + base + j) * 256 + lane * 8);
+          const float2 a = Elem<T>::to_f2(vv.x), b = Elem<T>::to_f2(vv.y);
+          o_acc[0] = fmaf(pj, a.x, o_acc[0]);
+          o_acc[1] = fmaf(pj, a.y, o_acc[1]);
+          o_acc[2] = fmaf(pj, b.x, o_acc[2]);
+          o_acc[3] = fmaf(pj, b.y, o_acc[3]);
         }
       }
     }
-    __syncthreads();
   }
 
-  // ---- 4: partial to rank 0, merge -----------------------------------------------------------------------
-  ADAMAS_STAMP(1, 7, tid == 0);
-#pragma unroll
-  for (int d = 0; d < 8; ++d) o_acc[d] += __shfl_xor_sync(0xffffffffu, o_acc[d], 16);   // the warp's two groups
-  if (lane < 16) {
-#pragma unroll
-    for (int d = 0; d < 8; ++d) s_o[warp][pv_c * 8 + d] = o_acc[d];
+  // ---- merge: warps -> block -> rank 0 ---------------------------------------------------------------------
+  // a warp parks its partial output in its own K rows (tpw * 256 >= 512 bytes), which nobody else reads
+  __syncwarp();
+  reinterpret_cast<float4*>(sk + warp * tpw * 256)[lane] = make_float4(o_acc[0], o_acc[1], o_acc[2], o_acc[3]);
+  if (lane == 0) {
+    sh.ml[warp][0] = m_run;
+    sh.ml[warp][1] = l_run;
   }
   __syncthreads();
   if (tid < kHeadDim) {
-    float od = 0.f;
+    float M = -INFINITY;
 #pragma unroll
-    for (int g = 0; g < kWarps; ++g) od += s_o[g][tid];
+    for (int w2 = 0; w2 < kSaWarps; ++w2) M = fmaxf(M, sh.ml[w2][0]);
+    float od = 0.f, L = 0.f;
+#pragma unroll
+    for (int w2 = 0; w2 < kSaWarps; ++w2) {
+      const float m = sh.ml[w2][0];
+      const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
+      L += w * sh.ml[w2][1];
+      if (w != 0.f) od += w * reinterpret_cast<const float*>(sk + w2 * tpw * 256)[tid];
+    }
     *cluster.map_shared_rank(part_o + cr * kHeadDim + tid, 0) = od;
-  }
-  if (tid == 0) {
-    float* ml = cluster.map_shared_rank(part_ml + cr * 2, 0);
-    ml[0] = m_run;
-    ml[1] = l_run;
+    if (tid == 0) {
+      float* ml = cluster.map_shared_rank(part_ml + cr * 2, 0);
+      ml[0] = M;
+      ml[1] = L;
+    }
   }
   cluster_arrive_release();
   cluster_wait_acquire();
-  ADAMAS_STAMP(1, 8, tid == 0);
-  ADAMAS_TRACE(1, p.trace_tag, 1, tid == 0);
-#ifdef ADAMAS_PHASE_TIMING
-  if (tid == 0 && blockIdx.x < kTimingBlocks) g_phase_timing[1][blockIdx.x][11] = static_cast<unsigned long long>(n_loc);
-#endif
+  // every peer has read the head's histograms long ago: clear this block's row for the next launch
+  p.hist[(static_cast<size_t>(head) * kSaMaxSlices + cr) * kSaBins + tid] = 0u;
   if (cr != 0 || tid >= kHeadDim) return;
   float M = -INFINITY;
   for (unsigned r = 0; r < CL; ++r) M = fmaxf(M, part_ml[r * 2]);
@@ -495,18 +470,52 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
     const float m = part_ml[r * 2];
     const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
     L += w * part_ml[r * 2 + 1];
-    accd += w * part_o[r * kHeadDim + tid];
+    if (w != 0.f) accd += w * part_o[r * kHeadDim + tid];
   }
   const float res = L > 0.f ? accd / L : 0.f;
   const float res1 = __shfl_down_sync(0xffffffffu, res, 1);
-  T* op = static_cast<T*>(p.o) + static_cast<int64_t>(head) * kHeadDim;
-  if ((tid & 1) == 0) reinterpret_cast<uint32_t*>(op)[tid >> 1] = Elem<T>::from_f2(res, res1);
+  if (p.o_f32) p.o_f32[static_cast<int64_t>(head) * kHeadDim + tid] = res;
+  if (p.o && (tid & 1) == 0)
+    reinterpret_cast<uint32_t*>(static_cast<T*>(p.o) + static_cast<int64_t>(head) * kHeadDim)[tid >> 1] =
+        Elem<T>::from_f2(res, res1);
   if (tid == 0 && p.lse) p.lse[head] = L > 0.f ? M + log2f(L) : -INFINITY;
-  ADAMAS_STAMP(1, 9, tid == 0);
-  ADAMAS_CHAIN(2, 2, true, blockIdx.x == 0 && tid == 0);
-#ifdef ADAMAS_PHASE_TIMING
-  if (tid == 0 && blockIdx.x < kTimingBlocks) g_phase_timing[1][blockIdx.x][11] = static_cast<unsigned long long>(n_loc);
-#endif
+}
+
+// Per-slice histograms of distance rows, for callers of select_attend that did not get them from an
+// estimate kernel: grid (cl, H); block (r, h) counts slice r of head h in shared memory and STORES the
+// row (the table needs no clearing beforehand).
+struct DistHistogramParams {
+  const uint16_t* dist;
+  int64_t dist_stride;
+  uint32_t* hist;
+  int n;
+  int cl;
+};
+
+__global__ void __launch_bounds__(kSaThreads) dist_histogram_kernel(const DistHistogramParams p) {
+  __shared__ unsigned h_local[kSaBins];
+  const int tid = threadIdx.x;
+  const int r = blockIdx.x, head = blockIdx.y;
+  h_local[tid] = 0;
+  __syncthreads();
+  grid_dependency_wait();
+  grid_launch_dependents();
+  const int G = (p.n + 7) >> 3;
+  const int gpb = sa_granules_per_block(p.n, p.cl);
+  const int g_end = min(G, (r + 1) * gpb);
+  const uint4* gbase = reinterpret_cast<const uint4*>(p.dist + static_cast<int64_t>(head) * p.dist_stride);
+  for (int g = r * gpb + tid; g < g_end; g += kSaThreads) {
+    const uint4 v = ld_16(gbase + g);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    const int valid = min(8, p.n - g * 8);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const unsigned d = (w[j >> 1] >> ((j & 1) * 16)) & 0xffffu;
+      if (j < valid) atomicAdd(&h_local[min(d, static_cast<unsigned>(kSaBins - 1))], 1u);
+    }
+  }
+  __syncthreads();
+  p.hist[(static_cast<size_t>(head) * kSaMaxSlices + r) * kSaBins + tid] = h_local[tid];
 }
 
 }  // namespace adamas

@@ -43,6 +43,11 @@ struct DecodeParams {
   float* partial_ml;      // [H, num_splits, 2]
   unsigned* counters;     // [H], zero on entry and on exit
   float scale_log2;       // sm_scale * log2(e)
+  // optional: attend to EVERY token of a sequence whose length lives on the device (the dense layers
+  // of a graph-captured decode step): `indices` is then the page table (idx_stride 0, idx_unit =
+  // page_size) and n_idx, n_tokens, tail_slot0 and tiles_per_block are derived from *seq_len_dev here;
+  // num_splits (the grid) was sized for the longest sequence.
+  const int32_t* seq_len_dev;
 };
 
 template <typename T>
@@ -64,11 +69,6 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
   const int warp = tid >> 5;
   const int H = prm.H;
 
-  const int tok_begin = split * prm.tiles_per_block * kDecTile;
-  const int tok_end = min(prm.n_tokens, tok_begin + prm.tiles_per_block * kDecTile);
-  const int n_tiles = (tok_end - tok_begin + kDecTile - 1) / kDecTile;
-  const int n_listed = prm.n_idx * prm.idx_unit;
-
   const T* kvp = static_cast<const T*>(prm.kv);
   const int32_t* idx_row = prm.indices + static_cast<int64_t>(head) * prm.idx_stride;
   const int64_t v_delta = static_cast<int64_t>(prm.page_size) * H * kHeadDim;
@@ -84,6 +84,25 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
     mbar_fence_init();
   }
   __syncthreads();
+  // The index list, the query and a device-resident length are the preceding kernels' output (a
+  // RoPE-fused append rotates q in place), so nothing of them is touched before the dependency has
+  // resolved.
+  grid_dependency_wait();
+  grid_launch_dependents();
+  int n_tokens = prm.n_tokens, tiles_per_block = prm.tiles_per_block, n_listed = prm.n_idx * prm.idx_unit;
+  unsigned tail_slot0 = prm.tail_slot0;
+  if (prm.seq_len_dev) {
+    const int len = __ldg(prm.seq_len_dev);
+    const int pages = (len + prm.page_size - 1) / prm.page_size;
+    n_listed = (pages - 1) * prm.page_size;
+    n_tokens = len;
+    tail_slot0 = static_cast<unsigned>(__ldg(prm.indices + pages - 1)) * static_cast<unsigned>(prm.page_size);
+    const int tiles = (len + kDecTile - 1) / kDecTile;
+    tiles_per_block = (tiles + prm.num_splits - 1) / prm.num_splits;
+  }
+  const int tok_begin = split * tiles_per_block * kDecTile;
+  const int tok_end = min(n_tokens, tok_begin + tiles_per_block * kDecTile);
+  const int n_tiles = max(0, (tok_end - tok_begin + kDecTile - 1) / kDecTile);
   auto issue_tile = [&](int tile, int stage) {
     uint8_t* sk = smem + stage * kDecStageBytes;
     uint8_t* sv = sk + kDecTile * kDecRowBytes;
@@ -111,7 +130,7 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
           slot = static_cast<unsigned>(__ldg(idx_row + item)) * ps + off;
         }
       } else {
-        slot = prm.tail_slot0 + static_cast<unsigned>(j - n_listed);
+        slot = tail_slot0 + static_cast<unsigned>(j - n_listed);
       }
     }
     if (is_v == 0) s_skip[stage][tl] = ok ? 0 : 1;
@@ -133,6 +152,8 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
     }
   };
 
+  issue_tile(0, 0);
+
   // ---- query: 64 dims per thread, in the order the thread walks its chunks ---------------------
   // thread pair (tl = tid / 2, half = tid % 2); step i reads logical chunk half*8 + (i ^ half*4)
   const int qk_tl = tid >> 1;
@@ -149,10 +170,6 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
     }
   }
 
-  // the index list is the preceding kernel's output
-  grid_dependency_wait();
-  grid_launch_dependents();
-  issue_tile(0, 0);
 
   float m_run = -INFINITY, l_run = 0.f;
   float o_acc[8];
@@ -321,14 +338,15 @@ merge_states_kernel(const float* __restrict__ o_parts, const float* __restrict__
     const float l = lse_parts[static_cast<int64_t>(p) * H + head];
     const float w = (l == -INFINITY) ? 0.f : exp2f(l - M);
     den += w;
-    acc += w * o_parts[(static_cast<int64_t>(p) * H + head) * kHeadDim + d];
+    if (w != 0.f) acc += w * o_parts[(static_cast<int64_t>(p) * H + head) * kHeadDim + d];
   }
-  const float r = acc / den;
+  // every part empty (lse = -inf everywhere): zeros and lse = -inf, as the decode kernel itself writes
+  const float r = den > 0.f ? acc / den : 0.f;
   const float r1 = __shfl_down_sync(0xffffffffu, r, 1);
   if ((d & 1) == 0)
     reinterpret_cast<uint32_t*>(o + static_cast<int64_t>(head) * kHeadDim)[d >> 1] =
         Elem<T>::from_f2(r, r1);
-  if (d == 0 && lse) lse[head] = M + log2f(den);
+  if (d == 0 && lse) lse[head] = den > 0.f ? M + log2f(den) : -INFINITY;
 }
 
 }  // namespace adamas

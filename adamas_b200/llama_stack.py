@@ -8,10 +8,13 @@ linear position scaling, append, estimate, top-k, sparse attention, o_proj).  Ev
 path is library code: torch GEMMs (cuBLAS), F.rms_norm, and scaled_dot_product_attention for the
 dense causal prefill attention.
 
-Decode runs without any host synchronisation per token: the sampled token stays on the device, the
-dense parts between two attention calls (o_proj, MLP, norms, next layer's QKV projection) are
-captured once as CUDA graphs, and the attention path is called eagerly between them because its
-lengths change every token.
+Decode runs without any host synchronisation per token: the sampled token stays on the device and
+the WHOLE token (embedding, every layer's projections, attention path, MLP, the language-model head,
+the argmax and the bump of the device-resident sequence length) is one CUDA graph, captured once
+and replayed per token.  That is possible because the attention path takes the sequence length from
+device memory (utils.decode_step_dev); per token the host only reserves cache room, which uploads one
+page number every `page_size` tokens.  The graph is re-captured once, when the context outgrows the
+token budget and the sparse layers switch from "attend to everything" to the sparse step.
 """
 from __future__ import annotations
 
@@ -75,7 +78,8 @@ class LlamaStack:
         self._qkv = torch.zeros(3, 1, cfg.num_heads, cfg.head_dim, dtype=dtype, device=self.device)
         self._o = torch.zeros(1, cfg.num_heads, cfg.head_dim, dtype=dtype, device=self.device)
         self._logits = torch.zeros(1, cfg.vocab, dtype=torch.float32, device=self.device)
-        self._graphs = None
+        self._token_graphs = {}       # sparse layers dense / sparse -> graph of a whole token
+        self._expected_dev_len = -1   # value seq_len_dev holds if nothing else has touched the caches
 
     # ---- controller (adamas/models/llama.py:528-560) -------------------------------------------
     def init_controller(self, page_size: int, token_budget: int, max_seq_len: int) -> None:
@@ -165,48 +169,64 @@ class LlamaStack:
             self._logits.copy_(F.linear(self._norm(self._x, self.ln_f), self.lm_head))
             self._tok.copy_(self._logits.argmax(dim=-1))
 
-    def _capture(self) -> None:
-        """One CUDA graph for the embedding + first projection and one per layer for everything
-        between two attention calls.  All of it has fixed shapes and addresses."""
-        side = torch.cuda.Stream(device=self.device)
-        side.wait_stream(torch.cuda.current_stream(self.device))
-        keep = (self._tok.clone(), self._x.clone(), self._qkv.clone(), self._logits.clone())
-        with torch.cuda.stream(side):     # warm-up outside capture (cuBLAS handles, workspaces)
-            self._segment_first()
-            for layer in range(self.cfg.num_layers):
-                self._segment_after(layer)
-        torch.cuda.current_stream(self.device).wait_stream(side)
-        torch.cuda.synchronize(self.device)
-        graphs, pool = [], None
-        for seg in [self._segment_first] + [lambda l=l: self._segment_after(l) for l in range(self.cfg.num_layers)]:
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, pool=pool):
-                seg()
-            pool = g.pool()
-            graphs.append(g)
-        for dst, src in zip((self._tok, self._x, self._qkv, self._logits), keep):
-            dst.copy_(src)
-        self._graphs = graphs
+    def _rope(self):
+        return (self.cfg.rope_scale, self.cfg.rope_theta)
+
+    def _token_body(self, sparse: bool) -> None:
+        """One whole token with device-resident lengths: nothing in here depends on the host's view of
+        the sequence, so it runs eagerly or under graph capture alike."""
+        cfg, c = self.cfg, self.controller
+        self._segment_first()
+        q, k, v = self._qkv[0], self._qkv[1], self._qkv[2]
+        for layer in range(cfg.num_layers):
+            U.decode_step_dev(q, k, v, c, layer, out=self._o, dense=(layer < cfg.skip_layers or not sparse),
+                              rope=self._rope())
+            self._segment_after(layer)
+        U.seq_len_advance(c)
 
     @torch.no_grad()
     def decode_one(self, token: Optional[int] = None, use_graphs: bool = True) -> None:
         """One decode step.  Consumes the token left on the device by the previous step (or
-        `token`, to force it) and leaves the next one there; nothing is read back to the host."""
+        `token`, to force it) and leaves the next one there; nothing is read back to the host.
+
+        use_graphs=True: the whole token is one CUDA graph replay (captured the first time, after
+        one eager run of the same launches).  use_graphs=False: eager launches through the
+        host-length operators, the way the reference's model drives them."""
         if token is not None:
             self._tok.fill_(int(token))
-        if use_graphs and self._graphs is None:
-            self._capture()
-        (self._graphs[0].replay if use_graphs else self._segment_first)()
-        q, k, v = self._qkv[0], self._qkv[1], self._qkv[2]
+        if not use_graphs:
+            self._segment_first()
+            q, k, v = self._qkv[0], self._qkv[1], self._qkv[2]
 
-        def body(layer):
-            self._decode_attention(layer, q, k, v, self._o)
-            if use_graphs:
-                self._graphs[layer + 1].replay()
-            else:
+            def body(layer):
+                self._decode_attention(layer, q, k, v, self._o)
                 self._segment_after(layer)
 
-        self._layer_loop(1, body)
+            self._layer_loop(1, body)
+            return
+        c = self.controller
+        c.prepare_hadamard(1)
+        c.kv_cache.table_all()          # uploads the page number of a page that has just been opened
+        c.hadamard_cache.table_all()
+        if self._expected_dev_len != c.kv_cache.seqlen:
+            c.sync_seq_len()
+        sparse = c.kv_cache.seqlen > c.token_budget()
+        g = self._token_graphs.get(sparse)
+        if g is None:
+            # first token in this mode: run it eagerly (it is a real token and warms up every library
+            # call), then record the same launches for the tokens to come
+            c.set_page_budget(self._page_budget)
+            c.begin_forward(1)
+            self._token_body(sparse)
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._token_body(sparse)
+            c.end_forward()
+            self._token_graphs[sparse] = g
+        else:
+            g.replay()
+        self._expected_dev_len = c.kv_cache.seqlen + 1
 
     def last_logits(self) -> torch.Tensor:
         return self._logits

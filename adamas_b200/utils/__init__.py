@@ -22,6 +22,8 @@ __all__ = [
     "decode_topk",
     "decode_sparse_attn",
     "decode_step",
+    "decode_step_dev",
+    "seq_len_advance",
 ]
 
 
@@ -129,16 +131,44 @@ def decode_step(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, iController: 
     if not c.need_estimate():
         append_qkv_fused(q, k, v, c, layer_idx, scale=scale, rope=rope)
         return decode_sparse_attn(q, c, layer_idx, c.kv_indices_without_last, out=o)
-    # the packed query code is scratch here (one buffer per controller: launches of one sequence are
-    # ordered on one stream)
-    q_code = getattr(c, "_q_code_scratch", None)
-    if q_code is None or q_code.dtype != k.dtype or q_code.device != k.device or q_code.size(1) != k.size(1):
-        q_code = torch.empty(1, k.size(1), k.size(2) // 8, dtype=k.dtype, device=k.device)
-        c._q_code_scratch = q_code
     n = c.hadamard_cache.seqlen - 1
     _kernels.decode_step(
-        q, k, v, o, q_code, c.kv_cache.buf_layer(layer_idx), c.kv_indices_with_last, c.kv_cache.last_page_len,
-        c.kv_last_page_idx, c.hadamard_cache.buf_layer(layer_idx), c.hadamard_indices,
-        c.hadamard_cache.last_page_len, c.inference_token_budget, c.distance_scratch(n),
+        q, k, v, o, c.q_code_scratch(k.dtype), c.kv_cache.buf_layer(layer_idx), c.kv_indices_with_last,
+        c.kv_cache.last_page_len, c.kv_last_page_idx, c.hadamard_cache.buf_layer(layer_idx), c.hadamard_indices,
+        c.hadamard_cache.last_page_len, c.inference_token_budget, c.distance_scratch(n), c.hist_scratch,
         indices_out=c.topk_dindices_buffer if record_indices else None, scale=scale, rope=rope)
     return o
+
+
+def decode_step_dev(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, iController: InferenceController,
+                    layer_idx: int, out: Optional[torch.Tensor] = None, dense: bool = False,
+                    scale: Optional[float] = None, rope=None) -> torch.Tensor:
+    """decode_step whose launches do not depend on the sequence length: the kernels read it from
+    iController.seq_len_dev, so the call can be captured in a CUDA graph once and replayed for every
+    token (the reference re-plans on the host every step: adamas/utils/controller.py:82-131,
+    kernels/include/decode/decode_handler.cuh:73-121).  Per token the host still reserves cache room
+    (prepare_hadamard(1), which uploads a new page number when a page fills up); the device length is
+    advanced with seq_len_advance at the END of the token's work (or set with sync_seq_len()).
+
+    dense=True: append and attend to every token (the first layers of the reference's model);
+    otherwise the sparse step at the controller's token budget, which needs a longer context.
+    rope: None, (rope_scale, rope_theta) or {"inv_freq": tensor[64], "mscale": float}."""
+    c = iController
+    o = out if out is not None else torch.empty_like(q)
+    kv_table = c.kv_cache.table_all()
+    code_table = c.hadamard_cache.table_all()
+    if dense:
+        c._decode_handler.dense_step_dev(q, k, v, o, c.q_code_scratch(k.dtype), c.kv_cache.buf_layer(layer_idx),
+                                         kv_table, c.hadamard_cache.buf_layer(layer_idx), code_table, c.seq_len_dev,
+                                         c.max_seq_len, scale=scale, rope=rope)
+        return o
+    _kernels.decode_step_dev(q, k, v, o, c.q_code_scratch(k.dtype), c.kv_cache.buf_layer(layer_idx), kv_table,
+                             c.hadamard_cache.buf_layer(layer_idx), code_table, c.seq_len_dev, c.max_seq_len,
+                             c.token_budget(), c.distance_scratch(c.max_seq_len - 1), c.hist_scratch,
+                             scale=scale, rope=rope)
+    return o
+
+
+def seq_len_advance(iController: InferenceController, delta: int = 1) -> None:
+    """iController.seq_len_dev += delta on the device (one capturable launch)."""
+    _kernels.seq_len_advance(iController.seq_len_dev, delta)

@@ -9,7 +9,9 @@ Differences from the reference, none of which change what its callers see at pag
 * the small ``*_indptr_*`` tensors are created on first access (the kernels here take the page
   count as a host integer);
 * for page_size > 1 the code cache holds one entry per token (the reference's layout is only
-  consistent at page_size 1) and budgets are counted in tokens: budget = page_budget * page_size.
+  consistent at page_size 1) and budgets are counted in tokens: budget = page_budget * page_size;
+* the sequence length is also kept in device memory (``seq_len_dev``), for decode steps whose launches
+  do not depend on the length and can therefore be replayed from one CUDA graph (utils.decode_step_dev).
 """
 from __future__ import annotations
 
@@ -60,6 +62,11 @@ class InferenceController:
         self.topk_buf = None
         self._topk_store = None
         self._estimate_store = None
+
+        self.max_seq_len = self.kv_cache.pool.capacity * page_size
+        self._hist = None
+        self._seq_len_dev = None
+        self._q_code_scratch = None
 
     # ---- small index tensors, made on demand -------------------------------------------------
     def _indptr(self, name):
@@ -161,6 +168,41 @@ class InferenceController:
         """[H, n] int16 view of the same buffer, rows on 16-byte boundaries (fused decode step)."""
         self.estimate_buffer(n)
         return self._estimate_store[:, :n]
+
+    # ---- state of the fused / graph-replayable decode step ------------------------------------
+    @property
+    def hist_scratch(self) -> torch.Tensor:
+        """Histogram table of the fused decode step ([H, 16, 512] int32; zero between steps)."""
+        if self._hist is None:
+            self._hist = torch.zeros(self.num_heads, 16, 512, dtype=torch.int32, device=self.device)
+        return self._hist
+
+    @property
+    def seq_len_dev(self) -> torch.Tensor:
+        """One-element int32 device tensor with the sequence length the next device-state decode step
+        sees (tokens in the caches, the one being appended included).  sync_seq_len() sets it from the
+        host's count; utils.seq_len_advance adds one on the device."""
+        if self._seq_len_dev is None:
+            self._seq_len_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
+        return self._seq_len_dev
+
+    def sync_seq_len(self) -> None:
+        """seq_len_dev := the host's sequence length (after prepare_hadamard(1): the length the coming
+        decode step works on)."""
+        self.seq_len_dev.fill_(self.kv_cache.seqlen)
+
+    def q_code_scratch(self, dtype) -> torch.Tensor:
+        """[1, H, D/8] packed query code of the step in flight (one per controller: the launches of one
+        sequence are ordered on one stream)."""
+        q = self._q_code_scratch
+        if q is None or q.dtype != dtype:
+            q = torch.empty(1, self.num_heads, self.head_dim // 8, dtype=dtype, device=self.device)
+            self._q_code_scratch = q
+        return q
+
+    def token_budget(self) -> int:
+        """The configured budget in tokens (not capped by the current length)."""
+        return self._page_budget * self.page_size
 
     def clean_states(self):
         self.kv_cache.release()

@@ -41,3 +41,8 @@ class BatchDecodeWithPagedKVCacheWrapper:
         self._wrapper.forward(q, o, paged_kv_data, paged_kv_indices, paged_kv_indptr, paged_kv_last_page_len,
                               paged_kv_last_page_idx, rope_scale, rope_theta, token_granular=token_granular,
                               lse=lse)
+
+    def dense_step_dev(self, *args, **kwargs):
+        """Dense decode step with the sequence length on the device (see
+        _kernels.BatchDecodeWithPagedKVCachePyTorchWrapper.dense_step_dev)."""
+        self._wrapper.dense_step_dev(*args, **kwargs)

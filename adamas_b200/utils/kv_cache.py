@@ -101,6 +101,13 @@ class KvCache:
             self._uploaded = n
         return self._table[:n]
 
+    def table_all(self) -> torch.Tensor:
+        """The whole persistent table buffer (capacity entries; entries beyond the current page count
+        are not meaningful), after uploading any new entries: what a kernel that takes the sequence
+        length from device memory indexes."""
+        self.table_device()
+        return self._table
+
     def release(self) -> None:
         """Give all pages back."""
         self._seqlen = 0

@@ -287,9 +287,15 @@ class Workload:
             U.decode_sparse_attn(q, c, layer, c.topk_dindices_buffer, out=self.d_out[layer])
         elif stage == "select_attend":
             n = c.hadamard_cache.seqlen - 1
-            K.select_attend(c.distance_scratch(n), c.inference_token_budget - 1, q, self.d_out[layer],
+            k = c.inference_token_budget - 1
+            # first launch of the step without the append: leaves the distances and the histograms
+            K.estimate_attn_score(self.q_code[layer], c.distance_scratch(n), c.hadamard_cache.buf_layer(layer),
+                                  c.hadamard_indices, None, c.hadamard_cache.last_page_len,
+                                  c.hadamard_last_page_idx, c.layout, hist=c.hist_scratch,
+                                  hist_slices=K.select_attend_slices(n, k, self.args.heads))
+            K.select_attend(c.distance_scratch(n), k, q, self.d_out[layer],
                             c.kv_cache.buf_layer(layer), c.kv_indices_with_last, c.kv_cache.last_page_len,
-                            c.kv_last_page_idx)
+                            c.kv_last_page_idx, hist=c.hist_scratch, hist_ready=True)
         else:
             raise ValueError(stage)
 

@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define ADAMAS_ABI_VERSION 2
+#define ADAMAS_ABI_VERSION 3
 
 /* status codes */
 #define ADAMAS_OK 0
@@ -48,13 +48,21 @@ extern "C" {
 
 typedef void* adamas_stream_t;   /* a cudaStream_t */
 
+/* Histogram scratch of the fused decode step: 32-bit words per head.  The estimate launch of a step
+ * counts the distances of every head into it (one 512-bin histogram per slice of the row, up to 16
+ * slices), the select+attend launch reads the counts and clears them again.  The caller allocates
+ * num_heads * ADAMAS_HIST_WORDS_PER_HEAD words and zeroes them ONCE; every call that uses the table
+ * leaves it all zero.  Calls that may overlap on the GPU need separate tables. */
+#define ADAMAS_HIST_WORDS_PER_HEAD (16 * 512)
+
 int adamas_abi_version(void);
 const char* adamas_last_error(void);
 
 /* Reads (and optionally clears) the current device's error flags.  Kernels never spin without a
  * limit: one that gives up on a wait (bit 0: the estimate kernel's copy pipeline; bit 1: the decode
  * kernel's; bit 2: the gather of select+attend) sets a flag here and
- * finishes, leaving wrong results behind.  Synchronises with the device.  No counterpart in the
+ * finishes, leaving wrong results behind.  Bit 3: select+attend was given a histogram table that does
+ * not describe its distance rows (not zeroed before the step, or shared by overlapping calls).  Synchronises with the device.  No counterpart in the
  * reference, whose kernels have no waits of this kind. */
 int adamas_device_error(unsigned* flags, int clear);
 
@@ -163,12 +171,15 @@ int adamas_append_prefill(const void* k, const void* v, const void* h, int64_t n
  * n_tokens = (code_num_pages-1)*page_size + code_last_page_len - exclude_last; exclude_last = 1 leaves
  * the newest token out, as the reference does; 0 is for a sequence shard that does not hold it.
  * q_code [H, D/8]; out_format ADAMAS_VAL_F16 (reference) or ADAMAS_VAL_U16.
+ * hist (optional, may be NULL): histogram scratch (see ADAMAS_HIST_WORDS_PER_HEAD) that additionally
+ * receives the counts a following adamas_select_attend(..., hist_ready = 1) needs; hist_slices is then
+ * the value adamas_select_attend_slices gives for that call.
  * Replaces estimate_attn_score (adamas/ops/csrc/estimate.cu:6-84,
  * kernels/include/decode/decode_attn.cuh:287-443,1144-1211). */
 int adamas_estimate(const void* q_code, const void* code_data, const int32_t* code_page_table,
                     int code_num_pages, int code_last_page_len, int page_size, int num_heads,
                     int head_dim, void* out, int64_t out_stride, int out_format, int metric,
-                    int exclude_last, adamas_stream_t stream);
+                    int exclude_last, uint32_t* hist, int hist_slices, adamas_stream_t stream);
 
 /* ---- stage 3: top-k ------------------------------------------------------------------------ */
 
@@ -252,38 +263,56 @@ int adamas_decode_forward_static(const void* q, void* o, float* lse, const void*
                                  int last_page_idx, int last_page_len, int tail_len, float sm_scale,
                                  adamas_stream_t stream);
 
-/* Stages 3 and 4 in one launch: per head, the k smallest of n distances (ADAMAS_VAL_U16 values below
- * 512, rows on 16-byte boundaries; ties to the lower position) are selected and attended together with
- * the newest token (entry last_page_len-1 of page last_page_idx).  Token t of the row is looked up as
- * kv_page_table[t / page_size] * page_size + t % page_size.  out_idx (optional, [H, out_stride])
- * receives the winners' physical token slots in ascending position order, exactly what adamas_topk
- * would write.  Replaces the topk_filtering + BatchDecodeWithPagedKVCachePyTorchWrapper::Forward pair
+/* Stages 3 and 4 in one launch: per head, the k smallest of n distances (ADAMAS_VAL_U16, rows on
+ * 16-byte boundaries; values of 511 and more count as equal; ties to the lower position) are selected
+ * and attended together with the newest token (entry last_page_len-1 of page last_page_idx;
+ * last_page_len = 0: there is no newest token, as on a sequence shard that does not hold it).  Token t
+ * of the row is looked up as kv_page_table[t / page_size] * page_size + t % page_size.
+ * o [H, D] in dtype and / or o_f32 [H, D] fp32 (the partial result of a sequence shard; needs lse).
+ * out_idx (optional, [H, out_stride]) receives the winners' physical token slots in ascending position
+ * order, exactly what adamas_topk would write.
+ * hist: histogram scratch (see ADAMAS_HIST_WORDS_PER_HEAD), all zero on entry unless hist_ready, all
+ * zero on exit.  hist_ready = 0: the call counts the distances itself first (one more launch);
+ * hist_ready = 1: an adamas_estimate / adamas_append_estimate call with hist_slices =
+ * adamas_select_attend_slices(n, k, num_heads) has left the counts there.
+ * ext_cut (optional, device, [H][2] int32, 8-byte aligned): the cut distance and the number of
+ * cut-valued elements THIS call takes, per head, decided elsewhere (the global cut of a sequence split
+ * over several GPUs); k is then only an upper bound for the winners of this call.
+ * Replaces the topk_filtering + BatchDecodeWithPagedKVCachePyTorchWrapper::Forward pair
  * (adamas/models/Adamas.py:185-200) for n up to 262144 (32768 x the adamas_set_max_cluster bound). */
 int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, const void* q, void* o,
-                         float* lse, const void* kv_data, const int32_t* kv_page_table, int page_size,
-                         int num_heads, int head_dim, int dtype, int last_page_idx, int last_page_len,
+                         float* o_f32, float* lse, const void* kv_data, const int32_t* kv_page_table,
+                         int page_size, int num_heads, int head_dim, int dtype, int last_page_idx,
+                         int last_page_len, uint32_t* hist, int hist_ready, const int32_t* ext_cut,
                          int32_t* out_idx, int64_t out_stride, float sm_scale, adamas_stream_t stream);
+
+/* Number of slices (thread blocks per head) adamas_select_attend uses for rows of n distances, k
+ * winners and num_heads heads on the current device: the hist_slices an estimate call must be given
+ * when it prepares the histogram table for that call.  No counterpart in the reference. */
+int adamas_select_attend_slices(int n, int k, int num_heads, int* slices);
 
 /* Stages 1 and 2 of a decode step in one launch, for 16, 32 or 64 heads: the append of
  * adamas_append_decode_fused (new token's K, V and code into the caches, query code to q_code; q and k
  * already rotated) and the estimate of adamas_estimate with ADAMAS_VAL_U16 output, the L1 metric and
  * exclude_last = 1 (dist [H, dist_stride], rows on 16-byte boundaries, dist_stride >= context - 1).
  * Every thread block derives the query code from q by itself, so the scan does not wait for an append
- * launch.  Replaces hadamard_transform + append_kvh + decode_estimate of
- * adamas/models/Adamas.py:145-180. */
+ * launch.  hist / hist_slices as for adamas_estimate.  Replaces hadamard_transform + append_kvh +
+ * decode_estimate of adamas/models/Adamas.py:145-180. */
 int adamas_append_estimate(const void* q, const void* k, const void* v, void* q_code, void* kv_data,
                            const int32_t* kv_page_table, int kv_num_pages, int kv_last_page_len,
                            void* code_data, const int32_t* code_page_table, int code_num_pages,
                            int code_last_page_len, int num_heads, int head_dim, int page_size, int dtype,
                            void* dist, int64_t dist_stride, float hadamard_scale,
-                           const float* thresholds3_host, adamas_stream_t stream);
+                           const float* thresholds3_host, uint32_t* hist, int hist_slices,
+                           adamas_stream_t stream);
 
 /* One layer's whole decode step in one call: two launches (the estimate with the append inside, then
  * select+attend) for 32 or 64 heads and rotated inputs, three (fused append, estimate,
  * select+attend) otherwise:
  * what adamas/models/Adamas.py:145-200 does with seven launches.  q, k, v, o [1,H,D]; q_code
  * [1,H,D/8] scratch/output; dist_scratch [H, dist_stride] 16-bit, rows on 16-byte boundaries,
- * dist_stride >= context - 1.  Requires context > budget (otherwise every page is attended: use
+ * dist_stride >= context - 1; hist_scratch: see ADAMAS_HIST_WORDS_PER_HEAD.  Requires context > budget
+ * (otherwise every page is attended: use
  * adamas_decode_forward).  kv_last_page_idx is the physical number of the last KV page.  With
  * rope_scale > 0, q and k arrive un-rotated and the append launch rotates them in place first
  * (apply_rope_in_place, adamas/models/Adamas.py:113); rope_scale <= 0: q and k are already rotated. */
@@ -292,10 +321,59 @@ int adamas_decode_step(void* q, void* k, const void* v, void* o, float* lse, voi
                        int kv_last_page_len, int kv_last_page_idx, void* code_data,
                        const int32_t* code_page_table, int code_num_pages, int code_last_page_len,
                        int num_heads, int head_dim, int page_size, int dtype, int budget,
-                       void* dist_scratch, int64_t dist_stride, int32_t* out_idx, int64_t out_stride,
-                       float hadamard_scale, const float* thresholds3_host, float rope_scale,
-                       float rope_theta, float sm_scale,
+                       void* dist_scratch, int64_t dist_stride, uint32_t* hist_scratch, int32_t* out_idx,
+                       int64_t out_stride, float hadamard_scale, const float* thresholds3_host,
+                       float rope_scale, float rope_theta, float sm_scale,
                        adamas_stream_t stream);
+
+/* ---- decode steps whose sequence length lives on the device ----------------------------------
+ * The reference rebuilds its index tensors on the host and re-plans the decode every step
+ * (adamas/utils/controller.py:82-131, kernels/include/decode/decode_handler.cuh:73-121), so no two
+ * steps are the same sequence of launches.  Here a step can take the sequence length from device
+ * memory: *seq_len_dev = tokens in the caches, the one being appended included (int32).  The
+ * launches are then shaped by max_seq_len only, every kernel derives page numbers, slots, positions
+ * and row lengths from the device value, and ONE captured CUDA graph of the step serves every token:
+ * replay it, and add 1 to the length between replays (adamas_seq_len_advance, itself capturable).
+ * Rules: *seq_len_dev <= max_seq_len; the page tables hold an entry for every page of the current
+ * length before the step runs; the value must not be written by the kernel that directly precedes
+ * a step in the stream (parts of a step start early and read it before that kernel has finished):
+ * advance it at the END of a token's work, not in front of the next step. */
+
+/* adamas_decode_step with the length on the device.  Needs *seq_len_dev > budget.
+ * rope_inv_freq (optional, device, 64 floats): per-pair rotation frequencies with any position
+ * scaling folded in; the angle of pair j at position t is t * rope_inv_freq[j] and the rotated values
+ * are multiplied by rope_mscale (YaRN-style scaling; rope_scale / rope_theta are then unused). */
+int adamas_decode_step_dev(void* q, void* k, const void* v, void* o, float* lse, void* q_code, void* kv_data,
+                           const int32_t* kv_page_table, void* code_data, const int32_t* code_page_table,
+                           const int32_t* seq_len_dev, int max_seq_len, int num_heads, int head_dim,
+                           int page_size, int dtype, int budget, void* dist_scratch, int64_t dist_stride,
+                           uint32_t* hist_scratch, int32_t* out_idx, int64_t out_stride, float hadamard_scale,
+                           const float* thresholds3_host, float rope_scale, float rope_theta,
+                           const float* rope_inv_freq, float rope_mscale, float sm_scale,
+                           adamas_stream_t stream);
+
+/* The dense counterpart (the reference's first layers, adamas/models/llama.py:428-439: every page is
+ * "selected"): fused append (with the rotary embedding when rope_scale > 0 or rope_inv_freq is given)
+ * and attention over all *seq_len_dev tokens.  The handler must have been planned with
+ * adamas_decode_begin_forward(handler, max_seq_len, ...). */
+int adamas_dense_step_dev(adamas_decode_handler_t* handler, void* q, void* k, const void* v, void* o, float* lse,
+                          void* q_code, void* kv_data, const int32_t* kv_page_table, void* code_data,
+                          const int32_t* code_page_table, const int32_t* seq_len_dev, int max_seq_len,
+                          int num_heads, int head_dim, int page_size, int dtype, float hadamard_scale,
+                          const float* thresholds3_host, float rope_scale, float rope_theta,
+                          const float* rope_inv_freq, float rope_mscale, float sm_scale,
+                          adamas_stream_t stream);
+
+/* *seq_len_dev += delta, as one tiny launch that is ordered after everything before it in the stream
+ * and before everything after it. */
+int adamas_seq_len_advance(int32_t* seq_len_dev, int delta, adamas_stream_t stream);
+
+/* adamas_apply_rope_in_place with a table of rotation frequencies (device, 64 floats) and a factor on
+ * the rotated values instead of (rope_scale, rope_theta): the prefill side of YaRN-scaled models.  The
+ * reference's kernel knows linear scaling only (kernels/include/decode/decode_page.cuh:650-659). */
+int adamas_apply_rope_table_in_place(void* q, void* k, int64_t seq_len, int num_q_heads, int num_kv_heads,
+                                     int head_dim, int64_t past_kv_len, const float* inv_freq_dev, float mscale,
+                                     int dtype, adamas_stream_t stream);
 
 /* Merge P partial results over disjoint token sets: o_parts [P, H, D] fp32 (each already
  * normalised), lse_parts [P, H] base-2; writes o [H, D] in dtype and, optionally, lse [H].

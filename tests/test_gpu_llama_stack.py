@@ -126,24 +126,54 @@ def test_sparse_stack_matches_oracle_layer_by_layer(page_size, budget):
     st.init_controller(page_size=page_size, token_budget=budget, max_seq_len=352)
     st.prefill(ids[:320])
     for t in range(320, 330):
-        st.decode_one(token=int(ids[t]))
+        st.decode_one(token=int(ids[t]), use_graphs=False)      # the eager, host-length path is the one checked in place
     assert cls.checks == 10 * (st.cfg.num_layers - st.cfg.skip_layers)      # every sparse layer, every step
     assert st.controller.need_estimate()
     from adamas_b200 import _lib
     assert _lib.device_error() == 0
 
 
-def test_graph_segments_equal_eager_and_generate_runs():
-    ids = _ids(200, seed=2)
-    outs = []
+@pytest.mark.parametrize("prefill,budget,new_tokens", [(200, 64, 40), (50, 64, 40)])
+def test_whole_token_graph_equals_eager_loop(prefill, budget, new_tokens):
+    """decode_one as ONE graph replay per token (device-resident sequence length) against the eager
+    loop over the host-length operators: same sampled tokens, same logits, same caches.  The second
+    case starts with every layer dense and crosses the token budget on the way (the graph is
+    re-captured once), both cross several page boundaries."""
+    ids = _ids(prefill, seed=2)
+    forced = _ids(new_tokens, seed=5).tolist()     # the same input token at every step of both runs
+    runs = []
     for use_graphs in (True, False):
         st = _stack()
-        st.init_controller(page_size=16, token_budget=64, max_seq_len=256)
+        st.init_controller(page_size=16, token_budget=budget, max_seq_len=prefill + new_tokens + 16)
         st.prefill(ids)
-        for _ in range(12):
-            st.decode_one(use_graphs=use_graphs)
-        outs.append(st.last_logits().clone())
-    assert torch.allclose(outs[0], outs[1], atol=1e-3)
+        toks, logits = [], []
+        for t in range(new_tokens):
+            st.decode_one(token=forced[t], use_graphs=use_graphs)
+            toks.append(st._tok.clone())
+            logits.append(st.last_logits().clone())
+        c = st.controller
+        n_pages = len(c.kv_cache.indicies)
+        table = torch.tensor(c.kv_cache.indicies, device=DEV)
+        kv = c.kv_cache.pool.buf[:, table].clone()
+        codes = c.hadamard_cache.pool.buf[:, torch.tensor(c.hadamard_cache.indicies, device=DEV)].clone()
+        runs.append((torch.cat(toks).cpu(), torch.cat(logits).cpu(), kv.cpu(), codes.cpu(), c.kv_cache.seqlen, n_pages))
+        if use_graphs:
+            assert len(st._token_graphs) == (2 if prefill < budget else 1)
+            assert int(c.seq_len_dev.item()) == c.kv_cache.seqlen + 1
+    (tg, lg, kvg, cg, ng, pg), (te, le, kve, ce, ne, pe) = runs
+    assert ng == ne == prefill + new_tokens and pg == pe
+    assert torch.allclose(lg, le, atol=2e-3), (lg - le).abs().max().item()
+    assert (tg == te).float().mean().item() > 0.9      # argmax of near-identical logits
+    last = (ng - 1) % 16 + 1           # entries of the last page beyond the sequence are never written
+    assert torch.equal(cg[:, :-1].view(torch.int16), ce[:, :-1].view(torch.int16))
+    assert torch.equal(cg[:, -1, :, :last].view(torch.int16), ce[:, -1, :, :last].view(torch.int16))
+    assert torch.allclose(kvg[:, :-1].float(), kve[:, :-1].float(), atol=2e-3)
+    from adamas_b200 import _lib
+    assert _lib.device_error() == 0
+
+
+def test_generate_runs():
+    ids = _ids(200, seed=2)
     st = _stack()
     st.init_controller(page_size=16, token_budget=64, max_seq_len=256)
     toks = st.generate(ids, 20)

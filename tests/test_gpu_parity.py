@@ -527,7 +527,7 @@ def test_two_launch_step_equals_three_launch_step(dtype, rope, L, ps, budget, H)
             K.decode_step(q, k_new, v_new, o, q_code, c.kv_cache.buf_layer(0), c.kv_indices_with_last,
                           c.kv_cache.last_page_len, c.kv_last_page_idx, c.hadamard_cache.buf_layer(0),
                           c.hadamard_indices, c.hadamard_cache.last_page_len, c.inference_token_budget, dist,
-                          indices_out=c.topk_dindices_buffer, rope=rope)
+                          c.hist_scratch, indices_out=c.topk_dindices_buffer, rope=rope)
             torch.cuda.synchronize()
         finally:
             K.set_fused_append(True)

@@ -21,7 +21,7 @@ def test_library_exports_every_declared_symbol():
     for name in sorted(declared):
         assert hasattr(_lib.lib, name), f"{name} declared in the header but not exported"
     assert set(_lib.SIGNATURES) | {"adamas_abi_version", "adamas_last_error"} == declared
-    assert _lib.lib.adamas_abi_version() == _lib.ABI_VERSION == 2
+    assert _lib.lib.adamas_abi_version() == _lib.ABI_VERSION == 3
 
 
 def test_argument_validation_without_gpu():
