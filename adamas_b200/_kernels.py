@@ -130,17 +130,23 @@ def pack_2bit(h: torch.Tensor, o: torch.Tensor, past_kv_len: int = 0) -> None:
 
 
 def histogram_scratch(num_heads: int, device) -> torch.Tensor:
-    """A zeroed histogram table for decode_step / select_attend ([H, 16, 512] 32-bit counts).  Every
-    call that uses it leaves it all zero, so one table serves all steps of a sequence; calls that
-    may overlap on the GPU need separate tables."""
-    return torch.zeros(num_heads, 16, 512, dtype=torch.int32, device=device)
+    """A zeroed scratch table for decode_step / select_attend: per head 16 histograms of 512 32-bit
+    counts, then the slots through which the thread blocks of a head pass their partial results.
+    Every call that uses it leaves the histograms all zero, so one table serves all steps of a
+    sequence; calls that may overlap on the GPU need separate tables."""
+    return torch.zeros(num_heads, _lib.HIST_WORDS_PER_HEAD, dtype=torch.int32, device=device)
+
+
+def histogram_counts(hist: torch.Tensor) -> torch.Tensor:
+    """The [H, 16, 512] histogram part of a histogram_scratch table."""
+    return hist.view(hist.size(0), -1)[:, : 16 * 512].view(hist.size(0), 16, 512)
 
 
 def _check_hist(hist: Optional[torch.Tensor], num_heads: int) -> Optional[torch.Tensor]:
     if hist is not None:
         _require(hist.is_cuda and hist.is_contiguous() and hist.dtype == torch.int32
                  and hist.numel() >= num_heads * _lib.HIST_WORDS_PER_HEAD,
-                 "hist must be a contiguous int32 CUDA tensor of H * 16 * 512 elements")
+                 "hist must be a contiguous int32 CUDA tensor made by histogram_scratch(H)")
     return hist
 
 

@@ -82,7 +82,7 @@ lib.adamas_last_error.argtypes = []
 lib.adamas_last_error.restype = c_char_p
 
 ABI_VERSION = 3
-HIST_WORDS_PER_HEAD = 16 * 512
+HIST_WORDS_PER_HEAD = 16 * 512 + 16 * 132
 if lib.adamas_abi_version() != ABI_VERSION:
     raise ImportError(f"{LIB_PATH} has ABI version {lib.adamas_abi_version()}, expected {ABI_VERSION}; rebuild it")
 

@@ -74,13 +74,14 @@ int check_common(int num_heads, int head_dim, int page_size, int dtype) {
 
 constexpr int kEstAppendStatic = 1280;   // static shared memory of estimate_append_kernel, rounded up
 constexpr int kEstPagesStatic = 8448;    // static shared memory of estimate_pages_kernel, rounded up
-constexpr int kSaMaxDynSmem = 160 * 1024;   // dynamic shared memory select_attend may ask for
+constexpr int kSaMaxDynSmem = 160 * 1024;   // dynamic shared memory select_attend may ask for (a long winner list)
 
 // Per-device facts and one-time kernel attributes.
 struct DeviceInfo {
   bool ready = false;
   int num_sms = 0;
   int max_smem_optin = 0;
+  int smem_per_sm = 0;
   int topk_dyn_smem = 0;
 };
 
@@ -96,6 +97,7 @@ int get_device_info(const DeviceInfo** out) {
   if (!d.ready) {
     ADAMAS_CUDA(cudaDeviceGetAttribute(&d.num_sms, cudaDevAttrMultiProcessorCount, dev));
     ADAMAS_CUDA(cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    ADAMAS_CUDA(cudaDeviceGetAttribute(&d.smem_per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev));
     d.topk_dyn_smem = d.max_smem_optin - static_cast<int>(sizeof(TopkShared)) - 1024;
     ADAMAS_CUDA(cudaFuncSetAttribute(topk_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, d.topk_dyn_smem));
     ADAMAS_CUDA(cudaFuncSetAttribute(topk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, d.topk_dyn_smem));
@@ -156,12 +158,10 @@ int get_device_info(const DeviceInfo** out) {
     SET_CARVEOUT((sparse_decode_kernel<__half>));
     SET_CARVEOUT((sparse_decode_kernel<__nv_bfloat16>));
 #undef SET_CARVEOUT
-    // select+attend: large dynamic shared memory; clusters of 16 blocks (long rows of few heads) are
-    // beyond the portable size
+    // select+attend: large dynamic shared memory
 #define SA_ATTR(T, I)                                                                                          \
   ADAMAS_CUDA(cudaFuncSetAttribute(select_attend_kernel<T, I>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
                                    kSaMaxDynSmem));                                                            \
-  ADAMAS_CUDA(cudaFuncSetAttribute(select_attend_kernel<T, I>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1)); \
   ADAMAS_CUDA(cudaFuncSetAttribute(select_attend_kernel<T, I>, cudaFuncAttributePreferredSharedMemoryCarveout, \
                                    cudaSharedmemCarveoutMaxShared))
 #define SA_ATTR_ALL(T) \
@@ -572,7 +572,7 @@ static int estimate_impl(const void* q_code, const void* code_data, const int32_
     pp.hist = hist;
     pp.hist_cl = hist_cl;
 #define LAUNCH_ESTP(M, OT) \
-  ADAMAS_LAUNCH("estimate_pages_kernel", (estimate_pages_kernel<M, OT>), dim3(blocks), dim3(kEstThreads), smem, st, 1, pp)
+  ADAMAS_LAUNCH("estimate_pages_kernel", (estimate_pages_kernel<M, OT>), dim3(blocks), dim3(kEstPagesThreads), smem, st, 1, pp)
     if (metric == ADAMAS_METRIC_L1) {
       if (out_format == ADAMAS_VAL_F16) LAUNCH_ESTP(0, __half); else LAUNCH_ESTP(0, uint16_t);
     } else {
@@ -1064,8 +1064,8 @@ namespace {
 
 template <typename T, int I>
 int launch_select_attend_one(const SelectAttendParams& prm, int cl, int num_heads, size_t smem, cudaStream_t st) {
-  const dim3 grid(static_cast<unsigned>(num_heads) * cl);
-  ADAMAS_LAUNCH("select_attend_kernel", (select_attend_kernel<T, I>), grid, dim3(kSaThreads), smem, st, cl, prm);
+  const dim3 grid(static_cast<unsigned>(cl), static_cast<unsigned>(num_heads));
+  ADAMAS_LAUNCH("select_attend_kernel", (select_attend_kernel<T, I>), grid, dim3(kSaThreads), smem, st, 1, prm);
   return check_launch("select_attend_kernel");
 }
 
@@ -1082,62 +1082,19 @@ int launch_select_attend(const SelectAttendParams& prm, int items, int cl, int n
   return fail(ADAMAS_ERR_INVALID, "unsupported row length for select_attend");
 }
 
-// How many clusters of 16 select_attend blocks with `smem` bytes of dynamic shared memory the device
-// holds at once; 0 if it cannot launch them.  Queried once per device and shared-memory size (in KB);
-// the kernel's attributes have been set by get_device_info.
-int big_cluster_capacity(size_t smem, int* out) {
-  static int cap[64][161];
-  static bool known[64][161] = {};
-  int dev = 0;
-  ADAMAS_CUDA(cudaGetDevice(&dev));
-  const int kb = static_cast<int>(std::min<size_t>((smem + 1023) / 1024, 160));
-  std::lock_guard<std::mutex> lock(g_init_mutex);
-  if (!known[dev & 63][kb]) {
-    cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = kSaBigCluster;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cfg.gridDim = dim3(kSaBigCluster * 64);
-    cfg.blockDim = dim3(kSaThreads);
-    cfg.dynamicSmemBytes = static_cast<size_t>(kb) * 1024;
-    int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, select_attend_kernel<__half, 2>, &cfg) != cudaSuccess) {
-      cudaGetLastError();   // not an error of the caller: big clusters are simply not used
-      n = 0;
-    }
-    cap[dev & 63][kb] = n;
-    known[dev & 63][kb] = true;
-  }
-  *out = cap[dev & 63][kb];
-  return ADAMAS_OK;
-}
-
-// Shape of a select_attend launch: blocks per head (= histogram slices), granules per thread, attention
-// tile, overflow list and dynamic shared memory (K and V tile | overflow list | rank 0's table of
-// partial results).  Planned for rows of up to n distances; shorter rows run in the same shape.
+// Shape of a select_attend launch: blocks per head (= histogram slices), granules per thread, winner
+// list and dynamic shared memory (the tile | winner list).  Planned for rows of up to n distances; shorter rows run in the same shape.
 struct SaPlan {
-  int cl, items, tile_cap, list_capacity;
+  int cl, items, list_capacity;
   size_t smem;
 };
 
 void sa_shape(int n, int k, int cl, SaPlan* pl) {
   const int slice_tokens = std::min(n, sa_granules_per_block(n, cl) * 8);
   const int max_loc = std::min(k, slice_tokens) + 1;   // winners of one block at most, plus the newest token
-  // Attention tile: the winners spread over the cl slices about evenly (binomially for unordered
-  // data); a tile with room for the mean plus four standard deviations makes a second, serial
-  // pass rare.  Lists that exceed the tile are still handled, pass after pass.
-  const int unit = 64;
-  const int mean = (k + cl - 1) / cl + 1;
-  const int want = std::min(max_loc, mean + static_cast<int>(4.0 * std::sqrt(static_cast<double>(mean))) + 8);
-  pl->tile_cap = want <= unit ? unit : (want <= 2 * unit ? 2 * unit : 3 * unit);
-  pl->list_capacity = std::max(0, max_loc - pl->tile_cap);
-  pl->smem = static_cast<size_t>(2) * pl->tile_cap * 256 +
-             ((static_cast<size_t>(pl->list_capacity) * 4 + 15) & ~static_cast<size_t>(15)) +
-             static_cast<size_t>(cl) * (kHeadDim + 2) * sizeof(float);
+  pl->list_capacity = max_loc;
+  pl->smem = static_cast<size_t>(kSaWarps) * 2 * kSaWarpRows * 256 +
+             ((static_cast<size_t>(pl->list_capacity) * 4 + 15) & ~static_cast<size_t>(15));
 }
 
 int sa_plan(int n, int k, int num_heads, const DeviceInfo* di, SaPlan* pl) {
@@ -1155,18 +1112,12 @@ int sa_plan(int n, int k, int num_heads, const DeviceInfo* di, SaPlan* pl) {
   }
   ADAMAS_REQUIRE(cl > 0, "select_attend supports at most %d distances per head at cluster size %d (got %d)",
                  cl_limit * 8 * kSaThreads * 8, cl_limit, n);
-  if (cl == kSaMaxCluster && items >= 2 && cl_limit == kSaMaxCluster) {
+  if (cl == kSaMaxCluster && items >= 2 && cl_limit == kSaMaxCluster && kSaBigCluster * num_heads <= 2 * di->num_sms) {
     // A long row (16 or more distances per thread) of few heads (a head-sharded model): most SMs would
     // idle while 8 blocks per head walk their slices.  Sixteen blocks per head halve the slices, as
-    // long as all clusters are resident at once.
-    SaPlan big_shape;
-    sa_shape(n, k, kSaBigCluster, &big_shape);
-    int big = 0;
-    if (int rc = big_cluster_capacity(big_shape.smem, &big)) return rc;
-    if (num_heads <= big) {
-      cl = kSaBigCluster;
-      items /= 2;
-    }
+    // long as all blocks are resident at once.
+    cl = kSaBigCluster;
+    items /= 2;
   }
   // a large budget on a short row: more blocks per head than the scan needs, so that each block
   // attends to about one tile of winners, as long as all blocks stay resident at once
@@ -1206,13 +1157,13 @@ int select_attend_impl(const void* dist, int64_t dist_stride, int n, int k, cons
   prm.out_idx = out_idx;
   prm.out_stride = out_stride;
   prm.list_capacity = pl.list_capacity;
-  prm.tile_cap = pl.tile_cap;
   prm.scale_log2 = sm_scale * 1.4426950408889634f;
   if (dtype == ADAMAS_F16)
     return launch_select_attend<__half>(prm, pl.items, pl.cl, num_heads, pl.smem, to_stream(stream));
   return launch_select_attend<__nv_bfloat16>(prm, pl.items, pl.cl, num_heads, pl.smem, to_stream(stream));
 }
 
+static_assert(ADAMAS_HIST_WORDS_PER_HEAD == kSaScratchWordsPerHead, "scratch layout of select_attend");
 size_t hist_bytes(int num_heads) {
   return static_cast<size_t>(num_heads) * ADAMAS_HIST_WORDS_PER_HEAD * sizeof(uint32_t);
 }

@@ -103,6 +103,20 @@ struct Elem<__half> {
     return *reinterpret_cast<uint32_t*>(&h);
   }
   static __device__ __forceinline__ float round(float a) { return __half2float(__float2half_rn(a)); }
+  // c + a.lo * b.lo + a.hi * b.hi on two packed pairs, in that order, each step one fused multiply-add
+  // in fp32 on the 16-bit operands (mixed-precision fma of sm_100: the same result as converting
+  // first, without the conversions)
+  static __device__ __forceinline__ float dot2(uint32_t a, uint32_t b, float c) {
+    float d;
+    asm("{\n\t.reg .b16 alo, ahi, blo, bhi;\n\t"
+        "mov.b32 {alo, ahi}, %1;\n\t"
+        "mov.b32 {blo, bhi}, %2;\n\t"
+        "fma.rn.f32.f16 %0, alo, blo, %3;\n\t"
+        "fma.rn.f32.f16 %0, ahi, bhi, %0;\n\t}"
+        : "=f"(d)
+        : "r"(a), "r"(b), "f"(c));
+    return d;
+  }
 };
 template <>
 struct Elem<__nv_bfloat16> {
@@ -116,6 +130,17 @@ struct Elem<__nv_bfloat16> {
   }
   static __device__ __forceinline__ float round(float a) {
     return __bfloat162float(__float2bfloat16_rn(a));
+  }
+  static __device__ __forceinline__ float dot2(uint32_t a, uint32_t b, float c) {
+    float d;
+    asm("{\n\t.reg .b16 alo, ahi, blo, bhi;\n\t"
+        "mov.b32 {alo, ahi}, %1;\n\t"
+        "mov.b32 {blo, bhi}, %2;\n\t"
+        "fma.rn.f32.bf16 %0, alo, blo, %3;\n\t"
+        "fma.rn.f32.bf16 %0, ahi, bhi, %0;\n\t}"
+        : "=f"(d)
+        : "r"(a), "r"(b), "f"(c));
+    return d;
   }
 };
 

@@ -24,7 +24,9 @@ namespace adamas {
 
 constexpr int kEstTile = 32;      // tokens per tile
 constexpr int kEstConsumerWarps = 16;
-constexpr int kEstThreads = (kEstConsumerWarps + 1) * 32;   // 16 consumer warps + 1 producer warp
+constexpr int kEstProducerWarps = 2;   // token-copy kernels: see est_produce
+constexpr int kEstThreads = (kEstConsumerWarps + kEstProducerWarps) * 32;
+constexpr int kEstPagesThreads = (kEstConsumerWarps + 1) * 32;   // page-copy kernel: 16 consumer warps + 1 producer warp
 constexpr int kEstStages = 3;     // ring depth (tiles in flight per block: kEstStages - 1)
 
 struct QPlanes {
@@ -101,8 +103,8 @@ struct EstimateParams {
   // the grid).  Read before the kernel's dependency resolves: the value must be final before the
   // kernel that precedes this one in the stream starts.
   const int32_t* seq_len_dev;
-  // optional: per-slice histograms of the distance rows for select_attend, table [H][kSaMaxSlices][512]
-  // u32, zero on entry; slice = token / (8 * sa_granules_per_block(n_tokens, hist_cl))
+  // optional: per-slice histograms of the distance rows for select_attend, in the histogram rows of its
+  // scratch table ([H][kSaScratchWordsPerHead] u32, rows zero on entry); slice = token / (8 * sa_granules_per_block(n_tokens, hist_cl))
   uint32_t* hist;
   int hist_cl;
 };
@@ -126,7 +128,7 @@ __device__ __forceinline__ EstGeom est_geom(const EstimateParams& p, int tile_sp
 }
 
 __device__ __forceinline__ void hist_count(uint32_t* hist, int head, int slice, unsigned d) {
-  uint32_t* a = hist + ((static_cast<size_t>(head) * kSaMaxSlices + slice) << 9) + d;
+  uint32_t* a = hist + static_cast<size_t>(head) * kSaScratchWordsPerHead + (slice << 9) + d;
   asm volatile("red.global.add.u32 [%0], 1;" ::"l"(a) : "memory");
 }
 
@@ -147,35 +149,59 @@ __device__ __forceinline__ int est_tiles_of_block(int num_tiles) {
                     static_cast<int>(gridDim.x));
 }
 
-// Producer warp: one bulk copy per token (its H codes) into the padded ring slot.  GROUPED: a tile
-// holds p.groups groups of 32 tokens and a lane issues one copy per group.
+// Producer warps: one bulk copy per token (its H codes) into the padded ring slot.  GROUPED: a tile
+// holds p.groups groups of 32 tokens.
+// A bulk copy with a different address in every lane is issued lane after lane, about 45 ns each
+// (measured: the 32 copies of a tile kept a single producer warp busy for 1.4 us, so that it needed
+// over 4 us to ask for the first three tiles and the ring was never ahead of the consumers; the SM's
+// copy unit itself takes a request every 2 ns).  So the copies of a tile are split over
+// kEstProducerWarps warps: producer `pw` issues the tokens tl with (tl / 16) % kEstProducerWarps == pw,
+// 16 lanes at a time.  Producer 0 also announces the tile's bytes on the "full" barrier; a copy of
+// another producer that lands before that announcement only makes the barrier's byte count negative
+// for a moment, which it allows.
+__device__ __forceinline__ void est_token_slot(const EstimateParams& p, int t, int* lp, int* e) {
+  if (p.ps_shift >= 0) {
+    *lp = t >> p.ps_shift;
+    *e = t & (p.page_size - 1);
+  } else {
+    *lp = t / p.page_size;
+    *e = t - *lp * p.page_size;
+  }
+}
+
 template <bool GROUPED>
 __device__ __forceinline__ void est_produce(const EstimateParams& p, const EstGeom& g, const EstRing& r, int my_tiles,
-                                            int lane) {
+                                            int lane, int pw) {
   const unsigned token_bytes = static_cast<unsigned>(r.cpt) * 16u;
   const int tile_span = GROUPED ? kEstTile * p.groups : kEstTile;
+  // this lane's tokens of a tile: tl = first_tl, first_tl + 16 * kEstProducerWarps * 2, ... (lanes 0-15 and
+  // 16-31 of a producer take alternate 16-token runs of its share)
+  const int first_tl = ((lane >> 4) * kEstProducerWarps + pw) * 16 + (lane & 15);
   int slot = 0;
   unsigned parity = 0;   // parity of the previous use of the slot, for the empty barrier
   for (int j = 0; j < my_tiles; ++j) {
     const int tile0 = (blockIdx.x + j * gridDim.x) * tile_span;
     const int tile_tokens = min(tile_span, g.n_tokens - tile0);
+    // the physical page of the first token does not depend on the slot: fetch it before waiting
+    int64_t tok_first = 0;
+    if (first_tl < tile_tokens) {
+      int lp, e;
+      est_token_slot(p, tile0 + first_tl, &lp, &e);
+      tok_first = static_cast<int64_t>(__ldg(p.page_table + lp)) * p.page_size + e;
+    }
     if (j >= kEstStages) {
       // every consumer warp has finished reading the tile that used this slot before
       if (!mbar_wait_bounded(&r.empty_bar[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
     }
-    if (lane == 0) mbar_arrive_expect_tx(&r.full_bar[slot], static_cast<unsigned>(tile_tokens) * token_bytes);
+    if (pw == 0 && lane == 0) mbar_arrive_expect_tx(&r.full_bar[slot], static_cast<unsigned>(tile_tokens) * token_bytes);
     __syncwarp();
-    for (int tl = lane; tl < (GROUPED ? tile_tokens : min(tile_tokens, kEstTile)); tl += 32) {
-      const int t = tile0 + tl;
-      int lp, e;
-      if (p.ps_shift >= 0) {
-        lp = t >> p.ps_shift;
-        e = t & (p.page_size - 1);
-      } else {
-        lp = t / p.page_size;
-        e = t - lp * p.page_size;
+    for (int tl = first_tl; tl < tile_tokens; tl += 32 * kEstProducerWarps) {
+      int64_t tok = tok_first;
+      if (tl != first_tl) {
+        int lp, e;
+        est_token_slot(p, tile0 + tl, &lp, &e);
+        tok = static_cast<int64_t>(__ldg(p.page_table + lp)) * p.page_size + e;
       }
-      const int64_t tok = static_cast<int64_t>(__ldg(p.page_table + lp)) * p.page_size + e;
       bulk_copy_g2s(r.base + slot * r.stage_chunks + tl * r.row_chunks, p.codes + tok * r.cpt, token_bytes,
                     &r.full_bar[slot]);
     }
@@ -302,13 +328,13 @@ __global__ void __launch_bounds__(kEstThreads) estimate_kernel(const EstimatePar
   __syncthreads();
   const EstGeom geom = est_geom(p, HPW == 0 ? kEstTile * p.groups : kEstTile);
   const int my_tiles = est_tiles_of_block(geom.num_tiles);
-  if (warp == kEstConsumerWarps) {
-    est_produce<HPW == 0>(p, geom, ring, my_tiles, lane);
+  if (warp >= kEstConsumerWarps) {
+    est_produce<HPW == 0>(p, geom, ring, my_tiles, lane, warp - kEstConsumerWarps);
     grid_launch_dependents();
     return;
   }
-  // The cached codes the producer streams were final before the preceding kernel started; the query
-  // code is that kernel's output, so the consumers wait for it here (the producer does not).
+  // The cached codes the producers stream were final before the preceding kernel started; the query
+  // code is that kernel's output, so the consumers wait for it here (the producers do not).
   grid_dependency_wait();
   grid_launch_dependents();
   QPlanes qp[HPW > 0 ? HPW : 1][2];
@@ -357,9 +383,9 @@ __global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const Esti
   __syncthreads();
   const EstGeom geom = est_geom(p, kEstTile);
   const int my_tiles = est_tiles_of_block(geom.num_tiles);
-  if (warp == kEstConsumerWarps) {
+  if (warp >= kEstConsumerWarps) {
     // the cached codes were final before the preceding kernel started: stream them right away
-    est_produce<false>(p, geom, ring, my_tiles, lane);
+    est_produce<false>(p, geom, ring, my_tiles, lane, warp - kEstConsumerWarps);
     grid_launch_dependents();
     return;
   }
@@ -439,6 +465,8 @@ __global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const Esti
 // step (conflict-free), lane l always holds half (l & 1) of head (l % 2H) / 2, so its query planes stay
 // in registers; the two halves of a (token, head) are joined by one shuffle.  Needs 2H | 32.  Partial
 // last units read a few chunks past the valid ones (the allocation has 512 spare bytes).
+constexpr int kEstLookahead = 8;   // tiles whose page numbers the page-copy producer fetches together
+
 struct EstimatePagesParams {
   const uint4* codes;
   const int32_t* page_table;
@@ -457,7 +485,7 @@ struct EstimatePagesParams {
 };
 
 template <int METRIC, typename OutT>
-__global__ void __launch_bounds__(kEstThreads, 2) estimate_pages_kernel(const EstimatePagesParams p) {
+__global__ void __launch_bounds__(kEstPagesThreads, 2) estimate_pages_kernel(const EstimatePagesParams p) {
   extern __shared__ uint4 est_smem[];
   __shared__ __align__(8) uint64_t full_bar[kEstStages];
   __shared__ __align__(8) uint64_t empty_bar[kEstStages];
@@ -487,28 +515,43 @@ __global__ void __launch_bounds__(kEstThreads, 2) estimate_pages_kernel(const Es
   const int my_tiles = est_tiles_of_block(num_tiles);
 
   if (warp == kEstConsumerWarps) {
-    // ---- producer: one bulk copy per page of the tile (the last page of the row may be partial)
+    // ---- producer: one bulk copy per page of the tile (the last page of the row may be partial); the
+    // page numbers of the next kEstLookahead tiles are fetched together, ahead of the copies
     int slot = 0;
     unsigned parity = 0;
-    for (int j = 0; j < my_tiles; ++j) {
-      const int tile = blockIdx.x + j * gridDim.x;
-      const int tok0 = tile * tile_span;
-      const int ntok = min(tile_span, n_tokens - tok0);
-      if (j >= kEstStages) {
-        if (!mbar_wait_bounded(&empty_bar[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
+    for (int j0 = 0; j0 < my_tiles; j0 += kEstLookahead) {
+      int page[kEstLookahead];
+#pragma unroll
+      for (int u = 0; u < kEstLookahead; ++u) {
+        const int tile = blockIdx.x + (j0 + u) * gridDim.x;
+        const int tok0 = tile * tile_span;
+        page[u] = 0;
+        if (j0 + u < my_tiles && tok0 + lane * p.page_size < n_tokens)
+          page[u] = __ldg(p.page_table + tile * p.pages_per_tile + lane);
       }
-      if (lane == 0) mbar_arrive_expect_tx(&full_bar[slot], static_cast<unsigned>(ntok) * H2 * 16u);
-      __syncwarp();
-      const int npages = (ntok + p.page_size - 1) / p.page_size;
-      for (int pg = lane; pg < npages; pg += 32) {
-        const int64_t phys = __ldg(p.page_table + tile * p.pages_per_tile + pg);
-        const int toks = min(p.page_size, ntok - pg * p.page_size);
-        bulk_copy_g2s(est_smem + slot * tile_chunks + pg * page_chunks, p.codes + phys * page_chunks,
-                      static_cast<unsigned>(toks) * H2 * 16u, &full_bar[slot]);
-      }
-      if (++slot == kEstStages) {
-        slot = 0;
-        if (j >= kEstStages) parity ^= 1u;
+#pragma unroll
+      for (int u = 0; u < kEstLookahead; ++u) {
+        const int j = j0 + u;
+        if (j >= my_tiles) break;
+        const int tile = blockIdx.x + j * gridDim.x;
+        const int tok0 = tile * tile_span;
+        const int ntok = min(tile_span, n_tokens - tok0);
+        if (j >= kEstStages) {
+          if (!mbar_wait_bounded(&empty_bar[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
+        }
+        if (lane == 0) mbar_arrive_expect_tx(&full_bar[slot], static_cast<unsigned>(ntok) * H2 * 16u);
+        __syncwarp();
+        const int npages = (ntok + p.page_size - 1) / p.page_size;   // at most 32: one per lane
+        if (lane < npages) {
+          const int64_t phys = page[u];
+          const int toks = min(p.page_size, ntok - lane * p.page_size);
+          bulk_copy_g2s(est_smem + slot * tile_chunks + lane * page_chunks, p.codes + phys * page_chunks,
+                        static_cast<unsigned>(toks) * H2 * 16u, &full_bar[slot]);
+        }
+        if (++slot == kEstStages) {
+          slot = 0;
+          if (j >= kEstStages) parity ^= 1u;
+        }
       }
     }
     grid_launch_dependents();

@@ -8,28 +8,27 @@
 // in a global table [H][kSaMaxSlices][512] u32: slice r covers the granules (8 distances) that block
 // r of the head's cluster owns.  A distance is at most 3 * 128 = 384; larger values count as 511.
 //
-// One thread-block cluster (CL <= 16 blocks x 512 threads) per head.  Block `cr`:
+// CL <= 16 blocks x 512 threads per head (grid (CL, H)); the blocks of a head never wait for one another.
+// Block `cr`:
 //   load   its slice of the distance row (registers), the head's CL histograms (one bin per thread)
 //          and the query chunks, all in flight together;
 //   cut    block-wide scan of the summed histogram: the cut distance, how many cut-valued elements
 //          are taken in all, how many of them and how many smaller elements lie in lower-ranked
 //          slices (= this slice's tie quota and its offset in the output list).  Every block
-//          derives this by itself from the same table: no cluster barrier;
-//   pick   ordered compaction: a thread that holds a winner computes its row in the tile and issues
-//          the two 256-byte bulk (TMA) copies of its K and V row right away; winner number `pos`
-//          goes to warp pos / tpw, which owns tpw = tile_cap / 16 consecutive rows and one mbarrier;
-//   attend every warp waits for its own rows only (bounded wait), computes q.K with four lanes per
-//          token, a softmax in base 2 over its tokens and P.V with four dimensions per lane: no
-//          block barrier inside the attention.  Winners beyond the tile (rare: the host sizes the
-//          tile for the mean plus four standard deviations) go through a list in shared memory and
-//          further passes;
-//   merge  the 16 warps' partial (o, m, l) are merged in shared memory, the block's partial is
-//          stored into slot `cr` of rank 0's shared memory; one cluster barrier; rank 0 merges the
-//          CL partials and writes the head's output; every block clears its own histogram row, so
-//          that the table is all zero again when the kernel ends.
+//          derives this by itself from the same table: no exchange between blocks;
+//   pick   ordered compaction of the block's winners into a list in shared memory;
+//   attend the rows of the list are dealt out evenly to the 16 warps; a warp gathers the K and V rows of
+//          its tokens itself (one 256-byte bulk (TMA) copy per row into its own part of the tile,
+//          counted by its own mbarrier, bounded wait), computes q.K with four lanes per token, a
+//          softmax in base 2 over its tokens and P.V with four dimensions per lane: no block barrier
+//          inside the attention;
+//   merge  the 16 warps' partial (o, m, l) are merged in shared memory and the block's partial goes to
+//          the head's slot table in global scratch; the block that arrives LAST at the head's counter
+//          merges the CL partials, writes the head's output, clears the head's histogram rows and the
+//          counter.  Every other block is gone by then: its SM is free for the next kernel's blocks
+//          while the slowest block of the head still works (with a cluster barrier at this point all
+//          blocks of a head stayed resident until the slowest had finished, 2 us at 32K / 1024).
 #pragma once
-#include <cooperative_groups.h>
-
 #include "common.cuh"
 
 namespace adamas {
@@ -39,9 +38,14 @@ constexpr int kSaWarps = kSaThreads / 32;
 constexpr int kSaBins = 512;
 constexpr int kSaMaxSlices = 16;      // histogram rows per head = largest cluster
 constexpr int kSaTile = 128;          // planning unit of the host (winners per block it aims for)
-constexpr int kSaTileMax = 192;       // largest attention tile (rows of K and of V in shared memory)
-constexpr int kSaMaxCluster = 8;      // portable cluster size
-constexpr int kSaBigCluster = 16;     // non-portable: long rows of few heads (see the host code)
+constexpr int kSaWarpRows = 12;       // rows a warp gathers per round (its part of the tile: 12 K + 12 V rows)
+constexpr int kSaMaxCluster = 8;      // blocks per head by default
+constexpr int kSaBigCluster = 16;     // long rows of few heads (see the host code)
+// Scratch words (32 bit) per head: kSaMaxSlices histogram rows of 512 counts, then kSaMaxSlices slots of
+// kSaSlotWords floats for the blocks' partial results (128 outputs, running max, running sum; word 130
+// of slot 0 is the head's arrival counter).
+constexpr int kSaSlotWords = 132;
+constexpr int kSaScratchWordsPerHead = kSaMaxSlices * kSaBins + kSaMaxSlices * kSaSlotWords;
 
 // Granules (8 distances) of a row that each of `cl` blocks owns: a multiple of 4, so that a slice
 // starts on a multiple of 32 tokens and no 32-token tile of an estimate kernel straddles two slices.
@@ -53,7 +57,8 @@ __host__ __device__ __forceinline__ int sa_granules_per_block(int n, int cl) {
 struct SelectAttendParams {
   const uint16_t* dist;     // [H, dist_stride] u16 distances, rows 16-byte aligned
   int64_t dist_stride;
-  uint32_t* hist;           // [H][kSaMaxSlices][512]: per-slice histograms of the rows; cleared on exit
+  uint32_t* hist;           // [H][kSaScratchWordsPerHead]: per-slice histograms of the rows (cleared on exit),
+                            // then the slots of the blocks' partial results and the arrival counter
   const int2* ext_cut;      // optional [H]: (cut distance, cut-valued winners this call takes), decided
                             // elsewhere (sequence shards); k is then unused
   const int32_t* seq_len_dev;  // optional: n = *seq_len_dev - 1 and the newest token sits at position n
@@ -72,8 +77,7 @@ struct SelectAttendParams {
   unsigned tail_slot;       // physical slot of the newest token (tail_mode 1)
   int32_t* out_idx;         // optional [H, out_stride]: physical slots of the winners, ascending position
   int64_t out_stride;
-  int list_capacity;        // entries of the shared-memory overflow list (winners beyond the tile)
-  int tile_cap;             // rows per attention tile: 64, 128 or 192
+  int list_capacity;        // entries of the shared-memory winner list (a block's winners at most, plus the newest token)
   float scale_log2;
 };
 
@@ -82,45 +86,33 @@ struct SaShared {
   unsigned warp_a[kSaWarps];
   unsigned warp_b[kSaWarps];
   unsigned cut, need_eq, lt_before, eq_before;
-  unsigned long long bar[kSaWarps];
+  unsigned last;   // this block arrived last at the head's counter
+  uint4 q[16];     // the head's query row
+  unsigned long long bar[kSaWarps];   // one mbarrier per warp: the bytes of its own rows
 };
 
-// The two halves of a cluster barrier (all threads of all blocks of the cluster execute both).
-__device__ __forceinline__ void cluster_arrive_release() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void cluster_wait_acquire() {
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
-// Dynamic shared memory: K tile (tile_cap * 256 B) | V tile (same) | overflow list (list_capacity * 4 B,
-// rounded up to 16) | rank 0's table of the blocks' partial results (CL * 130 floats).
-// After its last pass a warp parks its partial output in its own K rows.
+// Dynamic shared memory: the tile (16 warps x (12 K rows + 12 V rows) x 256 B; a warp parks its partial
+// output in its own K rows at the end) | winner list (list_capacity * 4 B).
 template <typename T, int ITEMS>
 __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const SelectAttendParams p) {
   constexpr int NT = kSaThreads;
   static_assert(NT >= kSaBins, "one histogram bin per thread");
-  namespace cg = cooperative_groups;
-  cg::cluster_group cluster = cg::this_cluster();
   extern __shared__ __align__(16) uint8_t sa_smem[];
   __shared__ __align__(16) SaShared sh;
 
-  const unsigned CL = cluster.num_blocks();
-  const unsigned cr = cluster.block_rank();
-  const int head = blockIdx.x / CL;
+  const unsigned CL = gridDim.x;
+  const unsigned cr = blockIdx.x;
+  const int head = blockIdx.y;
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
   const int H = p.H;
-  const int cap = p.tile_cap;
-  const int tpw = cap / kSaWarps;     // rows per warp and pass: 4, 8 or 12
-  const unsigned tpw_rcp = 65536u / static_cast<unsigned>(tpw) + 1u;   // pos / tpw == (pos * tpw_rcp) >> 16 for pos < 192
 
-  uint8_t* sk = sa_smem;
-  uint8_t* sv = sa_smem + cap * 256;
-  int32_t* s_list = reinterpret_cast<int32_t*>(sa_smem + 2 * cap * 256);
-  float* part_o = reinterpret_cast<float*>(sa_smem + 2 * cap * 256 + ((p.list_capacity * 4 + 15) & ~15));  // [CL][128]
-  float* part_ml = part_o + CL * kHeadDim;                                                                  // [CL][2]
+  uint8_t* sa_tile = sa_smem;                                                         // [16 warps][K rows | V rows]
+  int32_t* s_list = reinterpret_cast<int32_t*>(sa_smem + kSaWarps * 2 * kSaWarpRows * 256);   // the block's winners, in position order
+  uint32_t* head_scratch = p.hist + static_cast<size_t>(head) * kSaScratchWordsPerHead;
+  float* slots = reinterpret_cast<float*>(head_scratch + kSaMaxSlices * kSaBins);     // [CL][kSaSlotWords]
+  uint4* s_q = sh.q;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sh.bar);
 
   // ---- set-up that needs no input (overlaps the tail of the preceding kernel) -----------------------
@@ -157,14 +149,12 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
     raw[i][0] = v.x; raw[i][1] = v.y; raw[i][2] = v.z; raw[i][3] = v.w;
     vmask[i] = m;
   }
-  unsigned tot = 0, low = 0;
+  // (all loads are issued before the first count is used: one trip to L2, not one per slice)
+  unsigned hcnt[kSaMaxSlices];
   {
-    const uint32_t* hrow = p.hist + (static_cast<size_t>(head) * kSaMaxSlices) * kSaBins + tid;
-    for (unsigned r = 0; r < CL; ++r) {
-      const unsigned c = __ldcg(hrow + r * kSaBins);
-      tot += c;
-      if (r < cr) low += c;
-    }
+    const uint32_t* hrow = head_scratch + tid;
+#pragma unroll
+    for (unsigned r = 0; r < kSaMaxSlices; ++r) hcnt[r] = r < CL ? __ldcg(hrow + r * kSaBins) : 0u;
   }
   // With pages of 8 tokens or more (a power of two) a granule lies inside one page: fetch its
   // physical page number now, long before the winners are known.
@@ -183,23 +173,13 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
     const unsigned pg = p.ps_shift >= 0 ? (un >> p.ps_shift) : (un / ps);
     tail_slot = static_cast<unsigned>(__ldg(p.kv_table + pg)) * ps + (un - pg * ps);
   }
-  // q.K mapping: four lanes per token (tq = lane / 4, quarter = lane % 4); step i of a lane reads chunk
-  // 4*quarter + ((i + quarter + tq) & 3).  A quarter-warp covers an even and an odd token; the rows are
-  // 256 bytes apart (the same banks), and with this order the two tokens' four chunks fall on
-  // complementary 16-byte bank groups, so the 8 lanes hit 8 different ones.  The query chunks stay
-  // packed in registers, in the lane's own order (a warp's first row is a multiple of 4).
-  const int tq = lane >> 2;
-  const int quarter = lane & 3;
-  // They are fetched once the copies of the winners' rows are on their way: the latency hides behind
-  // the gather, and the selection keeps its registers.
-  uint4 qpk[4];
-  auto load_query = [&]() {
-    const T* qp = static_cast<const T*>(p.q) + static_cast<int64_t>(head) * kHeadDim;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) qpk[i] = ld_16(qp + (4 * quarter + ((i + quarter + tq) & 3)) * 8);
-  };
-
   // ---- cut: one bin per thread ------------------------------------------------------------------------
+  unsigned tot = 0, low = 0;
+#pragma unroll
+  for (unsigned r = 0; r < kSaMaxSlices; ++r) {
+    tot += hcnt[r];
+    low += r < cr ? hcnt[r] : 0u;
+  }
   {
     unsigned it = tot, il = low;
 #pragma unroll
@@ -287,41 +267,12 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   unsigned run_lt = excl & 0xffffu, run_eq = excl >> 16;
   const unsigned blk_lt = blk_tot & 0xffffu, blk_eq = blk_tot >> 16;
   const int n_win = static_cast<int>(blk_lt + min(blk_eq, take_eq));
-  const int n_loc = min(n_win + (tail_here ? 1 : 0), cap + p.list_capacity);
+  const int n_loc = min(n_win + (tail_here ? 1 : 0), p.list_capacity);
 
   const T* kvp = static_cast<const T*>(p.kv);
   const unsigned ps = static_cast<unsigned>(p.page_size);
   const int64_t v_delta = static_cast<int64_t>(p.page_size) * H * kHeadDim;
-  // K row of a physical token slot
-  auto row_of = [&](unsigned slot) -> const T* {
-    unsigned page, e;
-    if (p.ps_shift >= 0) {
-      page = slot >> p.ps_shift;
-      e = slot & (ps - 1);
-    } else {
-      page = slot / ps;
-      e = slot - page * ps;
-    }
-    const int64_t row = static_cast<int64_t>(page) * (2 * ps) + e;
-    return kvp + (row * H + head) * kHeadDim;
-  };
-  // rows of pass `pass` (tile rows pass*cap ..) that warp `w` owns
-  auto rows_of_warp = [&](int pass, int w) -> int { return max(0, min(tpw, n_loc - pass * cap - w * tpw)); };
-  // winner number `pos` of the block lives at physical slot `slot`: copy its rows now (first tile) or
-  // remember it (later passes)
-  auto place = [&](int pos, unsigned slot) {
-    if (pos < cap) {
-      const T* src = row_of(slot);
-      uint64_t* bar = &bars[(static_cast<unsigned>(pos) * tpw_rcp) >> 16];
-      bulk_copy_g2s(sk + pos * 256, src, kHeadDim * 2, bar);
-      bulk_copy_g2s(sv + pos * 256, src + v_delta, kHeadDim * 2, bar);
-    } else if (pos - cap < p.list_capacity) {
-      s_list[pos - cap] = static_cast<int32_t>(slot);
-    }
-  };
-
-  // every warp announces the bytes of its rows of the first pass, then the copies are issued
-  if (lane == 0) mbar_arrive_expect_tx(&bars[warp], static_cast<unsigned>(rows_of_warp(0, warp)) * (2 * kHeadDim * 2));
+  // The winners go to a list in shared memory (a few instructions on a divergent path).
   int32_t* oi = p.out_idx ? p.out_idx + static_cast<int64_t>(head) * p.out_stride + out_base : nullptr;
   if (c_lt | c_eq) {
 #pragma unroll
@@ -354,49 +305,87 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
               }
               slot = static_cast<unsigned>(__ldg(p.kv_table + pg)) * ps + e;
             }
-            place(pos, slot);
+            if (pos < p.list_capacity) s_list[pos] = static_cast<int32_t>(slot);
             if (oi) oi[pos] = static_cast<int32_t>(slot);
           }
         }
       }
     }
   }
-  if (tail_here && tid == 0) place(n_win, tail_slot);
-  load_query();
+  if (tail_here && tid == 0 && n_win < p.list_capacity) s_list[n_win] = static_cast<int32_t>(tail_slot);
+  if (tid < 16) s_q[tid] = ld_16(static_cast<const T*>(p.q) + static_cast<int64_t>(head) * kHeadDim + tid * 8);
 
   // ---- attend: every warp over its own rows --------------------------------------------------------------
+  // The rows are dealt out evenly: warp w owns rows w*rpw .. of the list.  It gathers them itself, kSaWarpRows
+  // at a time: lanes 0-15 issue the 256-byte bulk (TMA) copies of its K rows, lanes 16-31 those of its V
+  // rows, into the warp's own part of the tile, counted by the warp's own mbarrier (bounded wait); then
+  // q.K with four lanes per token, a softmax in base 2 over its tokens and P.V with four dimensions per
+  // lane.  Nothing in here is shared between warps: no block barrier inside the attention.
+  // A bulk copy with a different address in every lane is issued lane after lane (about 45 ns each), so
+  // what matters is that all 16 warps issue at once and no warp more than a couple of dozen copies.
+  // Measured alternatives: all copies issued by the first n_loc / 16 warps (1.9 us instead of 0.7);
+  // plain vector loads into registers instead of the tile (all rows cannot be in flight at once in 64
+  // registers: the second round of a warp pays the memory latency again, 4.5 us in this phase).
+  __syncthreads();   // the list and the query are complete
   float m_run = -INFINITY, l_run = 0.f;   // l_run is kept by the lanes with quarter == 0
   float o_acc[4] = {0.f, 0.f, 0.f, 0.f};  // dimensions 4*lane .. 4*lane+3
-  const int n_pass = (n_loc + cap - 1) / cap;
-  for (int pass = 0; pass < n_pass; ++pass) {
-    if (pass > 0) {
-      // the tile is refilled from the list: all warps have finished with the rows of the pass before
-      __syncthreads();
-      if (lane == 0)
-        mbar_arrive_expect_tx(&bars[warp], static_cast<unsigned>(rows_of_warp(pass, warp)) * (2 * kHeadDim * 2));
-      const int tl = tid >> 1;
-      const int is_v = tid & 1;
-      for (int r = tl; r < min(cap, n_loc - pass * cap); r += NT / 2) {
-        const T* src = row_of(static_cast<unsigned>(s_list[(pass - 1) * cap + r]));
-        bulk_copy_g2s((is_v ? sv : sk) + r * 256, src + (is_v ? v_delta : 0), kHeadDim * 2, &bars[(static_cast<unsigned>(r) * tpw_rcp) >> 16]);
+  const int rpw = (n_loc + kSaWarps - 1) / kSaWarps;
+  const int my_first = warp * rpw;
+  const int my_total = max(0, min(rpw, n_loc - my_first));
+  uint8_t* wk = sa_tile + warp * (2 * kSaWarpRows * 256);   // this warp's K rows, then its V rows
+  uint8_t* wv = wk + kSaWarpRows * 256;
+  uint64_t* bar = &bars[warp];
+  // q.K mapping: four lanes per token (tq = lane / 4, quarter = lane % 4); step i of a lane reads chunk
+  // 4*quarter + ((i + quarter + tq) & 3).  A quarter-warp covers an even and an odd token; the rows are
+  // 256 bytes apart (the same banks), and with this order the two tokens' four chunks fall on
+  // complementary 16-byte bank groups, so the 8 lanes hit 8 different ones.
+  const int tq = lane >> 2;
+  const int quarter = lane & 3;
+  uint4 qpk[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) qpk[i] = s_q[4 * quarter + ((i + quarter + tq) & 3)];
+  unsigned phase = 0;
+  for (int done = 0; done < my_total; done += kSaWarpRows) {
+    const int my_rows = min(kSaWarpRows, my_total - done);
+    if (done > 0) {
+      // the rows of the round before have been read (generic proxy); the copies write through the async proxy
+      __syncwarp();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<unsigned>(my_rows) * (2 * kHeadDim * 2));
+    __syncwarp();
+    {
+      const int r = lane & 15;
+      const int is_v = lane >> 4;
+      if (r < my_rows) {
+        const unsigned slot = static_cast<unsigned>(s_list[my_first + done + r]);
+        unsigned page, e;
+        if (p.ps_shift >= 0) {
+          page = slot >> p.ps_shift;
+          e = slot & (ps - 1);
+        } else {
+          page = slot / ps;
+          e = slot - page * ps;
+        }
+        const T* src = kvp + (static_cast<int64_t>(page * (2 * ps) + e) * H + head) * kHeadDim + (is_v ? v_delta : 0);
+        bulk_copy_g2s((is_v ? wv : wk) + r * 256, src, kHeadDim * 2, bar);
       }
     }
-    const int my_rows = rows_of_warp(pass, warp);
-    if (!mbar_wait_bounded(&bars[warp], static_cast<unsigned>(pass & 1), 1u << 22)) atomicOr(&g_adamas_error, kErrGatherTimeout);
+    if (!mbar_wait_bounded(bar, phase, 1u << 22)) atomicOr(&g_adamas_error, kErrGatherTimeout);
+    phase ^= 1u;
     for (int base = 0; base < my_rows; base += 8) {
-      const int r_in_warp = base + tq;
-      const bool live = r_in_warp < my_rows;
-      const int row = warp * tpw + r_in_warp;
+      const int row = base + tq;
+      const bool live = row < my_rows;
       float acc = 0.f;
       if (live) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int lc = 4 * quarter + ((i + quarter + tq) & 3);
-          float kf[8], qf[8];
-          unpack8<T>(*reinterpret_cast<const uint4*>(sk + row * 256 + lc * 16), kf);
-          unpack8<T>(qpk[i], qf);
-#pragma unroll
-          for (int d = 0; d < 8; ++d) acc = fmaf(qf[d], kf[d], acc);
+          const uint4 kk = *reinterpret_cast<const uint4*>(wk + row * 256 + lc * 16);
+          acc = Elem<T>::dot2(qpk[i].x, kk.x, acc);
+          acc = Elem<T>::dot2(qpk[i].y, kk.y, acc);
+          acc = Elem<T>::dot2(qpk[i].z, kk.z, acc);
+          acc = Elem<T>::dot2(qpk[i].w, kk.w, acc);
         }
       }
       acc += __shfl_xor_sync(0xffffffffu, acc, 1);
@@ -419,7 +408,7 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
       for (int j = 0; j < 8; ++j) {
         const float pj = __shfl_sync(0xffffffffu, pr, 4 * j);
         if (pj != 0.f) {   // warp-uniform; rows past the end are stale
-          const uint2 vv = *reinterpret_cast<const uint2*>(sv + (warp * tpw + base + j) * 256 + lane * 8);
+          const uint2 vv = *reinterpret_cast<const uint2*>(wv + (base + j) * 256 + lane * 8);
           const float2 a = Elem<T>::to_f2(vv.x), b = Elem<T>::to_f2(vv.y);
           o_acc[0] = fmaf(pj, a.x, o_acc[0]);
           o_acc[1] = fmaf(pj, a.y, o_acc[1]);
@@ -430,10 +419,10 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
     }
   }
 
-  // ---- merge: warps -> block -> rank 0 ---------------------------------------------------------------------
-  // a warp parks its partial output in its own K rows (tpw * 256 >= 512 bytes), which nobody else reads
+  // ---- merge: warps -> block -> head ----------------------------------------------------------------------
+  // a warp parks its partial output in its own K rows, which nobody else touches
   __syncwarp();
-  reinterpret_cast<float4*>(sk + warp * tpw * 256)[lane] = make_float4(o_acc[0], o_acc[1], o_acc[2], o_acc[3]);
+  reinterpret_cast<float4*>(wk)[lane] = make_float4(o_acc[0], o_acc[1], o_acc[2], o_acc[3]);
   if (lane == 0) {
     sh.ml[warp][0] = m_run;
     sh.ml[warp][1] = l_run;
@@ -449,28 +438,51 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
       const float m = sh.ml[w2][0];
       const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
       L += w * sh.ml[w2][1];
-      if (w != 0.f) od += w * reinterpret_cast<const float*>(sk + w2 * tpw * 256)[tid];
+      if (w != 0.f) od += w * reinterpret_cast<const float*>(sa_tile + w2 * (2 * kSaWarpRows * 256))[tid];
     }
-    *cluster.map_shared_rank(part_o + cr * kHeadDim + tid, 0) = od;
+    float* slot = slots + cr * kSaSlotWords;
+    __stcg(slot + tid, od);
     if (tid == 0) {
-      float* ml = cluster.map_shared_rank(part_ml + cr * 2, 0);
-      ml[0] = M;
-      ml[1] = L;
+      __stcg(slot + kHeadDim, M);
+      __stcg(slot + kHeadDim + 1, L);
     }
   }
-  cluster_arrive_release();
-  cluster_wait_acquire();
-  // every peer has read the head's histograms long ago: clear this block's row for the next launch
-  p.hist[(static_cast<size_t>(head) * kSaMaxSlices + cr) * kSaBins + tid] = 0u;
-  if (cr != 0 || tid >= kHeadDim) return;
+  // the block that arrives last at the head's counter merges; nobody waits
+  unsigned* counter = head_scratch + kSaMaxSlices * kSaBins + kHeadDim + 2;   // word 130 of slot 0
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) sh.last = (atomicAdd(counter, 1u) == CL - 1) ? 1u : 0u;
+  __syncthreads();
+  if (!sh.last) return;
+  __threadfence();
+  // every block of the head has read the histograms long ago: clear them and the counter for the next launch
+#pragma unroll
+  for (unsigned r = 0; r < kSaMaxSlices; ++r)
+    if (r < CL) head_scratch[r * kSaBins + tid] = 0u;
+  if (tid == 0) *counter = 0u;
+  if (tid >= kHeadDim) return;
+  // all loads of the CL partials are issued before the first is used: one trip to L2
+  float pm[kSaMaxSlices], pl[kSaMaxSlices], po[kSaMaxSlices];
+#pragma unroll
+  for (unsigned r = 0; r < kSaMaxSlices; ++r) {
+    pm[r] = -INFINITY;
+    pl[r] = 0.f;
+    po[r] = 0.f;
+    if (r < CL) {
+      pm[r] = __ldcg(slots + r * kSaSlotWords + kHeadDim);
+      pl[r] = __ldcg(slots + r * kSaSlotWords + kHeadDim + 1);
+      po[r] = __ldcg(slots + r * kSaSlotWords + tid);
+    }
+  }
   float M = -INFINITY;
-  for (unsigned r = 0; r < CL; ++r) M = fmaxf(M, part_ml[r * 2]);
+#pragma unroll
+  for (unsigned r = 0; r < kSaMaxSlices; ++r) M = fmaxf(M, pm[r]);
   float accd = 0.f, L = 0.f;
-  for (unsigned r = 0; r < CL; ++r) {
-    const float m = part_ml[r * 2];
-    const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
-    L += w * part_ml[r * 2 + 1];
-    if (w != 0.f) accd += w * part_o[r * kHeadDim + tid];
+#pragma unroll
+  for (unsigned r = 0; r < kSaMaxSlices; ++r) {
+    const float w = (pm[r] == -INFINITY) ? 0.f : exp2f(pm[r] - M);
+    L += w * pl[r];
+    if (w != 0.f) accd += w * po[r];
   }
   const float res = L > 0.f ? accd / L : 0.f;
   const float res1 = __shfl_down_sync(0xffffffffu, res, 1);
@@ -515,7 +527,7 @@ __global__ void __launch_bounds__(kSaThreads) dist_histogram_kernel(const DistHi
     }
   }
   __syncthreads();
-  p.hist[(static_cast<size_t>(head) * kSaMaxSlices + r) * kSaBins + tid] = h_local[tid];
+  p.hist[static_cast<size_t>(head) * kSaScratchWordsPerHead + r * kSaBins + tid] = h_local[tid];
 }
 
 }  // namespace adamas

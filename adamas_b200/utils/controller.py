@@ -172,9 +172,11 @@ class InferenceController:
     # ---- state of the fused / graph-replayable decode step ------------------------------------
     @property
     def hist_scratch(self) -> torch.Tensor:
-        """Histogram table of the fused decode step ([H, 16, 512] int32; zero between steps)."""
+        """Scratch table of the fused decode step (_kernels.histogram_scratch; its histograms are zero
+        between steps)."""
         if self._hist is None:
-            self._hist = torch.zeros(self.num_heads, 16, 512, dtype=torch.int32, device=self.device)
+            from .. import _kernels
+            self._hist = _kernels.histogram_scratch(self.num_heads, self.device)
         return self._hist
 
     @property

@@ -9,9 +9,15 @@ and code cache, so one step streams ~1.6 GB of distinct data (inputs far larger 
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
+Every timed step ADVANCES the sequence: step i appends at position ctx - 1 + i.  The step is one CUDA
+graph (the kernels take the sequence length from device memory, see utils.decode_step_dev) that is
+replayed; per step the host only reserves cache room, which uploads one page number every page_size
+tokens.  The K timed steps are repeated in several blocks and the median block is reported.
+
 N > 1 is launched by torch.distributed.run; each rank owns the same number of KV heads of a model
 N times as wide (head sharding, no collective inside the path; the per-step gather of the layer
-outputs is included in the timed region).  Rank 0 prints one JSON line.
+outputs is part of the step graph).  The line then also carries a "strong" record: the 32-head model
+split N ways.  Rank 0 prints one JSON line.
 """
 from __future__ import annotations
 
@@ -172,15 +178,19 @@ def launches_per_layer(args) -> int:
 def workload_config(args, extra=None):
     cfg = {
         "workload": (f"llama2-7b-shaped attention stack: {args.layers} layers x {args.heads} heads x 128, "
-                     f"ctx {args.ctx}, token budget {args.budget}, page size {args.page_size}, batch 1; "
-                     "per layer: fused append + estimate + top-k + sparse paged attention "
+                     f"ctx {args.ctx} growing by one token per step, token budget {args.budget}, page size "
+                     f"{args.page_size}, batch 1; per layer: fused append + estimate + top-k + sparse paged attention "
                      + ("(4 launches)" if args.unfused else
                         ("(decode_step: 2 launches, append inside the estimate kernel, top-k and attention in one kernel)"
                          if two_launch_step(args) else "(decode_step: 3 launches, top-k and attention in one kernel)"))),
         "layers": args.layers, "heads_per_gpu": args.heads, "ctx": args.ctx, "budget": args.budget,
         "page_size": args.page_size, "parallelism": f"head-sharded x{args.gpus}" if args.gpus > 1 else "single GPU",
         "l2": "inputs larger than L2 (each layer has its own caches; ~1.6 GB touched per step)",
-        "launch": "CUDA graph of the step" if not args.eager else "eager",
+        "launch": ("eager" if args.eager else
+                   ("CUDA graph of the four operators at a fixed position" if args.unfused else
+                    "one CUDA graph of the step, replayed; every step appends at the next position "
+                    "(sequence length in device memory)")),
+        "timing": "median of several blocks of `steps` steps, CUDA events, max over ranks",
     }
     if extra:
         cfg.update(extra)
@@ -191,14 +201,21 @@ def workload_config(args, extra=None):
 # GPU arm
 # --------------------------------------------------------------------------------------------
 class Workload:
-    def __init__(self, args, dev, seed_offset=0):
+    """One sequence of `ctx` tokens in every layer's caches, ready to decode `room` more tokens."""
+
+    def __init__(self, args, dev, seed_offset=0, room=0, heads=None, ctx=None, budget=None, layers=None, dtype=None):
         import adamas_b200.utils as U
         self.U = U
         self.args = args
         self.dev = dev
-        L, H, ps, B, layers = args.ctx, args.heads, args.page_size, args.budget, args.layers
-        dtype = torch.bfloat16 if getattr(args, "dtype", "f16") == "bf16" else torch.float16
-        self.c = c = U.InferenceController(layers, H, 128, ps, B // ps, L, dtype, dev)
+        self.H = H = heads or args.heads
+        self.L = L = ctx or args.ctx
+        self.B = B = budget or args.budget
+        self.layers = layers = layers or args.layers
+        ps = args.page_size
+        dtype = dtype or (torch.bfloat16 if getattr(args, "dtype", "f16") == "bf16" else torch.float16)
+        self.dtype = dtype
+        self.c = c = U.InferenceController(layers, H, 128, ps, B // ps, L + room + ps, dtype, dev)
         gen = torch.Generator(device=dev).manual_seed(1234 + int(os.environ.get("RANK", "0")) + 1000 * seed_offset)
         c.prepare_hadamard(L - 1)
         c.begin_forward(L - 1)
@@ -219,12 +236,14 @@ class Workload:
         self.h_out = torch.zeros(layers, 1, H, 128, dtype=dtype).pin_memory()
         self.q_code = torch.zeros(layers, 1, H, 16, dtype=dtype, device=dev)
         self.graph = None
+        self.advancing = False
+        self.after_layers = None      # e.g. the gather of the layer outputs over the ranks
 
+    # ---- the step at a FIXED position (host lengths): four separate operators, or one kernel class alone
     def layer_step(self, layer):
         U, c = self.U, self.c
         q, k, v = self.d_qkv[0, layer], self.d_qkv[1, layer], self.d_qkv[2, layer]
         if not self.args.unfused:
-            # public fused API: append + estimate + select/attend, two or three launches
             U.decode_step(q, k, v, c, layer, out=self.d_out[layer], record_indices=False)
             return
         q_code = U.append_qkv_fused(q, k, v, c, layer, out=self.q_code[layer])
@@ -232,27 +251,67 @@ class Workload:
         U.decode_topk(est, c)
         U.decode_sparse_attn(q, c, layer, c.topk_dindices_buffer, out=self.d_out[layer])
 
-    def step_eager(self):
-        for layer in range(self.args.layers):
+    def step_fixed(self):
+        for layer in range(self.layers):
             self.layer_step(layer)
+        if self.after_layers is not None:
+            self.after_layers()
+
+    # ---- the step that advances (device-resident length): the public fused API, graph-replayable
+    def step_body_dev(self):
+        U, c = self.U, self.c
+        for layer in range(self.layers):
+            U.decode_step_dev(self.d_qkv[0, layer], self.d_qkv[1, layer], self.d_qkv[2, layer], c, layer,
+                              out=self.d_out[layer])
+        if self.after_layers is not None:
+            self.after_layers()
+        U.seq_len_advance(c)
+
+    def host_advance(self):
+        """What the host does per token: reserve cache room (one page number travels to the device
+        every page_size tokens)."""
+        c = self.c
+        c.prepare_hadamard(1)
+        c.kv_cache.table_all()
+        c.hadamard_cache.table_all()
 
     def capture(self):
+        """Captures the step as one CUDA graph.  Fused step: the advancing, device-length form (the
+        warm-up runs are real tokens).  --unfused: the four host-length operators at a fixed position."""
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
+        self.advancing = not self.args.unfused
         with torch.cuda.stream(s):
-            for _ in range(2):
-                self.step_eager()
+            if self.advancing:
+                self.c.sync_seq_len()
+                self.step_body_dev()          # token at position ctx - 1
+                self.host_advance()
+                self.step_body_dev()
+            else:
+                self.step_fixed()
+                self.step_fixed()
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
+        if self.args.eager:
+            return
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
-            self.step_eager()
+            if self.advancing:
+                self.step_body_dev()
+            else:
+                self.step_fixed()
 
     def step(self):
-        if self.graph is not None:
+        if self.advancing:
+            self.host_advance()
+            if self.graph is not None:
+                self.graph.replay()
+            else:
+                self.step_body_dev()
+        elif self.graph is not None:
             self.graph.replay()
         else:
-            self.step_eager()
+            self.step_fixed()
 
     def step_e2e(self):
         """Host buffers in, host buffers out: H2D of this step's q/k/v, the step, D2H of the outputs."""
@@ -261,67 +320,63 @@ class Workload:
         self.h_out.copy_(self.d_out, non_blocking=True)
 
     def stage_op(self, stage, layer):
-        """One kernel class of one layer ("step": the whole layer step)."""
+        """One kernel class of one layer at the fixed position the host holds."""
         U, c = self.U, self.c
         from adamas_b200 import _kernels as K
         q, k, v = self.d_qkv[0, layer], self.d_qkv[1, layer], self.d_qkv[2, layer]
+        n = c.hadamard_cache.seqlen - 1
+        kk = c.inference_token_budget - 1
         if stage == "step":
             self.layer_step(layer)
         elif stage == "append":
             U.append_qkv_fused(q, k, v, c, layer, out=self.q_code[layer])
-        elif stage == "append_estimate":   # first launch of the two-launch step
-            n = c.hadamard_cache.seqlen - 1
+        elif stage == "append_estimate":   # first launch of the two-launch step (it also fills the histograms)
             K.append_estimate(q, k, v, self.q_code[layer], c.kv_cache.buf_layer(layer), c.kv_indices_with_last,
                               c.kv_cache.last_page_len, c.hadamard_cache.buf_layer(layer), c.hadamard_indices,
-                              c.hadamard_cache.last_page_len, c.distance_scratch(n))
+                              c.hadamard_cache.last_page_len, c.distance_scratch(n), hist=c.hist_scratch,
+                              hist_slices=K.select_attend_slices(n, kk, self.H))
         elif stage == "estimate" and self.args.unfused:
             U.decode_estimate(self.q_code[layer], c, layer)
-        elif stage == "estimate":      # fused step: integer distances, as decode_step asks for
-            n = c.hadamard_cache.seqlen - 1
-            K.estimate_attn_score(self.q_code[layer], c.distance_scratch(n), c.hadamard_cache.buf_layer(layer),
-                                  c.hadamard_indices, None, c.hadamard_cache.last_page_len,
-                                  c.hadamard_last_page_idx, c.layout)
-        elif stage == "topk":
-            U.decode_topk(c.estimate_buffer(c.hadamard_cache.seqlen - 1), c)
-        elif stage == "attention":
-            U.decode_sparse_attn(q, c, layer, c.topk_dindices_buffer, out=self.d_out[layer])
-        elif stage == "select_attend":
-            n = c.hadamard_cache.seqlen - 1
-            k = c.inference_token_budget - 1
-            # first launch of the step without the append: leaves the distances and the histograms
+        elif stage == "estimate":      # fused step: integer distances + histograms, as decode_step asks for
             K.estimate_attn_score(self.q_code[layer], c.distance_scratch(n), c.hadamard_cache.buf_layer(layer),
                                   c.hadamard_indices, None, c.hadamard_cache.last_page_len,
                                   c.hadamard_last_page_idx, c.layout, hist=c.hist_scratch,
-                                  hist_slices=K.select_attend_slices(n, k, self.args.heads))
-            K.select_attend(c.distance_scratch(n), k, q, self.d_out[layer],
-                            c.kv_cache.buf_layer(layer), c.kv_indices_with_last, c.kv_cache.last_page_len,
-                            c.kv_last_page_idx, hist=c.hist_scratch, hist_ready=True)
+                                  hist_slices=K.select_attend_slices(n, kk, self.H))
+        elif stage == "topk":
+            U.decode_topk(c.estimate_buffer(n), c)
+        elif stage == "attention":
+            U.decode_sparse_attn(q, c, layer, c.topk_dindices_buffer, out=self.d_out[layer])
+        elif stage == "select_attend":     # second launch of the step; the histograms are ready
+            K.select_attend(c.distance_scratch(n), kk, q, self.d_out[layer], c.kv_cache.buf_layer(layer),
+                            c.kv_indices_with_last, c.kv_cache.last_page_len, c.kv_last_page_idx,
+                            hist=c.hist_scratch, hist_ready=True)
         else:
             raise ValueError(stage)
 
-    # one kernel class alone (a graph with one launch per layer, so the data comes from HBM)
-    def capture_stage_only(self, stage):
-        return capture_batch([self], stage)
 
+def capture_batch(wls, stage, pre_stage=None):
+    """CUDA graph of `stage` for every layer of every sequence in `wls` (`pre_stage`, if given, runs in
+    front of it in every layer).  The sequences are independent (each has its own controller, page tables
+    and caches); within a layer they run on one stream each, forked from and joined to the capturing
+    stream, the way a batched model step proceeds layer by layer."""
+    layers = wls[0].layers
 
-def capture_batch(wls, stage):
-    """CUDA graph of `stage` for every layer of every sequence in `wls`.  The sequences are
-    independent (each has its own controller, page tables and caches); within a layer they run on
-    one stream each, forked from and joined to the capturing stream, the way a batched model step
-    proceeds layer by layer."""
-    layers = wls[0].args.layers
+    def ops(wl, layer):
+        if pre_stage is not None:
+            wl.stage_op(pre_stage, layer)
+        wl.stage_op(stage, layer)
 
     def body(main, streams):
         for layer in range(layers):
             if len(wls) == 1:
-                wls[0].stage_op(stage, layer)
+                ops(wls[0], layer)
                 continue
             fork = torch.cuda.Event()
             fork.record(main)
             for wl, st in zip(wls, streams):
                 st.wait_event(fork)
                 with torch.cuda.stream(st):
-                    wl.stage_op(stage, layer)
+                    ops(wl, layer)
                 join = torch.cuda.Event()
                 join.record(st)
                 main.wait_event(join)
@@ -361,6 +416,12 @@ def timed(fn, steps, dist_on, dev):
     return ms
 
 
+def timed_blocks(fn, steps, blocks, dist_on, dev):
+    """`blocks` repetitions of timed(fn, steps): the median block (ms for `steps` calls) and all of them."""
+    all_ms = sorted(timed(fn, steps, dist_on, dev) for _ in range(blocks))
+    return all_ms[len(all_ms) // 2], all_ms
+
+
 def measured_peak():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -368,6 +429,48 @@ def measured_peak():
             return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
     except Exception:
         return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def ncu_traffic(kernel, args):
+    """DRAM bytes per launch of `kernel` from an ncu capture of this workload, if one is on record
+    (profiles/ncu_traffic.json: a list of {kernel, ctx, heads, budget, page_size, dtype, bytes, source}),
+    else None: the figure is never guessed."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
+            table = json.load(f)
+    except Exception:
+        return None, None
+    for row in table:
+        if (row.get("kernel"), row.get("ctx"), row.get("heads"), row.get("budget"), row.get("page_size"),
+                row.get("dtype")) == (kernel, args.ctx, args.heads, args.budget, args.page_size, args.dtype):
+            return float(row["bytes"]), row.get("source")
+    return None, None
+
+
+def strong_scaling_record(args, dev, world, dist_on):
+    """The 32-head model split over the ranks (32 / N heads each; the configuration the head-sharded
+    scaling is stated for), next to the whole model on one GPU, each as the advancing step graph:
+    32K context / budget 1024 in fp16 and 128K / budget 2048 in bf16."""
+    out = []
+    for ctx, budget, dtype, name, layers in ((32768, 1024, torch.float16, "f16", 16), (131072, 2048, torch.bfloat16, "bf16", 4)):
+        rec = {"ctx": ctx, "budget": budget, "dtype": name, "layers_timed": layers, "total_heads": 32, "n_gpus": world}
+        for label, heads in (("one_gpu_32_heads", 32), ("sharded", 32 // world)):
+            wl = Workload(args, dev, seed_offset=7, room=64, heads=heads, ctx=ctx, budget=budget, layers=layers, dtype=dtype)
+            wl.capture()
+            for _ in range(3):
+                wl.step()
+            ms, _ = timed_blocks(wl.step, 10, 3, dist_on, dev)
+            rec[label + "_us_per_layer"] = ms / 10 * 1e3 / layers
+            rec[label + "_heads_per_gpu"] = heads
+            del wl
+            torch.cuda.empty_cache()
+        rec["speedup"] = rec["one_gpu_32_heads_us_per_layer"] / rec["sharded_us_per_layer"]
+        rec["efficiency"] = rec["speedup"] / world
+        peak, _ = measured_peak()
+        rec["sharded_path_roofline_frac_per_gpu"] = (stage_bytes(ctx, 32 // world, budget)["total"] /
+                                                     (rec["sharded_us_per_layer"] * 1e-6) / 1e9 / peak)
+        out.append(rec)
+    return out
 
 
 def run_ours(args):
@@ -382,62 +485,87 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if dist_on:
         dist.init_process_group("nccl", device_id=dev)
-    wl = Workload(args, dev)
-    gather_buf = None
+    blocks = max(1, args.blocks)
+    warm = max(3, args.warmup)
+    # room for every token the run appends: warm-ups, the timed blocks of both legs, the eager leg
+    room = 2 * (warm + blocks * args.steps) + 64 + 64
+    wl = Workload(args, dev, room=room)
     if dist_on:
         gather_buf = torch.empty(world, *wl.d_out.shape, dtype=wl.d_out.dtype, device=dev)
+        # the layer outputs of all ranks, gathered inside the step (NCCL collectives can be captured)
+        wl.after_layers = lambda: dist.all_gather_into_tensor(gather_buf, wl.d_out)
+        dist.all_gather_into_tensor(gather_buf, wl.d_out)     # communicator set-up outside any capture
+        torch.cuda.synchronize()
 
-    def step_dev():
+    wl.capture()
+    for _ in range(warm):
         wl.step()
-        if dist_on:
-            dist.all_gather_into_tensor(gather_buf, wl.d_out)
-
-    def step_e2e():
-        wl.step_e2e()
-        if dist_on:
-            dist.all_gather_into_tensor(gather_buf, wl.d_out)
-
-    if not args.eager:
-        wl.capture()
-    for _ in range(max(3, args.warmup)):
-        step_dev()
     torch.cuda.synchronize()
 
     sampler = ClockSampler(local)
     sampler.start()
-    ms = timed(step_dev, args.steps, dist_on, dev)
+    ms, ms_blocks = timed_blocks(wl.step, args.steps, blocks, dist_on, dev)
     clocks = sampler.stop()
 
     for _ in range(3):
-        step_e2e()
-    ms_e2e = timed(step_e2e, args.steps, dist_on, dev)
+        wl.step_e2e()
+    ms_e2e, _ = timed_blocks(wl.step_e2e, args.steps, blocks, dist_on, dev)
 
-    # eager (no graph) end to end, for information
+    # eager (no graph) end to end, for information: the same advancing step, launched call by call
     saved = wl.graph
     wl.graph = None
     for _ in range(2):
-        step_e2e()
-    ms_eager = timed(step_e2e, max(1, min(args.steps, 20)), dist_on, dev)
+        wl.step_e2e()
+    n_eager = max(1, min(args.steps, 20))
+    ms_eager = timed(wl.step_e2e, n_eager, dist_on, dev)
     wl.graph = saved
+    ctx_end = wl.c.kv_cache.seqlen
 
-    # dominant kernel alone (estimate), one launch per layer so the data comes from HBM
+    # Every kernel class of the step alone (a graph with one launch per layer, so the data comes from HBM),
+    # at the position the host holds now.  select_attend needs the estimate's distances and histograms in
+    # front of it: it is timed as (estimate + select_attend) - estimate.
+    c = wl.c
+    c.begin_forward(1)
     stage_us = {}
-    # leave integer distances of the last layer in the scratch for the select/attend stage
-    wl.U.decode_step(wl.d_qkv[0, 0], wl.d_qkv[1, 0], wl.d_qkv[2, 0], wl.c, 0, out=wl.d_out[0], record_indices=True)
     for layer in range(args.layers):   # query codes of every layer, for the estimate stage run alone
-        wl.U.append_qkv_fused(wl.d_qkv[0, layer], wl.d_qkv[1, layer], wl.d_qkv[2, layer], wl.c, layer, out=wl.q_code[layer])
-    stage_list = ("estimate", "append", "select_attend") if not args.unfused else ("estimate", "append", "topk", "attention")
-    if two_launch_step(args):
-        stage_list = ("append_estimate",) + stage_list
-    for stage in stage_list:
-        g_st = wl.capture_stage_only(stage)
+        wl.U.append_qkv_fused(wl.d_qkv[0, layer], wl.d_qkv[1, layer], wl.d_qkv[2, layer], c, layer, out=wl.q_code[layer])
+    torch.cuda.synchronize()
+
+    def stage_time(stage, pre=None):
+        g_st = capture_batch([wl], stage, pre_stage=pre)
         for _ in range(3):
             g_st.replay()
-        stage_us[stage] = timed(g_st.replay, args.steps, False, dev) * 1e3 / args.steps / args.layers
+        us = timed_blocks(g_st.replay, max(10, args.steps // 2), 3, False, dev)[0] * 1e3 / max(10, args.steps // 2) / args.layers
         del g_st
-    # the dominant kernel of the timed region: the estimate, with the append inside in the two-launch step
-    est_kernel = "estimate_append_kernel" if two_launch_step(args) else "estimate_kernel"
-    est_us = stage_us["append_estimate" if two_launch_step(args) else "estimate"]
+        return us
+
+    if args.unfused:
+        for stage in ("append", "estimate", "topk", "attention"):
+            stage_us[stage] = stage_time(stage)
+        kernels = {"append": "append_decode_kernel", "estimate": "estimate_kernel", "topk": "topk_cluster_kernel",
+                   "attention": "sparse_decode_kernel"}
+        kbytes = lambda by: {"append": 0, "estimate": by["estimate"], "topk": by["topk"], "attention": by["attention"]}
+    else:
+        first = "append_estimate" if two_launch_step(args) else "estimate"
+        stage_us[first] = stage_time(first)
+        if first != "estimate":
+            stage_us["estimate"] = stage_time("estimate")
+        else:
+            stage_us["append"] = stage_time("append")
+        both = stage_time("select_attend", pre="estimate")
+        stage_us["estimate_then_select_attend"] = both
+        stage_us["select_attend"] = both - stage_us["estimate"]
+        kernels = {first: "estimate_append_kernel" if first == "append_estimate" else "estimate_kernel",
+                   "select_attend": "select_attend_kernel"}
+        if first == "estimate":
+            kernels["append"] = "append_decode_kernel"
+        kbytes = lambda by: {first: by["estimate"], "select_attend": by["topk"] + by["attention"], "append": 0}
+
+    strong = None
+    if dist_on and not args.no_strong and 32 % world == 0:
+        del wl
+        torch.cuda.empty_cache()
+        strong = strong_scaling_record(args, dev, world, dist_on)
 
     if rank != 0:
         if dist_on:
@@ -451,29 +579,43 @@ def run_ours(args):
     value = step_bytes / (ms_per_step * 1e-3) / 1e9
     e2e_value = step_bytes / (ms_e2e / args.steps * 1e-3) / 1e9
     peak, peak_src = measured_peak()
-    est_gbs = by["estimate"] / (est_us * 1e-6) / 1e9
+    # roofline of every kernel of the step; the headline block is the one with the largest share of the time
+    kb = kbytes(by)
+    per_kernel = []
+    for stage, kname in kernels.items():
+        if stage not in stage_us or kb.get(stage, 0) == 0:
+            continue
+        traffic, src = ncu_traffic(kname, args)
+        gbs = kb[stage] / (stage_us[stage] * 1e-6) / 1e9
+        per_kernel.append({"kernel": kname, "bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s",
+                           "frac": gbs / peak, "traffic": traffic, "traffic_source": src, "peak_source": peak_src,
+                           "us_per_launch": stage_us[stage], "algorithmic_bytes_per_launch": kb[stage],
+                           "share_of_step_time": stage_us[stage] / sum(stage_us[s] for s in kernels if s in stage_us)})
+    per_kernel.sort(key=lambda r: -r["us_per_launch"])
+    launches = launches_per_layer(args) * args.layers + (1 if not args.unfused else 0)
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": getattr(args, "dtype", "f16"), "data": "synthetic",
         "us_per_layer": ms_per_step * 1e3 / args.layers,
         "us_per_layer_e2e": ms_e2e / args.steps * 1e3 / args.layers,
-        "us_per_layer_e2e_eager": ms_eager / max(1, min(args.steps, 20)) * 1e3 / args.layers,
+        "us_per_layer_e2e_eager": ms_eager / n_eager * 1e3 / args.layers,
         "path_roofline_frac": value / world / peak,
+        "timed_blocks_ms": ms_blocks,
+        "context_at_end": ctx_end,
         "config": workload_config(args),
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT,
-                "h2d_bytes_per_step": wl.h_qkv.numel() * wl.h_qkv.element_size(),
-                "d2h_bytes_per_step": wl.h_out.numel() * wl.h_out.element_size()},
-        "gpu_launches": args.steps * args.layers * launches_per_layer(args),
-        "roofline": {"kernel": est_kernel, "bound": "hbm", "achieved": est_gbs, "peak": peak,
-                     "unit": "GB/s", "frac": est_gbs / peak, "traffic": args.traffic,
-                     "peak_source": peak_src, "us_per_launch": est_us,
-                     "algorithmic_bytes_per_launch": by["estimate"]},
+                "h2d_bytes_per_step": args.layers * 3 * H * 128 * 2,
+                "d2h_bytes_per_step": args.layers * H * 128 * 2},
+        "gpu_launches": args.steps * blocks * launches,
+        "roofline": per_kernel[0] if per_kernel else None,
+        "roofline_other_kernels": per_kernel[1:],
         "stage_bytes_per_layer": by,
         "stage_us_alone": stage_us,
-        "stage_gbs_alone": {k: by[k] / (stage_us[k] * 1e-6) / 1e9 for k in ("estimate", "topk", "attention") if k in stage_us},
     }
+    if strong is not None:
+        line["strong"] = strong
     if not args.no_cpu and world >= 1:
         sec, n = time_cpu_reference(L, H, B, steps=60, warmup=2, budget_s=15.0)
         line["cpu_baseline"] = {
@@ -516,26 +658,32 @@ def run_sweep(args):
                 K.set_estimate_blocks_per_sm(args.sweep_est_blocks or (1 if batch > 1 else 2))
                 wls = [Workload(a, dev, seed_offset=i) for i in range(batch)]
                 for wl in wls:
-                    wl.step_eager()
+                    wl.step_fixed()
                 torch.cuda.synchronize()
                 by = stage_bytes(ctx, args.heads, budget, batch)
                 out = {"sweep": True, "batch": batch, "ctx": ctx, "budget": budget, "heads": args.heads,
                        "page_size": args.page_size, "layers_rotated": layers, "max_cluster": cluster,
                        "est_blocks_per_sm": args.sweep_est_blocks or (1 if batch > 1 else 2)}
-                for stage in ("estimate", "topk", "attention", "select_attend", "append", "step"):
-                    if stage in ("select_attend", "step"):
-                        a.unfused = False      # the estimate must have left integer distances
-                        for wl in wls:
-                            wl.U.decode_step(wl.d_qkv[0, 0], wl.d_qkv[1, 0], wl.d_qkv[2, 0], wl.c, 0, out=wl.d_out[0])
-                    g = capture_batch(wls, stage)
+                def sweep_time(stage, pre=None):
+                    g = capture_batch(wls, stage, pre_stage=pre)
                     for _ in range(3):
                         g.replay()
                     us = timed(g.replay, args.steps, False, dev) * 1e3 / args.steps / layers
-                    a.unfused = True
-                    out[stage + "_us"] = round(us, 2)
-                    if stage in by:
-                        out[stage + "_GBps"] = round(by[stage] / (us * 1e-6) / 1e9, 1)
                     del g
+                    return us
+
+                for stage in ("estimate", "topk", "attention", "append"):     # the four separate operators
+                    out[stage + "_us"] = round(sweep_time(stage), 2)
+                    if stage in by:
+                        out[stage + "_GBps"] = round(by[stage] / (out[stage + "_us"] * 1e-6) / 1e9, 1)
+                # the fused step and its second kernel (timed behind the estimate that feeds it)
+                a.unfused = False
+                for wl in wls:
+                    wl.step_fixed()
+                est_fused = sweep_time("estimate")
+                out["select_attend_us"] = round(sweep_time("select_attend", pre="estimate") - est_fused, 2)
+                out["step_us"] = round(sweep_time("step"), 2)
+                a.unfused = True
                 out["select_attend_GBps"] = round((by["topk"] + by["attention"]) / (out["select_attend_us"] * 1e-6) / 1e9, 1)
                 out["step_GBps"] = round(by["total"] / (out["step_us"] * 1e-6) / 1e9, 1)
                 print(json.dumps(out), flush=True)
@@ -694,9 +842,9 @@ def main():
     ap.add_argument("--unfused", action="store_true",
                     help="four launches per layer (append, estimate, top-k, sparse decode) instead of the fused step")
     ap.add_argument("--no-cpu", dest="no_cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--traffic", type=float, default=None,
-                    help="DRAM bytes per launch of the dominant kernel from an ncu capture; default: the figure in "
-                         "profiles/fused_step_kernels_32k_b1024_ncu.md when the workload matches it")
+    ap.add_argument("--blocks", type=int, default=5, help="the timed steps are repeated this many times; the median block is reported")
+    ap.add_argument("--no-strong", dest="no_strong", action="store_true",
+                    help="N > 1: skip the strong-scaling record (the 32-head model split over the ranks)")
     ap.add_argument("--sweep", action="store_true", help="per-operator sweep over context x budget (one GPU)")
     ap.add_argument("--sweep-ctx", dest="sweep_ctx", type=int, nargs="+", default=[8192, 32768, 131072])
     ap.add_argument("--sweep-budget", dest="sweep_budget", type=int, nargs="+", default=[64, 128, 512, 2048])
@@ -722,11 +870,6 @@ def main():
     if args.sweep:
         run_sweep(args)
         return
-    if args.traffic is None and (args.ctx, args.heads, args.page_size) == (32768, 32, 16):
-        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel (ncu, 32K
-        # context, 32 heads): 33.62 MB for the estimate with the append inside
-        # (profiles/fused_step_kernels_32k_b1024_ncu.md), 33.58 MB for the plain estimate
-        args.traffic = 33.62e6 if two_launch_step(args) else 33.58e6 + 1.0e3
     if args.impl == "reference":
         run_reference_arm(args)
     else:

@@ -48,12 +48,14 @@ extern "C" {
 
 typedef void* adamas_stream_t;   /* a cudaStream_t */
 
-/* Histogram scratch of the fused decode step: 32-bit words per head.  The estimate launch of a step
- * counts the distances of every head into it (one 512-bin histogram per slice of the row, up to 16
- * slices), the select+attend launch reads the counts and clears them again.  The caller allocates
- * num_heads * ADAMAS_HIST_WORDS_PER_HEAD words and zeroes them ONCE; every call that uses the table
- * leaves it all zero.  Calls that may overlap on the GPU need separate tables. */
-#define ADAMAS_HIST_WORDS_PER_HEAD (16 * 512)
+/* Scratch of the fused decode step ("histogram scratch"): 32-bit words per head.  The estimate launch
+ * of a step counts the distances of every head into its first 16 * 512 words (one 512-bin histogram
+ * per slice of the row, up to 16 slices); the select+attend launch reads the counts, passes the thread
+ * blocks' partial attention results through the remaining words, and clears the counts and its
+ * arrival counter again.  The caller allocates num_heads * ADAMAS_HIST_WORDS_PER_HEAD words and zeroes
+ * them ONCE; every call that uses the table leaves it ready for the next one (histogram part all
+ * zero).  Calls that may overlap on the GPU need separate tables. */
+#define ADAMAS_HIST_WORDS_PER_HEAD (16 * 512 + 16 * 132)
 
 int adamas_abi_version(void);
 const char* adamas_last_error(void);
@@ -88,7 +90,7 @@ int adamas_set_estimate_blocks_per_sm(int blocks);
 
 /* Upper bound (1, 2, 4 or 8; default 8, or ADAMAS_MAX_CLUSTER in the environment) on the number of
  * thread blocks that share one head in adamas_select_attend / adamas_decode_step.  Eight blocks per
- * head give the shortest single call; a smaller cluster takes longer per call but leaves room on the
+ * head give the shortest single call; fewer take longer per call but leave room on the
  * GPU for calls of other sequences running on other streams (a batch of independent sequences).  Rows
  * longer than 32768 x the bound are rejected.  No counterpart in the reference (batch 1 only). */
 int adamas_set_max_cluster(int blocks);

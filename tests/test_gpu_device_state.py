@@ -85,7 +85,7 @@ def test_graph_replay_equals_eager_loop(dtype, L0, ps, budget, H, rope, tokens):
         assert torch.equal(idx_a, idx_b), f"selected slots differ at token {t}"
         _assert_attn_close(ob[0], oa[0].float())
         assert torch.equal(qs.view(torch.int16), qa.view(torch.int16)), "rotated q"
-        assert int(cb.hist_scratch.abs().sum().item()) == 0
+        assert int(K.histogram_counts(cb.hist_scratch).abs().sum().item()) == 0
         q_last = qa
     L = L0 + tokens
     assert ca.kv_cache.seqlen == cb.kv_cache.seqlen == L and int(cb.seq_len_dev.item()) == L + 1
