@@ -658,6 +658,28 @@ def append_estimate(q, k, v, q_code, kv_data, kv_indices, kv_last_page_len, hada
         int(hist_slices), _stream()), "append_estimate")
 
 
+def hist_rowsum(hist: torch.Tensor, slices: int, out: torch.Tensor) -> None:
+    """out [H, 512] int32 = sum of the first `slices` histogram rows per head of a histogram_scratch
+    table an estimate call has filled (a sequence shard's histogram, ready to be exchanged)."""
+    h = out.size(0)
+    _check_hist(hist, h)
+    _require(out.is_cuda and out.dtype == torch.int32 and out.is_contiguous() and tuple(out.shape) == (h, 512),
+             "out must be a contiguous int32 CUDA tensor [H, 512]")
+    _lib.check(lib.adamas_hist_rowsum(_ptr(hist), h, int(slices), _ptr(out), _stream()), "hist_rowsum")
+
+
+def global_cut(all_hists: torch.Tensor, shard: int, k: int, ext_cut: torch.Tensor) -> None:
+    """all_hists [G, H, 512] int32 (the shards' histograms, ascending token ranges) -> ext_cut [H, 2]
+    int32 for shard `shard`: the cut distance of the k smallest distances of the whole sequence and
+    this shard's share of the cut-valued elements."""
+    _require(all_hists.is_cuda and all_hists.dtype == torch.int32 and all_hists.is_contiguous()
+             and all_hists.dim() == 3 and all_hists.size(2) == 512, "all_hists must be int32 [G, H, 512]")
+    g, h, _ = all_hists.shape
+    _require(ext_cut.is_cuda and ext_cut.dtype == torch.int32 and ext_cut.is_contiguous()
+             and tuple(ext_cut.shape) == (h, 2), "ext_cut must be a contiguous int32 CUDA tensor [H, 2]")
+    _lib.check(lib.adamas_global_cut(_ptr(all_hists), g, int(shard), h, int(k), _ptr(ext_cut), _stream()), "global_cut")
+
+
 def merge_states(o_parts: torch.Tensor, lse_parts: torch.Tensor, o: torch.Tensor,
                  lse: Optional[torch.Tensor] = None) -> None:
     """o_parts [P,H,D] fp32 normalised partial outputs, lse_parts [P,H] base-2 -> o [H,D] (or [1,H,D])."""

@@ -1099,29 +1099,32 @@ void sa_shape(int n, int k, int cl, SaPlan* pl) {
 
 int sa_plan(int n, int k, int num_heads, const DeviceInfo* di, SaPlan* pl) {
   const int g_total = (n + 7) / 8;
+  // Blocks per head: any number up to 16 (the blocks of a head do not wait for one another), as few
+  // granules per thread as possible.  By default up to 8 blocks, or more as long as every block of the
+  // launch is resident at once (a row a little beyond 8 * 512 granules then takes 9 blocks instead of
+  // two granules per thread, which would double the selection's work); adamas_set_max_cluster lowers the
+  // bound.
+  const int user_limit = max_cluster();
+  const int resident = std::max(1, 2 * di->num_sms / num_heads);
+  const int cl_limit = user_limit < kSaMaxCluster ? user_limit
+                                                  : std::min(kSaBigCluster, std::max(kSaMaxCluster, resident));
   int cl = 0, items = 0;
-  const int cl_limit = max_cluster();
   for (int it = 1; it <= 8 && cl == 0; it *= 2) {
-    for (int c = 1; c <= cl_limit; c *= 2) {
-      if (static_cast<int64_t>(c) * it * kSaThreads >= g_total) {
-        cl = c;
-        items = it;
-        break;
-      }
+    const int need = (g_total + it * kSaThreads - 1) / (it * kSaThreads);
+    if (need <= cl_limit) {
+      cl = std::max(1, need);
+      items = it;
     }
   }
-  ADAMAS_REQUIRE(cl > 0, "select_attend supports at most %d distances per head at cluster size %d (got %d)",
+  ADAMAS_REQUIRE(cl > 0, "select_attend supports at most %d distances per head with %d blocks per head (got %d)",
                  cl_limit * 8 * kSaThreads * 8, cl_limit, n);
-  if (cl == kSaMaxCluster && items >= 2 && cl_limit == kSaMaxCluster && kSaBigCluster * num_heads <= 2 * di->num_sms) {
-    // A long row (16 or more distances per thread) of few heads (a head-sharded model): most SMs would
-    // idle while 8 blocks per head walk their slices.  Sixteen blocks per head halve the slices, as
-    // long as all blocks are resident at once.
-    cl = kSaBigCluster;
-    items /= 2;
-  }
+  // with several granules per thread, rather twice the blocks with half-filled threads than the fewest
+  // blocks that cover the row: a block's work is a chain of short steps, more blocks shorten it
+  if (items >= 2) cl = std::min(cl_limit, std::max(cl, (g_total + items * kSaThreads / 2 - 1) / (items * kSaThreads / 2)));
   // a large budget on a short row: more blocks per head than the scan needs, so that each block
   // attends to about one tile of winners, as long as all blocks stay resident at once
-  while (cl < cl_limit && k > cl * kSaTile && 2 * cl * num_heads <= 2 * di->num_sms) cl *= 2;
+  while (cl < std::min(cl_limit, kSaMaxCluster) && k > cl * kSaTile && 2 * cl * num_heads <= 2 * di->num_sms) cl *= 2;
+  cl = std::min(cl, cl_limit);
   pl->cl = cl;
   pl->items = items;
   sa_shape(n, k, cl, pl);
@@ -1220,6 +1223,25 @@ int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, co
   return select_attend_impl(dist, dist_stride, n, k, q, o, o_f32, lse, kv_data, kv_page_table, page_size, num_heads,
                             dtype, last_page_len > 0 ? 1 : 0, static_cast<unsigned>(std::max<int64_t>(tail, 0)), hist,
                             ext_cut, nullptr, out_idx, out_stride, sm_scale, pl, stream);
+}
+
+int adamas_hist_rowsum(const uint32_t* hist, int num_heads, int slices, uint32_t* out, adamas_stream_t stream) {
+  ADAMAS_REQUIRE(hist && out, "null pointer");
+  ADAMAS_REQUIRE(num_heads >= 1 && slices >= 1 && slices <= kSaMaxSlices, "num_heads / slices out of range");
+  ADAMAS_LAUNCH("hist_rowsum_kernel", hist_rowsum_kernel, dim3(num_heads), dim3(kSaBins), 0, to_stream(stream), 1, hist,
+                slices, out);
+  return check_launch("hist_rowsum_kernel");
+}
+
+int adamas_global_cut(const uint32_t* all_hists, int num_shards, int shard, int num_heads, int k, int32_t* ext_cut,
+                      adamas_stream_t stream) {
+  ADAMAS_REQUIRE(all_hists && ext_cut, "null pointer");
+  ADAMAS_REQUIRE(num_shards >= 1 && shard >= 0 && shard < num_shards && num_heads >= 1 && k >= 1,
+                 "shard / num_shards / num_heads / k out of range");
+  ADAMAS_REQUIRE((reinterpret_cast<uintptr_t>(ext_cut) & 7) == 0, "ext_cut must be 8-byte aligned");
+  global_cut_kernel<<<num_heads, kSaBins, 0, to_stream(stream)>>>(all_hists, num_shards, shard, num_heads, k,
+                                                                  reinterpret_cast<int2*>(ext_cut));
+  return check_launch("global_cut_kernel");
 }
 
 int adamas_seq_len_advance(int32_t* seq_len_dev, int delta, adamas_stream_t stream) {

@@ -39,7 +39,7 @@ constexpr int kSaBins = 512;
 constexpr int kSaMaxSlices = 16;      // histogram rows per head = largest cluster
 constexpr int kSaTile = 128;          // planning unit of the host (winners per block it aims for)
 constexpr int kSaWarpRows = 12;       // rows a warp gathers per round (its part of the tile: 12 K + 12 V rows)
-constexpr int kSaMaxCluster = 8;      // blocks per head by default
+constexpr int kSaMaxCluster = 8;      // blocks per head by default (more, up to 16, while all blocks are resident at once)
 constexpr int kSaBigCluster = 16;     // long rows of few heads (see the host code)
 // Scratch words (32 bit) per head: kSaMaxSlices histogram rows of 512 counts, then kSaMaxSlices slots of
 // kSaSlotWords floats for the blocks' partial results (128 outputs, running max, running sum; word 130
@@ -204,22 +204,24 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
     }
     const unsigned excl = wa + it - tot;        // elements of smaller value, whole row
     const unsigned excl_low = wb + il - low;    // ... in lower-ranked slices
-    bool mine;
+    bool mine, all_win = false;
     unsigned need = 0;
     if (p.ext_cut) {
+      // (a cut of 512, beyond every bin: the whole row wins; thread 511 stands in, there are no ties)
       const int2 e = __ldg(p.ext_cut + head);
-      mine = tid == e.x;
-      need = static_cast<unsigned>(e.y);
+      all_win = e.x >= kSaBins;
+      mine = tid == min(e.x, kSaBins - 1);
+      need = all_win ? 0u : static_cast<unsigned>(e.y);
     } else {
       const unsigned want = static_cast<unsigned>(p.k);
       mine = excl < want && excl + tot >= want;   // exactly one thread
       need = want - excl;
     }
     if (mine) {
-      sh.cut = tid;
-      sh.need_eq = need;               // cut-valued winners in all
-      sh.lt_before = excl_low;         // smaller-valued elements in lower-ranked slices
-      sh.eq_before = low;              // cut-valued elements in lower-ranked slices
+      sh.cut = all_win ? static_cast<unsigned>(kSaBins) : static_cast<unsigned>(tid);
+      sh.need_eq = need;                                  // cut-valued winners in all
+      sh.lt_before = excl_low + (all_win ? low : 0u);     // smaller-valued elements in lower-ranked slices
+      sh.eq_before = all_win ? 0u : low;                  // cut-valued elements in lower-ranked slices
     }
     __syncthreads();
   }
@@ -428,33 +430,47 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
     sh.ml[warp][1] = l_run;
   }
   __syncthreads();
-  if (tid < kHeadDim) {
+  {
+    // all 512 threads: thread (part = tid / 128, d = tid % 128) folds the partials of warps 4*part .. 4*part+3
+    // for output d; the four parts are added by the first 128 threads
     float M = -INFINITY;
 #pragma unroll
     for (int w2 = 0; w2 < kSaWarps; ++w2) M = fmaxf(M, sh.ml[w2][0]);
+    const int d = tid & (kHeadDim - 1), part = tid >> 7;
     float od = 0.f, L = 0.f;
 #pragma unroll
-    for (int w2 = 0; w2 < kSaWarps; ++w2) {
+    for (int j = 0; j < kSaWarps / 4; ++j) {
+      const int w2 = part * (kSaWarps / 4) + j;
       const float m = sh.ml[w2][0];
       const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
       L += w * sh.ml[w2][1];
-      if (w != 0.f) od += w * reinterpret_cast<const float*>(sa_tile + w2 * (2 * kSaWarpRows * 256))[tid];
+      if (w != 0.f) od += w * reinterpret_cast<const float*>(sa_tile + w2 * (2 * kSaWarpRows * 256))[d];
     }
-    float* slot = slots + cr * kSaSlotWords;
-    __stcg(slot + tid, od);
-    if (tid == 0) {
-      __stcg(slot + kHeadDim, M);
-      __stcg(slot + kHeadDim + 1, L);
+    float* fold = reinterpret_cast<float*>(sa_tile + kSaWarpRows * 256);   // [4][130], in warp 0's V rows (free by now)
+    fold[part * 130 + d] = od;
+    if (d == 0) fold[part * 130 + kHeadDim] = L;
+    __syncthreads();
+    if (tid < kHeadDim) {
+      float* slot = slots + cr * kSaSlotWords;
+      __stcg(slot + tid, (fold[tid] + fold[130 + tid]) + (fold[260 + tid] + fold[390 + tid]));
+      if (tid == 0) {
+        __stcg(slot + kHeadDim, M);
+        __stcg(slot + kHeadDim + 1, (fold[kHeadDim] + fold[130 + kHeadDim]) + (fold[260 + kHeadDim] + fold[390 + kHeadDim]));
+      }
     }
   }
-  // the block that arrives last at the head's counter merges; nobody waits
+  // the block that arrives last at the head's counter merges; nobody waits.  The block barrier orders
+  // the slot stores of all threads before thread 0's release at the counter; the last block's acquire
+  // there, followed by the second barrier, orders its loads of the slots after every block's stores.
   unsigned* counter = head_scratch + kSaMaxSlices * kSaBins + kHeadDim + 2;   // word 130 of slot 0
-  __threadfence();
   __syncthreads();
-  if (tid == 0) sh.last = (atomicAdd(counter, 1u) == CL - 1) ? 1u : 0u;
+  if (tid == 0) {
+    unsigned ticket;
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(ticket) : "l"(counter) : "memory");
+    sh.last = (ticket == CL - 1) ? 1u : 0u;
+  }
   __syncthreads();
   if (!sh.last) return;
-  __threadfence();
   // every block of the head has read the histograms long ago: clear them and the counter for the next launch
 #pragma unroll
   for (unsigned r = 0; r < kSaMaxSlices; ++r)
@@ -528,6 +544,60 @@ __global__ void __launch_bounds__(kSaThreads) dist_histogram_kernel(const DistHi
   }
   __syncthreads();
   p.hist[static_cast<size_t>(head) * kSaScratchWordsPerHead + r * kSaBins + tid] = h_local[tid];
+}
+
+// ---- a sequence split over several GPUs: one cut for all shards -----------------------------------------------
+// Every shard counts its own distances (estimate kernel, per-slice histograms).  hist_rowsum_kernel adds
+// a shard's slices to one 512-bin histogram per head; the shards exchange those ([G][H][512], one
+// all-gather); global_cut_kernel then derives, identically on every shard, the cut distance of the k
+// smallest distances of the whole sequence and this shard's share of the cut-valued elements (shards
+// hold ascending token ranges, so "the lower position wins a tie" means: lower shards first): the
+// ext_cut input of select_attend_kernel.  No candidate list ever crosses the link.
+__global__ void __launch_bounds__(kSaBins) hist_rowsum_kernel(const uint32_t* __restrict__ scratch, int slices,
+                                                              uint32_t* __restrict__ out) {
+  const int head = blockIdx.x, tid = threadIdx.x;
+  grid_dependency_wait();
+  grid_launch_dependents();
+  const uint32_t* rows = scratch + static_cast<size_t>(head) * kSaScratchWordsPerHead + tid;
+  uint32_t c = 0;
+  for (int r = 0; r < slices; ++r) c += __ldcg(rows + r * kSaBins);
+  out[static_cast<size_t>(head) * kSaBins + tid] = c;
+}
+
+// all: [G][H][512] counts; ext_cut[h] = (cut distance, cut-valued elements shard `rank` takes).  If the
+// whole sequence holds fewer than k distances every element wins: cut = 512, nothing to share out.
+__global__ void __launch_bounds__(kSaBins) global_cut_kernel(const uint32_t* __restrict__ all, int G, int rank, int H,
+                                                             int k, int2* __restrict__ ext_cut) {
+  __shared__ unsigned warp_tot[kSaBins / 32];
+  __shared__ int2 result;
+  const int head = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) result = make_int2(kSaBins, 0);
+  unsigned tot = 0, low = 0, own = 0;
+  for (int g = 0; g < G; ++g) {
+    const unsigned c = all[(static_cast<size_t>(g) * H + head) * kSaBins + tid];
+    tot += c;
+    if (g < rank) low += c;
+    if (g == rank) own = c;
+  }
+  unsigned incl = tot;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) warp_tot[warp] = incl;
+  __syncthreads();
+  unsigned before = 0;
+  for (int w2 = 0; w2 < warp; ++w2) before += warp_tot[w2];
+  const unsigned excl = before + incl - tot;
+  const unsigned want = static_cast<unsigned>(k);
+  if (excl < want && excl + tot >= want) {   // exactly one thread, if the sequence holds k distances
+    const unsigned need = want - excl;       // cut-valued winners in all
+    const unsigned take = need > low ? min(need - low, own) : 0u;
+    result = make_int2(tid, static_cast<int>(take));
+  }
+  __syncthreads();
+  if (tid == 0) ext_cut[head] = result;
 }
 
 }  // namespace adamas

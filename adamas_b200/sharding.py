@@ -8,15 +8,17 @@ adamas/models/Adamas.py:83).  Two partitionings are provided on top of the singl
   (`gather_heads`).
 * by sequence (million-token contexts): rank g owns a contiguous token range for all heads.  Per
   layer-step (`sequence_sharded_step`):
-    1. local distances and a local top-(budget-1) (values + local slots, ascending position);
-    2. all-gather of the candidate VALUES only ([G, H, budget-1] 16-bit);
-    3. every rank selects the global budget-1 smallest among the G*(budget-1) candidates laid out
-       rank-major, so that "lower position wins a tie" means lower rank, then lower local index:
-       the same rule as on one GPU; each rank keeps its own winners (holes are -1);
-    4. local attention over the winners (the rank that owns the newest token adds it), giving a
-       partial (o, lse);
-    5. all-gather of the partials and a merge (same rule as the split-KV merge inside one GPU).
-  No K/V or code bytes ever cross the link.
+    1. local distances, counted into a 512-bin histogram per head (a distance is at most 384);
+    2. all-gather of the histograms ([G, H, 512] int32, 64 KB per rank at 32 heads);
+    3. every rank derives the same cut distance of the budget-1 smallest distances of the whole
+       sequence and its own share of the cut-valued ones (ranks hold ascending token ranges, so
+       "lower position wins a tie" means lower rank first, then lower local index: the single-GPU
+       rule), and selects exactly its winners locally;
+    4. local attention over them (the rank that owns the newest token adds it): a partial
+       (o fp32, lse);
+    5. all-gather of the partials ([G, H, 129] fp32) and a merge (same rule as the split-KV merge
+       inside one GPU, kernels/include/decode/decode_attn.cuh:264-283, 1050-1059).
+  Two collectives; no K/V, code or candidate bytes ever cross the link.
 
 The numerical operators are injected (`ops`), so the protocol can be exercised on CPU ranks (gloo)
 with stand-in operators and on GPUs with the CUDA ones (`CudaOps`).
@@ -62,90 +64,57 @@ def gather_heads(o_local: torch.Tensor, group=None) -> torch.Tensor:
 # ------------------------------------------------------------------------------------------------
 # sequence-sharded decode step
 # ------------------------------------------------------------------------------------------------
-@dataclass
-class LocalCandidates:
-    values: torch.Tensor   # [H, K] 16-bit distances (fp16 or int16), padded with the largest key
-    slots: torch.Tensor    # [H, K] int32 local token slots of the candidates, -1 where padded
-    count: int             # valid candidates per head (same for all heads)
-
-
-def pad_value(dtype: torch.dtype):
-    """A value that sorts after every real distance."""
-    return float("inf") if dtype == torch.float16 else 0x7FFF
-
-
 def sequence_sharded_step(ops, q: torch.Tensor, budget: int, group=None):
     """One layer's decode step over a sequence split across the ranks of `group`.
 
     `ops` provides, for this rank's shard:
-      ops.local_candidates(k) -> LocalCandidates with K == k columns: the rank's k smallest distances
-          (fewer if the shard is shorter; padded), ascending local position;
-      ops.select(values [H, n], k) -> int64/int32 [H, k] positions of the k smallest, ties to the lower
-          position, ascending;
-      ops.attend(q, slots [H, m] with -1 holes, with_tail: bool) -> (o [H, D] fp32, lse [H] fp32 base 2);
-      ops.merge(o_parts [G, H, D], lse_parts [G, H]) -> o [H, D];
-      ops.owns_tail: this rank holds the newest token.
-    Returns (o [H, D], selected [H, budget-1] int64 as rank * K + local candidate number).
+      ops.local_histograms(k) -> int32 [H, 512]: counts of the shard's distances per head (it also
+          leaves the distances where ops.select_attend finds them);
+      ops.cut(all_hists [G, H, 512], rank, k) -> int32 [H, 2]: (cut distance, cut-valued elements
+          this rank takes);
+      ops.select_attend(q, ext_cut, k) -> (o [H, D] fp32, lse [H] fp32 base 2, idx int32 [H, k]: the
+          rank's winners as local token slots, ascending position, -1 beyond their number);
+      ops.merge(o_parts [G, H, D], lse_parts [G, H]) -> o [H, D].
+    Returns (o [H, D], idx).  The whole sequence must hold at least budget - 1 tokens besides the
+    newest one.
     """
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     k = budget - 1
-    cand = ops.local_candidates(k)
-    h = cand.values.size(0)
-
-    # 16-bit integers travel as fp16 bit patterns (all-gather only copies; NCCL has no int16 type)
-    wire = cand.values.contiguous()
-    as_int = wire.dtype in (torch.int16, torch.uint16)
-    if as_int:
-        wire = wire.view(torch.float16)
-    gathered = [torch.empty_like(wire) for _ in range(world)]
-    dist.all_gather(gathered, wire, group=group)
-    table = torch.stack(gathered, dim=1).reshape(h, world * k)        # rank-major candidate table
-    if as_int:
-        table = table.view(cand.values.dtype)
-    sel = ops.select(table, k).to(torch.int64)                        # [H, k] positions in the table
-
-    slots = winners_of_rank(sel, cand.slots, rank)
-
-    o_part, lse_part = ops.attend(q, slots, ops.owns_tail)
-    o_all = [torch.empty_like(o_part) for _ in range(world)]
-    l_all = [torch.empty_like(lse_part) for _ in range(world)]
-    dist.all_gather(o_all, o_part.contiguous(), group=group)
-    dist.all_gather(l_all, lse_part.contiguous(), group=group)
-    o = ops.merge(torch.stack(o_all), torch.stack(l_all))
-    return o, sel
-
-
-def winners_of_rank(sel: torch.Tensor, cand_slots: torch.Tensor, rank: int) -> torch.Tensor:
-    """sel [H, k] positions in the rank-major candidate table, cand_slots [H, k] this rank's candidate
-    slots -> int32 [H, k]: the rank's own winners' slots, -1 elsewhere."""
-    k = cand_slots.size(1)
-    sel = sel.to(torch.int64)
-    mine = (sel // k) == rank
-    local_no = (sel % k).clamp(0, k - 1)
-    slots = torch.gather(cand_slots.to(torch.int64), 1, local_no)
-    return torch.where(mine, slots, torch.full_like(slots, -1)).to(torch.int32).contiguous()
+    hist = ops.local_histograms(k).contiguous()
+    # (gathered along the first dimension, then viewed by rank: the layout every backend accepts)
+    all_hists = torch.empty((world * hist.size(0), hist.size(1)), dtype=hist.dtype, device=hist.device)
+    dist.all_gather_into_tensor(all_hists, hist, group=group)
+    ext_cut = ops.cut(all_hists.view(world, hist.size(0), hist.size(1)), rank, k)
+    o_part, lse_part, idx = ops.select_attend(q, ext_cut, k)
+    packed = torch.cat((o_part, lse_part.unsqueeze(1)), dim=1).contiguous()          # [H, D + 1]
+    gathered = torch.empty((world * packed.size(0), packed.size(1)), dtype=packed.dtype, device=packed.device)
+    dist.all_gather_into_tensor(gathered, packed, group=group)
+    gathered = gathered.view(world, packed.size(0), packed.size(1))
+    d = o_part.size(1)
+    o = ops.merge(gathered[:, :, :d].contiguous(), gathered[:, :, d].contiguous())
+    return o, idx
 
 
 def sequence_sharded_step_local(ops_list, q: torch.Tensor, budget: int):
     """The same protocol with all shards driven by one process (shards of one GPU, or CPU stand-ins):
-    the collectives become concatenations.  Returns (o [H, D], sel [H, budget-1])."""
+    the collectives become stacks.  Returns (o [H, D], [idx of every shard])."""
     k = budget - 1
-    cands = [ops.local_candidates(k) for ops in ops_list]
-    h = cands[0].values.size(0)
-    table = torch.stack([c.values for c in cands], dim=1).reshape(h, len(ops_list) * k)
-    sel = ops_list[0].select(table, k).to(torch.int64)
-    parts = []
-    for rank, (ops, cand) in enumerate(zip(ops_list, cands)):
-        parts.append(ops.attend(q, winners_of_rank(sel, cand.slots, rank), ops.owns_tail))
+    all_hists = torch.stack([ops.local_histograms(k) for ops in ops_list]).contiguous()
+    parts, idxs = [], []
+    for rank, ops in enumerate(ops_list):
+        o_part, lse_part, idx = ops.select_attend(q, ops.cut(all_hists, rank, k), k)
+        parts.append((o_part, lse_part))
+        idxs.append(idx)
     o = ops_list[0].merge(torch.stack([p[0] for p in parts]), torch.stack([p[1] for p in parts]))
-    return o, sel
+    return o, idxs
 
 
 class CudaOps:
     """The CUDA operators of this package on one rank's shard (an InferenceController that holds
     the rank's token range as its own sequence).  The rank that owns the newest token has appended
-    it like any decode step; the other ranks' controllers hold only past tokens."""
+    it like any decode step; the other ranks' controllers hold only past tokens.  A shard may be
+    empty (more ranks than pages): it contributes empty histograms and an empty partial."""
 
     def __init__(self, controller, layer_idx: int, q_code: torch.Tensor, owns_tail: bool):
         from . import _kernels
@@ -154,46 +123,55 @@ class CudaOps:
         self.layer = layer_idx
         self.q_code = q_code
         self.owns_tail = owns_tail
-        w = controller._decode_handler._wrapper
-        if not w._started:   # a shard without the newest token never went through a decode begin_forward
-            controller._decode_handler.begin_forward(torch.zeros(2, dtype=torch.int32), controller.num_heads,
-                                                     controller.num_heads, controller.head_dim,
-                                                     controller.page_size, controller.dtype)
+        h, dev = controller.num_heads, q_code.device
+        # buffers of the step, made once
+        self._hist_out = torch.zeros(h, 512, dtype=torch.int32, device=dev)
+        self._ext = torch.zeros(h, 2, dtype=torch.int32, device=dev)
+        self._o = torch.zeros(h, controller.head_dim, dtype=torch.float32, device=dev)
+        self._lse = torch.full((h,), -float("inf"), dtype=torch.float32, device=dev)
+        self._slices = 0
 
     def _n_local(self) -> int:
         # the tail owner's newest token is excluded from the estimate, as on one GPU
         return self.c.hadamard_cache.seqlen - (1 if self.owns_tail else 0)
 
-    def local_candidates(self, k: int) -> LocalCandidates:
+    def local_histograms(self, k: int) -> torch.Tensor:
         c = self.c
         n = self._n_local()
-        dev = self.q_code.device
-        vdtype = torch.float16 if c.dtype == torch.float16 else torch.int16
-        values = torch.full((c.num_heads, k), pad_value(vdtype), dtype=vdtype, device=dev)
-        slots = torch.full((c.num_heads, k), -1, dtype=torch.int32, device=dev)
-        kk = min(k, n)
-        if kk > 0:
-            dist_buf = c.estimate_buffer(n)
-            self.k.estimate_attn_score(self.q_code, dist_buf, c.hadamard_cache.buf_layer(self.layer),
-                                       c.hadamard_indices, None, c.hadamard_cache.last_page_len,
-                                       c.hadamard_last_page_idx, c.layout, exclude_last=self.owns_tail)
-            self.k.topk_select(dist_buf, kk, slots[:, :kk], values[:, :kk], page_table=c.kv_indices_with_last,
-                               page_size=c.page_size)
-        return LocalCandidates(values, slots, kk)
+        if n <= 0:
+            self._hist_out.zero_()
+            return self._hist_out
+        # (the slice count depends on the shard's length and on the upper bound of its winners)
+        self._slices = self.k.select_attend_slices(n, max(1, min(k, n)), c.num_heads)
+        self.k.estimate_attn_score(self.q_code, c.distance_scratch(n), c.hadamard_cache.buf_layer(self.layer),
+                                   c.hadamard_indices, None, c.hadamard_cache.last_page_len,
+                                   c.hadamard_last_page_idx, c.layout, exclude_last=self.owns_tail,
+                                   hist=c.hist_scratch, hist_slices=self._slices)
+        self.k.hist_rowsum(c.hist_scratch, self._slices, self._hist_out)
+        return self._hist_out
 
-    def select(self, values: torch.Tensor, k: int) -> torch.Tensor:
-        out = torch.empty((values.size(0), k), dtype=torch.int32, device=values.device)
-        self.k.topk_select(values.contiguous(), k, out)
-        return out
+    def cut(self, all_hists: torch.Tensor, rank: int, k: int) -> torch.Tensor:
+        self.k.global_cut(all_hists.contiguous(), rank, k, self._ext)
+        return self._ext
 
-    def attend(self, q: torch.Tensor, slots: torch.Tensor, with_tail: bool):
+    def select_attend(self, q: torch.Tensor, ext_cut: torch.Tensor, k: int):
         c = self.c
-        o = torch.empty((c.num_heads, c.head_dim), dtype=torch.float32, device=q.device)
-        lse = torch.empty(c.num_heads, dtype=torch.float32, device=q.device)
-        w = c._decode_handler._wrapper
-        w.forward(q, torch.empty(0), c.kv_cache.buf_layer(self.layer), slots, None, c.kv_cache.last_page_len,
-                  c.kv_last_page_idx, token_granular=True, lse=lse, tail_len=1 if with_tail else 0, o_f32=o)
-        return o, lse
+        n = self._n_local()
+        idx = torch.full((c.num_heads, k), -1, dtype=torch.int32, device=q.device)
+        if n <= 0:
+            if not self.owns_tail:
+                self._o.zero_()
+                self._lse.fill_(-float("inf"))
+                return self._o, self._lse, idx
+            raise RuntimeError("the shard that owns the newest token must hold at least one older token")
+        kk = max(1, min(k, n))
+        assert self.k.select_attend_slices(n, kk, c.num_heads) == self._slices, "histograms were built for another shape"
+        qq = q if q.dim() == 3 else q.unsqueeze(0)
+        self.k.select_attend(c.distance_scratch(n), kk, qq, None, c.kv_cache.buf_layer(self.layer),
+                             c.kv_cache.table_device(), c.kv_cache.last_page_len if self.owns_tail else 0,
+                             c.kv_cache.indicies[-1], indices_out=idx[:, :kk],
+                             lse=self._lse, hist=c.hist_scratch, hist_ready=True, ext_cut=ext_cut, o_f32=self._o)
+        return self._o, self._lse, idx
 
     def merge(self, o_parts: torch.Tensor, lse_parts: torch.Tensor) -> torch.Tensor:
         h, d = o_parts.shape[1], o_parts.shape[2]

@@ -694,9 +694,10 @@ def run_sweep(args):
 def run_seqshard(args):
     """Sequence-sharded decode of one long context over the ranks (million-token configuration):
     rank g holds tokens [g*L/G, (g+1)*L/G) of every head and layer; per layer-step the ranks run the
-    local estimate and candidate selection, all-gather the candidate distances, pick the global
-    winners, attend over their own winners and merge the partial results (adamas_b200.sharding).
-    Eager launches (NCCL collectives between the kernels).  Prints one JSON line on rank 0."""
+    local estimate with its histograms, all-gather the histograms, derive the same cut and their own
+    share of the ties, select and attend locally, all-gather the partial (o, lse) results and merge
+    them (adamas_b200.sharding): two NCCL all-gathers per layer, everything else this library's
+    kernels.  The whole step is one CUDA graph unless --eager.  Prints one JSON line on rank 0."""
     import torch.distributed as dist
     from adamas_b200 import _kernels as K, sharding
     import adamas_b200.utils as U
@@ -733,20 +734,32 @@ def run_seqshard(args):
     out = torch.zeros(layers, H, 128, dtype=dtype, device=dev)
     q_code = torch.empty(1, H, 16, dtype=dtype, device=dev)
 
+    ops_of_layer = []
+    codes = [torch.empty(1, H, 16, dtype=dtype, device=dev) for _ in range(layers)]
+
     def step():
         for layer in range(layers):
             q, k, v = qkv[0, layer], qkv[1, layer], qkv[2, layer]
             if owns_tail:
-                U.append_qkv_fused(q, k, v, c, layer, out=q_code)
+                U.append_qkv_fused(q, k, v, c, layer, out=codes[layer])      # (re-appends the same token every step)
             else:
-                K.bucketize_pack(K.hadamard_transform(q), q_code)
-            ops = sharding.CudaOps(c, layer, q_code, owns_tail)
-            o, _ = sharding.sequence_sharded_step(ops, q, B)
+                K.bucketize_pack(K.hadamard_transform(q), codes[layer])
+            if len(ops_of_layer) <= layer:
+                ops_of_layer.append(sharding.CudaOps(c, layer, codes[layer], owns_tail))
+            o, _ = sharding.sequence_sharded_step(ops_of_layer[layer], q[0], B)
             out[layer].copy_(o)
 
     for _ in range(max(3, args.warmup)):
         step()
-    ms = timed(step, args.steps, True, dev)
+    torch.cuda.synchronize()
+    graph = None
+    if not args.eager:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        for _ in range(2):
+            graph.replay()
+    ms = timed(graph.replay if graph is not None else step, args.steps, True, dev)
     if rank == 0:
         per_layer_us = ms * 1e3 / args.steps / layers
         by = stage_bytes(L, H, B)
@@ -756,7 +769,9 @@ def run_seqshard(args):
             "ms_per_step": ms / args.steps, "us_per_layer": per_layer_us, "higher_is_better": True,
             "scaling": "strong", "dtype": args.dtype, "data": "synthetic",
             "config": {"workload": f"one sequence of {L} tokens split over {world} GPUs, {layers} layers x {H} heads x 128, "
-                                   f"budget {B}, page size {ps}; eager launches, 3 NCCL all-gathers per layer",
+                                   f"budget {B}, page size {ps}; "
+                                   + ("eager launches" if args.eager else "one CUDA graph per step")
+                                   + ", 2 NCCL all-gathers per layer (histograms, partial results)",
                        "tokens_per_gpu": n_local}}), flush=True)
     dist.destroy_process_group()
 

@@ -89,8 +89,9 @@ int adamas_set_fused_append(int enable);
 int adamas_set_estimate_blocks_per_sm(int blocks);
 
 /* Upper bound (1, 2, 4 or 8; default 8, or ADAMAS_MAX_CLUSTER in the environment) on the number of
- * thread blocks that share one head in adamas_select_attend / adamas_decode_step.  Eight blocks per
- * head give the shortest single call; fewer take longer per call but leave room on the
+ * thread blocks that share one head in adamas_select_attend / adamas_decode_step.  8 means automatic:
+ * eight blocks per head, or up to sixteen while all blocks of the launch are resident at once (the
+ * shortest single call); fewer take longer per call but leave room on the
  * GPU for calls of other sequences running on other streams (a batch of independent sequences).  Rows
  * longer than 32768 x the bound are rejected.  No counterpart in the reference (batch 1 only). */
 int adamas_set_max_cluster(int blocks);
@@ -292,6 +293,26 @@ int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, co
  * winners and num_heads heads on the current device: the hist_slices an estimate call must be given
  * when it prepares the histogram table for that call.  No counterpart in the reference. */
 int adamas_select_attend_slices(int n, int k, int num_heads, int* slices);
+
+/* ---- one sequence split over several GPUs by token range ("sequence shards") -------------------
+ * Shard g holds a contiguous token range of every head (its own KV and code caches).  Per layer-step
+ * every shard runs adamas_estimate with hist on its range, adamas_hist_rowsum, one all-gather of the
+ * [H][512] counts, adamas_global_cut, adamas_select_attend with that ext_cut and an fp32 partial
+ * output, one all-gather of the partials (o, lse) and adamas_merge_states: two collectives, and no
+ * candidate list ever crosses the link.  The reference is single-GPU; the scheme follows what its
+ * split-KV decode does inside one GPU (kernels/include/decode/decode_attn.cuh:1050-1059). */
+
+/* out[h][bin] = sum over the first `slices` histogram rows of head h in a histogram scratch table that
+ * an adamas_estimate call has filled: the shard's 512-bin histogram per head, ready to be exchanged. */
+int adamas_hist_rowsum(const uint32_t* hist, int num_heads, int slices, uint32_t* out, adamas_stream_t stream);
+
+/* all_hists [num_shards][H][512]: the shards' histograms in shard order (ascending token ranges).
+ * Writes ext_cut [H][2] for shard `shard`: the cut distance of the k smallest distances of the whole
+ * sequence and how many cut-valued elements this shard takes (lower shards are served first: the
+ * lower position wins a tie).  If the sequence holds fewer than k distances: (512, 0), every element
+ * wins. */
+int adamas_global_cut(const uint32_t* all_hists, int num_shards, int shard, int num_heads, int k, int32_t* ext_cut,
+                      adamas_stream_t stream);
 
 /* Stages 1 and 2 of a decode step in one launch, for 16, 32 or 64 heads: the append of
  * adamas_append_decode_fused (new token's K, V and code into the caches, query code to q_code; q and k

@@ -67,26 +67,30 @@ def test_sequence_sharded_on_one_gpu(world, L, budget, ps, dtype):
             o, qd = _make_shard(dev, q, k, v, t0, t1, L, ps, dtype)
             ops.append(o)
             spans.append(t0)
-    out, sel = sharding.sequence_sharded_step_local(ops, qd, budget)
+    out, idxs = sharding.sequence_sharded_step_local(ops, qd[0], budget)
+    torch.cuda.synchronize()
     want = ref.decode_step(q[0], k, v, budget)
     got = out.float().cpu()
     atol = REL_TOL * float(want["out"].abs().max())
     torch.testing.assert_close(got, want["out"], rtol=REL_TOL, atol=atol)
     # winners: map each rank's local slots back to global token numbers
-    k1 = budget - 1
-    cands = [o.local_candidates(k1) for o in ops]
     union = [set() for _ in range(H)]
-    for rank, (o, cand) in enumerate(zip(ops, cands)):
-        mine = sharding.winners_of_rank(sel, cand.slots, rank).cpu().numpy()
+    for rank, (o, idx) in enumerate(zip(ops, idxs)):
+        mine = idx.cpu().numpy()
         table = np.asarray(o.c.kv_cache.indicies)
         inv = np.full(table.max() + 1, -1)
         inv[table] = np.arange(len(table))
         for h in range(H):
             s = mine[h][mine[h] >= 0]
             logical = inv[s // ps] * ps + s % ps
+            assert np.all(np.diff(logical) > 0)                      # ascending position order
             union[h] |= set((logical + spans[rank]).tolist())
     for h in range(H):
         assert union[h] == set(want["sel"][h].tolist())
+    from adamas_b200 import _lib, _kernels as K
+    assert _lib.device_error(clear=False) == 0
+    for o in ops:
+        assert int(K.histogram_counts(o.c.hist_scratch).abs().sum().item()) == 0
 
 
 def test_holes_and_empty_lists_in_the_index_list():
@@ -104,7 +108,13 @@ def test_holes_and_empty_lists_in_the_index_list():
     holes = rng.random((H, 100)) < 0.3
     holes[3, :] = True                                    # head 3: everything masked
     slots_t = torch.from_numpy(np.where(holes, -1, slots).astype(np.int32)).to(dev)
-    o, lse = ops.attend(qd, slots_t, with_tail=False)
+    o = torch.empty((H, 128), dtype=torch.float32, device=dev)
+    lse = torch.empty(H, dtype=torch.float32, device=dev)
+    w = c._decode_handler._wrapper
+    if not w._started:
+        c._decode_handler.begin_forward(torch.zeros(2, dtype=torch.int32), H, H, 128, ps, torch.float16)
+    w.forward(qd, torch.empty(0), c.kv_cache.buf_layer(0), slots_t, None, c.kv_cache.last_page_len,
+              c.kv_cache.indicies[-1], token_granular=True, lse=lse, tail_len=0, o_f32=o)
     for h in range(H):
         keep = logical[h][~holes[h]]
         if len(keep) == 0:
@@ -127,7 +137,7 @@ def _nccl_worker(rank, world, port, L, H, budget, ps, q_out):
         q, k, v = _inputs(L, H, 21)
         t0, t1 = sharding.token_range(L, world, rank, ps)
         ops, qd = _make_shard(dev, q, k, v, t0, t1, L, ps, torch.float16)
-        out, _ = sharding.sequence_sharded_step(ops, qd, budget)
+        out, _ = sharding.sequence_sharded_step(ops, qd[0], budget)
         h0, h1 = sharding.head_range(H, world, rank)
         full = sharding.gather_heads(out[None, h0:h1].contiguous())
         torch.cuda.synchronize()

@@ -22,38 +22,53 @@ class OracleOps:
         self.q, self.k, self.v, self.owns_tail = q, k_shard, v_shard, owns_tail
         self.q_code = ref.encode(q)
         self.k_codes = ref.encode(k_shard)
+        self.dist = None
 
-    def local_candidates(self, k):
-        from adamas_b200.sharding import LocalCandidates, pad_value
+    def local_histograms(self, k):
         n = self.k.shape[0] - (1 if self.owns_tail else 0)
         h = self.q.shape[0]
-        values = torch.full((h, k), pad_value(torch.float16), dtype=torch.float16)
-        slots = torch.full((h, k), -1, dtype=torch.int32)
-        kk = min(k, n)
-        if kk > 0:
-            d = ref.code_distance(self.q_code, self.k_codes[:n])
-            sel = ref.select_topk(d, kk)
-            values[:, :kk] = torch.from_numpy(np.take_along_axis(d, sel, 1).astype(np.float16))
-            slots[:, :kk] = torch.from_numpy(sel.astype(np.int32))
-        return LocalCandidates(values, slots, kk)
+        hist = np.zeros((h, 512), dtype=np.int32)
+        self.dist = np.zeros((h, 0), dtype=np.int64)
+        if n > 0:
+            self.dist = ref.code_distance(self.q_code, self.k_codes[:n])
+            for head in range(h):
+                hist[head] = np.bincount(self.dist[head], minlength=512)
+        return torch.from_numpy(hist)
 
-    def select(self, values, k):
-        return torch.from_numpy(ref.select_topk(values.numpy(), k))
+    def cut(self, all_hists, rank, k):
+        a = all_hists.numpy().astype(np.int64)                    # [G, H, 512]
+        h = a.shape[1]
+        out = np.zeros((h, 2), dtype=np.int32)
+        for head in range(h):
+            tot = a[:, head].sum(0)
+            cum = np.cumsum(tot)
+            if cum[-1] < k:
+                out[head] = (512, 0)
+                continue
+            cut = int(np.searchsorted(cum, k))                    # first bin with cum >= k
+            need = k - (cum[cut] - tot[cut])
+            low = a[:rank, head, cut].sum()
+            out[head] = (cut, max(0, min(need - low, a[rank, head, cut])))
+        return torch.from_numpy(out)
 
-    def attend(self, q, slots, with_tail):
+    def select_attend(self, q, ext_cut, k):
         h, d = q.shape
         o = torch.zeros(h, d)
         lse = torch.full((h,), -float("inf"))
+        idx = torch.full((h, k), -1, dtype=torch.int32)
         for head in range(h):
-            tok = [int(s) for s in slots[head].tolist() if s >= 0]
-            if with_tail:
-                tok.append(self.k.shape[0] - 1)
+            cut, take = int(ext_cut[head, 0]), int(ext_cut[head, 1])
+            row = self.dist[head]
+            tok = np.sort(np.concatenate([np.flatnonzero(row < cut), np.flatnonzero(row == cut)[:take]])).tolist()
+            idx[head, : len(tok)] = torch.tensor(tok, dtype=torch.int32)
+            if self.owns_tail:
+                tok = tok + [self.k.shape[0] - 1]
             if tok:
                 oo, ll = ref.sparse_attention(q[head:head + 1], self.k[:, head:head + 1], self.v[:, head:head + 1],
                                               np.asarray([tok]), return_lse=True)
                 o[head] = oo[0]
                 lse[head] = ll[0] / LN2
-        return o, lse
+        return o, lse, idx
 
     def merge(self, o_parts, lse_parts):
         return ref.merge_states(o_parts, lse_parts * LN2)[0]
@@ -76,9 +91,7 @@ def _worker(rank, world, port, L, H, budget, page_size, q_out):
         q, k, v = _inputs(L, H, 11)
         t0, t1 = sharding.token_range(L, world, rank, page_size)
         ops = OracleOps(q, k[t0:t1], v[t0:t1], owns_tail=(t1 == L))
-        o, sel = sharding.sequence_sharded_step(ops, q, budget)
-        cand = ops.local_candidates(budget - 1)
-        mine = sharding.winners_of_rank(sel, cand.slots, rank)
+        o, mine = sharding.sequence_sharded_step(ops, q, budget)
         glob = torch.where(mine >= 0, mine + t0, mine)
         # head-sharded gather of a layer output
         h0, h1 = sharding.head_range(H, world, rank)
