@@ -228,6 +228,26 @@ class LlamaStack:
             g.replay()
         self._expected_dev_len = c.kv_cache.seqlen + 1
 
+    @torch.no_grad()
+    def capture_dense_rest(self) -> "torch.cuda.CUDAGraph":
+        """A CUDA graph of everything in a token EXCEPT the attention path (embedding, projections, MLPs,
+        head): what the dense rest of the model costs, for a breakdown of the token time.  Replaying it
+        overwrites the decode state; use it after the run that is being measured."""
+        def body():
+            self._segment_first()
+            for layer in range(self.cfg.num_layers):
+                self._segment_after(layer)
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            body()
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            body()
+        return g
+
     def last_logits(self) -> torch.Tensor:
         return self._logits
 

@@ -568,8 +568,7 @@ def run_ours(args):
         strong = strong_scaling_record(args, dev, world, dist_on)
 
     if rank != 0:
-        if dist_on:
-            dist.destroy_process_group()
+        leave(dist_on)
         return
 
     L, H, B = args.ctx, args.heads, args.budget
@@ -624,8 +623,18 @@ def run_ours(args):
                        f"decode path with cached key codes, ctx {L}, budget {B}, fp32 torch CPU; {sec * 1e3:.1f} ms each"),
         }
     print(json.dumps(line), flush=True)
+    leave(dist_on)
+
+
+def leave(dist_on):
+    """End of a multi-rank run.  The process group is not torn down: CUDA graphs that hold captured
+    collectives are still alive, and destroying the communicator under them has hung; every rank has
+    passed its last collective when it gets here, so the processes simply exit."""
     if dist_on:
-        dist.destroy_process_group()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        torch.cuda.synchronize()
+        os._exit(0)
 
 
 def run_sweep(args):
@@ -773,7 +782,7 @@ def run_seqshard(args):
                                    + ("eager launches" if args.eager else "one CUDA graph per step")
                                    + ", 2 NCCL all-gathers per layer (histograms, partial results)",
                        "tokens_per_gpu": n_local}}), flush=True)
-    dist.destroy_process_group()
+    leave(True)
 
 
 def run_model(args):
@@ -796,7 +805,7 @@ def run_model(args):
     ev[0].record()
     st.prefill(ids)
     ev[1].record()
-    for _ in range(max(3, args.warmup)):       # captures the graphs, warms the kernels
+    for _ in range(max(3, args.warmup)):       # the first token runs eagerly and captures the graph
         st.decode_one()
     out = torch.empty(n_new, dtype=torch.int64, device=dev)
     sampler = ClockSampler(0)
@@ -814,14 +823,11 @@ def run_model(args):
     toks = out.tolist()
     decode_ms = ev[2].elapsed_time(ev[3])
 
-    # the same loop without the attention path: what the dense rest of the model costs
-    def rest_only():
-        st._graphs[0].replay()
-        for layer in range(cfg.num_layers):
-            st._graphs[layer + 1].replay()
+    # the same token without the attention path: what the dense rest of the model costs
+    rest = st.capture_dense_rest()
     for _ in range(3):
-        rest_only()
-    rest_ms = timed(lambda: rest_only(), 20, False, dev) / 20
+        rest.replay()
+    rest_ms = timed(rest.replay, 20, False, dev) / 20
     from adamas_b200 import _lib
     per_tok = decode_ms / n_new
     print(json.dumps({
@@ -839,7 +845,8 @@ def run_model(args):
                                f"random-init {args.dtype} weights, prefill {args.ctx} random ids, decode {n_new} tokens, "
                                f"token budget {args.budget}, page size {args.page_size}, first {cfg.skip_layers} layers dense; "
                                "GEMMs, norms and the dense prefill attention are torch library calls, the decode "
-                               "attention path is this library"}}), flush=True)
+                               "attention path is this library; every token is ONE CUDA graph replay (sequence length "
+                               "in device memory)"}}), flush=True)
 
 
 def main():
