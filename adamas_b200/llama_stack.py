@@ -24,7 +24,9 @@ from typing import List, Optional
 import torch
 import torch.nn.functional as F
 
+from . import _kernels as K
 from . import utils as U
+from .rope import yarn_inv_freq
 
 _DENSE_PAGE_LIMIT = 1 << 24     # "attend to everything" page budget for the first layers
 
@@ -39,6 +41,8 @@ class StackConfig:
     vocab: int = 32000
     rope_scale: float = 8.0       # linear position scaling (adamas/models/Adamas.py:56-61)
     rope_theta: float = 1e4
+    yarn_factor: float = 0.0      # > 0: YaRN frequencies (rope_scale is then unused) ...
+    yarn_original_max_position: int = 4096      # ... stretched from this trained context
     rms_eps: float = 1e-5
     init_std: float = 0.02
     skip_layers: int = 2          # dense first layers (adamas/models/llama.py:538)
@@ -53,6 +57,7 @@ class LlamaStack:
         if not torch.cuda.is_available():
             raise RuntimeError("LlamaStack runs the CUDA decode path; no GPU is visible")
         self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
+        self._yarn = None
         g = torch.Generator(device=self.device).manual_seed(seed)
 
         def w(*shape):
@@ -106,7 +111,7 @@ class LlamaStack:
     def _decode_attention(self, layer: int, q, k, v, out) -> None:
         """The hot path: un-rotated q, k, v [1,H,D] of the new token -> attention output in `out`."""
         U.decode_step(q, k, v, self.controller, layer, out=out, record_indices=False,
-                      rope=(self.cfg.rope_scale, self.cfg.rope_theta))
+                      rope=self._rope())
 
     def _layer_loop(self, seq_len: int, body) -> None:
         """The controller protocol around the layers (adamas/models/llama.py:424-486)."""
@@ -140,7 +145,7 @@ class LlamaStack:
             nonlocal x
             qkv = F.linear(self._norm(x, self.ln1[layer]), self.wqkv[layer]).view(n, 3, cfg.num_heads, cfg.head_dim)
             q, k, v = (qkv[:, i].contiguous() for i in range(3))
-            U.apply_rope_in_place(q, k, past, rope_scale=cfg.rope_scale, rope_theta=cfg.rope_theta)
+            self._rope_prefill(q, k, past)
             U.append_kvh(k, v, None, c, layer)
             attn = F.scaled_dot_product_attention(q.transpose(0, 1).unsqueeze(0), k.transpose(0, 1).unsqueeze(0),
                                                   v.transpose(0, 1).unsqueeze(0), is_causal=True)
@@ -170,7 +175,22 @@ class LlamaStack:
             self._tok.copy_(self._logits.argmax(dim=-1))
 
     def _rope(self):
-        return (self.cfg.rope_scale, self.cfg.rope_theta)
+        """The rotation the step operators take: (scale, theta), or the YaRN table."""
+        cfg = self.cfg
+        if cfg.yarn_factor > 0:
+            if self._yarn is None:
+                inv_freq, mscale = yarn_inv_freq(cfg.yarn_factor, cfg.yarn_original_max_position, cfg.rope_theta,
+                                                 cfg.head_dim)
+                self._yarn = {"inv_freq": inv_freq.to(self.device), "mscale": mscale}
+            return self._yarn
+        return (cfg.rope_scale, cfg.rope_theta)
+
+    def _rope_prefill(self, q, k, past) -> None:
+        r = self._rope()
+        if isinstance(r, dict):
+            K.apply_rope_table_in_place(q, k, past, r["inv_freq"], r["mscale"])
+        else:
+            U.apply_rope_in_place(q, k, past, rope_scale=r[0], rope_theta=r[1])
 
     def _token_body(self, sparse: bool) -> None:
         """One whole token with device-resident lengths: nothing in here depends on the host's view of

@@ -142,6 +142,43 @@ def rope(x: torch.Tensor, past_len: int, rope_scale: float = 1.0, rope_theta: fl
     return (xf * cos + rot * sin).to(x.dtype)
 
 
+def rope_table(x: torch.Tensor, past_len: int, inv_freq: torch.Tensor, mscale: float = 1.0) -> torch.Tensor:
+    """Rotate-half RoPE of x [N, H, D] with one rotation frequency per dimension pair (inv_freq
+    float32 [D/2], any position scaling folded in) and a factor on cos and sin: the form
+    YaRN-scaled models use.  angle = position * inv_freq in float32; result in x.dtype."""
+    n, h, d = x.shape
+    pos = torch.arange(past_len, past_len + n, dtype=torch.float32)
+    freqs = torch.outer(pos, inv_freq.to(torch.float32))
+    emb = torch.cat((freqs, freqs), dim=-1)
+    cos, sin = emb.cos()[:, None, :] * mscale, emb.sin()[:, None, :] * mscale
+    xf = x.to(torch.float32)
+    rot = torch.cat((-xf[..., d // 2:], xf[..., : d // 2]), dim=-1)
+    return (xf * cos + rot * sin).to(x.dtype)
+
+
+def yarn_parameters(factor: float, original_max_position: int, rope_theta: float = 1e4, dim: int = 128,
+                    beta_fast: float = 32.0, beta_slow: float = 1.0):
+    """The published YaRN rule (Peng et al., "YaRN: Efficient Context Window Extension of Large
+    Language Models", sec. 3.2-3.4), restated: per dimension pair i with wavelength
+    2*pi*theta^(2i/d), pairs that complete more than beta_fast rotations over the original
+    context are left alone, pairs with fewer than beta_slow rotations are interpolated (divided by
+    `factor`), a linear ramp over the pair index blends between the two; attention factor
+    0.1 * ln(factor) + 1 multiplies cos and sin.  Returns (inv_freq float32 [dim/2], factor)."""
+    i = np.arange(0, dim, 2, dtype=np.float64)
+    pos_freqs = rope_theta ** (i / dim)
+
+    def pair_index_for(rotations):
+        return dim * math.log(original_max_position / (rotations * 2 * math.pi)) / (2 * math.log(rope_theta))
+
+    low = max(math.floor(pair_index_for(beta_fast)), 0)
+    high = min(math.ceil(pair_index_for(beta_slow)), dim - 1)
+    if low == high:
+        high += 0.001
+    ramp = np.clip((np.arange(dim // 2, dtype=np.float64) - low) / (high - low), 0.0, 1.0)
+    inv_freq = (1.0 / (factor * pos_freqs)) * ramp + (1.0 / pos_freqs) * (1.0 - ramp)
+    return torch.from_numpy(inv_freq.astype(np.float32)), 0.1 * math.log(factor) + 1.0
+
+
 # --------------------------------------------------------------------------
 # stage 2: distance estimate
 # --------------------------------------------------------------------------

@@ -133,17 +133,17 @@ def test_sparse_stack_matches_oracle_layer_by_layer(page_size, budget):
     assert _lib.device_error() == 0
 
 
-@pytest.mark.parametrize("prefill,budget,new_tokens", [(200, 64, 40), (50, 64, 40)])
-def test_whole_token_graph_equals_eager_loop(prefill, budget, new_tokens):
+@pytest.mark.parametrize("prefill,budget,new_tokens,yarn", [(200, 64, 40, 0.0), (50, 64, 40, 0.0), (120, 64, 24, 32.0)])
+def test_whole_token_graph_equals_eager_loop(prefill, budget, new_tokens, yarn):
     """decode_one as ONE graph replay per token (device-resident sequence length) against the eager
     loop over the host-length operators: same sampled tokens, same logits, same caches.  The second
     case starts with every layer dense and crosses the token budget on the way (the graph is
-    re-captured once), both cross several page boundaries."""
+    re-captured once), both cross several page boundaries; the third rotates with a YaRN table."""
     ids = _ids(prefill, seed=2)
     forced = _ids(new_tokens, seed=5).tolist()     # the same input token at every step of both runs
     runs = []
     for use_graphs in (True, False):
-        st = _stack()
+        st = _stack(yarn_factor=yarn, yarn_original_max_position=64)
         st.init_controller(page_size=16, token_budget=budget, max_seq_len=prefill + new_tokens + 16)
         st.prefill(ids)
         toks, logits = [], []

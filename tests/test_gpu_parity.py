@@ -185,6 +185,54 @@ def test_rope_in_place(past_kv_len, seq_len):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("past_kv_len,seq_len", [(0, 69), (4095, 3), (40000, 1), (131071, 1)])
+def test_rope_table_in_place_yarn(dtype, past_kv_len, seq_len):
+    """Per-dimension rotation frequencies and a factor on the rotated values (YaRN), against the
+    oracle's restatement, at the reference's tolerance for its own RoPE operator scaled by the factor."""
+    _, K, U = _mods()
+    from adamas_b200.rope import yarn_inv_freq
+    inv_freq, mscale = yarn_inv_freq(32.0, 4096)
+    q = _randn((seq_len, 32, 128), past_kv_len + seq_len, dtype)
+    k = _randn((seq_len, 8, 128), past_kv_len + seq_len + 1, dtype)
+    qd, kd = q.to(DEV), k.to(DEV)
+    K.apply_rope_table_in_place(qd, kd, past_kv_len, inv_freq.to(DEV), mscale)
+    tol = 5e-3 * (4 if dtype == torch.bfloat16 else 1) * mscale
+    want_inv, want_scale = ref.yarn_parameters(32.0, 4096)
+    torch.testing.assert_close(qd.cpu().float(), ref.rope_table(q, past_kv_len, want_inv, want_scale).float(), rtol=tol, atol=tol)
+    torch.testing.assert_close(kd.cpu().float(), ref.rope_table(k, past_kv_len, want_inv, want_scale).float(), rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_yarn_fused_append_equals_separate_launches(dtype):
+    """The append launch with the frequency table rotates exactly as the stand-alone table operator."""
+    _, K, U = _mods()
+    from adamas_b200.rope import yarn_inv_freq
+    inv_freq, mscale = yarn_inv_freq(32.0, 4096)
+    rope = {"inv_freq": inv_freq.to(DEV), "mscale": mscale}
+    L, H, ps = 9000, 32, 16
+    outs = []
+    for fused in (False, True):
+        st = State(L - 1, H, ps, dtype, seed=4, fused=True, max_seq_len=L + ps)
+        c = st.c
+        c.end_forward()
+        q = _randn((1, H, 128), 71, dtype).to(DEV)
+        k = _randn((1, H, 128), 72, dtype).to(DEV)
+        v = _randn((1, H, 128), 73, dtype).to(DEV)
+        c.prepare_hadamard(1)
+        c.begin_forward(1)
+        if fused:
+            code = U.append_qkv_fused(q, k, v, c, 0, rope=rope)
+        else:
+            K.apply_rope_table_in_place(q, k, L - 1, rope["inv_freq"], mscale)
+            code = U.append_qkv_fused(q, k, v, c, 0)
+        table = c.kv_cache.indicies
+        kv = c.kv_cache.buf_layer(0)[table[-1], :, (L - 1) % ps].clone()
+        outs.append((q.clone(), k.clone(), code.clone(), kv))
+    for a, b in zip(*outs):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_rope_fused_append_equals_separate_launches(dtype):
     """rope + cat + hadamard + append in one launch gives the same bits as the separate operators."""
     _, K, U = _mods()

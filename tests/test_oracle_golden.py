@@ -157,3 +157,26 @@ def test_rope_matches_hf_apply_rotary_pos_emb():
     torch.testing.assert_close(ref.rope(k, past), kh[0].transpose(0, 1), rtol=1e-5, atol=1e-5)
     # position scaling divides the position
     torch.testing.assert_close(ref.rope(q[:1], 16, rope_scale=8.0), ref.rope(q[:1], 2), rtol=1e-5, atol=1e-5)
+
+
+def test_yarn_parameters_match_transformers_and_table_rope_reduces_to_linear():
+    """The YaRN restatement against transformers' own rope initialiser, and rope_table against
+    rope for the table that encodes linear scaling."""
+    from transformers import LlamaConfig
+    from transformers.modeling_rope_utils import ROPE_INIT_FUNCTIONS
+    for factor, orig in [(32.0, 4096), (4.0, 8192), (16.0, 2048)]:
+        cfg = LlamaConfig(hidden_size=4096, num_attention_heads=32, max_position_embeddings=int(orig * factor),
+                          rope_theta=1e4, rope_scaling={"rope_type": "yarn", "factor": factor,
+                                                        "original_max_position_embeddings": orig})
+        inv, att = ROPE_INIT_FUNCTIONS["yarn"](cfg, "cpu")
+        mine, mscale = ref.yarn_parameters(factor, orig)
+        torch.testing.assert_close(mine, inv, rtol=1e-6, atol=1e-9)
+        assert abs(mscale - att) < 1e-12
+        from adamas_b200.rope import yarn_inv_freq
+        pkg, pkg_scale = yarn_inv_freq(factor, orig)
+        torch.testing.assert_close(pkg, inv, rtol=1e-6, atol=1e-9)
+        assert abs(pkg_scale - att) < 1e-12
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(5, 3, 128, generator=g)
+    from adamas_b200.rope import linear_inv_freq
+    torch.testing.assert_close(ref.rope_table(x, 1000, linear_inv_freq(8.0)), ref.rope(x, 1000, 8.0), rtol=1e-6, atol=1e-6)
