@@ -180,6 +180,15 @@ def _check_append(k, v, kv_data, kv_indices, hadamard_data, hadamard_indices, la
     return num_heads, head_dim, page_size
 
 
+def _query_heads(q, k, name: str) -> int:
+    """Query heads of q [1, Hq, D] over the cache heads of k [1, H, D]: Hq a multiple of H (grouped-query
+    attention when larger; the reference supports Hq == H only, kernels/include/decode/decode_handler.cuh:83)."""
+    _require(q.dim() == 3 and q.size(0) == 1 and q.size(2) == k.size(2) and q.dtype == k.dtype
+             and q.size(1) >= k.size(1) and q.size(1) % k.size(1) == 0,
+             f"{name}: q must be [1, Hq, D] in k.dtype with Hq a multiple of the cache's heads")
+    return q.size(1)
+
+
 def append_kv_cache_decode(k, v, h, o, kv_data, kv_indices, kv_indptr, kv_last_page_len, kv_last_page_idx,
                            hadamard_data, hadamard_indices, hadamard_indptr, hadamard_last_page_len,
                            hadamard_last_page_idx, layout, thresholds=None) -> None:
@@ -203,27 +212,31 @@ def append_kv_cache_decode_fused(q, k, v, o, kv_data, kv_indices, kv_last_page_l
                                  hadamard_indices, hadamard_last_page_len, layout=NHD, scale=None,
                                  thresholds=None, rope=None) -> None:
     """One launch for torch.cat((q, k)) + hadamard_transform + append_kv_cache_decode
-    (adamas/models/Adamas.py:145-161).  With rope=(rope_scale, rope_theta) q and k arrive
-    un-rotated and are rotated in place first (also replaces apply_rope_in_place, Adamas.py:113)."""
+    (adamas/models/Adamas.py:145-161).  With rope=(rope_scale, rope_theta), or a frequency table
+    {"inv_freq": tensor[64], "mscale": float}, q and k arrive un-rotated and are rotated in place first
+    (also replaces apply_rope_in_place, Adamas.py:113).  q may have a multiple of k's heads."""
     num_heads, head_dim, page_size = _check_append(k, v, kv_data, kv_indices, hadamard_data, hadamard_indices, layout)
     _check_input(q, "q", 3)
     _check_input(o, "o", 3)
-    _require(tuple(q.shape) == tuple(k.shape) and q.dtype == k.dtype and k.size(0) == 1, "q, k, v must be [1, H, D]")
-    _require(o.size(1) == num_heads and o.size(2) == head_dim // 8 and o.element_size() == 2, "o must be [1, H, D/8] 16-bit")
+    _require(k.size(0) == 1, "k, v must be [1, H, D]")
+    q_heads = _query_heads(q, k, "append_kv_cache_decode_fused")
+    _require(o.size(1) == q_heads and o.size(2) == head_dim // 8 and o.element_size() == 2, "o must be [1, Hq, D/8] 16-bit")
     s = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)
     if rope is not None:
+        rs, rt, inv_freq, mscale = _rope_args(rope)
         _lib.check(lib.adamas_append_decode_rope_fused(
             _ptr(q), _ptr(k), _ptr(v), _ptr(o),
             _ptr(kv_data), _ptr(kv_indices), kv_indices.numel(), int(kv_last_page_len),
             _ptr(hadamard_data), _ptr(hadamard_indices), hadamard_indices.numel(), int(hadamard_last_page_len),
-            num_heads, head_dim, page_size, s, _lib.thresholds_arg(thresholds), float(rope[0]), float(rope[1]),
+            num_heads, q_heads, head_dim, page_size, s, _lib.thresholds_arg(thresholds), rs if inv_freq is None else 1.0,
+            rt if inv_freq is None else 1e4, _ptr(inv_freq), mscale,
             _dtype_code(k.dtype, "append_kv_cache_decode_rope_fused"), _stream()), "append_kv_cache_decode_rope_fused")
         return
     _lib.check(lib.adamas_append_decode_fused(
         _ptr(q), _ptr(k), _ptr(v), _ptr(o),
         _ptr(kv_data), _ptr(kv_indices), kv_indices.numel(), int(kv_last_page_len),
         _ptr(hadamard_data), _ptr(hadamard_indices), hadamard_indices.numel(), int(hadamard_last_page_len),
-        num_heads, head_dim, page_size, s, _lib.thresholds_arg(thresholds),
+        num_heads, q_heads, head_dim, page_size, s, _lib.thresholds_arg(thresholds),
         _dtype_code(k.dtype, "append_kv_cache_decode_fused"), _stream()), "append_kv_cache_decode_fused")
 
 
@@ -264,19 +277,20 @@ def estimate_attn_score(q, o, metadata_data, metadata_indices, metadata_indptr, 
     _check_input(metadata_indices, "hadamard_indices", 1)
     _require(q.size(0) == 1, "q.size(0) must be 1")
     _require(metadata_indices.dtype == torch.int32, "hadamard_indices must be int32")
-    num_heads, code_words = q.size(1), q.size(2)
+    q_heads, code_words = q.size(1), q.size(2)
     page_size = metadata_data.size(2)
-    _require(metadata_data.size(3) == num_heads and metadata_data.size(4) == code_words and code_words == 16,
-             "hadamard_data must be [pages, 1, page_size, num_heads, 16]")
+    num_heads = metadata_data.size(3)          # heads of the cache; q_heads is a multiple of it
+    _require(q_heads >= num_heads and q_heads % num_heads == 0 and metadata_data.size(4) == code_words
+             and code_words == 16, "hadamard_data must be [pages, 1, page_size, num_heads, 16], q [1, Hq, 16]")
     _require(q.element_size() == 2 and metadata_data.element_size() == 2, "codes must be 16-bit words")
     n = (metadata_indices.numel() - 1) * page_size + int(metadata_last_page_len) - (1 if exclude_last else 0)
-    _require(o.size(0) == num_heads and o.size(1) == n, f"o must be [{num_heads}, {n}]")
+    _require(o.size(0) == q_heads and o.size(1) == n, f"o must be [{q_heads}, {n}]")
     _lib.check(lib.adamas_estimate(
         _ptr(q), _ptr(metadata_data), _ptr(metadata_indices), metadata_indices.numel(),
-        int(metadata_last_page_len), page_size, num_heads, code_words * 8, _ptr(o), o.stride(0),
+        int(metadata_last_page_len), page_size, num_heads, q_heads, code_words * 8, _ptr(o), o.stride(0),
         _value_format(o.dtype, "Estimate_attn_score"),
         {"l1": _lib.METRIC_L1, "xor": _lib.METRIC_XOR}[metric], 1 if exclude_last else 0,
-        _ptr(_check_hist(hist, num_heads)), int(hist_slices), _stream()),
+        _ptr(_check_hist(hist, q_heads)), int(hist_slices), _stream()),
         "Estimate_attn_score")
 
 
@@ -357,9 +371,11 @@ class BatchDecodeWithPagedKVCachePyTorchWrapper:
     def begin_forward(self, indptr, num_qo_heads, num_kv_heads, head_dim, page_size, empty_data) -> None:
         _require(indptr.dim() == 1 and indptr.dtype == torch.int32 and indptr.is_contiguous(),
                  "indptr must be a contiguous 1D int32 tensor")
-        _require(num_qo_heads == num_kv_heads, "grouped-query attention is not supported (the reference asserts MHA)")
+        _require(num_qo_heads >= num_kv_heads >= 1 and num_qo_heads % num_kv_heads == 0,
+                 "num_qo_heads must be a multiple of num_kv_heads")
         self._cfg = (int(num_qo_heads), int(head_dim), int(page_size),
                      _dtype_code(empty_data.dtype, "BatchDecodeWithPagedKVCache"))
+        self._kv_heads = int(num_kv_heads)
         self._started = True
         self._planned_tokens = 0   # scratch is sized on the first forward, from the index tensor
 
@@ -389,8 +405,8 @@ class BatchDecodeWithPagedKVCachePyTorchWrapper:
         _require(q.size(0) == 1 and q.size(1) == num_heads and q.size(2) == head_dim, "q must be [1, H, D]")
         _require(o_f32 is not None or (tuple(o.shape) == tuple(q.shape) and o.dtype == q.dtype), "o must match q")
         _require(paged_kv_data.size(1) == 2 and paged_kv_data.size(2) == page_size
-                 and paged_kv_data.size(3) == num_heads and paged_kv_data.size(4) == head_dim,
-                 "paged_kv_data must be [pages, 2, page_size, H, D]")
+                 and paged_kv_data.size(3) == self._kv_heads and paged_kv_data.size(4) == head_dim,
+                 "paged_kv_data must be [pages, 2, page_size, H_kv, D]")
         _require(paged_kv_indices.size(0) == num_heads and paged_kv_indices.dtype == torch.int32,
                  "paged_kv_indices must be int32 [H, n]")
         _require(_dtype_code(q.dtype, "BatchDecodeWithPagedKVCache") == dt and paged_kv_data.dtype == q.dtype,
@@ -402,8 +418,8 @@ class BatchDecodeWithPagedKVCachePyTorchWrapper:
             tail = int(tail_len)
         n_tokens = n_idx * unit + tail
         if n_tokens > self._planned_tokens:
-            _lib.check(lib.adamas_decode_begin_forward(self._handle, n_tokens, num_heads, head_dim, page_size, dt,
-                                                       _stream()), "BatchDecodeWithPagedKVCache")
+            _lib.check(lib.adamas_decode_begin_forward(self._handle, n_tokens, self._kv_heads, num_heads, head_dim,
+                                                       page_size, dt, _stream()), "BatchDecodeWithPagedKVCache")
             self._planned_tokens = n_tokens
         if lse is not None:
             _require(lse.is_cuda and lse.dtype == torch.float32 and lse.numel() == num_heads and lse.is_contiguous(),
@@ -432,25 +448,26 @@ class BatchDecodeWithPagedKVCachePyTorchWrapper:
             raise RuntimeError("BatchDecodeWithPagedKVCache failed with error: dense step called before begin_forward")
         num_heads, head_dim, page_size = _check_append(k, v, kv_data, kv_indices, hadamard_data, hadamard_indices, NHD)
         cfg_heads, cfg_dim, cfg_ps, dt = self._cfg
-        _require((num_heads, head_dim, page_size) == (cfg_heads, cfg_dim, cfg_ps)
-                 and _dtype_code(k.dtype, "dense_step_dev") == dt, "cache geometry differs from begin_forward")
         _check_input(q, "q", 3)
         _check_input(o, "o", 3)
         _check_input(q_code, "q_code", 3)
         _check_seq_len(seq_len)
-        _require(tuple(q.shape) == tuple(k.shape) == tuple(o.shape) and k.size(0) == 1, "q, k, v, o must be [1, H, D]")
+        q_heads = _query_heads(q, k, "dense_step_dev")
+        _require((q_heads, num_heads, head_dim, page_size) == (cfg_heads, self._kv_heads, cfg_dim, cfg_ps)
+                 and _dtype_code(k.dtype, "dense_step_dev") == dt, "cache geometry differs from begin_forward")
+        _require(tuple(q.shape) == tuple(o.shape) and k.size(0) == 1, "q, o must be [1, Hq, D], k, v [1, H, D]")
         _require(kv_indices.numel() * page_size >= max_seq_len, "the page table must have room for max_seq_len tokens")
         if max_seq_len > self._planned_tokens:
-            _lib.check(lib.adamas_decode_begin_forward(self._handle, int(max_seq_len), num_heads, head_dim, page_size,
-                                                       dt, _stream()), "BatchDecodeWithPagedKVCache")
+            _lib.check(lib.adamas_decode_begin_forward(self._handle, int(max_seq_len), num_heads, q_heads, head_dim,
+                                                       page_size, dt, _stream()), "BatchDecodeWithPagedKVCache")
             self._planned_tokens = int(max_seq_len)
         s = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)
         rs, rt, inv_freq, mscale = _rope_args(rope)
         _lib.check(lib.adamas_dense_step_dev(
             self._handle, _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(q_code), _ptr(kv_data),
             _ptr(kv_indices), _ptr(hadamard_data), _ptr(hadamard_indices), _ptr(seq_len), int(max_seq_len),
-            num_heads, head_dim, page_size, dt, s, _lib.thresholds_arg(thresholds), rs, rt, _ptr(inv_freq), mscale,
-            1.0 / math.sqrt(head_dim), _stream()), "dense_step_dev")
+            num_heads, q_heads, head_dim, page_size, dt, s, _lib.thresholds_arg(thresholds), rs, rt, _ptr(inv_freq),
+            mscale, 1.0 / math.sqrt(head_dim), _stream()), "dense_step_dev")
 
 
 def set_max_cluster(blocks: int) -> None:
@@ -497,8 +514,10 @@ def select_attend(dist: torch.Tensor, k: int, q: torch.Tensor, o: Optional[torch
     _require(o is not None or o_f32 is not None, "o or o_f32 must be given")
     _require(o is None or (tuple(o.shape) == tuple(q.shape) and o.dtype == q.dtype), "o must match q")
     page_size = kv_data.size(2)
-    _require(kv_data.size(1) == 2 and kv_data.size(3) == h and kv_data.size(4) == 128 and kv_data.dtype == q.dtype,
-             "kv_data must be [pages, 2, page_size, H, 128] in q.dtype")
+    kv_heads = kv_data.size(3)
+    _require(kv_data.size(1) == 2 and h >= kv_heads >= 1 and h % kv_heads == 0 and kv_data.size(4) == 128
+             and kv_data.dtype == q.dtype,
+             "kv_data must be [pages, 2, page_size, H_kv, 128] in q.dtype, with H a multiple of H_kv")
     _require(kv_indices.dtype == torch.int32 and kv_indices.numel() * page_size >= n, "page table too short")
     out_stride = 0
     if indices_out is not None:
@@ -520,7 +539,7 @@ def select_attend(dist: torch.Tensor, k: int, q: torch.Tensor, o: Optional[torch
         hist = histogram_scratch(h, dist.device)
     _lib.check(lib.adamas_select_attend(
         _ptr(dist), dist.stride(0), n, int(k), _ptr(q), _ptr(o), _ptr(o_f32), _ptr(lse), _ptr(kv_data),
-        _ptr(kv_indices), page_size, h, 128, _dtype_code(q.dtype, "select_attend"), int(last_page_idx),
+        _ptr(kv_indices), page_size, kv_heads, h, 128, _dtype_code(q.dtype, "select_attend"), int(last_page_idx),
         int(last_page_len), _ptr(_check_hist(hist, h)), 1 if hist_ready else 0, _ptr(ext_cut),
         _ptr(indices_out), out_stride, 1.0 / math.sqrt(128.0), _stream()), "select_attend")
 
@@ -533,30 +552,33 @@ def decode_step(q, k, v, o, q_code, kv_data, kv_indices, kv_last_page_len, kv_la
     """One layer's decode step in one call: append + estimate, select + attend (two launches for 16, 32
     or 64 heads and already rotated q/k, else three, for what adamas/models/Adamas.py:145-200 does with
     seven).  Needs context > budget.  `hist`: a histogram_scratch(H), all zero between steps.  With
-    rope=(rope_scale, rope_theta) q and k arrive un-rotated and are rotated in place first."""
+    rope=(rope_scale, rope_theta) or {"inv_freq": tensor[64], "mscale": float} q and k arrive un-rotated
+    and are rotated in place first.  q, o may have a multiple of k's heads (grouped-query attention)."""
     num_heads, head_dim, page_size = _check_append(k, v, kv_data, kv_indices, hadamard_data, hadamard_indices, NHD)
     _check_input(q, "q", 3)
     _check_input(o, "o", 3)
     _check_input(q_code, "q_code", 3)
     _check_rows(dist_scratch, "dist_scratch")
-    _require(tuple(q.shape) == tuple(k.shape) == tuple(o.shape) and k.size(0) == 1, "q, k, v, o must be [1, H, D]")
-    _require(q_code.element_size() == 2 and q_code.numel() == num_heads * head_dim // 8, "q_code must be [1, H, D/8] 16-bit")
-    _require(dist_scratch.element_size() == 2 and dist_scratch.size(0) == num_heads, "dist_scratch must be 16-bit [H, n]")
+    q_heads = _query_heads(q, k, "decode_step")
+    _require(tuple(q.shape) == tuple(o.shape) and k.size(0) == 1, "q, o must be [1, Hq, D], k, v [1, H, D]")
+    _require(q_code.element_size() == 2 and q_code.numel() == q_heads * head_dim // 8, "q_code must be [1, Hq, D/8] 16-bit")
+    _require(dist_scratch.element_size() == 2 and dist_scratch.size(0) == q_heads, "dist_scratch must be 16-bit [Hq, n]")
     out_stride = 0
     if indices_out is not None:
         _check_rows(indices_out, "indices_out")
-        _require(indices_out.dtype == torch.int32 and indices_out.size(0) == num_heads
-                 and indices_out.size(1) >= budget - 1, "indices_out must be int32 [H, >=budget-1]")
+        _require(indices_out.dtype == torch.int32 and indices_out.size(0) == q_heads
+                 and indices_out.size(1) >= budget - 1, "indices_out must be int32 [Hq, >=budget-1]")
         out_stride = indices_out.stride(0)
     s = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)
+    rs, rt, inv_freq, mscale = _rope_args(rope)
     _lib.check(lib.adamas_decode_step(
         _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(q_code),
         _ptr(kv_data), _ptr(kv_indices), kv_indices.numel(), int(kv_last_page_len), int(kv_last_page_idx),
         _ptr(hadamard_data), _ptr(hadamard_indices), hadamard_indices.numel(), int(hadamard_last_page_len),
-        num_heads, head_dim, page_size, _dtype_code(k.dtype, "decode_step"), int(budget),
-        _ptr(dist_scratch), dist_scratch.stride(0), _ptr(_check_hist(hist, num_heads)), _ptr(indices_out), out_stride, s,
-        _lib.thresholds_arg(thresholds), float(rope[0]) if rope is not None else 0.0,
-        float(rope[1]) if rope is not None else 0.0, 1.0 / math.sqrt(head_dim), _stream()), "decode_step")
+        num_heads, q_heads, head_dim, page_size, _dtype_code(k.dtype, "decode_step"), int(budget),
+        _ptr(dist_scratch), dist_scratch.stride(0), _ptr(_check_hist(hist, q_heads)), _ptr(indices_out), out_stride, s,
+        _lib.thresholds_arg(thresholds), rs, rt, _ptr(inv_freq), mscale, 1.0 / math.sqrt(head_dim), _stream()),
+        "decode_step")
 
 
 def _rope_args(rope):
@@ -591,25 +613,26 @@ def decode_step_dev(q, k, v, o, q_code, kv_data, kv_indices, hadamard_data, hada
     _check_input(q_code, "q_code", 3)
     _check_rows(dist_scratch, "dist_scratch")
     _check_seq_len(seq_len)
-    _require(tuple(q.shape) == tuple(k.shape) == tuple(o.shape) and k.size(0) == 1, "q, k, v, o must be [1, H, D]")
-    _require(q_code.element_size() == 2 and q_code.numel() == num_heads * head_dim // 8, "q_code must be [1, H, D/8] 16-bit")
-    _require(dist_scratch.element_size() == 2 and dist_scratch.size(0) == num_heads
-             and dist_scratch.size(1) >= max_seq_len - 1, "dist_scratch must be 16-bit [H, >= max_seq_len - 1]")
+    q_heads = _query_heads(q, k, "decode_step_dev")
+    _require(tuple(q.shape) == tuple(o.shape) and k.size(0) == 1, "q, o must be [1, Hq, D], k, v [1, H, D]")
+    _require(q_code.element_size() == 2 and q_code.numel() == q_heads * head_dim // 8, "q_code must be [1, Hq, D/8] 16-bit")
+    _require(dist_scratch.element_size() == 2 and dist_scratch.size(0) == q_heads
+             and dist_scratch.size(1) >= max_seq_len - 1, "dist_scratch must be 16-bit [Hq, >= max_seq_len - 1]")
     _require(kv_indices.numel() * page_size >= max_seq_len and hadamard_indices.numel() * page_size >= max_seq_len,
              "the page tables must have room for max_seq_len tokens")
     out_stride = 0
     if indices_out is not None:
         _check_rows(indices_out, "indices_out")
-        _require(indices_out.dtype == torch.int32 and indices_out.size(0) == num_heads
-                 and indices_out.size(1) >= budget - 1, "indices_out must be int32 [H, >=budget-1]")
+        _require(indices_out.dtype == torch.int32 and indices_out.size(0) == q_heads
+                 and indices_out.size(1) >= budget - 1, "indices_out must be int32 [Hq, >=budget-1]")
         out_stride = indices_out.stride(0)
     s = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)
     rs, rt, inv_freq, mscale = _rope_args(rope)
     _lib.check(lib.adamas_decode_step_dev(
         _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(q_code), _ptr(kv_data), _ptr(kv_indices),
-        _ptr(hadamard_data), _ptr(hadamard_indices), _ptr(seq_len), int(max_seq_len), num_heads, head_dim,
+        _ptr(hadamard_data), _ptr(hadamard_indices), _ptr(seq_len), int(max_seq_len), num_heads, q_heads, head_dim,
         page_size, _dtype_code(k.dtype, "decode_step_dev"), int(budget), _ptr(dist_scratch),
-        dist_scratch.stride(0), _ptr(_check_hist(hist, num_heads)), _ptr(indices_out), out_stride, s,
+        dist_scratch.stride(0), _ptr(_check_hist(hist, q_heads)), _ptr(indices_out), out_stride, s,
         _lib.thresholds_arg(thresholds), rs, rt, _ptr(inv_freq), mscale, 1.0 / math.sqrt(head_dim), _stream()),
         "decode_step_dev")
 

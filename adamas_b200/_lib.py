@@ -35,26 +35,28 @@ SIGNATURES = {
     "adamas_hadamard_transform": [_P, _P, _L, _I, _F, _I, _P],
     "adamas_bucketize_pack": [_P, _P, _L, _I, _FP, _I, _P],
     "adamas_append_decode": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _FP, _I, _P],
-    "adamas_append_decode_fused": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _FP, _I, _P],
+    "adamas_append_decode_fused": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _FP, _I, _P],
     "adamas_apply_rope_in_place": [_P, _P, _L, _I, _I, _I, _L, _F, _F, _I, _P],
-    "adamas_append_decode_rope_fused": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _FP, _F, _F, _I, _P],
+    "adamas_append_decode_rope_fused": [_P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _FP, _F, _F,
+                                        _P, _F, _I, _P],
     "adamas_append_prefill": [_P, _P, _P, _L, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _FP, _I, _P],
-    "adamas_estimate": [_P, _P, _P, _I, _I, _I, _I, _I, _P, _L, _I, _I, _I, _P, _I, _P],
+    "adamas_estimate": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _L, _I, _I, _I, _P, _I, _P],
     "adamas_topk": [_P, _I, _L, _I, _P, _L, _I, _I, _I, _P, _P, _L, _P],
     "adamas_decode_handler_create": [POINTER(c_void_p)],
     "adamas_decode_handler_destroy": [_P],
-    "adamas_decode_begin_forward": [_P, _L, _I, _I, _I, _I, _P],
+    "adamas_decode_begin_forward": [_P, _L, _I, _I, _I, _I, _I, _P],
     "adamas_decode_end_forward": [_P],
     "adamas_decode_forward": [_P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _P],
     "adamas_decode_forward_partial": [_P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _P],
     "adamas_decode_forward_static": [_P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P],
-    "adamas_select_attend": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P, _L, _F, _P],
+    "adamas_select_attend": [_P, _L, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P, _L, _F,
+                             _P],
     "adamas_select_attend_slices": [_I, _I, _I, POINTER(c_int)],
-    "adamas_decode_step": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I,
-                           _P, _L, _P, _P, _L, _F, _FP, _F, _F, _F, _P],
-    "adamas_decode_step_dev": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
+    "adamas_decode_step": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
+                           _P, _L, _P, _P, _L, _F, _FP, _F, _F, _P, _F, _F, _P],
+    "adamas_decode_step_dev": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
                                _P, _L, _P, _P, _L, _F, _FP, _F, _F, _P, _F, _F, _P],
-    "adamas_dense_step_dev": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I,
+    "adamas_dense_step_dev": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
                               _F, _FP, _F, _F, _P, _F, _F, _P],
     "adamas_seq_len_advance": [_P, _I, _P],
     "adamas_hist_rowsum": [_P, _I, _I, _P, _P],
@@ -83,7 +85,7 @@ lib.adamas_abi_version.restype = c_int
 lib.adamas_last_error.argtypes = []
 lib.adamas_last_error.restype = c_char_p
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 HIST_WORDS_PER_HEAD = 16 * 512 + 16 * 132
 if lib.adamas_abi_version() != ABI_VERSION:
     raise ImportError(f"{LIB_PATH} has ABI version {lib.adamas_abi_version()}, expected {ABI_VERSION}; rebuild it")

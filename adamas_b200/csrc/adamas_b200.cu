@@ -72,6 +72,15 @@ int check_common(int num_heads, int head_dim, int page_size, int dtype) {
   return ADAMAS_OK;
 }
 
+// Grouped-query attention: num_q_heads query heads over num_heads cache heads, query head r reads cache
+// head r / (num_q_heads / num_heads).  num_q_heads == num_heads is multi-head attention, all the
+// reference knows (kernels/include/decode/decode_handler.cuh:83 asserts it).
+int check_q_heads(int num_heads, int num_q_heads) {
+  ADAMAS_REQUIRE(num_q_heads >= num_heads && num_q_heads <= 1024 && num_q_heads % num_heads == 0,
+                 "num_q_heads (%d) must be a multiple of num_heads (%d)", num_q_heads, num_heads);
+  return ADAMAS_OK;
+}
+
 constexpr int kEstAppendStatic = 1280;   // static shared memory of estimate_append_kernel, rounded up
 constexpr int kEstPagesStatic = 8448;    // static shared memory of estimate_pages_kernel, rounded up
 constexpr int kSaMaxDynSmem = 160 * 1024;   // dynamic shared memory select_attend may ask for (a long winner list)
@@ -377,8 +386,11 @@ static int append_decode_impl(const void* k, const void* v, const void* qh, cons
                               int code_last_page_len, int num_heads, int head_dim, int page_size,
                               float scale, const float* thresholds3_host, int dtype,
                               adamas_stream_t stream, const RopeSpec& rope = RopeSpec(),
-                              const int32_t* seq_len_dev = nullptr) {
+                              const int32_t* seq_len_dev = nullptr, int q_heads = 0) {
   if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
+  if (q_heads == 0) q_heads = num_heads;
+  if (int rc = check_q_heads(num_heads, q_heads)) return rc;
+  ADAMAS_REQUIRE(q_heads == num_heads || fused, "grouped-query attention needs the fused append (q, k, v)");
   ADAMAS_REQUIRE(k && v && qh && kh && q_code_out && kv_data && code_data && kv_page_table &&
                      code_page_table, "null pointer");
   ADAMAS_REQUIRE(!rope.on || rope.inv_freq || (rope.scale > 0.f && rope.theta > 0.f),
@@ -393,7 +405,7 @@ static int append_decode_impl(const void* k, const void* v, const void* qh, cons
   PagedTarget tgt{kv_data, kv_page_table, static_cast<uint16_t*>(code_data), code_page_table, page_size,
                   num_heads};
   const Thresholds th = make_thresholds(thresholds3_host);
-  const unsigned blocks = rows_to_blocks(num_heads);
+  const unsigned blocks = rows_to_blocks(q_heads);
   cudaStream_t st = to_stream(stream);
   {
     const DeviceInfo* di = nullptr;
@@ -407,7 +419,7 @@ static int append_decode_impl(const void* k, const void* v, const void* qh, cons
                 st, 1, static_cast<const T*>(k), static_cast<const T*>(v), static_cast<const T*>(qh), \
                 static_cast<const T*>(kh), static_cast<uint16_t*>(q_code_out), tgt, kv_num_pages - 1, \
                 kv_last_page_len - 1, code_num_pages - 1, code_last_page_len - 1, scale, th, pos, rp, \
-                seq_len_dev)
+                seq_len_dev, q_heads)
   if (dtype == ADAMAS_F16) {
     if (rope.on) LAUNCH_AD(__half, true, true);
     else if (fused) LAUNCH_AD(__half, true, false);
@@ -439,25 +451,31 @@ int adamas_append_decode_fused(const void* q, const void* k, const void* v, void
                                void* kv_data, const int32_t* kv_page_table, int kv_num_pages,
                                int kv_last_page_len, void* code_data,
                                const int32_t* code_page_table, int code_num_pages,
-                               int code_last_page_len, int num_heads, int head_dim, int page_size,
-                               float scale, const float* thresholds3_host, int dtype,
+                               int code_last_page_len, int num_heads, int num_q_heads, int head_dim,
+                               int page_size, float scale, const float* thresholds3_host, int dtype,
                                adamas_stream_t stream) {
   return append_decode_impl(k, v, q, k, true, q_code_out, kv_data, kv_page_table, kv_num_pages,
                             kv_last_page_len, code_data, code_page_table, code_num_pages,
                             code_last_page_len, num_heads, head_dim, page_size, scale,
-                            thresholds3_host, dtype, stream);
+                            thresholds3_host, dtype, stream, RopeSpec(), nullptr, num_q_heads);
 }
 
 int adamas_append_decode_rope_fused(void* q, void* k, const void* v, void* q_code_out, void* kv_data,
                                     const int32_t* kv_page_table, int kv_num_pages, int kv_last_page_len,
                                     void* code_data, const int32_t* code_page_table, int code_num_pages,
-                                    int code_last_page_len, int num_heads, int head_dim, int page_size,
-                                    float scale, const float* thresholds3_host, float rope_scale,
-                                    float rope_theta, int dtype, adamas_stream_t stream) {
+                                    int code_last_page_len, int num_heads, int num_q_heads, int head_dim,
+                                    int page_size, float scale, const float* thresholds3_host, float rope_scale,
+                                    float rope_theta, const float* rope_inv_freq, float rope_mscale, int dtype,
+                                    adamas_stream_t stream) {
+  RopeSpec rope = linear_rope(rope_scale, rope_theta);
+  if (rope_inv_freq) {
+    rope.inv_freq = rope_inv_freq;
+    rope.mscale = rope_mscale;
+  }
   return append_decode_impl(k, v, q, k, true, q_code_out, kv_data, kv_page_table, kv_num_pages,
                             kv_last_page_len, code_data, code_page_table, code_num_pages,
                             code_last_page_len, num_heads, head_dim, page_size, scale,
-                            thresholds3_host, dtype, stream, linear_rope(rope_scale, rope_theta));
+                            thresholds3_host, dtype, stream, rope, nullptr, num_q_heads);
 }
 
 int adamas_apply_rope_in_place(void* q, void* k, int64_t seq_len, int num_q_heads, int num_kv_heads,
@@ -530,9 +548,12 @@ int adamas_append_prefill(const void* k, const void* v, const void* h, int64_t n
 // ---------------------------------------------------------------------------------------------
 // n: distances per head (host mode), or their upper bound when seq_len_dev gives the length on the
 // device (the grid is then sized for n and each block derives its share from the device value).
+// num_heads: heads of the code cache; q_heads: rows of q_code / out / hist (a multiple of num_heads).
 static int estimate_impl(const void* q_code, const void* code_data, const int32_t* code_page_table, int n,
-                         int page_size, int num_heads, void* out, int64_t out_stride, int out_format, int metric,
-                         const int32_t* seq_len_dev, uint32_t* hist, int hist_cl, adamas_stream_t stream) {
+                         int page_size, int num_heads, int q_heads, void* out, int64_t out_stride, int out_format,
+                         int metric, const int32_t* seq_len_dev, uint32_t* hist, int hist_cl, adamas_stream_t stream) {
+  if (int rc = check_q_heads(num_heads, q_heads)) return rc;
+  const int q_group = q_heads / num_heads;
   ADAMAS_REQUIRE(q_code && code_data && code_page_table && out, "null pointer");
   ADAMAS_REQUIRE(out_stride >= n, "out_stride (%lld) smaller than the row length (%d)",
                  static_cast<long long>(out_stride), n);
@@ -543,7 +564,7 @@ static int estimate_impl(const void* q_code, const void* code_data, const int32_
   const DeviceInfo* di = nullptr;
   if (int rc = get_device_info(&di)) return rc;
   cudaStream_t st = to_stream(stream);
-  if (num_heads <= 16 && 32 % (2 * num_heads) == 0 && page_size * num_heads * 32 >= 512) {
+  if (q_group == 1 && num_heads <= 16 && 32 % (2 * num_heads) == 0 && page_size * num_heads * 32 >= 512) {
     // few heads (a head-sharded model): whole pages per copy, one chunk per lane
     const int page_bytes = page_size * num_heads * 32;
     const int ppt = std::max(1, std::min(32, 32768 / page_bytes));
@@ -582,15 +603,15 @@ static int estimate_impl(const void* q_code, const void* code_data, const int32_
     return check_launch("estimate_pages_kernel");
   }
   const int hpw = (num_heads % kEstConsumerWarps == 0) ? num_heads / kEstConsumerWarps : 0;
-  const bool in_regs = hpw == 1 || hpw == 2 || hpw == 4;
+  const bool in_regs = q_group == 1 && (hpw == 1 || hpw == 2 || hpw == 4);   // grouped queries: the generic kernel
   // fewer than 16 heads: a tile holds 32 / H groups of 32 tokens, so that all 16 consumer warps work,
   // each on one head of two token groups
-  const int groups = (num_heads < kEstConsumerWarps && kEstConsumerWarps % num_heads == 0)
+  const int groups = (q_group == 1 && num_heads < kEstConsumerWarps && kEstConsumerWarps % num_heads == 0)
                          ? 2 * kEstConsumerWarps / num_heads : 1;
   const int tile_span = kEstTile * groups;
   const int num_tiles = (n + tile_span - 1) / tile_span;
   const size_t smem = static_cast<size_t>(kEstStages) * tile_span * (2 * num_heads + 1) * 16 +
-                      (in_regs ? 0 : static_cast<size_t>(2 * num_heads) * sizeof(QPlanes));
+                      (in_regs ? 0 : static_cast<size_t>(2 * q_heads) * sizeof(QPlanes));
   ADAMAS_REQUIRE(smem <= static_cast<size_t>(di->max_smem_optin - 1024),
                  "num_heads (%d) too large for the estimate kernel", num_heads);
   const int per_sm = std::min(est_blocks_per_sm(), (smem + 1024) * 2 <= static_cast<size_t>(di->max_smem_optin) ? 2 : 1);
@@ -603,6 +624,7 @@ static int estimate_impl(const void* q_code, const void* code_data, const int32_
   prm.out_stride = out_stride;
   prm.n_tokens = n;
   prm.H = num_heads;
+  prm.q_group = q_group;
   prm.page_size = page_size;
   prm.ps_shift = log2_exact(page_size);
   prm.groups = groups;
@@ -632,7 +654,7 @@ static int estimate_impl(const void* q_code, const void* code_data, const int32_
 
 int adamas_estimate(const void* q_code, const void* code_data, const int32_t* code_page_table,
                     int code_num_pages, int code_last_page_len, int page_size, int num_heads,
-                    int head_dim, void* out, int64_t out_stride, int out_format, int metric,
+                    int num_q_heads, int head_dim, void* out, int64_t out_stride, int out_format, int metric,
                     int exclude_last, uint32_t* hist, int hist_slices, adamas_stream_t stream) {
   if (int rc = check_common(num_heads, head_dim, page_size, ADAMAS_F16)) return rc;
   ADAMAS_REQUIRE(code_num_pages >= 1, "page table must not be empty");
@@ -646,8 +668,8 @@ int adamas_estimate(const void* q_code, const void* code_data, const int32_t* co
       static_cast<int64_t>(code_num_pages - 1) * page_size + code_last_page_len - exclude_last;
   ADAMAS_REQUIRE(n64 < (int64_t(1) << 31) - kEstTile * kEstConsumerWarps * 2, "sequence too long");
   if (n64 == 0) return ADAMAS_OK;
-  return estimate_impl(q_code, code_data, code_page_table, static_cast<int>(n64), page_size, num_heads, out,
-                       out_stride, out_format, metric, nullptr, hist, hist_slices, stream);
+  return estimate_impl(q_code, code_data, code_page_table, static_cast<int>(n64), page_size, num_heads, num_q_heads,
+                       out, out_stride, out_format, metric, nullptr, hist, hist_slices, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -766,7 +788,8 @@ struct adamas_decode_handler {
   int num_sms = 0;
   int device = -1;
   bool forward_started = false;
-  int num_heads = 0, page_size = 0, dtype = 0;
+  int num_heads = 0, page_size = 0, dtype = 0;   // num_heads: query heads (rows of q, o and the index lists)
+  int kv_heads = 0;                              // heads of the KV cache (num_heads / kv_heads query heads share one)
 };
 
 namespace {
@@ -821,9 +844,12 @@ int adamas_decode_handler_destroy(adamas_decode_handler_t* handler) {
 }
 
 int adamas_decode_begin_forward(adamas_decode_handler_t* handler, int64_t max_tokens, int num_heads,
-                                int head_dim, int page_size, int dtype, adamas_stream_t stream) {
+                                int num_q_heads, int head_dim, int page_size, int dtype, adamas_stream_t stream) {
   ADAMAS_REQUIRE(handler, "null handler");
   if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
+  if (int rc = check_q_heads(num_heads, num_q_heads)) return rc;
+  const int kv_heads = num_heads;
+  num_heads = num_q_heads;   // from here on: the rows of the launch
   ADAMAS_REQUIRE(max_tokens >= 1 && max_tokens < (int64_t(1) << 31) - kDecTile, "max_tokens out of range");
   int dev = 0;
   ADAMAS_CUDA(cudaGetDevice(&dev));
@@ -859,6 +885,7 @@ int adamas_decode_begin_forward(adamas_decode_handler_t* handler, int64_t max_to
   }
   handler->forward_started = true;
   handler->num_heads = num_heads;
+  handler->kv_heads = kv_heads;
   handler->page_size = page_size;
   handler->dtype = dtype;
   return ADAMAS_OK;
@@ -912,7 +939,8 @@ static int decode_forward_impl(adamas_decode_handler_t* handler, const void* q, 
   prm.n_idx = n_idx;
   prm.idx_unit = idx_unit;
   prm.page_size = ps;
-  prm.H = H;
+  prm.H = handler->kv_heads;
+  prm.q_group = H / handler->kv_heads;
   const int64_t tail0 = static_cast<int64_t>(last_page_idx) * ps + (last_page_len - tail_len);
   ADAMAS_REQUIRE(tail0 + tail_len < (int64_t(1) << 31), "token slots must be below 2^31");
   prm.tail_slot0 = static_cast<unsigned>(tail0);
@@ -1032,6 +1060,7 @@ int adamas_decode_forward_static(const void* q, void* o, float* lse, const void*
   prm.idx_unit = idx_unit;
   prm.page_size = page_size;
   prm.H = num_heads;
+  prm.q_group = 1;
   const int64_t tail0 = static_cast<int64_t>(last_page_idx) * page_size + (last_page_len - tail_len);
   ADAMAS_REQUIRE(tail0 + tail_len < (int64_t(1) << 31), "token slots must be below 2^31");
   prm.tail_slot0 = static_cast<unsigned>(tail0);
@@ -1133,9 +1162,10 @@ int sa_plan(int n, int k, int num_heads, const DeviceInfo* di, SaPlan* pl) {
 }
 
 // n: distances per head, or their upper bound when seq_len_dev is given.
+// num_heads: heads of the KV cache; q_heads: rows of the launch (a multiple of num_heads).
 int select_attend_impl(const void* dist, int64_t dist_stride, int n, int k, const void* q, void* o, float* o_f32,
                        float* lse, const void* kv_data, const int32_t* kv_page_table, int page_size, int num_heads,
-                       int dtype, int tail_mode, unsigned tail_slot, uint32_t* hist, const int32_t* ext_cut,
+                       int q_heads, int dtype, int tail_mode, unsigned tail_slot, uint32_t* hist, const int32_t* ext_cut,
                        const int32_t* seq_len_dev, int32_t* out_idx, int64_t out_stride, float sm_scale,
                        const SaPlan& pl, adamas_stream_t stream) {
   SelectAttendParams prm;
@@ -1155,6 +1185,7 @@ int select_attend_impl(const void* dist, int64_t dist_stride, int n, int k, cons
   prm.page_size = page_size;
   prm.ps_shift = log2_exact(page_size);
   prm.H = num_heads;
+  prm.q_group = q_heads / num_heads;
   prm.tail_mode = tail_mode;
   prm.tail_slot = tail_slot;
   prm.out_idx = out_idx;
@@ -1162,8 +1193,8 @@ int select_attend_impl(const void* dist, int64_t dist_stride, int n, int k, cons
   prm.list_capacity = pl.list_capacity;
   prm.scale_log2 = sm_scale * 1.4426950408889634f;
   if (dtype == ADAMAS_F16)
-    return launch_select_attend<__half>(prm, pl.items, pl.cl, num_heads, pl.smem, to_stream(stream));
-  return launch_select_attend<__nv_bfloat16>(prm, pl.items, pl.cl, num_heads, pl.smem, to_stream(stream));
+    return launch_select_attend<__half>(prm, pl.items, pl.cl, q_heads, pl.smem, to_stream(stream));
+  return launch_select_attend<__nv_bfloat16>(prm, pl.items, pl.cl, q_heads, pl.smem, to_stream(stream));
 }
 
 static_assert(ADAMAS_HIST_WORDS_PER_HEAD == kSaScratchWordsPerHead, "scratch layout of select_attend");
@@ -1190,10 +1221,14 @@ int adamas_select_attend_slices(int n, int k, int num_heads, int* slices) {
 
 int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, const void* q, void* o,
                          float* o_f32, float* lse, const void* kv_data, const int32_t* kv_page_table,
-                         int page_size, int num_heads, int head_dim, int dtype, int last_page_idx,
-                         int last_page_len, uint32_t* hist, int hist_ready, const int32_t* ext_cut,
-                         int32_t* out_idx, int64_t out_stride, float sm_scale, adamas_stream_t stream) {
+                         int page_size, int num_heads, int num_q_heads, int head_dim, int dtype,
+                         int last_page_idx, int last_page_len, uint32_t* hist, int hist_ready,
+                         const int32_t* ext_cut, int32_t* out_idx, int64_t out_stride, float sm_scale,
+                         adamas_stream_t stream) {
   if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
+  if (int rc = check_q_heads(num_heads, num_q_heads)) return rc;
+  const int kv_heads = num_heads;
+  num_heads = num_q_heads;   // rows of dist, q, o, hist, out_idx
   ADAMAS_REQUIRE(dist && q && (o || o_f32) && kv_data && kv_page_table && hist, "null pointer");
   ADAMAS_REQUIRE(!o_f32 || lse, "a partial result (o_f32) needs lse");
   ADAMAS_REQUIRE(n >= 1 && k >= 1 && k <= n, "need 1 <= k <= n (k=%d, n=%d)", k, n);
@@ -1220,8 +1255,8 @@ int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, co
     ADAMAS_LAUNCH("dist_histogram_kernel", dist_histogram_kernel, dim3(pl.cl, num_heads), dim3(kSaThreads), 0,
                   to_stream(stream), 1, hp);
   }
-  return select_attend_impl(dist, dist_stride, n, k, q, o, o_f32, lse, kv_data, kv_page_table, page_size, num_heads,
-                            dtype, last_page_len > 0 ? 1 : 0, static_cast<unsigned>(std::max<int64_t>(tail, 0)), hist,
+  return select_attend_impl(dist, dist_stride, n, k, q, o, o_f32, lse, kv_data, kv_page_table, page_size, kv_heads,
+                            num_heads, dtype, last_page_len > 0 ? 1 : 0, static_cast<unsigned>(std::max<int64_t>(tail, 0)), hist,
                             ext_cut, nullptr, out_idx, out_stride, sm_scale, pl, stream);
 }
 
@@ -1287,6 +1322,7 @@ static int estimate_append_launch(const void* q, const void* k, const void* v, v
   prm.out_stride = dist_stride;
   prm.n_tokens = n;
   prm.H = num_heads;
+  prm.q_group = 1;
   prm.page_size = page_size;
   prm.ps_shift = log2_exact(page_size);
   prm.groups = 1;
@@ -1352,11 +1388,13 @@ int adamas_append_estimate(const void* q, const void* k, const void* v, void* q_
 static int decode_step_impl(void* q, void* k, const void* v, void* o, float* lse, void* q_code, void* kv_data,
                             const int32_t* kv_page_table, int kv_last_page_idx, void* code_data,
                             const int32_t* code_page_table, int64_t seq_len, const int32_t* seq_len_dev,
-                            int num_heads, int head_dim, int page_size, int dtype, int budget, void* dist_scratch,
+                            int num_heads, int q_heads, int head_dim, int page_size, int dtype, int budget,
+                            void* dist_scratch,
                             int64_t dist_stride, uint32_t* hist, int32_t* out_idx, int64_t out_stride,
                             float hadamard_scale, const float* thresholds3_host, const RopeSpec& rope,
                             float sm_scale, adamas_stream_t stream) {
   if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
+  if (int rc = check_q_heads(num_heads, q_heads)) return rc;
   ADAMAS_REQUIRE(kv_page_table && code_page_table, "page table missing");
   ADAMAS_REQUIRE(budget >= 2 && seq_len > budget,
                  "a decode step needs budget >= 2 and a context longer than the budget (%lld vs %d); "
@@ -1366,18 +1404,18 @@ static int decode_step_impl(void* q, void* k, const void* v, void* o, float* lse
   ADAMAS_REQUIRE(q && o && dist_scratch && q_code && hist, "null pointer");
   ADAMAS_REQUIRE((reinterpret_cast<uintptr_t>(dist_scratch) & 15) == 0 && (dist_stride * 2) % 16 == 0,
                  "distance rows must start on 16-byte boundaries");
-  ADAMAS_REQUIRE(out_idx == nullptr || out_stride >= budget - 1 || num_heads == 1, "out_stride smaller than budget - 1");
+  ADAMAS_REQUIRE(out_idx == nullptr || out_stride >= budget - 1 || q_heads == 1, "out_stride smaller than budget - 1");
   const int n = static_cast<int>(seq_len - 1);
   const int pages = static_cast<int>((seq_len + page_size - 1) / page_size);
   const int last_len = static_cast<int>(seq_len - static_cast<int64_t>(pages - 1) * page_size);
   const DeviceInfo* di = nullptr;
   if (int rc = get_device_info(&di)) return rc;
   SaPlan pl;
-  if (int rc = sa_plan(n, budget - 1, num_heads, di, &pl)) return rc;
+  if (int rc = sa_plan(n, budget - 1, q_heads, di, &pl)) return rc;
   int rc;
   // (16 heads: the page-copy estimate after a separate append is faster than the fused kernel's 512-byte
   // copies per token)
-  if (fused_append_enabled() && !rope.on && (num_heads == 32 || num_heads == 64)) {
+  if (fused_append_enabled() && !rope.on && q_heads == num_heads && (num_heads == 32 || num_heads == 64)) {
     // two launches: the estimate with the append inside, then select + attend.  Not with RoPE: every
     // block of the estimate would repeat the rotation, which costs more than the append launch.
     rc = estimate_append_launch(q, k, v, q_code, kv_data, kv_page_table, pages, last_len, code_data,
@@ -1387,44 +1425,21 @@ static int decode_step_impl(void* q, void* k, const void* v, void* o, float* lse
   } else {
     rc = append_decode_impl(k, v, q, k, true, q_code, kv_data, kv_page_table, pages, last_len, code_data,
                             code_page_table, pages, last_len, num_heads, head_dim, page_size, hadamard_scale,
-                            thresholds3_host, dtype, stream, rope, seq_len_dev);
+                            thresholds3_host, dtype, stream, rope, seq_len_dev, q_heads);
     if (rc) return rc;
-    rc = estimate_impl(q_code, code_data, code_page_table, n, page_size, num_heads, dist_scratch, dist_stride,
-                       ADAMAS_VAL_U16, ADAMAS_METRIC_L1, seq_len_dev, hist, pl.cl, stream);
+    rc = estimate_impl(q_code, code_data, code_page_table, n, page_size, num_heads, q_heads, dist_scratch,
+                       dist_stride, ADAMAS_VAL_U16, ADAMAS_METRIC_L1, seq_len_dev, hist, pl.cl, stream);
     if (rc) return rc;
   }
   const int64_t tail = static_cast<int64_t>(kv_last_page_idx) * page_size + last_len - 1;
   rc = select_attend_impl(dist_scratch, dist_stride, n, budget - 1, q, o, nullptr, lse, kv_data, kv_page_table,
-                          page_size, num_heads, dtype, seq_len_dev ? 2 : 1, static_cast<unsigned>(tail), hist, nullptr,
+                          page_size, num_heads, q_heads, dtype, seq_len_dev ? 2 : 1, static_cast<unsigned>(tail), hist, nullptr,
                           seq_len_dev, out_idx, out_stride, sm_scale, pl, stream);
   if (rc) {
     // the estimate has filled the histogram table and nothing will clear it: restore the all-zero state
-    cudaMemsetAsync(hist, 0, hist_bytes(num_heads), to_stream(stream));
+    cudaMemsetAsync(hist, 0, hist_bytes(q_heads), to_stream(stream));
   }
   return rc;
-}
-
-int adamas_decode_step(void* q, void* k, const void* v, void* o, float* lse, void* q_code,
-                       void* kv_data, const int32_t* kv_page_table, int kv_num_pages,
-                       int kv_last_page_len, int kv_last_page_idx, void* code_data,
-                       const int32_t* code_page_table, int code_num_pages, int code_last_page_len,
-                       int num_heads, int head_dim, int page_size, int dtype, int budget,
-                       void* dist_scratch, int64_t dist_stride, uint32_t* hist_scratch, int32_t* out_idx,
-                       int64_t out_stride, float hadamard_scale, const float* thresholds3_host,
-                       float rope_scale, float rope_theta, float sm_scale, adamas_stream_t stream) {
-  ADAMAS_REQUIRE(kv_num_pages >= 1 && code_num_pages >= 1, "page tables must not be empty");
-  ADAMAS_REQUIRE(page_size >= 1, "page_size must be >= 1");
-  ADAMAS_REQUIRE(kv_last_page_len >= 1 && kv_last_page_len <= page_size, "kv_last_page_len out of range");
-  ADAMAS_REQUIRE(kv_num_pages == code_num_pages && kv_last_page_len == code_last_page_len,
-                 "the KV cache and the code cache must hold the same number of tokens");
-  ADAMAS_REQUIRE(kv_last_page_idx >= 0, "kv_last_page_idx must be >= 0");
-  const int64_t seq_len = static_cast<int64_t>(kv_num_pages - 1) * page_size + kv_last_page_len;
-  RopeSpec rope;
-  if (rope_scale > 0.f) rope = linear_rope(rope_scale, rope_theta);
-  return decode_step_impl(q, k, v, o, lse, q_code, kv_data, kv_page_table, kv_last_page_idx, code_data,
-                          code_page_table, seq_len, nullptr, num_heads, head_dim, page_size, dtype, budget,
-                          dist_scratch, dist_stride, hist_scratch, out_idx, out_stride, hadamard_scale,
-                          thresholds3_host, rope, sm_scale, stream);
 }
 
 static RopeSpec rope_from_args(float rope_scale, float rope_theta, const float* rope_inv_freq, float rope_mscale) {
@@ -1439,10 +1454,33 @@ static RopeSpec rope_from_args(float rope_scale, float rope_theta, const float* 
   return rope;
 }
 
+int adamas_decode_step(void* q, void* k, const void* v, void* o, float* lse, void* q_code,
+                       void* kv_data, const int32_t* kv_page_table, int kv_num_pages,
+                       int kv_last_page_len, int kv_last_page_idx, void* code_data,
+                       const int32_t* code_page_table, int code_num_pages, int code_last_page_len,
+                       int num_heads, int num_q_heads, int head_dim, int page_size, int dtype, int budget,
+                       void* dist_scratch, int64_t dist_stride, uint32_t* hist_scratch, int32_t* out_idx,
+                       int64_t out_stride, float hadamard_scale, const float* thresholds3_host,
+                       float rope_scale, float rope_theta, const float* rope_inv_freq, float rope_mscale,
+                       float sm_scale, adamas_stream_t stream) {
+  ADAMAS_REQUIRE(kv_num_pages >= 1 && code_num_pages >= 1, "page tables must not be empty");
+  ADAMAS_REQUIRE(page_size >= 1, "page_size must be >= 1");
+  ADAMAS_REQUIRE(kv_last_page_len >= 1 && kv_last_page_len <= page_size, "kv_last_page_len out of range");
+  ADAMAS_REQUIRE(kv_num_pages == code_num_pages && kv_last_page_len == code_last_page_len,
+                 "the KV cache and the code cache must hold the same number of tokens");
+  ADAMAS_REQUIRE(kv_last_page_idx >= 0, "kv_last_page_idx must be >= 0");
+  const int64_t seq_len = static_cast<int64_t>(kv_num_pages - 1) * page_size + kv_last_page_len;
+  const RopeSpec rope = rope_from_args(rope_scale, rope_theta, rope_inv_freq, rope_mscale);
+  return decode_step_impl(q, k, v, o, lse, q_code, kv_data, kv_page_table, kv_last_page_idx, code_data,
+                          code_page_table, seq_len, nullptr, num_heads, num_q_heads, head_dim, page_size, dtype, budget,
+                          dist_scratch, dist_stride, hist_scratch, out_idx, out_stride, hadamard_scale,
+                          thresholds3_host, rope, sm_scale, stream);
+}
+
 int adamas_decode_step_dev(void* q, void* k, const void* v, void* o, float* lse, void* q_code, void* kv_data,
                            const int32_t* kv_page_table, void* code_data, const int32_t* code_page_table,
-                           const int32_t* seq_len_dev, int max_seq_len, int num_heads, int head_dim,
-                           int page_size, int dtype, int budget, void* dist_scratch, int64_t dist_stride,
+                           const int32_t* seq_len_dev, int max_seq_len, int num_heads, int num_q_heads,
+                           int head_dim, int page_size, int dtype, int budget, void* dist_scratch, int64_t dist_stride,
                            uint32_t* hist_scratch, int32_t* out_idx, int64_t out_stride, float hadamard_scale,
                            const float* thresholds3_host, float rope_scale, float rope_theta,
                            const float* rope_inv_freq, float rope_mscale, float sm_scale,
@@ -1450,7 +1488,7 @@ int adamas_decode_step_dev(void* q, void* k, const void* v, void* o, float* lse,
   ADAMAS_REQUIRE(seq_len_dev, "null pointer");
   ADAMAS_REQUIRE(page_size >= 1 && max_seq_len >= 1, "page_size and max_seq_len must be >= 1");
   return decode_step_impl(q, k, v, o, lse, q_code, kv_data, kv_page_table, 0, code_data, code_page_table,
-                          max_seq_len, seq_len_dev, num_heads, head_dim, page_size, dtype, budget, dist_scratch,
+                          max_seq_len, seq_len_dev, num_heads, num_q_heads, head_dim, page_size, dtype, budget, dist_scratch,
                           dist_stride, hist_scratch, out_idx, out_stride, hadamard_scale, thresholds3_host,
                           rope_from_args(rope_scale, rope_theta, rope_inv_freq, rope_mscale), sm_scale, stream);
 }
@@ -1458,8 +1496,8 @@ int adamas_decode_step_dev(void* q, void* k, const void* v, void* o, float* lse,
 int adamas_dense_step_dev(adamas_decode_handler_t* handler, void* q, void* k, const void* v, void* o, float* lse,
                           void* q_code, void* kv_data, const int32_t* kv_page_table, void* code_data,
                           const int32_t* code_page_table, const int32_t* seq_len_dev, int max_seq_len,
-                          int num_heads, int head_dim, int page_size, int dtype, float hadamard_scale,
-                          const float* thresholds3_host, float rope_scale, float rope_theta,
+                          int num_heads, int num_q_heads, int head_dim, int page_size, int dtype,
+                          float hadamard_scale, const float* thresholds3_host, float rope_scale, float rope_theta,
                           const float* rope_inv_freq, float rope_mscale, float sm_scale,
                           adamas_stream_t stream) {
   ADAMAS_REQUIRE(handler && seq_len_dev, "null pointer");
@@ -1468,14 +1506,16 @@ int adamas_dense_step_dev(adamas_decode_handler_t* handler, void* q, void* k, co
   ADAMAS_REQUIRE(q && k && v && o && q_code, "null pointer");
   if (!handler->forward_started)
     return fail(ADAMAS_ERR_STATE, "dense step called before begin_forward");
-  ADAMAS_REQUIRE(handler->num_heads == num_heads && handler->page_size == page_size && handler->dtype == dtype,
+  ADAMAS_REQUIRE(handler->kv_heads == num_heads && handler->num_heads == num_q_heads &&
+                     handler->page_size == page_size && handler->dtype == dtype,
                  "the handler was planned for another cache geometry");
   const int pages = (max_seq_len + page_size - 1) / page_size;
   const int last_len = max_seq_len - (pages - 1) * page_size;
   if (int rc = append_decode_impl(k, v, q, k, true, q_code, kv_data, kv_page_table, pages, last_len, code_data,
                                   code_page_table, pages, last_len, num_heads, head_dim, page_size, hadamard_scale,
                                   thresholds3_host, dtype, stream,
-                                  rope_from_args(rope_scale, rope_theta, rope_inv_freq, rope_mscale), seq_len_dev))
+                                  rope_from_args(rope_scale, rope_theta, rope_inv_freq, rope_mscale), seq_len_dev,
+                                  num_q_heads))
     return rc;
   return decode_forward_impl(handler, q, o, nullptr, lse, kv_data, kv_page_table, 0, pages - 1, page_size, 0,
                              last_len, last_len, sm_scale, stream, seq_len_dev);

@@ -92,7 +92,9 @@ struct EstimateParams {
   void* out;
   int64_t out_stride;
   int n_tokens;
-  int H;
+  int H;            // heads of the code cache
+  int q_group;      // query heads per cache head (grouped-query attention; 1 otherwise): q_code, out and hist
+                    // have H * q_group rows, row r reads the codes of cache head r / q_group (generic kernel only)
   int page_size;
   int ps_shift;     // log2(page_size) or -1
   int groups;       // token groups of 32 per tile: 1, or 2 * 16 / H for H < 16 (generic kernel only): each
@@ -268,8 +270,10 @@ __device__ __forceinline__ void est_consume(const EstimateParams& p, const EstGe
           if (p.hist) hist_count(p.hist, h, (tile0 + tl[rr] - lane) / g.slice_tokens, d[rr]);
         }
     } else {
-      for (int h = warp; h < H; h += kEstConsumerWarps) {
-        const unsigned d = chunk_distance<METRIC>(row[2 * h], sq[2 * h]) + chunk_distance<METRIC>(row[2 * h + 1], sq[2 * h + 1]);
+      const int rows = H * p.q_group;
+      for (int h = warp; h < rows; h += kEstConsumerWarps) {
+        const int hc = p.q_group == 1 ? h : h / p.q_group;   // the cache head this query head reads
+        const unsigned d = chunk_distance<METRIC>(row[2 * hc], sq[2 * h]) + chunk_distance<METRIC>(row[2 * hc + 1], sq[2 * h + 1]);
         if (lane < tile_tokens) {
           o[static_cast<int64_t>(h) * p.out_stride] = dist_to_out<OutT>(d);
           if (p.hist) hist_count(p.hist, h, slice, d);
@@ -305,8 +309,8 @@ __device__ __forceinline__ EstRing est_ring_init(uint4* smem, uint64_t* full_bar
   return r;
 }
 
-// Dynamic shared memory: kEstStages * kEstTile * groups * (2H + 1) * 16 bytes (ring), plus 2H * 32 bytes
-// of query planes when HPW == 0.
+// Dynamic shared memory: kEstStages * kEstTile * groups * (2H + 1) * 16 bytes (ring), plus 2H * q_group * 32
+// bytes of query planes when HPW == 0.
 // HPW > 0: H == kEstConsumerWarps * HPW and warp w keeps the query planes of heads w*HPW .. in
 // registers.  HPW == 0: any H, warp w handles heads w, w + 16, ... with the planes in shared memory.
 template <int METRIC, typename OutT, int HPW>
@@ -323,7 +327,7 @@ __global__ void __launch_bounds__(kEstThreads) estimate_kernel(const EstimatePar
     // generic path: the query planes go through shared memory, so the query code (written by the
     // preceding append kernel) is needed before the block barrier
     grid_dependency_wait();
-    for (int c = tid; c < ring.cpt; c += kEstThreads) sq[c] = make_qplanes<METRIC>(__ldg(p.q_code + c));
+    for (int c = tid; c < ring.cpt * p.q_group; c += kEstThreads) sq[c] = make_qplanes<METRIC>(__ldg(p.q_code + c));
   }
   __syncthreads();
   const EstGeom geom = est_geom(p, HPW == 0 ? kEstTile * p.groups : kEstTile);

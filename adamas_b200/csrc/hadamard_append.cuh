@@ -148,7 +148,9 @@ struct PagedTarget {
 };
 
 // Decode append: one half-warp per head.  FUSED: qh = q, kh = k and the transform runs here;
-// otherwise qh/kh point at rows 0/1 of the pre-transformed h.  ROPE (needs FUSED): q and k arrive
+// otherwise qh/kh point at rows 0/1 of the pre-transformed h.  Grouped-query attention (FUSED only):
+// q has q_heads = group * H rows and the caches H; half-warp i takes query row i and K/V row i, each
+// where it exists.  ROPE (needs FUSED): q and k arrive
 // un-rotated; they are rotated for position `pos`, written back in place (the attention reads the
 // rotated q, the caller's k stays consistent with the cache) and then coded.
 template <typename T, bool FUSED, bool ROPE = false>
@@ -156,7 +158,7 @@ __global__ void __launch_bounds__(256)
 append_decode_kernel(const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ qh,
                      const T* __restrict__ kh, uint16_t* __restrict__ q_code_out, PagedTarget tgt,
                      int kv_last_page, int kv_entry, int code_last_page, int code_entry, float scale,
-                     Thresholds th, float pos, RopeParams rp, const int32_t* seq_len_dev) {
+                     Thresholds th, float pos, RopeParams rp, const int32_t* seq_len_dev, int q_heads) {
   // The kernel after this one (the estimate) may become resident right away: its producer warps only
   // read the code cache as it was before this step, and its consumers wait for this grid to complete,
   // which in turn waits for the grid before it.  (Two appends to one cache back to back, followed by an
@@ -177,9 +179,12 @@ append_decode_kernel(const T* __restrict__ k, const T* __restrict__ v, const T* 
   const unsigned l16 = threadIdx.x & 15;
   const int head = (blockIdx.x * blockDim.x + threadIdx.x) >> 4;
   const int H = tgt.num_heads;
-  const bool valid = head < H;
+  const bool valid = head < H;            // a K/V row of the caches
+  const bool valid_q = head < q_heads;    // a query row
   const int hh = valid ? head : 0;
+  const int hq = valid_q ? head : 0;
   const int64_t in_off = static_cast<int64_t>(hh) * kHeadDim + l16 * 8;
+  const int64_t q_off = static_cast<int64_t>(hq) * kHeadDim + l16 * 8;
 
   // copy K and V rows into the page slot
   T* kv = static_cast<T*>(tgt.kv_data);
@@ -189,16 +194,14 @@ append_decode_kernel(const T* __restrict__ k, const T* __restrict__ v, const T* 
   uint4 kraw = ld_16(k + in_off);
   uint4 vraw = ld_16(v + in_off);
   float a[8], b[8];
-  unpack8<T>(ld_16(qh + in_off), a);
+  unpack8<T>(ld_16(qh + q_off), a);
   if (ROPE) {
     unpack8<T>(kraw, b);
     rope_halfwarp<T>(a, l16, pos, rp);
     rope_halfwarp<T>(b, l16, pos, rp);
     kraw = pack8<T>(b);
-    if (valid) {
-      st_16(const_cast<T*>(qh) + in_off, pack8<T>(a));
-      st_16(const_cast<T*>(k) + in_off, kraw);
-    }
+    if (valid_q) st_16(const_cast<T*>(qh) + q_off, pack8<T>(a));
+    if (valid) st_16(const_cast<T*>(k) + in_off, kraw);
   }
   if (valid) {
     st_16(kv + k_off, kraw);
@@ -214,8 +217,8 @@ append_decode_kernel(const T* __restrict__ k, const T* __restrict__ v, const T* 
   } else {
     unpack8<T>(ld_16(kh + in_off), b);
   }
+  if (valid_q) q_code_out[hq * kCodeWords + l16] = bucketize_pack8(a, th);
   if (valid) {
-    q_code_out[hh * kCodeWords + l16] = bucketize_pack8(a, th);
     const int64_t c_off =
         ((static_cast<int64_t>(code_page) * tgt.page_size + code_entry) * H + hh) * kCodeWords + l16;
     tgt.code_data[c_off] = bucketize_pack8(b, th);

@@ -72,7 +72,9 @@ struct SelectAttendParams {
   const int32_t* kv_table;  // logical page -> physical page
   int page_size;
   int ps_shift;             // log2(page_size) or -1
-  int H;
+  int H;                    // heads of the KV cache
+  int q_group;              // query heads per cache head (grouped-query attention; 1 otherwise): the grid, dist,
+                            // hist, q, o, lse and out_idx have H * q_group rows; row r attends cache head r / q_group
   int tail_mode;            // 0: no newest token; 1: it is at tail_slot; 2: at logical position n
   unsigned tail_slot;       // physical slot of the newest token (tail_mode 1)
   int32_t* out_idx;         // optional [H, out_stride]: physical slots of the winners, ascending position
@@ -107,6 +109,7 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   const int lane = tid & 31;
   const int warp = tid >> 5;
   const int H = p.H;
+  const int head_kv = p.q_group == 1 ? head : head / p.q_group;
 
   uint8_t* sa_tile = sa_smem;                                                         // [16 warps][K rows | V rows]
   int32_t* s_list = reinterpret_cast<int32_t*>(sa_smem + kSaWarps * 2 * kSaWarpRows * 256);   // the block's winners, in position order
@@ -369,7 +372,7 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
           page = slot / ps;
           e = slot - page * ps;
         }
-        const T* src = kvp + (static_cast<int64_t>(page * (2 * ps) + e) * H + head) * kHeadDim + (is_v ? v_delta : 0);
+        const T* src = kvp + (static_cast<int64_t>(page * (2 * ps) + e) * H + head_kv) * kHeadDim + (is_v ? v_delta : 0);
         bulk_copy_g2s((is_v ? wv : wk) + r * 256, src, kHeadDim * 2, bar);
       }
     }

@@ -33,7 +33,8 @@ struct DecodeParams {
   int n_idx;              // indices used per head
   int idx_unit;           // token slots covered by one index
   int page_size;
-  int H;
+  int H;                  // heads of the KV cache
+  int q_group;            // query heads per cache head (1: multi-head attention); the grid has H * q_group rows
   unsigned tail_slot0;    // physical token slot of the first tail token
   int ps_shift;           // log2(page_size) or -1
   int n_tokens;           // n_idx * idx_unit + tail_len
@@ -68,6 +69,7 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
   const int lane = tid & 31;
   const int warp = tid >> 5;
   const int H = prm.H;
+  const int head_kv = prm.q_group == 1 ? head : head / prm.q_group;
 
   const T* kvp = static_cast<const T*>(prm.kv);
   const int32_t* idx_row = prm.indices + static_cast<int64_t>(head) * prm.idx_stride;
@@ -144,7 +146,7 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
         e = slot - page * ps;
       }
       const int64_t row = static_cast<int64_t>(page) * (2 * ps) + e;
-      const T* src = kvp + (row * H + head) * kHeadDim + (is_v ? v_delta : 0);
+      const T* src = kvp + (row * H + head_kv) * kHeadDim + (is_v ? v_delta : 0);
       mbar_arrive_expect_tx(&full_bar[stage], kHeadDim * 2);
       bulk_copy_g2s((is_v ? sv : sk) + tl * kDecRowBytes, src, kHeadDim * 2, &full_bar[stage]);
     } else {

@@ -36,6 +36,8 @@ class StackConfig:
     """Llama-2-7B by default (32 layers, hidden 4096, 32 heads x 128, FFN 11008, vocab 32000)."""
     num_layers: int = 32
     num_heads: int = 32
+    num_kv_heads: int = 0         # heads of the K/V projections and caches; 0: as many as num_heads (multi-head
+                                  # attention, all the reference supports); a divisor of num_heads: grouped queries
     head_dim: int = 128
     ffn: int = 11008
     vocab: int = 32000
@@ -50,6 +52,10 @@ class StackConfig:
     @property
     def hidden(self) -> int:
         return self.num_heads * self.head_dim
+
+    @property
+    def kv_heads(self) -> int:
+        return self.num_kv_heads or self.num_heads
 
 
 class LlamaStack:
@@ -66,7 +72,9 @@ class LlamaStack:
         hd = cfg.hidden
         self.embed = w(cfg.vocab, hd)
         self.lm_head = w(cfg.vocab, hd)
-        self.wqkv = [w(3 * hd, hd) for _ in range(cfg.num_layers)]      # rows: q heads, k heads, v heads
+        assert cfg.num_heads % cfg.kv_heads == 0, "num_kv_heads must divide num_heads"
+        kvd = cfg.kv_heads * cfg.head_dim
+        self.wqkv = [w(hd + 2 * kvd, hd) for _ in range(cfg.num_layers)]      # rows: q heads, k heads, v heads
         self.wo = [w(hd, hd) for _ in range(cfg.num_layers)]
         self.w_gate_up = [w(2 * cfg.ffn, hd) for _ in range(cfg.num_layers)]
         self.w_down = [w(hd, cfg.ffn) for _ in range(cfg.num_layers)]
@@ -80,7 +88,10 @@ class LlamaStack:
         # static buffers of the decode step
         self._tok = torch.zeros(1, dtype=torch.int64, device=self.device)
         self._x = torch.zeros(1, hd, dtype=dtype, device=self.device)
-        self._qkv = torch.zeros(3, 1, cfg.num_heads, cfg.head_dim, dtype=dtype, device=self.device)
+        self._qkv_flat = torch.zeros(1, hd + 2 * kvd, dtype=dtype, device=self.device)
+        self._qkv = (self._qkv_flat[:, :hd].view(1, cfg.num_heads, cfg.head_dim),              # q, k, v of the token
+                     self._qkv_flat[:, hd:hd + kvd].view(1, cfg.kv_heads, cfg.head_dim),
+                     self._qkv_flat[:, hd + kvd:].view(1, cfg.kv_heads, cfg.head_dim))
         self._o = torch.zeros(1, cfg.num_heads, cfg.head_dim, dtype=dtype, device=self.device)
         self._logits = torch.zeros(1, cfg.vocab, dtype=torch.float32, device=self.device)
         self._token_graphs = {}       # sparse layers dense / sparse -> graph of a whole token
@@ -92,9 +103,9 @@ class LlamaStack:
         assert token_budget % page_size == 0, "the token budget must be a whole number of pages"
         self._page_budget = token_budget // page_size
         self.controller = U.InferenceController(
-            num_layers=self.cfg.num_layers, num_heads=self.cfg.num_heads, head_dim=self.cfg.head_dim,
+            num_layers=self.cfg.num_layers, num_heads=self.cfg.kv_heads, head_dim=self.cfg.head_dim,
             page_size=page_size, page_budget=self._page_budget, max_seq_len=max_seq_len,
-            dtype=self.dtype, device=self.device)
+            dtype=self.dtype, device=self.device, num_q_heads=self.cfg.num_heads)
 
     def clean_states(self) -> None:
         self.controller.clean_states()
@@ -143,12 +154,17 @@ class LlamaStack:
 
         def body(layer):
             nonlocal x
-            qkv = F.linear(self._norm(x, self.ln1[layer]), self.wqkv[layer]).view(n, 3, cfg.num_heads, cfg.head_dim)
-            q, k, v = (qkv[:, i].contiguous() for i in range(3))
+            qkv = F.linear(self._norm(x, self.ln1[layer]), self.wqkv[layer])
+            kvd = cfg.kv_heads * cfg.head_dim
+            q = qkv[:, :cfg.hidden].reshape(n, cfg.num_heads, cfg.head_dim).contiguous()
+            k = qkv[:, cfg.hidden:cfg.hidden + kvd].reshape(n, cfg.kv_heads, cfg.head_dim).contiguous()
+            v = qkv[:, cfg.hidden + kvd:].reshape(n, cfg.kv_heads, cfg.head_dim).contiguous()
             self._rope_prefill(q, k, past)
             U.append_kvh(k, v, None, c, layer)
-            attn = F.scaled_dot_product_attention(q.transpose(0, 1).unsqueeze(0), k.transpose(0, 1).unsqueeze(0),
-                                                  v.transpose(0, 1).unsqueeze(0), is_causal=True)
+            group = cfg.num_heads // cfg.kv_heads
+            kk, vv = (k, v) if group == 1 else (k.repeat_interleave(group, 1), v.repeat_interleave(group, 1))
+            attn = F.scaled_dot_product_attention(q.transpose(0, 1).unsqueeze(0), kk.transpose(0, 1).unsqueeze(0),
+                                                  vv.transpose(0, 1).unsqueeze(0), is_causal=True)
             x = x + F.linear(attn.squeeze(0).transpose(0, 1).reshape(n, cfg.hidden), self.wo[layer])
             x = x + self._mlp(x, layer)
 
@@ -161,7 +177,7 @@ class LlamaStack:
     # ---- decode -------------------------------------------------------------------------------
     def _segment_first(self):
         self._x.copy_(self.embed[self._tok])
-        torch.matmul(self._norm(self._x, self.ln1[0]), self.wqkv[0].t(), out=self._qkv.view(1, -1))
+        torch.matmul(self._norm(self._x, self.ln1[0]), self.wqkv[0].t(), out=self._qkv_flat)
 
     def _segment_after(self, layer: int):
         cfg = self.cfg
@@ -169,7 +185,7 @@ class LlamaStack:
         self._x.add_(self._mlp(self._x, layer))
         if layer + 1 < cfg.num_layers:
             torch.matmul(self._norm(self._x, self.ln1[layer + 1]), self.wqkv[layer + 1].t(),
-                         out=self._qkv.view(1, -1))
+                         out=self._qkv_flat)
         else:
             self._logits.copy_(F.linear(self._norm(self._x, self.ln_f), self.lm_head))
             self._tok.copy_(self._logits.argmax(dim=-1))

@@ -70,7 +70,7 @@ def append_qkv_fused(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, iControl
     Returns the packed query code [1,H,D/8] (written into `out` when given).  rope=(rope_scale,
     rope_theta): q and k are un-rotated and get rotated in place inside the same launch."""
     c = iController
-    o = out if out is not None else torch.empty(1, k.size(1), k.size(2) // 8, dtype=k.dtype, device=k.device)
+    o = out if out is not None else torch.empty(1, q.size(1), k.size(2) // 8, dtype=k.dtype, device=k.device)
     _kernels.append_kv_cache_decode_fused(
         q, k, v, o, c.kv_cache.buf_layer(layer_idx), c.kv_indices_with_last, c.kv_cache.last_page_len,
         c.hadamard_cache.buf_layer(layer_idx), c.hadamard_indices, c.hadamard_cache.last_page_len,

@@ -26,7 +26,8 @@ class InferenceController:
     def __init__(self, num_layers, num_heads, head_dim, page_size,
                  page_budget,   # page budget including the last page
                  max_seq_len,   # capacity of the KV / code caches in tokens
-                 dtype, device):
+                 dtype, device,
+                 num_q_heads=None):   # query heads when they outnumber the cache's (grouped-query attention)
         self.kv_cache = KvCache(num_layers=num_layers, num_heads=num_heads, head_dim=head_dim,
                                 max_seq_len=max_seq_len, page_size=page_size, items=2, dtype=dtype,
                                 device=device)
@@ -38,7 +39,10 @@ class InferenceController:
         self.layout = TensorLayout.NHD
         self.device = device
         self.dtype = dtype
-        self.num_heads = num_heads
+        self.num_heads = num_heads          # heads of the caches
+        self.num_q_heads = num_heads if num_q_heads is None else int(num_q_heads)   # rows of q, o, distances, lists
+        if self.num_q_heads < num_heads or self.num_q_heads % num_heads:
+            raise ValueError("num_q_heads must be a multiple of num_heads")
         self.head_dim = head_dim
         self.page_size = page_size
 
@@ -114,7 +118,7 @@ class InferenceController:
         assert cur_page_nums > 1 or self.page_size > 1   # the newest token is always kept apart
         if updateTensor:
             n = cur_page_nums - 1
-            self.kv_indices_without_last = self.kv_indices_with_last[:n].unsqueeze(0).expand(self.num_heads, n)
+            self.kv_indices_without_last = self.kv_indices_with_last[:n].unsqueeze(0).expand(self.num_q_heads, n)
 
         if self.page_size == 1:
             self.inference_page_budget = min(self._page_budget, cur_page_nums)
@@ -126,22 +130,22 @@ class InferenceController:
         self._set_indptr("approx", [0, k])
 
         # top-k outputs: values and indices share one row stride; reused across steps
-        if self._topk_store is None or self._topk_store[0].size(1) < k or self._topk_store[0].size(0) != self.num_heads:
+        if self._topk_store is None or self._topk_store[0].size(1) < k or self._topk_store[0].size(0) != self.num_q_heads:
             # grows geometrically: in the dense first layers k is the whole context, one more each step
             cap = max(k, 1) if self._topk_store is None else max(k, 2 * self._topk_store[0].size(1))
             cap = max(min(cap, self.kv_cache.pool.capacity * self.page_size), k, 1)
-            vals = torch.zeros((self.num_heads, cap), dtype=torch.int16, device=self.device)
-            idx = torch.zeros((self.num_heads, cap), dtype=torch.int32, device=self.device)
+            vals = torch.zeros((self.num_q_heads, cap), dtype=torch.int16, device=self.device)
+            idx = torch.zeros((self.num_q_heads, cap), dtype=torch.int32, device=self.device)
             self._topk_store = (vals, idx)
         vdtype = self.dtype if self.dtype == torch.float16 else torch.int16
         self.topk_dout_buffer = self._topk_store[0].view(vdtype)[:, :k]
         self.topk_dindices_buffer = self._topk_store[1][:, :k]
         if self.topk_buf is None:
             # the reference's radix-select scratch (controller.py:122); unused here, kept for callers
-            self.topk_buf = torch.zeros((self.num_heads, 8192 * 2 * (2 + 4) // 2 // 48), dtype=self.dtype,
+            self.topk_buf = torch.zeros((self.num_q_heads, 8192 * 2 * (2 + 4) // 2 // 48), dtype=self.dtype,
                                         device=self.device)
 
-        self._decode_handler.begin_forward(torch.tensor([0, k], dtype=torch.int32), self.num_heads,
+        self._decode_handler.begin_forward(torch.tensor([0, k], dtype=torch.int32), self.num_q_heads,
                                            self.num_heads, self.head_dim, self.page_size, self.dtype)
 
     def end_forward(self):
@@ -161,7 +165,7 @@ class InferenceController:
             cap = max(n, 1) if self._estimate_store is None else max(n, 2 * self._estimate_store.size(1))
             cap = max(min(cap, self.kv_cache.pool.capacity * self.page_size), n)
             cap = (cap + 7) // 8 * 8     # rows start on 16-byte boundaries (the top-k kernel's fast layout)
-            self._estimate_store = torch.empty((self.num_heads, cap), dtype=torch.int16, device=self.device)
+            self._estimate_store = torch.empty((self.num_q_heads, cap), dtype=torch.int16, device=self.device)
         return self._estimate_store.view(vdtype)[:, :n]
 
     def distance_scratch(self, n: int) -> torch.Tensor:
@@ -176,7 +180,7 @@ class InferenceController:
         between steps)."""
         if self._hist is None:
             from .. import _kernels
-            self._hist = _kernels.histogram_scratch(self.num_heads, self.device)
+            self._hist = _kernels.histogram_scratch(self.num_q_heads, self.device)
         return self._hist
 
     @property
@@ -198,7 +202,7 @@ class InferenceController:
         sequence are ordered on one stream)."""
         q = self._q_code_scratch
         if q is None or q.dtype != dtype:
-            q = torch.empty(1, self.num_heads, self.head_dim // 8, dtype=dtype, device=self.device)
+            q = torch.empty(1, self.num_q_heads, self.head_dim // 8, dtype=dtype, device=self.device)
             self._q_code_scratch = q
         return q
 

@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define ADAMAS_ABI_VERSION 3
+#define ADAMAS_ABI_VERSION 4
 
 /* status codes */
 #define ADAMAS_OK 0
@@ -47,6 +47,16 @@ extern "C" {
 #define ADAMAS_VAL_U16 1         /* unsigned 16-bit integer */
 
 typedef void* adamas_stream_t;   /* a cudaStream_t */
+
+/* Grouped-query attention.  Where a function takes num_heads AND num_q_heads, num_heads is the head
+ * count of the caches (KV heads) and num_q_heads that of the query side: q, o, q_code, lse, the
+ * distance rows, the histogram scratch and the index lists have num_q_heads rows, and query head r
+ * reads cache head r / (num_q_heads / num_heads).  num_q_heads must be a multiple of num_heads;
+ * num_q_heads == num_heads is multi-head attention, the only case the reference supports
+ * (kernels/include/decode/decode_handler.cuh:83 asserts num_qo_heads == num_kv_heads; its kernels
+ * carry a group-size parameter, kernels/include/decode/decode_attn.cuh:706,873, that is always 1).  Functions with num_heads alone (the stand-alone append
+ * forms that take a pre-transformed h, adamas_append_estimate, adamas_decode_forward_static) are
+ * multi-head only. */
 
 /* Scratch of the fused decode step ("histogram scratch"): 32-bit words per head.  The estimate launch
  * of a step counts the distances of every head into its first 16 * 512 words (one 512-bin histogram
@@ -133,7 +143,7 @@ int adamas_append_decode_fused(const void* q, const void* k, const void* v, void
                                int kv_last_page_len,
                                void* code_data, const int32_t* code_page_table, int code_num_pages,
                                int code_last_page_len,
-                               int num_heads, int head_dim, int page_size, float scale,
+                               int num_heads, int num_q_heads, int head_dim, int page_size, float scale,
                                const float* thresholds3_host, int dtype, adamas_stream_t stream);
 
 /* In-place rotary position embedding (Llama rotate-half form, linear position scaling) of
@@ -147,13 +157,15 @@ int adamas_apply_rope_in_place(void* q, void* k, int64_t seq_len, int num_q_head
 /* adamas_append_decode_fused with the rotary embedding in front: q and k [1,H,D] arrive un-rotated,
  * are rotated in place for the position of the token being appended, and are then transformed, coded
  * and stored.  One launch for apply_rope_in_place + torch.cat + hadamard_transform + append_kvh
- * (adamas/models/Adamas.py:113,145-161). */
+ * (adamas/models/Adamas.py:113,145-161).  rope_inv_freq (optional, device, 64 floats) and rope_mscale:
+ * a frequency table instead of (rope_scale, rope_theta), as in adamas_decode_step_dev. */
 int adamas_append_decode_rope_fused(void* q, void* k, const void* v, void* q_code_out, void* kv_data,
                                     const int32_t* kv_page_table, int kv_num_pages, int kv_last_page_len,
                                     void* code_data, const int32_t* code_page_table, int code_num_pages,
-                                    int code_last_page_len, int num_heads, int head_dim, int page_size,
-                                    float scale, const float* thresholds3_host, float rope_scale,
-                                    float rope_theta, int dtype, adamas_stream_t stream);
+                                    int code_last_page_len, int num_heads, int num_q_heads, int head_dim,
+                                    int page_size, float scale, const float* thresholds3_host, float rope_scale,
+                                    float rope_theta, const float* rope_inv_freq, float rope_mscale, int dtype,
+                                    adamas_stream_t stream);
 
 /* Prefill append of n_tokens tokens ending at the current sequence end.  k, v, h [n_tokens,H,D];
  * h holds transformed keys.  If h is NULL the transform of k is computed inside (scale used).
@@ -181,7 +193,7 @@ int adamas_append_prefill(const void* k, const void* v, const void* h, int64_t n
  * kernels/include/decode/decode_attn.cuh:287-443,1144-1211). */
 int adamas_estimate(const void* q_code, const void* code_data, const int32_t* code_page_table,
                     int code_num_pages, int code_last_page_len, int page_size, int num_heads,
-                    int head_dim, void* out, int64_t out_stride, int out_format, int metric,
+                    int num_q_heads, int head_dim, void* out, int64_t out_stride, int out_format, int metric,
                     int exclude_last, uint32_t* hist, int hist_slices, adamas_stream_t stream);
 
 /* ---- stage 3: top-k ------------------------------------------------------------------------ */
@@ -215,7 +227,8 @@ int adamas_decode_handler_destroy(adamas_decode_handler_t* handler);
  * handler's device scratch (partial outputs) is large enough (allocates on first use or growth).
  * Replaces BeginForward (kernels/include/decode/decode_handler.cuh:73-121). */
 int adamas_decode_begin_forward(adamas_decode_handler_t* handler, int64_t max_tokens, int num_heads,
-                                int head_dim, int page_size, int dtype, adamas_stream_t stream);
+                                int num_q_heads, int head_dim, int page_size, int dtype,
+                                adamas_stream_t stream);
 /* Replaces EndForward (decode_handler.cuh:123-136).  Scratch is kept for reuse until destroy. */
 int adamas_decode_end_forward(adamas_decode_handler_t* handler);
 
@@ -285,9 +298,10 @@ int adamas_decode_forward_static(const void* q, void* o, float* lse, const void*
  * (adamas/models/Adamas.py:185-200) for n up to 262144 (32768 x the adamas_set_max_cluster bound). */
 int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, const void* q, void* o,
                          float* o_f32, float* lse, const void* kv_data, const int32_t* kv_page_table,
-                         int page_size, int num_heads, int head_dim, int dtype, int last_page_idx,
-                         int last_page_len, uint32_t* hist, int hist_ready, const int32_t* ext_cut,
-                         int32_t* out_idx, int64_t out_stride, float sm_scale, adamas_stream_t stream);
+                         int page_size, int num_heads, int num_q_heads, int head_dim, int dtype,
+                         int last_page_idx, int last_page_len, uint32_t* hist, int hist_ready,
+                         const int32_t* ext_cut, int32_t* out_idx, int64_t out_stride, float sm_scale,
+                         adamas_stream_t stream);
 
 /* Number of slices (thread blocks per head) adamas_select_attend uses for rows of n distances, k
  * winners and num_heads heads on the current device: the hist_slices an estimate call must be given
@@ -338,16 +352,18 @@ int adamas_append_estimate(const void* q, const void* k, const void* v, void* q_
  * (otherwise every page is attended: use
  * adamas_decode_forward).  kv_last_page_idx is the physical number of the last KV page.  With
  * rope_scale > 0, q and k arrive un-rotated and the append launch rotates them in place first
- * (apply_rope_in_place, adamas/models/Adamas.py:113); rope_scale <= 0: q and k are already rotated. */
+ * (apply_rope_in_place, adamas/models/Adamas.py:113); rope_scale <= 0: q and k are already rotated.
+ * rope_inv_freq (optional, device, 64 floats) and rope_mscale: a frequency table instead of
+ * (rope_scale, rope_theta), see adamas_decode_step_dev. */
 int adamas_decode_step(void* q, void* k, const void* v, void* o, float* lse, void* q_code,
                        void* kv_data, const int32_t* kv_page_table, int kv_num_pages,
                        int kv_last_page_len, int kv_last_page_idx, void* code_data,
                        const int32_t* code_page_table, int code_num_pages, int code_last_page_len,
-                       int num_heads, int head_dim, int page_size, int dtype, int budget,
+                       int num_heads, int num_q_heads, int head_dim, int page_size, int dtype, int budget,
                        void* dist_scratch, int64_t dist_stride, uint32_t* hist_scratch, int32_t* out_idx,
                        int64_t out_stride, float hadamard_scale, const float* thresholds3_host,
-                       float rope_scale, float rope_theta, float sm_scale,
-                       adamas_stream_t stream);
+                       float rope_scale, float rope_theta, const float* rope_inv_freq, float rope_mscale,
+                       float sm_scale, adamas_stream_t stream);
 
 /* ---- decode steps whose sequence length lives on the device ----------------------------------
  * The reference rebuilds its index tensors on the host and re-plans the decode every step
@@ -368,8 +384,8 @@ int adamas_decode_step(void* q, void* k, const void* v, void* o, float* lse, voi
  * are multiplied by rope_mscale (YaRN-style scaling; rope_scale / rope_theta are then unused). */
 int adamas_decode_step_dev(void* q, void* k, const void* v, void* o, float* lse, void* q_code, void* kv_data,
                            const int32_t* kv_page_table, void* code_data, const int32_t* code_page_table,
-                           const int32_t* seq_len_dev, int max_seq_len, int num_heads, int head_dim,
-                           int page_size, int dtype, int budget, void* dist_scratch, int64_t dist_stride,
+                           const int32_t* seq_len_dev, int max_seq_len, int num_heads, int num_q_heads,
+                           int head_dim, int page_size, int dtype, int budget, void* dist_scratch, int64_t dist_stride,
                            uint32_t* hist_scratch, int32_t* out_idx, int64_t out_stride, float hadamard_scale,
                            const float* thresholds3_host, float rope_scale, float rope_theta,
                            const float* rope_inv_freq, float rope_mscale, float sm_scale,
@@ -382,8 +398,8 @@ int adamas_decode_step_dev(void* q, void* k, const void* v, void* o, float* lse,
 int adamas_dense_step_dev(adamas_decode_handler_t* handler, void* q, void* k, const void* v, void* o, float* lse,
                           void* q_code, void* kv_data, const int32_t* kv_page_table, void* code_data,
                           const int32_t* code_page_table, const int32_t* seq_len_dev, int max_seq_len,
-                          int num_heads, int head_dim, int page_size, int dtype, float hadamard_scale,
-                          const float* thresholds3_host, float rope_scale, float rope_theta,
+                          int num_heads, int num_q_heads, int head_dim, int page_size, int dtype,
+                          float hadamard_scale, const float* thresholds3_host, float rope_scale, float rope_theta,
                           const float* rope_inv_freq, float rope_mscale, float sm_scale,
                           adamas_stream_t stream);
 

@@ -267,6 +267,15 @@ def merge_states(o_parts: torch.Tensor, lse_parts: torch.Tensor) -> Tuple[torch.
 # --------------------------------------------------------------------------
 # whole decode step
 # --------------------------------------------------------------------------
+def repeat_kv(x: torch.Tensor, group: int) -> torch.Tensor:
+    """Grouped-query attention stated as multi-head attention: x [L, H_kv, D] ->
+    [L, H_kv * group, D] with query head r reading cache head r // group (the
+    kv_head_idx = qo_head_idx / GROUP_SIZE of kernels/src/include/cpu_reference.h:83;
+    the reference's operators themselves run group 1 only,
+    kernels/include/decode/decode_handler.cuh:83)."""
+    return x if group == 1 else x.repeat_interleave(group, dim=1)
+
+
 def decode_step(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, budget: int,
                 scale: Optional[float] = None, metric: str = "l1",
                 semantics: str = "ops", thresholds: Sequence[float] = THRESHOLDS):

@@ -17,7 +17,9 @@ LOGIT_ATOL = 2e-2      # fp16 GEMM chain against fp32 (logits are O(0.5) here)
 
 def _stack(cls=None, **over):
     from adamas_b200 import llama_stack as S
-    cfg = S.StackConfig(num_layers=4, num_heads=4, head_dim=128, ffn=1024, vocab=512, skip_layers=1, **over)
+    kw = dict(num_layers=4, num_heads=4, head_dim=128, ffn=1024, vocab=512, skip_layers=1)
+    kw.update(over)
+    cfg = S.StackConfig(**kw)
     return (cls or S.LlamaStack)(cfg, DEV, torch.float16, seed=3)
 
 
@@ -46,10 +48,13 @@ def _reference_logits(st, ids):
         return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + cfg.rms_eps) * w.float()
 
     for l in range(cfg.num_layers):
-        qkv = (norm(x, st.ln1[l]) @ st.wqkv[l].float().t()).view(n, 3, cfg.num_heads, cfg.head_dim)
-        q = _rope_f32(qkv[:, 0], cfg.rope_scale, cfg.rope_theta)
-        k = _rope_f32(qkv[:, 1], cfg.rope_scale, cfg.rope_theta)
-        v = qkv[:, 2]
+        qkv = norm(x, st.ln1[l]) @ st.wqkv[l].float().t()
+        kvd = cfg.kv_heads * cfg.head_dim
+        group = cfg.num_heads // cfg.kv_heads
+        q = _rope_f32(qkv[:, :cfg.hidden].reshape(n, cfg.num_heads, cfg.head_dim), cfg.rope_scale, cfg.rope_theta)
+        k = _rope_f32(qkv[:, cfg.hidden:cfg.hidden + kvd].reshape(n, cfg.kv_heads, cfg.head_dim), cfg.rope_scale, cfg.rope_theta)
+        v = qkv[:, cfg.hidden + kvd:].reshape(n, cfg.kv_heads, cfg.head_dim)
+        k, v = k.repeat_interleave(group, 1), v.repeat_interleave(group, 1)
         s = torch.einsum("qhd,khd->hqk", q, k) / math.sqrt(cfg.head_dim)
         s = s.masked_fill(torch.triu(torch.ones(n, n, dtype=torch.bool, device=x.device), 1), float("-inf"))
         a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v).reshape(n, cfg.hidden)
@@ -59,8 +64,9 @@ def _reference_logits(st, ids):
     return norm(x[-1:], st.ln_f) @ st.lm_head.float().t()
 
 
-def test_dense_stack_matches_fp32_model():
-    st = _stack()
+@pytest.mark.parametrize("heads,kv_heads", [(4, 0), (8, 2)])
+def test_dense_stack_matches_fp32_model(heads, kv_heads):
+    st = _stack(num_heads=heads, num_kv_heads=kv_heads)
     ids = _ids(150)
     st.init_controller(page_size=16, token_budget=4096, max_seq_len=256)     # budget > context: every layer dense
     logits = st.prefill(ids[:140])
@@ -133,17 +139,20 @@ def test_sparse_stack_matches_oracle_layer_by_layer(page_size, budget):
     assert _lib.device_error() == 0
 
 
-@pytest.mark.parametrize("prefill,budget,new_tokens,yarn", [(200, 64, 40, 0.0), (50, 64, 40, 0.0), (120, 64, 24, 32.0)])
-def test_whole_token_graph_equals_eager_loop(prefill, budget, new_tokens, yarn):
+@pytest.mark.parametrize("prefill,budget,new_tokens,yarn,kv_heads", [
+    (200, 64, 40, 0.0, 0), (50, 64, 40, 0.0, 0), (120, 64, 24, 32.0, 0), (120, 64, 24, 0.0, 2)])
+def test_whole_token_graph_equals_eager_loop(prefill, budget, new_tokens, yarn, kv_heads):
     """decode_one as ONE graph replay per token (device-resident sequence length) against the eager
     loop over the host-length operators: same sampled tokens, same logits, same caches.  The second
     case starts with every layer dense and crosses the token budget on the way (the graph is
-    re-captured once), both cross several page boundaries; the third rotates with a YaRN table."""
+    re-captured once), both cross several page boundaries; the third rotates with a YaRN table; the
+    fourth has 8 query heads over 2 cache heads."""
     ids = _ids(prefill, seed=2)
     forced = _ids(new_tokens, seed=5).tolist()     # the same input token at every step of both runs
     runs = []
     for use_graphs in (True, False):
-        st = _stack(yarn_factor=yarn, yarn_original_max_position=64)
+        st = _stack(yarn_factor=yarn, yarn_original_max_position=64, num_heads=8 if kv_heads else 4,
+                    num_kv_heads=kv_heads)
         st.init_controller(page_size=16, token_budget=budget, max_seq_len=prefill + new_tokens + 16)
         st.prefill(ids)
         toks, logits = [], []

@@ -190,14 +190,15 @@ def test_rope_table_in_place_yarn(dtype, past_kv_len, seq_len):
     """Per-dimension rotation frequencies and a factor on the rotated values (YaRN), against the
     oracle's restatement, at the reference's tolerance for its own RoPE operator scaled by the factor."""
     _, K, U = _mods()
-    from adamas_b200.rope import yarn_inv_freq
-    inv_freq, mscale = yarn_inv_freq(32.0, 4096)
+    # the same table on both sides: at position 131071 one unit in the last place of a frequency moves the
+    # angle by 0.008 rad (the table itself is compared with transformers' on the CPU)
+    want_inv, want_scale = ref.yarn_parameters(32.0, 4096)
+    mscale = want_scale
     q = _randn((seq_len, 32, 128), past_kv_len + seq_len, dtype)
     k = _randn((seq_len, 8, 128), past_kv_len + seq_len + 1, dtype)
     qd, kd = q.to(DEV), k.to(DEV)
-    K.apply_rope_table_in_place(qd, kd, past_kv_len, inv_freq.to(DEV), mscale)
+    K.apply_rope_table_in_place(qd, kd, past_kv_len, want_inv.to(DEV), mscale)
     tol = 5e-3 * (4 if dtype == torch.bfloat16 else 1) * mscale
-    want_inv, want_scale = ref.yarn_parameters(32.0, 4096)
     torch.testing.assert_close(qd.cpu().float(), ref.rope_table(q, past_kv_len, want_inv, want_scale).float(), rtol=tol, atol=tol)
     torch.testing.assert_close(kd.cpu().float(), ref.rope_table(k, past_kv_len, want_inv, want_scale).float(), rtol=tol, atol=tol)
 

@@ -21,7 +21,35 @@ def test_library_exports_every_declared_symbol():
     for name in sorted(declared):
         assert hasattr(_lib.lib, name), f"{name} declared in the header but not exported"
     assert set(_lib.SIGNATURES) | {"adamas_abi_version", "adamas_last_error"} == declared
-    assert _lib.lib.adamas_abi_version() == _lib.ABI_VERSION == 3
+    assert _lib.lib.adamas_abi_version() == _lib.ABI_VERSION == 4
+
+
+def test_ctypes_signatures_match_the_header():
+    """Every declaration's parameter list against the ctypes table: count, and pointer / integer /
+    float kind of each parameter."""
+    from adamas_b200 import _lib
+    header = open(os.path.join(ROOT, "include", "adamas_b200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    decls = dict(re.findall(r"\bint\s+(adamas_[a-z0-9_]+)\s*\(([^)]*)\)\s*;", header))
+    assert set(decls) >= set(_lib.SIGNATURES)
+
+    def kind(param: str) -> str:
+        param = param.strip()
+        if "*" in param or param.startswith("adamas_stream_t"):
+            return "p"
+        if param.startswith("float"):
+            return "f"
+        if param.startswith("int64_t"):
+            return "l"
+        assert param.startswith(("int ", "unsigned")), param
+        return "i"
+
+    ctype_kind = {ctypes.c_int: "i", ctypes.c_int64: "l", ctypes.c_float: "f", ctypes.c_void_p: "p"}
+    for name, args in _lib.SIGNATURES.items():
+        params = [p for p in decls[name].split(",") if p.strip() and p.strip() != "void"]
+        got = "".join(ctype_kind.get(a, "p") for a in args)
+        want = "".join(kind(p) for p in params)
+        assert got == want, f"{name}: ctypes {got} vs header {want}"
 
 
 def test_argument_validation_without_gpu():
