@@ -376,6 +376,7 @@ class BatchDecodeWithPagedKVCachePyTorchWrapper:
         self._cfg = (int(num_qo_heads), int(head_dim), int(page_size),
                      _dtype_code(empty_data.dtype, "BatchDecodeWithPagedKVCache"))
         self._kv_heads = int(num_kv_heads)
+        self._batch = max(1, indptr.numel() - 1)      # the reference's indptr has one entry per sequence, plus one
         self._started = True
         self._planned_tokens = 0   # scratch is sized on the first forward, from the index tensor
 
@@ -418,8 +419,8 @@ class BatchDecodeWithPagedKVCachePyTorchWrapper:
             tail = int(tail_len)
         n_tokens = n_idx * unit + tail
         if n_tokens > self._planned_tokens:
-            _lib.check(lib.adamas_decode_begin_forward(self._handle, n_tokens, self._kv_heads, num_heads, head_dim,
-                                                       page_size, dt, _stream()), "BatchDecodeWithPagedKVCache")
+            _lib.check(lib.adamas_decode_begin_forward(self._handle, n_tokens, self._batch, self._kv_heads, num_heads,
+                                                       head_dim, page_size, dt, _stream()), "BatchDecodeWithPagedKVCache")
             self._planned_tokens = n_tokens
         if lse is not None:
             _require(lse.is_cuda and lse.dtype == torch.float32 and lse.numel() == num_heads and lse.is_contiguous(),
@@ -458,8 +459,8 @@ class BatchDecodeWithPagedKVCachePyTorchWrapper:
         _require(tuple(q.shape) == tuple(o.shape) and k.size(0) == 1, "q, o must be [1, Hq, D], k, v [1, H, D]")
         _require(kv_indices.numel() * page_size >= max_seq_len, "the page table must have room for max_seq_len tokens")
         if max_seq_len > self._planned_tokens:
-            _lib.check(lib.adamas_decode_begin_forward(self._handle, int(max_seq_len), num_heads, q_heads, head_dim,
-                                                       page_size, dt, _stream()), "BatchDecodeWithPagedKVCache")
+            _lib.check(lib.adamas_decode_begin_forward(self._handle, int(max_seq_len), self._batch, num_heads, q_heads,
+                                                       head_dim, page_size, dt, _stream()), "BatchDecodeWithPagedKVCache")
             self._planned_tokens = int(max_seq_len)
         s = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)
         rs, rt, inv_freq, mscale = _rope_args(rope)
@@ -468,6 +469,30 @@ class BatchDecodeWithPagedKVCachePyTorchWrapper:
             _ptr(kv_indices), _ptr(hadamard_data), _ptr(hadamard_indices), _ptr(seq_len), int(max_seq_len),
             num_heads, q_heads, head_dim, page_size, dt, s, _lib.thresholds_arg(thresholds), rs, rt, _ptr(inv_freq),
             mscale, 1.0 / math.sqrt(head_dim), _stream()), "dense_step_dev")
+
+    def dense_step_batch_dev(self, q, k, v, o, q_code, seqs, seq_lens, max_seq_len: int, page_size: int,
+                              scale: Optional[float] = None, thresholds=None, rope=None,
+                              lse: Optional[torch.Tensor] = None) -> None:
+        """dense_step_dev for several sequences in the same launches (shapes as decode_step_batch_dev).  The
+        wrapper must have been begun with an indptr of batch + 1 entries."""
+        if not self._started:
+            raise RuntimeError("BatchDecodeWithPagedKVCache failed with error: dense step called before begin_forward")
+        batch, num_heads, q_heads = _check_batch(q, k, v, o, q_code, seqs, seq_lens, "dense_step_batch_dev")
+        cfg_heads, cfg_dim, cfg_ps, dt = self._cfg
+        _require((q_heads, num_heads, 128, int(page_size)) == (cfg_heads, self._kv_heads, cfg_dim, cfg_ps)
+                 and _dtype_code(k.dtype, "dense_step_batch_dev") == dt and batch <= self._batch,
+                 "cache geometry or batch differs from begin_forward")
+        if max_seq_len > self._planned_tokens:
+            _lib.check(lib.adamas_decode_begin_forward(self._handle, int(max_seq_len), self._batch, num_heads, q_heads,
+                                                       128, cfg_ps, dt, _stream()), "BatchDecodeWithPagedKVCache")
+            self._planned_tokens = int(max_seq_len)
+        s = 1.0 / math.sqrt(128.0) if scale is None else float(scale)
+        rs, rt, inv_freq, mscale = _rope_args(rope)
+        _lib.check(lib.adamas_dense_step_batch_dev(
+            self._handle, _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(q_code), _ptr(seqs), _ptr(seq_lens), batch,
+            int(max_seq_len), num_heads, q_heads, 128, cfg_ps, dt, s, _lib.thresholds_arg(thresholds), rs, rt,
+            _ptr(inv_freq), mscale, 1.0 / math.sqrt(128.0), _stream()), "dense_step_batch_dev")
+
 
 
 def set_max_cluster(blocks: int) -> None:
@@ -593,9 +618,10 @@ def _rope_args(rope):
     return float(rope[0]), float(rope[1]), None, 1.0
 
 
-def _check_seq_len(seq_len: torch.Tensor) -> None:
+def _check_seq_len(seq_len: torch.Tensor, count: int = 1) -> None:
     _require(isinstance(seq_len, torch.Tensor) and seq_len.is_cuda and seq_len.dtype == torch.int32
-             and seq_len.numel() == 1, "seq_len must be a one-element int32 CUDA tensor")
+             and seq_len.is_contiguous() and seq_len.numel() == count,
+             f"seq_len must be a contiguous int32 CUDA tensor of {count} element(s)")
 
 
 def decode_step_dev(q, k, v, o, q_code, kv_data, kv_indices, hadamard_data, hadamard_indices,
@@ -638,9 +664,80 @@ def decode_step_dev(q, k, v, o, q_code, kv_data, kv_indices, hadamard_data, hada
 
 
 def seq_len_advance(seq_len: torch.Tensor, delta: int = 1) -> None:
-    """seq_len += delta on the device, as one launch ordered against its neighbours in the stream."""
-    _check_seq_len(seq_len)
-    _lib.check(lib.adamas_seq_len_advance(_ptr(seq_len), int(delta), _stream()), "seq_len_advance")
+    """seq_len += delta on the device (every element: one per sequence of a batch), as one launch
+    ordered against its neighbours in the stream."""
+    _check_seq_len(seq_len, seq_len.numel())
+    _lib.check(lib.adamas_seq_len_advance(_ptr(seq_len), seq_len.numel(), int(delta), _stream()), "seq_len_advance")
+
+
+# ----------------------------------------------------------------------------------------------
+# several sequences in one launch
+# ----------------------------------------------------------------------------------------------
+def sequence_descriptors(kv_datas, code_datas, kv_tables, code_tables) -> torch.Tensor:
+    """Device array of adamas_seq_desc_t for one layer: int64 [batch, 4] holding, per sequence, the
+    addresses of its KV cache, code cache, KV page table and code page table.  The tensors must stay
+    alive (and in place) for as long as the array is used."""
+    rows = []
+    for kv, cd, kt, ct in zip(kv_datas, code_datas, kv_tables, code_tables):
+        _check_input(kv, "kv_data", 5)
+        _check_input(cd, "hadamard_data", 5)
+        _require(kt.is_cuda and ct.is_cuda and kt.dtype == torch.int32 and ct.dtype == torch.int32
+                 and kt.is_contiguous() and ct.is_contiguous(), "page tables must be contiguous int32 CUDA tensors")
+        rows.append([kv.data_ptr(), cd.data_ptr(), kt.data_ptr(), ct.data_ptr()])
+    _require(len(rows) >= 1, "no sequences")
+    return torch.tensor(rows, dtype=torch.int64).to(kv_datas[0].device)
+
+
+def _check_batch(q, k, v, o, q_code, seqs, seq_lens, name):
+    _check_input(q, "q", 3)
+    _check_input(k, "k", 3)
+    _check_input(v, "v", 3)
+    _check_input(o, "o", 3)
+    _check_input(q_code, "q_code", 3)
+    batch = seqs.size(0)
+    _require(seqs.is_cuda and seqs.dtype == torch.int64 and seqs.is_contiguous() and seqs.dim() == 2 and seqs.size(1) == 4,
+             "seqs must be the int64 [batch, 4] array sequence_descriptors() makes")
+    _check_seq_len(seq_lens, batch)
+    _require(k.size(0) == batch and tuple(v.shape) == tuple(k.shape) and k.size(2) == 128 and k.dtype == q.dtype == v.dtype,
+             f"{name}: k, v must be [batch, H, 128] in q.dtype")
+    num_heads = k.size(1)
+    q_heads = q.size(1)
+    _require(q.size(0) == batch and q.size(2) == 128 and q_heads >= num_heads and q_heads % num_heads == 0
+             and tuple(o.shape) == tuple(q.shape) and o.dtype == q.dtype, f"{name}: q, o must be [batch, Hq, 128]")
+    _require(q_code.element_size() == 2 and q_code.numel() == batch * q_heads * 16, "q_code must be [batch, Hq, 16] 16-bit")
+    return batch, num_heads, q_heads
+
+
+def decode_step_batch_dev(q, k, v, o, q_code, seqs: torch.Tensor, seq_lens: torch.Tensor, max_seq_len: int,
+                          page_size: int, budget: int, dist_scratch: torch.Tensor, hist: torch.Tensor,
+                          indices_out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
+                          scale: Optional[float] = None, thresholds=None, rope=None) -> None:
+    """decode_step_dev for several sequences in the same launches.  q, o [batch, Hq, 128]; k, v
+    [batch, H, 128]; q_code [batch, Hq, 16]; seqs: sequence_descriptors() of this layer; seq_lens int32
+    [batch]; dist_scratch 16-bit [batch * Hq, >= max_seq_len - 1]; hist: histogram_scratch(batch * Hq);
+    indices_out int32 [batch * Hq, >= budget - 1]."""
+    batch, num_heads, q_heads = _check_batch(q, k, v, o, q_code, seqs, seq_lens, "decode_step_batch_dev")
+    _check_rows(dist_scratch, "dist_scratch")
+    rows = batch * q_heads
+    _require(dist_scratch.element_size() == 2 and dist_scratch.size(0) == rows and dist_scratch.size(1) >= max_seq_len - 1,
+             "dist_scratch must be 16-bit [batch * Hq, >= max_seq_len - 1]")
+    out_stride = 0
+    if indices_out is not None:
+        _check_rows(indices_out, "indices_out")
+        _require(indices_out.dtype == torch.int32 and indices_out.size(0) == rows and indices_out.size(1) >= budget - 1,
+                 "indices_out must be int32 [batch * Hq, >= budget - 1]")
+        out_stride = indices_out.stride(0)
+    if lse is not None:
+        _require(lse.is_cuda and lse.dtype == torch.float32 and lse.numel() == rows and lse.is_contiguous(),
+                 "lse must be a contiguous float32 CUDA tensor of batch * Hq elements")
+    s = 1.0 / math.sqrt(128.0) if scale is None else float(scale)
+    rs, rt, inv_freq, mscale = _rope_args(rope)
+    _lib.check(lib.adamas_decode_step_batch_dev(
+        _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(lse), _ptr(q_code), _ptr(seqs), _ptr(seq_lens), batch,
+        int(max_seq_len), num_heads, q_heads, 128, int(page_size), _dtype_code(k.dtype, "decode_step_batch_dev"),
+        int(budget), _ptr(dist_scratch), dist_scratch.stride(0), _ptr(_check_hist(hist, rows)), _ptr(indices_out),
+        out_stride, s, _lib.thresholds_arg(thresholds), rs, rt, _ptr(inv_freq), mscale, 1.0 / math.sqrt(128.0),
+        _stream()), "decode_step_batch_dev")
 
 
 def apply_rope_table_in_place(q: torch.Tensor, k: torch.Tensor, past_kv_len: int, inv_freq: torch.Tensor,

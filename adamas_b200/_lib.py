@@ -44,7 +44,7 @@ SIGNATURES = {
     "adamas_topk": [_P, _I, _L, _I, _P, _L, _I, _I, _I, _P, _P, _L, _P],
     "adamas_decode_handler_create": [POINTER(c_void_p)],
     "adamas_decode_handler_destroy": [_P],
-    "adamas_decode_begin_forward": [_P, _L, _I, _I, _I, _I, _I, _P],
+    "adamas_decode_begin_forward": [_P, _L, _I, _I, _I, _I, _I, _I, _P],
     "adamas_decode_end_forward": [_P],
     "adamas_decode_forward": [_P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _P],
     "adamas_decode_forward_partial": [_P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _P],
@@ -58,7 +58,11 @@ SIGNATURES = {
                                _P, _L, _P, _P, _L, _F, _FP, _F, _F, _P, _F, _F, _P],
     "adamas_dense_step_dev": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
                               _F, _FP, _F, _F, _P, _F, _F, _P],
-    "adamas_seq_len_advance": [_P, _I, _P],
+    "adamas_seq_len_advance": [_P, _I, _I, _P],
+    "adamas_decode_step_batch_dev": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
+                                     _P, _L, _P, _P, _L, _F, _FP, _F, _F, _P, _F, _F, _P],
+    "adamas_dense_step_batch_dev": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
+                                    _F, _FP, _F, _F, _P, _F, _F, _P],
     "adamas_hist_rowsum": [_P, _I, _I, _P, _P],
     "adamas_global_cut": [_P, _I, _I, _I, _I, _P, _P],
     "adamas_apply_rope_table_in_place": [_P, _P, _L, _I, _I, _I, _L, _P, _F, _I, _P],

@@ -7,6 +7,7 @@
 #include <atomic>
 #include <cmath>
 #include <cstdarg>
+#include <cstddef>
 #include <cstdlib>
 #include <cstdio>
 #include <cstring>
@@ -386,13 +387,15 @@ static int append_decode_impl(const void* k, const void* v, const void* qh, cons
                               int code_last_page_len, int num_heads, int head_dim, int page_size,
                               float scale, const float* thresholds3_host, int dtype,
                               adamas_stream_t stream, const RopeSpec& rope = RopeSpec(),
-                              const int32_t* seq_len_dev = nullptr, int q_heads = 0) {
+                              const int32_t* seq_len_dev = nullptr, int q_heads = 0,
+                              const SeqDesc* seqs = nullptr, int batch = 1) {
   if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
   if (q_heads == 0) q_heads = num_heads;
   if (int rc = check_q_heads(num_heads, q_heads)) return rc;
   ADAMAS_REQUIRE(q_heads == num_heads || fused, "grouped-query attention needs the fused append (q, k, v)");
-  ADAMAS_REQUIRE(k && v && qh && kh && q_code_out && kv_data && code_data && kv_page_table &&
-                     code_page_table, "null pointer");
+  ADAMAS_REQUIRE(k && v && qh && kh && q_code_out, "null pointer");
+  ADAMAS_REQUIRE(seqs || (kv_data && code_data && kv_page_table && code_page_table), "null pointer");
+  ADAMAS_REQUIRE(!seqs || (fused && seq_len_dev && batch >= 1), "a batched append needs the fused form and device lengths");
   ADAMAS_REQUIRE(!rope.on || rope.inv_freq || (rope.scale > 0.f && rope.theta > 0.f),
                  "rope_scale and rope_theta must be positive");
   ADAMAS_REQUIRE(!rope.on || fused, "the rotary embedding needs the fused append");
@@ -415,11 +418,11 @@ static int append_decode_impl(const void* k, const void* v, const void* qh, cons
   const float pos = static_cast<float>(static_cast<int64_t>(kv_num_pages - 1) * page_size + kv_last_page_len - 1);
   const RopeParams rp{rope.scale > 0.f ? 1.0f / rope.scale : 1.f, rope.theta, rope.inv_freq, rope.mscale};
 #define LAUNCH_AD(T, F, R)                                                                            \
-  ADAMAS_LAUNCH("append_decode_kernel", (append_decode_kernel<T, F, R>), dim3(blocks), dim3(256), 0,  \
+  ADAMAS_LAUNCH("append_decode_kernel", (append_decode_kernel<T, F, R>), dim3(blocks, seqs ? batch : 1), dim3(256), 0,  \
                 st, 1, static_cast<const T*>(k), static_cast<const T*>(v), static_cast<const T*>(qh), \
                 static_cast<const T*>(kh), static_cast<uint16_t*>(q_code_out), tgt, kv_num_pages - 1, \
                 kv_last_page_len - 1, code_num_pages - 1, code_last_page_len - 1, scale, th, pos, rp, \
-                seq_len_dev, q_heads)
+                seq_len_dev, q_heads, seqs)
   if (dtype == ADAMAS_F16) {
     if (rope.on) LAUNCH_AD(__half, true, true);
     else if (fused) LAUNCH_AD(__half, true, false);
@@ -551,10 +554,13 @@ int adamas_append_prefill(const void* k, const void* v, const void* h, int64_t n
 // num_heads: heads of the code cache; q_heads: rows of q_code / out / hist (a multiple of num_heads).
 static int estimate_impl(const void* q_code, const void* code_data, const int32_t* code_page_table, int n,
                          int page_size, int num_heads, int q_heads, void* out, int64_t out_stride, int out_format,
-                         int metric, const int32_t* seq_len_dev, uint32_t* hist, int hist_cl, adamas_stream_t stream) {
+                         int metric, const int32_t* seq_len_dev, uint32_t* hist, int hist_cl, adamas_stream_t stream,
+                         const SeqDesc* seqs = nullptr, int batch = 1) {
   if (int rc = check_q_heads(num_heads, q_heads)) return rc;
+  if (!seqs) batch = 1;
   const int q_group = q_heads / num_heads;
-  ADAMAS_REQUIRE(q_code && code_data && code_page_table && out, "null pointer");
+  ADAMAS_REQUIRE(q_code && out && (seqs || (code_data && code_page_table)), "null pointer");
+  ADAMAS_REQUIRE(!seqs || seq_len_dev, "a batched estimate needs device lengths");
   ADAMAS_REQUIRE(out_stride >= n, "out_stride (%lld) smaller than the row length (%d)",
                  static_cast<long long>(out_stride), n);
   ADAMAS_REQUIRE((reinterpret_cast<uintptr_t>(q_code) & 15) == 0 &&
@@ -576,7 +582,7 @@ static int estimate_impl(const void* q_code, const void* code_data, const int32_
                    "page too large for the estimate kernel");
     const int per_sm = std::min(est_blocks_per_sm(),
                                 (smem + 1024 + kEstPagesStatic) * 2 <= static_cast<size_t>(di->max_smem_optin) ? 2 : 1);
-    const unsigned blocks = static_cast<unsigned>(std::min(num_tiles, di->num_sms * per_sm));
+    const unsigned blocks = static_cast<unsigned>(std::min(num_tiles, std::max(1, di->num_sms * per_sm / batch)));
     EstimatePagesParams pp;
     pp.codes = static_cast<const uint4*>(code_data);
     pp.page_table = code_page_table;
@@ -592,8 +598,9 @@ static int estimate_impl(const void* q_code, const void* code_data, const int32_
     pp.seq_len_dev = seq_len_dev;
     pp.hist = hist;
     pp.hist_cl = hist_cl;
+    pp.seqs = seqs;
 #define LAUNCH_ESTP(M, OT) \
-  ADAMAS_LAUNCH("estimate_pages_kernel", (estimate_pages_kernel<M, OT>), dim3(blocks), dim3(kEstPagesThreads), smem, st, 1, pp)
+  ADAMAS_LAUNCH("estimate_pages_kernel", (estimate_pages_kernel<M, OT>), dim3(blocks, batch), dim3(kEstPagesThreads), smem, st, 1, pp)
     if (metric == ADAMAS_METRIC_L1) {
       if (out_format == ADAMAS_VAL_F16) LAUNCH_ESTP(0, __half); else LAUNCH_ESTP(0, uint16_t);
     } else {
@@ -615,8 +622,9 @@ static int estimate_impl(const void* q_code, const void* code_data, const int32_
   ADAMAS_REQUIRE(smem <= static_cast<size_t>(di->max_smem_optin - 1024),
                  "num_heads (%d) too large for the estimate kernel", num_heads);
   const int per_sm = std::min(est_blocks_per_sm(), (smem + 1024) * 2 <= static_cast<size_t>(di->max_smem_optin) ? 2 : 1);
-  const unsigned blocks = static_cast<unsigned>(std::min(num_tiles, di->num_sms * per_sm));
+  const unsigned blocks = static_cast<unsigned>(std::min(num_tiles, std::max(1, di->num_sms * per_sm / batch)));
   EstimateParams prm;
+  prm.seqs = seqs;
   prm.codes = static_cast<const uint4*>(code_data);
   prm.page_table = code_page_table;
   prm.q_code = static_cast<const uint4*>(q_code);
@@ -635,13 +643,13 @@ static int estimate_impl(const void* q_code, const void* code_data, const int32_
 #define LAUNCH_EST(M, OT)                                                                      \
   do {                                                                                         \
     if (in_regs && hpw == 1)                                                                   \
-      ADAMAS_LAUNCH("estimate_kernel", estimate_kernel<M, OT, 1>, dim3(blocks), dim3(kEstThreads), smem, st, 1, prm);                       \
+      ADAMAS_LAUNCH("estimate_kernel", estimate_kernel<M, OT, 1>, dim3(blocks, batch), dim3(kEstThreads), smem, st, 1, prm);                       \
     else if (in_regs && hpw == 2)                                                              \
-      ADAMAS_LAUNCH("estimate_kernel", estimate_kernel<M, OT, 2>, dim3(blocks), dim3(kEstThreads), smem, st, 1, prm);                       \
+      ADAMAS_LAUNCH("estimate_kernel", estimate_kernel<M, OT, 2>, dim3(blocks, batch), dim3(kEstThreads), smem, st, 1, prm);                       \
     else if (in_regs && hpw == 4)                                                              \
-      ADAMAS_LAUNCH("estimate_kernel", estimate_kernel<M, OT, 4>, dim3(blocks), dim3(kEstThreads), smem, st, 1, prm);                       \
+      ADAMAS_LAUNCH("estimate_kernel", estimate_kernel<M, OT, 4>, dim3(blocks, batch), dim3(kEstThreads), smem, st, 1, prm);                       \
     else                                                                                       \
-      ADAMAS_LAUNCH("estimate_kernel", estimate_kernel<M, OT, 0>, dim3(blocks), dim3(kEstThreads), smem, st, 1, prm);                       \
+      ADAMAS_LAUNCH("estimate_kernel", estimate_kernel<M, OT, 0>, dim3(blocks, batch), dim3(kEstThreads), smem, st, 1, prm);                       \
   } while (0)
   if (metric == ADAMAS_METRIC_L1) {
     if (out_format == ADAMAS_VAL_F16) LAUNCH_EST(0, __half); else LAUNCH_EST(0, uint16_t);
@@ -790,6 +798,7 @@ struct adamas_decode_handler {
   bool forward_started = false;
   int num_heads = 0, page_size = 0, dtype = 0;   // num_heads: query heads (rows of q, o and the index lists)
   int kv_heads = 0;                              // heads of the KV cache (num_heads / kv_heads query heads share one)
+  int batch = 1;                                 // sequences a batched dense step may carry (sizes the scratch)
 };
 
 namespace {
@@ -843,9 +852,10 @@ int adamas_decode_handler_destroy(adamas_decode_handler_t* handler) {
   return ADAMAS_OK;
 }
 
-int adamas_decode_begin_forward(adamas_decode_handler_t* handler, int64_t max_tokens, int num_heads,
+int adamas_decode_begin_forward(adamas_decode_handler_t* handler, int64_t max_tokens, int batch, int num_heads,
                                 int num_q_heads, int head_dim, int page_size, int dtype, adamas_stream_t stream) {
   ADAMAS_REQUIRE(handler, "null handler");
+  ADAMAS_REQUIRE(batch >= 1 && batch <= 1024, "batch out of range (%d)", batch);
   if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
   if (int rc = check_q_heads(num_heads, num_q_heads)) return rc;
   const int kv_heads = num_heads;
@@ -863,11 +873,12 @@ int adamas_decode_begin_forward(adamas_decode_handler_t* handler, int64_t max_to
   // The planner never gives a head more than ceil(4 * SMs / H) splits, so H * splits <= 4 * SMs + H
   // whatever the length: sized once for that bound, the scratch never has to grow while the head count
   // stays (a regrow costs a stream synchronisation and a cudaFree / cudaMalloc pair).
-  const int64_t units = static_cast<int64_t>(4) * handler->num_sms + num_heads;
-  if (units > handler->cap_units || num_heads > handler->cap_heads) {
+  const int rows = num_heads * batch;
+  const int64_t units = static_cast<int64_t>(4) * handler->num_sms + rows;
+  if (units > handler->cap_units || rows > handler->cap_heads) {
     size_t off_ml, off_cnt;
     const int64_t new_units = units > handler->cap_units ? units : handler->cap_units;
-    const int new_heads = num_heads > handler->cap_heads ? num_heads : handler->cap_heads;
+    const int new_heads = rows > handler->cap_heads ? rows : handler->cap_heads;
     const size_t bytes = scratch_layout(new_units, new_heads, &off_ml, &off_cnt);
     if (handler->scratch) {
       // earlier launches on this stream may still use the old buffer
@@ -886,6 +897,7 @@ int adamas_decode_begin_forward(adamas_decode_handler_t* handler, int64_t max_to
   handler->forward_started = true;
   handler->num_heads = num_heads;
   handler->kv_heads = kv_heads;
+  handler->batch = batch;
   handler->page_size = page_size;
   handler->dtype = dtype;
   return ADAMAS_OK;
@@ -904,12 +916,16 @@ static int decode_forward_impl(adamas_decode_handler_t* handler, const void* q, 
                                float* lse, const void* kv_data, const int32_t* indices,
                                int64_t idx_stride, int n_idx, int idx_unit, int last_page_idx,
                                int last_page_len, int tail_len, float sm_scale,
-                               adamas_stream_t stream, const int32_t* seq_len_dev = nullptr) {
+                               adamas_stream_t stream, const int32_t* seq_len_dev = nullptr,
+                               const SeqDesc* seqs = nullptr, int batch = 1) {
   ADAMAS_REQUIRE(handler, "null handler");
   if (!handler->forward_started)
     return fail(ADAMAS_ERR_STATE, "decode forward called before begin_forward");
-  ADAMAS_REQUIRE(q && (o || o_f32) && kv_data, "null pointer");
-  ADAMAS_REQUIRE(n_idx >= 0 && (n_idx == 0 || indices), "indices missing");
+  ADAMAS_REQUIRE(q && (o || o_f32) && (kv_data || seqs), "null pointer");
+  ADAMAS_REQUIRE(n_idx >= 0 && (n_idx == 0 || indices || seqs), "indices missing");
+  ADAMAS_REQUIRE(!seqs || (seq_len_dev && batch >= 1 && batch <= handler->batch),
+                 "a batched dense step needs device lengths and a handler planned for the batch");
+  if (!seqs) batch = 1;
   const int ps = handler->page_size;
   ADAMAS_REQUIRE(idx_unit == 1 || idx_unit == ps, "idx_unit must be 1 or page_size");
   ADAMAS_REQUIRE(tail_len >= 0 && tail_len <= last_page_len && last_page_len <= ps,
@@ -921,8 +937,8 @@ static int decode_forward_impl(adamas_decode_handler_t* handler, const void* q, 
   ADAMAS_REQUIRE(idx_stride == 0 || idx_stride >= n_idx || handler->num_heads == 1,
                  "idx_stride must be 0 (shared row) or >= n_idx");
   const int H = handler->num_heads;
-  const SplitPlan p = plan_splits(n_tokens, H, handler->num_sms);
-  if (static_cast<int64_t>(H) * p.num_splits > handler->cap_units)
+  const SplitPlan p = plan_splits(n_tokens, H * batch, handler->num_sms);
+  if (static_cast<int64_t>(H) * batch * p.num_splits > handler->cap_units)
     return fail(ADAMAS_ERR_STATE,
                 "decode forward needs %d splits per head but begin_forward planned for fewer tokens",
                 p.num_splits);
@@ -935,6 +951,7 @@ static int decode_forward_impl(adamas_decode_handler_t* handler, const void* q, 
   prm.lse = lse;
   prm.kv = kv_data;
   prm.indices = indices ? indices : reinterpret_cast<const int32_t*>(kv_data);
+  prm.seqs = seqs;
   prm.idx_stride = idx_stride;
   prm.n_idx = n_idx;
   prm.idx_unit = idx_unit;
@@ -960,7 +977,7 @@ static int decode_forward_impl(adamas_decode_handler_t* handler, const void* q, 
   prm.seq_len_dev = seq_len_dev;
   // (with the length on the device a block may get more than one tile later on: two stages)
   const size_t smem = static_cast<size_t>(p.tiles_per_block > 1 || seq_len_dev ? 2 : 1) * kDecStageBytes;
-  dim3 grid(p.num_splits, H);
+  dim3 grid(p.num_splits, H, batch);
   if (handler->dtype == ADAMAS_F16)
     ADAMAS_LAUNCH("sparse_decode_kernel", sparse_decode_kernel<__half>, grid, dim3(kDecThreads), smem,
                   to_stream(stream), 1, prm);
@@ -1061,6 +1078,7 @@ int adamas_decode_forward_static(const void* q, void* o, float* lse, const void*
   prm.page_size = page_size;
   prm.H = num_heads;
   prm.q_group = 1;
+  prm.seqs = nullptr;
   const int64_t tail0 = static_cast<int64_t>(last_page_idx) * page_size + (last_page_len - tail_len);
   ADAMAS_REQUIRE(tail0 + tail_len < (int64_t(1) << 31), "token slots must be below 2^31");
   prm.tail_slot0 = static_cast<unsigned>(tail0);
@@ -1092,20 +1110,21 @@ int adamas_decode_forward_static(const void* q, void* o, float* lse, const void*
 namespace {
 
 template <typename T, int I>
-int launch_select_attend_one(const SelectAttendParams& prm, int cl, int num_heads, size_t smem, cudaStream_t st) {
-  const dim3 grid(static_cast<unsigned>(cl), static_cast<unsigned>(num_heads));
+int launch_select_attend_one(const SelectAttendParams& prm, int cl, int num_heads, int batch, size_t smem,
+                             cudaStream_t st) {
+  const dim3 grid(static_cast<unsigned>(cl), static_cast<unsigned>(num_heads), static_cast<unsigned>(batch));
   ADAMAS_LAUNCH("select_attend_kernel", (select_attend_kernel<T, I>), grid, dim3(kSaThreads), smem, st, 1, prm);
   return check_launch("select_attend_kernel");
 }
 
 template <typename T>
-int launch_select_attend(const SelectAttendParams& prm, int items, int cl, int num_heads, size_t smem,
+int launch_select_attend(const SelectAttendParams& prm, int items, int cl, int num_heads, int batch, size_t smem,
                          cudaStream_t st) {
   switch (items) {
-    case 1: return launch_select_attend_one<T, 1>(prm, cl, num_heads, smem, st);
-    case 2: return launch_select_attend_one<T, 2>(prm, cl, num_heads, smem, st);
-    case 4: return launch_select_attend_one<T, 4>(prm, cl, num_heads, smem, st);
-    case 8: return launch_select_attend_one<T, 8>(prm, cl, num_heads, smem, st);
+    case 1: return launch_select_attend_one<T, 1>(prm, cl, num_heads, batch, smem, st);
+    case 2: return launch_select_attend_one<T, 2>(prm, cl, num_heads, batch, smem, st);
+    case 4: return launch_select_attend_one<T, 4>(prm, cl, num_heads, batch, smem, st);
+    case 8: return launch_select_attend_one<T, 8>(prm, cl, num_heads, batch, smem, st);
     default: break;
   }
   return fail(ADAMAS_ERR_INVALID, "unsupported row length for select_attend");
@@ -1167,8 +1186,10 @@ int select_attend_impl(const void* dist, int64_t dist_stride, int n, int k, cons
                        float* lse, const void* kv_data, const int32_t* kv_page_table, int page_size, int num_heads,
                        int q_heads, int dtype, int tail_mode, unsigned tail_slot, uint32_t* hist, const int32_t* ext_cut,
                        const int32_t* seq_len_dev, int32_t* out_idx, int64_t out_stride, float sm_scale,
-                       const SaPlan& pl, adamas_stream_t stream) {
+                       const SaPlan& pl, adamas_stream_t stream, const SeqDesc* seqs = nullptr, int batch = 1) {
   SelectAttendParams prm;
+  prm.seqs = seqs;
+  if (!seqs) batch = 1;
   prm.dist = static_cast<const uint16_t*>(dist);
   prm.dist_stride = dist_stride;
   prm.hist = hist;
@@ -1193,8 +1214,8 @@ int select_attend_impl(const void* dist, int64_t dist_stride, int n, int k, cons
   prm.list_capacity = pl.list_capacity;
   prm.scale_log2 = sm_scale * 1.4426950408889634f;
   if (dtype == ADAMAS_F16)
-    return launch_select_attend<__half>(prm, pl.items, pl.cl, q_heads, pl.smem, to_stream(stream));
-  return launch_select_attend<__nv_bfloat16>(prm, pl.items, pl.cl, q_heads, pl.smem, to_stream(stream));
+    return launch_select_attend<__half>(prm, pl.items, pl.cl, q_heads, batch, pl.smem, to_stream(stream));
+  return launch_select_attend<__nv_bfloat16>(prm, pl.items, pl.cl, q_heads, batch, pl.smem, to_stream(stream));
 }
 
 static_assert(ADAMAS_HIST_WORDS_PER_HEAD == kSaScratchWordsPerHead, "scratch layout of select_attend");
@@ -1202,7 +1223,9 @@ size_t hist_bytes(int num_heads) {
   return static_cast<size_t>(num_heads) * ADAMAS_HIST_WORDS_PER_HEAD * sizeof(uint32_t);
 }
 
-__global__ void seq_len_advance_kernel(int32_t* seq_len, int delta) { *seq_len += delta; }
+__global__ void seq_len_advance_kernel(int32_t* seq_len, int count, int delta) {
+  if (static_cast<int>(threadIdx.x) < count) seq_len[threadIdx.x] += delta;
+}
 
 }  // namespace
 
@@ -1279,11 +1302,12 @@ int adamas_global_cut(const uint32_t* all_hists, int num_shards, int shard, int 
   return check_launch("global_cut_kernel");
 }
 
-int adamas_seq_len_advance(int32_t* seq_len_dev, int delta, adamas_stream_t stream) {
+int adamas_seq_len_advance(int32_t* seq_len_dev, int count, int delta, adamas_stream_t stream) {
   ADAMAS_REQUIRE(seq_len_dev, "null pointer");
+  ADAMAS_REQUIRE(count >= 1 && count <= 1024, "count out of range (%d)", count);
   // an ordinary launch: it completes before anything that follows it in the stream starts
-  ADAMAS_LAUNCH("seq_len_advance_kernel", seq_len_advance_kernel, dim3(1), dim3(1), 0, to_stream(stream), -1,
-                seq_len_dev, delta);
+  ADAMAS_LAUNCH("seq_len_advance_kernel", seq_len_advance_kernel, dim3(1), dim3(static_cast<unsigned>((count + 31) / 32 * 32)),
+                0, to_stream(stream), -1, seq_len_dev, count, delta);
   return check_launch("seq_len_advance_kernel");
 }
 
@@ -1294,13 +1318,15 @@ static int estimate_append_launch(const void* q, const void* k, const void* v, v
                                   void* code_data, const int32_t* code_page_table, int code_num_pages,
                                   int code_last_page_len, int n, int num_heads, int page_size, int dtype, void* dist,
                                   int64_t dist_stride, float hadamard_scale, const float* thresholds3_host,
-                                  const int32_t* seq_len_dev, uint32_t* hist, int hist_cl, adamas_stream_t stream) {
-  ADAMAS_REQUIRE(q && k && v && q_code && kv_data && code_data && kv_page_table && code_page_table && dist,
+                                  const int32_t* seq_len_dev, uint32_t* hist, int hist_cl, adamas_stream_t stream,
+                                  const SeqDesc* seqs = nullptr, int batch = 1) {
+  ADAMAS_REQUIRE(q && k && v && q_code && dist && (seqs || (kv_data && code_data && kv_page_table && code_page_table)),
                  "null pointer");
+  if (!seqs) batch = 1;
   ADAMAS_REQUIRE(n >= 1 && n < 2147483647 - kEstTile, "sequence length out of range");
   ADAMAS_REQUIRE(dist_stride >= n, "dist_stride (%lld) smaller than the row length (%d)",
                  static_cast<long long>(dist_stride), n);
-  ADAMAS_REQUIRE((reinterpret_cast<uintptr_t>(code_data) & 15) == 0 && (reinterpret_cast<uintptr_t>(q) & 15) == 0 &&
+  ADAMAS_REQUIRE((seqs || (reinterpret_cast<uintptr_t>(code_data) & 15) == 0) && (reinterpret_cast<uintptr_t>(q) & 15) == 0 &&
                      (reinterpret_cast<uintptr_t>(k) & 15) == 0 && (reinterpret_cast<uintptr_t>(v) & 15) == 0,
                  "q, k, v and code_data must be 16-byte aligned");
   ADAMAS_REQUIRE(!hist || (hist_cl >= 1 && hist_cl <= kSaMaxSlices), "histogram slices out of range (%d)", hist_cl);
@@ -1313,8 +1339,9 @@ static int estimate_append_launch(const void* q, const void* k, const void* v, v
                  "num_heads (%d) too large", num_heads);
   const int per_sm = std::min(est_blocks_per_sm(),
                               (smem + 1024 + kEstAppendStatic) * 2 <= static_cast<size_t>(di->max_smem_optin) ? 2 : 1);
-  const unsigned blocks = static_cast<unsigned>(std::min(num_tiles, di->num_sms * per_sm));
+  const unsigned blocks = static_cast<unsigned>(std::min(num_tiles, std::max(1, di->num_sms * per_sm / batch)));
   EstimateParams prm;
+  prm.seqs = seqs;
   prm.codes = static_cast<const uint4*>(code_data);
   prm.page_table = code_page_table;
   prm.q_code = nullptr;
@@ -1345,7 +1372,7 @@ static int estimate_append_launch(const void* q, const void* k, const void* v, v
   ap.th = make_thresholds(thresholds3_host);
   cudaStream_t st = to_stream(stream);
 #define LAUNCH_ESTA(T, HPW)                                                                        \
-  ADAMAS_LAUNCH("estimate_append_kernel", (estimate_append_kernel<T, HPW>), dim3(blocks),          \
+  ADAMAS_LAUNCH("estimate_append_kernel", (estimate_append_kernel<T, HPW>), dim3(blocks, batch),   \
                 dim3(kEstThreads), smem, st, 1, prm, ap)
 #define LAUNCH_ESTA_T(T)                  \
   do {                                    \
@@ -1392,10 +1419,12 @@ static int decode_step_impl(void* q, void* k, const void* v, void* o, float* lse
                             void* dist_scratch,
                             int64_t dist_stride, uint32_t* hist, int32_t* out_idx, int64_t out_stride,
                             float hadamard_scale, const float* thresholds3_host, const RopeSpec& rope,
-                            float sm_scale, adamas_stream_t stream) {
+                            float sm_scale, adamas_stream_t stream, const SeqDesc* seqs = nullptr, int batch = 1) {
   if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
   if (int rc = check_q_heads(num_heads, q_heads)) return rc;
-  ADAMAS_REQUIRE(kv_page_table && code_page_table, "page table missing");
+  ADAMAS_REQUIRE(seqs || (kv_page_table && code_page_table), "page table missing");
+  ADAMAS_REQUIRE(!seqs || (seq_len_dev && batch >= 1 && batch <= 1024), "a batched step needs device lengths");
+  if (!seqs) batch = 1;
   ADAMAS_REQUIRE(budget >= 2 && seq_len > budget,
                  "a decode step needs budget >= 2 and a context longer than the budget (%lld vs %d); "
                  "shorter contexts attend to every page through adamas_decode_forward",
@@ -1404,14 +1433,14 @@ static int decode_step_impl(void* q, void* k, const void* v, void* o, float* lse
   ADAMAS_REQUIRE(q && o && dist_scratch && q_code && hist, "null pointer");
   ADAMAS_REQUIRE((reinterpret_cast<uintptr_t>(dist_scratch) & 15) == 0 && (dist_stride * 2) % 16 == 0,
                  "distance rows must start on 16-byte boundaries");
-  ADAMAS_REQUIRE(out_idx == nullptr || out_stride >= budget - 1 || q_heads == 1, "out_stride smaller than budget - 1");
+  ADAMAS_REQUIRE(out_idx == nullptr || out_stride >= budget - 1 || q_heads * batch == 1, "out_stride smaller than budget - 1");
   const int n = static_cast<int>(seq_len - 1);
   const int pages = static_cast<int>((seq_len + page_size - 1) / page_size);
   const int last_len = static_cast<int>(seq_len - static_cast<int64_t>(pages - 1) * page_size);
   const DeviceInfo* di = nullptr;
   if (int rc = get_device_info(&di)) return rc;
   SaPlan pl;
-  if (int rc = sa_plan(n, budget - 1, q_heads, di, &pl)) return rc;
+  if (int rc = sa_plan(n, budget - 1, q_heads * batch, di, &pl)) return rc;
   int rc;
   // (16 heads: the page-copy estimate after a separate append is faster than the fused kernel's 512-byte
   // copies per token)
@@ -1420,24 +1449,25 @@ static int decode_step_impl(void* q, void* k, const void* v, void* o, float* lse
     // block of the estimate would repeat the rotation, which costs more than the append launch.
     rc = estimate_append_launch(q, k, v, q_code, kv_data, kv_page_table, pages, last_len, code_data,
                                 code_page_table, pages, last_len, n, num_heads, page_size, dtype, dist_scratch,
-                                dist_stride, hadamard_scale, thresholds3_host, seq_len_dev, hist, pl.cl, stream);
+                                dist_stride, hadamard_scale, thresholds3_host, seq_len_dev, hist, pl.cl, stream, seqs,
+                                batch);
     if (rc) return rc;
   } else {
     rc = append_decode_impl(k, v, q, k, true, q_code, kv_data, kv_page_table, pages, last_len, code_data,
                             code_page_table, pages, last_len, num_heads, head_dim, page_size, hadamard_scale,
-                            thresholds3_host, dtype, stream, rope, seq_len_dev, q_heads);
+                            thresholds3_host, dtype, stream, rope, seq_len_dev, q_heads, seqs, batch);
     if (rc) return rc;
     rc = estimate_impl(q_code, code_data, code_page_table, n, page_size, num_heads, q_heads, dist_scratch,
-                       dist_stride, ADAMAS_VAL_U16, ADAMAS_METRIC_L1, seq_len_dev, hist, pl.cl, stream);
+                       dist_stride, ADAMAS_VAL_U16, ADAMAS_METRIC_L1, seq_len_dev, hist, pl.cl, stream, seqs, batch);
     if (rc) return rc;
   }
   const int64_t tail = static_cast<int64_t>(kv_last_page_idx) * page_size + last_len - 1;
   rc = select_attend_impl(dist_scratch, dist_stride, n, budget - 1, q, o, nullptr, lse, kv_data, kv_page_table,
                           page_size, num_heads, q_heads, dtype, seq_len_dev ? 2 : 1, static_cast<unsigned>(tail), hist, nullptr,
-                          seq_len_dev, out_idx, out_stride, sm_scale, pl, stream);
+                          seq_len_dev, out_idx, out_stride, sm_scale, pl, stream, seqs, batch);
   if (rc) {
     // the estimate has filled the histogram table and nothing will clear it: restore the all-zero state
-    cudaMemsetAsync(hist, 0, hist_bytes(q_heads), to_stream(stream));
+    cudaMemsetAsync(hist, 0, hist_bytes(q_heads * batch), to_stream(stream));
   }
   return rc;
 }
@@ -1519,6 +1549,55 @@ int adamas_dense_step_dev(adamas_decode_handler_t* handler, void* q, void* k, co
     return rc;
   return decode_forward_impl(handler, q, o, nullptr, lse, kv_data, kv_page_table, 0, pages - 1, page_size, 0,
                              last_len, last_len, sm_scale, stream, seq_len_dev);
+}
+
+static_assert(sizeof(adamas_seq_desc_t) == sizeof(SeqDesc) && offsetof(adamas_seq_desc_t, code_page_table) == offsetof(SeqDesc, code_table),
+              "sequence descriptor layout");
+
+int adamas_decode_step_batch_dev(void* q, void* k, const void* v, void* o, float* lse, void* q_code,
+                                 const adamas_seq_desc_t* seqs_dev, const int32_t* seq_lens_dev, int batch,
+                                 int max_seq_len, int num_heads, int num_q_heads, int head_dim, int page_size,
+                                 int dtype, int budget, void* dist_scratch, int64_t dist_stride,
+                                 uint32_t* hist_scratch, int32_t* out_idx, int64_t out_stride, float hadamard_scale,
+                                 const float* thresholds3_host, float rope_scale, float rope_theta,
+                                 const float* rope_inv_freq, float rope_mscale, float sm_scale,
+                                 adamas_stream_t stream) {
+  ADAMAS_REQUIRE(seqs_dev && seq_lens_dev, "null pointer");
+  ADAMAS_REQUIRE(batch >= 1 && batch <= 1024, "batch out of range (%d)", batch);
+  ADAMAS_REQUIRE(page_size >= 1 && max_seq_len >= 1, "page_size and max_seq_len must be >= 1");
+  return decode_step_impl(q, k, v, o, lse, q_code, nullptr, nullptr, 0, nullptr, nullptr, max_seq_len, seq_lens_dev,
+                          num_heads, num_q_heads, head_dim, page_size, dtype, budget, dist_scratch, dist_stride,
+                          hist_scratch, out_idx, out_stride, hadamard_scale, thresholds3_host,
+                          rope_from_args(rope_scale, rope_theta, rope_inv_freq, rope_mscale), sm_scale, stream,
+                          reinterpret_cast<const SeqDesc*>(seqs_dev), batch);
+}
+
+int adamas_dense_step_batch_dev(adamas_decode_handler_t* handler, void* q, void* k, const void* v, void* o,
+                                float* lse, void* q_code, const adamas_seq_desc_t* seqs_dev,
+                                const int32_t* seq_lens_dev, int batch, int max_seq_len, int num_heads,
+                                int num_q_heads, int head_dim, int page_size, int dtype, float hadamard_scale,
+                                const float* thresholds3_host, float rope_scale, float rope_theta,
+                                const float* rope_inv_freq, float rope_mscale, float sm_scale,
+                                adamas_stream_t stream) {
+  ADAMAS_REQUIRE(handler && seqs_dev && seq_lens_dev, "null pointer");
+  if (int rc = check_common(num_heads, head_dim, page_size, dtype)) return rc;
+  ADAMAS_REQUIRE(max_seq_len >= 1, "max_seq_len must be >= 1");
+  ADAMAS_REQUIRE(q && k && v && o && q_code, "null pointer");
+  if (!handler->forward_started)
+    return fail(ADAMAS_ERR_STATE, "dense step called before begin_forward");
+  ADAMAS_REQUIRE(handler->kv_heads == num_heads && handler->num_heads == num_q_heads &&
+                     handler->page_size == page_size && handler->dtype == dtype,
+                 "the handler was planned for another cache geometry");
+  const SeqDesc* seqs = reinterpret_cast<const SeqDesc*>(seqs_dev);
+  const int pages = (max_seq_len + page_size - 1) / page_size;
+  const int last_len = max_seq_len - (pages - 1) * page_size;
+  if (int rc = append_decode_impl(k, v, q, k, true, q_code, nullptr, nullptr, pages, last_len, nullptr, nullptr, pages,
+                                  last_len, num_heads, head_dim, page_size, hadamard_scale, thresholds3_host, dtype,
+                                  stream, rope_from_args(rope_scale, rope_theta, rope_inv_freq, rope_mscale),
+                                  seq_lens_dev, num_q_heads, seqs, batch))
+    return rc;
+  return decode_forward_impl(handler, q, o, nullptr, lse, nullptr, nullptr, 0, pages - 1, page_size, 0, last_len,
+                             last_len, sm_scale, stream, seq_lens_dev, seqs, batch);
 }
 
 int adamas_apply_rope_table_in_place(void* q, void* k, int64_t seq_len, int num_q_heads, int num_kv_heads,

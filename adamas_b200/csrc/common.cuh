@@ -7,6 +7,18 @@
 
 namespace adamas {
 
+// One sequence of a batched decode step: its caches and page tables.  An array of these lives in device
+// memory (one entry per sequence); a kernel of a batched launch picks its entry by a grid coordinate.
+// Everything else of a batched step (q, k, v, o, query codes, distances, histogram scratch, index lists)
+// is one contiguous array over (sequence, head) rows, and the sequence lengths are an int32 array.
+struct SeqDesc {
+  void* kv_data;
+  void* code_data;
+  const int32_t* kv_table;
+  const int32_t* code_table;
+};
+
+
 constexpr int kHeadDim = 128;           // the only head dimension the path supports
 constexpr int kCodeWords = kHeadDim / 8;  // 16-bit words per (token, head) code = 32 bytes
 

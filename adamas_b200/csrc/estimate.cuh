@@ -109,20 +109,38 @@ struct EstimateParams {
   // scratch table ([H][kSaScratchWordsPerHead] u32, rows zero on entry); slice = token / (8 * sa_granules_per_block(n_tokens, hist_cl))
   uint32_t* hist;
   int hist_cl;
+  // optional (needs seq_len_dev): a batch of sequences, grid.y = sequence, each with gridDim.x blocks.
+  // q_code, out and hist have one row per (sequence, head); codes, page table and length are the sequence's.
+  const SeqDesc* seqs;
 };
 
-// Lengths of this launch, from the host or from the device-resident sequence length.
+// What a block works on: lengths from the host or from the device-resident sequence length, and, in a
+// batched launch, its sequence's cache and first row.
 struct EstGeom {
   int n_tokens;
   int num_tiles;
   int slice_tokens;   // tokens per histogram slice (a multiple of 32)
+  const uint4* codes;
+  const int32_t* page_table;
+  int row0;           // first row of this sequence in q_code, out and hist
 };
 __device__ __forceinline__ EstGeom est_geom(const EstimateParams& p, int tile_span) {
   EstGeom g;
   g.n_tokens = p.n_tokens;
   g.num_tiles = p.num_tiles;
-  if (p.seq_len_dev) {
-    g.n_tokens = __ldg(p.seq_len_dev) - 1;
+  g.codes = p.codes;
+  g.page_table = p.page_table;
+  g.row0 = 0;
+  const int32_t* len = p.seq_len_dev;
+  if (p.seqs) {   // (the table of sequences is set up once, long before this launch)
+    const int b = blockIdx.y;
+    g.codes = static_cast<const uint4*>(p.seqs[b].code_data);
+    g.page_table = p.seqs[b].code_table;
+    g.row0 = b * p.H * p.q_group;
+    len += b;
+  }
+  if (len) {
+    g.n_tokens = __ldg(len) - 1;
     g.num_tiles = (g.n_tokens + tile_span - 1) / tile_span;
   }
   g.slice_tokens = p.hist ? 8 * sa_granules_per_block(g.n_tokens, p.hist_cl) : 1;
@@ -189,7 +207,7 @@ __device__ __forceinline__ void est_produce(const EstimateParams& p, const EstGe
     if (first_tl < tile_tokens) {
       int lp, e;
       est_token_slot(p, tile0 + first_tl, &lp, &e);
-      tok_first = static_cast<int64_t>(__ldg(p.page_table + lp)) * p.page_size + e;
+      tok_first = static_cast<int64_t>(__ldg(g.page_table + lp)) * p.page_size + e;
     }
     if (j >= kEstStages) {
       // every consumer warp has finished reading the tile that used this slot before
@@ -202,9 +220,9 @@ __device__ __forceinline__ void est_produce(const EstimateParams& p, const EstGe
       if (tl != first_tl) {
         int lp, e;
         est_token_slot(p, tile0 + tl, &lp, &e);
-        tok = static_cast<int64_t>(__ldg(p.page_table + lp)) * p.page_size + e;
+        tok = static_cast<int64_t>(__ldg(g.page_table + lp)) * p.page_size + e;
       }
-      bulk_copy_g2s(r.base + slot * r.stage_chunks + tl * r.row_chunks, p.codes + tok * r.cpt, token_bytes,
+      bulk_copy_g2s(r.base + slot * r.stage_chunks + tl * r.row_chunks, g.codes + tok * r.cpt, token_bytes,
                     &r.full_bar[slot]);
     }
     if (++slot == kEstStages) {
@@ -220,7 +238,8 @@ template <int METRIC, typename OutT, int HPW>
 __device__ __forceinline__ void est_consume(const EstimateParams& p, const EstGeom& g, const EstRing& r, int my_tiles,
                                             int lane, int warp, const QPlanes (&qp)[HPW > 0 ? HPW : 1][2],
                                             const QPlanes* sq) {
-  OutT* out = static_cast<OutT*>(p.out);
+  OutT* out = static_cast<OutT*>(p.out) + static_cast<int64_t>(g.row0) * p.out_stride;   // this sequence's rows
+  uint32_t* hist = p.hist ? p.hist + static_cast<size_t>(g.row0) * kSaScratchWordsPerHead : nullptr;
   const int H = p.H;
   const int tile_span = (HPW == 0) ? kEstTile * p.groups : kEstTile;
   int slot = 0;
@@ -247,7 +266,7 @@ __device__ __forceinline__ void est_consume(const EstimateParams& p, const EstGe
           o[static_cast<int64_t>(warp * HPW + hh) * p.out_stride] = dist_to_out<OutT>(d[hh]);
         if (p.hist) {
 #pragma unroll
-          for (int hh = 0; hh < HPW; ++hh) hist_count(p.hist, warp * HPW + hh, slice, d[hh]);
+          for (int hh = 0; hh < HPW; ++hh) hist_count(hist, warp * HPW + hh, slice, d[hh]);
         }
       }
     } else if (p.groups > 1) {
@@ -267,7 +286,7 @@ __device__ __forceinline__ void est_consume(const EstimateParams& p, const EstGe
       for (int rr = 0; rr < 2; ++rr)
         if (tl[rr] < tile_tokens) {
           out[static_cast<int64_t>(h) * p.out_stride + tile0 + tl[rr]] = dist_to_out<OutT>(d[rr]);
-          if (p.hist) hist_count(p.hist, h, (tile0 + tl[rr] - lane) / g.slice_tokens, d[rr]);
+          if (p.hist) hist_count(hist, h, (tile0 + tl[rr] - lane) / g.slice_tokens, d[rr]);
         }
     } else {
       const int rows = H * p.q_group;
@@ -276,7 +295,7 @@ __device__ __forceinline__ void est_consume(const EstimateParams& p, const EstGe
         const unsigned d = chunk_distance<METRIC>(row[2 * hc], sq[2 * h]) + chunk_distance<METRIC>(row[2 * hc + 1], sq[2 * h + 1]);
         if (lane < tile_tokens) {
           o[static_cast<int64_t>(h) * p.out_stride] = dist_to_out<OutT>(d);
-          if (p.hist) hist_count(p.hist, h, slice, d);
+          if (p.hist) hist_count(hist, h, slice, d);
         }
       }
     }
@@ -323,14 +342,15 @@ __global__ void __launch_bounds__(kEstThreads) estimate_kernel(const EstimatePar
   const int warp = tid >> 5;
   const EstRing ring = est_ring_init(est_smem, full_bar, empty_bar, p.H, tid, HPW == 0 ? p.groups : 1);
   QPlanes* sq = reinterpret_cast<QPlanes*>(est_smem + kEstStages * ring.stage_chunks);
+  const EstGeom geom = est_geom(p, HPW == 0 ? kEstTile * p.groups : kEstTile);
+  const uint4* q_code = p.q_code + 2 * geom.row0;   // this sequence's query codes
   if (HPW == 0) {
     // generic path: the query planes go through shared memory, so the query code (written by the
     // preceding append kernel) is needed before the block barrier
     grid_dependency_wait();
-    for (int c = tid; c < ring.cpt * p.q_group; c += kEstThreads) sq[c] = make_qplanes<METRIC>(__ldg(p.q_code + c));
+    for (int c = tid; c < ring.cpt * p.q_group; c += kEstThreads) sq[c] = make_qplanes<METRIC>(__ldg(q_code + c));
   }
   __syncthreads();
-  const EstGeom geom = est_geom(p, HPW == 0 ? kEstTile * p.groups : kEstTile);
   const int my_tiles = est_tiles_of_block(geom.num_tiles);
   if (warp >= kEstConsumerWarps) {
     est_produce<HPW == 0>(p, geom, ring, my_tiles, lane, warp - kEstConsumerWarps);
@@ -345,8 +365,8 @@ __global__ void __launch_bounds__(kEstThreads) estimate_kernel(const EstimatePar
   if (HPW > 0) {
 #pragma unroll
     for (int hh = 0; hh < HPW; ++hh) {
-      qp[hh][0] = make_qplanes<METRIC>(__ldg(p.q_code + 2 * (warp * HPW + hh)));
-      qp[hh][1] = make_qplanes<METRIC>(__ldg(p.q_code + 2 * (warp * HPW + hh) + 1));
+      qp[hh][0] = make_qplanes<METRIC>(__ldg(q_code + 2 * (warp * HPW + hh)));
+      qp[hh][1] = make_qplanes<METRIC>(__ldg(q_code + 2 * (warp * HPW + hh) + 1));
     }
   }
   est_consume<METRIC, OutT, HPW>(p, geom, ring, my_tiles, lane, warp, qp, sq);
@@ -407,20 +427,28 @@ __global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const Esti
   const unsigned l16 = lane & 15;
   const int half = lane >> 4;
   const int H = p.H;
+  PagedTarget tgt = a.tgt;
+  if (p.seqs) {
+    const SeqDesc sd = p.seqs[blockIdx.y];
+    tgt.kv_data = sd.kv_data;
+    tgt.kv_table = sd.kv_table;
+    tgt.code_data = static_cast<uint16_t*>(sd.code_data);
+    tgt.code_table = sd.code_table;
+  }
   QPlanes qp[HPW][2];
 #pragma unroll
   for (int pass = 0; pass < (HPW + 1) / 2; ++pass) {
     // this half-warp's row: head warp*HPW + 2*pass + half (HPW == 1: both halves take the one head)
     const int hh_mine = (HPW == 1) ? 0 : 2 * pass + half;
     const int head = warp * HPW + hh_mine;
-    const int64_t in_off = static_cast<int64_t>(head) * kHeadDim + l16 * 8;
+    const int64_t in_off = static_cast<int64_t>(geom.row0 + head) * kHeadDim + l16 * 8;   // rows of q, k, v: (sequence, head)
     const bool writer = appender && (HPW > 1 || half == 0);
     float x[8];
     unpack8<T>(ld_16(static_cast<const T*>(a.q) + in_off), x);
     wht128_halfwarp(x, l16);
     scale_round<T>(x, a.scale);
     const unsigned word = bucketize_pack8(x, a.th);   // code word l16 of `head`
-    if (writer) a.q_code_out[head * kCodeWords + l16] = static_cast<uint16_t>(word);
+    if (writer) a.q_code_out[(geom.row0 + head) * kCodeWords + l16] = static_cast<uint16_t>(word);
     // spread the 16 code words of each row over the warp: through shared memory (one 2-byte store per
     // lane, two 16-byte broadcast loads per head)
     __syncwarp();
@@ -434,10 +462,10 @@ __global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const Esti
       qp[hh][1] = make_qplanes<0>(cw[1]);
     }
     if (appender) {   // block-uniform
-      const int kv_page = __ldg(a.tgt.kv_table + kv_last_page);
-      const int code_page = __ldg(a.tgt.code_table + code_last_page);
-      const int ps = a.tgt.page_size;
-      T* kv = static_cast<T*>(a.tgt.kv_data);
+      const int kv_page = __ldg(tgt.kv_table + kv_last_page);
+      const int code_page = __ldg(tgt.code_table + code_last_page);
+      const int ps = tgt.page_size;
+      T* kv = static_cast<T*>(tgt.kv_data);
       const int64_t k_off =
           ((static_cast<int64_t>(kv_page) * 2 * ps + kv_entry) * H + head) * kHeadDim + l16 * 8;
       const int64_t v_delta = static_cast<int64_t>(ps) * H * kHeadDim;
@@ -454,7 +482,7 @@ __global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const Esti
       if (writer) {
         const int64_t c_off =
             ((static_cast<int64_t>(code_page) * ps + code_entry) * H + head) * kCodeWords + l16;
-        a.tgt.code_data[c_off] = bucketize_pack8(b, a.th);
+        tgt.code_data[c_off] = bucketize_pack8(b, a.th);
       }
     }
   }
@@ -486,6 +514,7 @@ struct EstimatePagesParams {
   const int32_t* seq_len_dev;   // optional device-resident sequence length, as in EstimateParams
   uint32_t* hist;               // optional per-slice histograms, as in EstimateParams
   int hist_cl;
+  const SeqDesc* seqs;          // optional batch of sequences (grid.y = sequence), as in EstimateParams
 };
 
 template <int METRIC, typename OutT>
@@ -511,8 +540,19 @@ __global__ void __launch_bounds__(kEstPagesThreads, 2) estimate_pages_kernel(con
   }
   __syncthreads();
   int n_tokens = p.n_tokens, num_tiles = p.num_tiles;
-  if (p.seq_len_dev) {
-    n_tokens = __ldg(p.seq_len_dev) - 1;
+  const uint4* codes = p.codes;
+  const int32_t* page_table = p.page_table;
+  const int32_t* len = p.seq_len_dev;
+  int row0 = 0;
+  if (p.seqs) {
+    const int b = blockIdx.y;
+    codes = static_cast<const uint4*>(p.seqs[b].code_data);
+    page_table = p.seqs[b].code_table;
+    len += b;
+    row0 = b * p.H;
+  }
+  if (len) {
+    n_tokens = __ldg(len) - 1;
     num_tiles = (n_tokens + tile_span - 1) / tile_span;
   }
   const int slice_tokens = p.hist ? 8 * sa_granules_per_block(n_tokens, p.hist_cl) : 1;
@@ -531,7 +571,7 @@ __global__ void __launch_bounds__(kEstPagesThreads, 2) estimate_pages_kernel(con
         const int tok0 = tile * tile_span;
         page[u] = 0;
         if (j0 + u < my_tiles && tok0 + lane * p.page_size < n_tokens)
-          page[u] = __ldg(p.page_table + tile * p.pages_per_tile + lane);
+          page[u] = __ldg(page_table + tile * p.pages_per_tile + lane);
       }
 #pragma unroll
       for (int u = 0; u < kEstLookahead; ++u) {
@@ -549,7 +589,7 @@ __global__ void __launch_bounds__(kEstPagesThreads, 2) estimate_pages_kernel(con
         if (lane < npages) {
           const int64_t phys = page[u];
           const int toks = min(p.page_size, ntok - lane * p.page_size);
-          bulk_copy_g2s(est_smem + slot * tile_chunks + lane * page_chunks, p.codes + phys * page_chunks,
+          bulk_copy_g2s(est_smem + slot * tile_chunks + lane * page_chunks, codes + phys * page_chunks,
                         static_cast<unsigned>(toks) * H2 * 16u, &full_bar[slot]);
         }
         if (++slot == kEstStages) {
@@ -567,7 +607,7 @@ __global__ void __launch_bounds__(kEstPagesThreads, 2) estimate_pages_kernel(con
   grid_launch_dependents();
   const int half = lane & 1;
   const int h = (lane % H2) >> 1;
-  const QPlanes qp = make_qplanes<METRIC>(__ldg(p.q_code + 2 * h + half));
+  const QPlanes qp = make_qplanes<METRIC>(__ldg(p.q_code + 2 * (row0 + h) + half));
   const int toks_per_step = 32 / H2;
   const int tok_in_step = lane / H2;
   // A warp works in units of 8 consecutive tokens (16 for one head).  With stage_out its lanes drop
@@ -579,7 +619,8 @@ __global__ void __launch_bounds__(kEstPagesThreads, 2) estimate_pages_kernel(con
   const int steps_per_unit = unit_tok / toks_per_step;
   const int parts = unit_tok >> 3;
   uint16_t(*stage)[16] = s_stage[warp];
-  OutT* out = static_cast<OutT*>(p.out);
+  OutT* out = static_cast<OutT*>(p.out) + static_cast<int64_t>(row0) * p.out_stride;   // this sequence's rows
+  uint32_t* hist = p.hist ? p.hist + static_cast<size_t>(row0) * kSaScratchWordsPerHead : nullptr;
   const bool rows_aligned = ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0) && ((p.out_stride * sizeof(OutT)) % 16 == 0);
   int slot = 0;
   unsigned parity = 0;
@@ -608,7 +649,7 @@ __global__ void __launch_bounds__(kEstPagesThreads, 2) estimate_pages_kernel(con
           }
           if (p.hist && u * unit_tok + t < ntok) {
             const int off = off0 + u * unit_tok + t;
-            hist_count(p.hist, h, slice0 + (off >= slice_tokens ? off / slice_tokens : 0), d);
+            hist_count(hist, h, slice0 + (off >= slice_tokens ? off / slice_tokens : 0), d);
           }
         }
       }

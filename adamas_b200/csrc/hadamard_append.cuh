@@ -158,7 +158,8 @@ __global__ void __launch_bounds__(256)
 append_decode_kernel(const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ qh,
                      const T* __restrict__ kh, uint16_t* __restrict__ q_code_out, PagedTarget tgt,
                      int kv_last_page, int kv_entry, int code_last_page, int code_entry, float scale,
-                     Thresholds th, float pos, RopeParams rp, const int32_t* seq_len_dev, int q_heads) {
+                     Thresholds th, float pos, RopeParams rp, const int32_t* seq_len_dev, int q_heads,
+                     const SeqDesc* seqs) {
   // The kernel after this one (the estimate) may become resident right away: its producer warps only
   // read the code cache as it was before this step, and its consumers wait for this grid to complete,
   // which in turn waits for the grid before it.  (Two appends to one cache back to back, followed by an
@@ -166,6 +167,22 @@ append_decode_kernel(const T* __restrict__ k, const T* __restrict__ v, const T* 
   // slot unwritten.  A decode step appends once.)
   grid_launch_dependents();
   grid_dependency_wait();
+  if (seqs) {
+    // a batch of sequences (grid.y = sequence): rows of q, k, v and the query codes are (sequence, head)
+    const int b = blockIdx.y;
+    tgt.kv_data = seqs[b].kv_data;
+    tgt.kv_table = seqs[b].kv_table;
+    tgt.code_data = static_cast<uint16_t*>(seqs[b].code_data);
+    tgt.code_table = seqs[b].code_table;
+    const int64_t kv_rows = static_cast<int64_t>(b) * tgt.num_heads * kHeadDim;
+    const int64_t q_rows = static_cast<int64_t>(b) * q_heads * kHeadDim;
+    k += kv_rows;
+    v += kv_rows;
+    kh += FUSED ? kv_rows : 0;
+    qh += q_rows;
+    q_code_out += static_cast<int64_t>(b) * q_heads * kCodeWords;
+    seq_len_dev += b;
+  }
   if (seq_len_dev) {
     // the token being appended sits at position *seq_len_dev - 1 of both caches
     const int t = __ldg(seq_len_dev) - 1;

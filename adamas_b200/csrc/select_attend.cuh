@@ -62,6 +62,8 @@ struct SelectAttendParams {
   const int2* ext_cut;      // optional [H]: (cut distance, cut-valued winners this call takes), decided
                             // elsewhere (sequence shards); k is then unused
   const int32_t* seq_len_dev;  // optional: n = *seq_len_dev - 1 and the newest token sits at position n
+  const SeqDesc* seqs;      // optional (needs seq_len_dev): a batch of sequences, grid.z = sequence; dist, hist, q, o,
+                            // lse and out_idx have one row per (sequence, head); cache, page table and length are the sequence's
   int n;                    // distances per head (tokens 0 .. n-1) when seq_len_dev is null
   int k;                    // winners per head, 1 <= k <= n
   const void* q;            // [H, 128]; read after the preceding kernel has completed
@@ -104,12 +106,20 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
 
   const unsigned CL = gridDim.x;
   const unsigned cr = blockIdx.x;
-  const int head = blockIdx.y;
+  const int head = blockIdx.z * gridDim.y + blockIdx.y;   // row of dist, hist, q, o, lse, out_idx: (sequence, query head)
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
   const int H = p.H;
-  const int head_kv = p.q_group == 1 ? head : head / p.q_group;
+  const int head_kv = p.q_group == 1 ? blockIdx.y : blockIdx.y / p.q_group;
+  const int32_t* kv_table = p.kv_table;
+  const void* kv_base = p.kv;
+  const int32_t* seq_len_dev = p.seq_len_dev;
+  if (p.seqs) {   // (the table of sequences is set up once, long before this launch)
+    kv_table = p.seqs[blockIdx.z].kv_table;
+    kv_base = p.seqs[blockIdx.z].kv_data;
+    seq_len_dev += blockIdx.z;
+  }
 
   uint8_t* sa_tile = sa_smem;                                                         // [16 warps][K rows | V rows]
   int32_t* s_list = reinterpret_cast<int32_t*>(sa_smem + kSaWarps * 2 * kSaWarpRows * 256);   // the block's winners, in position order
@@ -130,7 +140,7 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   grid_launch_dependents();
 
   // ---- loads: distances, histograms, query, page numbers --------------------------------------------
-  const int n = p.seq_len_dev ? (__ldg(p.seq_len_dev) - 1) : p.n;
+  const int n = seq_len_dev ? (__ldg(seq_len_dev) - 1) : p.n;
   const int G = (n + 7) >> 3;
   const int gpb = sa_granules_per_block(n, static_cast<int>(CL));
   const int blk_first = cr * gpb;
@@ -166,7 +176,7 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
     granule_page[i] = 0;
-    if (page_per_granule && g0 + i < blk_end) granule_page[i] = __ldg(p.kv_table + (((g0 + i) * 8) >> p.ps_shift));
+    if (page_per_granule && g0 + i < blk_end) granule_page[i] = __ldg(kv_table + (((g0 + i) * 8) >> p.ps_shift));
   }
   // the newest token rides with the last slice
   const bool tail_here = p.tail_mode != 0 && cr == CL - 1;
@@ -174,7 +184,7 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   if (tail_here && tid == 0 && p.tail_mode == 2) {
     const unsigned un = static_cast<unsigned>(n), ps = static_cast<unsigned>(p.page_size);
     const unsigned pg = p.ps_shift >= 0 ? (un >> p.ps_shift) : (un / ps);
-    tail_slot = static_cast<unsigned>(__ldg(p.kv_table + pg)) * ps + (un - pg * ps);
+    tail_slot = static_cast<unsigned>(__ldg(kv_table + pg)) * ps + (un - pg * ps);
   }
   // ---- cut: one bin per thread ------------------------------------------------------------------------
   unsigned tot = 0, low = 0;
@@ -274,7 +284,7 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   const int n_win = static_cast<int>(blk_lt + min(blk_eq, take_eq));
   const int n_loc = min(n_win + (tail_here ? 1 : 0), p.list_capacity);
 
-  const T* kvp = static_cast<const T*>(p.kv);
+  const T* kvp = static_cast<const T*>(kv_base);
   const unsigned ps = static_cast<unsigned>(p.page_size);
   const int64_t v_delta = static_cast<int64_t>(p.page_size) * H * kHeadDim;
   // The winners go to a list in shared memory (a few instructions on a divergent path).
@@ -308,7 +318,7 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
                 pg = t / ps;
                 e = t - pg * ps;
               }
-              slot = static_cast<unsigned>(__ldg(p.kv_table + pg)) * ps + e;
+              slot = static_cast<unsigned>(__ldg(kv_table + pg)) * ps + e;
             }
             if (pos < p.list_capacity) s_list[pos] = static_cast<int32_t>(slot);
             if (oi) oi[pos] = static_cast<int32_t>(slot);

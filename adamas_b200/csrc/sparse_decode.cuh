@@ -49,6 +49,9 @@ struct DecodeParams {
   // page_size) and n_idx, n_tokens, tail_slot0 and tiles_per_block are derived from *seq_len_dev here;
   // num_splits (the grid) was sized for the longest sequence.
   const int32_t* seq_len_dev;
+  // optional (needs seq_len_dev): a batch of sequences, grid.z = sequence.  q, o, o_f32, lse and the
+  // scratch have one row per (sequence, head); the cache, its page table and the length are the sequence's.
+  const SeqDesc* seqs;
 };
 
 template <typename T>
@@ -64,15 +67,21 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
   __shared__ __align__(8) uint64_t full_bar[2];
 
   const int split = blockIdx.x;
-  const int head = blockIdx.y;
+  const int head = blockIdx.z * gridDim.y + blockIdx.y;   // row of q, o, lse and the scratch: (sequence, query head)
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
   const int H = prm.H;
-  const int head_kv = prm.q_group == 1 ? head : head / prm.q_group;
+  const int head_kv = prm.q_group == 1 ? blockIdx.y : blockIdx.y / prm.q_group;
 
   const T* kvp = static_cast<const T*>(prm.kv);
   const int32_t* idx_row = prm.indices + static_cast<int64_t>(head) * prm.idx_stride;
+  const int32_t* seq_len_dev = prm.seq_len_dev;
+  if (prm.seqs) {   // (the table of sequences is set up once, long before this launch)
+    kvp = static_cast<const T*>(prm.seqs[blockIdx.z].kv_data);
+    idx_row = prm.seqs[blockIdx.z].kv_table;
+    seq_len_dev += blockIdx.z;
+  }
   const int64_t v_delta = static_cast<int64_t>(prm.page_size) * H * kHeadDim;
 
   // ---- gather one tile into a stage --------------------------------------------------------------
@@ -93,12 +102,12 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
   grid_launch_dependents();
   int n_tokens = prm.n_tokens, tiles_per_block = prm.tiles_per_block, n_listed = prm.n_idx * prm.idx_unit;
   unsigned tail_slot0 = prm.tail_slot0;
-  if (prm.seq_len_dev) {
-    const int len = __ldg(prm.seq_len_dev);
+  if (seq_len_dev) {
+    const int len = __ldg(seq_len_dev);
     const int pages = (len + prm.page_size - 1) / prm.page_size;
     n_listed = (pages - 1) * prm.page_size;
     n_tokens = len;
-    tail_slot0 = static_cast<unsigned>(__ldg(prm.indices + pages - 1)) * static_cast<unsigned>(prm.page_size);
+    tail_slot0 = static_cast<unsigned>(__ldg(idx_row + pages - 1)) * static_cast<unsigned>(prm.page_size);
     const int tiles = (len + kDecTile - 1) / kDecTile;
     tiles_per_block = (tiles + prm.num_splits - 1) / prm.num_splits;
   }

@@ -8,6 +8,7 @@ from .. import _kernels
 from .controller import InferenceController
 from .decode_wrapper import BatchDecodeWithPagedKVCacheWrapper
 from .kv_cache import KvCache
+from .sequence_batch import SequenceBatch
 from .utils import TensorLayout
 
 __all__ = [
@@ -24,6 +25,7 @@ __all__ = [
     "decode_step",
     "decode_step_dev",
     "seq_len_advance",
+    "SequenceBatch",
 ]
 
 

@@ -226,8 +226,8 @@ int adamas_decode_handler_destroy(adamas_decode_handler_t* handler);
 /* Plans the split of max_tokens attended tokens per head over thread blocks and makes sure the
  * handler's device scratch (partial outputs) is large enough (allocates on first use or growth).
  * Replaces BeginForward (kernels/include/decode/decode_handler.cuh:73-121). */
-int adamas_decode_begin_forward(adamas_decode_handler_t* handler, int64_t max_tokens, int num_heads,
-                                int num_q_heads, int head_dim, int page_size, int dtype,
+int adamas_decode_begin_forward(adamas_decode_handler_t* handler, int64_t max_tokens, int batch,
+                                int num_heads, int num_q_heads, int head_dim, int page_size, int dtype,
                                 adamas_stream_t stream);
 /* Replaces EndForward (decode_handler.cuh:123-136).  Scratch is kept for reuse until destroy. */
 int adamas_decode_end_forward(adamas_decode_handler_t* handler);
@@ -403,9 +403,49 @@ int adamas_dense_step_dev(adamas_decode_handler_t* handler, void* q, void* k, co
                           const float* rope_inv_freq, float rope_mscale, float sm_scale,
                           adamas_stream_t stream);
 
-/* *seq_len_dev += delta, as one tiny launch that is ordered after everything before it in the stream
- * and before everything after it. */
-int adamas_seq_len_advance(int32_t* seq_len_dev, int delta, adamas_stream_t stream);
+/* seq_len_dev[i] += delta for i < count (count = 1 for a single sequence, the batch size for a batched
+ * step), as one tiny launch that is ordered after everything before it in the stream and before
+ * everything after it. */
+int adamas_seq_len_advance(int32_t* seq_len_dev, int count, int delta, adamas_stream_t stream);
+
+/* ---- several sequences in one launch ------------------------------------------------------------
+ * The reference decodes one sequence per call (adamas/models/Adamas.py:83 asserts batch size 1, and an
+ * InferenceController holds one sequence); a server loops over its sequences.
+ * Here `batch` sequences of one cache geometry go through the SAME two or three launches of a step:
+ * every kernel's grid gets a sequence coordinate.  Each sequence keeps its own caches and page
+ * tables, described by one adamas_seq_desc_t in a device array; everything else is one contiguous
+ * array over (sequence, head) rows: q, o [batch, Hq, D]; k, v [batch, H, D]; q_code [batch, Hq, D/8];
+ * dist_scratch [batch * Hq, dist_stride]; hist_scratch batch * Hq * ADAMAS_HIST_WORDS_PER_HEAD words;
+ * out_idx [batch * Hq, out_stride]; lse [batch * Hq]; seq_lens_dev int32 [batch] (advance all of them
+ * with adamas_seq_len_advance(seq_lens_dev, batch, 1, ...)).  The sequences may have different
+ * lengths; every one must be longer than the budget for the sparse step.  The descriptor array must be
+ * complete before the first step is launched and must not change while steps are in flight. */
+typedef struct adamas_seq_desc {
+  void* kv_data;                    /* this layer's KV cache of the sequence [pages, 2, page_size, H, D] */
+  void* code_data;                  /* this layer's code cache [pages, 1, page_size, H, D/8] */
+  const int32_t* kv_page_table;     /* device, an entry for every page of the current length */
+  const int32_t* code_page_table;
+} adamas_seq_desc_t;
+
+/* adamas_decode_step_dev for `batch` sequences. */
+int adamas_decode_step_batch_dev(void* q, void* k, const void* v, void* o, float* lse, void* q_code,
+                                 const adamas_seq_desc_t* seqs_dev, const int32_t* seq_lens_dev, int batch,
+                                 int max_seq_len, int num_heads, int num_q_heads, int head_dim, int page_size,
+                                 int dtype, int budget, void* dist_scratch, int64_t dist_stride,
+                                 uint32_t* hist_scratch, int32_t* out_idx, int64_t out_stride, float hadamard_scale,
+                                 const float* thresholds3_host, float rope_scale, float rope_theta,
+                                 const float* rope_inv_freq, float rope_mscale, float sm_scale,
+                                 adamas_stream_t stream);
+
+/* adamas_dense_step_dev for `batch` sequences; the handler must have been planned with
+ * adamas_decode_begin_forward(handler, max_seq_len, batch, ...). */
+int adamas_dense_step_batch_dev(adamas_decode_handler_t* handler, void* q, void* k, const void* v, void* o,
+                                float* lse, void* q_code, const adamas_seq_desc_t* seqs_dev,
+                                const int32_t* seq_lens_dev, int batch, int max_seq_len, int num_heads,
+                                int num_q_heads, int head_dim, int page_size, int dtype, float hadamard_scale,
+                                const float* thresholds3_host, float rope_scale, float rope_theta,
+                                const float* rope_inv_freq, float rope_mscale, float sm_scale,
+                                adamas_stream_t stream);
 
 /* adamas_apply_rope_in_place with a table of rotation frequencies (device, 64 floats) and a factor on
  * the rotated values instead of (rope_scale, rope_theta): the prefill side of YaRN-scaled models.  The
