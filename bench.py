@@ -665,7 +665,7 @@ def run_sweep(args):
                 # several sequences: one estimate block per SM, so that other sequences' select+attend
                 # blocks find room while an estimate streams
                 K.set_estimate_blocks_per_sm(args.sweep_est_blocks or (1 if batch > 1 else 2))
-                wls = [Workload(a, dev, seed_offset=i) for i in range(batch)]
+                wls = [Workload(a, dev, seed_offset=i, room=(args.steps + 16 if batch > 1 else 0)) for i in range(batch)]
                 for wl in wls:
                     wl.step_fixed()
                 torch.cuda.synchronize()
@@ -695,6 +695,36 @@ def run_sweep(args):
                 a.unfused = True
                 out["select_attend_GBps"] = round((by["topk"] + by["attention"]) / (out["select_attend_us"] * 1e-6) / 1e9, 1)
                 out["step_GBps"] = round(by["total"] / (out["step_us"] * 1e-6) / 1e9, 1)
+                if batch > 1:
+                    # all sequences through the SAME launches (utils.SequenceBatch), advancing one token per replay
+                    import adamas_b200.utils as U
+                    K.set_max_cluster(8)
+                    K.set_estimate_blocks_per_sm(2)
+                    sb = U.SequenceBatch([wl.c for wl in wls])
+                    bq, bk, bv = ([torch.stack([wl.d_qkv[j, l, 0] for wl in wls]) for l in range(layers)] for j in range(3))
+                    bo = [torch.zeros_like(t) for t in bq]
+
+                    def batched_body():
+                        for l in range(layers):
+                            sb.decode_step_dev(bq[l], bk[l], bv[l], l, out=bo[l])
+                        sb.advance()
+
+                    def batched_step():
+                        sb.prepare(1)
+                        gb.replay()
+
+                    sb.sync_seq_lens()
+                    batched_body()
+                    torch.cuda.synchronize()
+                    sb.prepare(1)
+                    gb = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gb):
+                        batched_body()
+                    for _ in range(3):
+                        batched_step()
+                    out["step_one_launch_us"] = round(timed(batched_step, args.steps, False, dev) * 1e3 / args.steps / layers, 2)
+                    out["step_one_launch_GBps"] = round(by["total"] / (out["step_one_launch_us"] * 1e-6) / 1e9, 1)
+                    del sb, gb, bq, bk, bv, bo
                 print(json.dumps(out), flush=True)
                 del wls, wl
                 torch.cuda.empty_cache()

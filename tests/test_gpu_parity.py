@@ -146,6 +146,10 @@ def test_bucketize_pack_all_buckets_and_boundaries():
     K.bucketize_pack(h.to(DEV), o)
     want = ref.pack_2bit(ref.bucketize(h.float().numpy()))
     np.testing.assert_array_equal(_codes_of(o), want)
+    # the reference's name for the same operator (adamas/ops/csrc/page.cu:271-298)
+    o2 = torch.zeros_like(o)
+    K.pack_2bit(h.to(DEV), o2, 0)
+    assert torch.equal(o2, o)
     # custom thresholds
     K.bucketize_pack(h.to(DEV), o, thresholds=(-1.0, 0.25, 2.0))
     want = ref.pack_2bit(ref.bucketize(h.float().numpy(), (-1.0, 0.25, 2.0)))
