@@ -92,7 +92,8 @@ struct SaShared {
   unsigned cut, need_eq, lt_before, eq_before;
   unsigned last;   // this block arrived last at the head's counter
   uint4 q[16];     // the head's query row
-  unsigned long long bar[kSaWarps];   // one mbarrier per warp: the bytes of its own rows
+  unsigned long long bar[kSaWarps];   // one mbarrier per warp: the bytes of its own K rows
+  unsigned long long bar_v[kSaWarps];  // ... and of its own V rows
 };
 
 // Dynamic shared memory: the tile (16 warps x (12 K rows + 12 V rows) x 256 B; a warp parks its partial
@@ -127,11 +128,15 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   float* slots = reinterpret_cast<float*>(head_scratch + kSaMaxSlices * kSaBins);     // [CL][kSaSlotWords]
   uint4* s_q = sh.q;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sh.bar);
+  uint64_t* bars_v = reinterpret_cast<uint64_t*>(sh.bar_v);
 
   // ---- set-up that needs no input (overlaps the tail of the preceding kernel) -----------------------
   if (tid == 0) {
 #pragma unroll
-    for (int w2 = 0; w2 < kSaWarps; ++w2) mbar_init(&bars[w2], 1);
+    for (int w2 = 0; w2 < kSaWarps; ++w2) {
+      mbar_init(&bars[w2], 1);
+      mbar_init(&bars_v[w2], 1);
+    }
     sh.cut = 0xffffffffu;
     mbar_fence_init();
   }
@@ -251,16 +256,26 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   const unsigned out_base = ((sh.cut == 0xffffffffu) ? 0u : sh.lt_before) + min(eq_before, need_eq);
 
   // ---- pick: ordered compaction of this block's winners -----------------------------------------------
+  // Two halfword-parallel compares per register give, per granule, the 8-bit masks of the elements below
+  // the cut and at the cut (values of 511 and more count as 511).
+  const unsigned cut2 = min(cut, 0xffffu) * 0x00010001u;
+  unsigned m_lt[ITEMS], m_eq[ITEMS];
   unsigned c_lt = 0, c_eq = 0;
 #pragma unroll
   for (int i = 0; i < ITEMS; ++i) {
+    unsigned lt = 0, eq = 0;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const unsigned d = min((raw[i][j >> 1] >> ((j & 1) * 16)) & 0xffffu, static_cast<unsigned>(kSaBins - 1));
-      const bool ok = (vmask[i] >> j) & 1u;
-      c_lt += (ok && d < cut);
-      c_eq += (ok && d == cut);
+    for (int w = 0; w < 4; ++w) {
+      const unsigned x = __vminu2(raw[i][w], 0x01ff01ffu);
+      const unsigned l = __vcmpltu2(x, cut2);   // 0xffff per halfword that is below the cut
+      const unsigned e = __vcmpeq2(x, cut2);
+      lt |= ((l & 1u) | ((l >> 15) & 2u)) << (2 * w);
+      eq |= ((e & 1u) | ((e >> 15) & 2u)) << (2 * w);
     }
+    m_lt[i] = lt & vmask[i];
+    m_eq[i] = eq & vmask[i];
+    c_lt += __popc(m_lt[i]);
+    c_eq += __popc(m_eq[i]);
   }
   const unsigned packed = c_lt | (c_eq << 16);
   unsigned incl = packed;
@@ -292,37 +307,38 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   if (c_lt | c_eq) {
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const unsigned d = min((raw[i][j >> 1] >> ((j & 1) * 16)) & 0xffffu, static_cast<unsigned>(kSaBins - 1));
-        if (((vmask[i] >> j) & 1u) && d <= cut) {
-          int pos = -1;
-          if (d < cut) {
-            pos = static_cast<int>(run_lt + min(run_eq, take_eq));
-            ++run_lt;
+      // only the elements at or below the cut are visited, in position order (a warp takes as many turns
+      // as its busiest lane has candidates: one or two at the usual budgets)
+      unsigned cand = m_lt[i] | m_eq[i];
+      while (cand) {
+        const int j = __ffs(cand) - 1;
+        cand &= cand - 1;
+        int pos = -1;
+        if ((m_lt[i] >> j) & 1u) {
+          pos = static_cast<int>(run_lt + min(run_eq, take_eq));
+          ++run_lt;
+        } else {
+          if (run_eq < take_eq) pos = static_cast<int>(run_lt + run_eq);
+          ++run_eq;
+        }
+        if (pos >= 0) {
+          const unsigned t = static_cast<unsigned>((g0 + i) * 8 + j);   // logical token position
+          unsigned slot;
+          if (page_per_granule) {
+            slot = static_cast<unsigned>(granule_page[i]) * ps + (t & (ps - 1));
           } else {
-            if (run_eq < take_eq) pos = static_cast<int>(run_lt + run_eq);
-            ++run_eq;
-          }
-          if (pos >= 0) {
-            const unsigned t = static_cast<unsigned>((g0 + i) * 8 + j);   // logical token position
-            unsigned slot;
-            if (page_per_granule) {
-              slot = static_cast<unsigned>(granule_page[i]) * ps + (t & (ps - 1));
+            unsigned pg, e;
+            if (p.ps_shift >= 0) {
+              pg = t >> p.ps_shift;
+              e = t & (ps - 1);
             } else {
-              unsigned pg, e;
-              if (p.ps_shift >= 0) {
-                pg = t >> p.ps_shift;
-                e = t & (ps - 1);
-              } else {
-                pg = t / ps;
-                e = t - pg * ps;
-              }
-              slot = static_cast<unsigned>(__ldg(kv_table + pg)) * ps + e;
+              pg = t / ps;
+              e = t - pg * ps;
             }
-            if (pos < p.list_capacity) s_list[pos] = static_cast<int32_t>(slot);
-            if (oi) oi[pos] = static_cast<int32_t>(slot);
+            slot = static_cast<unsigned>(__ldg(kv_table + pg)) * ps + e;
           }
+          if (pos < p.list_capacity) s_list[pos] = static_cast<int32_t>(slot);
+          if (oi) oi[pos] = static_cast<int32_t>(slot);
         }
       }
     }
@@ -350,6 +366,7 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   uint8_t* wk = sa_tile + warp * (2 * kSaWarpRows * 256);   // this warp's K rows, then its V rows
   uint8_t* wv = wk + kSaWarpRows * 256;
   uint64_t* bar = &bars[warp];
+  uint64_t* bar_v = &bars_v[warp];
   // q.K mapping: four lanes per token (tq = lane / 4, quarter = lane % 4); step i of a lane reads chunk
   // 4*quarter + ((i + quarter + tq) & 3).  A quarter-warp covers an even and an odd token; the rows are
   // 256 bytes apart (the same banks), and with this order the two tokens' four chunks fall on
@@ -359,6 +376,7 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   uint4 qpk[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) qpk[i] = s_q[4 * quarter + ((i + quarter + tq) & 3)];
+  constexpr int kGroups = (kSaWarpRows + 7) / 8;   // groups of 8 rows per round
   unsigned phase = 0;
   for (int done = 0; done < my_total; done += kSaWarpRows) {
     const int my_rows = min(kSaWarpRows, my_total - done);
@@ -367,7 +385,10 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
       __syncwarp();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<unsigned>(my_rows) * (2 * kHeadDim * 2));
+    if (lane == 0) {
+      mbar_arrive_expect_tx(bar, static_cast<unsigned>(my_rows) * (kHeadDim * 2));
+      mbar_arrive_expect_tx(bar_v, static_cast<unsigned>(my_rows) * (kHeadDim * 2));
+    }
     __syncwarp();
     {
       const int r = lane & 15;
@@ -383,13 +404,16 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
           e = slot - page * ps;
         }
         const T* src = kvp + (static_cast<int64_t>(page * (2 * ps) + e) * H + head_kv) * kHeadDim + (is_v ? v_delta : 0);
-        bulk_copy_g2s((is_v ? wv : wk) + r * 256, src, kHeadDim * 2, bar);
+        bulk_copy_g2s((is_v ? wv : wk) + r * 256, src, kHeadDim * 2, is_v ? bar_v : bar);
       }
     }
+    // The K rows are asked for first (lanes 0-15) and land first: the logits of the whole round are formed
+    // while the V rows are still on their way.
     if (!mbar_wait_bounded(bar, phase, 1u << 22)) atomicOr(&g_adamas_error, kErrGatherTimeout);
-    phase ^= 1u;
-    for (int base = 0; base < my_rows; base += 8) {
-      const int row = base + tq;
+    float logit[kGroups];
+#pragma unroll
+    for (int g = 0; g < kGroups; ++g) {
+      const int row = g * 8 + tq;
       const bool live = row < my_rows;
       float acc = 0.f;
       if (live) {
@@ -405,13 +429,21 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
       }
       acc += __shfl_xor_sync(0xffffffffu, acc, 1);
       acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      const float logit = live ? acc * p.scale_log2 : -INFINITY;
-      float m_new = logit;
+      logit[g] = live ? acc * p.scale_log2 : -INFINITY;
+    }
+    if (!mbar_wait_bounded(bar_v, phase, 1u << 22)) atomicOr(&g_adamas_error, kErrGatherTimeout);
+    phase ^= 1u;
+#pragma unroll
+    for (int g = 0; g < kGroups; ++g) {
+      const int base = g * 8;
+      if (base >= my_rows) break;   // warp-uniform
+      const bool live = base + tq < my_rows;
+      float m_new = logit[g];
 #pragma unroll
       for (int o = 4; o < 32; o <<= 1) m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, o));
       m_new = fmaxf(m_new, m_run);      // finite: the first row of a group is live
       const float rescale = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
-      const float pr = live ? exp2f(logit - m_new) : 0.f;
+      const float pr = live ? exp2f(logit[g] - m_new) : 0.f;
       float psum = quarter == 0 ? pr : 0.f;
 #pragma unroll
       for (int o = 4; o < 32; o <<= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
