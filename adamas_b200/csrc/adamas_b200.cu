@@ -1147,31 +1147,47 @@ void sa_shape(int n, int k, int cl, SaPlan* pl) {
 
 int sa_plan(int n, int k, int num_heads, const DeviceInfo* di, SaPlan* pl) {
   const int g_total = (n + 7) / 8;
-  // Blocks per head: any number up to 16 (the blocks of a head do not wait for one another), as few
-  // granules per thread as possible.  By default up to 8 blocks, or more as long as every block of the
-  // launch is resident at once (a row a little beyond 8 * 512 granules then takes 9 blocks instead of
-  // two granules per thread, which would double the selection's work); adamas_set_max_cluster lowers the
-  // bound.
+  // Blocks per head: any number up to 16 (the blocks of a head do not wait for one another).  num_heads
+  // counts the rows of the launch (query heads x sequences).  By default up to 8 blocks, or more as long as
+  // every block of the launch is resident at once (a row a little beyond 8 * 512 granules then takes 9
+  // blocks instead of two granules per thread, which would double the selection's work);
+  // adamas_set_max_cluster lowers the bound.
   const int user_limit = max_cluster();
-  const int resident = std::max(1, 2 * di->num_sms / num_heads);
+  const int resident_blocks = 2 * di->num_sms;
+  const int resident = std::max(1, resident_blocks / num_heads);
   const int cl_limit = user_limit < kSaMaxCluster ? user_limit
                                                   : std::min(kSaBigCluster, std::max(kSaMaxCluster, resident));
-  int cl = 0, items = 0;
+  // As few granules per thread as possible while the whole launch is resident at once: a block's work is a
+  // chain of short dependent steps that leaves the SM mostly idle, so a second wave of blocks costs a whole
+  // chain again, while more granules per thread only lengthen the first steps (many rows, i.e. a batch of
+  // sequences: 128 rows of 32K distances run as 2 blocks x 4 granules, not 8 x 1 in four waves).  If no
+  // shape is resident at once, the one with the fewest blocks.
+  int cl = 0, items = 0, fewest_cl = 0, fewest_items = 0;
   for (int it = 1; it <= 8 && cl == 0; it *= 2) {
-    const int need = (g_total + it * kSaThreads - 1) / (it * kSaThreads);
-    if (need <= cl_limit) {
-      cl = std::max(1, need);
+    const int need = std::max(1, (g_total + it * kSaThreads - 1) / (it * kSaThreads));
+    if (need > cl_limit) continue;
+    fewest_cl = need;
+    fewest_items = it;
+    if (need * num_heads <= resident_blocks) {
+      cl = need;
       items = it;
     }
+  }
+  if (cl == 0) {
+    cl = fewest_cl;
+    items = fewest_items;
   }
   ADAMAS_REQUIRE(cl > 0, "select_attend supports at most %d distances per head with %d blocks per head (got %d)",
                  cl_limit * 8 * kSaThreads * 8, cl_limit, n);
   // with several granules per thread, rather twice the blocks with half-filled threads than the fewest
-  // blocks that cover the row: a block's work is a chain of short steps, more blocks shorten it
-  if (items >= 2) cl = std::min(cl_limit, std::max(cl, (g_total + items * kSaThreads / 2 - 1) / (items * kSaThreads / 2)));
+  // blocks that cover the row, if they are still resident at once
+  if (items >= 2) {
+    const int twice = std::min(cl_limit, std::max(cl, (g_total + items * kSaThreads / 2 - 1) / (items * kSaThreads / 2)));
+    if (twice * num_heads <= resident_blocks) cl = twice;
+  }
   // a large budget on a short row: more blocks per head than the scan needs, so that each block
   // attends to about one tile of winners, as long as all blocks stay resident at once
-  while (cl < std::min(cl_limit, kSaMaxCluster) && k > cl * kSaTile && 2 * cl * num_heads <= 2 * di->num_sms) cl *= 2;
+  while (cl < std::min(cl_limit, kSaMaxCluster) && k > cl * kSaTile && 2 * cl * num_heads <= resident_blocks) cl *= 2;
   cl = std::min(cl, cl_limit);
   pl->cl = cl;
   pl->items = items;
