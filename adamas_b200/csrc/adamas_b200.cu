@@ -570,7 +570,13 @@ static int estimate_impl(const void* q_code, const void* code_data, const int32_
   const DeviceInfo* di = nullptr;
   if (int rc = get_device_info(&di)) return rc;
   cudaStream_t st = to_stream(stream);
-  if (q_group == 1 && num_heads <= 16 && 32 % (2 * num_heads) == 0 && page_size * num_heads * 32 >= 512) {
+  // (8 and 16 heads with histograms go token by token: in the page-copy kernel the 16 lanes of a count
+  // instruction hit the tables of different heads, one L2 transaction each, where a warp of the token-copy
+  // kernel counts 32 tokens of ONE head into a few neighbouring bins.  Measured at 32K with the counts: 16
+  // heads 13.9 us by pages, 6.0 by tokens; 8 heads 7.9 / 6.6; 4 heads 4.7 / 7.7)
+  constexpr int kPagesMaxHeadsWithHist = 4;
+  if (q_group == 1 && num_heads <= 16 && !(hist && num_heads > kPagesMaxHeadsWithHist) && 32 % (2 * num_heads) == 0 &&
+      page_size * num_heads * 32 >= 512) {
     // few heads (a head-sharded model): whole pages per copy, one chunk per lane
     const int page_bytes = page_size * num_heads * 32;
     const int ppt = std::max(1, std::min(32, 32768 / page_bytes));
@@ -1458,9 +1464,8 @@ static int decode_step_impl(void* q, void* k, const void* v, void* o, float* lse
   SaPlan pl;
   if (int rc = sa_plan(n, budget - 1, q_heads * batch, di, &pl)) return rc;
   int rc;
-  // (16 heads: the page-copy estimate after a separate append is faster than the fused kernel's 512-byte
-  // copies per token)
-  if (fused_append_enabled() && !rope.on && q_heads == num_heads && (num_heads == 32 || num_heads == 64)) {
+  if (fused_append_enabled() && !rope.on && q_heads == num_heads &&
+      (num_heads == 16 || num_heads == 32 || num_heads == 64)) {
     // two launches: the estimate with the append inside, then select + attend.  Not with RoPE: every
     // block of the estimate would repeat the rotation, which costs more than the append launch.
     rc = estimate_append_launch(q, k, v, q_code, kv_data, kv_page_table, pages, last_len, code_data,

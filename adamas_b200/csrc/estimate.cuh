@@ -211,7 +211,7 @@ __device__ __forceinline__ void est_produce(const EstimateParams& p, const EstGe
     }
     if (j >= kEstStages) {
       // every consumer warp has finished reading the tile that used this slot before
-      if (!mbar_wait_bounded(&r.empty_bar[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
+      if (!mbar_wait_bounded(&r.empty_bar[slot], parity, 1u << 20)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
     }
     if (pw == 0 && lane == 0) mbar_arrive_expect_tx(&r.full_bar[slot], static_cast<unsigned>(tile_tokens) * token_bytes);
     __syncwarp();
@@ -250,7 +250,7 @@ __device__ __forceinline__ void est_consume(const EstimateParams& p, const EstGe
     const int slice = p.hist ? tile0 / g.slice_tokens : 0;   // a 32-token group never straddles two slices
     // bounded wait for this tile's bytes; on failure flag the error and carry on (results are then
     // wrong, which the flag reports, but nothing spins forever)
-    if (!mbar_wait_bounded(&r.full_bar[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
+    if (!mbar_wait_bounded(&r.full_bar[slot], parity, 1u << 20)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
     const uint4* row = r.base + slot * r.stage_chunks + lane * r.row_chunks;
     OutT* o = out + tile0 + lane;
     if (HPW > 0) {
@@ -581,7 +581,7 @@ __global__ void __launch_bounds__(kEstPagesThreads, 2) estimate_pages_kernel(con
         const int tok0 = tile * tile_span;
         const int ntok = min(tile_span, n_tokens - tok0);
         if (j >= kEstStages) {
-          if (!mbar_wait_bounded(&empty_bar[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
+          if (!mbar_wait_bounded(&empty_bar[slot], parity, 1u << 20)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
         }
         if (lane == 0) mbar_arrive_expect_tx(&full_bar[slot], static_cast<unsigned>(ntok) * H2 * 16u);
         __syncwarp();
@@ -630,7 +630,7 @@ __global__ void __launch_bounds__(kEstPagesThreads, 2) estimate_pages_kernel(con
     const int ntok = min(tile_span, n_tokens - tok0);
     const int slice0 = p.hist ? tok0 / slice_tokens : 0;
     const int off0 = tok0 - slice0 * slice_tokens;
-    if (!mbar_wait_bounded(&full_bar[slot], parity, 1u << 22)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
+    if (!mbar_wait_bounded(&full_bar[slot], parity, 1u << 20)) atomicOr(&g_adamas_error, kErrEstimateTimeout);
     const uint4* base = est_smem + slot * tile_chunks;
     const int units = (ntok + unit_tok - 1) / unit_tok;
     for (int u = warp; u < units; u += kEstConsumerWarps) {

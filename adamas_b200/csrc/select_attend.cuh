@@ -409,7 +409,7 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
     }
     // The K rows are asked for first (lanes 0-15) and land first: the logits of the whole round are formed
     // while the V rows are still on their way.
-    if (!mbar_wait_bounded(bar, phase, 1u << 22)) atomicOr(&g_adamas_error, kErrGatherTimeout);
+    if (!mbar_wait_bounded(bar, phase, 1u << 20)) atomicOr(&g_adamas_error, kErrGatherTimeout);
     float logit[kGroups];
 #pragma unroll
     for (int g = 0; g < kGroups; ++g) {
@@ -431,7 +431,7 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
       acc += __shfl_xor_sync(0xffffffffu, acc, 2);
       logit[g] = live ? acc * p.scale_log2 : -INFINITY;
     }
-    if (!mbar_wait_bounded(bar_v, phase, 1u << 22)) atomicOr(&g_adamas_error, kErrGatherTimeout);
+    if (!mbar_wait_bounded(bar_v, phase, 1u << 20)) atomicOr(&g_adamas_error, kErrGatherTimeout);
     phase ^= 1u;
 #pragma unroll
     for (int g = 0; g < kGroups; ++g) {

@@ -193,7 +193,7 @@ __global__ void __launch_bounds__(kDecThreads, 4) sparse_decode_kernel(DecodePar
     const int stage = tile & 1;
     if (tile + 1 < n_tiles) issue_tile(tile + 1, stage ^ 1);
     // bounded wait for this tile's bytes (a stage is used every other tile: its phase parity follows)
-    if (!mbar_wait_bounded(&full_bar[stage], (tile >> 1) & 1, 1u << 22)) atomicOr(&g_adamas_error, kErrDecodeTimeout);
+    if (!mbar_wait_bounded(&full_bar[stage], (tile >> 1) & 1, 1u << 20)) atomicOr(&g_adamas_error, kErrDecodeTimeout);
     __syncthreads();   // s_skip of this stage is visible to all threads
     const uint8_t* sk = smem + stage * kDecStageBytes;
     const uint8_t* sv = sk + kDecTile * kDecRowBytes;

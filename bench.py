@@ -690,6 +690,7 @@ def run_sweep(args):
                 for wl in wls:
                     wl.step_fixed()
                 est_fused = sweep_time("estimate")
+                out["estimate_with_histograms_us"] = round(est_fused, 2)      # u16 distances + per-slice counts
                 out["select_attend_us"] = round(sweep_time("select_attend", pre="estimate") - est_fused, 2)
                 out["step_us"] = round(sweep_time("step"), 2)
                 a.unfused = True
