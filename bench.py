@@ -191,6 +191,9 @@ def workload_config(args, extra=None):
                     "one CUDA graph of the step, replayed; every step appends at the next position "
                     "(sequence length in device memory)")),
         "timing": "median of several blocks of `steps` steps, CUDA events, max over ranks",
+        "appended_tokens": ("the same q/k/v at every step" if getattr(args, "repeat_token", False) else
+                            "a different key at every step (device copy of k rotated by one dimension per step; "
+                            "the end-to-end leg cycles through 64 pinned host buffers)"),
     }
     if extra:
         cfg.update(extra)
@@ -232,6 +235,16 @@ class Workload:
         hg = torch.Generator().manual_seed(99 + seed_offset)
         self.h_qkv = torch.randn(3, layers, 1, H, 128, generator=hg).to(dtype).pin_memory()
         self.d_qkv = self.h_qkv.to(dev)
+        # Every appended token differs from the one before: the keys of the device copy are rotated by one
+        # dimension at the end of a step (two small launches), and the end-to-end leg cycles through a ring of
+        # host buffers.  (The same key appended
+        # hundreds of times would put hundreds of equal distances into one histogram bin per head, a pile of
+        # same-address atomics that no real sequence produces.)
+        self.vary = not getattr(args, "repeat_token", False)
+        self.d_tmp = torch.empty_like(self.d_qkv[1]) if self.vary else None
+        self.roll_idx = torch.roll(torch.arange(128, device=dev), 1)
+        self.h_ring = [self.h_qkv]
+        self.e2e_i = 0
         self.d_out = torch.zeros(layers, 1, H, 128, dtype=dtype, device=dev)
         self.h_out = torch.zeros(layers, 1, H, 128, dtype=dtype).pin_memory()
         self.q_code = torch.zeros(layers, 1, H, 16, dtype=dtype, device=dev)
@@ -266,6 +279,9 @@ class Workload:
         if self.after_layers is not None:
             self.after_layers()
         U.seq_len_advance(c)
+        if self.vary:      # the next token's projections
+            torch.index_select(self.d_qkv[1], -1, self.roll_idx, out=self.d_tmp)
+            self.d_qkv[1].copy_(self.d_tmp)
 
     def host_advance(self):
         """What the host does per token: reserve cache room (one page number travels to the device
@@ -315,7 +331,12 @@ class Workload:
 
     def step_e2e(self):
         """Host buffers in, host buffers out: H2D of this step's q/k/v, the step, D2H of the outputs."""
-        self.d_qkv.copy_(self.h_qkv, non_blocking=True)
+        if self.vary and len(self.h_ring) < 64:      # built on first use: 64 different tokens' projections, pinned
+            g = torch.Generator().manual_seed(1234)
+            while len(self.h_ring) < 64:
+                self.h_ring.append(torch.randn(self.h_qkv.shape, generator=g).to(self.h_qkv.dtype).pin_memory())
+        self.d_qkv.copy_(self.h_ring[self.e2e_i % len(self.h_ring)], non_blocking=True)
+        self.e2e_i += 1
         self.step()
         self.h_out.copy_(self.d_out, non_blocking=True)
 
@@ -896,6 +917,8 @@ def main():
                     help="four launches per layer (append, estimate, top-k, sparse decode) instead of the fused step")
     ap.add_argument("--no-cpu", dest="no_cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--blocks", type=int, default=5, help="the timed steps are repeated this many times; the median block is reported")
+    ap.add_argument("--repeat-token", dest="repeat_token", action="store_true",
+                    help="append the same token's q/k/v at every step instead of a different one")
     ap.add_argument("--no-strong", dest="no_strong", action="store_true",
                     help="N > 1: skip the strong-scaling record (the 32-head model split over the ranks)")
     ap.add_argument("--sweep", action="store_true", help="per-operator sweep over context x budget (one GPU)")
