@@ -137,7 +137,13 @@ int adamas_append_decode(const void* k, const void* v, const void* h, void* q_co
 
 /* Same, with the Hadamard transform done inside: takes q and k (after RoPE) instead of h.
  * Replaces the torch.cat + hadamard_transform + append_kvh sequence of
- * adamas/models/Adamas.py:145-161 with one launch. */
+ * adamas/models/Adamas.py:145-161 with one launch.
+ * Ordering (all decode appends): the launch lets the kernel that follows it in the stream start its
+ * input-independent part early (programmatic dependent launch), and an adamas_estimate that follows
+ * streams the cached codes AS THEY WERE BEFORE this append while the append runs (it excludes the
+ * newest token).  One append per cache between two estimates, as a decode step does, is always safe; two
+ * appends to the same cache back to back followed by an estimate that is to see the first of them need
+ * adamas_set_pdl(0) or an intervening launch. */
 int adamas_append_decode_fused(const void* q, const void* k, const void* v, void* q_code_out,
                                void* kv_data, const int32_t* kv_page_table, int kv_num_pages,
                                int kv_last_page_len,
