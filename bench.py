@@ -167,8 +167,9 @@ def run_reference_arm(args):
 
 
 def two_launch_step(args) -> bool:
-    """decode_step folds the append into the estimate launch for 32 or 64 heads."""
-    return (not args.unfused) and args.heads in (32, 64) and os.environ.get("ADAMAS_FUSED_APPEND", "1") != "0"
+    """decode_step folds the append into the estimate launch for 16, 32 or 64 heads that arrive rotated."""
+    return ((not args.unfused) and args.heads in (16, 32, 64) and not getattr(args, "yarn", 0.0)
+            and os.environ.get("ADAMAS_FUSED_APPEND", "1") != "0")
 
 
 def launches_per_layer(args) -> int:
@@ -240,6 +241,13 @@ class Workload:
         # host buffers.  (The same key appended
         # hundreds of times would put hundreds of equal distances into one histogram bin per head, a pile of
         # same-address atomics that no real sequence produces.)
+        # --yarn F: q and k arrive un-rotated and the step rotates them with a YaRN frequency table (factor F over
+        # an original context of 4096), which makes the append a launch of its own (three launches per layer)
+        self.rope = None
+        if getattr(args, "yarn", 0.0) > 0:
+            from adamas_b200.rope import yarn_inv_freq
+            inv_freq, mscale = yarn_inv_freq(float(args.yarn), 4096)
+            self.rope = {"inv_freq": inv_freq.to(dev), "mscale": mscale}
         self.vary = not getattr(args, "repeat_token", False)
         self.d_tmp = torch.empty_like(self.d_qkv[1]) if self.vary else None
         self.roll_idx = torch.roll(torch.arange(128, device=dev), 1)
@@ -257,7 +265,7 @@ class Workload:
         U, c = self.U, self.c
         q, k, v = self.d_qkv[0, layer], self.d_qkv[1, layer], self.d_qkv[2, layer]
         if not self.args.unfused:
-            U.decode_step(q, k, v, c, layer, out=self.d_out[layer], record_indices=False)
+            U.decode_step(q, k, v, c, layer, out=self.d_out[layer], record_indices=False, rope=self.rope)
             return
         q_code = U.append_qkv_fused(q, k, v, c, layer, out=self.q_code[layer])
         est = U.decode_estimate(q_code, c, layer)
@@ -275,7 +283,7 @@ class Workload:
         U, c = self.U, self.c
         for layer in range(self.layers):
             U.decode_step_dev(self.d_qkv[0, layer], self.d_qkv[1, layer], self.d_qkv[2, layer], c, layer,
-                              out=self.d_out[layer])
+                              out=self.d_out[layer], rope=self.rope)
         if self.after_layers is not None:
             self.after_layers()
         U.seq_len_advance(c)
@@ -728,7 +736,7 @@ def run_sweep(args):
 
                     def batched_body():
                         for l in range(layers):
-                            sb.decode_step_dev(bq[l], bk[l], bv[l], l, out=bo[l])
+                            sb.decode_step_dev(bq[l], bk[l], bv[l], l, out=bo[l], rope=wls[0].rope)
                         sb.advance()
 
                     def batched_step():
@@ -917,6 +925,8 @@ def main():
                     help="four launches per layer (append, estimate, top-k, sparse decode) instead of the fused step")
     ap.add_argument("--no-cpu", dest="no_cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--blocks", type=int, default=5, help="the timed steps are repeated this many times; the median block is reported")
+    ap.add_argument("--yarn", type=float, default=0.0,
+                    help="rotate q and k inside the step with a YaRN table of this factor (original context 4096)")
     ap.add_argument("--repeat-token", dest="repeat_token", action="store_true",
                     help="append the same token's q/k/v at every step instead of a different one")
     ap.add_argument("--no-strong", dest="no_strong", action="store_true",
