@@ -88,6 +88,22 @@ __device__ __forceinline__ void rope_halfwarp(float (&x)[8], unsigned l16, float
   }
 }
 
+// The same rotation with the 64 (cos, sin) pairs of the position given (shared memory): what the decode
+// append uses, where every row of the launch sits at the same position.
+template <typename T>
+__device__ __forceinline__ void rope_halfwarp_cs(float (&x)[8], unsigned l16, const float2* cs_table, bool scaled,
+                                                 float mscale) {
+  const bool upper = (l16 & 8) != 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float other = __shfl_xor_sync(0xffffffffu, x[i], 8);
+    const float2 cs = cs_table[static_cast<int>(l16 & 7) * 8 + i];
+    float r = upper ? fmaf(other, cs.y, x[i] * cs.x) : fmaf(-other, cs.y, x[i] * cs.x);
+    if (scaled) r *= mscale;
+    x[i] = Elem<T>::round(r);
+  }
+}
+
 // In-place rotary embedding of q [seq, Hq, 128] and k [seq, Hk, 128]; token s has position past_len + s.
 template <typename T>
 __global__ void __launch_bounds__(256) rope_kernel(T* __restrict__ q, T* __restrict__ k, int64_t rows_q,
@@ -190,6 +206,21 @@ append_decode_kernel(const T* __restrict__ k, const T* __restrict__ v, const T* 
     kv_entry = code_entry = t - kv_last_page * tgt.page_size;
     pos = static_cast<float>(t);
   }
+  // ROPE: the 64 (cos, sin) pairs of the position, once per block (every row of the launch has the same
+  // position; a sine/cosine of an angle beyond 1e5 rad takes the slow argument reduction, and eight of them
+  // one after the other in every lane cost 6 us per layer at 128K tokens)
+  __shared__ float2 s_cs[kHeadDim / 2];
+  if (ROPE) {
+    if (threadIdx.x < kHeadDim / 2) {
+      const int j = threadIdx.x;
+      const float inv_freq = rp.inv_freq ? __ldg(rp.inv_freq + j)
+                                         : rp.rcp_scale / powf(rp.theta, static_cast<float>(2 * j) * (1.0f / kHeadDim));
+      float sn, cs;
+      sincosf(pos * inv_freq, &sn, &cs);
+      s_cs[j] = make_float2(cs, sn);
+    }
+    __syncthreads();
+  }
   // physical pages of the slot being written: last entries of the two page tables
   const int kv_page = __ldg(tgt.kv_table + kv_last_page);
   const int code_page = __ldg(tgt.code_table + code_last_page);
@@ -214,8 +245,8 @@ append_decode_kernel(const T* __restrict__ k, const T* __restrict__ v, const T* 
   unpack8<T>(ld_16(qh + q_off), a);
   if (ROPE) {
     unpack8<T>(kraw, b);
-    rope_halfwarp<T>(a, l16, pos, rp);
-    rope_halfwarp<T>(b, l16, pos, rp);
+    rope_halfwarp_cs<T>(a, l16, s_cs, rp.inv_freq != nullptr, rp.mscale);
+    rope_halfwarp_cs<T>(b, l16, s_cs, rp.inv_freq != nullptr, rp.mscale);
     kraw = pack8<T>(b);
     if (valid_q) st_16(const_cast<T*>(qh) + q_off, pack8<T>(a));
     if (valid) st_16(const_cast<T*>(k) + in_off, kraw);
