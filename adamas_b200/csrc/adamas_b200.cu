@@ -1297,6 +1297,7 @@ int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, co
     hp.hist = hist;
     hp.n = n;
     hp.cl = pl.cl;
+    hp.seq_len_dev = nullptr;
     ADAMAS_LAUNCH("dist_histogram_kernel", dist_histogram_kernel, dim3(pl.cl, num_heads), dim3(kSaThreads), 0,
                   to_stream(stream), 1, hp);
   }
@@ -1464,13 +1465,19 @@ static int decode_step_impl(void* q, void* k, const void* v, void* o, float* lse
   SaPlan pl;
   if (int rc = sa_plan(n, budget - 1, q_heads * batch, di, &pl)) return rc;
   int rc;
+  // The histogram counts: one L2 atomic per distance from inside the estimate, or, for launches with 3 M
+  // distances and more (a 128K context of 32 heads, three 32K sequences), a launch of their own that
+  // counts in shared memory (measured: the estimate of one 128K sequence 31.7 us with the counts, 23.7
+  // without).  Few heads per GPU keep the counts inside (the extra launch costs more than it saves).
+  const bool count_apart = static_cast<int64_t>(q_heads) * batch * n >= (int64_t(3) << 20) && q_heads >= 16;
+  uint32_t* est_hist = count_apart ? nullptr : hist;
   if (fused_append_enabled() && !rope.on && q_heads == num_heads &&
       (num_heads == 16 || num_heads == 32 || num_heads == 64)) {
     // two launches: the estimate with the append inside, then select + attend.  Not with RoPE: every
     // block of the estimate would repeat the rotation, which costs more than the append launch.
     rc = estimate_append_launch(q, k, v, q_code, kv_data, kv_page_table, pages, last_len, code_data,
                                 code_page_table, pages, last_len, n, num_heads, page_size, dtype, dist_scratch,
-                                dist_stride, hadamard_scale, thresholds3_host, seq_len_dev, hist, pl.cl, stream, seqs,
+                                dist_stride, hadamard_scale, thresholds3_host, seq_len_dev, est_hist, pl.cl, stream, seqs,
                                 batch);
     if (rc) return rc;
   } else {
@@ -1479,8 +1486,20 @@ static int decode_step_impl(void* q, void* k, const void* v, void* o, float* lse
                             thresholds3_host, dtype, stream, rope, seq_len_dev, q_heads, seqs, batch);
     if (rc) return rc;
     rc = estimate_impl(q_code, code_data, code_page_table, n, page_size, num_heads, q_heads, dist_scratch,
-                       dist_stride, ADAMAS_VAL_U16, ADAMAS_METRIC_L1, seq_len_dev, hist, pl.cl, stream, seqs, batch);
+                       dist_stride, ADAMAS_VAL_U16, ADAMAS_METRIC_L1, seq_len_dev, est_hist, pl.cl, stream, seqs, batch);
     if (rc) return rc;
+  }
+  if (count_apart) {
+    DistHistogramParams hp;
+    hp.dist = static_cast<const uint16_t*>(dist_scratch);
+    hp.dist_stride = dist_stride;
+    hp.hist = hist;
+    hp.n = n;
+    hp.cl = pl.cl;
+    hp.seq_len_dev = seq_len_dev;
+    ADAMAS_LAUNCH("dist_histogram_kernel", dist_histogram_kernel, dim3(pl.cl, q_heads, batch), dim3(kSaThreads), 0,
+                  to_stream(stream), 1, hp);
+    if (int rc2 = check_launch("dist_histogram_kernel")) return rc2;
   }
   const int64_t tail = static_cast<int64_t>(kv_last_page_idx) * page_size + last_len - 1;
   rc = select_attend_impl(dist_scratch, dist_stride, n, budget - 1, q, o, nullptr, lse, kv_data, kv_page_table,

@@ -561,26 +561,33 @@ struct DistHistogramParams {
   const uint16_t* dist;
   int64_t dist_stride;
   uint32_t* hist;
-  int n;
+  int n;                        // distances per row, or their upper bound with seq_len_dev
   int cl;
+  const int32_t* seq_len_dev;   // optional: n = *seq_len_dev - 1 (grid.z = sequence: seq_len_dev[z], rows (z, y))
 };
 
+// Per-slice histograms of given distance rows: grid (slices, rows[, sequences]).  Used where the rows exist
+// already (the stand-alone select_attend call) and, in the fused step, for launches with so many distances
+// that one L2 atomic per distance from inside the estimate would bound it (3 M and more per launch): a
+// block counts its slice in shared memory and stores 512 totals.
 __global__ void __launch_bounds__(kSaThreads) dist_histogram_kernel(const DistHistogramParams p) {
   __shared__ unsigned h_local[kSaBins];
   const int tid = threadIdx.x;
-  const int r = blockIdx.x, head = blockIdx.y;
+  const int r = blockIdx.x;
+  const int head = blockIdx.z * gridDim.y + blockIdx.y;
   h_local[tid] = 0;
   __syncthreads();
   grid_dependency_wait();
   grid_launch_dependents();
-  const int G = (p.n + 7) >> 3;
-  const int gpb = sa_granules_per_block(p.n, p.cl);
+  const int n = p.seq_len_dev ? __ldg(p.seq_len_dev + blockIdx.z) - 1 : p.n;
+  const int G = (n + 7) >> 3;
+  const int gpb = sa_granules_per_block(n, p.cl);
   const int g_end = min(G, (r + 1) * gpb);
   const uint4* gbase = reinterpret_cast<const uint4*>(p.dist + static_cast<int64_t>(head) * p.dist_stride);
   for (int g = r * gpb + tid; g < g_end; g += kSaThreads) {
     const uint4 v = ld_16(gbase + g);
     const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-    const int valid = min(8, p.n - g * 8);
+    const int valid = min(8, n - g * 8);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const unsigned d = (w[j >> 1] >> ((j & 1) * 16)) & 0xffffu;

@@ -158,3 +158,53 @@ def test_batched_graph_replay_over_tokens():
     assert batch.seq_lens.cpu().tolist() == [L + tokens for L in lengths]
     from adamas_b200 import _lib
     assert _lib.device_error(clear=False) == 0
+
+
+def test_large_launches_count_their_histograms_in_a_launch_of_their_own():
+    """From 3 M distances per launch the fused step counts the histograms in a separate launch instead of
+    inside the estimate.  Four sequences of 33K tokens x 32 heads cross that line as a batch and stay below
+    it one by one: both forms must select the same slots; one 66K sequence of 64 heads is checked against
+    the oracle."""
+    _, K, U = _mods()
+    lengths, Hq, H, ps, budget, dtype = [33100, 32900, 33500, 33001], 32, 32, 16, 1024, torch.float16
+    B = len(lengths)
+    cap = max(lengths) + 2 * ps
+    cs, ks, vs = _controllers(lengths, Hq, H, ps, budget // ps, dtype, cap, seed=21)
+    cs2, _, _ = _controllers(lengths, Hq, H, ps, budget // ps, dtype, cap, seed=21)
+    q = _randn((B, Hq, 128), 5, dtype)
+    k_new = torch.stack([ks[i][L - 1] for i, L in enumerate(lengths)])
+    v_new = torch.stack([vs[i][L - 1] for i, L in enumerate(lengths)])
+    want_o, want_idx = [], []
+    for i, c in enumerate(cs2):
+        c.prepare_hadamard(1)
+        c.begin_forward(1)
+        o = U.decode_step(q[i:i + 1].to(DEV), k_new[i:i + 1].to(DEV), v_new[i:i + 1].to(DEV), c, 0)
+        want_o.append(o[0].clone()); want_idx.append(c.topk_dindices_buffer.clone())
+        c.end_forward()
+    batch = U.SequenceBatch(cs)
+    batch.prepare(1)
+    batch.sync_seq_lens()
+    idx = torch.full((B * Hq, budget - 1), -1, dtype=torch.int32, device=DEV)
+    o = batch.decode_step_dev(q.to(DEV), k_new.to(DEV), v_new.to(DEV), 0, indices_out=idx)
+    torch.cuda.synchronize()
+    assert int(K.histogram_counts(batch._hist).abs().sum().item()) == 0
+    for i in range(B):
+        assert torch.equal(idx[i * Hq:(i + 1) * Hq], want_idx[i]), f"sequence {i}: selected slots"
+        _assert_attn_close(o[i], want_o[i])
+    del cs, cs2, ks, vs, batch
+    torch.cuda.empty_cache()
+    # one long sequence of many heads, against the oracle
+    L, H2 = 66000, 64
+    cs, ks, vs = _controllers([L], H2, H2, ps, budget // ps, dtype, L + 2 * ps, seed=33)
+    c = cs[0]
+    q1 = _randn((1, H2, 128), 6, dtype)
+    c.prepare_hadamard(1)
+    c.begin_forward(1)
+    o = U.decode_step(q1.to(DEV), ks[0][L - 1:L].to(DEV), vs[0][L - 1:L].to(DEV), c, 0)
+    torch.cuda.synchronize()
+    r = ref.decode_step(q1[0], ks[0][:L], vs[0][:L], budget)
+    table = np.asarray(c.kv_cache.indicies)
+    np.testing.assert_array_equal(c.topk_dindices_buffer.cpu().numpy(), table[r["sel"] // ps] * ps + r["sel"] % ps)
+    _assert_attn_close(o[0], r["out"])
+    from adamas_b200 import _lib
+    assert _lib.device_error(clear=False) == 0
