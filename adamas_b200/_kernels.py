@@ -673,6 +673,16 @@ def seq_len_advance(seq_len: torch.Tensor, delta: int = 1) -> None:
 # ----------------------------------------------------------------------------------------------
 # several sequences in one launch
 # ----------------------------------------------------------------------------------------------
+def dist_histograms(dist: torch.Tensor, hist: torch.Tensor, slices: int) -> None:
+    """Counts the integer distance rows `dist` [H, n] into the histogram scratch (`slices` per-slice
+    histograms per row): what estimate_attn_score(..., hist=...) does on the side, as a launch of its own."""
+    _check_rows(dist, "dist")
+    _require(dist.dtype in (torch.int16, torch.uint16), "dist must hold 16-bit integer distances")
+    h, n = dist.shape
+    _lib.check(lib.adamas_dist_histograms(_ptr(dist), dist.stride(0), n, h, int(slices), _ptr(_check_hist(hist, h)),
+                                          _stream()), "dist_histograms")
+
+
 def sequence_descriptors(kv_datas, code_datas, kv_tables, code_tables) -> torch.Tensor:
     """Device array of adamas_seq_desc_t for one layer: int64 [batch, 4] holding, per sequence, the
     addresses of its KV cache, code cache, KV page table and code page table.  The tensors must stay

@@ -63,6 +63,7 @@ SIGNATURES = {
                                      _P, _L, _P, _P, _L, _F, _FP, _F, _F, _P, _F, _F, _P],
     "adamas_dense_step_batch_dev": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
                                     _F, _FP, _F, _F, _P, _F, _F, _P],
+    "adamas_dist_histograms": [_P, _L, _I, _I, _I, _P, _P],
     "adamas_hist_rowsum": [_P, _I, _I, _P, _P],
     "adamas_global_cut": [_P, _I, _I, _I, _I, _P, _P],
     "adamas_apply_rope_table_in_place": [_P, _P, _L, _I, _I, _I, _L, _P, _F, _I, _P],

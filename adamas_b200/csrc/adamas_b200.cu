@@ -1306,6 +1306,25 @@ int adamas_select_attend(const void* dist, int64_t dist_stride, int n, int k, co
                             ext_cut, nullptr, out_idx, out_stride, sm_scale, pl, stream);
 }
 
+int adamas_dist_histograms(const void* dist, int64_t dist_stride, int n, int num_heads, int slices, uint32_t* hist,
+                           adamas_stream_t stream) {
+  ADAMAS_REQUIRE(dist && hist, "null pointer");
+  ADAMAS_REQUIRE(n >= 1 && num_heads >= 1 && slices >= 1 && slices <= kSaMaxSlices, "n / num_heads / slices out of range");
+  ADAMAS_REQUIRE((reinterpret_cast<uintptr_t>(dist) & 15) == 0 && (num_heads == 1 || (dist_stride * 2) % 16 == 0),
+                 "distance rows must start on 16-byte boundaries");
+  ADAMAS_REQUIRE(dist_stride >= n || num_heads == 1, "dist_stride smaller than n");
+  DistHistogramParams hp;
+  hp.dist = static_cast<const uint16_t*>(dist);
+  hp.dist_stride = dist_stride;
+  hp.hist = hist;
+  hp.n = n;
+  hp.cl = slices;
+  hp.seq_len_dev = nullptr;
+  ADAMAS_LAUNCH("dist_histogram_kernel", dist_histogram_kernel, dim3(slices, num_heads), dim3(kSaThreads), 0,
+                to_stream(stream), 1, hp);
+  return check_launch("dist_histogram_kernel");
+}
+
 int adamas_hist_rowsum(const uint32_t* hist, int num_heads, int slices, uint32_t* out, adamas_stream_t stream) {
   ADAMAS_REQUIRE(hist && out, "null pointer");
   ADAMAS_REQUIRE(num_heads >= 1 && slices >= 1 && slices <= kSaMaxSlices, "num_heads / slices out of range");

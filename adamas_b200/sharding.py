@@ -143,10 +143,16 @@ class CudaOps:
             return self._hist_out
         # (the slice count depends on the shard's length and on the upper bound of its winners)
         self._slices = self.k.select_attend_slices(n, max(1, min(k, n)), c.num_heads)
-        self.k.estimate_attn_score(self.q_code, c.distance_scratch(n), c.hadamard_cache.buf_layer(self.layer),
+        # (from about 3 M distances per launch a counting launch of its own is cheaper than one L2 atomic
+        # per distance from inside the estimate)
+        count_apart = c.num_heads * n >= (3 << 20)
+        dist = c.distance_scratch(n)
+        self.k.estimate_attn_score(self.q_code, dist, c.hadamard_cache.buf_layer(self.layer),
                                    c.hadamard_indices, None, c.hadamard_cache.last_page_len,
                                    c.hadamard_last_page_idx, c.layout, exclude_last=self.owns_tail,
-                                   hist=c.hist_scratch, hist_slices=self._slices)
+                                   hist=None if count_apart else c.hist_scratch, hist_slices=self._slices)
+        if count_apart:
+            self.k.dist_histograms(dist, c.hist_scratch, self._slices)
         self.k.hist_rowsum(c.hist_scratch, self._slices, self._hist_out)
         return self._hist_out
 

@@ -324,6 +324,13 @@ int adamas_select_attend_slices(int n, int k, int num_heads, int* slices);
 
 /* out[h][bin] = sum over the first `slices` histogram rows of head h in a histogram scratch table that
  * an adamas_estimate call has filled: the shard's 512-bin histogram per head, ready to be exchanged. */
+/* Counts rows of integer distances (ADAMAS_VAL_U16, as adamas_estimate writes them) into the histogram
+ * scratch, `slices` per-slice histograms per row, the layout adamas_select_attend(..., hist_ready = 1)
+ * reads: what adamas_estimate does on the side when it is given `hist`, as a launch of its own that counts
+ * in shared memory.  Cheaper than counting inside the estimate from about 3 M distances per call. */
+int adamas_dist_histograms(const void* dist, int64_t dist_stride, int n, int num_heads, int slices,
+                           uint32_t* hist, adamas_stream_t stream);
+
 int adamas_hist_rowsum(const uint32_t* hist, int num_heads, int slices, uint32_t* out, adamas_stream_t stream);
 
 /* all_hists [num_shards][H][512]: the shards' histograms in shard order (ascending token ranges).

@@ -134,6 +134,10 @@ def test_select_attend_with_prepared_histograms_and_without_newest_token():
     got_hist = K.histogram_counts(hist).cpu().numpy().sum(1)[:, :385]
     want_hist = np.stack([np.bincount(row, minlength=385) for row in r["dist"]])
     np.testing.assert_array_equal(got_hist, want_hist)
+    # the counting launch of its own gives the same table, slice by slice
+    hist2 = K.histogram_scratch(H, DEV)
+    K.dist_histograms(dist, hist2, slices)
+    assert torch.equal(K.histogram_counts(hist2), K.histogram_counts(hist))
     o32 = torch.zeros(H, 128, dtype=torch.float32, device=DEV)
     lse = torch.zeros(H, dtype=torch.float32, device=DEV)
     idx = torch.zeros(H, k, dtype=torch.int32, device=DEV)
