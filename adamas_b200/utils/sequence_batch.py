@@ -69,7 +69,7 @@ class SequenceBatch:
         o = out if out is not None else torch.empty_like(q)
         c0 = self.controllers[0]
         if dense:
-            self._dense._wrapper.dense_step_batch_dev(q, k, v, o, self._q_code, self._seqs[layer_idx], self.seq_lens,
+            self._dense.dense_step_batch_dev(q, k, v, o, self._q_code, self._seqs[layer_idx], self.seq_lens,
                                                       self.max_seq_len, self.page_size, scale=scale, rope=rope)
             return o
         _kernels.decode_step_batch_dev(q, k, v, o, self._q_code, self._seqs[layer_idx], self.seq_lens,
