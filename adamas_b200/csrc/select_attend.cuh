@@ -18,8 +18,8 @@
 //          derives this by itself from the same table: no exchange between blocks;
 //   pick   ordered compaction of the block's winners into a list in shared memory;
 //   attend the rows of the list are dealt out evenly to the 16 warps; a warp gathers the K and V rows of
-//          its tokens itself (one 256-byte bulk (TMA) copy per row into its own part of the tile,
-//          counted by its own mbarrier, bounded wait), computes q.K with four lanes per token, a
+//          its tokens itself (16-byte asynchronous copies, a half-warp per 256-byte row, into its own
+//          part of the tile; K rows as one group, V rows as a second), computes q.K with four lanes per token, a
 //          softmax in base 2 over its tokens and P.V with four dimensions per lane: no block barrier
 //          inside the attention;
 //   merge  the 16 warps' partial (o, m, l) are merged in shared memory and the block's partial goes to
@@ -92,8 +92,6 @@ struct SaShared {
   unsigned cut, need_eq, lt_before, eq_before;
   unsigned last;   // this block arrived last at the head's counter
   uint4 q[16];     // the head's query row
-  unsigned long long bar[kSaWarps];   // one mbarrier per warp: the bytes of its own K rows
-  unsigned long long bar_v[kSaWarps];  // ... and of its own V rows
 };
 
 // Dynamic shared memory: the tile (16 warps x (12 K rows + 12 V rows) x 256 B; a warp parks its partial
@@ -127,19 +125,9 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   uint32_t* head_scratch = p.hist + static_cast<size_t>(head) * kSaScratchWordsPerHead;
   float* slots = reinterpret_cast<float*>(head_scratch + kSaMaxSlices * kSaBins);     // [CL][kSaSlotWords]
   uint4* s_q = sh.q;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sh.bar);
-  uint64_t* bars_v = reinterpret_cast<uint64_t*>(sh.bar_v);
 
   // ---- set-up that needs no input (overlaps the tail of the preceding kernel) -----------------------
-  if (tid == 0) {
-#pragma unroll
-    for (int w2 = 0; w2 < kSaWarps; ++w2) {
-      mbar_init(&bars[w2], 1);
-      mbar_init(&bars_v[w2], 1);
-    }
-    sh.cut = 0xffffffffu;
-    mbar_fence_init();
-  }
+  if (tid == 0) sh.cut = 0xffffffffu;
   __syncthreads();
   grid_dependency_wait();
   grid_launch_dependents();
@@ -348,15 +336,17 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
 
   // ---- attend: every warp over its own rows --------------------------------------------------------------
   // The rows are dealt out evenly: warp w owns rows w*rpw .. of the list.  It gathers them itself, kSaWarpRows
-  // at a time: lanes 0-15 issue the 256-byte bulk (TMA) copies of its K rows, lanes 16-31 those of its V
-  // rows, into the warp's own part of the tile, counted by the warp's own mbarrier (bounded wait); then
-  // q.K with four lanes per token, a softmax in base 2 over its tokens and P.V with four dimensions per
-  // lane.  Nothing in here is shared between warps: no block barrier inside the attention.
-  // A bulk copy with a different address in every lane is issued lane after lane (about 45 ns each), so
-  // what matters is that all 16 warps issue at once and no warp more than a couple of dozen copies.
-  // Measured alternatives: all copies issued by the first n_loc / 16 warps (1.9 us instead of 0.7);
-  // plain vector loads into registers instead of the tile (all rows cannot be in flight at once in 64
-  // registers: the second round of a warp pays the memory latency again, 4.5 us in this phase).
+  // at a time, with 16-byte asynchronous copies (cp.async), a half-warp per 256-byte row, into the warp's own
+  // part of the tile: first all K rows (one commit group), then all V rows (a second group); then q.K with
+  // four lanes per token as soon as the K group has landed, a softmax in base 2 over its tokens and, after
+  // the V group, P.V with four dimensions per lane.  Nothing in here is shared between warps: no block
+  // barrier inside the attention.
+  // Measured alternatives for the gather (select+attend alone, 32K / 1024): one 256-byte bulk (TMA) copy
+  // per row with an mbarrier per warp 12.4-12.5 us against 12.2 with the 16-byte copies (a bulk copy with
+  // a different address in every lane is issued lane after lane, about 45 ns each: 0.7 us for the 16 rows
+  // of a warp); all bulk copies issued by the first n_loc / 16 warps 1.9 us instead of 0.7; plain vector
+  // loads into registers instead of the tile (all rows cannot be in flight at once in 64 registers: the
+  // second round of a warp pays the memory latency again) 4.5 us in this phase.
   __syncthreads();   // the list and the query are complete
   float m_run = -INFINITY, l_run = 0.f;   // l_run is kept by the lanes with quarter == 0
   float o_acc[4] = {0.f, 0.f, 0.f, 0.f};  // dimensions 4*lane .. 4*lane+3
@@ -365,8 +355,6 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   const int my_total = max(0, min(rpw, n_loc - my_first));
   uint8_t* wk = sa_tile + warp * (2 * kSaWarpRows * 256);   // this warp's K rows, then its V rows
   uint8_t* wv = wk + kSaWarpRows * 256;
-  uint64_t* bar = &bars[warp];
-  uint64_t* bar_v = &bars_v[warp];
   // q.K mapping: four lanes per token (tq = lane / 4, quarter = lane % 4); step i of a lane reads chunk
   // 4*quarter + ((i + quarter + tq) & 3).  A quarter-warp covers an even and an odd token; the rows are
   // 256 bytes apart (the same banks), and with this order the two tokens' four chunks fall on
@@ -377,39 +365,33 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
 #pragma unroll
   for (int i = 0; i < 4; ++i) qpk[i] = s_q[4 * quarter + ((i + quarter + tq) & 3)];
   constexpr int kGroups = (kSaWarpRows + 7) / 8;   // groups of 8 rows per round
-  unsigned phase = 0;
   for (int done = 0; done < my_total; done += kSaWarpRows) {
     const int my_rows = min(kSaWarpRows, my_total - done);
-    if (done > 0) {
-      // the rows of the round before have been read (generic proxy); the copies write through the async proxy
-      __syncwarp();
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
-    if (lane == 0) {
-      mbar_arrive_expect_tx(bar, static_cast<unsigned>(my_rows) * (kHeadDim * 2));
-      mbar_arrive_expect_tx(bar_v, static_cast<unsigned>(my_rows) * (kHeadDim * 2));
-    }
-    __syncwarp();
+    if (done > 0) __syncwarp();   // every lane has read the rows of the round before
+    // 16-byte asynchronous copies, a half-warp per 256-byte row: all K rows of the round as one group, then
+    // all V rows as a second one, so that the logits are formed while the V rows are still on their way.
     {
-      const int r = lane & 15;
-      const int is_v = lane >> 4;
-      if (r < my_rows) {
-        const unsigned slot = static_cast<unsigned>(s_list[my_first + done + r]);
-        unsigned page, e;
-        if (p.ps_shift >= 0) {
-          page = slot >> p.ps_shift;
-          e = slot & (ps - 1);
-        } else {
-          page = slot / ps;
-          e = slot - page * ps;
+      const int half = lane >> 4, l16 = lane & 15;
+#pragma unroll
+      for (int kv = 0; kv < 2; ++kv) {
+        for (int r = half; r < my_rows; r += 2) {
+          const unsigned slot = static_cast<unsigned>(s_list[my_first + done + r]);
+          unsigned page, e;
+          if (p.ps_shift >= 0) {
+            page = slot >> p.ps_shift;
+            e = slot & (ps - 1);
+          } else {
+            page = slot / ps;
+            e = slot - page * ps;
+          }
+          const T* src = kvp + (static_cast<int64_t>(page * (2 * ps) + e) * H + head_kv) * kHeadDim + (kv ? v_delta : 0);
+          cp_async_16((kv ? wv : wk) + r * 256 + l16 * 16, src + l16 * 8);
         }
-        const T* src = kvp + (static_cast<int64_t>(page * (2 * ps) + e) * H + head_kv) * kHeadDim + (is_v ? v_delta : 0);
-        bulk_copy_g2s((is_v ? wv : wk) + r * 256, src, kHeadDim * 2, is_v ? bar_v : bar);
+        cp_async_commit();
       }
     }
-    // The K rows are asked for first (lanes 0-15) and land first: the logits of the whole round are formed
-    // while the V rows are still on their way.
-    if (!mbar_wait_bounded(bar, phase, 1u << 20)) atomicOr(&g_adamas_error, kErrGatherTimeout);
+    cp_async_wait<1>();
+    __syncwarp();
     float logit[kGroups];
 #pragma unroll
     for (int g = 0; g < kGroups; ++g) {
@@ -431,8 +413,8 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
       acc += __shfl_xor_sync(0xffffffffu, acc, 2);
       logit[g] = live ? acc * p.scale_log2 : -INFINITY;
     }
-    if (!mbar_wait_bounded(bar_v, phase, 1u << 20)) atomicOr(&g_adamas_error, kErrGatherTimeout);
-    phase ^= 1u;
+    cp_async_wait<0>();
+    __syncwarp();
 #pragma unroll
     for (int g = 0; g < kGroups; ++g) {
       const int base = g * 8;
