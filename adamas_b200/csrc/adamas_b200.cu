@@ -82,7 +82,7 @@ int check_q_heads(int num_heads, int num_q_heads) {
   return ADAMAS_OK;
 }
 
-constexpr int kEstAppendStatic = 1280;   // static shared memory of estimate_append_kernel, rounded up
+constexpr int kEstAppendStatic = 1792;   // static shared memory of estimate_append_kernel (with the cos / sin table), rounded up
 constexpr int kEstPagesStatic = 8448;    // static shared memory of estimate_pages_kernel, rounded up
 constexpr int kSaMaxDynSmem = 160 * 1024;   // dynamic shared memory select_attend may ask for (a long winner list)
 
@@ -126,15 +126,18 @@ int get_device_info(const DeviceInfo** out) {
     EST_ATTR_ALL(1, uint16_t);
 #undef EST_ATTR_ALL
 #undef EST_ATTR
-#define ESTA_ATTR(T, HPW)                                                                              \
-  ADAMAS_CUDA(cudaFuncSetAttribute(estimate_append_kernel<T, HPW>,                                     \
+#define ESTA_ATTR(T, HPW, R)                                                                           \
+  ADAMAS_CUDA(cudaFuncSetAttribute((estimate_append_kernel<T, HPW, R>),                                \
                                    cudaFuncAttributeMaxDynamicSharedMemorySize, est_max - kEstAppendStatic)); \
-  ADAMAS_CUDA(cudaFuncSetAttribute(estimate_append_kernel<T, HPW>,                                     \
+  ADAMAS_CUDA(cudaFuncSetAttribute((estimate_append_kernel<T, HPW, R>),                                \
                                    cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared))
-#define ESTA_ATTR_ALL(T) \
-  ESTA_ATTR(T, 1);       \
-  ESTA_ATTR(T, 2);       \
-  ESTA_ATTR(T, 4)
+#define ESTA_ATTR_ALL(T)    \
+  ESTA_ATTR(T, 1, false);   \
+  ESTA_ATTR(T, 2, false);   \
+  ESTA_ATTR(T, 4, false);   \
+  ESTA_ATTR(T, 1, true);    \
+  ESTA_ATTR(T, 2, true);    \
+  ESTA_ATTR(T, 4, true)
     ESTA_ATTR_ALL(__half);
     ESTA_ATTR_ALL(__nv_bfloat16);
 #undef ESTA_ATTR_ALL
@@ -1208,8 +1211,13 @@ int select_attend_impl(const void* dist, int64_t dist_stride, int n, int k, cons
                        float* lse, const void* kv_data, const int32_t* kv_page_table, int page_size, int num_heads,
                        int q_heads, int dtype, int tail_mode, unsigned tail_slot, uint32_t* hist, const int32_t* ext_cut,
                        const int32_t* seq_len_dev, int32_t* out_idx, int64_t out_stride, float sm_scale,
-                       const SaPlan& pl, adamas_stream_t stream, const SeqDesc* seqs = nullptr, int batch = 1) {
+                       const SaPlan& pl, adamas_stream_t stream, const SeqDesc* seqs = nullptr, int batch = 1,
+                       const RopeSpec* rope_q = nullptr) {
   SelectAttendParams prm;
+  prm.rope_on = rope_q != nullptr && rope_q->on;
+  prm.rope = RopeParams{1.f, 1e4f, nullptr, 1.f};
+  if (prm.rope_on)
+    prm.rope = RopeParams{rope_q->scale > 0.f ? 1.0f / rope_q->scale : 1.f, rope_q->theta, rope_q->inv_freq, rope_q->mscale};
   prm.seqs = seqs;
   if (!seqs) batch = 1;
   prm.dist = static_cast<const uint16_t*>(dist);
@@ -1361,7 +1369,7 @@ static int estimate_append_launch(const void* q, const void* k, const void* v, v
                                   int code_last_page_len, int n, int num_heads, int page_size, int dtype, void* dist,
                                   int64_t dist_stride, float hadamard_scale, const float* thresholds3_host,
                                   const int32_t* seq_len_dev, uint32_t* hist, int hist_cl, adamas_stream_t stream,
-                                  const SeqDesc* seqs = nullptr, int batch = 1) {
+                                  const SeqDesc* seqs = nullptr, int batch = 1, const RopeSpec& rope = RopeSpec()) {
   ADAMAS_REQUIRE(q && k && v && q_code && dist && (seqs || (kv_data && code_data && kv_page_table && code_page_table)),
                  "null pointer");
   if (!seqs) batch = 1;
@@ -1412,15 +1420,22 @@ static int estimate_append_launch(const void* q, const void* k, const void* v, v
   ap.code_entry = code_last_page_len - 1;
   ap.scale = hadamard_scale;
   ap.th = make_thresholds(thresholds3_host);
+  ap.rp = RopeParams{rope.scale > 0.f ? 1.0f / rope.scale : 1.f, rope.theta, rope.inv_freq, rope.mscale};
   cudaStream_t st = to_stream(stream);
-#define LAUNCH_ESTA(T, HPW)                                                                        \
-  ADAMAS_LAUNCH("estimate_append_kernel", (estimate_append_kernel<T, HPW>), dim3(blocks, batch),   \
+#define LAUNCH_ESTA(T, HPW, R)                                                                        \
+  ADAMAS_LAUNCH("estimate_append_kernel", (estimate_append_kernel<T, HPW, R>), dim3(blocks, batch),   \
                 dim3(kEstThreads), smem, st, 1, prm, ap)
-#define LAUNCH_ESTA_T(T)                  \
-  do {                                    \
-    if (hpw == 1) LAUNCH_ESTA(T, 1);      \
-    else if (hpw == 2) LAUNCH_ESTA(T, 2); \
-    else LAUNCH_ESTA(T, 4);               \
+#define LAUNCH_ESTA_T(T)                                                        \
+  do {                                                                          \
+    if (rope.on) {                                                              \
+      if (hpw == 1) LAUNCH_ESTA(T, 1, true);                                    \
+      else if (hpw == 2) LAUNCH_ESTA(T, 2, true);                               \
+      else LAUNCH_ESTA(T, 4, true);                                             \
+    } else {                                                                    \
+      if (hpw == 1) LAUNCH_ESTA(T, 1, false);                                   \
+      else if (hpw == 2) LAUNCH_ESTA(T, 2, false);                              \
+      else LAUNCH_ESTA(T, 4, false);                                            \
+    }                                                                           \
   } while (0)
   if (dtype == ADAMAS_F16) LAUNCH_ESTA_T(__half); else LAUNCH_ESTA_T(__nv_bfloat16);
 #undef LAUNCH_ESTA_T
@@ -1490,14 +1505,14 @@ static int decode_step_impl(void* q, void* k, const void* v, void* o, float* lse
   // without).  Few heads per GPU keep the counts inside (the extra launch costs more than it saves).
   const bool count_apart = static_cast<int64_t>(q_heads) * batch * n >= (int64_t(3) << 20) && q_heads >= 16;
   uint32_t* est_hist = count_apart ? nullptr : hist;
-  if (fused_append_enabled() && !rope.on && q_heads == num_heads &&
-      (num_heads == 16 || num_heads == 32 || num_heads == 64)) {
-    // two launches: the estimate with the append inside, then select + attend.  Not with RoPE: every
-    // block of the estimate would repeat the rotation, which costs more than the append launch.
+  const bool two_launches = fused_append_enabled() && q_heads == num_heads &&
+                            (num_heads == 16 || num_heads == 32 || num_heads == 64);
+  if (two_launches) {
+    // two launches: the estimate with the append (and, with RoPE, the rotation) inside, then select + attend
     rc = estimate_append_launch(q, k, v, q_code, kv_data, kv_page_table, pages, last_len, code_data,
                                 code_page_table, pages, last_len, n, num_heads, page_size, dtype, dist_scratch,
                                 dist_stride, hadamard_scale, thresholds3_host, seq_len_dev, est_hist, pl.cl, stream, seqs,
-                                batch);
+                                batch, rope);
     if (rc) return rc;
   } else {
     rc = append_decode_impl(k, v, q, k, true, q_code, kv_data, kv_page_table, pages, last_len, code_data,
@@ -1523,7 +1538,8 @@ static int decode_step_impl(void* q, void* k, const void* v, void* o, float* lse
   const int64_t tail = static_cast<int64_t>(kv_last_page_idx) * page_size + last_len - 1;
   rc = select_attend_impl(dist_scratch, dist_stride, n, budget - 1, q, o, nullptr, lse, kv_data, kv_page_table,
                           page_size, num_heads, q_heads, dtype, seq_len_dev ? 2 : 1, static_cast<unsigned>(tail), hist, nullptr,
-                          seq_len_dev, out_idx, out_stride, sm_scale, pl, stream, seqs, batch);
+                          seq_len_dev, out_idx, out_stride, sm_scale, pl, stream, seqs, batch,
+                          two_launches ? &rope : nullptr);   // (after a separate append q is rotated already)
   if (rc) {
     // the estimate has filled the histogram table and nothing will clear it: restore the all-zero state
     cudaMemsetAsync(hist, 0, hist_bytes(q_heads * batch), to_stream(stream));

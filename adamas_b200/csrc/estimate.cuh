@@ -391,15 +391,23 @@ struct StepAppend {
   int kv_last_page, kv_entry, code_last_page, code_entry;
   float scale;
   Thresholds th;
+  RopeParams rp;           // ROPE: q and k arrive un-rotated
 };
 
-template <typename T, int HPW>
+// ROPE: q and k arrive un-rotated.  Every block forms the position's 64 (cos, sin) pairs once (64 consumer
+// threads, before the kernel's dependency resolves: the position does not depend on the preceding kernel) and
+// each consumer warp rotates its query rows in registers before it codes them.  The block that appends also
+// rotates the key, stores the rotated row into the cache and back into the caller's k.  The caller's q is NOT
+// rotated here (other blocks are still reading it un-rotated): the select+attend launch that follows rotates
+// it the same way for its own use and writes it back.
+template <typename T, int HPW, bool ROPE>
 __global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const EstimateParams p, const StepAppend a) {
   static_assert(HPW == 1 || HPW == 2 || HPW == 4, "heads per warp");
   extern __shared__ uint4 est_smem[];
   __shared__ __align__(8) uint64_t full_bar[kEstStages];
   __shared__ __align__(8) uint64_t empty_bar[kEstStages];
   __shared__ __align__(16) uint16_t s_code[kEstConsumerWarps][32];   // a warp's two rows of code words
+  __shared__ float2 s_cs[ROPE ? kHeadDim / 2 : 1];
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
@@ -412,6 +420,11 @@ __global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const Esti
     est_produce<false>(p, geom, ring, my_tiles, lane, warp - kEstConsumerWarps);
     grid_launch_dependents();
     return;
+  }
+  if (ROPE) {
+    // the new token sits at position n_tokens (= tokens before it)
+    if (tid < kHeadDim / 2) s_cs[tid] = rope_cos_sin(tid, static_cast<float>(geom.n_tokens), a.rp);
+    asm volatile("bar.sync 1, %0;" ::"n"(kEstConsumerWarps * 32) : "memory");   // the consumer warps only
   }
   // q, k, v are the preceding kernel's output
   grid_dependency_wait();
@@ -445,6 +458,7 @@ __global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const Esti
     const bool writer = appender && (HPW > 1 || half == 0);
     float x[8];
     unpack8<T>(ld_16(static_cast<const T*>(a.q) + in_off), x);
+    if (ROPE) rope_halfwarp_cs<T>(x, l16, s_cs, a.rp.inv_freq != nullptr, a.rp.mscale);
     wht128_halfwarp(x, l16);
     scale_round<T>(x, a.scale);
     const unsigned word = bucketize_pack8(x, a.th);   // code word l16 of `head`
@@ -469,10 +483,15 @@ __global__ void __launch_bounds__(kEstThreads) estimate_append_kernel(const Esti
       const int64_t k_off =
           ((static_cast<int64_t>(kv_page) * 2 * ps + kv_entry) * H + head) * kHeadDim + l16 * 8;
       const int64_t v_delta = static_cast<int64_t>(ps) * H * kHeadDim;
-      const uint4 kraw = ld_16(static_cast<const T*>(a.k) + in_off);
+      uint4 kraw = ld_16(static_cast<const T*>(a.k) + in_off);
       const uint4 vraw = ld_16(static_cast<const T*>(a.v) + in_off);
       float b[8];
       unpack8<T>(kraw, b);
+      if (ROPE) {
+        rope_halfwarp_cs<T>(b, l16, s_cs, a.rp.inv_freq != nullptr, a.rp.mscale);
+        kraw = pack8<T>(b);
+        if (writer) st_16(static_cast<T*>(const_cast<void*>(a.k)) + in_off, kraw);
+      }
       if (writer) {
         st_16(kv + k_off, kraw);
         st_16(kv + k_off + v_delta, vraw);

@@ -88,6 +88,16 @@ __device__ __forceinline__ void rope_halfwarp(float (&x)[8], unsigned l16, float
   }
 }
 
+// (cos, sin) of dimension pair j at position pos: the one expression every kernel that rotates a decode
+// token uses, so that all of them produce the same bits.
+__device__ __forceinline__ float2 rope_cos_sin(int j, float pos, const RopeParams& rp) {
+  const float inv_freq = rp.inv_freq ? __ldg(rp.inv_freq + j)
+                                     : rp.rcp_scale / powf(rp.theta, static_cast<float>(2 * j) * (1.0f / kHeadDim));
+  float sn, cs;
+  sincosf(pos * inv_freq, &sn, &cs);
+  return make_float2(cs, sn);
+}
+
 // The same rotation with the 64 (cos, sin) pairs of the position given (shared memory): what the decode
 // append uses, where every row of the launch sits at the same position.
 template <typename T>
@@ -211,14 +221,7 @@ append_decode_kernel(const T* __restrict__ k, const T* __restrict__ v, const T* 
   // one after the other in every lane cost 6 us per layer at 128K tokens)
   __shared__ float2 s_cs[kHeadDim / 2];
   if (ROPE) {
-    if (threadIdx.x < kHeadDim / 2) {
-      const int j = threadIdx.x;
-      const float inv_freq = rp.inv_freq ? __ldg(rp.inv_freq + j)
-                                         : rp.rcp_scale / powf(rp.theta, static_cast<float>(2 * j) * (1.0f / kHeadDim));
-      float sn, cs;
-      sincosf(pos * inv_freq, &sn, &cs);
-      s_cs[j] = make_float2(cs, sn);
-    }
+    if (threadIdx.x < kHeadDim / 2) s_cs[threadIdx.x] = rope_cos_sin(threadIdx.x, pos, rp);
     __syncthreads();
   }
   // physical pages of the slot being written: last entries of the two page tables

@@ -30,6 +30,7 @@
 //          blocks of a head stayed resident until the slowest had finished, 2 us at 32K / 1024).
 #pragma once
 #include "common.cuh"
+#include "hadamard_append.cuh"
 
 namespace adamas {
 
@@ -83,6 +84,11 @@ struct SelectAttendParams {
   int64_t out_stride;
   int list_capacity;        // entries of the shared-memory winner list (a block's winners at most, plus the newest token)
   float scale_log2;
+  // q arrives un-rotated (the append-fused estimate in front of this launch has coded the rotated query but left
+  // q alone): every block rotates it for position n for its own use, the block that finishes a head writes
+  // the rotated row back into q
+  int rope_on;
+  RopeParams rope;
 };
 
 struct SaShared {
@@ -92,6 +98,7 @@ struct SaShared {
   unsigned cut, need_eq, lt_before, eq_before;
   unsigned last;   // this block arrived last at the head's counter
   uint4 q[16];     // the head's query row
+  float2 cs[kHeadDim / 2];   // rope_on: (cos, sin) of the position
 };
 
 // Dynamic shared memory: the tile (16 warps x (12 K rows + 12 V rows) x 256 B; a warp parks its partial
@@ -137,6 +144,9 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   const int G = (n + 7) >> 3;
   const int gpb = sa_granules_per_block(n, static_cast<int>(CL));
   const int blk_first = cr * gpb;
+  // (rope_on: warps 2 and 3 form the position's cos / sin pairs; the block barriers of the cut phase order
+  // them before the query is rotated)
+  const bool rope_thread = p.rope_on && tid >= kHeadDim / 2 && tid < kHeadDim;
   const int blk_end = min(G, blk_first + gpb);
   const int g0 = blk_first + tid * ITEMS;
   const uint4* gbase = reinterpret_cast<const uint4*>(p.dist + static_cast<int64_t>(head) * p.dist_stride);
@@ -179,6 +189,7 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
     const unsigned pg = p.ps_shift >= 0 ? (un >> p.ps_shift) : (un / ps);
     tail_slot = static_cast<unsigned>(__ldg(kv_table + pg)) * ps + (un - pg * ps);
   }
+  if (rope_thread) sh.cs[tid - kHeadDim / 2] = rope_cos_sin(tid - kHeadDim / 2, static_cast<float>(n), p.rope);
   // ---- cut: one bin per thread ------------------------------------------------------------------------
   unsigned tot = 0, low = 0;
 #pragma unroll
@@ -332,7 +343,18 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
     }
   }
   if (tail_here && tid == 0 && n_win < p.list_capacity) s_list[n_win] = static_cast<int32_t>(tail_slot);
-  if (tid < 16) s_q[tid] = ld_16(static_cast<const T*>(p.q) + static_cast<int64_t>(head) * kHeadDim + tid * 8);
+  if (warp == 0) {
+    // the query row: 16 lanes x 16 bytes (with rope_on rotated first: dimension pairs sit in lanes l and l ^ 8)
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (lane < 16) raw = ld_16(static_cast<const T*>(p.q) + static_cast<int64_t>(head) * kHeadDim + lane * 8);
+    if (p.rope_on) {
+      float x[8];
+      unpack8<T>(raw, x);
+      rope_halfwarp_cs<T>(x, lane & 15, sh.cs, p.rope.inv_freq != nullptr, p.rope.mscale);
+      raw = pack8<T>(x);
+    }
+    if (lane < 16) s_q[lane] = raw;
+  }
 
   // ---- attend: every warp over its own rows --------------------------------------------------------------
   // The rows are dealt out evenly: warp w owns rows w*rpw .. of the list.  It gathers them itself, kSaWarpRows
@@ -503,6 +525,9 @@ __global__ void __launch_bounds__(kSaThreads, 2) select_attend_kernel(const Sele
   for (unsigned r = 0; r < kSaMaxSlices; ++r)
     if (r < CL) head_scratch[r * kSaBins + tid] = 0u;
   if (tid == 0) *counter = 0u;
+  // (every block of the head has read the un-rotated query long ago)
+  if (p.rope_on && tid < 16)
+    st_16(static_cast<T*>(const_cast<void*>(p.q)) + static_cast<int64_t>(head) * kHeadDim + tid * 8, s_q[tid]);
   if (tid >= kHeadDim) return;
   // all loads of the CL partials are issued before the first is used: one trip to L2
   float pm[kSaMaxSlices], pl[kSaMaxSlices], po[kSaMaxSlices];

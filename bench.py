@@ -167,9 +167,8 @@ def run_reference_arm(args):
 
 
 def two_launch_step(args) -> bool:
-    """decode_step folds the append into the estimate launch for 16, 32 or 64 heads that arrive rotated."""
-    return ((not args.unfused) and args.heads in (16, 32, 64) and not getattr(args, "yarn", 0.0)
-            and os.environ.get("ADAMAS_FUSED_APPEND", "1") != "0")
+    """decode_step folds the append (and a rotation) into the estimate launch for 16, 32 or 64 heads."""
+    return (not args.unfused) and args.heads in (16, 32, 64) and os.environ.get("ADAMAS_FUSED_APPEND", "1") != "0"
 
 
 def launches_per_layer(args) -> int:
@@ -242,7 +241,7 @@ class Workload:
         # hundreds of times would put hundreds of equal distances into one histogram bin per head, a pile of
         # same-address atomics that no real sequence produces.)
         # --yarn F: q and k arrive un-rotated and the step rotates them with a YaRN frequency table (factor F over
-        # an original context of 4096), which makes the append a launch of its own (three launches per layer)
+        # an original context of 4096)
         self.rope = None
         if getattr(args, "yarn", 0.0) > 0:
             from adamas_b200.rope import yarn_inv_freq
