@@ -575,8 +575,7 @@ def decode_step(q, k, v, o, q_code, kv_data, kv_indices, kv_last_page_len, kv_la
                 lse: Optional[torch.Tensor] = None, scale: Optional[float] = None, thresholds=None,
                 rope=None) -> None:
     """One layer's decode step in one call: append + estimate, select + attend (two launches for 16, 32
-    or 64 heads and already rotated q/k, else three, for what adamas/models/Adamas.py:145-200 does with
-    seven).  Needs context > budget.  `hist`: a histogram_scratch(H), all zero between steps.  With
+    or 64 heads, else three, for what adamas/models/Adamas.py:145-200 does with seven).  Needs context > budget.  `hist`: a histogram_scratch(H), all zero between steps.  With
     rope=(rope_scale, rope_theta) or {"inv_freq": tensor[64], "mscale": float} q and k arrive un-rotated
     and are rotated in place first.  q, o may have a multiple of k's heads (grouped-query attention)."""
     num_heads, head_dim, page_size = _check_append(k, v, kv_data, kv_indices, hadamard_data, hadamard_indices, NHD)

@@ -85,10 +85,11 @@ int adamas_device_error(unsigned* flags, int clear);
  * reference launches everything on the legacy default stream (e.g. adamas/ops/csrc/page.cu:99). */
 int adamas_set_pdl(int enable);
 
-/* Chooses how adamas_decode_step launches a step whose head count is 32 or 64 and whose q and k
- * are already rotated: with the append folded into the estimate launch (two launches; the default) or
- * as three launches (append, estimate, select+attend; ADAMAS_FUSED_APPEND=0 in the environment selects
- * it).  Results are identical.  No counterpart in the reference. */
+/* Chooses how the decode-step entry points launch a step of 16, 32 or 64 heads (multi-head attention):
+ * with the append, and the rotary embedding if one is asked for, folded into the estimate launch (two
+ * launches; the default) or as three launches (append, estimate, select+attend;
+ * ADAMAS_FUSED_APPEND=0 in the environment selects it).  Other head counts and grouped queries always
+ * take three.  Results are identical.  No counterpart in the reference. */
 int adamas_set_fused_append(int enable);
 
 /* How many blocks of the estimate kernel may be resident per SM: 2 (default; fastest for one sequence)

@@ -28,7 +28,7 @@ def _gather_cache(c, L, ps):
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("L0,ps,budget,H,rope,tokens", [
     (300, 16, 64, 32, None, 64),            # two-launch step
-    (300, 16, 64, 32, (8.0, 1e4), 64),      # three launches, rotary embedding inside the append
+    (300, 16, 64, 32, (8.0, 1e4), 64),      # rotary embedding inside the append-fused estimate
     (500, 1, 96, 16, None, 40),             # page size 1: a new page every token
     (2100, 16, 256, 4, (1.0, 1e4), 40),     # page-copy estimate (few heads)
     (32750, 16, 1024, 32, None, 40),        # crosses 32768 tokens: the row outgrows one granule per thread
