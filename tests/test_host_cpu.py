@@ -151,3 +151,26 @@ def test_kv_pool_reuses_lowest_page_first():
     assert kc.append_seq(0) == 0
     with pytest.raises(RuntimeError):
         kc.append_seq(100)
+
+
+def test_header_is_plain_c_and_a_c_program_links(tmp_path):
+    """include/adamas_b200.h compiles as C99 and a C program linked against the library sees the same
+    ABI version: the boundary needs neither C++ nor Python."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    from adamas_b200 import _lib
+    src = tmp_path / "abi_check.c"
+    src.write_text('#include "adamas_b200.h"\n'
+                   "int main(void) {\n"
+                   "  adamas_seq_desc_t d = {0, 0, 0, 0};\n"
+                   "  (void)d;\n"
+                   "  return adamas_abi_version() == ADAMAS_ABI_VERSION ? 0 : 1;\n"
+                   "}\n")
+    exe = tmp_path / "abi_check"
+    lib_dir = os.path.dirname(_lib.LIB_PATH)
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I", os.path.join(ROOT, "include"),
+                    str(src), "-o", str(exe), "-L", lib_dir, "-ladamas_b200", f"-Wl,-rpath,{lib_dir}"], check=True)
+    assert subprocess.run([str(exe)]).returncode == 0
