@@ -643,7 +643,7 @@ def run_ours(args):
     }
     if strong is not None:
         line["strong"] = strong
-    if not args.no_cpu and world >= 1:
+    if not args.no_cpu and world == 1:      # (the CPU baseline is a single-GPU-run figure)
         sec, n = time_cpu_reference(L, H, B, steps=60, warmup=2, budget_s=15.0)
         line["cpu_baseline"] = {
             "value": by["total"] / sec / 1e9, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
